@@ -1,0 +1,93 @@
+/*
+ * Flat C-ABI over the B200 (sm_100a) kernels of libggml-b200.so: plain pointers,
+ * sizes and ggml_type numbers, no ggml or torch types.  This is the layer a
+ * foreign-function binding (ctypes, cgo, JNI ...) would call; the ggml backend
+ * plugin declared in ggml-b200.h sits on the same kernels.
+ *
+ * Conventions
+ *  - `type` arguments are ggml_type values (ggml/include/ggml.h:351-392):
+ *    0 F32, 1 F16, 2 Q4_0, 3 Q4_1, 6 Q5_0, 7 Q5_1, 8 Q8_0, 12 Q4_K, 13 Q5_K, 14 Q6_K.
+ *  - Matrices use ggml's layout: a weight matrix W[K, M] is M rows of K values,
+ *    each row a run of quantized blocks (ggml/src/ggml-common.h:161-328);
+ *    activations X[K, N] are N contiguous F32 columns; dst[M, N] is N columns of M.
+ *  - Functions ending in `_host` take HOST pointers; they allocate device
+ *    memory, copy in, run the kernels on the current device and copy the result
+ *    back before returning.  All others take DEVICE pointers and are
+ *    asynchronous on `stream` (a cudaStream_t passed as void *).
+ *  - Return value: 0 on success, otherwise a cudaError_t value or a negative
+ *    B200_E_* code; b200_last_error() returns a message for the calling thread.
+ *  - Nothing here falls back to the CPU: without a B200 the calls fail.
+ */
+#ifndef B200_KERNELS_H
+#define B200_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_E_UNSUPPORTED  (-1)   /* type / shape not handled by the kernels */
+#define B200_E_BAD_ARG      (-2)
+#define B200_E_NO_DEVICE    (-3)   /* no sm_100 device visible */
+#define B200_E_SCRATCH      (-4)   /* scratch buffer too small */
+#define B200_E_DEVICE_WAIT  (-5)   /* a kernel gave up a bounded wait (status word set) */
+
+int          b200_device_count(void);      /* number of visible sm_100 devices (0 without a GPU) */
+const char * b200_last_error(void);
+size_t       b200_row_size(int type, int64_t k);   /* bytes of one row of k values; ggml_row_size, ggml/src/ggml.c:1204 */
+
+/* ---- MUL_MAT with quantized weights -------------------------------------
+ * dst[n][m] = sum_k W[m][k] * X[n][k], as GGML_OP_MUL_MAT computes it
+ * (ggml_mul_mat, ggml/src/ggml.c:2694-2709; CUDA path ggml_cuda_mul_mat,
+ * ggml/src/ggml-cuda/ggml-cuda.cu:1839-1900).  Activations are quantized to int8
+ * per 32 values on the device (the scratch buffer holds them), N <= 8 takes the
+ * bandwidth-bound mat-vec kernel, larger N the tensor-core kernel.            */
+size_t b200_mul_mat_q_scratch_bytes(int type, int64_t M, int64_t K, int64_t N);
+int    b200_mul_mat_q(int type, const void * W, int64_t w_row_stride_bytes, int64_t M, int64_t K,
+                      const float * X, int64_t x_col_stride_elems, int64_t N,
+                      float * dst, int64_t dst_col_stride_elems,
+                      void * scratch, size_t scratch_bytes, void * stream);
+int    b200_mul_mat_q_host(int type, const void * W, int64_t M, int64_t K, const float * X, int64_t N, float * dst);
+
+/* ---- FLASH_ATTN_EXT -------------------------------------------------------
+ * GGML_OP_FLASH_ATTN_EXT (ggml_flash_attn_ext, ggml/src/ggml.c:4306-4345; CPU
+ * semantics ggml/src/ggml-cpu/ggml-cpu.c:10916-11129).  q F32 [D, n_q, n_head],
+ * k/v F16 [D, n_kv, n_head_kv] with byte strides (token, head), mask F16
+ * [n_kv, >= n_q] contiguous or NULL, dst F32 [D, n_head, n_q].               */
+size_t b200_flash_attn_scratch_bytes(int64_t D, int64_t n_q, int64_t n_head, int64_t n_kv);
+int    b200_flash_attn(const float * q, int64_t q_nb1, int64_t q_nb2,
+                       const void * k, int64_t k_nb1, int64_t k_nb2,
+                       const void * v, int64_t v_nb1, int64_t v_nb2,
+                       const void * mask, int64_t mask_nb1, float * dst,
+                       int64_t D, int64_t n_q, int64_t n_head, int64_t n_kv, int64_t n_head_kv,
+                       float scale, float max_bias, float logit_softcap,
+                       void * scratch, size_t scratch_bytes, void * stream);
+int    b200_flash_attn_host(const float * q, const void * k, const void * v, const void * mask, float * dst,
+                            int64_t D, int64_t n_q, int64_t n_head, int64_t n_kv, int64_t n_head_kv,
+                            float scale, float max_bias, float logit_softcap);
+
+/* ---- bit-exact format conversions ----------------------------------------
+ * dequantize: what GET_ROWS / dequantize_row_* produce (ggml/src/ggml-quants.c:
+ * 255-363, 1280-1302, 1482-1507, 1690-1719).  quantize: what CPY F32 -> Q does,
+ * i.e. quantize_row_{q8_0,q4_0,q4_1,q5_0,q5_1}_ref (:31-217).  f32_to_f16: the
+ * KV-cache store (CPY F32 -> F16, round to nearest even).                     */
+int b200_dequantize_rows_host(int type, const void * src, int64_t n_rows, int64_t k, float * dst);
+int b200_get_rows_host(int type, const void * src, int64_t n_src_rows, int64_t k, const int32_t * idx, int64_t n_idx, float * dst);
+int b200_quantize_rows_host(int type, const float * src, int64_t n_rows, int64_t k, void * dst);
+int b200_f32_to_f16_host(const float * src, int64_t n, void * dst);
+
+/* ---- glue ops (host-buffer forms, used by the parity tests) --------------- */
+int b200_rms_norm_host(const float * x, int64_t n_rows, int64_t k, float eps, const float * weight /* [k] or NULL */, float * dst);
+int b200_rope_host(const float * x, int64_t head_dim, int64_t n_head, int64_t n_tok, const int32_t * pos,
+                   const float * freq_factors /* [n_dims/2] or NULL */, int n_dims, int mode, int n_ctx_orig,
+                   float freq_base, float freq_scale, float ext_factor, float attn_factor, float beta_fast, float beta_slow,
+                   float * dst);
+int b200_silu_mul_host(const float * gate, const float * up, int64_t n, float * dst);
+int b200_soft_max_host(const float * x, int64_t n_rows, int64_t k, const void * mask_f16 /* [k, n_rows] or NULL */, float scale, float * dst);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_KERNELS_H */

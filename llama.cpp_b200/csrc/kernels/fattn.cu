@@ -1,0 +1,217 @@
+// FLASH_ATTN_EXT over an F16 K/V cache (ggml_flash_attn_ext, ggml/src/ggml.c:4306-4345;
+// CPU semantics ggml/src/ggml-cpu/ggml-cpu.c:10916-11129):
+//
+//   O[d, h, q] = sum_k softmax_k( scale * K[k, h/g] . Q[q, h]  (softcap)  + slope_h * mask[q, k] ) * V[k, h/g][d]
+//
+// with Q F32 [D, n_q, n_head, n3], K/V F16 [D, n_kv, n_head_kv, n3] as arbitrary
+// strided views of the cache, mask F16 [n_kv, >= n_q] and dst F32 [D, n_head, n_q, n3].
+//
+// Split-KV ("flash decoding"): the KV range of one (query, head) is divided over
+// CTAs so that a single decode token at 32K context still fills every SM;
+// partial (max, sum, O) triples go to a workspace and are merged by a second
+// kernel.  Softmax statistics and the PV accumulation are FP32 (libllama asks for
+// GGML_PREC_F32 on this op, src/llama.cpp:595).
+#include "common.cuh"
+#include "kernels.h"
+#include <math.h>
+
+namespace b200 {
+
+static constexpr int FA_WARPS = 4;
+
+struct FaK {
+    const char * q; int64_t q_nb1, q_nb2, q_nb3;
+    const char * k; int64_t k_nb1, k_nb2, k_nb3;
+    const char * v; int64_t v_nb1, v_nb2, v_nb3;
+    const char * mask; int64_t m_nb1;
+    float * dst;
+    float * ws;               // [rows][n_splits][D + 2]
+    int n_q, n_kv, n_head, gqa, q3_per_k3;
+    int n_splits, kv_per_split;
+    float scale, softcap, max_bias, m0, m1; int n_head_log2;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FA_WARPS * 32) fattn_vec_kernel(const FaK p) {
+    constexpr int DPL = (D + 31) / 32;            // head-dim elements per lane
+    __shared__ float qs[D];
+    __shared__ float mg_m[FA_WARPS], mg_l[FA_WARPS];
+    __shared__ float mg_o[FA_WARPS][D];
+
+    const int split = blockIdx.x, head = blockIdx.y;
+    const int iq = blockIdx.z % p.n_q, i3 = blockIdx.z / p.n_q;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const float * qrow = (const float *) (p.q + (int64_t) iq * p.q_nb1 + (int64_t) head * p.q_nb2 + (int64_t) i3 * p.q_nb3);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = qrow[d];
+    __syncthreads();
+
+    const int hk = head / p.gqa, k3 = i3 / p.q3_per_k3;
+    const char * kbase = p.k + (int64_t) hk * p.k_nb2 + (int64_t) k3 * p.k_nb3;
+    const char * vbase = p.v + (int64_t) hk * p.v_nb2 + (int64_t) k3 * p.v_nb3;
+    const __half * mrow = p.mask ? (const __half *) (p.mask + (int64_t) iq * p.m_nb1) : nullptr;
+
+    float slope = 1.0f;
+    if (p.max_bias > 0.0f)
+        slope = head < p.n_head_log2 ? powf(p.m0, (float) (head + 1)) : powf(p.m1, (float) (2 * (head - p.n_head_log2) + 1));
+
+    const int kv0 = split * p.kv_per_split;
+    const int kv1 = min(p.n_kv, kv0 + p.kv_per_split);
+
+    float m = -INFINITY, l = 0.0f, o[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o[i] = 0.0f;
+
+    for (int base = kv0 + warp * 32; base < kv1; base += FA_WARPS * 32) {
+        const int j = base + lane;
+        float s = -INFINITY;
+        if (j < kv1) {
+            const float mv = mrow ? slope * __half2float(mrow[j]) : 0.0f;
+            if (mv != -INFINITY) {
+                const __half2 * kr = (const __half2 *) (kbase + (int64_t) j * p.k_nb1);
+                float acc = 0.0f;
+#pragma unroll 8
+                for (int d2 = 0; d2 < D / 2; ++d2) {
+                    const float2 kk = __half22float2(kr[d2]);
+                    acc += kk.x * qs[2 * d2] + kk.y * qs[2 * d2 + 1];
+                }
+                s = acc * p.scale;
+                if (p.softcap != 0.0f) s = p.softcap * tanhf(s);
+                s += mv;
+            }
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        if (m_new == -INFINITY) continue;         // everything so far is masked out
+        const float pj   = (s == -INFINITY) ? 0.0f : expf(s - m_new);
+        const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
+        l = l * corr + warp_sum(pj);
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) o[i] *= corr;
+        for (int jj = 0; jj < 32; ++jj) {
+            const float pp = __shfl_sync(0xffffffffu, pj, jj);
+            if (pp == 0.0f) continue;             // warp-uniform; also covers rows past kv1
+            const __half * vr = (const __half *) (vbase + (int64_t) (base + jj) * p.v_nb1);
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < D) o[i] += pp * __half2float(vr[d]);
+            }
+        }
+    }
+
+    // merge the warps of this CTA
+    if (lane == 0) { mg_m[warp] = m; mg_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) { const int d = lane + 32 * i; if (d < D) mg_o[warp][d] = o[i]; }
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; ++w) M = fmaxf(M, mg_m[w]);
+    float L = 0.0f;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; ++w) L += (mg_m[w] == -INFINITY) ? 0.0f : mg_l[w] * expf(mg_m[w] - M);
+
+    const int64_t row = ((int64_t) i3 * p.n_q + iq) * p.n_head + head;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < FA_WARPS; ++w) acc += (mg_m[w] == -INFINITY) ? 0.0f : mg_o[w][d] * expf(mg_m[w] - M);
+        if (p.n_splits == 1) p.dst[row * D + d] = acc / L;
+        else                 p.ws[(row * p.n_splits + split) * (D + 2) + d] = acc;
+    }
+    if (p.n_splits > 1 && threadIdx.x == 0) {
+        p.ws[(row * p.n_splits + split) * (D + 2) + D]     = M;
+        p.ws[(row * p.n_splits + split) * (D + 2) + D + 1] = L;
+    }
+}
+
+// merges the per-split partials of one (query, head) row
+template <int D>
+__global__ void fattn_combine_kernel(const float * __restrict__ ws, float * __restrict__ dst, int n_splits) {
+    const int64_t row = blockIdx.x;
+    const float * w = ws + row * n_splits * (D + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, w[s * (D + 2) + D]);
+    float L = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = w[s * (D + 2) + D];
+        L += (ms == -INFINITY) ? 0.0f : w[s * (D + 2) + D + 1] * expf(ms - M);
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = w[s * (D + 2) + D];
+            if (ms != -INFINITY) acc += w[s * (D + 2) + d] * expf(ms - M);
+        }
+        dst[row * D + d] = acc / L;
+    }
+}
+
+bool fattn_supported(int64_t D, int kt, int vt) {
+    if (kt != T_F16 || vt != T_F16) return false;
+    return D == 64 || D == 80 || D == 96 || D == 112 || D == 128 || D == 256;
+}
+
+static int fattn_pick_splits(int64_t rows, int64_t n_kv, int sm_count) {
+    // enough CTAs for ~4 per SM, at least 256 KV positions per CTA
+    int64_t want = ((int64_t) sm_count * 4 + rows - 1) / rows;
+    int64_t max_by_kv = (n_kv + 255) / 256;
+    int64_t s = want < max_by_kv ? want : max_by_kv;
+    if (s < 1) s = 1;
+    if (s > 128) s = 128;
+    return (int) s;
+}
+
+size_t fattn_workspace_bytes(const TensorD & q, const TensorD & k, int sm_count) {
+    const int64_t rows = q.ne[1] * q.ne[2] * q.ne[3];
+    const int splits = fattn_pick_splits(rows, k.ne[1], sm_count);
+    return splits > 1 ? (size_t) rows * splits * (q.ne[0] + 2) * sizeof(float) : 0;
+}
+
+template <int D>
+static cudaError_t fattn_launch_d(const FaK & p, int64_t rows, int n3, const LaunchCtx & c) {
+    dim3 grid((unsigned) p.n_splits, (unsigned) p.n_head, (unsigned) (p.n_q * n3));
+    fattn_vec_kernel<D><<<grid, FA_WARPS * 32, 0, c.stream>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (p.n_splits > 1) {
+        fattn_combine_kernel<D><<<(unsigned) rows, D >= 128 ? 128 : 64, 0, c.stream>>>(p.ws, p.dst, p.n_splits);
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
+                         const FattnParams & fp, void * workspace, const LaunchCtx & c) {
+    const int64_t D = q.ne[0], rows = q.ne[1] * q.ne[2] * q.ne[3];
+    if (rows == 0) return cudaSuccess;
+    FaK p = {};
+    p.q = (const char *) q.data; p.q_nb1 = q.nb[1]; p.q_nb2 = q.nb[2]; p.q_nb3 = q.nb[3];
+    p.k = (const char *) k.data; p.k_nb1 = k.nb[1]; p.k_nb2 = k.nb[2]; p.k_nb3 = k.nb[3];
+    p.v = (const char *) v.data; p.v_nb1 = v.nb[1]; p.v_nb2 = v.nb[2]; p.v_nb3 = v.nb[3];
+    p.mask = mask ? (const char *) mask->data : nullptr; p.m_nb1 = mask ? mask->nb[1] : 0;
+    p.dst = (float *) dst.data; p.ws = (float *) workspace;
+    p.n_q = (int) q.ne[1]; p.n_kv = (int) k.ne[1]; p.n_head = (int) q.ne[2];
+    p.gqa = (int) (q.ne[2] / k.ne[2]); p.q3_per_k3 = (int) (q.ne[3] / k.ne[3]);
+    p.n_splits = fattn_pick_splits(rows, k.ne[1], c.sm_count);
+    p.kv_per_split = (int) (((k.ne[1] + p.n_splits - 1) / p.n_splits + 31) / 32 * 32);
+    p.scale = fp.scale; p.softcap = fp.logit_softcap; p.max_bias = fp.max_bias;
+    if (p.softcap != 0.0f) p.scale /= p.softcap;
+    int nh2 = 1; while (nh2 * 2 <= p.n_head) nh2 *= 2;
+    p.n_head_log2 = nh2;
+    p.m0 = powf(2.0f, -fp.max_bias / (float) nh2);
+    p.m1 = powf(2.0f, -(fp.max_bias / 2.0f) / (float) nh2);
+    const int n3 = (int) q.ne[3];
+    switch (D) {
+        case 64:  return fattn_launch_d<64>(p, rows, n3, c);
+        case 80:  return fattn_launch_d<80>(p, rows, n3, c);
+        case 96:  return fattn_launch_d<96>(p, rows, n3, c);
+        case 112: return fattn_launch_d<112>(p, rows, n3, c);
+        case 128: return fattn_launch_d<128>(p, rows, n3, c);
+        case 256: return fattn_launch_d<256>(p, rows, n3, c);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace b200

@@ -1,0 +1,636 @@
+// Small row-wise / element-wise ops a Llama graph needs between the mat-muls so
+// that no node leaves the device: RMS_NORM, NORM, ADD/SUB/MUL/DIV with
+// broadcasting, unary activations, SCALE, CLAMP, ROPE (normal + NeoX, YaRN,
+// frequency factors), CPY/DUP/CONT with type conversion (incl. F32 -> Q8_0/Q4_0
+// for a quantized KV cache), GET_ROWS with on-the-fly dequantization, SOFT_MAX.
+//
+// Semantics follow the reference CPU ops (ggml/src/ggml-cpu/ggml-cpu.c:
+// rms_norm 7015, rope 9366, get_rows 8464, soft_max 8900ff, dup 3390ff) and the
+// behaviour of ggml/src/ggml-cuda/{norm,binbcast,unary,rope,cpy,getrows,softmax}.cu.
+// All of these are HBM-bound; they are fused where the graph allows
+// (rms_norm*weight, silu*up, both optionally emitting the int8 activation
+// blocks the following mat-vec consumes).
+#include "common.cuh"
+#include "kernels.h"
+#include <math.h>
+
+namespace b200 {
+
+#define B200_LAUNCH_CHECK() cudaGetLastError()
+
+__device__ __forceinline__ float block_sum(float v, float * sh /* >= 32 floats */) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    float r = (threadIdx.x < nw) ? sh[threadIdx.x] : 0.0f;
+    if (w == 0) { r = warp_sum(r); if (lane == 0) sh[0] = r; }
+    __syncthreads();
+    r = sh[0];
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float * sh) {
+    v = warp_max(v);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    float r = (threadIdx.x < nw) ? sh[threadIdx.x] : -INFINITY;
+    if (w == 0) { r = warp_max(r); if (lane == 0) sh[0] = r; }
+    __syncthreads();
+    r = sh[0];
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ float ld_f(const void * p, int type) {
+    if (type == T_F32) return *(const float *) p;
+    if (type == T_F16) return __half2float(*(const __half *) p);
+    return __bfloat162float(*(const __nv_bfloat16 *) p);
+}
+__device__ __forceinline__ void st_f(void * p, int type, float v) {
+    if (type == T_F32) *(float *) p = v;
+    else if (type == T_F16) *(__half *) p = __float2half(v);
+    else *(__nv_bfloat16 *) p = __float2bfloat16(v);
+}
+
+// quantize four values that are already scaled and write one blk_act128 group
+// (used by the fused producers below): each thread owns 4 consecutive values of
+// a row, 8 threads form one 32-value group
+__device__ __forceinline__ void emit_act128(const float (&v)[4], int64_t k0, int64_t K, blk_act128 * col) {
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d  = amax / 127.0f;
+    const float id = amax > 0.0f ? 127.0f / amax : 0.0f;
+    int q[4], qsum = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { q[i] = __float2int_rn(v[i] * id); qsum += q[i]; }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
+    if (k0 < K) {
+        blk_act128 * yb = col + (k0 >> 7);
+        const uint32_t packed = (uint32_t) (q[0] & 0xff) | ((uint32_t) (q[1] & 0xff) << 8) |
+                                ((uint32_t) (q[2] & 0xff) << 16) | ((uint32_t) (q[3] & 0xff) << 24);
+        ((uint32_t *) yb->q)[(k0 & 127) >> 2] = packed;
+        if (((k0 >> 2) & 7) == 0) yb->ds[(k0 & 127) >> 5] = make_float2(d, d * (float) qsum);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// RMS_NORM (+ optional weight multiply, + optional activation quantization)
+// ---------------------------------------------------------------------------
+template <bool HAS_W, bool EMIT>
+__global__ void rms_norm_kernel(const TensorD src, const TensorD w, const TensorD dst, float eps, blk_act128 * act) {
+    __shared__ float sh[32];
+    const int64_t row = blockIdx.x;
+    const int64_t i1 = row % src.ne[1], i2 = (row / src.ne[1]) % src.ne[2], i3 = row / (src.ne[1] * src.ne[2]);
+    const float * x = (const float *) ((const char *) src.data + i1 * src.nb[1] + i2 * src.nb[2] + i3 * src.nb[3]);
+    float *       y = (float *) ((char *) dst.data + i1 * dst.nb[1] + i2 * dst.nb[2] + i3 * dst.nb[3]);
+    const int64_t n = src.ne[0];
+    float ss = 0.0f;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = x[i]; ss += v * v; }
+    ss = block_sum(ss, sh);
+    const float scale = rsqrtf(ss / (float) n + eps);
+    const float * wr = nullptr;
+    if (HAS_W) wr = (const float *) ((const char *) w.data + (i1 % w.ne[1]) * w.nb[1] + (i2 % w.ne[2]) * w.nb[2] + (i3 % w.ne[3]) * w.nb[3]);
+    if (!EMIT) {
+        for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+            float v = x[i] * scale;
+            if (HAS_W) v *= wr[i % w.ne[0]];
+            y[i] = v;
+        }
+    } else {
+        // 4 consecutive values per thread so that 8 threads cover one 32-value group
+        const int64_t npad = (n + 127) & ~(int64_t) 127;
+        blk_act128 * col = act + row * (npad >> 7);
+        for (int64_t k0 = (int64_t) threadIdx.x * 4; k0 < npad; k0 += (int64_t) blockDim.x * 4) {
+            float v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[i] = 0.0f;
+                if (k0 + i < n) {
+                    v[i] = x[k0 + i] * scale;
+                    if (HAS_W) v[i] *= wr[(k0 + i) % w.ne[0]];
+                    y[k0 + i] = v[i];
+                }
+            }
+            emit_act128(v, k0, npad, col);
+        }
+    }
+}
+
+static int row_block(int64_t n) { return n >= 4096 ? 1024 : (n >= 1024 ? 512 : (n >= 256 ? 256 : 128)); }
+
+cudaError_t launch_rms_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c) {
+    const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
+    if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
+    rms_norm_kernel<false, false><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, src, dst, eps, nullptr);
+    return B200_LAUNCH_CHECK();
+}
+cudaError_t launch_rms_norm_mul(const TensorD & src, const TensorD & w, const TensorD & dst, float eps, void * act, const LaunchCtx & c) {
+    const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
+    if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
+    if (act) rms_norm_kernel<true, true><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, w, dst, eps, (blk_act128 *) act);
+    else     rms_norm_kernel<true, false><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, w, dst, eps, nullptr);
+    return B200_LAUNCH_CHECK();
+}
+
+// NORM: (x - mean) / sqrt(var + eps)
+__global__ void norm_kernel(const TensorD src, const TensorD dst, float eps) {
+    __shared__ float sh[32];
+    const int64_t row = blockIdx.x;
+    const int64_t i1 = row % src.ne[1], i2 = (row / src.ne[1]) % src.ne[2], i3 = row / (src.ne[1] * src.ne[2]);
+    const float * x = (const float *) ((const char *) src.data + i1 * src.nb[1] + i2 * src.nb[2] + i3 * src.nb[3]);
+    float *       y = (float *) ((char *) dst.data + i1 * dst.nb[1] + i2 * dst.nb[2] + i3 * dst.nb[3]);
+    const int64_t n = src.ne[0];
+    float s = 0.0f;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) s += x[i];
+    const float mean = block_sum(s, sh) / (float) n;
+    float v2 = 0.0f;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float d = x[i] - mean; v2 += d * d; }
+    const float var = block_sum(v2, sh) / (float) n;
+    const float scale = rsqrtf(var + eps);
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) y[i] = (x[i] - mean) * scale;
+}
+cudaError_t launch_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c) {
+    const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
+    if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
+    norm_kernel<<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, dst, eps);
+    return B200_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// broadcasting binary ops
+// ---------------------------------------------------------------------------
+template <int OP> __device__ __forceinline__ float bin_apply(float a, float b) {
+    if (OP == BIN_ADD) return a + b;
+    if (OP == BIN_SUB) return a - b;
+    if (OP == BIN_MUL) return a * b;
+    return a / b;
+}
+
+template <int OP>
+__global__ void bin_bcast_kernel(const TensorD a, const TensorD b, const TensorD d, int64_t total) {
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
+        const int64_t i0 = i % d.ne[0], r1 = i / d.ne[0];
+        const int64_t i1 = r1 % d.ne[1], r2 = r1 / d.ne[1];
+        const int64_t i2 = r2 % d.ne[2], i3 = r2 / d.ne[2];
+        const char * pa = (const char *) a.data + (i0 % a.ne[0]) * a.nb[0] + (i1 % a.ne[1]) * a.nb[1] + (i2 % a.ne[2]) * a.nb[2] + (i3 % a.ne[3]) * a.nb[3];
+        const char * pb = (const char *) b.data + (i0 % b.ne[0]) * b.nb[0] + (i1 % b.ne[1]) * b.nb[1] + (i2 % b.ne[2]) * b.nb[2] + (i3 % b.ne[3]) * b.nb[3];
+        char *       pd = (char *) d.data + i0 * d.nb[0] + i1 * d.nb[1] + i2 * d.nb[2] + i3 * d.nb[3];
+        st_f(pd, d.type, bin_apply<OP>(ld_f(pa, a.type), ld_f(pb, b.type)));
+    }
+}
+
+// fast path: all F32, a and dst contiguous with identical shape, b contiguous with
+// shape either identical or a single row [ne0]; 4 elements per thread
+template <int OP>
+__global__ void bin_fast_kernel(const float4 * __restrict__ a, const float4 * __restrict__ b, float4 * __restrict__ d,
+                                int64_t n4, int64_t b_n4 /* elements/4 of b (row or full) */) {
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t) gridDim.x * blockDim.x) {
+        const float4 x = a[i], y = b[i % b_n4];
+        d[i] = make_float4(bin_apply<OP>(x.x, y.x), bin_apply<OP>(x.y, y.y), bin_apply<OP>(x.z, y.z), bin_apply<OP>(x.w, y.w));
+    }
+}
+
+static bool is_contig(const TensorD & t) {
+    int64_t s = type_block_bytes(t.type);
+    if (type_block_elems(t.type) != 1) return false;
+    for (int i = 0; i < 4; ++i) { if (t.ne[i] != 1 && t.nb[i] != s) return false; s *= t.ne[i]; }
+    return true;
+}
+static int64_t nelem(const TensorD & t) { return t.ne[0] * t.ne[1] * t.ne[2] * t.ne[3]; }
+static unsigned grid_for(int64_t n, int block, int sm) {
+    int64_t g = (n + block - 1) / block;
+    const int64_t cap = (int64_t) sm * 16;
+    if (g > cap) g = cap;
+    return (unsigned) (g < 1 ? 1 : g);
+}
+
+template <int OP>
+static cudaError_t bin_dispatch(const TensorD & a, const TensorD & b, const TensorD & d, const LaunchCtx & c) {
+    const int64_t total = nelem(d);
+    if (total == 0) return cudaSuccess;
+    const bool f32 = a.type == T_F32 && b.type == T_F32 && d.type == T_F32;
+    bool same_a = true;
+    for (int i = 0; i < 4; ++i) same_a = same_a && a.ne[i] == d.ne[i];
+    const int64_t nb_ = nelem(b);
+    const bool b_full = nb_ == total, b_row = nb_ == b.ne[0] && b.ne[0] == d.ne[0];
+    if (f32 && same_a && is_contig(a) && is_contig(b) && is_contig(d) && (b_full || b_row) && d.ne[0] % 4 == 0 &&
+        ((uintptr_t) a.data % 16 == 0) && ((uintptr_t) b.data % 16 == 0) && ((uintptr_t) d.data % 16 == 0)) {
+        bool same_b = true;
+        if (b_full) for (int i = 0; i < 4; ++i) same_b = same_b && b.ne[i] == d.ne[i];
+        if (same_b) {
+            bin_fast_kernel<OP><<<grid_for(total / 4, 256, c.sm_count), 256, 0, c.stream>>>(
+                (const float4 *) a.data, (const float4 *) b.data, (float4 *) d.data, total / 4, nb_ / 4);
+            return B200_LAUNCH_CHECK();
+        }
+    }
+    bin_bcast_kernel<OP><<<grid_for(total, 256, c.sm_count), 256, 0, c.stream>>>(a, b, d, total);
+    return B200_LAUNCH_CHECK();
+}
+
+cudaError_t launch_bin_bcast(int op, const TensorD & a, const TensorD & b, const TensorD & d, const LaunchCtx & c) {
+    switch (op) {
+        case BIN_ADD: return bin_dispatch<BIN_ADD>(a, b, d, c);
+        case BIN_SUB: return bin_dispatch<BIN_SUB>(a, b, d, c);
+        case BIN_MUL: return bin_dispatch<BIN_MUL>(a, b, d, c);
+        case BIN_DIV: return bin_dispatch<BIN_DIV>(a, b, d, c);
+    }
+    return cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------------------
+// unary ops (contiguous F32)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float un_apply(int op, float x) {
+    switch (op) {
+        case UN_SILU:        return x / (1.0f + expf(-x));
+        case UN_GELU:        return 0.5f * x * (1.0f + tanhf(0.79788456080286535587989211986876f * x * (1.0f + 0.044715f * x * x)));
+        case UN_GELU_QUICK:  return x * (1.0f / (1.0f + expf(-1.702f * x)));
+        case UN_RELU:        return fmaxf(x, 0.0f);
+        case UN_TANH:        return tanhf(x);
+        case UN_SIGMOID:     return 1.0f / (1.0f + expf(-x));
+        case UN_NEG:         return -x;
+        case UN_EXP:         return expf(x);
+        case UN_ABS:         return fabsf(x);
+        case UN_SGN:         return x > 0.0f ? 1.0f : (x < 0.0f ? -1.0f : 0.0f);
+        case UN_STEP:        return x > 0.0f ? 1.0f : 0.0f;
+        case UN_ELU:         return x > 0.0f ? x : expm1f(x);
+        case UN_HARDSIGMOID: return fminf(1.0f, fmaxf(0.0f, (x + 3.0f) / 6.0f));
+        case UN_HARDSWISH:   return x * fminf(1.0f, fmaxf(0.0f, (x + 3.0f) / 6.0f));
+        case UN_SQR:         return x * x;
+        case UN_SQRT:        return sqrtf(x);
+        case UN_SIN:         return sinf(x);
+        case UN_COS:         return cosf(x);
+        case UN_LOG:         return logf(x);
+    }
+    return x;
+}
+__global__ void unary_kernel(int op, const float * __restrict__ x, float * __restrict__ y, int64_t n) {
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) y[i] = un_apply(op, x[i]);
+}
+cudaError_t launch_unary(int op, const TensorD & src, const TensorD & dst, const LaunchCtx & c) {
+    const int64_t n = nelem(src);
+    if (n == 0) return cudaSuccess;
+    unary_kernel<<<grid_for(n, 256, c.sm_count), 256, 0, c.stream>>>(op, (const float *) src.data, (float *) dst.data, n);
+    return B200_LAUNCH_CHECK();
+}
+
+__global__ void scale_kernel(const float * __restrict__ x, float * __restrict__ y, float s, int64_t n) {
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) y[i] = x[i] * s;
+}
+cudaError_t launch_scale(const TensorD & src, const TensorD & dst, float s, const LaunchCtx & c) {
+    const int64_t n = nelem(src);
+    if (n == 0) return cudaSuccess;
+    scale_kernel<<<grid_for(n, 256, c.sm_count), 256, 0, c.stream>>>((const float *) src.data, (float *) dst.data, s, n);
+    return B200_LAUNCH_CHECK();
+}
+__global__ void clamp_kernel(const float * __restrict__ x, float * __restrict__ y, float lo, float hi, int64_t n) {
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) y[i] = fminf(fmaxf(x[i], lo), hi);
+}
+cudaError_t launch_clamp(const TensorD & src, const TensorD & dst, float lo, float hi, const LaunchCtx & c) {
+    const int64_t n = nelem(src);
+    if (n == 0) return cudaSuccess;
+    clamp_kernel<<<grid_for(n, 256, c.sm_count), 256, 0, c.stream>>>((const float *) src.data, (float *) dst.data, lo, hi, n);
+    return B200_LAUNCH_CHECK();
+}
+
+// silu(gate) * up on contiguous F32 rows, optionally emitting activation blocks
+template <bool EMIT>
+__global__ void silu_mul_kernel(const float * __restrict__ g, const float * __restrict__ u, float * __restrict__ y,
+                                int64_t n0, int64_t rows, blk_act128 * act) {
+    const int64_t npad = (n0 + 127) & ~(int64_t) 127;
+    const int64_t per_row = npad / 4;
+    const int64_t total = per_row * rows;
+    // whole warps stay together (emit_act128 shuffles), so loop bounds are warp-uniform
+    const int64_t total_w = (total + 31) & ~(int64_t) 31;
+    for (int64_t t = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; t < total_w; t += (int64_t) gridDim.x * blockDim.x) {
+        const int64_t row = t / per_row, k0 = (t % per_row) * 4;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (t < total) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (k0 + i < n0) {
+                    const float a = g[row * n0 + k0 + i];
+                    v[i] = (a / (1.0f + expf(-a))) * u[row * n0 + k0 + i];
+                    y[row * n0 + k0 + i] = v[i];
+                }
+            }
+        }
+        if (EMIT) emit_act128(v, t < total ? k0 : npad, npad, act + (t < total ? row : 0) * (npad >> 7));
+    }
+}
+cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const TensorD & dst, void * act, const LaunchCtx & c) {
+    const int64_t n0 = gate.ne[0], rows = nelem(gate) / (n0 ? n0 : 1);
+    if (n0 == 0 || rows == 0) return cudaSuccess;
+    const int64_t threads = ((n0 + 127) / 128 * 32) * rows;
+    if (act) silu_mul_kernel<true><<<grid_for(threads, 256, c.sm_count), 256, 0, c.stream>>>(
+                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, (blk_act128 *) act);
+    else     silu_mul_kernel<false><<<grid_for(threads, 256, c.sm_count), 256, 0, c.stream>>>(
+                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, nullptr);
+    return B200_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// ROPE
+// ---------------------------------------------------------------------------
+struct RopeK {
+    int n_dims, neox;
+    float freq_scale, ext_factor, attn_factor, theta_scale, corr0, corr1;
+};
+__device__ __forceinline__ void rope_cs(const RopeK & r, float theta_extrap, int i0, float & c, float & s) {
+    // YaRN mix of interpolated and extrapolated angles (ggml-cpu.c:9275-9306)
+    const float theta_interp = r.freq_scale * theta_extrap;
+    float theta = theta_interp, mscale = r.attn_factor;
+    if (r.ext_factor != 0.0f) {
+        const float y = ((float) (i0 / 2) - r.corr0) / fmaxf(0.001f, r.corr1 - r.corr0);
+        const float ramp_mix = (1.0f - fminf(1.0f, fmaxf(0.0f, y))) * r.ext_factor;
+        theta = theta_interp * (1.0f - ramp_mix) + theta_extrap * ramp_mix;
+        mscale *= 1.0f + 0.1f * logf(1.0f / r.freq_scale);
+    }
+    c = cosf(theta) * mscale;
+    s = sinf(theta) * mscale;
+}
+template <typename T>
+__global__ void rope_kernel(const TensorD src, const int32_t * __restrict__ pos, const float * __restrict__ ff,
+                            const TensorD dst, const RopeK r, int64_t total_pairs) {
+    const int64_t half0 = src.ne[0] / 2;
+    for (int64_t t = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; t < total_pairs; t += (int64_t) gridDim.x * blockDim.x) {
+        const int64_t ip = t % half0, r1 = t / half0;
+        const int64_t i1 = r1 % src.ne[1], r2 = r1 / src.ne[1];
+        const int64_t i2 = r2 % src.ne[2], i3 = r2 / src.ne[2];
+        const char * xs = (const char *) src.data + i1 * src.nb[1] + i2 * src.nb[2] + i3 * src.nb[3];
+        char *       yd = (char *) dst.data + i1 * dst.nb[1] + i2 * dst.nb[2] + i3 * dst.nb[3];
+        const int i0 = (int) (2 * ip);
+        if (i0 >= r.n_dims) {
+            ((T *) yd)[i0] = ((const T *) xs)[i0];
+            ((T *) yd)[i0 + 1] = ((const T *) xs)[i0 + 1];
+            continue;
+        }
+        const float theta_base = (float) pos[i2] * powf(r.theta_scale, (float) ip);
+        const float f = ff ? ff[ip] : 1.0f;
+        float c, s;
+        rope_cs(r, theta_base / f, i0, c, s);
+        const int64_t ia = r.neox ? ip : i0, ib = r.neox ? ip + r.n_dims / 2 : i0 + 1;
+        const float x0 = (float) ((const T *) xs)[ia], x1 = (float) ((const T *) xs)[ib];
+        ((T *) yd)[ia] = (T) (x0 * c - x1 * s);
+        ((T *) yd)[ib] = (T) (x0 * s + x1 * c);
+    }
+}
+cudaError_t launch_rope(const TensorD & src, const int32_t * pos, const float * ff, const TensorD & dst,
+                        const RopeParams & rp, const LaunchCtx & c) {
+    const int64_t total = nelem(src) / 2;
+    if (total == 0) return cudaSuccess;
+    RopeK r;
+    r.n_dims = rp.n_dims; r.neox = (rp.mode & 2) ? 1 : 0;
+    r.freq_scale = rp.freq_scale; r.ext_factor = rp.ext_factor; r.attn_factor = rp.attn_factor;
+    r.theta_scale = powf(rp.freq_base, -2.0f / (float) rp.n_dims);
+    // correction range of YaRN (ggml_rope_yarn_corr_dims, ggml/src/ggml.c)
+    auto corr_dim = [&](float n_rot) {
+        return (float) rp.n_dims * logf((float) rp.n_ctx_orig / (n_rot * 2.0f * 3.14159265358979323846f)) / (2.0f * logf(rp.freq_base));
+    };
+    const float start = floorf(corr_dim(rp.beta_fast)), end = ceilf(corr_dim(rp.beta_slow));
+    r.corr0 = fmaxf(0.0f, start);
+    r.corr1 = fminf((float) rp.n_dims - 1.0f, end);
+    if (src.type == T_F32)      rope_kernel<float><<<grid_for(total, 256, c.sm_count), 256, 0, c.stream>>>(src, pos, ff, dst, r, total);
+    else if (src.type == T_F16) rope_kernel<__half><<<grid_for(total, 256, c.sm_count), 256, 0, c.stream>>>(src, pos, ff, dst, r, total);
+    else return cudaErrorInvalidValue;
+    return B200_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// CPY / DUP / CONT
+// ---------------------------------------------------------------------------
+__global__ void cpy_elem_kernel(const TensorD s, const TensorD d, int64_t total) {
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
+        int64_t r = i;
+        const int64_t s0 = r % s.ne[0]; r /= s.ne[0];
+        const int64_t s1 = r % s.ne[1]; r /= s.ne[1];
+        const int64_t s2 = r % s.ne[2]; const int64_t s3 = r / s.ne[2];
+        r = i;
+        const int64_t d0 = r % d.ne[0]; r /= d.ne[0];
+        const int64_t d1 = r % d.ne[1]; r /= d.ne[1];
+        const int64_t d2 = r % d.ne[2]; const int64_t d3 = r / d.ne[2];
+        const char * ps = (const char *) s.data + s0 * s.nb[0] + s1 * s.nb[1] + s2 * s.nb[2] + s3 * s.nb[3];
+        char *       pd = (char *) d.data + d0 * d.nb[0] + d1 * d.nb[1] + d2 * d.nb[2] + d3 * d.nb[3];
+        if (s.type == d.type) {
+            if (s.type == T_F32 || s.type == T_I32) *(uint32_t *) pd = *(const uint32_t *) ps;
+            else *(uint16_t *) pd = *(const uint16_t *) ps;
+        } else {
+            st_f(pd, d.type, ld_f(ps, s.type));
+        }
+    }
+}
+
+// F32 -> quantized block (32 values): one thread per block, restating
+// quantize_row_q8_0_ref / q4_0_ref / q4_1_ref / q5_0_ref / q5_1_ref
+// (ggml/src/ggml-quants.c:31-217) operation by operation (no fused multiply-add)
+template <int QT>
+__device__ void quantize_block32(const float * x, uint8_t * out) {
+    if (QT == T_Q8_0) {
+        float amax = 0.0f;
+        for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(x[j]));
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float id = d ? __fdiv_rn(1.0f, d) : 0.0f;
+        blk_q8_0 * b = (blk_q8_0 *) out;
+        b->d = __half_as_ushort(__float2half_rn(d));
+        for (int j = 0; j < 32; ++j) b->qs[j] = (int8_t) roundf(__fmul_rn(x[j], id));
+    } else if (QT == T_Q4_0 || QT == T_Q5_0) {
+        float amax = 0.0f, mx = 0.0f;
+        for (int j = 0; j < 32; ++j) { const float v = x[j]; if (amax < fabsf(v)) { amax = fabsf(v); mx = v; } }
+        const float d = __fdiv_rn(mx, QT == T_Q4_0 ? -8.0f : -16.0f);
+        const float id = d ? __fdiv_rn(1.0f, d) : 0.0f;
+        if (QT == T_Q4_0) {
+            blk_q4_0 * b = (blk_q4_0 *) out;
+            b->d = __half_as_ushort(__float2half_rn(d));
+            for (int j = 0; j < 16; ++j) {
+                const float x0 = __fmul_rn(x[j], id), x1 = __fmul_rn(x[16 + j], id);
+                const uint8_t q0 = (uint8_t) min(15, (int) (int8_t) __fadd_rn(x0, 8.5f));
+                const uint8_t q1 = (uint8_t) min(15, (int) (int8_t) __fadd_rn(x1, 8.5f));
+                b->qs[j] = q0 | (q1 << 4);
+            }
+        } else {
+            blk_q5_0 * b = (blk_q5_0 *) out;
+            b->d = __half_as_ushort(__float2half_rn(d));
+            uint32_t qh = 0;
+            for (int j = 0; j < 16; ++j) {
+                const float x0 = __fmul_rn(x[j], id), x1 = __fmul_rn(x[16 + j], id);
+                const uint8_t q0 = (uint8_t) min(31, (int) (int8_t) __fadd_rn(x0, 16.5f));
+                const uint8_t q1 = (uint8_t) min(31, (int) (int8_t) __fadd_rn(x1, 16.5f));
+                b->qs[j] = (q0 & 0x0F) | ((q1 & 0x0F) << 4);
+                qh |= ((q0 & 0x10u) >> 4) << (j + 0);
+                qh |= ((q1 & 0x10u) >> 4) << (j + 16);
+            }
+            b->qh[0] = qh & 0xff; b->qh[1] = (qh >> 8) & 0xff; b->qh[2] = (qh >> 16) & 0xff; b->qh[3] = (qh >> 24) & 0xff;
+        }
+    } else {   // Q4_1 / Q5_1
+        float mn = INFINITY, mx = -INFINITY;
+        for (int j = 0; j < 32; ++j) { mn = fminf(mn, x[j]); mx = fmaxf(mx, x[j]); }
+        const int levels = QT == T_Q4_1 ? 15 : 31;
+        const float d = __fdiv_rn(__fsub_rn(mx, mn), (float) levels);
+        const float id = d ? __fdiv_rn(1.0f, d) : 0.0f;
+        if (QT == T_Q4_1) {
+            blk_q4_1 * b = (blk_q4_1 *) out;
+            b->d = __half_as_ushort(__float2half_rn(d)); b->m = __half_as_ushort(__float2half_rn(mn));
+            for (int j = 0; j < 16; ++j) {
+                const float x0 = __fmul_rn(__fsub_rn(x[j], mn), id), x1 = __fmul_rn(__fsub_rn(x[16 + j], mn), id);
+                const uint8_t q0 = (uint8_t) min(15, (int) (int8_t) __fadd_rn(x0, 0.5f));
+                const uint8_t q1 = (uint8_t) min(15, (int) (int8_t) __fadd_rn(x1, 0.5f));
+                b->qs[j] = q0 | (q1 << 4);
+            }
+        } else {
+            blk_q5_1 * b = (blk_q5_1 *) out;
+            b->d = __half_as_ushort(__float2half_rn(d)); b->m = __half_as_ushort(__float2half_rn(mn));
+            uint32_t qh = 0;
+            for (int j = 0; j < 16; ++j) {
+                const float x0 = __fmul_rn(__fsub_rn(x[j], mn), id), x1 = __fmul_rn(__fsub_rn(x[16 + j], mn), id);
+                const uint8_t q0 = (uint8_t) (int8_t) __fadd_rn(x0, 0.5f);
+                const uint8_t q1 = (uint8_t) (int8_t) __fadd_rn(x1, 0.5f);
+                b->qs[j] = (q0 & 0x0F) | ((q1 & 0x0F) << 4);
+                qh |= ((q0 & 0x10u) >> 4) << (j + 0);
+                qh |= ((q1 & 0x10u) >> 4) << (j + 16);
+            }
+            b->qh[0] = qh & 0xff; b->qh[1] = (qh >> 8) & 0xff; b->qh[2] = (qh >> 16) & 0xff; b->qh[3] = (qh >> 24) & 0xff;
+        }
+    }
+}
+
+template <int QT>
+__global__ void cpy_f32_q_kernel(const TensorD s, const TensorD d, int64_t nblocks) {
+    const int bb = type_block_bytes(QT);
+    for (int64_t ib = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; ib < nblocks; ib += (int64_t) gridDim.x * blockDim.x) {
+        // element index of the first value of this block, in src order
+        int64_t r = ib * 32;
+        const int64_t s0 = r % s.ne[0]; r /= s.ne[0];
+        const int64_t s1 = r % s.ne[1]; r /= s.ne[1];
+        const int64_t s2 = r % s.ne[2]; const int64_t s3 = r / s.ne[2];
+        r = ib * 32;
+        const int64_t d0 = r % d.ne[0]; r /= d.ne[0];
+        const int64_t d1 = r % d.ne[1]; r /= d.ne[1];
+        const int64_t d2 = r % d.ne[2]; const int64_t d3 = r / d.ne[2];
+        const char * ps = (const char *) s.data + s0 * s.nb[0] + s1 * s.nb[1] + s2 * s.nb[2] + s3 * s.nb[3];
+        char *       pd = (char *) d.data + (d0 / 32) * bb + d1 * d.nb[1] + d2 * d.nb[2] + d3 * d.nb[3];
+        float v[32];
+        for (int j = 0; j < 32; ++j) v[j] = *(const float *) (ps + j * s.nb[0]);
+        quantize_block32<QT>(v, (uint8_t *) pd);
+    }
+}
+
+bool cpy_supported(int st, int dt) {
+    auto flt = [](int t) { return t == T_F32 || t == T_F16 || t == T_BF16; };
+    if (flt(st) && flt(dt)) return true;
+    if (st == T_I32 && dt == T_I32) return true;
+    if (st == T_F32 && (dt == T_Q8_0 || dt == T_Q4_0 || dt == T_Q4_1 || dt == T_Q5_0 || dt == T_Q5_1)) return true;
+    return false;
+}
+
+cudaError_t launch_cpy(const TensorD & s, const TensorD & d, const LaunchCtx & c) {
+    const int64_t total = nelem(s);
+    if (total == 0) return cudaSuccess;
+    if (type_block_elems(d.type) == 32) {
+        const int64_t nb = total / 32;
+        const unsigned g = grid_for(nb, 128, c.sm_count);
+        switch (d.type) {
+            case T_Q8_0: cpy_f32_q_kernel<T_Q8_0><<<g, 128, 0, c.stream>>>(s, d, nb); break;
+            case T_Q4_0: cpy_f32_q_kernel<T_Q4_0><<<g, 128, 0, c.stream>>>(s, d, nb); break;
+            case T_Q4_1: cpy_f32_q_kernel<T_Q4_1><<<g, 128, 0, c.stream>>>(s, d, nb); break;
+            case T_Q5_0: cpy_f32_q_kernel<T_Q5_0><<<g, 128, 0, c.stream>>>(s, d, nb); break;
+            case T_Q5_1: cpy_f32_q_kernel<T_Q5_1><<<g, 128, 0, c.stream>>>(s, d, nb); break;
+            default: return cudaErrorInvalidValue;
+        }
+        return B200_LAUNCH_CHECK();
+    }
+    cpy_elem_kernel<<<grid_for(total, 256, c.sm_count), 256, 0, c.stream>>>(s, d, total);
+    return B200_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// GET_ROWS
+// ---------------------------------------------------------------------------
+template <int T>
+__global__ void get_rows_kernel(const TensorD src, const TensorD idx, const TensorD dst) {
+    // grid: x over chunks of the row, y = index position, z = batch (i11 + i12*ne11)
+    const int64_t i10 = blockIdx.y;
+    const int64_t i11 = blockIdx.z % idx.ne[1], i12 = blockIdx.z / idx.ne[1];
+    const int32_t row = *(const int32_t *) ((const char *) idx.data + i10 * idx.nb[0] + i11 * idx.nb[1] + i12 * idx.nb[2]);
+    const uint8_t * sr = (const uint8_t *) src.data + (int64_t) row * src.nb[1] + i11 * src.nb[2] + i12 * src.nb[3];
+    float * dr = (float *) ((char *) dst.data + i10 * dst.nb[1] + i11 * dst.nb[2] + i12 * dst.nb[3]);
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < src.ne[0]; i += (int64_t) gridDim.x * blockDim.x)
+        dr[i] = dequant_elem<T>(sr, i);
+}
+bool get_rows_supported(int t) {
+    switch (t) {
+        case T_F32: case T_F16: case T_BF16: case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0:
+        case T_Q4_K: case T_Q5_K: case T_Q6_K: return true;
+        default: return false;
+    }
+}
+cudaError_t launch_get_rows(const TensorD & src, const TensorD & idx, const TensorD & dst, const LaunchCtx & c) {
+    if (nelem(dst) == 0) return cudaSuccess;
+    const int block = 256;
+    int64_t gx = (src.ne[0] + block - 1) / block; if (gx > 64) gx = 64;
+    dim3 grid((unsigned) gx, (unsigned) idx.ne[0], (unsigned) (idx.ne[1] * idx.ne[2]));
+#define GR(T) case T: get_rows_kernel<T><<<grid, block, 0, c.stream>>>(src, idx, dst); break;
+    switch (src.type) {
+        GR(T_F32) GR(T_F16) GR(T_BF16) GR(T_Q4_0) GR(T_Q4_1) GR(T_Q5_0) GR(T_Q5_1) GR(T_Q8_0) GR(T_Q4_K) GR(T_Q5_K) GR(T_Q6_K)
+        default: return cudaErrorInvalidValue;
+    }
+#undef GR
+    return B200_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// SOFT_MAX: y = softmax(x*scale + slope(head)*mask) per row
+// ---------------------------------------------------------------------------
+__global__ void soft_max_kernel(const TensorD src, const TensorD mask, int has_mask, const TensorD dst,
+                                float scale, float max_bias, float m0, float m1, int n_head_log2) {
+    extern __shared__ float row_cache[];
+    __shared__ float sh[32];
+    const int64_t row = blockIdx.x;
+    const int64_t ne0 = src.ne[0], ne1 = src.ne[1];
+    const int64_t i1 = row % ne1, h = (row / ne1) % src.ne[2];
+    const float * x = (const float *) src.data + row * ne0;
+    float *       y = (float *) dst.data + row * ne0;
+    float slope = 1.0f;
+    if (max_bias > 0.0f) slope = h < n_head_log2 ? powf(m0, (float) (h + 1)) : powf(m1, (float) (2 * (h - n_head_log2) + 1));
+    const char * mrow = has_mask ? (const char *) mask.data + i1 * mask.nb[1] : nullptr;
+    float mx = -INFINITY;
+    for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) {
+        float v = x[i] * scale;
+        if (has_mask) v += slope * ld_f(mrow + i * mask.nb[0], mask.type);
+        row_cache[i] = v;
+        mx = fmaxf(mx, v);
+    }
+    mx = block_max(mx, sh);
+    float sum = 0.0f;
+    for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) {
+        const float e = expf(row_cache[i] - mx);
+        row_cache[i] = e;
+        sum += e;
+    }
+    sum = block_sum(sum, sh);
+    const float inv = 1.0f / sum;
+    for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) y[i] = row_cache[i] * inv;
+}
+cudaError_t launch_soft_max(const TensorD & src, const TensorD * mask, const TensorD & dst, float scale, float max_bias, const LaunchCtx & c) {
+    const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
+    if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
+    const int n_head = (int) src.ne[2];
+    int n_head_log2 = 1; while (n_head_log2 * 2 <= n_head) n_head_log2 *= 2;
+    const float m0 = powf(2.0f, -max_bias / (float) n_head_log2), m1 = powf(2.0f, -(max_bias / 2.0f) / (float) n_head_log2);
+    const size_t smem = (size_t) src.ne[0] * sizeof(float);
+    static unsigned attr_mask = 0;
+    if (smem > 48 * 1024 && !(attr_mask & (1u << c.device))) {
+        cudaError_t e = cudaFuncSetAttribute(soft_max_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_mask |= 1u << c.device;
+    }
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    soft_max_kernel<<<(unsigned) rows, row_block(src.ne[0]), smem, c.stream>>>(src, mask ? *mask : src, mask ? 1 : 0, dst,
+                                                                               scale, max_bias, m0, m1, n_head_log2);
+    return B200_LAUNCH_CHECK();
+}
+
+}  // namespace b200

@@ -1,0 +1,97 @@
+// Internal C++ interface between the host layer and the CUDA kernels.
+// No ggml types here: tensors are described by a plain descriptor that mirrors
+// ggml's ne[]/nb[] convention (element counts, byte strides; dim 0 innermost).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+namespace b200 {
+
+struct TensorD {
+    void *  data;
+    int     type;        // ggml_type value
+    int64_t ne[4];
+    int64_t nb[4];
+};
+
+// launch context shared by all kernels of one backend instance
+struct LaunchCtx {
+    cudaStream_t stream;
+    int   device;
+    int   sm_count;
+    int * status;        // device status word (ERR_* codes), never reset by kernels
+    int   use_pdl;       // launch with programmatic stream serialization where supported
+};
+
+// ---- quantized mat-vec (mmvq.cu) ----
+struct MmvqArgs {
+    int type;
+    const void * W;  int64_t w_nb1, w_nb2, w_nb3;
+    const void * Xq;                                   // blk_act128 columns ordered [i13][i12][n]
+    float * dst;     int64_t dst_nb1, dst_nb2, dst_nb3;
+    int M, K, N, ne12, ne13, r2, r3;                   // N = columns of this launch (1..8)
+    int x_col0, x_ncols, xq_ne12;                      // first column, columns per batch in Xq, dim-2 extent of Xq (0 = ne12)
+    const int32_t * ids; int64_t ids_s12, ids_s13;     // MUL_MAT_ID expert indices (or null)
+    int * status; int sm_count, device, use_pdl;
+};
+bool        mmvq_type_supported(int type);
+size_t      act128_bytes(int64_t K, int64_t ncols);
+// columns ordered [i13][i12][i11]; s11..s13 are element strides of x
+cudaError_t launch_quantize_act128(const float * x, int64_t ne11, int64_t ne12, int64_t ne13,
+                                   int64_t s11, int64_t s12, int64_t s13, void * y, int K, cudaStream_t stream);
+cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream);
+
+// ---- float mat-mul for F32/F16/BF16 weights (matmul_f.cu) ----
+// dst[i3][i2][n][m] = sum_k W[..][m][k] * X[i3][i2][n][k]; W broadcast over dims 2,3
+cudaError_t launch_matmul_f(const TensorD & W, const TensorD & X, const TensorD & dst, const LaunchCtx & c);
+
+// ---- prefill quantized GEMM on tcgen05 (mmq_tc.cu) ----
+bool        mmq_tc_supported(int type, int64_t M, int64_t N, int64_t K);
+size_t      mmq_tc_workspace_bytes(int64_t N, int64_t K);
+cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float * X, int64_t x_nb1,
+                          float * dst, int64_t dst_nb1, int64_t M, int64_t N, int64_t K,
+                          void * workspace, const LaunchCtx & c);
+
+// ---- glue ops (glue.cu) ----
+enum BinOp { BIN_ADD = 0, BIN_SUB = 1, BIN_MUL = 2, BIN_DIV = 3 };
+enum UnOp  { UN_SILU = 0, UN_GELU, UN_GELU_QUICK, UN_RELU, UN_TANH, UN_SIGMOID, UN_NEG, UN_EXP, UN_ABS, UN_SGN,
+             UN_STEP, UN_ELU, UN_HARDSIGMOID, UN_HARDSWISH, UN_SQR, UN_SQRT, UN_SIN, UN_COS, UN_LOG };
+
+cudaError_t launch_rms_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c);
+// y = rms_norm(x) * w   (w broadcast like ggml MUL's src1); optionally also emits blk_act128 of y
+cudaError_t launch_rms_norm_mul(const TensorD & src, const TensorD & w, const TensorD & dst, float eps,
+                                void * act128_out, const LaunchCtx & c);
+cudaError_t launch_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c);
+cudaError_t launch_bin_bcast(int op, const TensorD & a, const TensorD & b, const TensorD & dst, const LaunchCtx & c);
+cudaError_t launch_unary(int op, const TensorD & src, const TensorD & dst, const LaunchCtx & c);
+// dst = silu(gate) * up, optionally also emitting blk_act128 of dst
+cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const TensorD & dst, void * act128_out, const LaunchCtx & c);
+cudaError_t launch_scale(const TensorD & src, const TensorD & dst, float scale, const LaunchCtx & c);
+cudaError_t launch_clamp(const TensorD & src, const TensorD & dst, float lo, float hi, const LaunchCtx & c);
+
+struct RopeParams {
+    int n_dims, mode, n_ctx_orig;
+    float freq_base, freq_scale, ext_factor, attn_factor, beta_fast, beta_slow;
+};
+cudaError_t launch_rope(const TensorD & src, const int32_t * pos, const float * freq_factors, const TensorD & dst,
+                        const RopeParams & rp, const LaunchCtx & c);
+
+bool        cpy_supported(int src_type, int dst_type);
+cudaError_t launch_cpy(const TensorD & src, const TensorD & dst, const LaunchCtx & c);
+
+bool        get_rows_supported(int src_type);
+cudaError_t launch_get_rows(const TensorD & src, const TensorD & idx, const TensorD & dst, const LaunchCtx & c);
+
+cudaError_t launch_soft_max(const TensorD & src, const TensorD * mask, const TensorD & dst, float scale, float max_bias,
+                            const LaunchCtx & c);
+
+// ---- flash attention (fattn.cu) ----
+struct FattnParams { float scale, max_bias, logit_softcap; };
+bool        fattn_supported(int64_t head_dim, int k_type, int v_type);
+size_t      fattn_workspace_bytes(const TensorD & q, const TensorD & k, int sm_count);
+cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
+                         const FattnParams & fp, void * workspace, const LaunchCtx & c);
+
+}  // namespace b200

@@ -1,0 +1,292 @@
+#!/usr/bin/env python
+"""Benchmark: Llama-3-8B architecture, Q4_K_M, pp512 + tg128 per step, through the B200 ggml backend.
+
+One step = what one repetition of the reference's llama-bench does (examples/llama-bench/llama-bench.cpp:
+1430-1468): a 512-token prompt evaluated as one batch at an empty KV cache, then 128 single-token decodes.
+Weights are random-init (seeded N(0, 0.02), quantized to the Q4_K_M tensor-type mixture); token ids are
+uniform random, as llama-bench feeds them.  The model (4.6 GB of weights) is far larger than L2, so every
+timed token re-reads it from HBM; no L2 flush is needed.
+
+  value      tg128 tokens/s from the device time of graph_compute (CUDA events on the backend's stream;
+             inputs already resident), summed over the 128 decodes of each timed step
+  e2e        the same tokens/s by host clock around the driver's decode call: token ids and mask copied
+             host->device, logits copied device->host, every token
+  roofline   the decode mat-vec kernel alone, launched through the flat C-ABI over every weight matrix of
+             the model in order (cold L2), bracketed by CUDA events: algorithmic bytes / duration
+  cpu_baseline  the reference's ggml CPU backend (oracle/_ref) running the same graph on the same weights
+             on a bounded sample (pp128 + tg16), all host cores
+
+`--impl reference` times only the reference CPU backend on the bounded sample and prints the same line.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+N_PROMPT, N_GEN = 512, 128
+CPU_PROMPT, CPU_GEN = 128, 16
+METRIC = "llama3-8b-q4_k_m tg128 tokens/s (pp512+tg128 per step)"
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0, set()
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx = max(mx, float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def fill_weights(models, device):
+    """Random-init weights, generated once per tensor and handed to every model as host bytes."""
+    from llama_cpp_b200 import synth
+    t0 = time.time()
+    total = 0
+    for t in models[0].tensors():
+        data = synth.make_tensor(t["type"], t["ne0"], t["ne1"], seed=1000 + t["index"], device=device)
+        for m in models:
+            m.set_tensor(t["index"], data)
+        total += data.size
+    log(f"[bench] weights: {total / 1e9:.2f} GB generated and uploaded in {time.time() - t0:.1f} s")
+
+
+def run_step(m, tokens, n_prompt, n_gen):
+    """pp + tg pass; returns (pp_wall_s, tg_wall_s, pp_dev_ms, tg_dev_ms)."""
+    t0 = time.perf_counter()
+    m.decode(tokens[:n_prompt], 0)
+    t1 = time.perf_counter()
+    pp_dev = m.last_compute_ms
+    tg_dev = 0.0
+    for i in range(n_gen):
+        m.decode(tokens[n_prompt + i:n_prompt + i + 1], n_prompt + i)
+        tg_dev += m.last_compute_ms
+    t2 = time.perf_counter()
+    return t1 - t0, t2 - t1, pp_dev, tg_dev
+
+
+def io_bytes_per_step(n_prompt, n_gen, n_vocab):
+    h2d = d2h = 0
+    for n_tok, pos0 in [(n_prompt, 0)] + [(1, n_prompt + i) for i in range(n_gen)]:
+        n_kv = (pos0 + n_tok + 255) // 256 * 256
+        n_pad = (n_tok + 63) // 64 * 64
+        h2d += n_tok * 4 * 2 + n_kv * n_pad * 4 + 4
+        d2h += n_vocab * 4
+    return h2d, d2h
+
+
+def gemv_roofline(pkg, m, torch):
+    """Times the decode mat-vec kernel over every weight matrix of the model, in graph order, with CUDA events."""
+    l = pkg.lib()
+    mats = [t for t in m.tensors() if t["type"] != 0 and t["name"] != "token_embd.weight"]
+    order = sorted(mats, key=lambda t: (t["name"] == "output.weight", t["index"]))
+    kmax = max(t["ne0"] for t in order)
+    x = torch.randn(kmax, device="cuda", dtype=torch.float32)
+    xq = {k: torch.empty(int(l.b200_act_bytes(k, 1)), device="cuda", dtype=torch.uint8) for k in {t["ne0"] for t in order}}
+    dst = torch.empty(max(t["ne1"] for t in order), device="cuda", dtype=torch.float32)
+    stream = torch.cuda.current_stream().cuda_stream
+    for k, buf in xq.items():
+        assert l.b200_quantize_act(x.data_ptr(), k, k, 1, buf.data_ptr(), stream) == 0
+    algo = 0
+
+    def one_pass():
+        nonlocal algo
+        algo = 0
+        for t in order:
+            rb = t["nbytes"] // t["ne1"]
+            rc = l.b200_mul_mat_vec_q(t["type"], m.tensor_data(t["index"]), rb, t["ne1"], t["ne0"], xq[t["ne0"]].data_ptr(), 1,
+                                      dst.data_ptr(), t["ne1"], stream)
+            assert rc == 0, l.b200_last_error()
+            algo += t["nbytes"] + 4 * t["ne0"] + 4 * t["ne1"]        # weights + F32 activations in + F32 out
+    for _ in range(3):
+        one_pass()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        one_pass()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    return algo, ms, len(order)
+
+
+def cpu_model(arch, n_threads):
+    from llama_cpp_b200 import llama
+    orc = entry.load_oracle()
+    if not orc.ref_available():
+        raise RuntimeError("oracle/_ref (the reference CPU backend) is not built")
+    return llama.Llama(n_ctx=256, n_ubatch=CPU_PROMPT, reg=orc.ref_cpu_backend_reg(), n_threads=n_threads, **arch)
+
+
+def time_cpu(m, tokens, steps, warmup):
+    """Bounded sample on the reference CPU backend: pp128 + tg16 per step."""
+    for _ in range(warmup):
+        m.decode(tokens[:8], 0, want_logits=False)
+        m.decode(tokens[8:9], 8, want_logits=False)
+    pp_s = tg_s = 0.0
+    for _ in range(steps):
+        pp, tg, _, _ = run_step(m, tokens, CPU_PROMPT, CPU_GEN)
+        pp_s += pp; tg_s += tg
+    return steps * CPU_PROMPT / pp_s, steps * CPU_GEN / tg_s, (pp_s + tg_s) / steps
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    pkg = entry.load_package()   # registers the package under the alias llama_cpp_b200
+    from llama_cpp_b200 import llama
+    arch = dict(llama.LLAMA3_8B)
+    cores = os.cpu_count() or 1
+    rng = np.random.default_rng(1234)
+    tokens = rng.integers(0, arch["n_vocab"], N_PROMPT + N_GEN).astype(np.int32)
+    config = {"workload": "llama3-8b-arch q4_k_m pp512+tg128 (BASELINE configs[3])", "n_prompt": N_PROMPT, "n_gen": N_GEN,
+              "flash_attn": True, "kv_type": "f16", "l2": "working set 4.6 GB of weights per token >> L2, no flush needed"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        import torch
+        m = cpu_model(arch, cores)
+        fill_weights([m], "cuda" if torch.cuda.is_available() else "cpu")
+        pp_tps, tg_tps, step_s = time_cpu(m, tokens, args.steps, min(args.warmup, 1))
+        m.close()
+        sample = f"pp{CPU_PROMPT}+tg{CPU_GEN} per step on the reference ggml CPU backend, {cores} threads"
+        print(json.dumps({"impl": "reference", "metric": METRIC, "value": tg_tps, "unit": "tokens/s", "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4/6 dot, f32 accumulate", "data": "synthetic",
+                          "config": dict(config, sample=sample), "pp_tokens_per_s": pp_tps,
+                          "cpu_baseline": {"value": tg_tps, "unit": "tokens/s", "cores": cores, "kind": "reference", "sample": sample},
+                          "e2e": {"value": tg_tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import torch
+    if world > 1:
+        raise SystemExit("row-split multi-GPU bench is not wired up yet")
+    if pkg.device_count() < 1:
+        raise SystemExit("no sm_100 device visible: the B200 path has no CPU fallback")
+    torch.cuda.set_device(0)
+    m = llama.Llama(n_ctx=1024, n_ubatch=N_PROMPT, **arch)
+    cpu = None
+    if not args.no_cpu_baseline and rank == 0:
+        try:
+            cpu = cpu_model(arch, cores)
+        except Exception as e:  # the baseline is reported, never required for the GPU number
+            log(f"[bench] cpu baseline unavailable: {e}")
+    fill_weights([m] + ([cpu] if cpu else []), "cuda")
+
+    for _ in range(max(args.warmup, 3)):
+        run_step(m, tokens, N_PROMPT, N_GEN)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = m.launch_count
+    pp_wall = tg_wall = pp_dev = tg_dev = 0.0
+    t_start = time.perf_counter()
+    for _ in range(args.steps):
+        a, b, c, d = run_step(m, tokens, N_PROMPT, N_GEN)
+        pp_wall += a; tg_wall += b; pp_dev += c; tg_dev += d
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t_start
+    clocks = sampler.stop()
+    launches = m.launch_count - launches0
+    logits = m.decode(tokens[:8], 0).copy()
+    assert np.isfinite(logits).all(), "non-finite logits"
+
+    n_tg, n_pp = args.steps * N_GEN, args.steps * N_PROMPT
+    tg_tps_dev, pp_tps_dev = n_tg / (tg_dev / 1e3), n_pp / (pp_dev / 1e3)
+    tg_tps_e2e, pp_tps_e2e = n_tg / tg_wall, n_pp / pp_wall
+    h2d, d2h = io_bytes_per_step(N_PROMPT, N_GEN, arch["n_vocab"])
+
+    peak, peak_kind = measured_peaks()
+    algo, gemv_ms, n_mats = gemv_roofline(pkg, m, torch)
+    achieved = algo / (gemv_ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "mmvq_kernel (decode mat-vec)", "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
+                "unit": "GB/s", "frac": achieved / peak, "traffic": None, "launches_per_pass": n_mats,
+                "algorithmic_bytes_per_pass": algo, "ms_per_pass": gemv_ms,
+                "whole_decode_step": {"weight_bytes_per_token": m.weight_bytes, "achieved_gbs": m.weight_bytes * tg_tps_dev / 1e9,
+                                      "frac": m.weight_bytes * tg_tps_dev / 1e9 / peak}}
+    cpu_baseline = None
+    if cpu is not None:
+        c_pp, c_tg, _ = time_cpu(cpu, tokens, 1, 1)
+        # parity on the same weights and tokens: logits of an 8-token prompt
+        ref_logits = cpu.decode(tokens[:8], 0).copy()
+        den = float(np.sum(ref_logits.astype(np.float64) ** 2))
+        nmse = float(np.sum((ref_logits.astype(np.float64) - logits) ** 2)) / den
+        cpu_baseline = {"value": c_tg, "unit": "tokens/s", "cores": cores, "kind": "reference",
+                        "sample": f"pp{CPU_PROMPT}+tg{CPU_GEN} on the reference ggml CPU backend, {cores} threads",
+                        "pp_tokens_per_s": c_pp, "logits_nmse_vs_b200": nmse}
+        cpu.close()
+    out = {"metric": METRIC, "value": tg_tps_dev, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+           "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+           "dtype": "int8 x int4/6 dot, f32 accumulate", "data": "synthetic", "config": config,
+           "pp512_tokens_per_s": pp_tps_dev, "tg128_tokens_per_s": tg_tps_dev,
+           "e2e": {"value": tg_tps_e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "pp512_tokens_per_s": pp_tps_e2e},
+           "gpu_launches": launches, "graph_nodes_per_token": m.last_n_nodes, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline}
+    m.close()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -49,6 +49,13 @@ int    b200_mul_mat_q(int type, const void * W, int64_t w_row_stride_bytes, int6
                       const float * X, int64_t x_col_stride_elems, int64_t N,
                       float * dst, int64_t dst_col_stride_elems,
                       void * scratch, size_t scratch_bytes, void * stream);
+/* The two halves of the N <= 8 path on their own: the activation quantizer (what the reference does in
+ * quantize_q8_1, ggml/src/ggml-cuda/quantize.cu:4-38) writing b200_act_bytes(K, N) bytes, and the mat-vec
+ * kernel on activations quantized earlier (mul_mat_vec_q, ggml/src/ggml-cuda/mmvq.cu:50-130).          */
+size_t b200_act_bytes(int64_t K, int64_t N);
+int    b200_quantize_act(const float * X, int64_t x_col_stride_elems, int64_t K, int64_t N, void * xq, void * stream);
+int    b200_mul_mat_vec_q(int type, const void * W, int64_t w_row_stride_bytes, int64_t M, int64_t K,
+                          const void * xq, int64_t N, float * dst, int64_t dst_col_stride_elems, void * stream);
 int    b200_mul_mat_q_host(int type, const void * W, int64_t M, int64_t K, const float * X, int64_t N, float * dst);
 
 /* ---- FLASH_ATTN_EXT -------------------------------------------------------

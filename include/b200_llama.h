@@ -1,0 +1,70 @@
+/*
+ * Llama-architecture graph driver over the ggml backend C-ABI.
+ *
+ * It plays the part that libllama + llama-bench play for the reference
+ * (llama_decode, src/llama.cpp:8586; graph llm_build_context::build_llama,
+ * src/llama.cpp:1476-1640; timing loop examples/llama-bench/llama-bench.cpp:1430-1468):
+ * it builds the per-ubatch cgraph of a Llama model (struct ggml_tensor /
+ * struct ggml_cgraph laid out by hand, exactly as ggml's constructors would) and
+ * runs it through a backend's function tables -- buffer type alloc_buffer,
+ * buffer set_tensor/get_tensor, backend graph_compute and synchronize
+ * (ggml/src/ggml-backend-impl.h).  Any backend that implements that ABI can be
+ * driven: the B200 plugin in this library, or the reference CPU backend loaded
+ * from its own shared object (used as the timed CPU baseline).
+ *
+ * All data crossing this interface are host buffers: quantized weight bytes in,
+ * token ids in, logits out.
+ */
+#ifndef B200_LLAMA_H
+#define B200_LLAMA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b200_llama b200_llama;
+
+typedef struct b200_llama_config {
+    int32_t n_layer, n_embd, n_head, n_head_kv, n_ff, n_vocab;
+    int32_t n_ctx;          /* KV cache length (tokens) */
+    int32_t n_ubatch;       /* largest number of tokens per graph */
+    float   rope_theta, rms_eps;
+    int32_t n_threads;      /* forwarded to the backend's "ggml_backend_set_n_threads" when it has one */
+} b200_llama_config;
+
+/* reg: a ggml_backend_reg_t (as returned by a backend library's ggml_backend_init), or NULL for
+ * this library's own B200 registry.  Weight tensor types follow the reference's Q4_K_M mixture
+ * (src/llama-quant.cpp:129-131, 235-236, 291-298): Q4_K, with Q6_K for output.weight and for
+ * attn_v / ffn_down on the "more bits" layers.  Returns NULL on failure (b200_llama_error()). */
+b200_llama * b200_llama_create(void * reg, int32_t device_index, const b200_llama_config * cfg);
+void         b200_llama_free(b200_llama * m);
+const char * b200_llama_error(void);
+
+/* weight tensors, in a fixed order; names follow the GGUF convention ("blk.0.attn_q.weight") */
+int32_t      b200_llama_n_tensors(const b200_llama * m);
+int32_t      b200_llama_tensor_info(const b200_llama * m, int32_t i, char * name, size_t name_cap,
+                                    int32_t * type, int64_t * ne0, int64_t * ne1, size_t * nbytes);
+int32_t      b200_llama_set_tensor(b200_llama * m, int32_t i, const void * host_data, size_t nbytes);
+/* address of tensor i inside the backend's weight buffer (a device pointer on the B200 backend) */
+void *       b200_llama_tensor_data(const b200_llama * m, int32_t i);
+
+/* Evaluates n_tokens tokens at KV positions [pos0, pos0 + n_tokens) (one ubatch, n_tokens <= n_ubatch):
+ * token ids are copied host->device, the graph is computed, and the logits of the LAST token
+ * (n_vocab floats) are copied device->host into logits_host (may be NULL to skip the read).
+ * Returns 0 on success. */
+int32_t      b200_llama_decode(b200_llama * m, const int32_t * tokens, int32_t n_tokens, int32_t pos0, float * logits_host);
+
+/* statistics of the most recent decode */
+int32_t      b200_llama_last_n_nodes(const b200_llama * m);      /* nodes handed to graph_compute */
+double       b200_llama_last_compute_ms(const b200_llama * m);   /* device time of graph_compute (CUDA events) on the
+                                                                    B200 backend; host wall time on other backends */
+uint64_t     b200_llama_launch_count(const b200_llama * m);      /* kernels launched so far (B200 backend only) */
+size_t       b200_llama_weight_bytes(const b200_llama * m);      /* bytes of all weight tensors read per token */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_LLAMA_H */

@@ -27,10 +27,14 @@ BLOCK = {"f32": (1, 4), "f16": (1, 2), "q4_0": (32, 18), "q4_1": (32, 20), "q5_0
 EXPORTS = [
     "b200_device_count", "b200_last_error", "b200_row_size",
     "b200_mul_mat_q_scratch_bytes", "b200_mul_mat_q", "b200_mul_mat_q_host",
+    "b200_act_bytes", "b200_quantize_act", "b200_mul_mat_vec_q",
     "b200_flash_attn_scratch_bytes", "b200_flash_attn", "b200_flash_attn_host",
     "b200_dequantize_rows_host", "b200_get_rows_host", "b200_quantize_rows_host", "b200_f32_to_f16_host",
     "b200_rms_norm_host", "b200_rope_host", "b200_silu_mul_host", "b200_soft_max_host",
     "ggml_backend_init", "ggml_backend_score",
+    "b200_llama_create", "b200_llama_free", "b200_llama_error", "b200_llama_n_tensors", "b200_llama_tensor_info",
+    "b200_llama_set_tensor", "b200_llama_tensor_data", "b200_llama_decode", "b200_llama_last_n_nodes",
+    "b200_llama_last_compute_ms", "b200_llama_launch_count", "b200_llama_weight_bytes",
 ]
 
 
@@ -66,6 +70,10 @@ def lib() -> C.CDLL:
         l.b200_mul_mat_q_scratch_bytes.argtypes = [C.c_int, i64, i64, i64]
         l.b200_mul_mat_q.argtypes = [C.c_int, vp, i64, i64, i64, vp, i64, i64, vp, i64, vp, sz, vp]
         l.b200_mul_mat_q_host.argtypes = [C.c_int, vp, i64, i64, vp, i64, vp]
+        l.b200_act_bytes.restype = sz
+        l.b200_act_bytes.argtypes = [i64, i64]
+        l.b200_quantize_act.argtypes = [vp, i64, i64, i64, vp, vp]
+        l.b200_mul_mat_vec_q.argtypes = [C.c_int, vp, i64, i64, i64, vp, i64, vp, i64, vp]
         l.b200_flash_attn_scratch_bytes.restype = sz
         l.b200_flash_attn_scratch_bytes.argtypes = [i64, i64, i64, i64]
         l.b200_flash_attn.argtypes = [vp, i64, i64, vp, i64, i64, vp, i64, i64, vp, i64, vp,

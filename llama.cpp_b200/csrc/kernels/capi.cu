@@ -118,6 +118,29 @@ API int b200_mul_mat_q(int type, const void * W, int64_t w_nb1, int64_t M, int64
     return 0;
 }
 
+API size_t b200_act_bytes(int64_t K, int64_t N) { return act128_bytes(K, N); }
+
+API int b200_quantize_act(const float * X, int64_t x_stride, int64_t K, int64_t N, void * xq, void * stream) {
+    if (K <= 0 || N <= 0) return fail(B200_E_BAD_ARG, "bad shape");
+    LaunchCtx lc; int rc = get_ctx(stream, lc); if (rc) return rc;
+    CK(launch_quantize_act128(X, N, 1, 1, x_stride, 0, 0, xq, (int) K, lc.stream));
+    return 0;
+}
+
+API int b200_mul_mat_vec_q(int type, const void * W, int64_t w_nb1, int64_t M, int64_t K, const void * xq, int64_t N,
+                           float * dst, int64_t dst_stride, void * stream) {
+    if (!mmvq_type_supported(type)) return fail(B200_E_UNSUPPORTED, "weight type not supported");
+    if (K <= 0 || M <= 0 || N <= 0 || N > 8 || K % type_block_elems(type) != 0) return fail(B200_E_BAD_ARG, "bad shape");
+    LaunchCtx lc; int rc = get_ctx(stream, lc); if (rc) return rc;
+    MmvqArgs a = {};
+    a.type = type; a.W = W; a.w_nb1 = w_nb1; a.Xq = xq; a.M = (int) M; a.K = (int) K; a.N = (int) N;
+    a.ne12 = 1; a.ne13 = 1; a.r2 = 1; a.r3 = 1; a.x_ncols = (int) N; a.xq_ne12 = 1; a.x_col0 = 0;
+    a.dst = dst; a.dst_nb1 = dst_stride * 4;
+    a.status = lc.status; a.sm_count = lc.sm_count; a.device = lc.device; a.use_pdl = 0;
+    CK(launch_mmvq(a, lc.stream));
+    return 0;
+}
+
 API int b200_mul_mat_q_host(int type, const void * W, int64_t M, int64_t K, const float * X, int64_t N, float * dst) {
     if (!mmvq_type_supported(type)) return fail(B200_E_UNSUPPORTED, "weight type not supported");
     if (K <= 0 || M <= 0 || N <= 0 || K % type_block_elems(type) != 0) return fail(B200_E_BAD_ARG, "bad shape");

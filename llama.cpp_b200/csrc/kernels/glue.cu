@@ -427,6 +427,9 @@ __global__ void cpy_elem_kernel(const TensorD s, const TensorD d, int64_t total)
 // F32 -> quantized block (32 values): one thread per block, restating
 // quantize_row_q8_0_ref / q4_0_ref / q4_1_ref / q5_0_ref / q5_1_ref
 // (ggml/src/ggml-quants.c:31-217) operation by operation (no fused multiply-add)
+// blocks are 2-byte aligned; scales are stored with one explicit 16-bit store
+__device__ __forceinline__ void st_h(uint8_t * p, float v) { *(uint16_t *) p = __half_as_ushort(__float2half_rn(v)); }
+
 template <int QT>
 __device__ void quantize_block32(const float * x, uint8_t * out) {
     if (QT == T_Q8_0) {
@@ -435,7 +438,7 @@ __device__ void quantize_block32(const float * x, uint8_t * out) {
         const float d = __fdiv_rn(amax, 127.0f);
         const float id = d ? __fdiv_rn(1.0f, d) : 0.0f;
         blk_q8_0 * b = (blk_q8_0 *) out;
-        b->d = __half_as_ushort(__float2half_rn(d));
+        st_h(out, d);
         for (int j = 0; j < 32; ++j) b->qs[j] = (int8_t) roundf(__fmul_rn(x[j], id));
     } else if (QT == T_Q4_0 || QT == T_Q5_0) {
         float amax = 0.0f, mx = 0.0f;
@@ -444,7 +447,7 @@ __device__ void quantize_block32(const float * x, uint8_t * out) {
         const float id = d ? __fdiv_rn(1.0f, d) : 0.0f;
         if (QT == T_Q4_0) {
             blk_q4_0 * b = (blk_q4_0 *) out;
-            b->d = __half_as_ushort(__float2half_rn(d));
+            st_h(out, d);
             for (int j = 0; j < 16; ++j) {
                 const float x0 = __fmul_rn(x[j], id), x1 = __fmul_rn(x[16 + j], id);
                 const uint8_t q0 = (uint8_t) min(15, (int) (int8_t) __fadd_rn(x0, 8.5f));
@@ -453,7 +456,7 @@ __device__ void quantize_block32(const float * x, uint8_t * out) {
             }
         } else {
             blk_q5_0 * b = (blk_q5_0 *) out;
-            b->d = __half_as_ushort(__float2half_rn(d));
+            st_h(out, d);
             uint32_t qh = 0;
             for (int j = 0; j < 16; ++j) {
                 const float x0 = __fmul_rn(x[j], id), x1 = __fmul_rn(x[16 + j], id);
@@ -473,7 +476,7 @@ __device__ void quantize_block32(const float * x, uint8_t * out) {
         const float id = d ? __fdiv_rn(1.0f, d) : 0.0f;
         if (QT == T_Q4_1) {
             blk_q4_1 * b = (blk_q4_1 *) out;
-            b->d = __half_as_ushort(__float2half_rn(d)); b->m = __half_as_ushort(__float2half_rn(mn));
+            st_h(out, d); st_h(out + 2, mn);
             for (int j = 0; j < 16; ++j) {
                 const float x0 = __fmul_rn(__fsub_rn(x[j], mn), id), x1 = __fmul_rn(__fsub_rn(x[16 + j], mn), id);
                 const uint8_t q0 = (uint8_t) min(15, (int) (int8_t) __fadd_rn(x0, 0.5f));
@@ -482,7 +485,7 @@ __device__ void quantize_block32(const float * x, uint8_t * out) {
             }
         } else {
             blk_q5_1 * b = (blk_q5_1 *) out;
-            b->d = __half_as_ushort(__float2half_rn(d)); b->m = __half_as_ushort(__float2half_rn(mn));
+            st_h(out, d); st_h(out + 2, mn);
             uint32_t qh = 0;
             for (int j = 0; j < 16; ++j) {
                 const float x0 = __fmul_rn(__fsub_rn(x[j], mn), id), x1 = __fmul_rn(__fsub_rn(x[16 + j], mn), id);

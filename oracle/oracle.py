@@ -203,3 +203,26 @@ def ref_quantize_rows(qtype: str, x: np.ndarray) -> np.ndarray:
     out = np.empty((n, l.ggml_row_size(TYPES[qtype], k)), dtype=np.uint8)
     l.ggml_quantize_chunk(TYPES[qtype], _p(x), _p(out), 0, n, k, None)
     return out
+
+
+_cpu_lib = None
+
+
+def ref_cpu_backend_reg() -> int:
+    """Address of the reference CPU backend's ggml_backend_reg: the best-scoring libggml-cpu-*.so variant of
+    oracle/_ref is dlopen'ed and its ggml_backend_init() called, as ggml_backend_load_best does
+    (ggml/src/ggml-backend-reg.cpp:487-551)."""
+    global _cpu_lib
+    if _cpu_lib is None:
+        C.CDLL(str(REF_DIR / "libggml-base.so"), mode=C.RTLD_GLOBAL)
+        best, best_score = None, 0
+        for p in sorted(REF_DIR.glob("libggml-cpu-*.so")):
+            l = C.CDLL(str(p))
+            s = l.ggml_backend_score()
+            if s > best_score:
+                best, best_score = l, s
+        if best is None:
+            raise RuntimeError("no usable reference CPU backend variant in oracle/_ref")
+        best.ggml_backend_init.restype = C.c_void_p
+        _cpu_lib = best
+    return int(_cpu_lib.ggml_backend_init())

@@ -135,8 +135,17 @@ def test_flash_attn_decode_32k_properties(b200, oracle):
     k = rng.standard_normal((nhkv, n_kv, d)).astype(np.float16)
     v = rng.standard_normal((nhkv, n_kv, d)).astype(np.float16)
     got = b200.flash_attn(q, k, v, causal_mask(1, n_kv), 1.0 / np.sqrt(d))
+    # exact float64 attention for the 4 query heads of KV head 0
+    s = (k[0].astype(np.float64) @ q[:4, 0].astype(np.float64).T) / np.sqrt(d)            # [n_kv, 4]
+    p = np.exp(s - s.max(axis=0)); p /= p.sum(axis=0)
+    exact = (p.T @ v[0].astype(np.float64))[None]                                         # [1, 4, d]
+    assert oracle.nmse(exact, got[:, :4]) <= NMSE_MM
+    # The CPU algorithm keeps its V accumulator in F16; over 32768 near-uniform keys that rounding alone
+    # costs about as much as the whole tolerance, so the oracle is compared with a doubled bound here
+    # and must itself sit no closer to the exact result than the CUDA kernel does.
     want = oracle.flash_attn(q[:4], k[:1], v[:1], causal_mask(1, n_kv), 1.0 / np.sqrt(d))
-    assert oracle.nmse(want, got[:, :4]) <= NMSE_MM
+    assert oracle.nmse(want, got[:, :4]) <= 2 * NMSE_MM
+    assert oracle.nmse(exact, got[:, :4]) <= oracle.nmse(exact, want)
     vconst = np.broadcast_to(v[:, :1, :], v.shape).copy()
     got = b200.flash_attn(q, k, vconst, None, 1.0 / np.sqrt(d))
     for h in range(nh):

@@ -42,6 +42,9 @@ size_t      act128_bytes(int64_t K, int64_t ncols);
 cudaError_t launch_quantize_act128(const float * x, int64_t ne11, int64_t ne12, int64_t ne13,
                                    int64_t s11, int64_t s12, int64_t s13, void * y, int K, cudaStream_t stream);
 cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream);
+// direct 128-bit-coalesced variant for Q4_K / Q5_K (mmvq_k.cu); launch_mmvq routes to it when applicable
+bool        mmvq_k_applicable(const MmvqArgs & a);
+cudaError_t launch_mmvq_k(const MmvqArgs & a, cudaStream_t stream);
 
 // ---- float mat-mul for F32/F16/BF16 weights (matmul_f.cu) ----
 // dst[i3][i2][n][m] = sum_k W[..][m][k] * X[i3][i2][n][k]; W broadcast over dims 2,3

@@ -82,6 +82,20 @@ __device__ __forceinline__ uint32_t lds_u32_a2(const uint8_t * p) {
     const uint16_t * h = (const uint16_t *) p;
     return (uint32_t) h[0] | ((uint32_t) h[1] << 16);
 }
+// NW consecutive 32-bit words starting at a 2-byte aligned shared-memory address: NW+1 aligned
+// loads and a funnel shift each instead of 2*NW 16-bit loads (the slot keeps 16 bytes of slack)
+template <int NW>
+__device__ __forceinline__ void lds_words(const uint8_t * p, uint32_t (&out)[NW]) {
+    const uint32_t * base = (const uint32_t *) ((uintptr_t) p & ~(uintptr_t) 3);
+    const uint32_t sh = ((uint32_t) (uintptr_t) p & 3u) * 8u;
+    uint32_t prev = base[0];
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+        const uint32_t next = base[i + 1];
+        out[i] = __funnelshift_r(prev, next, sh);
+        prev = next;
+    }
+}
 
 template <int T> struct WT;   // weight-type traits: UNIT = weights per unit, dot() accumulates one unit
 
@@ -90,12 +104,10 @@ template <> struct WT<T_Q4_0> {
     template <int N> static __device__ __forceinline__ void dot(const uint8_t * row, int u, const ActView & xv, float (&acc)[N]) {
         const uint8_t * b = row + u * 18;
         const float dw = h2f(*(const uint16_t *) b);
-        uint32_t lo[4], hi[4];
+        uint32_t w[4], lo[4], hi[4];
+        lds_words<4>(b + 2, w);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t w = lds_u32_a2(b + 2 + 4 * i);
-            lo[i] = w & 0x0F0F0F0Fu; hi[i] = (w >> 4) & 0x0F0F0F0Fu;
-        }
+        for (int i = 0; i < 4; ++i) { lo[i] = w[i] & 0x0F0F0F0Fu; hi[i] = (w[i] >> 4) & 0x0F0F0F0Fu; }
 #pragma unroll
         for (int n = 0; n < N; ++n) {
             const int * xq = xv.q32(n, u);
@@ -191,9 +203,11 @@ template <> struct WT<T_Q8_0> {
     template <int N> static __device__ __forceinline__ void dot(const uint8_t * row, int u, const ActView & xv, float (&acc)[N]) {
         const uint8_t * b = row + u * 34;
         const float dw = h2f(*(const uint16_t *) b);
+        uint32_t wu[8];
+        lds_words<8>(b + 2, wu);
         int w[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) w[i] = (int) lds_u32_a2(b + 2 + 4 * i);
+        for (int i = 0; i < 8; ++i) w[i] = (int) wu[i];
 #pragma unroll
         for (int n = 0; n < N; ++n) {
             const int * xq = xv.q32(n, u);
@@ -280,12 +294,13 @@ template <> struct WT<T_Q6_K> {
         const float d = h2f(*(const uint16_t *) (b + 208));
         const int8_t * sc = (const int8_t *) (b + 192) + n128 * 8 + (g8 >> 1);
         int q[4][2];
+        uint32_t Aw[2], Bw[2], Hw[2];
+        lds_words<2>(b + n128 * 64 + g8 * 8, Aw);
+        lds_words<2>(b + n128 * 64 + 32 + g8 * 8, Bw);
+        lds_words<2>(b + 128 + n128 * 32 + g8 * 8, Hw);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const int l = g8 * 8 + 4 * i;
-            const uint32_t A = lds_u32_a2(b + n128 * 64 + l);
-            const uint32_t B = lds_u32_a2(b + n128 * 64 + 32 + l);
-            const uint32_t H = lds_u32_a2(b + 128 + n128 * 32 + l);
+            const uint32_t A = Aw[i], B = Bw[i], H = Hw[i];
             q[0][i] = (int) __vsubss4((A & 0x0F0F0F0Fu)        | ((H << 4) & 0x30303030u), 0x20202020u);
             q[1][i] = (int) __vsubss4((B & 0x0F0F0F0Fu)        | ((H << 2) & 0x30303030u), 0x20202020u);
             q[2][i] = (int) __vsubss4(((A >> 4) & 0x0F0F0F0Fu) | ( H       & 0x30303030u), 0x20202020u);
@@ -551,6 +566,7 @@ cudaError_t launch_quantize_act128(const float * x, int64_t ne11, int64_t ne12, 
 }
 
 cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream) {
+    if (mmvq_k_applicable(a)) return launch_mmvq_k(a, stream);
     MmvqParams p = {};
     p.W = (const uint8_t *) a.W; p.w_nb1 = a.w_nb1; p.w_nb2 = a.w_nb2; p.w_nb3 = a.w_nb3;
     p.Xq = (const uint8_t *) a.Xq; p.xq_col_bytes = (int64_t) ((a.K + 127) / 128) * 160;

@@ -176,8 +176,33 @@ static const ggml_backend_buffer_type_i k_host_buft_iface = {
 // ---------------------------------------------------------------------------
 static uint8_t k_guid[16] = {0xb2, 0x00, 0x5a, 0x10, 0x0a, 0x9e, 0x41, 0x7c, 0x8d, 0x13, 0x67, 0x2f, 0xc4, 0x55, 0x90, 0xee};
 
+BackendCtx::ActEntry * BackendCtx::act_cache_find(const void * src_data, int64_t K, int64_t ncols) {
+    for (ActEntry & e : act_cache) if (e.src_data == src_data && e.K == K && e.ncols == ncols) return &e;
+    return nullptr;
+}
+BackendCtx::ActEntry * BackendCtx::act_cache_take(const void * src_data, int64_t K, int64_t ncols) {
+    act_cache_invalidate(src_data);
+    ActEntry & e = act_cache[act_next];
+    act_next ^= 1;
+    const size_t need = act128_bytes(K, ncols);
+    if (need > e.cap) {
+        if (capturing) { capture_failed = true; return nullptr; }
+        B200_CUDA_CHECK(cudaStreamSynchronize(stream));
+        if (e.q) B200_CUDA_CHECK(cudaFree(e.q));
+        size_t cap = e.cap ? e.cap : (size_t) 1 << 20;
+        while (cap < need) cap *= 2;
+        B200_CUDA_CHECK(cudaMalloc(&e.q, cap));
+        e.cap = cap;
+        scratch_generation++;
+    }
+    e.src_data = src_data; e.K = K; e.ncols = ncols;
+    return &e;
+}
+
 void * BackendCtx::get_scratch(size_t bytes) {
     if (bytes <= scratch_size) return scratch;
+    if (capturing) { capture_failed = true; return scratch; }
+    scratch_generation++;
     B200_CUDA_CHECK(cudaStreamSynchronize(stream));
     if (scratch) B200_CUDA_CHECK(cudaFree(scratch));
     size_t cap = scratch_size ? scratch_size : (size_t) 8 << 20;
@@ -195,6 +220,10 @@ static void backend_free(ggml_backend_t backend) {
     set_device(ctx->dev->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    for (auto & e : ctx->act_cache) if (e.q) cudaFree(e.q);
+    if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
+    if (ctx->dyn_dev) cudaFree(ctx->dyn_dev);
+    free(ctx->dyn_host);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->copy_event) cudaEventDestroy(ctx->copy_event);
@@ -307,6 +336,10 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t dev, const char * /*pa
     B200_CUDA_CHECK(cudaMemset(ctx->status_dev, 0, sizeof(int)));
     B200_CUDA_CHECK(cudaMallocHost((void **) &ctx->status_host, sizeof(int)));
     *ctx->status_host = 0;
+    B200_CUDA_CHECK(cudaMalloc((void **) &ctx->dyn_dev, sizeof(int64_t) * BackendCtx::DYN_CAP));
+    // pageable on purpose: cudaMemcpyAsync then snapshots the values at call time, so the next call may overwrite them
+    ctx->dyn_host = (int64_t *) malloc(sizeof(int64_t) * BackendCtx::DYN_CAP);
+    ctx->use_graphs = getenv("GGML_B200_GRAPHS") ? atoi(getenv("GGML_B200_GRAPHS")) : 1;
     const char * pdl = getenv("GGML_B200_PDL");
     ctx->use_pdl = pdl ? atoi(pdl) : 0;
     ctx->trace = getenv("GGML_B200_TRACE") ? atoi(getenv("GGML_B200_TRACE")) : 0;

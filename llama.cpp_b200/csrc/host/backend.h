@@ -42,6 +42,31 @@ struct BackendCtx {
     uint64_t     n_launches = 0;           // kernels launched by graph_compute since creation
     std::string  name;
 
+    // int8 activation blocks of recent MUL_MAT inputs, so that mat-muls sharing an input (wq/wk/wv,
+    // gate/up) quantize it once and producers (rms_norm*w, silu*up) can emit it directly; valid only
+    // within one graph_compute call
+    struct ActEntry { const void * src_data = nullptr; int64_t K = 0, ncols = 0; void * q = nullptr; size_t cap = 0; };
+    ActEntry     act_cache[2];
+    int          act_next = 0;
+    void         act_cache_clear() { act_cache[0].src_data = act_cache[1].src_data = nullptr; }
+    // a node that writes memory starting at `data` makes blocks quantized from the old contents stale
+    void         act_cache_invalidate(const void * data) { for (ActEntry & e : act_cache) if (e.src_data == data) e.src_data = nullptr; }
+    ActEntry *   act_cache_find(const void * src_data, int64_t K, int64_t ncols);
+    ActEntry *   act_cache_take(const void * src_data, int64_t K, int64_t ncols);   // may allocate (never while capturing)
+
+    // CUDA-graph replay of small-batch graphs.  Values that change every token without changing the
+    // graph's shape (the byte offset of KV-cache stores) live in device memory (`dyn`), so a captured
+    // graph stays valid from token to token.
+    int          use_graphs = 1;
+    bool         capturing = false, capture_failed = false;
+    uint64_t     graph_key = 0, pending_key = 0;
+    cudaGraphExec_t graph_exec = nullptr;
+    uint64_t     graph_launches = 0;       // kernels inside the instantiated graph
+    int64_t *    dyn_host = nullptr, * dyn_dev = nullptr;
+    int          dyn_used = 0;
+    static constexpr int DYN_CAP = 1024;
+    uint64_t     scratch_generation = 0;
+
     LaunchCtx launch_ctx() const { return LaunchCtx{stream, dev->device, dev->sm_count, status_dev, use_pdl}; }
     void *    get_scratch(size_t bytes);   // grows (after a stream sync) when needed
 };

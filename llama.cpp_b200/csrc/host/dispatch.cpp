@@ -123,6 +123,11 @@ bool device_supports_op(DeviceCtx * dev, const ggml_tensor * op) {
         ctx->n_launches++;                                                                  \
     } while (0)
 
+// can the int8 activation blocks of X be produced/kept in the per-graph cache?
+static bool act_cacheable(const ggml_tensor * X) {
+    return X->type == GGML_TYPE_F32 && t_contiguous(X) && X->ne[1] * X->ne[2] * X->ne[3] <= 8;
+}
+
 static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_tensor * ids) {
     const ggml_tensor * W = dst->src[0];
     const ggml_tensor * X = dst->src[1];
@@ -133,8 +138,19 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
     }
     const int64_t K = W->ne[0], M = W->ne[1];
     const int64_t ne11 = X->ne[1], ne12 = X->ne[2], ne13 = X->ne[3];
-    void * xq = ctx->get_scratch(act128_bytes(K, ne11 * ne12 * ne13));
-    RUN(launch_quantize_act128((const float *) X->data, ne11, ne12, ne13, X->nb[1] / 4, X->nb[2] / 4, X->nb[3] / 4, xq, (int) K, lc.stream));
+    void * xq = nullptr;
+    if (act_cacheable(X)) {
+        BackendCtx::ActEntry * e = ctx->act_cache_find(X->data, K, ne11 * ne12 * ne13);
+        if (!e) {
+            e = ctx->act_cache_take(X->data, K, ne11 * ne12 * ne13);
+            if (!e) return false;
+            RUN(launch_quantize_act128((const float *) X->data, ne11, ne12, ne13, X->nb[1] / 4, X->nb[2] / 4, X->nb[3] / 4, e->q, (int) K, lc.stream));
+        }
+        xq = e->q;
+    } else {
+        xq = ctx->get_scratch(act128_bytes(K, ne11 * ne12 * ne13));
+        RUN(launch_quantize_act128((const float *) X->data, ne11, ne12, ne13, X->nb[1] / 4, X->nb[2] / 4, X->nb[3] / 4, xq, (int) K, lc.stream));
+    }
 
     MmvqArgs a = {};
     a.type = W->type; a.W = W->data; a.w_nb1 = W->nb[1]; a.w_nb2 = W->nb[2]; a.w_nb3 = W->nb[3];
@@ -166,13 +182,32 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
     return true;
 }
 
-static bool run_node(BackendCtx * ctx, ggml_tensor * dst) {
+// does node `user` consume `t` as the activation operand of a quantized mat-mul?
+static bool feeds_quant_mul_mat(const ggml_cgraph * g, int from, const ggml_tensor * t) {
+    for (int i = from; i < g->n_nodes && i < from + 8; ++i) {
+        const ggml_tensor * n = g->nodes[i];
+        if (n->op == GGML_OP_MUL_MAT && n->src[1] == t && mmvq_type_supported(n->src[0]->type)) return true;
+    }
+    return false;
+}
+
+// Executes node i, fusing it with its successor where the graph allows:
+//   RMS_NORM -> MUL(x, w)        one launch; both outputs are written (the MUL result, and the plain
+//                                norm in case something else reads it), plus the int8 blocks of the
+//                                result when quantized mat-muls consume it
+//   UNARY(SILU) -> MUL(silu, up) likewise
+// Returns the number of nodes consumed, or 0 on failure.
+static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
+    ggml_tensor * dst = g->nodes[i];
     const LaunchCtx lc = ctx->launch_ctx();
     const ggml_tensor * a = dst->src[0];
     const ggml_tensor * b = dst->src[1];
+    auto fail = [&]() { return 0; };
+#define RUN0(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) { B200_LOG_ERROR("ggml-b200: %s failed: %s\n", #expr, cudaGetErrorString(e_)); return fail(); } ctx->n_launches++; } while (0)
+    ggml_tensor * next = i + 1 < g->n_nodes ? g->nodes[i + 1] : nullptr;
     switch (dst->op) {
-        case GGML_OP_MUL_MAT:    return run_mul_mat(ctx, dst, nullptr);
-        case GGML_OP_MUL_MAT_ID: return run_mul_mat(ctx, dst, dst->src[2]);
+        case GGML_OP_MUL_MAT:    return run_mul_mat(ctx, dst, nullptr) ? 1 : 0;
+        case GGML_OP_MUL_MAT_ID: return run_mul_mat(ctx, dst, dst->src[2]) ? 1 : 0;
         case GGML_OP_FLASH_ATTN_EXT: {
             const ggml_tensor * v = dst->src[2];
             const ggml_tensor * mask = dst->src[3];
@@ -181,64 +216,215 @@ static bool run_node(BackendCtx * ctx, ggml_tensor * dst) {
             TensorD md; if (mask) md = to_desc(mask);
             const size_t ws = fattn_workspace_bytes(qd, kd, lc.sm_count);
             void * wsp = ws ? ctx->get_scratch(ws) : nullptr;
-            RUN(launch_fattn(qd, kd, vd, mask ? &md : nullptr, dd, fp, wsp, lc));
+            if (ctx->capture_failed) return fail();
+            RUN0(launch_fattn(qd, kd, vd, mask ? &md : nullptr, dd, fp, wsp, lc));
             if (ws) ctx->n_launches++;
-            return true;
+            return 1;
         }
-        case GGML_OP_RMS_NORM: RUN(launch_rms_norm(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc)); return true;
-        case GGML_OP_NORM:     RUN(launch_norm(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc)); return true;
-        case GGML_OP_ADD: RUN(launch_bin_bcast(BIN_ADD, to_desc(a), to_desc(b), to_desc(dst), lc)); return true;
-        case GGML_OP_SUB: RUN(launch_bin_bcast(BIN_SUB, to_desc(a), to_desc(b), to_desc(dst), lc)); return true;
-        case GGML_OP_MUL: RUN(launch_bin_bcast(BIN_MUL, to_desc(a), to_desc(b), to_desc(dst), lc)); return true;
-        case GGML_OP_DIV: RUN(launch_bin_bcast(BIN_DIV, to_desc(a), to_desc(b), to_desc(dst), lc)); return true;
-        case GGML_OP_UNARY: RUN(launch_unary(unary_to_unop(op_param_i32(dst, 0)), to_desc(a), to_desc(dst), lc)); return true;
-        case GGML_OP_SQR:  RUN(launch_unary(UN_SQR, to_desc(a), to_desc(dst), lc)); return true;
-        case GGML_OP_SQRT: RUN(launch_unary(UN_SQRT, to_desc(a), to_desc(dst), lc)); return true;
-        case GGML_OP_SIN:  RUN(launch_unary(UN_SIN, to_desc(a), to_desc(dst), lc)); return true;
-        case GGML_OP_COS:  RUN(launch_unary(UN_COS, to_desc(a), to_desc(dst), lc)); return true;
-        case GGML_OP_LOG:  RUN(launch_unary(UN_LOG, to_desc(a), to_desc(dst), lc)); return true;
-        case GGML_OP_SCALE: RUN(launch_scale(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc)); return true;
-        case GGML_OP_CLAMP: RUN(launch_clamp(to_desc(a), to_desc(dst), op_param_f32(dst, 0), op_param_f32(dst, 1), lc)); return true;
+        case GGML_OP_RMS_NORM: {
+            if (next && next->op == GGML_OP_MUL && next->src[0] == dst && next->type == GGML_TYPE_F32 && next->src[1]->type == GGML_TYPE_F32 &&
+                next->src[1]->nb[0] == 4 && t_contiguous(next) && t_can_repeat(next->src[1], dst) && device_supports_op(ctx->dev, next)) {
+                void * act = nullptr;
+                if (act_cacheable(next) && next->ne[0] % 128 == 0 && feeds_quant_mul_mat(g, i + 2, next)) {
+                    BackendCtx::ActEntry * e = ctx->act_cache_take(next->data, next->ne[0], next->ne[1] * next->ne[2] * next->ne[3]);
+                    if (!e) return fail();
+                    act = e->q;
+                }
+                RUN0(launch_rms_norm_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), op_param_f32(dst, 0), act, (float *) dst->data, lc));
+                return 2;
+            }
+            RUN0(launch_rms_norm(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc));
+            return 1;
+        }
+        case GGML_OP_NORM: RUN0(launch_norm(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc)); return 1;
+        case GGML_OP_ADD: RUN0(launch_bin_bcast(BIN_ADD, to_desc(a), to_desc(b), to_desc(dst), lc)); return 1;
+        case GGML_OP_SUB: RUN0(launch_bin_bcast(BIN_SUB, to_desc(a), to_desc(b), to_desc(dst), lc)); return 1;
+        case GGML_OP_MUL: RUN0(launch_bin_bcast(BIN_MUL, to_desc(a), to_desc(b), to_desc(dst), lc)); return 1;
+        case GGML_OP_DIV: RUN0(launch_bin_bcast(BIN_DIV, to_desc(a), to_desc(b), to_desc(dst), lc)); return 1;
+        case GGML_OP_UNARY: {
+            const int uop = op_param_i32(dst, 0);
+            if (uop == GGML_UNARY_OP_SILU && next && next->op == GGML_OP_MUL && next->src[0] == dst && next->type == GGML_TYPE_F32 &&
+                next->src[1]->type == GGML_TYPE_F32 && t_same_shape(next->src[1], dst) && t_contiguous(next->src[1]) && t_contiguous(next)) {
+                void * act = nullptr;
+                if (act_cacheable(next) && next->ne[0] % 128 == 0 && feeds_quant_mul_mat(g, i + 2, next)) {
+                    BackendCtx::ActEntry * e = ctx->act_cache_take(next->data, next->ne[0], next->ne[1] * next->ne[2] * next->ne[3]);
+                    if (!e) return fail();
+                    act = e->q;
+                }
+                RUN0(launch_silu_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), act, (float *) dst->data, lc));
+                return 2;
+            }
+            RUN0(launch_unary(unary_to_unop(uop), to_desc(a), to_desc(dst), lc));
+            return 1;
+        }
+        case GGML_OP_SQR:  RUN0(launch_unary(UN_SQR, to_desc(a), to_desc(dst), lc)); return 1;
+        case GGML_OP_SQRT: RUN0(launch_unary(UN_SQRT, to_desc(a), to_desc(dst), lc)); return 1;
+        case GGML_OP_SIN:  RUN0(launch_unary(UN_SIN, to_desc(a), to_desc(dst), lc)); return 1;
+        case GGML_OP_COS:  RUN0(launch_unary(UN_COS, to_desc(a), to_desc(dst), lc)); return 1;
+        case GGML_OP_LOG:  RUN0(launch_unary(UN_LOG, to_desc(a), to_desc(dst), lc)); return 1;
+        case GGML_OP_SCALE: RUN0(launch_scale(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc)); return 1;
+        case GGML_OP_CLAMP: RUN0(launch_clamp(to_desc(a), to_desc(dst), op_param_f32(dst, 0), op_param_f32(dst, 1), lc)); return 1;
         case GGML_OP_ROPE: {
             RopeParams rp;
             rp.n_dims = op_param_i32(dst, 1); rp.mode = op_param_i32(dst, 2); rp.n_ctx_orig = op_param_i32(dst, 4);
             rp.freq_base = op_param_f32(dst, 5); rp.freq_scale = op_param_f32(dst, 6); rp.ext_factor = op_param_f32(dst, 7);
             rp.attn_factor = op_param_f32(dst, 8); rp.beta_fast = op_param_f32(dst, 9); rp.beta_slow = op_param_f32(dst, 10);
             const ggml_tensor * ff = dst->src[2];
-            RUN(launch_rope(to_desc(a), (const int32_t *) b->data, ff ? (const float *) ff->data : nullptr, to_desc(dst), rp, lc));
-            return true;
+            RUN0(launch_rope(to_desc(a), (const int32_t *) b->data, ff ? (const float *) ff->data : nullptr, to_desc(dst), rp, lc));
+            return 1;
         }
         case GGML_OP_CPY: case GGML_OP_DUP: case GGML_OP_CONT: {
             // CPY writes into src1's memory (dst is a view of it); DUP/CONT write dst
             const ggml_tensor * out = dst->op == GGML_OP_CPY ? b : dst;
-            if (a->type == out->type && t_contiguous(a) && t_contiguous(out)) {
-                RUN(cudaMemcpyAsync(out->data, a->data, t_nbytes(a), cudaMemcpyDeviceToDevice, lc.stream));
-            } else {
-                RUN(launch_cpy(to_desc(a), to_desc(out), lc));
+            if (ctx->capturing && dst->op == GGML_OP_CPY && out->view_src && out->view_src->data && ctx->dyn_used < BackendCtx::DYN_CAP) {
+                // a store into a view (the KV-cache rows of this token): the view's byte offset is read by the
+                // kernel from device memory, so the captured launch is independent of the token position
+                TensorD od = to_desc(out);
+                od.data = out->view_src->data;
+                ctx->dyn_host[ctx->dyn_used] = (int64_t) ((const char *) out->data - (const char *) out->view_src->data);
+                RUN0(launch_cpy(to_desc(a), od, lc, ctx->dyn_dev + ctx->dyn_used));
+                ctx->dyn_used++;
+                return 1;
             }
-            return true;
+            if (a->type == out->type && t_contiguous(a) && t_contiguous(out)) {
+                RUN0(cudaMemcpyAsync(out->data, a->data, t_nbytes(a), cudaMemcpyDeviceToDevice, lc.stream));
+            } else {
+                RUN0(launch_cpy(to_desc(a), to_desc(out), lc));
+            }
+            return 1;
         }
-        case GGML_OP_GET_ROWS: RUN(launch_get_rows(to_desc(a), to_desc(b), to_desc(dst), lc)); return true;
+        case GGML_OP_GET_ROWS: RUN0(launch_get_rows(to_desc(a), to_desc(b), to_desc(dst), lc)); return 1;
         case GGML_OP_SOFT_MAX: {
             TensorD md; if (b) md = to_desc(b);
-            RUN(launch_soft_max(to_desc(a), b ? &md : nullptr, to_desc(dst), op_param_f32(dst, 0), op_param_f32(dst, 1), lc));
-            return true;
+            RUN0(launch_soft_max(to_desc(a), b ? &md : nullptr, to_desc(dst), op_param_f32(dst, 0), op_param_f32(dst, 1), lc));
+            return 1;
         }
         default:
             B200_LOG_ERROR("ggml-b200: op %d reached graph_compute but is not supported\n", (int) dst->op);
-            return false;
+            return 0;
     }
+#undef RUN0
+}
+
+static bool is_noop(const ggml_tensor * node) {
+    return t_empty(node) || node->op == GGML_OP_NONE || node->op == GGML_OP_RESHAPE || node->op == GGML_OP_VIEW ||
+           node->op == GGML_OP_PERMUTE || node->op == GGML_OP_TRANSPOSE;
+}
+
+static bool run_all(BackendCtx * ctx, ggml_cgraph * cgraph) {
+    ctx->act_cache_clear();
+    for (int i = 0; i < cgraph->n_nodes;) {
+        ggml_tensor * node = cgraph->nodes[i];
+        if (is_noop(node)) { ++i; continue; }
+        ctx->act_cache_invalidate(node->data);
+        if (node->op == GGML_OP_CPY && node->src[1]) ctx->act_cache_invalidate(node->src[1]->data);
+        if (i + 1 < cgraph->n_nodes) ctx->act_cache_invalidate(cgraph->nodes[i + 1]->data);   // it may be fused into this launch
+        const int used = run_node(ctx, cgraph, i);
+        if (used == 0) return false;
+        i += used;
+    }
+    return true;
+}
+
+// ---------------------------------------------------------------------------
+// CUDA-graph replay for small-batch (decode) graphs
+// ---------------------------------------------------------------------------
+static inline uint64_t mix(uint64_t h, uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); return h * 0xff51afd7ed558ccdull; }
+
+// A CPY whose destination is a view: its position inside the viewed tensor may change from call to
+// call (the KV-cache write position) without invalidating a captured graph.
+static const ggml_tensor * dyn_cpy_dst(const ggml_tensor * node) {
+    if (node->op != GGML_OP_CPY) return nullptr;
+    const ggml_tensor * out = node->src[1];
+    return (out && out->view_src && out->view_src->data) ? out : nullptr;
+}
+
+// key over everything a captured launch sequence depends on; returns 0 when the graph is not a
+// candidate (a large batch, or nothing to run)
+static uint64_t graph_signature(BackendCtx * ctx, const ggml_cgraph * g, int * n_dyn) {
+    uint64_t h = mix(0x1234, ctx->scratch_generation);
+    int exec_nodes = 0, dyn = 0;
+    for (int i = 0; i < g->n_nodes; ++i) {
+        const ggml_tensor * n = g->nodes[i];
+        if (is_noop(n)) continue;
+        ++exec_nodes;
+        if ((n->op == GGML_OP_MUL_MAT || n->op == GGML_OP_MUL_MAT_ID) && n->src[1]->ne[1] * n->src[1]->ne[2] * n->src[1]->ne[3] > 8) return 0;
+        const ggml_tensor * dd = dyn_cpy_dst(n);
+        h = mix(h, (uint64_t) n->op | ((uint64_t) n->type << 32));
+        h = mix(h, dd ? (uint64_t) (uintptr_t) dd->view_src->data : (uint64_t) (uintptr_t) n->data);
+        if (dd) ++dyn;
+        for (int d = 0; d < 4; ++d) { h = mix(h, (uint64_t) n->ne[d]); h = mix(h, (uint64_t) n->nb[d]); }
+        const uint64_t * op = (const uint64_t *) n->op_params;
+        for (int d = 0; d < 8; ++d) h = mix(h, op[d]);
+        for (int s = 0; s < GGML_MAX_SRC && n->src[s]; ++s) {
+            const ggml_tensor * t = n->src[s];
+            const bool is_dyn_dst = dd && t == dd;
+            h = mix(h, is_dyn_dst ? (uint64_t) (uintptr_t) dd->view_src->data : (uint64_t) (uintptr_t) t->data);
+            h = mix(h, (uint64_t) t->type);
+            for (int d = 0; d < 4; ++d) { h = mix(h, (uint64_t) t->ne[d]); h = mix(h, (uint64_t) t->nb[d]); }
+        }
+    }
+    *n_dyn = dyn;
+    if (exec_nodes < 8 || dyn > BackendCtx::DYN_CAP) return 0;
+    return h ? h : 1;
 }
 
 enum ggml_status graph_compute(BackendCtx * ctx, ggml_cgraph * cgraph) {
-    for (int i = 0; i < cgraph->n_nodes; ++i) {
-        ggml_tensor * node = cgraph->nodes[i];
-        if (t_empty(node) || node->op == GGML_OP_NONE || node->op == GGML_OP_RESHAPE || node->op == GGML_OP_VIEW ||
-            node->op == GGML_OP_PERMUTE || node->op == GGML_OP_TRANSPOSE) {
-            continue;
-        }
-        if (!run_node(ctx, node)) return GGML_STATUS_FAILED;
+    int n_dyn = 0;
+    const uint64_t key = ctx->use_graphs ? graph_signature(ctx, cgraph, &n_dyn) : 0;
+    if (key == 0) {
+        ctx->pending_key = 0;
+        return run_all(ctx, cgraph) ? GGML_STATUS_SUCCESS : GGML_STATUS_FAILED;
     }
+    if (key == ctx->graph_key && ctx->graph_exec) {
+        // replay: refresh the token-dependent offsets, then one graph launch
+        int k = 0;
+        for (int i = 0; i < cgraph->n_nodes; ++i) {
+            const ggml_tensor * n = cgraph->nodes[i];
+            if (is_noop(n)) continue;
+            if (const ggml_tensor * dd = dyn_cpy_dst(n)) ctx->dyn_host[k++] = (int64_t) ((const char *) dd->data - (const char *) dd->view_src->data);
+        }
+        if (k) B200_CUDA_CHECK(cudaMemcpyAsync(ctx->dyn_dev, ctx->dyn_host, sizeof(int64_t) * k, cudaMemcpyHostToDevice, ctx->stream));
+        B200_CUDA_CHECK(cudaGraphLaunch(ctx->graph_exec, ctx->stream));
+        ctx->n_launches += ctx->graph_launches;
+        return GGML_STATUS_SUCCESS;
+    }
+    if (key != ctx->pending_key) {
+        // first sighting of this graph: run it directly (this also performs any lazy allocation and
+        // per-kernel attribute set-up); capture if it comes back
+        ctx->pending_key = key;
+        return run_all(ctx, cgraph) ? GGML_STATUS_SUCCESS : GGML_STATUS_FAILED;
+    }
+    // second sighting: capture
+    if (ctx->graph_exec) { cudaGraphExecDestroy(ctx->graph_exec); ctx->graph_exec = nullptr; ctx->graph_key = 0; }
+    ctx->capturing = true; ctx->capture_failed = false; ctx->dyn_used = 0;
+    const uint64_t launches_before = ctx->n_launches;
+    B200_CUDA_CHECK(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+    const bool ok = run_all(ctx, cgraph);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &graph);
+    ctx->capturing = false;
+    const uint64_t captured = ctx->n_launches - launches_before;
+    ctx->n_launches = launches_before;
+    if (!ok || ctx->capture_failed || ce != cudaSuccess || !graph) {
+        cudaGetLastError();
+        if (graph) cudaGraphDestroy(graph);
+        ctx->pending_key = 0;
+        B200_LOG_WARN("ggml-b200: CUDA graph capture abandoned, running the graph directly\n");
+        return run_all(ctx, cgraph) ? GGML_STATUS_SUCCESS : GGML_STATUS_FAILED;
+    }
+    cudaGraphExec_t exec = nullptr;
+    if (cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) {
+        cudaGetLastError();
+        cudaGraphDestroy(graph);
+        ctx->pending_key = 0;
+        return run_all(ctx, cgraph) ? GGML_STATUS_SUCCESS : GGML_STATUS_FAILED;
+    }
+    cudaGraphDestroy(graph);
+    ctx->graph_exec = exec; ctx->graph_key = key; ctx->graph_launches = captured;
+    if (ctx->dyn_used) B200_CUDA_CHECK(cudaMemcpyAsync(ctx->dyn_dev, ctx->dyn_host, sizeof(int64_t) * ctx->dyn_used, cudaMemcpyHostToDevice, ctx->stream));
+    B200_CUDA_CHECK(cudaGraphLaunch(ctx->graph_exec, ctx->stream));
+    ctx->n_launches += captured;
     return GGML_STATUS_SUCCESS;
 }
 

@@ -281,7 +281,7 @@ API int b200_rms_norm_host(const float * x, int64_t n_rows, int64_t k, float eps
     TensorD xd = desc(dx.p, T_F32, k, n_rows, 1, k * 4, k * 4 * n_rows), dd_ = desc(dd.p, T_F32, k, n_rows, 1, k * 4, k * 4 * n_rows);
     if (weight) {
         CK(cudaMemcpy(dw.p, weight, (size_t) k * 4, cudaMemcpyHostToDevice));
-        CK(launch_rms_norm_mul(xd, desc(dw.p, T_F32, k, 1, 1, k * 4, k * 4), dd_, eps, nullptr, lc));
+        CK(launch_rms_norm_mul(xd, desc(dw.p, T_F32, k, 1, 1, k * 4, k * 4), dd_, eps, nullptr, nullptr, lc));
     } else {
         CK(launch_rms_norm(xd, dd_, eps, lc));
     }
@@ -318,7 +318,7 @@ API int b200_silu_mul_host(const float * gate, const float * up, int64_t n, floa
     CK(cudaMemcpy(dg.p, gate, (size_t) n * 4, cudaMemcpyHostToDevice));
     CK(cudaMemcpy(du.p, up, (size_t) n * 4, cudaMemcpyHostToDevice));
     TensorD g = desc(dg.p, T_F32, n, 1, 1, n * 4, n * 4), u = desc(du.p, T_F32, n, 1, 1, n * 4, n * 4), d = desc(dd.p, T_F32, n, 1, 1, n * 4, n * 4);
-    CK(launch_silu_mul(g, u, d, nullptr, lc));
+    CK(launch_silu_mul(g, u, d, nullptr, nullptr, lc));
     CK(cudaDeviceSynchronize());
     CK(cudaMemcpy(dst, dd.p, (size_t) n * 4, cudaMemcpyDeviceToHost));
     return 0;

@@ -81,7 +81,7 @@ __device__ __forceinline__ void emit_act128(const float (&v)[4], int64_t k0, int
 // RMS_NORM (+ optional weight multiply, + optional activation quantization)
 // ---------------------------------------------------------------------------
 template <bool HAS_W, bool EMIT>
-__global__ void rms_norm_kernel(const TensorD src, const TensorD w, const TensorD dst, float eps, blk_act128 * act) {
+__global__ void rms_norm_kernel(const TensorD src, const TensorD w, const TensorD dst, float eps, blk_act128 * act, float * norm_out) {
     __shared__ float sh[32];
     const int64_t row = blockIdx.x;
     const int64_t i1 = row % src.ne[1], i2 = (row / src.ne[1]) % src.ne[2], i3 = row / (src.ne[1] * src.ne[2]);
@@ -94,9 +94,13 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
     const float scale = rsqrtf(ss / (float) n + eps);
     const float * wr = nullptr;
     if (HAS_W) wr = (const float *) ((const char *) w.data + (i1 % w.ne[1]) * w.nb[1] + (i2 % w.ne[2]) * w.nb[2] + (i3 % w.ne[3]) * w.nb[3]);
+    // norm_out: contiguous rows of the plain normalised values (the RMS_NORM node's own output when the
+    // following MUL is fused into this launch)
+    float * yn = norm_out ? norm_out + row * n : nullptr;
     if (!EMIT) {
         for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
             float v = x[i] * scale;
+            if (yn) yn[i] = v;
             if (HAS_W) v *= wr[i % w.ne[0]];
             y[i] = v;
         }
@@ -111,6 +115,7 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
                 v[i] = 0.0f;
                 if (k0 + i < n) {
                     v[i] = x[k0 + i] * scale;
+                    if (yn) yn[k0 + i] = v[i];
                     if (HAS_W) v[i] *= wr[(k0 + i) % w.ne[0]];
                     y[k0 + i] = v[i];
                 }
@@ -125,14 +130,14 @@ static int row_block(int64_t n) { return n >= 4096 ? 1024 : (n >= 1024 ? 512 : (
 cudaError_t launch_rms_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c) {
     const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
     if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
-    rms_norm_kernel<false, false><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, src, dst, eps, nullptr);
+    rms_norm_kernel<false, false><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, src, dst, eps, nullptr, nullptr);
     return B200_LAUNCH_CHECK();
 }
-cudaError_t launch_rms_norm_mul(const TensorD & src, const TensorD & w, const TensorD & dst, float eps, void * act, const LaunchCtx & c) {
+cudaError_t launch_rms_norm_mul(const TensorD & src, const TensorD & w, const TensorD & dst, float eps, void * act, float * norm_out, const LaunchCtx & c) {
     const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
     if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
-    if (act) rms_norm_kernel<true, true><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, w, dst, eps, (blk_act128 *) act);
-    else     rms_norm_kernel<true, false><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, w, dst, eps, nullptr);
+    if (act) rms_norm_kernel<true, true><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, w, dst, eps, (blk_act128 *) act, norm_out);
+    else     rms_norm_kernel<true, false><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, w, dst, eps, nullptr, norm_out);
     return B200_LAUNCH_CHECK();
 }
 
@@ -300,7 +305,7 @@ cudaError_t launch_clamp(const TensorD & src, const TensorD & dst, float lo, flo
 // silu(gate) * up on contiguous F32 rows, optionally emitting activation blocks
 template <bool EMIT>
 __global__ void silu_mul_kernel(const float * __restrict__ g, const float * __restrict__ u, float * __restrict__ y,
-                                int64_t n0, int64_t rows, blk_act128 * act) {
+                                int64_t n0, int64_t rows, blk_act128 * act, float * __restrict__ silu_out) {
     const int64_t npad = (n0 + 127) & ~(int64_t) 127;
     const int64_t per_row = npad / 4;
     const int64_t total = per_row * rows;
@@ -314,7 +319,9 @@ __global__ void silu_mul_kernel(const float * __restrict__ g, const float * __re
             for (int i = 0; i < 4; ++i) {
                 if (k0 + i < n0) {
                     const float a = g[row * n0 + k0 + i];
-                    v[i] = (a / (1.0f + expf(-a))) * u[row * n0 + k0 + i];
+                    const float sa = a / (1.0f + expf(-a));
+                    if (silu_out) silu_out[row * n0 + k0 + i] = sa;
+                    v[i] = sa * u[row * n0 + k0 + i];
                     y[row * n0 + k0 + i] = v[i];
                 }
             }
@@ -322,14 +329,14 @@ __global__ void silu_mul_kernel(const float * __restrict__ g, const float * __re
         if (EMIT) emit_act128(v, t < total ? k0 : npad, npad, act + (t < total ? row : 0) * (npad >> 7));
     }
 }
-cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const TensorD & dst, void * act, const LaunchCtx & c) {
+cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const TensorD & dst, void * act, float * silu_out, const LaunchCtx & c) {
     const int64_t n0 = gate.ne[0], rows = nelem(gate) / (n0 ? n0 : 1);
     if (n0 == 0 || rows == 0) return cudaSuccess;
     const int64_t threads = ((n0 + 127) / 128 * 32) * rows;
     if (act) silu_mul_kernel<true><<<grid_for(threads, 256, c.sm_count), 256, 0, c.stream>>>(
-                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, (blk_act128 *) act);
+                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, (blk_act128 *) act, silu_out);
     else     silu_mul_kernel<false><<<grid_for(threads, 256, c.sm_count), 256, 0, c.stream>>>(
-                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, nullptr);
+                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, nullptr, silu_out);
     return B200_LAUNCH_CHECK();
 }
 
@@ -403,7 +410,8 @@ cudaError_t launch_rope(const TensorD & src, const int32_t * pos, const float * 
 // ---------------------------------------------------------------------------
 // CPY / DUP / CONT
 // ---------------------------------------------------------------------------
-__global__ void cpy_elem_kernel(const TensorD s, const TensorD d, int64_t total) {
+__global__ void cpy_elem_kernel(const TensorD s, const TensorD d, int64_t total, const int64_t * __restrict__ dyn_off) {
+    const int64_t doff = dyn_off ? *dyn_off : 0;   // byte offset of the destination view, kept in device memory so a captured launch stays valid
     for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
         int64_t r = i;
         const int64_t s0 = r % s.ne[0]; r /= s.ne[0];
@@ -414,7 +422,7 @@ __global__ void cpy_elem_kernel(const TensorD s, const TensorD d, int64_t total)
         const int64_t d1 = r % d.ne[1]; r /= d.ne[1];
         const int64_t d2 = r % d.ne[2]; const int64_t d3 = r / d.ne[2];
         const char * ps = (const char *) s.data + s0 * s.nb[0] + s1 * s.nb[1] + s2 * s.nb[2] + s3 * s.nb[3];
-        char *       pd = (char *) d.data + d0 * d.nb[0] + d1 * d.nb[1] + d2 * d.nb[2] + d3 * d.nb[3];
+        char *       pd = (char *) d.data + doff + d0 * d.nb[0] + d1 * d.nb[1] + d2 * d.nb[2] + d3 * d.nb[3];
         if (s.type == d.type) {
             if (s.type == T_F32 || s.type == T_I32) *(uint32_t *) pd = *(const uint32_t *) ps;
             else *(uint16_t *) pd = *(const uint16_t *) ps;
@@ -501,8 +509,9 @@ __device__ void quantize_block32(const float * x, uint8_t * out) {
 }
 
 template <int QT>
-__global__ void cpy_f32_q_kernel(const TensorD s, const TensorD d, int64_t nblocks) {
+__global__ void cpy_f32_q_kernel(const TensorD s, const TensorD d, int64_t nblocks, const int64_t * __restrict__ dyn_off) {
     const int bb = type_block_bytes(QT);
+    const int64_t doff = dyn_off ? *dyn_off : 0;
     for (int64_t ib = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; ib < nblocks; ib += (int64_t) gridDim.x * blockDim.x) {
         // element index of the first value of this block, in src order
         int64_t r = ib * 32;
@@ -514,7 +523,7 @@ __global__ void cpy_f32_q_kernel(const TensorD s, const TensorD d, int64_t nbloc
         const int64_t d1 = r % d.ne[1]; r /= d.ne[1];
         const int64_t d2 = r % d.ne[2]; const int64_t d3 = r / d.ne[2];
         const char * ps = (const char *) s.data + s0 * s.nb[0] + s1 * s.nb[1] + s2 * s.nb[2] + s3 * s.nb[3];
-        char *       pd = (char *) d.data + (d0 / 32) * bb + d1 * d.nb[1] + d2 * d.nb[2] + d3 * d.nb[3];
+        char *       pd = (char *) d.data + doff + (d0 / 32) * bb + d1 * d.nb[1] + d2 * d.nb[2] + d3 * d.nb[3];
         float v[32];
         for (int j = 0; j < 32; ++j) v[j] = *(const float *) (ps + j * s.nb[0]);
         quantize_block32<QT>(v, (uint8_t *) pd);
@@ -529,23 +538,23 @@ bool cpy_supported(int st, int dt) {
     return false;
 }
 
-cudaError_t launch_cpy(const TensorD & s, const TensorD & d, const LaunchCtx & c) {
+cudaError_t launch_cpy(const TensorD & s, const TensorD & d, const LaunchCtx & c, const int64_t * dyn_off) {
     const int64_t total = nelem(s);
     if (total == 0) return cudaSuccess;
     if (type_block_elems(d.type) == 32) {
         const int64_t nb = total / 32;
         const unsigned g = grid_for(nb, 128, c.sm_count);
         switch (d.type) {
-            case T_Q8_0: cpy_f32_q_kernel<T_Q8_0><<<g, 128, 0, c.stream>>>(s, d, nb); break;
-            case T_Q4_0: cpy_f32_q_kernel<T_Q4_0><<<g, 128, 0, c.stream>>>(s, d, nb); break;
-            case T_Q4_1: cpy_f32_q_kernel<T_Q4_1><<<g, 128, 0, c.stream>>>(s, d, nb); break;
-            case T_Q5_0: cpy_f32_q_kernel<T_Q5_0><<<g, 128, 0, c.stream>>>(s, d, nb); break;
-            case T_Q5_1: cpy_f32_q_kernel<T_Q5_1><<<g, 128, 0, c.stream>>>(s, d, nb); break;
+            case T_Q8_0: cpy_f32_q_kernel<T_Q8_0><<<g, 128, 0, c.stream>>>(s, d, nb, dyn_off); break;
+            case T_Q4_0: cpy_f32_q_kernel<T_Q4_0><<<g, 128, 0, c.stream>>>(s, d, nb, dyn_off); break;
+            case T_Q4_1: cpy_f32_q_kernel<T_Q4_1><<<g, 128, 0, c.stream>>>(s, d, nb, dyn_off); break;
+            case T_Q5_0: cpy_f32_q_kernel<T_Q5_0><<<g, 128, 0, c.stream>>>(s, d, nb, dyn_off); break;
+            case T_Q5_1: cpy_f32_q_kernel<T_Q5_1><<<g, 128, 0, c.stream>>>(s, d, nb, dyn_off); break;
             default: return cudaErrorInvalidValue;
         }
         return B200_LAUNCH_CHECK();
     }
-    cpy_elem_kernel<<<grid_for(total, 256, c.sm_count), 256, 0, c.stream>>>(s, d, total);
+    cpy_elem_kernel<<<grid_for(total, 256, c.sm_count), 256, 0, c.stream>>>(s, d, total, dyn_off);
     return B200_LAUNCH_CHECK();
 }
 

@@ -64,13 +64,14 @@ enum UnOp  { UN_SILU = 0, UN_GELU, UN_GELU_QUICK, UN_RELU, UN_TANH, UN_SIGMOID, 
 
 cudaError_t launch_rms_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c);
 // y = rms_norm(x) * w   (w broadcast like ggml MUL's src1); optionally also emits blk_act128 of y
+// norm_out (optional): contiguous rows receiving the plain rms_norm(x)
 cudaError_t launch_rms_norm_mul(const TensorD & src, const TensorD & w, const TensorD & dst, float eps,
-                                void * act128_out, const LaunchCtx & c);
+                                void * act128_out, float * norm_out, const LaunchCtx & c);
 cudaError_t launch_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c);
 cudaError_t launch_bin_bcast(int op, const TensorD & a, const TensorD & b, const TensorD & dst, const LaunchCtx & c);
 cudaError_t launch_unary(int op, const TensorD & src, const TensorD & dst, const LaunchCtx & c);
 // dst = silu(gate) * up, optionally also emitting blk_act128 of dst
-cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const TensorD & dst, void * act128_out, const LaunchCtx & c);
+cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const TensorD & dst, void * act128_out, float * silu_out, const LaunchCtx & c);
 cudaError_t launch_scale(const TensorD & src, const TensorD & dst, float scale, const LaunchCtx & c);
 cudaError_t launch_clamp(const TensorD & src, const TensorD & dst, float lo, float hi, const LaunchCtx & c);
 
@@ -82,7 +83,8 @@ cudaError_t launch_rope(const TensorD & src, const int32_t * pos, const float * 
                         const RopeParams & rp, const LaunchCtx & c);
 
 bool        cpy_supported(int src_type, int dst_type);
-cudaError_t launch_cpy(const TensorD & src, const TensorD & dst, const LaunchCtx & c);
+// dyn_off (optional, device pointer): byte offset added to dst.data, read by the kernel at run time
+cudaError_t launch_cpy(const TensorD & src, const TensorD & dst, const LaunchCtx & c, const int64_t * dyn_off = nullptr);
 
 bool        get_rows_supported(int src_type);
 cudaError_t launch_get_rows(const TensorD & src, const TensorD & idx, const TensorD & dst, const LaunchCtx & c);

@@ -45,6 +45,9 @@ cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream);
 // direct 128-bit-coalesced variant for Q4_K / Q5_K (mmvq_k.cu); launch_mmvq routes to it when applicable
 bool        mmvq_k_applicable(const MmvqArgs & a);
 cudaError_t launch_mmvq_k(const MmvqArgs & a, cudaStream_t stream);
+// warp-staged variant for Q6_K (mmvq_q6k.cu)
+bool        mmvq_q6k_applicable(const MmvqArgs & a);
+cudaError_t launch_mmvq_q6k(const MmvqArgs & a, cudaStream_t stream);
 
 // ---- float mat-mul for F32/F16/BF16 weights (matmul_f.cu) ----
 // dst[i3][i2][n][m] = sum_k W[..][m][k] * X[i3][i2][n][k]; W broadcast over dims 2,3

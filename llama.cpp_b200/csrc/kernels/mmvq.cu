@@ -567,6 +567,7 @@ cudaError_t launch_quantize_act128(const float * x, int64_t ne11, int64_t ne12, 
 
 cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream) {
     if (mmvq_k_applicable(a)) return launch_mmvq_k(a, stream);
+    if (mmvq_q6k_applicable(a)) return launch_mmvq_q6k(a, stream);
     MmvqParams p = {};
     p.W = (const uint8_t *) a.W; p.w_nb1 = a.w_nb1; p.w_nb2 = a.w_nb2; p.w_nb3 = a.w_nb3;
     p.Xq = (const uint8_t *) a.Xq; p.xq_col_bytes = (int64_t) ((a.K + 127) / 128) * 160;

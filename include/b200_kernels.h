@@ -58,6 +58,32 @@ int    b200_mul_mat_vec_q(int type, const void * W, int64_t w_row_stride_bytes, 
                           const void * xq, int64_t N, float * dst, int64_t dst_col_stride_elems, void * stream);
 int    b200_mul_mat_q_host(int type, const void * W, int64_t M, int64_t K, const float * X, int64_t N, float * dst);
 
+/* ---- MUL_MAT without any allocation --------------------------------------
+ * No counterpart in the reference: an addition of this library.
+ *
+ * Some callers cannot allocate device memory at the point where they need the product: a
+ * real-time serving loop with a frozen memory budget, a plugin host that forbids cudaMalloc after
+ * start-up, or a process whose device allocator is owned by another framework.  b200_mul_mat_q needs a caller-provided scratch buffer for the int8 activation
+ * blocks; this variant keeps that scratch inside the library instead, in a fixed device array of
+ * B200_NOALLOC_SCRATCH_BYTES that every GPU loading the library holds until the process exits.
+ * The caller passes only inputs and outputs (device pointers).  The call makes no cudaMalloc,
+ * cudaFree or allocating library call.
+ *
+ *  - Limits: N <= 8 columns and b200_act_bytes(K, N) <= B200_NOALLOC_SCRATCH_BYTES (e.g. K up to
+ *    104857 at N = 8); anything larger is rejected with B200_E_SCRATCH / B200_E_UNSUPPORTED and a
+ *    message from b200_noalloc_last_error().
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current) and clears a status word; make that first call before any stream capture begins.
+ *  - All calls on a device share the one array, which keeps whatever the last call wrote.  The
+ *    kernels overwrite the part they use before reading it, so no clearing is needed between
+ *    calls; but two calls that overlap on the GPU (different streams, no ordering) race on it.
+ *  - Asynchronous on `stream`; same arithmetic and results as b200_mul_mat_q for N <= 8.        */
+#define B200_NOALLOC_SCRATCH_BYTES (1u << 20)
+int          b200_mul_mat_q_noalloc(int type, const void * W, int64_t w_row_stride_bytes, int64_t M, int64_t K,
+                                    const float * X, int64_t x_col_stride_elems, int64_t N,
+                                    float * dst, int64_t dst_col_stride_elems, void * stream);
+const char * b200_noalloc_last_error(void);
+
 /* ---- FLASH_ATTN_EXT -------------------------------------------------------
  * GGML_OP_FLASH_ATTN_EXT (ggml_flash_attn_ext, ggml/src/ggml.c:4306-4345; CPU
  * semantics ggml/src/ggml-cpu/ggml-cpu.c:10916-11129).  q F32 [D, n_q, n_head],

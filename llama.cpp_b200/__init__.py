@@ -28,6 +28,7 @@ EXPORTS = [
     "b200_device_count", "b200_last_error", "b200_row_size",
     "b200_mul_mat_q_scratch_bytes", "b200_mul_mat_q", "b200_mul_mat_q_host",
     "b200_act_bytes", "b200_quantize_act", "b200_mul_mat_vec_q",
+    "b200_mul_mat_q_noalloc", "b200_noalloc_last_error",
     "b200_flash_attn_scratch_bytes", "b200_flash_attn", "b200_flash_attn_host",
     "b200_dequantize_rows_host", "b200_get_rows_host", "b200_quantize_rows_host", "b200_f32_to_f16_host",
     "b200_rms_norm_host", "b200_rope_host", "b200_silu_mul_host", "b200_soft_max_host",
@@ -74,6 +75,8 @@ def lib() -> C.CDLL:
         l.b200_act_bytes.argtypes = [i64, i64]
         l.b200_quantize_act.argtypes = [vp, i64, i64, i64, vp, vp]
         l.b200_mul_mat_vec_q.argtypes = [C.c_int, vp, i64, i64, i64, vp, i64, vp, i64, vp]
+        l.b200_mul_mat_q_noalloc.argtypes = [C.c_int, vp, i64, i64, i64, vp, i64, i64, vp, i64, vp]
+        l.b200_noalloc_last_error.restype = C.c_char_p
         l.b200_flash_attn_scratch_bytes.restype = sz
         l.b200_flash_attn_scratch_bytes.argtypes = [i64, i64, i64, i64]
         l.b200_flash_attn.argtypes = [vp, i64, i64, vp, i64, i64, vp, i64, i64, vp, i64, vp,

@@ -340,6 +340,7 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t dev, const char * /*pa
     // pageable on purpose: cudaMemcpyAsync then snapshots the values at call time, so the next call may overwrite them
     ctx->dyn_host = (int64_t *) malloc(sizeof(int64_t) * BackendCtx::DYN_CAP);
     ctx->use_graphs = getenv("GGML_B200_GRAPHS") ? atoi(getenv("GGML_B200_GRAPHS")) : 1;
+    ctx->use_tc = getenv("GGML_B200_TC") ? atoi(getenv("GGML_B200_TC")) : 1;
     const char * pdl = getenv("GGML_B200_PDL");
     ctx->use_pdl = pdl ? atoi(pdl) : 0;
     ctx->trace = getenv("GGML_B200_TRACE") ? atoi(getenv("GGML_B200_TRACE")) : 0;

@@ -38,6 +38,7 @@ struct BackendCtx {
     size_t       scratch_size = 0;
     cudaEvent_t  copy_event = nullptr;
     int          use_pdl = 0;
+    int          use_tc = 1;                // tensor-core GEMM for N > 8 (GGML_B200_TC=0 falls back to the mat-vec kernel)
     int          trace = 0;
     uint64_t     n_launches = 0;           // kernels launched by graph_compute since creation
     std::string  name;

@@ -138,6 +138,21 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
     }
     const int64_t K = W->ne[0], M = W->ne[1];
     const int64_t ne11 = X->ne[1], ne12 = X->ne[2], ne13 = X->ne[3];
+    if (!ids && ctx->use_tc && mmq_tc_supported(W->type, M, ne11, K) && mmq_tc_ptr_ok(W->type, W->data, W->nb[1], X->data, X->nb[1]) &&
+        W->nb[2] % 16 == 0 && W->nb[3] % 16 == 0 && X->nb[2] % 8 == 0 && X->nb[3] % 8 == 0) {
+        // prefill: tensor-core GEMM per 2-D slice (weights broadcast over the batch dims)
+        void * ws = ctx->get_scratch(mmq_tc_workspace_bytes(ne11, K));
+        if (ctx->capture_failed) return false;
+        const int64_t r2 = ne12 / W->ne[2], r3 = ne13 / W->ne[3];
+        for (int64_t i13 = 0; i13 < ne13; ++i13) for (int64_t i12 = 0; i12 < ne12; ++i12) {
+            const char * w = (const char *) W->data + (i12 / r2) * W->nb[2] + (i13 / r3) * W->nb[3];
+            const char * x = (const char *) X->data + i12 * X->nb[2] + i13 * X->nb[3];
+            char * d = (char *) dst->data + i12 * dst->nb[2] + i13 * dst->nb[3];
+            RUN(launch_mmq_tc(W->type, w, W->nb[1], (const float *) x, X->nb[1], (float *) d, dst->nb[1], M, ne11, K, ws, lc));
+            ctx->n_launches++;
+        }
+        return true;
+    }
     void * xq = nullptr;
     if (act_cacheable(X)) {
         BackendCtx::ActEntry * e = ctx->act_cache_find(X->data, K, ne11 * ne12 * ne13);

@@ -99,7 +99,7 @@ API int b200_mul_mat_q(int type, const void * W, int64_t w_nb1, int64_t M, int64
     if (K <= 0 || M <= 0 || N <= 0 || K % type_block_elems(type) != 0) return fail(B200_E_BAD_ARG, "bad shape");
     if (scratch_bytes < b200_mul_mat_q_scratch_bytes(type, M, K, N)) return fail(B200_E_SCRATCH, "scratch buffer too small");
     LaunchCtx lc; int rc = get_ctx(stream, lc); if (rc) return rc;
-    if (mmq_tc_supported(type, M, N, K)) {
+    if (mmq_tc_supported(type, M, N, K) && mmq_tc_ptr_ok(type, W, w_nb1, X, x_stride * 4)) {
         CK(launch_mmq_tc(type, W, w_nb1, X, x_stride * 4, dst, dst_stride * 4, M, N, K, scratch, lc));
         return 0;
     }

@@ -56,6 +56,7 @@ cudaError_t launch_matmul_f(const TensorD & W, const TensorD & X, const TensorD 
 // ---- prefill quantized GEMM on tcgen05 (mmq_tc.cu) ----
 bool        mmq_tc_supported(int type, int64_t M, int64_t N, int64_t K);
 size_t      mmq_tc_workspace_bytes(int64_t N, int64_t K);
+bool        mmq_tc_ptr_ok(int type, const void * W, int64_t w_nb1, const void * X, int64_t x_nb1_bytes);
 cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float * X, int64_t x_nb1,
                           float * dst, int64_t dst_nb1, int64_t M, int64_t N, int64_t K,
                           void * workspace, const LaunchCtx & c);

@@ -232,8 +232,9 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
             const size_t ws = fattn_workspace_bytes(qd, kd, lc.sm_count);
             void * wsp = ws ? ctx->get_scratch(ws) : nullptr;
             if (ctx->capture_failed) return fail();
-            RUN0(launch_fattn(qd, kd, vd, mask ? &md : nullptr, dd, fp, wsp, lc));
-            if (ws) ctx->n_launches++;
+            int nk = 1;
+            RUN0(launch_fattn(qd, kd, vd, mask ? &md : nullptr, dd, fp, wsp, lc, &nk));
+            ctx->n_launches += nk - 1;                               // second kernel: split-KV combine or mask-tile flags
             return 1;
         }
         case GGML_OP_RMS_NORM: {

@@ -166,7 +166,9 @@ static int fattn_pick_splits(int64_t rows, int64_t n_kv, int sm_count) {
 size_t fattn_workspace_bytes(const TensorD & q, const TensorD & k, int sm_count) {
     const int64_t rows = q.ne[1] * q.ne[2] * q.ne[3];
     const int splits = fattn_pick_splits(rows, k.ne[1], sm_count);
-    return splits > 1 ? (size_t) rows * splits * (q.ne[0] + 2) * sizeof(float) : 0;
+    const size_t vec = splits > 1 ? (size_t) rows * splits * (q.ne[0] + 2) * sizeof(float) : 0;
+    const size_t mma = fattn_mma_workspace_bytes(q, k);
+    return vec > mma ? vec : mma;
 }
 
 template <int D>
@@ -183,9 +185,13 @@ static cudaError_t fattn_launch_d(const FaK & p, int64_t rows, int n3, const Lau
 }
 
 cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
-                         const FattnParams & fp, void * workspace, const LaunchCtx & c) {
+                         const FattnParams & fp, void * workspace, const LaunchCtx & c, int * n_kernels) {
     const int64_t D = q.ne[0], rows = q.ne[1] * q.ne[2] * q.ne[3];
     if (rows == 0) return cudaSuccess;
+    if (fattn_mma_applicable(q, k, v, mask)) {
+        if (n_kernels) *n_kernels = mask ? 2 : 1;
+        return launch_fattn_mma(q, k, v, mask, dst, fp, workspace, c);
+    }
     FaK p = {};
     p.q = (const char *) q.data; p.q_nb1 = q.nb[1]; p.q_nb2 = q.nb[2]; p.q_nb3 = q.nb[3];
     p.k = (const char *) k.data; p.k_nb1 = k.nb[1]; p.k_nb2 = k.nb[2]; p.k_nb3 = k.nb[3];
@@ -196,6 +202,7 @@ cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v
     p.gqa = (int) (q.ne[2] / k.ne[2]); p.q3_per_k3 = (int) (q.ne[3] / k.ne[3]);
     p.n_splits = fattn_pick_splits(rows, k.ne[1], c.sm_count);
     p.kv_per_split = (int) (((k.ne[1] + p.n_splits - 1) / p.n_splits + 31) / 32 * 32);
+    if (n_kernels) *n_kernels = p.n_splits > 1 ? 2 : 1;
     p.scale = fp.scale; p.softcap = fp.logit_softcap; p.max_bias = fp.max_bias;
     if (p.softcap != 0.0f) p.scale /= p.softcap;
     int nh2 = 1; while (nh2 * 2 <= p.n_head) nh2 *= 2;

@@ -100,7 +100,13 @@ cudaError_t launch_soft_max(const TensorD & src, const TensorD * mask, const Ten
 struct FattnParams { float scale, max_bias, logit_softcap; };
 bool        fattn_supported(int64_t head_dim, int k_type, int v_type);
 size_t      fattn_workspace_bytes(const TensorD & q, const TensorD & k, int sm_count);
+// tensor-core kernel for batches of queries (fattn_mma.cu); launch_fattn routes to it when applicable
+bool        fattn_mma_applicable(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask);
+size_t      fattn_mma_workspace_bytes(const TensorD & q, const TensorD & k);
+cudaError_t launch_fattn_mma(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
+                             const FattnParams & fp, void * workspace, const LaunchCtx & c);
+// n_kernels (optional) receives the number of kernels launched
 cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
-                         const FattnParams & fp, void * workspace, const LaunchCtx & c);
+                         const FattnParams & fp, void * workspace, const LaunchCtx & c, int * n_kernels = nullptr);
 
 }  // namespace b200

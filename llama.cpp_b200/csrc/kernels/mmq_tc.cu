@@ -9,26 +9,32 @@
 // dequantized to F16 on its way into shared memory (exact up to the F16 rounding of d*q), and one
 // FP32 accumulator in TMEM runs over the whole K with tcgen05.mma kind::f16.
 //
-// CTA = 5 warps, one 128 (weight rows) x 128 (tokens) output tile:
-//   warps 0-3  producers: thread r dequantizes 64 consecutive weights of weight row r and copies 64
-//              F16 activations of token r per k-step, writing both operand tiles in the canonical
-//              K-major SWIZZLE_128B layout (row r at r*128 B, 16-byte chunk c at position c ^ (r & 7));
-//              then fence.proxy.async + mbarrier arrive.  After the K loop they become the epilogue:
-//              tcgen05.ld of the accumulator (lane = weight row, column = token) and coalesced stores.
-//   warp 4     one elected thread issues 4 x tcgen05.mma (M128 N128 K16) per k-step from shared-memory
-//              matrix descriptors, tcgen05.commit frees the stage / publishes the accumulator.
+// CTA = 9 warps, one 128 (weight rows) x 128 (tokens) output tile:
+//   warps 0-7  producers: thread (r, h) dequantizes 32 consecutive weights of weight row r per k-step
+//              (raw quant bytes of the next k-step are prefetched into registers first) and writes them
+//              as F16 in the canonical K-major SWIZZLE_128B layout (row r at r*128 B, 16-byte chunk c at
+//              position c ^ (r & 7)); then fence.proxy.async + mbarrier arrive.  The activation tile
+//              (128 tokens x 64 F16, pre-converted) is fetched by one plain, non-multicast TMA tile load
+//              with the same swizzle, completing on the same barrier.  After the K loop the producer
+//              warps become the epilogue: tcgen05.ld of the accumulator (lane = weight row, column =
+//              token; warps w and w+4 share a lane quadrant and split the columns) and coalesced stores.
+//   warp 8     one elected thread issues 4 x tcgen05.mma (M128 N128 K16) per k-step from shared-memory
+//              matrix descriptors; tcgen05.commit frees the stage / publishes the accumulator.
 // 4-stage ring of 32 KB stages; every mbarrier wait is bounded and failure is reported through the
-// status word; TMEM (128 columns) is allocated and released by warp 4 on every path.
+// status word; TMEM (128 columns) is allocated and released by warp 8 on every path.
 #include "common.cuh"
 #include "kernels.h"
+#include <cuda.h>
 
 namespace b200 {
 
 static constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
 static constexpr int TC_STAGES = 4;
 static constexpr int TC_STAGE_BYTES = (TC_BM + TC_BN) * TC_BK * 2;      // 32 KB
-static constexpr int TC_THREADS = 160;
+static constexpr int TC_PRODUCERS = 256;
+static constexpr int TC_THREADS = TC_PRODUCERS + 32;
 static constexpr int TC_TMEM_COLS = 128;
+static constexpr int TC_PF = 4;                                        // k-steps of raw weight bytes in flight per producer thread
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t * smem_dst, uint32_t ncols) {
@@ -80,67 +86,127 @@ __device__ __forceinline__ constexpr uint32_t umma_idesc_f16(int M, int N) {
     return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t) (N >> 3) << 17) | ((uint32_t) (M >> 4) << 24);
 }
 
-// ---- weight dequantization: 64 consecutive values of one row as F16 ---------------------------
+// ---- weight dequantization: 32 consecutive values of one row as F16 ---------------------------
+// Raw<T> holds the quant bytes a thread needs for its 32 values of one k-step; load() only issues the
+// loads (so the next k-step can be in flight while the current one is converted), get() converts.
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     __half2 h = __floats2half2_rn(a, b);
     return *(uint32_t *) &h;
 }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *(__half2 *) &v; }
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *(uint32_t *) &v; }
+// bytes (b0, b1) or (b2, b3) of v, each 0..255, as half2 (exact): 0x6400 | b is the F16 number 1024 + b
+__device__ __forceinline__ __half2 bytes01_h2(uint32_t v) { return __hsub2(u32_as_h2(__byte_perm(v, 0x64646464u, 0x4140)), u32_as_h2(0x64006400u)); }
+__device__ __forceinline__ __half2 bytes23_h2(uint32_t v) { return __hsub2(u32_as_h2(__byte_perm(v, 0x64646464u, 0x4342)), u32_as_h2(0x64006400u)); }
 
-template <int T> struct Deq64;     // get(row, k0, out[32]): out = 64 F16 values k0 .. k0+63 (k0 % 64 == 0)
+template <int T> struct Deq32 {                     // generic path: element-wise through the bit-exact dequantizer
+    struct Raw { const uint8_t * row; int k; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) { r.row = row; r.k = k; }
+    static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) out[i] = pack_h2(dequant_elem<T>(r.row, r.k + 2 * i), dequant_elem<T>(r.row, r.k + 2 * i + 1));
+    }
+};
 
-template <> struct Deq64<T_Q4_K> {
-    static __device__ __forceinline__ void get(const uint8_t * row, int k0, uint32_t (&out)[32]) {
-        const uint8_t * b = row + (k0 >> 8) * 144;
-        const int j = (k0 >> 6) & 3;
-        const uint4 hd = __ldg((const uint4 *) b);
-        const float2 dm = __half22float2(*(const __half2 *) &hd.x);
-        const uint8_t * sc = (const uint8_t *) &hd.y;
-        int s0, m0, s1, m1;
-        k4_scale_min(2 * j, sc, s0, m0);
-        k4_scale_min(2 * j + 1, sc, s1, m1);
-        const float d0 = dm.x * s0, n0 = dm.y * m0, d1 = dm.x * s1, n1 = dm.y * m1;
-        const uint4 qa = __ldg((const uint4 *) (b + 16 + 32 * j)), qb = __ldg((const uint4 *) (b + 32 + 32 * j));
-        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+// Q4_K: k .. k+31 is one sub-block sb = (k >> 5) & 7: nibble (sb & 1) of qs bytes [32 (sb >> 1), +32)
+template <> struct Deq32<T_Q4_K> {
+    struct Raw { uint4 hd, qa, qb; int sb; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
+        const uint8_t * b = row + (k >> 8) * 144;
+        r.sb = (k >> 5) & 7;
+        r.hd = __ldg((const uint4 *) b);
+        r.qa = __ldg((const uint4 *) (b + 16 + 32 * (r.sb >> 1)));
+        r.qb = __ldg((const uint4 *) (b + 32 + 32 * (r.sb >> 1)));
+    }
+    static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
+        const float2 dm = __half22float2(u32_as_h2(r.hd.x));
+        const uint32_t s0 = r.hd.y, s1 = r.hd.z, s2 = r.hd.w;
+        int sc, m;
+        if (r.sb < 4) { sc = (s0 >> (8 * r.sb)) & 63; m = (s1 >> (8 * r.sb)) & 63; }
+        else { const int t = r.sb - 4; sc = ((s2 >> (8 * t)) & 0xF) | (((s0 >> (8 * t + 6)) & 3) << 4); m = ((s2 >> (8 * t + 4)) & 0xF) | (((s1 >> (8 * t + 6)) & 3) << 4); }
+        const __half2 ds = __float2half2_rn(dm.x * (float) sc), nm = __float2half2_rn(-dm.y * (float) m);
+        const uint32_t w[8] = {r.qa.x, r.qa.y, r.qa.z, r.qa.w, r.qb.x, r.qb.y, r.qb.z, r.qb.w};
+        const int sh = (r.sb & 1) * 4;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {       // word i: bytes 4i..4i+3 -> low nibbles k0+4i.., high nibbles k0+32+4i..
-            const uint32_t v = w[i];
-            out[2 * i]          = pack_h2(d0 * (float) (v & 0xF) - n0,         d0 * (float) ((v >> 8) & 0xF) - n0);
-            out[2 * i + 1]      = pack_h2(d0 * (float) ((v >> 16) & 0xF) - n0, d0 * (float) ((v >> 24) & 0xF) - n0);
-            out[16 + 2 * i]     = pack_h2(d1 * (float) ((v >> 4) & 0xF) - n1,  d1 * (float) ((v >> 12) & 0xF) - n1);
-            out[16 + 2 * i + 1] = pack_h2(d1 * (float) ((v >> 20) & 0xF) - n1, d1 * (float) ((v >> 28) & 0xF) - n1);
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t v = (w[i] >> sh) & 0x0F0F0F0Fu;
+            out[2 * i]     = h2_as_u32(__hfma2(bytes01_h2(v), ds, nm));
+            out[2 * i + 1] = h2_as_u32(__hfma2(bytes23_h2(v), ds, nm));
         }
     }
 };
 
-// generic path: element-wise through the bit-exact dequantizer
-template <int T> struct Deq64 {
-    static __device__ __forceinline__ void get(const uint8_t * row, int k0, uint32_t (&out)[32]) {
-#pragma unroll 4
-        for (int i = 0; i < 32; ++i) out[i] = pack_h2(dequant_elem<T>(row, k0 + 2 * i), dequant_elem<T>(row, k0 + 2 * i + 1));
+// Q6_K: k .. k+31 is group t = (k >> 5) & 3 of half n128 = (k >> 7) & 1 (ggml-quants.c:1690-1719);
+// blocks are only 2-byte aligned, so the bytes come in as aligned words plus a funnel shift
+template <> struct Deq32<T_Q6_K> {
+    struct Raw { uint32_t ql[9], qh[9], scd[2]; uint32_t sh; int t, n128; uint32_t scsh; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
+        const uint8_t * b = row + (k >> 8) * 210;
+        r.n128 = (k >> 7) & 1; r.t = (k >> 5) & 3;
+        const uint8_t * pl = b + r.n128 * 64 + (r.t & 1) * 32;          // 32 bytes of ql
+        const uint8_t * ph = b + 128 + r.n128 * 32;                     // 32 bytes of qh
+        const uint32_t * al = (const uint32_t *) ((uintptr_t) pl & ~(uintptr_t) 3);
+        const uint32_t * ah = (const uint32_t *) ((uintptr_t) ph & ~(uintptr_t) 3);
+        r.sh = ((uint32_t) (uintptr_t) pl & 3u) * 8u;                   // pl and ph have the same alignment (offsets differ by a multiple of 4)
+#pragma unroll
+        for (int i = 0; i < 9; ++i) { r.ql[i] = __ldg(al + i); r.qh[i] = __ldg(ah + i); }
+        const uint8_t * ps = b + 192 + r.n128 * 8 + 2 * r.t;           // scales[2t], scales[2t+1]; then d at b+208
+        r.scd[0] = *(const uint16_t *) ps;
+        r.scd[1] = *(const uint16_t *) (b + 208);
+    }
+    static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
+        const float d = __half2float(__ushort_as_half((unsigned short) r.scd[1]));
+        const __half2 dlo = __float2half2_rn(d * (float) (int) (int8_t) (r.scd[0] & 0xff));
+        const __half2 dhi = __float2half2_rn(d * (float) (int) (int8_t) (r.scd[0] >> 8));
+        const __half2 off = u32_as_h2(0x50005000u);                     // 32.0 in F16
+        const int hs = 2 * r.t, ns = (r.t & 2) ? 4 : 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t L = __funnelshift_r(r.ql[i], r.ql[i + 1], r.sh), H = __funnelshift_r(r.qh[i], r.qh[i + 1], r.sh);
+            const uint32_t q = ((L >> ns) & 0x0F0F0F0Fu) | (((H >> hs) & 0x03030303u) << 4);     // 4 values 0..63
+            const __half2 sd = i < 4 ? dlo : dhi;                       // l < 16 uses scales[2t], l >= 16 scales[2t+1]
+            out[2 * i]     = h2_as_u32(__hmul2(__hsub2(bytes01_h2(q), off), sd));
+            out[2 * i + 1] = h2_as_u32(__hmul2(__hsub2(bytes23_h2(q), off), sd));
+        }
     }
 };
 
-template <> struct Deq64<T_Q6_K> {
-    static __device__ __forceinline__ void get(const uint8_t * row, int k0, uint32_t (&out)[32]) {
-        // 64 values = groups t0, t0+1 (32 each) of half n128; blocks are only 2-byte aligned
-        const uint8_t * b = row + (k0 >> 8) * 210;
-        const int n128 = (k0 >> 7) & 1, t0 = (k0 >> 5) & 3;            // t0 is 0 or 2
-        const float d = h2f(*(const uint16_t *) (b + 208));
-        const uint16_t * ql = (const uint16_t *) (b + n128 * 64);
-        const uint16_t * qh = (const uint16_t *) (b + 128 + n128 * 32);
-        const int8_t * sc = (const int8_t *) (b + 192 + n128 * 8);
+// Q4_0 / Q8_0: one 32-value block per thread and k-step
+template <> struct Deq32<T_Q4_0> {
+    struct Raw { uint32_t w[4]; uint32_t d; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
+        const uint16_t * b = (const uint16_t *) (row + (k >> 5) * 18);
+        r.d = b[0];
 #pragma unroll
-        for (int tt = 0; tt < 2; ++tt) {
-            const int t = t0 + tt;                                      // group: elements l + 32 t
-            const float dlo = d * (float) sc[2 * t], dhi = d * (float) sc[2 * t + 1];
+        for (int i = 0; i < 4; ++i) r.w[i] = (uint32_t) b[1 + 2 * i] | ((uint32_t) b[2 + 2 * i] << 16);
+    }
+    static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
+        const __half2 d = __half2half2(__ushort_as_half((unsigned short) r.d)), off = u32_as_h2(0x48004800u);   // 8.0
 #pragma unroll
-            for (int l2 = 0; l2 < 16; ++l2) {                           // two l values per 16-bit load
-                const uint32_t L = ql[(t & 1) * 16 + l2], H = qh[l2];
-                const uint32_t nib0 = (t & 2) ? (L >> 4) & 0xF : L & 0xF, nib1 = (t & 2) ? (L >> 12) & 0xF : (L >> 8) & 0xF;
-                const uint32_t h0 = (H >> (2 * t)) & 3, h1 = (H >> (8 + 2 * t)) & 3;
-                const float sd = l2 < 8 ? dlo : dhi;
-                out[tt * 16 + l2] = pack_h2(sd * (float) ((int) (nib0 | (h0 << 4)) - 32), sd * (float) ((int) (nib1 | (h1 << 4)) - 32));
-            }
+        for (int i = 0; i < 4; ++i) {                                   // low nibbles: elements 4i..4i+3, high: 16+4i..
+            const uint32_t lo = r.w[i] & 0x0F0F0F0Fu, hi = (r.w[i] >> 4) & 0x0F0F0F0Fu;
+            out[2 * i]         = h2_as_u32(__hmul2(__hsub2(bytes01_h2(lo), off), d));
+            out[2 * i + 1]     = h2_as_u32(__hmul2(__hsub2(bytes23_h2(lo), off), d));
+            out[8 + 2 * i]     = h2_as_u32(__hmul2(__hsub2(bytes01_h2(hi), off), d));
+            out[8 + 2 * i + 1] = h2_as_u32(__hmul2(__hsub2(bytes23_h2(hi), off), d));
+        }
+    }
+};
+template <> struct Deq32<T_Q8_0> {
+    struct Raw { uint32_t w[8]; uint32_t d; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
+        const uint16_t * b = (const uint16_t *) (row + (k >> 5) * 34);
+        r.d = b[0];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r.w[i] = (uint32_t) b[1 + 2 * i] | ((uint32_t) b[2 + 2 * i] << 16);
+    }
+    static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
+        const __half2 d = __half2half2(__ushort_as_half((unsigned short) r.d)), off = u32_as_h2(0x58005800u);   // 128.0
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {                                   // signed byte + 128 = unsigned byte
+            const uint32_t u = r.w[i] ^ 0x80808080u;
+            out[2 * i]     = h2_as_u32(__hmul2(__hsub2(bytes01_h2(u), off), d));
+            out[2 * i + 1] = h2_as_u32(__hmul2(__hsub2(bytes23_h2(u), off), d));
         }
     }
 };
@@ -158,14 +224,20 @@ __global__ void tc_convert_x_kernel(const float * __restrict__ x, int64_t x_nb1 
 // ---- the GEMM kernel ---------------------------------------------------------------------------
 struct TcParams {
     const uint8_t * W; int64_t w_nb1;
-    const __half * Xh;                 // [N][K] F16
+    const __half * Xh;                 // [N][K] F16 (read through the tensor map)
     float * dst; int64_t dst_nb1;      // bytes between token columns
     int M, N, K;
     int * status;
 };
 
+__device__ __forceinline__ void tma_load_2d(void * smem_dst, const CUtensorMap * tmap, int x, int y, uint64_t * bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        :: "r"(smem_u32(smem_dst)), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
 template <int T>
-__global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // operand stages must be 1024-byte aligned for the 128-byte swizzle pattern
     uint8_t * smem = (uint8_t *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
@@ -174,64 +246,75 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p)
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;    // adjacent CTAs share one weight tile (L2 reuse)
     const int ksteps = p.K / TC_BK;
+    constexpr int MMA_WARP = TC_PRODUCERS / 32;
 
     if (tid == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full_bar[s], 128); mbar_init(&empty_bar[s], 1); }
+        // per stage: one arrival per producer warp + 1 arrive.expect_tx for the activation tile
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full_bar[s], TC_PRODUCERS / 32 + 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&accum_bar, 1);
         abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 4) tmem_alloc(&tmem_base_sh, TC_TMEM_COLS);
+    if (warp == MMA_WARP) tmem_alloc(&tmem_base_sh, TC_TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_sh;
 
-    if (warp < 4) {
+    if (warp < MMA_WARP) {
         // ------------------------------ producers ------------------------------
-        const int r = tid;                                              // operand row handled by this thread
-        const bool wrow_ok = m0 + r < p.M, xrow_ok = n0 + r < p.N;
+        const int r = tid & 127, h = tid >> 7;                          // operand row, which 32 of the 64 k-values
+        const bool wrow_ok = m0 + r < p.M;
         const uint8_t * wrow = p.W + (int64_t) (wrow_ok ? m0 + r : 0) * p.w_nb1;
-        const __half * xrow = p.Xh + (int64_t) (xrow_ok ? n0 + r : 0) * p.K;
+        // raw quant bytes of the next TC_PF k-steps are kept in flight in registers (HBM latency is several
+        // k-steps long); weights do not depend on the previous kernel, so the first loads precede the wait
+        typename Deq32<T>::Raw raw[TC_PF];
+#pragma unroll
+        for (int u = 0; u < TC_PF; ++u) if (u < ksteps) Deq32<T>::load(wrow, u * TC_BK + h * 32, raw[u]);
         pdl_wait();
         bool ok = true;
-        for (int ks = 0; ks < ksteps; ++ks) {
-            const int s = ks % TC_STAGES;
-            const uint32_t round = (uint32_t) (ks / TC_STAGES);
-            if (ks >= TC_STAGES && !mbar_wait(&empty_bar[s], (round - 1) & 1)) { ok = false; break; }
-            if (*(volatile int *) &abort_flag) { ok = false; break; }
-            uint8_t * sa = smem + (size_t) s * TC_STAGE_BYTES;          // A: weights 128 x 64 F16
-            uint8_t * sb = sa + TC_BM * TC_BK * 2;                      // B: activations 128 x 64 F16
-            uint32_t wv[32];
-            if (wrow_ok) Deq64<T>::get(wrow, ks * TC_BK, wv);
-            else {
+        for (int ks0 = 0; ks0 < ksteps && ok; ks0 += TC_PF) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) wv[i] = 0;
+            for (int u = 0; u < TC_PF; ++u) {
+                const int ks = ks0 + u;
+                if (ks >= ksteps || !ok) break;
+                const int s = ks % TC_STAGES;
+                const uint32_t round = (uint32_t) (ks / TC_STAGES);
+                if (ks >= TC_STAGES && !mbar_wait(&empty_bar[s], (round - 1) & 1)) { ok = false; break; }
+                if (*(volatile int *) &abort_flag) { ok = false; break; }
+                uint8_t * sa = smem + (size_t) s * TC_STAGE_BYTES;      // A: weights 128 x 64 F16
+                if (tid == 0) {                                         // B: activations 128 x 64 F16 by TMA (rows past N read as zero)
+                    mbar_arrive_expect_tx(&full_bar[s], TC_BN * TC_BK * 2);
+                    tma_load_2d(sa + TC_BM * TC_BK * 2, &xmap, ks * TC_BK, n0, &full_bar[s]);
+                }
+                uint32_t wv[16];
+                Deq32<T>::get(raw[u], wv);
+                if (ks + TC_PF < ksteps) Deq32<T>::load(wrow, (ks + TC_PF) * TC_BK + h * 32, raw[u]);
+                if (!wrow_ok) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) wv[i] = 0;
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *(uint4 *) (sa + r * 128 + (((4 * h + c) ^ (r & 7)) << 4)) = make_uint4(wv[4 * c], wv[4 * c + 1], wv[4 * c + 2], wv[4 * c + 3]);
+                fence_async_smem();                                     // make the generic-proxy stores visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_bar[s]);               // one arrival per warp: 257 arrivals on one barrier serialise
             }
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *(uint4 *) (sa + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(wv[4 * c], wv[4 * c + 1], wv[4 * c + 2], wv[4 * c + 3]);
-            const uint4 * xs = (const uint4 *) (xrow + ks * TC_BK);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const uint4 v = xrow_ok ? __ldg(xs + c) : make_uint4(0, 0, 0, 0);
-                *(uint4 *) (sb + r * 128 + ((c ^ (r & 7)) << 4)) = v;
-            }
-            fence_async_smem();                                         // make the generic-proxy stores visible to the tensor core
-            mbar_arrive(&full_bar[s]);
         }
         if (!ok && lane == 0) { atomicExch(p.status, ERR_MBAR_TIMEOUT); abort_flag = 1; }
 
         // ------------------------------ epilogue ------------------------------
         if (ok && mbar_wait(&accum_bar, 0)) {
             tc_fence_after();
-            const int m = m0 + warp * 32 + lane;
+            const int quad = warp & 3, chalf = warp >> 2;               // lane quadrant; which 64 of the 128 columns
+            const int m = m0 + quad * 32 + lane;
 #pragma unroll 1
-            for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+            for (int c0 = chalf * 64; c0 < chalf * 64 + 64; c0 += 32) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t) (warp * 32) << 16) + (uint32_t) c0, v);
+                tmem_ld32(tmem_base + ((uint32_t) (quad * 32) << 16) + (uint32_t) c0, v);
                 tmem_ld_wait();
                 if (m < p.M) {
 #pragma unroll
@@ -271,7 +354,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p)
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem_base, TC_TMEM_COLS); }
+    if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, TC_TMEM_COLS); }
     pdl_launch_dependents();
 }
 
@@ -288,6 +371,21 @@ bool mmq_tc_ptr_ok(int type, const void * W, int64_t w_nb1, const void * X, int6
     return ((uintptr_t) W & 1) == 0 && (w_nb1 & 1) == 0;
 }
 
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static encode_tiled_fn get_encode_tiled() {
+    static encode_tiled_fn fn = nullptr;
+    if (!fn) {
+        void * p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (encode_tiled_fn) p;
+        else cudaGetLastError();
+    }
+    return fn;
+}
+
 template <int T>
 static cudaError_t launch_tc_t(const TcParams & p, int device, cudaStream_t stream) {
     auto kern = mmq_tc_kernel<T>;
@@ -298,8 +396,18 @@ static cudaError_t launch_tc_t(const TcParams & p, int device, cudaStream_t stre
         if (e != cudaSuccess) return e;
         attr_mask |= 1u << device;
     }
-    dim3 grid((unsigned) ((p.M + TC_BM - 1) / TC_BM), (unsigned) ((p.N + TC_BN - 1) / TC_BN));
-    kern<<<grid, TC_THREADS, smem, stream>>>(p);
+    // tensor map of the F16 activations [N][K]: boxes of 64 (k) x 128 (tokens), 128-byte swizzle, zero fill
+    encode_tiled_fn enc = get_encode_tiled();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap xmap;
+    const cuuint64_t gdim[2] = {(cuuint64_t) p.K, (cuuint64_t) p.N};
+    const cuuint64_t gstr[1] = {(cuuint64_t) p.K * 2};
+    const cuuint32_t box[2] = {TC_BK, TC_BN}, estr[2] = {1, 1};
+    if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *) p.Xh, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    dim3 grid((unsigned) ((p.N + TC_BN - 1) / TC_BN), (unsigned) ((p.M + TC_BM - 1) / TC_BM));
+    kern<<<grid, TC_THREADS, smem, stream>>>(p, xmap);
     return cudaGetLastError();
 }
 

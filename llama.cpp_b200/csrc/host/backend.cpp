@@ -223,6 +223,7 @@ static void backend_free(ggml_backend_t backend) {
     for (auto & e : ctx->act_cache) if (e.q) cudaFree(e.q);
     if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
     if (ctx->dyn_dev) cudaFree(ctx->dyn_dev);
+    if (ctx->fa_tickets) cudaFree(ctx->fa_tickets);
     free(ctx->dyn_host);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
@@ -336,13 +337,16 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t dev, const char * /*pa
     B200_CUDA_CHECK(cudaMemset(ctx->status_dev, 0, sizeof(int)));
     B200_CUDA_CHECK(cudaMallocHost((void **) &ctx->status_host, sizeof(int)));
     *ctx->status_host = 0;
+    B200_CUDA_CHECK(cudaMalloc((void **) &ctx->fa_tickets, sizeof(unsigned) * FATTN_DEC_TICKETS));
+    B200_CUDA_CHECK(cudaMemset(ctx->fa_tickets, 0, sizeof(unsigned) * FATTN_DEC_TICKETS));
     B200_CUDA_CHECK(cudaMalloc((void **) &ctx->dyn_dev, sizeof(int64_t) * BackendCtx::DYN_CAP));
     // pageable on purpose: cudaMemcpyAsync then snapshots the values at call time, so the next call may overwrite them
     ctx->dyn_host = (int64_t *) malloc(sizeof(int64_t) * BackendCtx::DYN_CAP);
     ctx->use_graphs = getenv("GGML_B200_GRAPHS") ? atoi(getenv("GGML_B200_GRAPHS")) : 1;
+    ctx->use_fusion = getenv("GGML_B200_FUSE") ? atoi(getenv("GGML_B200_FUSE")) : 1;
     ctx->use_tc = getenv("GGML_B200_TC") ? atoi(getenv("GGML_B200_TC")) : 1;
     const char * pdl = getenv("GGML_B200_PDL");
-    ctx->use_pdl = pdl ? atoi(pdl) : 0;
+    ctx->use_pdl = pdl ? atoi(pdl) : 1;
     ctx->trace = getenv("GGML_B200_TRACE") ? atoi(getenv("GGML_B200_TRACE")) : 0;
     ggml_backend_t backend = new ggml_backend;
     backend->guid = &k_guid;

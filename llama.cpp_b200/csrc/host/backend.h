@@ -38,6 +38,7 @@ struct BackendCtx {
     size_t       scratch_size = 0;
     cudaEvent_t  copy_event = nullptr;
     int          use_pdl = 0;
+    int          use_fusion = 1;            // multi-node fusions (GGML_B200_FUSE=0 runs one node per launch group)
     int          use_tc = 1;                // tensor-core GEMM for N > 8 (GGML_B200_TC=0 falls back to the mat-vec kernel)
     int          trace = 0;
     uint64_t     n_launches = 0;           // kernels launched by graph_compute since creation
@@ -68,7 +69,9 @@ struct BackendCtx {
     static constexpr int DYN_CAP = 1024;
     uint64_t     scratch_generation = 0;
 
-    LaunchCtx launch_ctx() const { return LaunchCtx{stream, dev->device, dev->sm_count, status_dev, use_pdl}; }
+    unsigned *   fa_tickets = nullptr;     // zero-initialised counters of the decode attention kernel
+
+    LaunchCtx launch_ctx() const { return LaunchCtx{stream, dev->device, dev->sm_count, status_dev, use_pdl, fa_tickets}; }
     void *    get_scratch(size_t bytes);   // grows (after a stream sync) when needed
 };
 

@@ -128,7 +128,7 @@ static bool act_cacheable(const ggml_tensor * X) {
     return X->type == GGML_TYPE_F32 && t_contiguous(X) && X->ne[1] * X->ne[2] * X->ne[3] <= 8;
 }
 
-static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_tensor * ids) {
+static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_tensor * ids, ggml_tensor * const * extra = nullptr, int n_extra = 0) {
     const ggml_tensor * W = dst->src[0];
     const ggml_tensor * X = dst->src[1];
     const LaunchCtx lc = ctx->launch_ctx();
@@ -159,18 +159,23 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
         if (!e) {
             e = ctx->act_cache_take(X->data, K, ne11 * ne12 * ne13);
             if (!e) return false;
-            RUN(launch_quantize_act128((const float *) X->data, ne11, ne12, ne13, X->nb[1] / 4, X->nb[2] / 4, X->nb[3] / 4, e->q, (int) K, lc.stream));
+            RUN(launch_quantize_act128((const float *) X->data, ne11, ne12, ne13, X->nb[1] / 4, X->nb[2] / 4, X->nb[3] / 4, e->q, (int) K, lc.stream, lc.use_pdl));
         }
         xq = e->q;
     } else {
         xq = ctx->get_scratch(act128_bytes(K, ne11 * ne12 * ne13));
-        RUN(launch_quantize_act128((const float *) X->data, ne11, ne12, ne13, X->nb[1] / 4, X->nb[2] / 4, X->nb[3] / 4, xq, (int) K, lc.stream));
+        RUN(launch_quantize_act128((const float *) X->data, ne11, ne12, ne13, X->nb[1] / 4, X->nb[2] / 4, X->nb[3] / 4, xq, (int) K, lc.stream, lc.use_pdl));
     }
 
     MmvqArgs a = {};
     a.type = W->type; a.W = W->data; a.w_nb1 = W->nb[1]; a.w_nb2 = W->nb[2]; a.w_nb3 = W->nb[3];
     a.Xq = xq; a.M = (int) M; a.K = (int) K;
     a.status = lc.status; a.sm_count = lc.sm_count; a.device = lc.device; a.use_pdl = lc.use_pdl;
+    for (int i = 0; i < n_extra; ++i) {             // grouped launch: more weight matrices on the same activations
+        a.extra_W[i] = extra[i]->src[0]->data; a.extra_dst[i] = (float *) extra[i]->data;
+        a.extra_dst_nb1[i] = extra[i]->nb[1]; a.extra_M[i] = (int) extra[i]->src[0]->ne[1];
+    }
+    a.n_extra = n_extra;
     if (!ids) {
         a.ne12 = (int) ne12; a.ne13 = (int) ne13;
         a.r2 = (int) (ne12 / W->ne[2]); a.r3 = (int) (ne13 / W->ne[3]);
@@ -206,6 +211,62 @@ static bool feeds_quant_mul_mat(const ggml_cgraph * g, int from, const ggml_tens
     return false;
 }
 
+static bool is_noop(const ggml_tensor * node);
+
+// Can MUL_MAT node `n` ride along with `first` in one grouped mat-vec launch?
+static bool groupable_mul_mat(const ggml_tensor * first, const ggml_tensor * n) {
+    if (n->op != GGML_OP_MUL_MAT || n->src[1] != first->src[1]) return false;
+    const ggml_tensor * w0 = first->src[0], * w = n->src[0];
+    if (w->type != w0->type || (w->type != GGML_TYPE_Q4_K && w->type != GGML_TYPE_Q5_K)) return false;
+    if (w->ne[0] != w0->ne[0] || w->nb[1] != w0->nb[1] || w->ne[2] != 1 || w->ne[3] != 1) return false;
+    if (((uintptr_t) w->data & 15) || !t_contiguous(n) || n->type != GGML_TYPE_F32) return false;
+    return !buft_is_split(w->buffer ? w->buffer->buft : nullptr);
+}
+static bool group_head_ok(const ggml_tensor * n) {
+    const ggml_tensor * w = n->src[0], * x = n->src[1];
+    if (w->type != GGML_TYPE_Q4_K && w->type != GGML_TYPE_Q5_K) return false;
+    if (x->ne[1] > 8 || x->ne[2] != 1 || x->ne[3] != 1 || w->ne[2] != 1 || w->ne[3] != 1) return false;
+    if ((size_t) x->ne[1] * ((w->ne[0] + 127) / 128) * 160 > 200 * 1024) return false;      // must fit the direct kernel's activation smem
+    return ((uintptr_t) w->data & 15) == 0 && (w->nb[1] & 15) == 0 && t_contiguous(n) && x->type == GGML_TYPE_F32 && t_contiguous(x);
+}
+static int next_exec(const ggml_cgraph * g, int i);
+
+static RopeParams rope_params_of(const ggml_tensor * dst) {
+    RopeParams rp;
+    rp.n_dims = op_param_i32(dst, 1); rp.mode = op_param_i32(dst, 2); rp.n_ctx_orig = op_param_i32(dst, 4);
+    rp.freq_base = op_param_f32(dst, 5); rp.freq_scale = op_param_f32(dst, 6); rp.ext_factor = op_param_f32(dst, 7);
+    rp.attn_factor = op_param_f32(dst, 8); rp.beta_fast = op_param_f32(dst, 9); rp.beta_slow = op_param_f32(dst, 10);
+    return rp;
+}
+
+// ROPE(Q), ROPE(K), CPY(K -> cache view), CPY(V -> cache view) as emitted per layer (src/llama.cpp:1511-1531,
+// :157-199), possibly with view-only nodes in between.  On a match returns the index of the last node.
+static int match_rope_kv(const ggml_cgraph * g, int i, const ggml_tensor ** ropek, const ggml_tensor ** cpyk, const ggml_tensor ** cpyv) {
+    const ggml_tensor * rq = g->nodes[i];
+    const int j1 = next_exec(g, i + 1); if (j1 < 0) return -1;
+    const ggml_tensor * rk = g->nodes[j1];
+    if (rk->op != GGML_OP_ROPE || rk->src[1] != rq->src[1] || rk->src[2] != rq->src[2]) return -1;
+    if (memcmp(rk->op_params, rq->op_params, sizeof(rq->op_params)) != 0) return -1;
+    auto plain = [](const ggml_tensor * t) { return t->type == GGML_TYPE_F32 && t_contiguous(t) && t_contiguous(t->src[0]) && t->ne[3] == 1; };
+    if (!plain(rq) || !plain(rk) || rq->ne[0] != rk->ne[0] || rq->ne[2] != rk->ne[2] || (rq->ne[0] & 1)) return -1;
+    if (op_param_i32(rq, 2) & ~GGML_ROPE_TYPE_NEOX) return -1;
+    const int j2 = next_exec(g, j1 + 1); if (j2 < 0) return -1;
+    const ggml_tensor * ck = g->nodes[j2];
+    auto cache_store = [](const ggml_tensor * c, const ggml_tensor * from) {
+        if (c->op != GGML_OP_CPY || c->src[0]->type != GGML_TYPE_F32 || !t_contiguous(c->src[0])) return false;
+        if (from && c->src[0] != from) return false;
+        const ggml_tensor * out = c->src[1];
+        return out->type == GGML_TYPE_F16 && t_contiguous(out) && out->view_src && out->view_src->data &&
+               t_nelements(out) == t_nelements(c->src[0]) && (t_nelements(out) & 1) == 0 && ((uintptr_t) out->data & 3) == 0;
+    };
+    if (!cache_store(ck, rk)) return -1;
+    const int j3 = next_exec(g, j2 + 1); if (j3 < 0) return -1;
+    const ggml_tensor * cv = g->nodes[j3];
+    if (!cache_store(cv, nullptr) || ((uintptr_t) cv->src[0]->data & 7)) return -1;
+    *ropek = rk; *cpyk = ck; *cpyv = cv;
+    return j3;
+}
+
 // Executes node i, fusing it with its successor where the graph allows:
 //   RMS_NORM -> MUL(x, w)        one launch; both outputs are written (the MUL result, and the plain
 //                                norm in case something else reads it), plus the int8 blocks of the
@@ -221,7 +282,15 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
 #define RUN0(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) { B200_LOG_ERROR("ggml-b200: %s failed: %s\n", #expr, cudaGetErrorString(e_)); return fail(); } ctx->n_launches++; } while (0)
     ggml_tensor * next = i + 1 < g->n_nodes ? g->nodes[i + 1] : nullptr;
     switch (dst->op) {
-        case GGML_OP_MUL_MAT:    return run_mul_mat(ctx, dst, nullptr) ? 1 : 0;
+        case GGML_OP_MUL_MAT: {
+            ggml_tensor * extra[2]; int n_extra = 0;
+            if (group_head_ok(dst) && !buft_is_split(dst->src[0]->buffer ? dst->src[0]->buffer->buft : nullptr)) {
+                while (n_extra < 2 && i + 1 + n_extra < g->n_nodes && groupable_mul_mat(dst, g->nodes[i + 1 + n_extra])) {
+                    extra[n_extra] = g->nodes[i + 1 + n_extra]; ctx->act_cache_invalidate(extra[n_extra]->data); ++n_extra;
+                }
+            }
+            return run_mul_mat(ctx, dst, nullptr, extra, n_extra) ? 1 + n_extra : 0;
+        }
         case GGML_OP_MUL_MAT_ID: return run_mul_mat(ctx, dst, dst->src[2]) ? 1 : 0;
         case GGML_OP_FLASH_ATTN_EXT: {
             const ggml_tensor * v = dst->src[2];
@@ -246,14 +315,37 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
                     if (!e) return fail();
                     act = e->q;
                 }
-                RUN0(launch_rms_norm_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), op_param_f32(dst, 0), act, (float *) dst->data, lc));
+                RUN0(launch_rms_norm_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), op_param_f32(dst, 0), act, (float *) dst->data, nullptr, nullptr, lc));
                 return 2;
             }
             RUN0(launch_rms_norm(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc));
             return 1;
         }
         case GGML_OP_NORM: RUN0(launch_norm(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc)); return 1;
-        case GGML_OP_ADD: RUN0(launch_bin_bcast(BIN_ADD, to_desc(a), to_desc(b), to_desc(dst), lc)); return 1;
+        case GGML_OP_ADD: {
+            // residual add feeding RMS_NORM -> MUL(x, w): one launch writes the sum, the norm, the product and,
+            // when quantized mat-muls read the product, its int8 blocks
+            ggml_tensor * rn = next;
+            ggml_tensor * mu = i + 2 < g->n_nodes ? g->nodes[i + 2] : nullptr;
+            if (rn && mu && rn->op == GGML_OP_RMS_NORM && rn->src[0] == dst && mu->op == GGML_OP_MUL && mu->src[0] == rn &&
+                dst->type == GGML_TYPE_F32 && a->type == GGML_TYPE_F32 && b->type == GGML_TYPE_F32 && t_same_shape(a, b) &&
+                t_contiguous(a) && t_contiguous(b) && t_contiguous(dst) && t_contiguous(rn) && t_contiguous(mu) &&
+                mu->type == GGML_TYPE_F32 && mu->src[1]->type == GGML_TYPE_F32 && mu->src[1]->nb[0] == 4 && t_can_repeat(mu->src[1], rn)) {
+                void * act = nullptr;
+                if (act_cacheable(mu) && mu->ne[0] % 128 == 0 && feeds_quant_mul_mat(g, i + 3, mu)) {
+                    ctx->act_cache_invalidate(mu->data);
+                    BackendCtx::ActEntry * e = ctx->act_cache_take(mu->data, mu->ne[0], mu->ne[1] * mu->ne[2] * mu->ne[3]);
+                    if (!e) return fail();
+                    act = e->q;
+                }
+                ctx->act_cache_invalidate(rn->data);
+                RUN0(launch_rms_norm_mul(to_desc(a), to_desc(mu->src[1]), to_desc(mu), op_param_f32(rn, 0), act, (float *) rn->data,
+                                         (const float *) b->data, (float *) dst->data, lc));
+                return 3;
+            }
+            RUN0(launch_bin_bcast(BIN_ADD, to_desc(a), to_desc(b), to_desc(dst), lc));
+            return 1;
+        }
         case GGML_OP_SUB: RUN0(launch_bin_bcast(BIN_SUB, to_desc(a), to_desc(b), to_desc(dst), lc)); return 1;
         case GGML_OP_MUL: RUN0(launch_bin_bcast(BIN_MUL, to_desc(a), to_desc(b), to_desc(dst), lc)); return 1;
         case GGML_OP_DIV: RUN0(launch_bin_bcast(BIN_DIV, to_desc(a), to_desc(b), to_desc(dst), lc)); return 1;
@@ -281,11 +373,29 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
         case GGML_OP_SCALE: RUN0(launch_scale(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc)); return 1;
         case GGML_OP_CLAMP: RUN0(launch_clamp(to_desc(a), to_desc(dst), op_param_f32(dst, 0), op_param_f32(dst, 1), lc)); return 1;
         case GGML_OP_ROPE: {
-            RopeParams rp;
-            rp.n_dims = op_param_i32(dst, 1); rp.mode = op_param_i32(dst, 2); rp.n_ctx_orig = op_param_i32(dst, 4);
-            rp.freq_base = op_param_f32(dst, 5); rp.freq_scale = op_param_f32(dst, 6); rp.ext_factor = op_param_f32(dst, 7);
-            rp.attn_factor = op_param_f32(dst, 8); rp.beta_fast = op_param_f32(dst, 9); rp.beta_slow = op_param_f32(dst, 10);
+            const RopeParams rp = rope_params_of(dst);
             const ggml_tensor * ff = dst->src[2];
+            const ggml_tensor * rk = nullptr, * ck = nullptr, * cv = nullptr;
+            const int last = ctx->use_fusion ? match_rope_kv(g, i, &rk, &ck, &cv) : -1;
+            if (last >= 0 && (!ctx->capturing || ctx->dyn_used + 2 <= BackendCtx::DYN_CAP)) {
+                RopeKvLaunch l = {};
+                l.q_src = (const float *) a->data; l.q_dst = (float *) dst->data;
+                l.k_src = (const float *) rk->src[0]->data; l.k_dst = (float *) rk->data;
+                l.v_src = (const float *) cv->src[0]->data; l.v_elems = t_nelements(cv->src[0]);
+                l.hd = dst->ne[0]; l.n_head = dst->ne[1]; l.n_head_kv = rk->ne[1]; l.n_tok = dst->ne[2];
+                const ggml_tensor * ko = ck->src[1], * vo = cv->src[1];
+                l.k_cache = ko->view_src->data; l.v_cache = vo->view_src->data;
+                l.k_off = (const char *) ko->data - (const char *) ko->view_src->data;
+                l.v_off = (const char *) vo->data - (const char *) vo->view_src->data;
+                if (ctx->capturing) {                   // same slot order as the CPY nodes appear in the graph
+                    ctx->dyn_host[ctx->dyn_used] = l.k_off; l.k_off_dev = ctx->dyn_dev + ctx->dyn_used++;
+                    ctx->dyn_host[ctx->dyn_used] = l.v_off; l.v_off_dev = ctx->dyn_dev + ctx->dyn_used++;
+                }
+                l.pos = (const int32_t *) b->data; l.ff = ff ? (const float *) ff->data : nullptr;
+                for (int j = i; j <= last; ++j) ctx->act_cache_invalidate(g->nodes[j]->data);
+                RUN0(launch_rope_kv(l, rp, lc));
+                return last - i + 1;
+            }
             RUN0(launch_rope(to_desc(a), (const int32_t *) b->data, ff ? (const float *) ff->data : nullptr, to_desc(dst), rp, lc));
             return 1;
         }
@@ -325,6 +435,11 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
 static bool is_noop(const ggml_tensor * node) {
     return t_empty(node) || node->op == GGML_OP_NONE || node->op == GGML_OP_RESHAPE || node->op == GGML_OP_VIEW ||
            node->op == GGML_OP_PERMUTE || node->op == GGML_OP_TRANSPOSE;
+}
+
+static int next_exec(const ggml_cgraph * g, int i) {
+    for (; i < g->n_nodes; ++i) if (!is_noop(g->nodes[i])) return i;
+    return -1;
 }
 
 static bool run_all(BackendCtx * ctx, ggml_cgraph * cgraph) {

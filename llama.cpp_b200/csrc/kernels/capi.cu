@@ -42,7 +42,7 @@ API size_t b200_row_size(int type, int64_t k) {
 }
 
 // per-device launch context for the flat API: SM count and a status word
-struct ApiDev { int sm_count = 0; int * status = nullptr; bool ready = false; };
+struct ApiDev { int sm_count = 0; int * status = nullptr; unsigned * tickets = nullptr; bool ready = false; };
 static ApiDev g_dev[64];
 
 static int get_ctx(void * stream, LaunchCtx & lc) {
@@ -56,9 +56,11 @@ static int get_ctx(void * stream, LaunchCtx & lc) {
         CK(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
         CK(cudaMalloc((void **) &d.status, sizeof(int)));
         CK(cudaMemset(d.status, 0, sizeof(int)));
+        CK(cudaMalloc((void **) &d.tickets, sizeof(unsigned) * FATTN_DEC_TICKETS));
+        CK(cudaMemset(d.tickets, 0, sizeof(unsigned) * FATTN_DEC_TICKETS));
         d.ready = true;
     }
-    lc.stream = (cudaStream_t) stream; lc.device = dev; lc.sm_count = d.sm_count; lc.status = d.status; lc.use_pdl = 0;
+    lc.stream = (cudaStream_t) stream; lc.device = dev; lc.sm_count = d.sm_count; lc.status = d.status; lc.use_pdl = 0; lc.fa_tickets = d.tickets;
     return 0;
 }
 static int check_status(const LaunchCtx & lc) {
@@ -281,7 +283,7 @@ API int b200_rms_norm_host(const float * x, int64_t n_rows, int64_t k, float eps
     TensorD xd = desc(dx.p, T_F32, k, n_rows, 1, k * 4, k * 4 * n_rows), dd_ = desc(dd.p, T_F32, k, n_rows, 1, k * 4, k * 4 * n_rows);
     if (weight) {
         CK(cudaMemcpy(dw.p, weight, (size_t) k * 4, cudaMemcpyHostToDevice));
-        CK(launch_rms_norm_mul(xd, desc(dw.p, T_F32, k, 1, 1, k * 4, k * 4), dd_, eps, nullptr, nullptr, lc));
+        CK(launch_rms_norm_mul(xd, desc(dw.p, T_F32, k, 1, 1, k * 4, k * 4), dd_, eps, nullptr, nullptr, nullptr, nullptr, lc));
     } else {
         CK(launch_rms_norm(xd, dd_, eps, lc));
     }

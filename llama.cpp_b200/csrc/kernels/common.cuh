@@ -209,7 +209,26 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Both halves of programmatic dependent launch at the top of a kernel that has nothing to prefetch:
+// let the next kernel in the stream start its own prologue now, then wait until everything this
+// kernel depends on has completed and is visible.  No-ops when launched without the attribute.
+__device__ __forceinline__ void pdl_enter() { pdl_launch_dependents(); pdl_wait(); }
+
 // error codes written to the device status word by kernels that give up a wait
 enum : int { ERR_NONE = 0, ERR_MBAR_TIMEOUT = 1, ERR_BAD_ARG = 2 };
+
+static thread_local cudaError_t launch_err = cudaSuccess;   // result of the most recent launch_k in this translation unit
+
+// host-side launch through cudaLaunchKernelEx so that the programmatic-serialization attribute can be set
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(int use_pdl, cudaStream_t stream, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args &&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 
 }  // namespace b200

@@ -33,6 +33,7 @@ struct FaK {
 
 template <int D>
 __global__ void __launch_bounds__(FA_WARPS * 32) fattn_vec_kernel(const FaK p) {
+    pdl_enter();
     constexpr int DPL = (D + 31) / 32;            // head-dim elements per lane
     __shared__ float qs[D];
     __shared__ float mg_m[FA_WARPS], mg_l[FA_WARPS];
@@ -129,6 +130,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fattn_vec_kernel(const FaK p) {
 // merges the per-split partials of one (query, head) row
 template <int D>
 __global__ void fattn_combine_kernel(const float * __restrict__ ws, float * __restrict__ dst, int n_splits) {
+    pdl_enter();
     const int64_t row = blockIdx.x;
     const float * w = ws + row * n_splits * (D + 2);
     float M = -INFINITY;
@@ -167,18 +169,19 @@ size_t fattn_workspace_bytes(const TensorD & q, const TensorD & k, int sm_count)
     const int64_t rows = q.ne[1] * q.ne[2] * q.ne[3];
     const int splits = fattn_pick_splits(rows, k.ne[1], sm_count);
     const size_t vec = splits > 1 ? (size_t) rows * splits * (q.ne[0] + 2) * sizeof(float) : 0;
-    const size_t mma = fattn_mma_workspace_bytes(q, k);
-    return vec > mma ? vec : mma;
+    const size_t mma = fattn_mma_workspace_bytes(q, k), dec = fattn_dec_workspace_bytes(q, k, sm_count);
+    const size_t m = vec > mma ? vec : mma;
+    return m > dec ? m : dec;
 }
 
 template <int D>
 static cudaError_t fattn_launch_d(const FaK & p, int64_t rows, int n3, const LaunchCtx & c) {
     dim3 grid((unsigned) p.n_splits, (unsigned) p.n_head, (unsigned) (p.n_q * n3));
-    fattn_vec_kernel<D><<<grid, FA_WARPS * 32, 0, c.stream>>>(p);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, fattn_vec_kernel<D>, dim3(grid), dim3(FA_WARPS * 32), 0, p));
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (p.n_splits > 1) {
-        fattn_combine_kernel<D><<<(unsigned) rows, D >= 128 ? 128 : 64, 0, c.stream>>>(p.ws, p.dst, p.n_splits);
+        (void) (launch_err = launch_k(c.use_pdl, c.stream, fattn_combine_kernel<D>, dim3((unsigned) rows), dim3(D >= 128 ? 128 : 64), 0, p.ws, p.dst, p.n_splits));
         e = cudaGetLastError();
     }
     return e;
@@ -188,6 +191,10 @@ cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v
                          const FattnParams & fp, void * workspace, const LaunchCtx & c, int * n_kernels) {
     const int64_t D = q.ne[0], rows = q.ne[1] * q.ne[2] * q.ne[3];
     if (rows == 0) return cudaSuccess;
+    if (c.fa_tickets && fattn_dec_applicable(q, k, v, mask)) {
+        if (n_kernels) *n_kernels = 1;
+        return launch_fattn_dec(q, k, v, mask, dst, fp, c.fa_tickets, workspace, c);
+    }
     if (fattn_mma_applicable(q, k, v, mask)) {
         if (n_kernels) *n_kernels = mask ? 2 : 1;
         return launch_fattn_mma(q, k, v, mask, dst, fp, workspace, c);

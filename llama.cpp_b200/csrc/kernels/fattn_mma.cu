@@ -30,6 +30,7 @@ struct FmParams {
 
 // classifies each 64x64 tile of the mask
 __global__ void fattn_mask_flags_kernel(const char * mask, int64_t m_nb1, int n_q, int n_kv, uint8_t * flags, int flags_stride) {
+    pdl_enter();
     __shared__ int any_finite, any_nonzero;
     if (threadIdx.x == 0) { any_finite = 0; any_nonzero = 0; }
     __syncthreads();
@@ -69,6 +70,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) { __half2 h = __floa
 
 template <int D>
 __global__ void __launch_bounds__(FM_WARPS * 32, 2) fattn_mma_kernel(const FmParams p) {
+    pdl_enter();
     constexpr int ROWB = D * 2 + 16;                   // padded smem row (bytes)
     constexpr int TILE = FM_BN * ROWB;
     extern __shared__ __align__(16) uint8_t smem[];
@@ -243,7 +245,7 @@ static cudaError_t fattn_mma_launch(const FmParams & p, int n3, const LaunchCtx 
         attr_mask |= 1u << c.device;
     }
     dim3 grid((unsigned) ((p.n_q + FM_BM - 1) / FM_BM), (unsigned) p.n_head, (unsigned) n3);
-    kern<<<grid, FM_WARPS * 32, smem, c.stream>>>(p);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, kern, dim3(grid), dim3(FM_WARPS * 32), smem, p));
     return cudaGetLastError();
 }
 
@@ -266,7 +268,7 @@ cudaError_t launch_fattn_mma(const TensorD & q, const TensorD & k, const TensorD
     if (mask) {
         const int qt = (p.n_q + FM_BM - 1) / FM_BM, kt = (p.n_kv + FM_BN - 1) / FM_BN;
         p.flags = (const uint8_t *) workspace; p.flags_stride = kt;
-        fattn_mask_flags_kernel<<<dim3((unsigned) kt, (unsigned) qt), 256, 0, c.stream>>>(p.mask, p.m_nb1, p.n_q, p.n_kv, (uint8_t *) workspace, kt);
+        (void) (launch_err = launch_k(c.use_pdl, c.stream, fattn_mask_flags_kernel, dim3(dim3((unsigned) kt, (unsigned) qt)), dim3(256), 0, p.mask, p.m_nb1, p.n_q, p.n_kv, (uint8_t *) workspace, kt));
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }

@@ -81,7 +81,9 @@ __device__ __forceinline__ void emit_act128(const float (&v)[4], int64_t k0, int
 // RMS_NORM (+ optional weight multiply, + optional activation quantization)
 // ---------------------------------------------------------------------------
 template <bool HAS_W, bool EMIT>
-__global__ void rms_norm_kernel(const TensorD src, const TensorD w, const TensorD dst, float eps, blk_act128 * act, float * norm_out) {
+__global__ void rms_norm_kernel(const TensorD src, const TensorD w, const TensorD dst, float eps, blk_act128 * act, float * norm_out,
+                                const float * __restrict__ addend, float * __restrict__ sum_out) {
+    pdl_enter();
     __shared__ float sh[32];
     const int64_t row = blockIdx.x;
     const int64_t i1 = row % src.ne[1], i2 = (row / src.ne[1]) % src.ne[2], i3 = row / (src.ne[1] * src.ne[2]);
@@ -89,8 +91,16 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
     float *       y = (float *) ((char *) dst.data + i1 * dst.nb[1] + i2 * dst.nb[2] + i3 * dst.nb[3]);
     const int64_t n = src.ne[0];
     float ss = 0.0f;
-    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = x[i]; ss += v * v; }
-    ss = block_sum(ss, sh);
+    if (addend) {
+        // fused residual add: x + addend is written to sum_out (contiguous rows) and normalised from there
+        float * so = sum_out + row * n;
+        const float * ad = addend + row * n;
+        for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = x[i] + ad[i]; so[i] = v; ss += v * v; }
+        x = so;
+    } else {
+        for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = x[i]; ss += v * v; }
+    }
+    ss = block_sum(ss, sh);                        // (its barriers also make the sums written above visible to the block)
     const float scale = rsqrtf(ss / (float) n + eps);
     const float * wr = nullptr;
     if (HAS_W) wr = (const float *) ((const char *) w.data + (i1 % w.ne[1]) * w.nb[1] + (i2 % w.ne[2]) * w.nb[2] + (i3 % w.ne[3]) * w.nb[3]);
@@ -130,19 +140,21 @@ static int row_block(int64_t n) { return n >= 4096 ? 1024 : (n >= 1024 ? 512 : (
 cudaError_t launch_rms_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c) {
     const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
     if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
-    rms_norm_kernel<false, false><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, src, dst, eps, nullptr, nullptr);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, rms_norm_kernel<false, false>, dim3((unsigned) rows), dim3(row_block(src.ne[0])), 0, src, src, dst, eps, nullptr, nullptr, nullptr, nullptr));
     return B200_LAUNCH_CHECK();
 }
-cudaError_t launch_rms_norm_mul(const TensorD & src, const TensorD & w, const TensorD & dst, float eps, void * act, float * norm_out, const LaunchCtx & c) {
+cudaError_t launch_rms_norm_mul(const TensorD & src, const TensorD & w, const TensorD & dst, float eps, void * act, float * norm_out,
+                                const float * addend, float * sum_out, const LaunchCtx & c) {
     const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
     if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
-    if (act) rms_norm_kernel<true, true><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, w, dst, eps, (blk_act128 *) act, norm_out);
-    else     rms_norm_kernel<true, false><<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, w, dst, eps, nullptr, norm_out);
+    if (act) (void) (launch_err = launch_k(c.use_pdl, c.stream, rms_norm_kernel<true, true>, dim3((unsigned) rows), dim3(row_block(src.ne[0])), 0, src, w, dst, eps, (blk_act128 *) act, norm_out, addend, sum_out));
+    else     (void) (launch_err = launch_k(c.use_pdl, c.stream, rms_norm_kernel<true, false>, dim3((unsigned) rows), dim3(row_block(src.ne[0])), 0, src, w, dst, eps, nullptr, norm_out, addend, sum_out));
     return B200_LAUNCH_CHECK();
 }
 
 // NORM: (x - mean) / sqrt(var + eps)
 __global__ void norm_kernel(const TensorD src, const TensorD dst, float eps) {
+    pdl_enter();
     __shared__ float sh[32];
     const int64_t row = blockIdx.x;
     const int64_t i1 = row % src.ne[1], i2 = (row / src.ne[1]) % src.ne[2], i3 = row / (src.ne[1] * src.ne[2]);
@@ -161,7 +173,7 @@ __global__ void norm_kernel(const TensorD src, const TensorD dst, float eps) {
 cudaError_t launch_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c) {
     const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
     if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
-    norm_kernel<<<(unsigned) rows, row_block(src.ne[0]), 0, c.stream>>>(src, dst, eps);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, norm_kernel, dim3((unsigned) rows), dim3(row_block(src.ne[0])), 0, src, dst, eps));
     return B200_LAUNCH_CHECK();
 }
 
@@ -177,6 +189,7 @@ template <int OP> __device__ __forceinline__ float bin_apply(float a, float b) {
 
 template <int OP>
 __global__ void bin_bcast_kernel(const TensorD a, const TensorD b, const TensorD d, int64_t total) {
+    pdl_enter();
     for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
         const int64_t i0 = i % d.ne[0], r1 = i / d.ne[0];
         const int64_t i1 = r1 % d.ne[1], r2 = r1 / d.ne[1];
@@ -193,6 +206,7 @@ __global__ void bin_bcast_kernel(const TensorD a, const TensorD b, const TensorD
 template <int OP>
 __global__ void bin_fast_kernel(const float4 * __restrict__ a, const float4 * __restrict__ b, float4 * __restrict__ d,
                                 int64_t n4, int64_t b_n4 /* elements/4 of b (row or full) */) {
+    pdl_enter();
     for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t) gridDim.x * blockDim.x) {
         const float4 x = a[i], y = b[i % b_n4];
         d[i] = make_float4(bin_apply<OP>(x.x, y.x), bin_apply<OP>(x.y, y.y), bin_apply<OP>(x.z, y.z), bin_apply<OP>(x.w, y.w));
@@ -227,12 +241,12 @@ static cudaError_t bin_dispatch(const TensorD & a, const TensorD & b, const Tens
         bool same_b = true;
         if (b_full) for (int i = 0; i < 4; ++i) same_b = same_b && b.ne[i] == d.ne[i];
         if (same_b) {
-            bin_fast_kernel<OP><<<grid_for(total / 4, 256, c.sm_count), 256, 0, c.stream>>>(
-                (const float4 *) a.data, (const float4 *) b.data, (float4 *) d.data, total / 4, nb_ / 4);
+            (void) (launch_err = launch_k(c.use_pdl, c.stream, bin_fast_kernel<OP>, dim3(grid_for(total / 4, 256, c.sm_count)), dim3(256), 0, 
+                (const float4 *) a.data, (const float4 *) b.data, (float4 *) d.data, total / 4, nb_ / 4));
             return B200_LAUNCH_CHECK();
         }
     }
-    bin_bcast_kernel<OP><<<grid_for(total, 256, c.sm_count), 256, 0, c.stream>>>(a, b, d, total);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, bin_bcast_kernel<OP>, dim3(grid_for(total, 256, c.sm_count)), dim3(256), 0, a, b, d, total));
     return B200_LAUNCH_CHECK();
 }
 
@@ -274,31 +288,34 @@ __device__ __forceinline__ float un_apply(int op, float x) {
     return x;
 }
 __global__ void unary_kernel(int op, const float * __restrict__ x, float * __restrict__ y, int64_t n) {
+    pdl_enter();
     for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) y[i] = un_apply(op, x[i]);
 }
 cudaError_t launch_unary(int op, const TensorD & src, const TensorD & dst, const LaunchCtx & c) {
     const int64_t n = nelem(src);
     if (n == 0) return cudaSuccess;
-    unary_kernel<<<grid_for(n, 256, c.sm_count), 256, 0, c.stream>>>(op, (const float *) src.data, (float *) dst.data, n);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, unary_kernel, dim3(grid_for(n, 256, c.sm_count)), dim3(256), 0, op, (const float *) src.data, (float *) dst.data, n));
     return B200_LAUNCH_CHECK();
 }
 
 __global__ void scale_kernel(const float * __restrict__ x, float * __restrict__ y, float s, int64_t n) {
+    pdl_enter();
     for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) y[i] = x[i] * s;
 }
 cudaError_t launch_scale(const TensorD & src, const TensorD & dst, float s, const LaunchCtx & c) {
     const int64_t n = nelem(src);
     if (n == 0) return cudaSuccess;
-    scale_kernel<<<grid_for(n, 256, c.sm_count), 256, 0, c.stream>>>((const float *) src.data, (float *) dst.data, s, n);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, scale_kernel, dim3(grid_for(n, 256, c.sm_count)), dim3(256), 0, (const float *) src.data, (float *) dst.data, s, n));
     return B200_LAUNCH_CHECK();
 }
 __global__ void clamp_kernel(const float * __restrict__ x, float * __restrict__ y, float lo, float hi, int64_t n) {
+    pdl_enter();
     for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) y[i] = fminf(fmaxf(x[i], lo), hi);
 }
 cudaError_t launch_clamp(const TensorD & src, const TensorD & dst, float lo, float hi, const LaunchCtx & c) {
     const int64_t n = nelem(src);
     if (n == 0) return cudaSuccess;
-    clamp_kernel<<<grid_for(n, 256, c.sm_count), 256, 0, c.stream>>>((const float *) src.data, (float *) dst.data, lo, hi, n);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, clamp_kernel, dim3(grid_for(n, 256, c.sm_count)), dim3(256), 0, (const float *) src.data, (float *) dst.data, lo, hi, n));
     return B200_LAUNCH_CHECK();
 }
 
@@ -306,6 +323,7 @@ cudaError_t launch_clamp(const TensorD & src, const TensorD & dst, float lo, flo
 template <bool EMIT>
 __global__ void silu_mul_kernel(const float * __restrict__ g, const float * __restrict__ u, float * __restrict__ y,
                                 int64_t n0, int64_t rows, blk_act128 * act, float * __restrict__ silu_out) {
+    pdl_enter();
     const int64_t npad = (n0 + 127) & ~(int64_t) 127;
     const int64_t per_row = npad / 4;
     const int64_t total = per_row * rows;
@@ -333,10 +351,10 @@ cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const Tens
     const int64_t n0 = gate.ne[0], rows = nelem(gate) / (n0 ? n0 : 1);
     if (n0 == 0 || rows == 0) return cudaSuccess;
     const int64_t threads = ((n0 + 127) / 128 * 32) * rows;
-    if (act) silu_mul_kernel<true><<<grid_for(threads, 256, c.sm_count), 256, 0, c.stream>>>(
-                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, (blk_act128 *) act, silu_out);
-    else     silu_mul_kernel<false><<<grid_for(threads, 256, c.sm_count), 256, 0, c.stream>>>(
-                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, nullptr, silu_out);
+    if (act) (void) (launch_err = launch_k(c.use_pdl, c.stream, silu_mul_kernel<true>, dim3(grid_for(threads, 256, c.sm_count)), dim3(256), 0, 
+                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, (blk_act128 *) act, silu_out));
+    else     (void) (launch_err = launch_k(c.use_pdl, c.stream, silu_mul_kernel<false>, dim3(grid_for(threads, 256, c.sm_count)), dim3(256), 0, 
+                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, nullptr, silu_out));
     return B200_LAUNCH_CHECK();
 }
 
@@ -363,6 +381,7 @@ __device__ __forceinline__ void rope_cs(const RopeK & r, float theta_extrap, int
 template <typename T>
 __global__ void rope_kernel(const TensorD src, const int32_t * __restrict__ pos, const float * __restrict__ ff,
                             const TensorD dst, const RopeK r, int64_t total_pairs) {
+    pdl_enter();
     const int64_t half0 = src.ne[0] / 2;
     for (int64_t t = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; t < total_pairs; t += (int64_t) gridDim.x * blockDim.x) {
         const int64_t ip = t % half0, r1 = t / half0;
@@ -401,9 +420,89 @@ cudaError_t launch_rope(const TensorD & src, const int32_t * pos, const float * 
     const float start = floorf(corr_dim(rp.beta_fast)), end = ceilf(corr_dim(rp.beta_slow));
     r.corr0 = fmaxf(0.0f, start);
     r.corr1 = fminf((float) rp.n_dims - 1.0f, end);
-    if (src.type == T_F32)      rope_kernel<float><<<grid_for(total, 256, c.sm_count), 256, 0, c.stream>>>(src, pos, ff, dst, r, total);
-    else if (src.type == T_F16) rope_kernel<__half><<<grid_for(total, 256, c.sm_count), 256, 0, c.stream>>>(src, pos, ff, dst, r, total);
+    if (src.type == T_F32)      (void) (launch_err = launch_k(c.use_pdl, c.stream, rope_kernel<float>, dim3(grid_for(total, 256, c.sm_count)), dim3(256), 0, src, pos, ff, dst, r, total));
+    else if (src.type == T_F16) (void) (launch_err = launch_k(c.use_pdl, c.stream, rope_kernel<__half>, dim3(grid_for(total, 256, c.sm_count)), dim3(256), 0, src, pos, ff, dst, r, total));
     else return cudaErrorInvalidValue;
+    return B200_LAUNCH_CHECK();
+}
+
+// ROPE of the query and key projections plus the KV-cache store of one layer in a single launch
+// (src/llama.cpp:157-199 and :1511-1531 emit ROPE, ROPE, CPY, CPY): work items are rotation pairs of Q,
+// rotation pairs of K (written as F32 and, rounded to F16, into the cache rows), then pairs of V values
+// (F32 -> F16 into the cache rows).  Q, K, V are contiguous [hd, n_head, n_tok] F32; the cache row
+// offsets are read from device memory so that a captured launch stays valid from token to token.
+struct RopeKvArgs {
+    const float * q_src; float * q_dst; int64_t q_pairs;      // n_tok * n_head   * hd / 2
+    const float * k_src; float * k_dst; int64_t k_pairs;      // n_tok * n_head_kv * hd / 2
+    const float * v_src; int64_t v_pairs;
+    __half * k_cache; __half * v_cache;                        // bases of the viewed cache tensors
+    const int64_t * k_off; const int64_t * v_off;             // byte offsets of the views (device memory) or null
+    int64_t k_off_imm, v_off_imm;                             // ... used when the pointers are null
+    const int32_t * pos; const float * ff;
+    int hd, n_head, n_head_kv;
+    RopeK r;
+};
+__global__ void rope_kv_kernel(const RopeKvArgs a) {
+    pdl_enter();
+    const int64_t total = a.q_pairs + a.k_pairs + a.v_pairs;
+    const int half_hd = a.hd / 2;
+    __half * kc = (__half *) ((char *) a.k_cache + (a.k_off ? *a.k_off : a.k_off_imm));
+    __half * vc = (__half *) ((char *) a.v_cache + (a.v_off ? *a.v_off : a.v_off_imm));
+    for (int64_t t = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t) gridDim.x * blockDim.x) {
+        if (t >= a.q_pairs + a.k_pairs) {
+            const int64_t i = t - a.q_pairs - a.k_pairs;
+            const float2 v = ((const float2 *) a.v_src)[i];
+            ((__half2 *) vc)[i] = __floats2half2_rn(v.x, v.y);
+            continue;
+        }
+        const bool is_k = t >= a.q_pairs;
+        const int64_t i = is_k ? t - a.q_pairs : t;
+        const int heads = is_k ? a.n_head_kv : a.n_head;
+        const int ip = (int) (i % half_hd);
+        const int64_t rowi = i / half_hd;                       // (token, head) row
+        const int64_t tok = rowi / heads;
+        const float * xs = (is_k ? a.k_src : a.q_src) + rowi * a.hd;
+        float *       yd = (is_k ? a.k_dst : a.q_dst) + rowi * a.hd;
+        const int i0 = 2 * ip;
+        float o0, o1; int ia, ib;
+        if (i0 >= a.r.n_dims) { ia = i0; ib = i0 + 1; o0 = xs[ia]; o1 = xs[ib]; }
+        else {
+            const float theta_base = (float) a.pos[tok] * powf(a.r.theta_scale, (float) ip);
+            const float f = a.ff ? a.ff[ip] : 1.0f;
+            float c, s;
+            rope_cs(a.r, theta_base / f, i0, c, s);
+            ia = a.r.neox ? ip : i0; ib = a.r.neox ? ip + a.r.n_dims / 2 : i0 + 1;
+            const float x0 = xs[ia], x1 = xs[ib];
+            o0 = x0 * c - x1 * s; o1 = x0 * s + x1 * c;
+        }
+        yd[ia] = o0; yd[ib] = o1;
+        if (is_k) { kc[rowi * a.hd + ia] = __float2half_rn(o0); kc[rowi * a.hd + ib] = __float2half_rn(o1); }
+    }
+}
+static RopeK make_ropek(const RopeParams & rp) {
+    RopeK r;
+    r.n_dims = rp.n_dims; r.neox = (rp.mode & 2) ? 1 : 0;
+    r.freq_scale = rp.freq_scale; r.ext_factor = rp.ext_factor; r.attn_factor = rp.attn_factor;
+    r.theta_scale = powf(rp.freq_base, -2.0f / (float) rp.n_dims);
+    auto corr_dim = [&](float n_rot) {
+        return (float) rp.n_dims * logf((float) rp.n_ctx_orig / (n_rot * 2.0f * 3.14159265358979323846f)) / (2.0f * logf(rp.freq_base));
+    };
+    r.corr0 = fmaxf(0.0f, floorf(corr_dim(rp.beta_fast)));
+    r.corr1 = fminf((float) rp.n_dims - 1.0f, ceilf(corr_dim(rp.beta_slow)));
+    return r;
+}
+cudaError_t launch_rope_kv(const RopeKvLaunch & l, const RopeParams & rp, const LaunchCtx & c) {
+    RopeKvArgs a;
+    a.q_src = l.q_src; a.q_dst = l.q_dst; a.q_pairs = l.n_tok * l.n_head * l.hd / 2;
+    a.k_src = l.k_src; a.k_dst = l.k_dst; a.k_pairs = l.n_tok * l.n_head_kv * l.hd / 2;
+    a.v_src = l.v_src; a.v_pairs = l.v_elems / 2;
+    a.k_cache = (__half *) l.k_cache; a.v_cache = (__half *) l.v_cache;
+    a.k_off = l.k_off_dev; a.v_off = l.v_off_dev; a.k_off_imm = l.k_off; a.v_off_imm = l.v_off;
+    a.pos = l.pos; a.ff = l.ff; a.hd = (int) l.hd; a.n_head = (int) l.n_head; a.n_head_kv = (int) l.n_head_kv;
+    a.r = make_ropek(rp);
+    const int64_t total = a.q_pairs + a.k_pairs + a.v_pairs;
+    if (total == 0) return cudaSuccess;
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, rope_kv_kernel, dim3(grid_for(total, 256, c.sm_count)), dim3(256), 0, a));
     return B200_LAUNCH_CHECK();
 }
 
@@ -411,6 +510,7 @@ cudaError_t launch_rope(const TensorD & src, const int32_t * pos, const float * 
 // CPY / DUP / CONT
 // ---------------------------------------------------------------------------
 __global__ void cpy_elem_kernel(const TensorD s, const TensorD d, int64_t total, const int64_t * __restrict__ dyn_off) {
+    pdl_enter();
     const int64_t doff = dyn_off ? *dyn_off : 0;   // byte offset of the destination view, kept in device memory so a captured launch stays valid
     for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
         int64_t r = i;
@@ -510,6 +610,7 @@ __device__ void quantize_block32(const float * x, uint8_t * out) {
 
 template <int QT>
 __global__ void cpy_f32_q_kernel(const TensorD s, const TensorD d, int64_t nblocks, const int64_t * __restrict__ dyn_off) {
+    pdl_enter();
     const int bb = type_block_bytes(QT);
     const int64_t doff = dyn_off ? *dyn_off : 0;
     for (int64_t ib = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; ib < nblocks; ib += (int64_t) gridDim.x * blockDim.x) {
@@ -545,16 +646,16 @@ cudaError_t launch_cpy(const TensorD & s, const TensorD & d, const LaunchCtx & c
         const int64_t nb = total / 32;
         const unsigned g = grid_for(nb, 128, c.sm_count);
         switch (d.type) {
-            case T_Q8_0: cpy_f32_q_kernel<T_Q8_0><<<g, 128, 0, c.stream>>>(s, d, nb, dyn_off); break;
-            case T_Q4_0: cpy_f32_q_kernel<T_Q4_0><<<g, 128, 0, c.stream>>>(s, d, nb, dyn_off); break;
-            case T_Q4_1: cpy_f32_q_kernel<T_Q4_1><<<g, 128, 0, c.stream>>>(s, d, nb, dyn_off); break;
-            case T_Q5_0: cpy_f32_q_kernel<T_Q5_0><<<g, 128, 0, c.stream>>>(s, d, nb, dyn_off); break;
-            case T_Q5_1: cpy_f32_q_kernel<T_Q5_1><<<g, 128, 0, c.stream>>>(s, d, nb, dyn_off); break;
+            case T_Q8_0: (void) (launch_err = launch_k(c.use_pdl, c.stream, cpy_f32_q_kernel<T_Q8_0>, dim3(g), dim3(128), 0, s, d, nb, dyn_off)); break;
+            case T_Q4_0: (void) (launch_err = launch_k(c.use_pdl, c.stream, cpy_f32_q_kernel<T_Q4_0>, dim3(g), dim3(128), 0, s, d, nb, dyn_off)); break;
+            case T_Q4_1: (void) (launch_err = launch_k(c.use_pdl, c.stream, cpy_f32_q_kernel<T_Q4_1>, dim3(g), dim3(128), 0, s, d, nb, dyn_off)); break;
+            case T_Q5_0: (void) (launch_err = launch_k(c.use_pdl, c.stream, cpy_f32_q_kernel<T_Q5_0>, dim3(g), dim3(128), 0, s, d, nb, dyn_off)); break;
+            case T_Q5_1: (void) (launch_err = launch_k(c.use_pdl, c.stream, cpy_f32_q_kernel<T_Q5_1>, dim3(g), dim3(128), 0, s, d, nb, dyn_off)); break;
             default: return cudaErrorInvalidValue;
         }
         return B200_LAUNCH_CHECK();
     }
-    cpy_elem_kernel<<<grid_for(total, 256, c.sm_count), 256, 0, c.stream>>>(s, d, total, dyn_off);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, cpy_elem_kernel, dim3(grid_for(total, 256, c.sm_count)), dim3(256), 0, s, d, total, dyn_off));
     return B200_LAUNCH_CHECK();
 }
 
@@ -563,6 +664,7 @@ cudaError_t launch_cpy(const TensorD & s, const TensorD & d, const LaunchCtx & c
 // ---------------------------------------------------------------------------
 template <int T>
 __global__ void get_rows_kernel(const TensorD src, const TensorD idx, const TensorD dst) {
+    pdl_enter();
     // grid: x over chunks of the row, y = index position, z = batch (i11 + i12*ne11)
     const int64_t i10 = blockIdx.y;
     const int64_t i11 = blockIdx.z % idx.ne[1], i12 = blockIdx.z / idx.ne[1];
@@ -584,7 +686,7 @@ cudaError_t launch_get_rows(const TensorD & src, const TensorD & idx, const Tens
     const int block = 256;
     int64_t gx = (src.ne[0] + block - 1) / block; if (gx > 64) gx = 64;
     dim3 grid((unsigned) gx, (unsigned) idx.ne[0], (unsigned) (idx.ne[1] * idx.ne[2]));
-#define GR(T) case T: get_rows_kernel<T><<<grid, block, 0, c.stream>>>(src, idx, dst); break;
+#define GR(T) case T: (void) (launch_err = launch_k(c.use_pdl, c.stream, get_rows_kernel<T>, dim3(grid), dim3(block), 0, src, idx, dst)); break;
     switch (src.type) {
         GR(T_F32) GR(T_F16) GR(T_BF16) GR(T_Q4_0) GR(T_Q4_1) GR(T_Q5_0) GR(T_Q5_1) GR(T_Q8_0) GR(T_Q4_K) GR(T_Q5_K) GR(T_Q6_K)
         default: return cudaErrorInvalidValue;
@@ -598,6 +700,7 @@ cudaError_t launch_get_rows(const TensorD & src, const TensorD & idx, const Tens
 // ---------------------------------------------------------------------------
 __global__ void soft_max_kernel(const TensorD src, const TensorD mask, int has_mask, const TensorD dst,
                                 float scale, float max_bias, float m0, float m1, int n_head_log2) {
+    pdl_enter();
     extern __shared__ float row_cache[];
     __shared__ float sh[32];
     const int64_t row = blockIdx.x;
@@ -640,8 +743,8 @@ cudaError_t launch_soft_max(const TensorD & src, const TensorD * mask, const Ten
         attr_mask |= 1u << c.device;
     }
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    soft_max_kernel<<<(unsigned) rows, row_block(src.ne[0]), smem, c.stream>>>(src, mask ? *mask : src, mask ? 1 : 0, dst,
-                                                                               scale, max_bias, m0, m1, n_head_log2);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, soft_max_kernel, dim3((unsigned) rows), dim3(row_block(src.ne[0])), smem, src, mask ? *mask : src, mask ? 1 : 0, dst,
+                                                                               scale, max_bias, m0, m1, n_head_log2));
     return B200_LAUNCH_CHECK();
 }
 

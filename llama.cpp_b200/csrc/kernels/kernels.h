@@ -23,7 +23,9 @@ struct LaunchCtx {
     int   sm_count;
     int * status;        // device status word (ERR_* codes), never reset by kernels
     int   use_pdl;       // launch with programmatic stream serialization where supported
+    unsigned * fa_tickets;   // FATTN_DEC_TICKETS zero-initialised counters for the decode attention kernel (or null)
 };
+static constexpr int FATTN_DEC_TICKETS = 4096;
 
 // ---- quantized mat-vec (mmvq.cu) ----
 struct MmvqArgs {
@@ -35,12 +37,14 @@ struct MmvqArgs {
     int x_col0, x_ncols, xq_ne12;                      // first column, columns per batch in Xq, dim-2 extent of Xq (0 = ne12)
     const int32_t * ids; int64_t ids_s12, ids_s13;     // MUL_MAT_ID expert indices (or null)
     int * status; int sm_count, device, use_pdl;
+    // up to two more weight matrices of the same type, K and row stride that share Xq (direct Q4_K/Q5_K kernel only)
+    int n_extra; const void * extra_W[2]; float * extra_dst[2]; int64_t extra_dst_nb1[2]; int extra_M[2];
 };
 bool        mmvq_type_supported(int type);
 size_t      act128_bytes(int64_t K, int64_t ncols);
 // columns ordered [i13][i12][i11]; s11..s13 are element strides of x
 cudaError_t launch_quantize_act128(const float * x, int64_t ne11, int64_t ne12, int64_t ne13,
-                                   int64_t s11, int64_t s12, int64_t s13, void * y, int K, cudaStream_t stream);
+                                   int64_t s11, int64_t s12, int64_t s13, void * y, int K, cudaStream_t stream, int use_pdl = 0);
 cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream);
 // direct 128-bit-coalesced variant for Q4_K / Q5_K (mmvq_k.cu); launch_mmvq routes to it when applicable
 bool        mmvq_k_applicable(const MmvqArgs & a);
@@ -68,9 +72,10 @@ enum UnOp  { UN_SILU = 0, UN_GELU, UN_GELU_QUICK, UN_RELU, UN_TANH, UN_SIGMOID, 
 
 cudaError_t launch_rms_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c);
 // y = rms_norm(x) * w   (w broadcast like ggml MUL's src1); optionally also emits blk_act128 of y
-// norm_out (optional): contiguous rows receiving the plain rms_norm(x)
+// norm_out (optional): contiguous rows receiving the plain rms_norm(x).  addend/sum_out (optional, contiguous
+// rows): the input becomes src + addend, which is also written to sum_out (fused residual add)
 cudaError_t launch_rms_norm_mul(const TensorD & src, const TensorD & w, const TensorD & dst, float eps,
-                                void * act128_out, float * norm_out, const LaunchCtx & c);
+                                void * act128_out, float * norm_out, const float * addend, float * sum_out, const LaunchCtx & c);
 cudaError_t launch_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c);
 cudaError_t launch_bin_bcast(int op, const TensorD & a, const TensorD & b, const TensorD & dst, const LaunchCtx & c);
 cudaError_t launch_unary(int op, const TensorD & src, const TensorD & dst, const LaunchCtx & c);
@@ -85,6 +90,16 @@ struct RopeParams {
 };
 cudaError_t launch_rope(const TensorD & src, const int32_t * pos, const float * freq_factors, const TensorD & dst,
                         const RopeParams & rp, const LaunchCtx & c);
+
+// ROPE(Q) + ROPE(K) + KV-cache store (K rotated, V as is; F32 -> F16) in one launch
+struct RopeKvLaunch {
+    const float * q_src; float * q_dst; const float * k_src; float * k_dst; const float * v_src;
+    int64_t hd, n_head, n_head_kv, n_tok, v_elems;
+    void * k_cache; void * v_cache; int64_t k_off, v_off;        // view bases and byte offsets
+    const int64_t * k_off_dev; const int64_t * v_off_dev;        // if set, offsets are read from device memory instead
+    const int32_t * pos; const float * ff;
+};
+cudaError_t launch_rope_kv(const RopeKvLaunch & l, const RopeParams & rp, const LaunchCtx & c);
 
 bool        cpy_supported(int src_type, int dst_type);
 // dyn_off (optional, device pointer): byte offset added to dst.data, read by the kernel at run time
@@ -106,6 +121,11 @@ size_t      fattn_mma_workspace_bytes(const TensorD & q, const TensorD & k);
 cudaError_t launch_fattn_mma(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
                              const FattnParams & fp, void * workspace, const LaunchCtx & c);
 // n_kernels (optional) receives the number of kernels launched
+// GQA-shared split-KV kernel for decode (fattn_dec.cu); needs LaunchCtx::fa_tickets
+bool        fattn_dec_applicable(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask);
+size_t      fattn_dec_workspace_bytes(const TensorD & q, const TensorD & k, int sm_count);
+cudaError_t launch_fattn_dec(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
+                             const FattnParams & fp, void * tickets, void * partials, const LaunchCtx & c);
 cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
                          const FattnParams & fp, void * workspace, const LaunchCtx & c, int * n_kernels = nullptr);
 

@@ -15,6 +15,7 @@ __device__ __forceinline__ float ldx(const char * p, int type) {
 }
 
 __global__ void __launch_bounds__(256) matmul_f_kernel(const TensorD W, const TensorD X, const TensorD dst) {
+    pdl_enter();
     __shared__ float Ws[32][33], Xs[32][33];
     const int tx = threadIdx.x, ty = threadIdx.y;
     const int64_t m0 = (int64_t) blockIdx.x * 32, n0 = (int64_t) blockIdx.y * 32;
@@ -51,7 +52,7 @@ cudaError_t launch_matmul_f(const TensorD & W, const TensorD & X, const TensorD 
     const int64_t M = W.ne[1], N = X.ne[1], batch = X.ne[2] * X.ne[3];
     if (M == 0 || N == 0 || batch == 0) return cudaSuccess;
     dim3 grid((unsigned) ((M + 31) / 32), (unsigned) ((N + 31) / 32), (unsigned) batch);
-    matmul_f_kernel<<<grid, dim3(32, 8), 0, c.stream>>>(W, X, dst);
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, matmul_f_kernel, dim3(grid), dim3(dim3(32, 8)), 0, W, X, dst));
     return cudaGetLastError();
 }
 

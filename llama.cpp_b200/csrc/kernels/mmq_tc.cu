@@ -213,6 +213,7 @@ template <> struct Deq32<T_Q8_0> {
 
 // ---- F32 -> F16 activations (pre-pass) --------------------------------------------------------
 __global__ void tc_convert_x_kernel(const float * __restrict__ x, int64_t x_nb1 /*bytes*/, __half * __restrict__ y, int64_t K, int64_t N) {
+    pdl_enter();
     const int64_t total = N * K / 2;
     for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
         const int64_t n = (2 * i) / K, k = (2 * i) % K;
@@ -239,6 +240,7 @@ __device__ __forceinline__ void tma_load_2d(void * smem_dst, const CUtensorMap *
 template <int T>
 __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
+    pdl_launch_dependents();          // the next kernel may start its prologue (its weight prefetch) right away
     // operand stages must be 1024-byte aligned for the 128-byte swizzle pattern
     uint8_t * smem = (uint8_t *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
     __shared__ uint64_t full_bar[TC_STAGES], empty_bar[TC_STAGES], accum_bar;
@@ -355,7 +357,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
     tc_fence_before();
     __syncthreads();
     if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, TC_TMEM_COLS); }
-    pdl_launch_dependents();
 }
 
 bool mmq_tc_supported(int type, int64_t M, int64_t N, int64_t K) {
@@ -387,7 +388,7 @@ static encode_tiled_fn get_encode_tiled() {
 }
 
 template <int T>
-static cudaError_t launch_tc_t(const TcParams & p, int device, cudaStream_t stream) {
+static cudaError_t launch_tc_t(const TcParams & p, int device, int use_pdl, cudaStream_t stream) {
     auto kern = mmq_tc_kernel<T>;
     const size_t smem = (size_t) TC_STAGES * TC_STAGE_BYTES + 1024;
     static unsigned attr_mask = 0;
@@ -407,8 +408,7 @@ static cudaError_t launch_tc_t(const TcParams & p, int device, cudaStream_t stre
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
     dim3 grid((unsigned) ((p.N + TC_BN - 1) / TC_BN), (unsigned) ((p.M + TC_BM - 1) / TC_BM));
-    kern<<<grid, TC_THREADS, smem, stream>>>(p, xmap);
-    return cudaGetLastError();
+    return launch_k(use_pdl, stream, kern, grid, dim3(TC_THREADS), smem, p, xmap);
 }
 
 cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float * X, int64_t x_nb1, float * dst, int64_t dst_nb1,
@@ -417,22 +417,21 @@ cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float *
     {
         const int64_t total = N * K / 2;
         int64_t g = (total + 255) / 256; if (g > (int64_t) c.sm_count * 8) g = (int64_t) c.sm_count * 8;
-        tc_convert_x_kernel<<<(unsigned) g, 256, 0, c.stream>>>(X, x_nb1, xh, K, N);
-        cudaError_t e = cudaGetLastError();
+        cudaError_t e = launch_k(c.use_pdl, c.stream, tc_convert_x_kernel, dim3((unsigned) g), dim3(256), 0, X, x_nb1, xh, K, N);
         if (e != cudaSuccess) return e;
     }
     TcParams p;
     p.W = (const uint8_t *) W; p.w_nb1 = w_nb1; p.Xh = xh; p.dst = dst; p.dst_nb1 = dst_nb1;
     p.M = (int) M; p.N = (int) N; p.K = (int) K; p.status = c.status;
     switch (type) {
-        case T_Q4_0: return launch_tc_t<T_Q4_0>(p, c.device, c.stream);
-        case T_Q4_1: return launch_tc_t<T_Q4_1>(p, c.device, c.stream);
-        case T_Q5_0: return launch_tc_t<T_Q5_0>(p, c.device, c.stream);
-        case T_Q5_1: return launch_tc_t<T_Q5_1>(p, c.device, c.stream);
-        case T_Q8_0: return launch_tc_t<T_Q8_0>(p, c.device, c.stream);
-        case T_Q4_K: return launch_tc_t<T_Q4_K>(p, c.device, c.stream);
-        case T_Q5_K: return launch_tc_t<T_Q5_K>(p, c.device, c.stream);
-        case T_Q6_K: return launch_tc_t<T_Q6_K>(p, c.device, c.stream);
+        case T_Q4_0: return launch_tc_t<T_Q4_0>(p, c.device, c.use_pdl, c.stream);
+        case T_Q4_1: return launch_tc_t<T_Q4_1>(p, c.device, c.use_pdl, c.stream);
+        case T_Q5_0: return launch_tc_t<T_Q5_0>(p, c.device, c.use_pdl, c.stream);
+        case T_Q5_1: return launch_tc_t<T_Q5_1>(p, c.device, c.use_pdl, c.stream);
+        case T_Q8_0: return launch_tc_t<T_Q8_0>(p, c.device, c.use_pdl, c.stream);
+        case T_Q4_K: return launch_tc_t<T_Q4_K>(p, c.device, c.use_pdl, c.stream);
+        case T_Q5_K: return launch_tc_t<T_Q5_K>(p, c.device, c.use_pdl, c.stream);
+        case T_Q6_K: return launch_tc_t<T_Q6_K>(p, c.device, c.use_pdl, c.stream);
     }
     return cudaErrorInvalidValue;
 }

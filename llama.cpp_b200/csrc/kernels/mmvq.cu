@@ -32,6 +32,7 @@ namespace b200 {
 __global__ void quantize_act128_kernel(const float * __restrict__ x, int64_t ne11, int64_t ne12,
                                        int64_t s11, int64_t s12, int64_t s13 /* element strides of dims 1,2,3 */,
                                        blk_act128 * __restrict__ y, int K, int nblk /*per column*/, int64_t ncols) {
+    pdl_enter();
     const int64_t gw   = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int     lane = threadIdx.x & 31;
     if (gw >= ncols * nblk) return;
@@ -353,6 +354,7 @@ template <int T, int N>
 __global__ void __launch_bounds__(MMVQ_THREADS, 1) mmvq_kernel(const MmvqParams p) {
     using W = WT<T>;
     extern __shared__ __align__(128) uint8_t smem[];
+    pdl_launch_dependents();          // the next kernel may start its prologue (its weight prefetch) right away
     __shared__ uint64_t full_bar[MMVQ_STAGES], empty_bar[MMVQ_STAGES];
     __shared__ int abort_flag;
 
@@ -476,7 +478,6 @@ __global__ void __launch_bounds__(MMVQ_THREADS, 1) mmvq_kernel(const MmvqParams 
             }
         }
     }
-    pdl_launch_dependents();
 }
 
 template <int T, int N>
@@ -554,15 +555,14 @@ bool mmvq_type_supported(int type) {
 size_t act128_bytes(int64_t K, int64_t ncols) { return (size_t) ((K + 127) / 128) * 160 * (size_t) ncols; }
 
 cudaError_t launch_quantize_act128(const float * x, int64_t ne11, int64_t ne12, int64_t ne13,
-                                   int64_t s11, int64_t s12, int64_t s13, void * y, int K, cudaStream_t stream) {
+                                   int64_t s11, int64_t s12, int64_t s13, void * y, int K, cudaStream_t stream, int use_pdl) {
     const int nblk = (K + 127) / 128;
     const int64_t ncols = ne11 * ne12 * ne13;
     const int64_t warps = ncols * nblk;
     if (warps == 0) return cudaSuccess;
     const int wpb = 8;
-    quantize_act128_kernel<<<(unsigned) ((warps + wpb - 1) / wpb), wpb * 32, 0, stream>>>(
-        x, ne11, ne12, s11, s12, s13, (blk_act128 *) y, K, nblk, ncols);
-    return cudaGetLastError();
+    return launch_k(use_pdl, stream, quantize_act128_kernel, dim3((unsigned) ((warps + wpb - 1) / wpb)), dim3(wpb * 32), 0,
+                    x, ne11, ne12, s11, s12, s13, (blk_act128 *) y, K, nblk, ncols);
 }
 
 cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream) {

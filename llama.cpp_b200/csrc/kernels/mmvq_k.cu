@@ -25,13 +25,21 @@ namespace b200 {
 static constexpr int MK_WARPS = 8;
 static constexpr int MK_BATCH = 2;          // 64-weight units per lane in flight (2 x 48 bytes of loads)
 
+// Up to three weight matrices that share the activation operand (wq/wk/wv, gate/up) are served by one
+// launch: their rows are concatenated into one row space of M = m_end[nmat-1] rows.
 struct MkParams {
-    const uint8_t * W;  int64_t w_nb1;
-    const uint8_t * Xq; int64_t xq_col_bytes;
-    float * dst;        int64_t dst_nb1;
+    const uint8_t * W[3];  int64_t w_nb1;
+    const uint8_t * Xq;    int64_t xq_col_bytes;
+    float * dst[3];        int64_t dst_nb1[3];
+    int m_end[3], nmat;
     int M, K;
     int x_col0;
 };
+__device__ __forceinline__ const uint8_t * mk_row_ptr(const MkParams & p, int row, int & mat, int & local) {
+    mat = (row >= p.m_end[0]) + (row >= p.m_end[1] && p.nmat > 2);
+    local = row - (mat ? p.m_end[mat - 1] : 0);
+    return p.W[mat] + (int64_t) local * p.w_nb1;
+}
 
 __device__ __forceinline__ uint4 ldg128(const void * p) { return __ldg((const uint4 *) p); }
 
@@ -40,6 +48,7 @@ __global__ void __launch_bounds__(MK_WARPS * 32, 3) mmvq_k_kernel(const MkParams
     constexpr int BLK = (T == T_Q4_K) ? 144 : 176;
     constexpr int QS_OFF = (T == T_Q4_K) ? 16 : 48;
     extern __shared__ __align__(16) uint8_t acts[];           // [N][nblk128 * 160]
+    pdl_launch_dependents();          // the next kernel may start its prologue (its weight prefetch) right away
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nsb = p.K >> 8;                                  // super-blocks per row
@@ -73,8 +82,9 @@ __global__ void __launch_bounds__(MK_WARPS * 32, 3) mmvq_k_kernel(const MkParams
             }
         }
     };
-    const uint8_t * wr = p.W + (int64_t) row * p.w_nb1;
-    if (row < p.M) load_batch(wr, 0);        // weights do not depend on the previous kernel: fetch before waiting
+    int mat = 0, lrow = 0;
+    const uint8_t * wr = p.W[0];
+    if (row < p.M) { wr = mk_row_ptr(p, row, mat, lrow); load_batch(wr, 0); }        // weights do not depend on the previous kernel: fetch before waiting
 
     pdl_wait();
     for (int n = 0; n < N; ++n) {
@@ -143,16 +153,15 @@ __global__ void __launch_bounds__(MK_WARPS * 32, 3) mmvq_k_kernel(const MkParams
                 }
             }
         }
-        const int cur_row = row;
-        if (row + row_stride < p.M) { wr = p.W + (int64_t) (row + row_stride) * p.w_nb1; load_batch(wr, 0); }
+        const int cur_mat = mat, cur_row = lrow;
+        if (row + row_stride < p.M) { wr = mk_row_ptr(p, row + row_stride, mat, lrow); load_batch(wr, 0); }
 #pragma unroll
         for (int n = 0; n < N; ++n) acc[n] = warp_sum(acc[n]);
         if (lane == 0) {
 #pragma unroll
-            for (int n = 0; n < N; ++n) ((float *) ((uint8_t *) p.dst + (int64_t) n * p.dst_nb1))[cur_row] = acc[n];
+            for (int n = 0; n < N; ++n) ((float *) ((uint8_t *) p.dst[cur_mat] + (int64_t) n * p.dst_nb1[cur_mat]))[cur_row] = acc[n];
         }
     }
-    pdl_launch_dependents();
 }
 
 template <int T, int N>
@@ -203,16 +212,25 @@ bool mmvq_k_applicable(const MmvqArgs & a) {
     if (a.type != T_Q4_K && a.type != T_Q5_K) return false;
     if (a.ids || a.ne12 * a.ne13 != 1) return false;
     if (((uintptr_t) a.W & 15) || (a.w_nb1 & 15)) return false;
+    for (int i = 0; i < a.n_extra; ++i) if ((uintptr_t) a.extra_W[i] & 15) return false;
     if ((size_t) a.N * ((a.K + 127) / 128) * 160 > 200 * 1024) return false;
     return true;
 }
 
 cudaError_t launch_mmvq_k(const MmvqArgs & a, cudaStream_t stream) {
     MkParams p = {};
-    p.W = (const uint8_t *) a.W; p.w_nb1 = a.w_nb1;
+    p.W[0] = (const uint8_t *) a.W; p.w_nb1 = a.w_nb1;
     p.Xq = (const uint8_t *) a.Xq; p.xq_col_bytes = (int64_t) ((a.K + 127) / 128) * 160;
-    p.dst = a.dst; p.dst_nb1 = a.dst_nb1;
-    p.M = a.M; p.K = a.K; p.x_col0 = a.x_col0;
+    p.dst[0] = a.dst; p.dst_nb1[0] = a.dst_nb1;
+    p.m_end[0] = a.M; p.nmat = 1 + a.n_extra;
+    for (int i = 0; i < 2; ++i) {
+        const bool on = i < a.n_extra;
+        p.W[i + 1] = on ? (const uint8_t *) a.extra_W[i] : p.W[0];
+        p.dst[i + 1] = on ? a.extra_dst[i] : a.dst; p.dst_nb1[i + 1] = on ? a.extra_dst_nb1[i] : a.dst_nb1;
+        p.m_end[i + 1] = p.m_end[i] + (on ? a.extra_M[i] : 0);
+    }
+    if (p.nmat < 2) p.m_end[1] = 0x7fffffff;        // row >= m_end[1] never holds
+    p.M = p.m_end[p.nmat - 1]; p.K = a.K; p.x_col0 = a.x_col0;
     if (a.type == T_Q4_K) return launch_mk_t<T_Q4_K>(p, a.N, a.sm_count, a.device, a.use_pdl, stream);
     return launch_mk_t<T_Q5_K>(p, a.N, a.sm_count, a.device, a.use_pdl, stream);
 }

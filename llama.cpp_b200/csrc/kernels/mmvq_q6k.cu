@@ -44,6 +44,7 @@ __device__ __forceinline__ void lds_run(const uint8_t * p, uint32_t (&out)[NW]) 
 template <int N>
 __global__ void __launch_bounds__(Q6_WARPS * 32, 2) mmvq_q6k_kernel(const Q6Params p) {
     extern __shared__ __align__(16) uint8_t smem[];
+    pdl_launch_dependents();          // the next kernel may start its prologue (its weight prefetch) right away
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nsb = p.K >> 8;
     const int col_bytes = ((p.K + 127) >> 7) * 160;
@@ -142,7 +143,6 @@ __global__ void __launch_bounds__(Q6_WARPS * 32, 2) mmvq_q6k_kernel(const Q6Para
         }
         row += row_stride;
     }
-    pdl_launch_dependents();
 }
 
 template <int N>

@@ -147,19 +147,28 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
         for (int rr = 0; rr < FD_RT; ++rr)
 #pragma unroll
             for (int i = 0; i < DPL; ++i) o[rr][i] = 0.0f;
-        for (int kl = 0; kl < nkeys; ++kl) {
-            const float4 pv = *(const float4 *) ps[warp][kl];
-            if (pv.x == 0.0f && pv.y == 0.0f && pv.z == 0.0f && pv.w == 0.0f) continue;   // masked key (warp-uniform)
-            const __half * vr = (const __half *) (vbase + (int64_t) (kw0 + kl) * p.v_nb1) + lane * DPL;
-            float vf[DPL];
-            if (DPL == 4) { const uint2 raw = __ldg((const uint2 *) vr); const __half2 * h = (const __half2 *) &raw;
-                            const float2 a = __half22float2(h[0]), b = __half22float2(h[1]); vf[0] = a.x; vf[1] = a.y; vf[2 % DPL] = b.x; vf[3 % DPL] = b.y; }
-            else { const uint32_t raw = __ldg((const uint32_t *) vr); const float2 a = __half22float2(*(const __half2 *) &raw); vf[0] = a.x; vf[1 % DPL] = a.y; }
-            const float pr[FD_RT] = {pv.x, pv.y, pv.z, pv.w};
+        for (int kb = 0; kb < nkeys; kb += 8) {                     // 8 V rows in flight per lane
+            uint2 raw[8];
 #pragma unroll
-            for (int rr = 0; rr < FD_RT; ++rr)
+            for (int u = 0; u < 8; ++u) {
+                const int kl = min(kb + u, nkeys - 1);
+                const char * vr = vbase + (int64_t) (kw0 + kl) * p.v_nb1 + lane * DPL * 2;
+                if (DPL == 4) raw[u] = __ldg((const uint2 *) vr);
+                else { raw[u].x = __ldg((const uint32_t *) vr); raw[u].y = 0; }
+            }
 #pragma unroll
-                for (int i = 0; i < DPL; ++i) o[rr][i] += pr[rr] * vf[i];
+            for (int u = 0; u < 8; ++u) {
+                if (kb + u >= nkeys) break;
+                const float4 pv = *(const float4 *) ps[warp][kb + u];
+                if (pv.x == 0.0f && pv.y == 0.0f && pv.z == 0.0f && pv.w == 0.0f) continue;   // masked key (warp-uniform)
+                const float2 a = __half22float2(*(const __half2 *) &raw[u].x), b2 = __half22float2(*(const __half2 *) &raw[u].y);
+                const float vf[4] = {a.x, a.y, b2.x, b2.y};
+                const float pr[FD_RT] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+                for (int rr = 0; rr < FD_RT; ++rr)
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) o[rr][i] += pr[rr] * vf[i];
+            }
         }
         // ---- merge the 4 warps ----
         if (lane == 0) {
@@ -202,18 +211,34 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
         if (ticket_sh == (unsigned) p.n_splits - 1) {
             __threadfence();
             const float * base = p.ws + (((int64_t) i3 * p.n_head_kv + hk) * p.n_splits) * R * (D + 2);
-            for (int i = threadIdx.x; i < R * D; i += blockDim.x) {
-                const int r = i / D, d = i % D;
+            // per (row, split) weights exp(m_s - M) / L, computed once into shared memory (reusing ps)
+            float * wgt = &ps[0][0][0];                               // R * n_splits floats (<= 64 * 512 fits: 4096 floats)
+            for (int r = threadIdx.x; r < R; r += blockDim.x) {
                 float M = -INFINITY;
                 for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, base[((int64_t) s * R + r) * (D + 2) + D]);
-                float L = 0.0f, acc = 0.0f;
+                float L = 0.0f;
                 for (int s = 0; s < p.n_splits; ++s) {
                     const float * ps_ = base + ((int64_t) s * R + r) * (D + 2);
                     const float f = (ps_[D] == -INFINITY) ? 0.0f : expf(ps_[D] - M);
-                    L += ps_[D + 1] * f; acc += ps_[d] * f;
+                    wgt[r * p.n_splits + s] = f; L += ps_[D + 1] * f;
                 }
+                const float inv = 1.0f / L;
+                for (int s = 0; s < p.n_splits; ++s) wgt[r * p.n_splits + s] *= inv;
+            }
+            __syncthreads();
+            for (int i = threadIdx.x; i < R * D; i += blockDim.x) {
+                const int r = i / D, d = i % D;
+                float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+                int s = 0;
+                for (; s + 4 <= p.n_splits; s += 4) {                  // four independent loads per step
+                    acc0 += base[((int64_t) (s + 0) * R + r) * (D + 2) + d] * wgt[r * p.n_splits + s + 0];
+                    acc1 += base[((int64_t) (s + 1) * R + r) * (D + 2) + d] * wgt[r * p.n_splits + s + 1];
+                    acc2 += base[((int64_t) (s + 2) * R + r) * (D + 2) + d] * wgt[r * p.n_splits + s + 2];
+                    acc3 += base[((int64_t) (s + 3) * R + r) * (D + 2) + d] * wgt[r * p.n_splits + s + 3];
+                }
+                for (; s < p.n_splits; ++s) acc0 += base[((int64_t) s * R + r) * (D + 2) + d] * wgt[r * p.n_splits + s];
                 const int iq = r / p.gqa, head = hk * p.gqa + r % p.gqa;
-                p.dst[(((int64_t) i3 * p.n_q + iq) * p.n_head + head) * D + d] = acc / L;
+                p.dst[(((int64_t) i3 * p.n_q + iq) * p.n_head + head) * D + d] = (acc0 + acc1) + (acc2 + acc3);
             }
             if (threadIdx.x == 0) p.tickets[i3 * p.n_head_kv + hk] = 0;      // ready for the next launch
         }
@@ -225,7 +250,7 @@ static constexpr int FD_TICKETS = FATTN_DEC_TICKETS;
 bool fattn_dec_applicable(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask) {
     const int64_t D = q.ne[0];
     if (D != 64 && D != 128) return false;
-    if (q.ne[1] > 8 || q.ne[2] % k.ne[2] != 0) return false;
+    if (q.ne[1] > 8 || q.ne[2] % k.ne[2] != 0 || k.ne[1] > 65536) return false;
     if ((q.ne[2] / k.ne[2]) * q.ne[1] > 64) return false;
     if (k.ne[2] * q.ne[3] > FD_TICKETS) return false;
     auto al16 = [](const TensorD & t) { return ((uintptr_t) t.data & 15) == 0 && (t.nb[1] & 15) == 0 && (t.nb[2] & 15) == 0 && (t.nb[3] & 15) == 0; };
@@ -241,6 +266,7 @@ static int fd_pick_splits(int64_t n_head_kv_total, int64_t n_kv, int sm_count) {
     int64_t s = want < max_by_kv ? want : max_by_kv;
     const int64_t min_by_cap = (n_kv + FD_WARPS * FD_MAX_KEYS_PER_WARP - 1) / (FD_WARPS * FD_MAX_KEYS_PER_WARP);
     if (s < min_by_cap) s = min_by_cap;
+    if (s > 64) s = s > min_by_cap ? (min_by_cap > 64 ? min_by_cap : 64) : s;
     if (s < 1) s = 1;
     return (int) s;
 }

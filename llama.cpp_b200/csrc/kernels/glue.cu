@@ -82,7 +82,7 @@ __device__ __forceinline__ void emit_act128(const float (&v)[4], int64_t k0, int
 // ---------------------------------------------------------------------------
 template <bool HAS_W, bool EMIT>
 __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const TensorD dst, float eps, blk_act128 * act, float * norm_out,
-                                const float * __restrict__ addend, float * __restrict__ sum_out) {
+                                const float * addend, float * sum_out) {
     pdl_enter();
     __shared__ float sh[32];
     const int64_t row = blockIdx.x;
@@ -90,6 +90,39 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
     const float * x = (const float *) ((const char *) src.data + i1 * src.nb[1] + i2 * src.nb[2] + i3 * src.nb[3]);
     float *       y = (float *) ((char *) dst.data + i1 * dst.nb[1] + i2 * dst.nb[2] + i3 * dst.nb[3]);
     const int64_t n = src.ne[0];
+    const float * wr = nullptr;
+    if (HAS_W) wr = (const float *) ((const char *) w.data + (i1 % w.ne[1]) * w.nb[1] + (i2 % w.ne[2]) * w.nb[2] + (i3 % w.ne[3]) * w.nb[3]);
+    float * yn = norm_out ? norm_out + row * n : nullptr;
+    const int64_t npad = (n + 127) & ~(int64_t) 127;
+    blk_act128 * col = EMIT ? act + row * (npad >> 7) : nullptr;
+
+    // fast path (the usual case: one row of a few thousand values): every thread keeps its four values
+    // in registers between the reduction and the output, so the row is read exactly once
+    const bool fast = (n & 3) == 0 && npad <= (int64_t) blockDim.x * 4 && (!HAS_W || w.ne[0] == n) &&
+                      (((uintptr_t) x | (uintptr_t) y | (uintptr_t) wr | (uintptr_t) yn | (uintptr_t) addend | (uintptr_t) sum_out) & 15) == 0;
+    if (fast) {
+        const int64_t k0 = (int64_t) threadIdx.x * 4;
+        const bool in = k0 < n;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f), wv = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        if (in) {
+            v = *(const float4 *) (x + k0);
+            if (HAS_W) wv = *(const float4 *) (wr + k0);
+            if (addend) {
+                const float4 a4 = *(const float4 *) (addend + row * n + k0);
+                v.x += a4.x; v.y += a4.y; v.z += a4.z; v.w += a4.w;
+                *(float4 *) (sum_out + row * n + k0) = v;
+            }
+        }
+        const float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, sh);
+        const float scale = rsqrtf(ss / (float) n + eps);
+        float o[4] = {v.x * scale, v.y * scale, v.z * scale, v.w * scale};
+        if (in && yn) *(float4 *) (yn + k0) = make_float4(o[0], o[1], o[2], o[3]);
+        if (HAS_W) { o[0] *= wv.x; o[1] *= wv.y; o[2] *= wv.z; o[3] *= wv.w; }
+        if (in) *(float4 *) (y + k0) = make_float4(o[0], o[1], o[2], o[3]);
+        if (EMIT && k0 < npad) emit_act128(o, k0, npad, col);     // whole warps take this branch together (npad % 128 == 0)
+        return;
+    }
+
     float ss = 0.0f;
     if (addend) {
         // fused residual add: x + addend is written to sum_out (contiguous rows) and normalised from there
@@ -102,11 +135,6 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
     }
     ss = block_sum(ss, sh);                        // (its barriers also make the sums written above visible to the block)
     const float scale = rsqrtf(ss / (float) n + eps);
-    const float * wr = nullptr;
-    if (HAS_W) wr = (const float *) ((const char *) w.data + (i1 % w.ne[1]) * w.nb[1] + (i2 % w.ne[2]) * w.nb[2] + (i3 % w.ne[3]) * w.nb[3]);
-    // norm_out: contiguous rows of the plain normalised values (the RMS_NORM node's own output when the
-    // following MUL is fused into this launch)
-    float * yn = norm_out ? norm_out + row * n : nullptr;
     if (!EMIT) {
         for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
             float v = x[i] * scale;
@@ -116,8 +144,6 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
         }
     } else {
         // 4 consecutive values per thread so that 8 threads cover one 32-value group
-        const int64_t npad = (n + 127) & ~(int64_t) 127;
-        blk_act128 * col = act + row * (npad >> 7);
         for (int64_t k0 = (int64_t) threadIdx.x * 4; k0 < npad; k0 += (int64_t) blockDim.x * 4) {
             float v[4];
 #pragma unroll

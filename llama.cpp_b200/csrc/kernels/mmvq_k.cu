@@ -6,8 +6,9 @@
 // one super-block: lane l takes run j = l & 3 of super-block l >> 2, so a warp-wide load
 // covers 8 consecutive super-blocks; the 16-byte header (and Q5_K's high-bit bytes) comes
 // with a second 128-bit load shared by the four lanes of a super-block.  One warp owns one
-// weight row at a time and keeps two units (96 bytes) per lane in flight; 24 warps per SM
-// give the bytes in flight HBM needs, with no shared-memory staging of weights at all.
+// weight row at a time and holds two register buffers of two units (96 bytes) each per lane
+// in ping-pong, so the loads of the next batch are in flight while one is consumed; 16-24
+// warps per SM give the bytes in flight HBM needs, with no shared-memory staging of weights.
 // The int8 activations (blk_act128) of all columns sit in shared memory.  Everything that
 // depends only on the lane (nibble run, scale bit positions, activation offsets) is
 // computed once, outside the row loop.
@@ -35,16 +36,28 @@ struct MkParams {
     int M, K;
     int x_col0;
 };
+// (no dynamic indexing into the parameter arrays: that would move them to local memory)
 __device__ __forceinline__ const uint8_t * mk_row_ptr(const MkParams & p, int row, int & mat, int & local) {
     mat = (row >= p.m_end[0]) + (row >= p.m_end[1] && p.nmat > 2);
-    local = row - (mat ? p.m_end[mat - 1] : 0);
-    return p.W[mat] + (int64_t) local * p.w_nb1;
+    local = row - (mat == 0 ? 0 : (mat == 1 ? p.m_end[0] : p.m_end[1]));
+    const uint8_t * w = mat == 0 ? p.W[0] : (mat == 1 ? p.W[1] : p.W[2]);
+    return w + (int64_t) local * p.w_nb1;
 }
 
 __device__ __forceinline__ uint4 ldg128(const void * p) { return __ldg((const uint4 *) p); }
+// unsigned bytes x signed bytes (the high nibbles are kept in place as value * 16, up to 240)
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 
-template <int T, int N>
-__global__ void __launch_bounds__(MK_WARPS * 32, 3) mmvq_k_kernel(const MkParams p) {
+template <int T> struct MkBuf {                       // raw bytes of MK_BATCH units of one lane
+    uint4 q0[MK_BATCH], q1[MK_BATCH], hd[MK_BATCH], qh0[T == T_Q5_K ? MK_BATCH : 1], qh1[T == T_Q5_K ? MK_BATCH : 1];
+};
+
+template <int T, int N, int OCC>
+__global__ void __launch_bounds__(MK_WARPS * 32, OCC) mmvq_k_kernel(const MkParams p) {
     constexpr int BLK = (T == T_Q4_K) ? 144 : 176;
     constexpr int QS_OFF = (T == T_Q4_K) ? 16 : 48;
     extern __shared__ __align__(16) uint8_t acts[];           // [N][nblk128 * 160]
@@ -54,7 +67,7 @@ __global__ void __launch_bounds__(MK_WARPS * 32, 3) mmvq_k_kernel(const MkParams
     const int nsb = p.K >> 8;                                  // super-blocks per row
     const int col_bytes = ((p.K + 127) >> 7) * 160;
     const int row_stride = gridDim.x * MK_WARPS;
-    int row = blockIdx.x * MK_WARPS + warp;
+    const int row0 = blockIdx.x * MK_WARPS + warp;
 
     // lane constants: a unit is the 32-byte qs run j of super-block lb (+8 per iteration):
     // low nibbles = sub-block 2j, high nibbles = sub-block 2j+1
@@ -63,29 +76,103 @@ __global__ void __launch_bounds__(MK_WARPS * 32, 3) mmvq_k_kernel(const MkParams
     const uint32_t h_off = lb * BLK;
     const uint32_t a_off = lb * 320 + (j >> 1) * 160 + (j & 1) * 64;          // 64 int8 of groups 2j, 2j+1
     const uint32_t d_off = lb * 320 + (j >> 1) * 160 + 128 + (j & 1) * 16;    // {d, s} of the two groups
-    // 6-bit scale/min extraction (get_scale_min_k4, ggml/src/ggml-quants.c:631-638) with the shifts fixed per lane
+    // 6-bit scale/min extraction (get_scale_min_k4, ggml/src/ggml-quants.c:631-638), branch-free: the entries
+    // of sub-blocks 2j and 2j+1 are adjacent bytes, so both are handled as one 16-bit pair.  With the three
+    // 32-bit words S0 S1 S2 of the 12 scale bytes shifted right by 16 * (j & 1):
+    //   j < 2 : scales = S0 & 0x3F3F                          mins = S1 & 0x3F3F
+    //   j >= 2: scales = (S2 & 0x0F0F) | ((S0 >> 2) & 0x3030) mins = ((S2 >> 4) & 0x0F0F) | ((S1 >> 2) & 0x3030)
     const bool low = j < 2;
-    const int sh_a = low ? 16 * j : 8 * (2 * j - 4);          // byte position of sub-block 2j's entry
-    const int sh_b = sh_a + 8;                                 // ... and of sub-block 2j+1
+    const int sh16 = 16 * (j & 1);
+    const uint32_t mk1 = low ? 0x3F3Fu : 0x0F0Fu, mk2 = low ? 0u : 0x3030u;
+    const int niter = (nsb + 7) >> 3;
 
-    uint4 q0[MK_BATCH], q1[MK_BATCH], hd[MK_BATCH], qh0[MK_BATCH], qh1[MK_BATCH];
-    auto load_batch = [&](const uint8_t * wr, int it0) {
+    auto load = [&](MkBuf<T> & B, int row, int it0) {
+        int mat, lrow;
+        const uint8_t * wr = mk_row_ptr(p, row, mat, lrow) + (uint32_t) it0 * (8 * BLK);
 #pragma unroll
         for (int b = 0; b < MK_BATCH; ++b) {
-            const int sb = (it0 + b) * 8 + lb;
-            if (sb < nsb) {
-                const uint8_t * base = wr + (uint32_t) (it0 + b) * (8 * BLK);
-                q0[b] = ldg128(base + w_off);
-                q1[b] = ldg128(base + w_off + 16);
-                hd[b] = ldg128(base + h_off);
-                if (T == T_Q5_K) { qh0[b] = ldg128(base + h_off + 16); qh1[b] = ldg128(base + h_off + 32); }
+            if (it0 + b < niter && (it0 + b) * 8 + lb < nsb) {
+                const uint8_t * base = wr + b * (8 * BLK);
+                B.q0[b] = ldg128(base + w_off);
+                B.q1[b] = ldg128(base + w_off + 16);
+                B.hd[b] = ldg128(base + h_off);
+                if (T == T_Q5_K) { B.qh0[b] = ldg128(base + h_off + 16); B.qh1[b] = ldg128(base + h_off + 32); }
             }
         }
     };
-    int mat = 0, lrow = 0;
-    const uint8_t * wr = p.W[0];
-    if (row < p.M) { wr = mk_row_ptr(p, row, mat, lrow); load_batch(wr, 0); }        // weights do not depend on the previous kernel: fetch before waiting
 
+    float acc[N];
+#pragma unroll
+    for (int n = 0; n < N; ++n) acc[n] = 0.0f;
+
+    auto compute = [&](const MkBuf<T> & B, int row, int it0) {
+#pragma unroll
+        for (int b = 0; b < MK_BATCH; ++b) {
+            if (it0 + b >= niter || (it0 + b) * 8 + lb >= nsb) continue;
+            const uint32_t w[8] = {B.q0[b].x, B.q0[b].y, B.q0[b].z, B.q0[b].w, B.q1[b].x, B.q1[b].y, B.q1[b].z, B.q1[b].w};
+            // Q4_K: high nibbles stay in place (value * 16): the unsigned x signed dp4a is exact and the
+            // factor 16 is folded into the activation scale, which saves a shift per word
+            uint32_t lo[8], hi[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { lo[i] = w[i] & 0x0F0F0F0Fu; hi[i] = (T == T_Q5_K) ? (w[i] >> 4) & 0x0F0F0F0Fu : w[i] & 0xF0F0F0F0u; }
+            if (T == T_Q5_K) {
+                const uint32_t hb[8] = {B.qh0[b].x, B.qh0[b].y, B.qh0[b].z, B.qh0[b].w, B.qh1[b].x, B.qh1[b].y, B.qh1[b].z, B.qh1[b].w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t t = hb[i] >> (2 * j);           // bit 0: sub-block 2j, bit 1: 2j+1
+                    lo[i] |= (t << 4) & 0x10101010u;
+                    hi[i] |= (t << 3) & 0x10101010u;
+                }
+            }
+            const float2 dm = __half22float2(*(const __half2 *) &B.hd[b].x);      // {d, dmin}
+            const uint32_t sa = B.hd[b].y >> sh16, sb_ = B.hd[b].z >> sh16, sc_ = B.hd[b].w >> sh16;
+            const uint32_t scp = ((low ? sa : sc_) & mk1) | ((sa >> 2) & mk2);
+            const uint32_t mnp = ((low ? sb_ : (sc_ >> 4)) & mk1) | ((sb_ >> 2) & mk2);
+            const int sc0 = scp & 0xFF, sc1 = (scp >> 8) & 0xFF;
+            const float fm0 = dm.y * (float) (mnp & 0xFF), fm1 = dm.y * (float) ((mnp >> 8) & 0xFF);
+            const float dhi = (T == T_Q5_K) ? dm.x : dm.x * 0.0625f;
+            const uint8_t * ab = acts + (uint32_t) (it0 + b) * (8 * 320);
+#pragma unroll
+            for (int n = 0; n < N; ++n, ab += col_bytes) {
+                const uint4 xa = *(const uint4 *) (ab + a_off);
+                const uint4 xb = *(const uint4 *) (ab + a_off + 16);
+                const uint4 xc = *(const uint4 *) (ab + a_off + 32);
+                const uint4 xd = *(const uint4 *) (ab + a_off + 48);
+                const float4 ds = *(const float4 *) (ab + d_off);            // {d0, s0, d1, s1}
+                int t0 = dp4a_us(lo[0], (int) xa.x, 0); t0 = dp4a_us(lo[1], (int) xa.y, t0);
+                t0 = dp4a_us(lo[2], (int) xa.z, t0);    t0 = dp4a_us(lo[3], (int) xa.w, t0);
+                t0 = dp4a_us(lo[4], (int) xb.x, t0);    t0 = dp4a_us(lo[5], (int) xb.y, t0);
+                t0 = dp4a_us(lo[6], (int) xb.z, t0);    t0 = dp4a_us(lo[7], (int) xb.w, t0);
+                int t1 = dp4a_us(hi[0], (int) xc.x, 0); t1 = dp4a_us(hi[1], (int) xc.y, t1);
+                t1 = dp4a_us(hi[2], (int) xc.z, t1);    t1 = dp4a_us(hi[3], (int) xc.w, t1);
+                t1 = dp4a_us(hi[4], (int) xd.x, t1);    t1 = dp4a_us(hi[5], (int) xd.y, t1);
+                t1 = dp4a_us(hi[6], (int) xd.z, t1);    t1 = dp4a_us(hi[7], (int) xd.w, t1);
+                // |sc * t| <= 63 * 32 * 240 * 127 < 2^26: the products are exact in int32
+                const float u = dm.x * ds.x * (float) (sc0 * t0) + dhi * ds.z * (float) (sc1 * t1);
+                acc[n] += u - fm0 * ds.y - fm1 * ds.w;
+            }
+        }
+        if (it0 + MK_BATCH >= niter) {                          // row finished: reduce and store
+            int mat, lrow;
+            mk_row_ptr(p, row, mat, lrow);
+            float * d0 = mat == 0 ? p.dst[0] : (mat == 1 ? p.dst[1] : p.dst[2]);
+            const int64_t nb1 = mat == 0 ? p.dst_nb1[0] : (mat == 1 ? p.dst_nb1[1] : p.dst_nb1[2]);
+#pragma unroll
+            for (int n = 0; n < N; ++n) {
+                const float v = warp_sum(acc[n]);
+                if (lane == 0) ((float *) ((uint8_t *) d0 + (int64_t) n * nb1))[lrow] = v;
+                acc[n] = 0.0f;
+            }
+        }
+    };
+
+    // Work items of this warp are (row, batch of MK_BATCH iterations) with rows row0, row0 + row_stride, ...
+    // Two register buffers in ping-pong: the loads of the next item are in flight while one is consumed.
+    auto advance = [&](int & row, int & it0) { it0 += MK_BATCH; if (it0 >= niter) { it0 = 0; row += row_stride; } };
+    MkBuf<T> A, B;
+    int lrow_ = row0, lit = 0;            // position of the load stream
+    int crow = row0, cit = 0;             // position of the compute stream
+    if (lrow_ < p.M) { load(A, lrow_, lit); advance(lrow_, lit); }   // weights do not depend on the previous kernel
     pdl_wait();
     for (int n = 0; n < N; ++n) {
         const uint4 * src = (const uint4 *) (p.Xq + (int64_t) (p.x_col0 + n) * p.xq_col_bytes);
@@ -93,81 +180,20 @@ __global__ void __launch_bounds__(MK_WARPS * 32, 3) mmvq_k_kernel(const MkParams
         for (int i = threadIdx.x; i < col_bytes / 16; i += blockDim.x) dstp[i] = src[i];
     }
     __syncthreads();
-
-    const int niter = (nsb + 7) >> 3;
-    for (; row < p.M; row += row_stride) {
-        float acc[N];
-#pragma unroll
-        for (int n = 0; n < N; ++n) acc[n] = 0.0f;
-        for (int it0 = 0; it0 < niter; it0 += MK_BATCH) {
-            if (it0 > 0) load_batch(wr, it0);
-#pragma unroll
-            for (int b = 0; b < MK_BATCH; ++b) {
-                const int sb = (it0 + b) * 8 + lb;
-                if (sb >= nsb) continue;
-                const uint32_t w[8] = {q0[b].x, q0[b].y, q0[b].z, q0[b].w, q1[b].x, q1[b].y, q1[b].z, q1[b].w};
-                uint32_t lo[8], hi[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) { lo[i] = w[i] & 0x0F0F0F0Fu; hi[i] = (w[i] >> 4) & 0x0F0F0F0Fu; }
-                if (T == T_Q5_K) {
-                    const uint32_t hb[8] = {qh0[b].x, qh0[b].y, qh0[b].z, qh0[b].w, qh1[b].x, qh1[b].y, qh1[b].z, qh1[b].w};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint32_t t = hb[i] >> (2 * j);       // bit 0: sub-block 2j, bit 1: 2j+1
-                        lo[i] |= (t << 4) & 0x10101010u;
-                        hi[i] |= (t << 3) & 0x10101010u;
-                    }
-                }
-                const float2 dm = __half22float2(*(const __half2 *) &hd[b].x);      // {d, dmin}
-                const uint32_t s0 = hd[b].y, s1 = hd[b].z, s2 = hd[b].w;
-                int sc0, sc1, m0, m1;
-                if (low) {
-                    sc0 = (s0 >> sh_a) & 63; sc1 = (s0 >> sh_b) & 63;
-                    m0  = (s1 >> sh_a) & 63; m1  = (s1 >> sh_b) & 63;
-                } else {
-                    sc0 = ((s2 >> sh_a) & 0xF)       | (((s0 >> (sh_a + 6)) & 3) << 4);
-                    sc1 = ((s2 >> sh_b) & 0xF)       | (((s0 >> (sh_b + 6)) & 3) << 4);
-                    m0  = ((s2 >> (sh_a + 4)) & 0xF) | (((s1 >> (sh_a + 6)) & 3) << 4);
-                    m1  = ((s2 >> (sh_b + 4)) & 0xF) | (((s1 >> (sh_b + 6)) & 3) << 4);
-                }
-                const float fs0 = dm.x * (float) sc0, fs1 = dm.x * (float) sc1;
-                const float fm0 = dm.y * (float) m0,  fm1 = dm.y * (float) m1;
-                const uint32_t it_a = (uint32_t) (it0 + b) * (8 * 320);
-#pragma unroll
-                for (int n = 0; n < N; ++n) {
-                    const uint8_t * ab = acts + n * col_bytes + it_a;
-                    const uint4 xa = *(const uint4 *) (ab + a_off);
-                    const uint4 xb = *(const uint4 *) (ab + a_off + 16);
-                    const uint4 xc = *(const uint4 *) (ab + a_off + 32);
-                    const uint4 xd = *(const uint4 *) (ab + a_off + 48);
-                    const float4 ds = *(const float4 *) (ab + d_off);            // {d0, s0, d1, s1}
-                    int t0 = __dp4a((int) lo[0], (int) xa.x, 0); t0 = __dp4a((int) lo[1], (int) xa.y, t0);
-                    t0 = __dp4a((int) lo[2], (int) xa.z, t0);    t0 = __dp4a((int) lo[3], (int) xa.w, t0);
-                    t0 = __dp4a((int) lo[4], (int) xb.x, t0);    t0 = __dp4a((int) lo[5], (int) xb.y, t0);
-                    t0 = __dp4a((int) lo[6], (int) xb.z, t0);    t0 = __dp4a((int) lo[7], (int) xb.w, t0);
-                    int t1 = __dp4a((int) hi[0], (int) xc.x, 0); t1 = __dp4a((int) hi[1], (int) xc.y, t1);
-                    t1 = __dp4a((int) hi[2], (int) xc.z, t1);    t1 = __dp4a((int) hi[3], (int) xc.w, t1);
-                    t1 = __dp4a((int) hi[4], (int) xd.x, t1);    t1 = __dp4a((int) hi[5], (int) xd.y, t1);
-                    t1 = __dp4a((int) hi[6], (int) xd.z, t1);    t1 = __dp4a((int) hi[7], (int) xd.w, t1);
-                    acc[n] += fs0 * ds.x * (float) t0 + fs1 * ds.z * (float) t1 - fm0 * ds.y - fm1 * ds.w;
-                }
-            }
-        }
-        const int cur_mat = mat, cur_row = lrow;
-        if (row + row_stride < p.M) { wr = mk_row_ptr(p, row + row_stride, mat, lrow); load_batch(wr, 0); }
-#pragma unroll
-        for (int n = 0; n < N; ++n) acc[n] = warp_sum(acc[n]);
-        if (lane == 0) {
-#pragma unroll
-            for (int n = 0; n < N; ++n) ((float *) ((uint8_t *) p.dst[cur_mat] + (int64_t) n * p.dst_nb1[cur_mat]))[cur_row] = acc[n];
-        }
+    while (crow < p.M) {
+        if (lrow_ < p.M) { load(B, lrow_, lit); advance(lrow_, lit); }
+        compute(A, crow, cit); advance(crow, cit);
+        if (crow >= p.M) break;
+        if (lrow_ < p.M) { load(A, lrow_, lit); advance(lrow_, lit); }
+        compute(B, crow, cit); advance(crow, cit);
     }
 }
 
 template <int T, int N>
 static cudaError_t launch_mk_tn(const MkParams & p, int sm_count, int device, int use_pdl, cudaStream_t stream) {
     const size_t smem = (size_t) N * ((p.K + 127) / 128) * 160;
-    auto kern = mmvq_k_kernel<T, N>;
+    constexpr int occ = (T == T_Q4_K && N <= 2) ? 3 : 2;      // the wider variants would spill at 80 registers
+    auto kern = mmvq_k_kernel<T, N, occ>;
     static unsigned attr_mask = 0;
     if (smem > 48 * 1024 && !(attr_mask & (1u << device))) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -176,7 +202,7 @@ static cudaError_t launch_mk_tn(const MkParams & p, int sm_count, int device, in
     }
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     const int64_t rows = p.M;
-    int ctas_per_sm = 3;
+    int ctas_per_sm = occ;
     if (smem) { const int by_smem = (int) ((220 * 1024) / (smem + 1024)); if (by_smem < ctas_per_sm) ctas_per_sm = by_smem < 1 ? 1 : by_smem; }
     int64_t grid = (int64_t) sm_count * ctas_per_sm;
     const int64_t need = (rows + MK_WARPS - 1) / MK_WARPS;

@@ -92,14 +92,17 @@ class ClockSampler:
 
 
 def fill_weights(models, device):
-    """Random-init weights, generated once per tensor and handed to every model as host bytes."""
-    from llama_cpp_b200 import synth
+    """Random-init weights, generated once per tensor and handed to every model as host bytes.  A row-split
+    model (models[0] on rank r of n) takes its rows of the same full tensor every rank generates."""
+    from llama_cpp_b200 import row_split, synth
     t0 = time.time()
     total = 0
-    for t in models[0].tensors():
-        data = synth.make_tensor(t["type"], t["ne0"], t["ne1"], seed=1000 + t["index"], device=device)
-        for m in models:
-            m.set_tensor(t["index"], data)
+    infos = [m.tensors() for m in models]
+    for i, t in enumerate(infos[0]):
+        data = synth.make_tensor(t["type"], t["ne0"], t["full_rows"], seed=1000 + t["index"], device=device)
+        for m, info in zip(models, infos):
+            ti = info[i]
+            m.set_tensor(ti["index"], row_split.slice_rows(data, ti["full_rows"], ti["row_low"], ti["ne1"]))
         total += data.size
     log(f"[bench] weights: {total / 1e9:.2f} GB generated and uploaded in {time.time() - t0:.1f} s")
 
@@ -235,23 +238,48 @@ def main():
         return
 
     import torch
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if pkg.device_count() <= local:
+        raise SystemExit("no sm_100 device visible for this rank: the B200 path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dist = None
     if world > 1:
-        raise SystemExit("row-split multi-GPU bench is not wired up yet")
-    if pkg.device_count() < 1:
-        raise SystemExit("no sm_100 device visible: the B200 path has no CPU fallback")
-    torch.cuda.set_device(0)
-    m = llama.Llama(n_ctx=1024, n_ubatch=N_PROMPT, **arch)
+        # one process per GPU; NCCL carries set-up data and the timing reductions, the row-split exchange itself
+        # is done by the backend's kernels with stores into peer memory
+        import torch.distributed as dist
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+        config["parallelism"] = f"row-split x{world} (weight rows over ranks, peer stores + barrier per MUL_MAT group)"
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(*vals):
+        if dist is None:
+            return list(vals)
+        t = torch.tensor(vals, dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    m = llama.Llama(n_ctx=1024, n_ubatch=N_PROMPT, device_index=local, rank=rank, n_ranks=world, **arch)
     cpu = None
-    if not args.no_cpu_baseline and rank == 0:
+    if not args.no_cpu_baseline and rank == 0 and world == 1:
         try:
             cpu = cpu_model(arch, cores)
         except Exception as e:  # the baseline is reported, never required for the GPU number
             log(f"[bench] cpu baseline unavailable: {e}")
     fill_weights([m] + ([cpu] if cpu else []), "cuda")
+    if dist is not None:
+        from llama_cpp_b200 import row_split
+        m.attach_peers(row_split.gather_bytes(dist))
 
+    sync_all()
     for _ in range(max(args.warmup, 3)):
         run_step(m, tokens, N_PROMPT, N_GEN)
-    sampler = ClockSampler(0)
+    sync_all()
+    sampler = ClockSampler(local)
     sampler.start()
     launches0 = m.launch_count
     pp_wall = tg_wall = pp_dev = tg_dev = 0.0
@@ -259,10 +287,12 @@ def main():
     for _ in range(args.steps):
         a, b, c, d = run_step(m, tokens, N_PROMPT, N_GEN)
         pp_wall += a; tg_wall += b; pp_dev += c; tg_dev += d
-    torch.cuda.synchronize()
+    sync_all()
     wall = time.perf_counter() - t_start
     clocks = sampler.stop()
     launches = m.launch_count - launches0
+    # the slowest rank sets the job's time (device times by CUDA events on each rank's stream)
+    pp_wall, tg_wall, pp_dev, tg_dev, wall = max_over_ranks(pp_wall, tg_wall, pp_dev, tg_dev, wall)
     logits = m.decode(tokens[:8], 0).copy()
     assert np.isfinite(logits).all(), "non-finite logits"
 
@@ -271,13 +301,18 @@ def main():
     tg_tps_e2e, pp_tps_e2e = n_tg / tg_wall, n_pp / pp_wall
     h2d, d2h = io_bytes_per_step(N_PROMPT, N_GEN, arch["n_vocab"])
 
+    if rank != 0:                 # rank 0 reports; the others wait for it to finish the single-GPU roofline pass
+        sync_all()
+        m.close()
+        dist.destroy_process_group()
+        return
     peak, peak_kind = measured_peaks()
     algo, gemv_ms, n_mats = gemv_roofline(pkg, m, torch)
     achieved = algo / (gemv_ms / 1e3) / 1e9
     roofline = {"bound": "hbm", "kernel": "mmvq_kernel (decode mat-vec)", "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
                 "unit": "GB/s", "frac": achieved / peak, "traffic": None, "launches_per_pass": n_mats,
                 "algorithmic_bytes_per_pass": algo, "ms_per_pass": gemv_ms,
-                "whole_decode_step": {"weight_bytes_per_token": m.weight_bytes, "achieved_gbs": m.weight_bytes * tg_tps_dev / 1e9,
+                "whole_decode_step": {"weight_bytes_per_token_per_gpu": m.weight_bytes, "achieved_gbs_per_gpu": m.weight_bytes * tg_tps_dev / 1e9,
                                       "frac": m.weight_bytes * tg_tps_dev / 1e9 / peak}}
     cpu_baseline = None
     if cpu is not None:
@@ -290,13 +325,17 @@ def main():
                         "sample": f"pp{CPU_PROMPT}+tg{CPU_GEN} on the reference ggml CPU backend, {cores} threads",
                         "pp_tokens_per_s": c_pp, "logits_nmse_vs_b200": nmse}
         cpu.close()
-    out = {"metric": METRIC, "value": tg_tps_dev, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+    out = {"metric": METRIC, "value": tg_tps_dev, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
            "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
            "dtype": "int8 x int4/6 dot, f32 accumulate", "data": "synthetic", "config": config,
            "pp512_tokens_per_s": pp_tps_dev, "tg128_tokens_per_s": tg_tps_dev,
            "e2e": {"value": tg_tps_e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "pp512_tokens_per_s": pp_tps_e2e},
-           "gpu_launches": launches, "graph_nodes_per_token": m.last_n_nodes, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline}
+           "gpu_launches": launches * world, "graph_nodes_per_token": m.last_n_nodes, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline}
+    if dist is not None:
+        sync_all()
     m.close()
+    if dist is not None:
+        dist.destroy_process_group()
     print(json.dumps(out))
 
 

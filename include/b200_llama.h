@@ -33,6 +33,7 @@ typedef struct b200_llama_config {
     int32_t n_ubatch;       /* largest number of tokens per graph */
     float   rope_theta, rms_eps;
     int32_t n_threads;      /* forwarded to the backend's "ggml_backend_set_n_threads" when it has one */
+    int32_t n_ranks, rank;  /* row-split over n_ranks processes, one GPU each (0 or 1: not split); B200 backend only */
 } b200_llama_config;
 
 /* reg: a ggml_backend_reg_t (as returned by a backend library's ggml_backend_init), or NULL for
@@ -50,6 +51,27 @@ int32_t      b200_llama_tensor_info(const b200_llama * m, int32_t i, char * name
 int32_t      b200_llama_set_tensor(b200_llama * m, int32_t i, const void * host_data, size_t nbytes);
 /* address of tensor i inside the backend's weight buffer (a device pointer on the B200 backend) */
 void *       b200_llama_tensor_data(const b200_llama * m, int32_t i);
+
+/* ---- row-split (the reference's split-mode row, one process per GPU) -----------------------
+ * With n_ranks > 1 every rank holds rows [row_low, row_high) of each 2-D projection matrix and of
+ * output.weight (norms, embeddings and the KV cache are replicated), computes that slice of every
+ * MUL_MAT and stores it into all peers' activation arenas over NVLink; a barrier kernel then makes
+ * the full result readable everywhere (include/ggml-b200.h).  All ranks must call b200_llama_decode
+ * with the same tokens.
+ *
+ * b200_row_split_range: equal shares with boundaries rounded down to a multiple of 128 rows, the last
+ *   rank taking the remainder (get_row_split, ggml/src/ggml-cuda/ggml-cuda.cu:725-742).
+ * b200_llama_tensor_rows: first row and full row count of tensor i (b200_llama_tensor_info reports
+ *   this rank's share: ne1 = row_high - row_low).
+ * b200_llama_ipc_handle / b200_llama_attach_peers: set-up.  Each rank exports the CUDA IPC handle of its
+ *   arena (B200_LLAMA_IPC_HANDLE_BYTES bytes), the caller gathers the handles of all ranks in rank order
+ *   (n_ranks x B200_LLAMA_IPC_HANDLE_BYTES bytes, e.g. with torch.distributed.all_gather_object) and hands
+ *   them to attach_peers.  These have no reference counterpart: the reference's ranks share one process. */
+#define B200_LLAMA_IPC_HANDLE_BYTES 64
+void         b200_row_split_range(int64_t n_rows, int32_t rank, int32_t n_ranks, int64_t * row_low, int64_t * row_high);
+int32_t      b200_llama_tensor_rows(const b200_llama * m, int32_t i, int64_t * row_low, int64_t * full_rows);
+int32_t      b200_llama_ipc_handle(b200_llama * m, void * handle_out);
+int32_t      b200_llama_attach_peers(b200_llama * m, const void * handles);
 
 /* Evaluates n_tokens tokens at KV positions [pos0, pos0 + n_tokens) (one ubatch, n_tokens <= n_ubatch):
  * token ids are copied host->device, the graph is computed, and the logits of the LAST token

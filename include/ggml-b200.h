@@ -39,8 +39,43 @@ int ggml_backend_score(void);
  *   "ggml_backend_b200_get_stream"       void *   (*)(ggml_backend_t)   the backend's cudaStream_t, for event timing
  *   "ggml_backend_b200_get_launch_count" uint64_t (*)(ggml_backend_t)   kernels launched by graph_compute so far
  *   "ggml_backend_b200_get_status"       int      (*)(ggml_backend_t)   device status word (0 = no kernel gave up a wait)
+ *   "ggml_backend_b200_set_peers"        int      (*)(ggml_backend_t, const ggml_b200_peers *)   row-split set-up, below
  * Unknown names return NULL.
  */
+
+/*
+ * Row-split across the GPUs of one node, one process per GPU.
+ *
+ * The reference splits the rows of a weight matrix over the devices of ONE process through its split
+ * buffer type and gathers the dst slices with peer copies (ggml/src/ggml-cuda/ggml-cuda.cu:714-1040,
+ * :1520-1660).  Here every rank is its own process with its own backend; each rank's graph holds only
+ * its rows of each split matrix, and a MUL_MAT node says where its slice belongs in the full result:
+ *
+ *   node->op == GGML_OP_MUL_MAT, node->src[0] = this rank's rows [row_low, row_low + node->ne[0]) of the matrix,
+ *   node->data = full_data + 4 * row_low, node->nb[1] = the full result's column stride,
+ *   node->extra -> ggml_b200_row_slice {GGML_B200_ROW_SLICE_MAGIC, full_data, full_rows, row_low}
+ *
+ * After computing such a node the backend stores the slice into the same place of every peer's arena and,
+ * before the next node that is not another sliced MUL_MAT, runs a barrier over all ranks; from then on the
+ * full result [full_rows x n_cols] at full_data is valid on every rank.  All ranks must run the same graph.
+ * ggml_backend_b200_set_peers tells the backend where the peers' arenas are mapped in this process
+ * (cudaIpcOpenMemHandle of the peers' compute buffers; they must have the same size and layout).  The
+ * first GGML_B200_PEER_FLAG_BYTES of the arena are reserved for the barrier's flags and must be zero.
+ */
+#define GGML_B200_ROW_SLICE_MAGIC 0x42323030524f5753ull
+#define GGML_B200_MAX_PEERS       8
+#define GGML_B200_PEER_FLAG_BYTES 256
+typedef struct ggml_b200_row_slice {
+    uint64_t magic;
+    void *   full_data;      /* start of the full [full_rows x n_cols] F32 result in this rank's arena */
+    int64_t  full_rows;
+    int64_t  row_low;
+} ggml_b200_row_slice;
+typedef struct ggml_b200_peers {
+    int32_t rank, n_ranks;
+    void *  arena[GGML_B200_MAX_PEERS];   /* arena[r]: where rank r's arena is mapped here; arena[rank] = this rank's own */
+    size_t  arena_bytes;
+} ggml_b200_peers;
 
 #ifdef __cplusplus
 }

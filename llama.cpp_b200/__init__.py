@@ -36,6 +36,7 @@ EXPORTS = [
     "b200_llama_create", "b200_llama_free", "b200_llama_error", "b200_llama_n_tensors", "b200_llama_tensor_info",
     "b200_llama_set_tensor", "b200_llama_tensor_data", "b200_llama_decode", "b200_llama_last_n_nodes",
     "b200_llama_last_compute_ms", "b200_llama_launch_count", "b200_llama_weight_bytes",
+    "b200_row_split_range", "b200_llama_tensor_rows", "b200_llama_ipc_handle", "b200_llama_attach_peers",
 ]
 
 

@@ -412,7 +412,21 @@ static int b200_get_status(ggml_backend_t backend) {
     return *ctx->status_host;
 }
 
+static int b200_set_peers(ggml_backend_t backend, const ggml_b200_peers * peers) {
+    if (!backend_is_ours(backend) || !peers) return -1;
+    BackendCtx * ctx = (BackendCtx *) backend->context;
+    if (peers->n_ranks < 1 || peers->n_ranks > GGML_B200_MAX_PEERS || peers->rank < 0 || peers->rank >= peers->n_ranks) return -2;
+    for (int r = 0; r < peers->n_ranks; ++r) if (!peers->arena[r] || ((uintptr_t) peers->arena[r] & 255)) return -3;
+    if (peers->arena_bytes < GGML_B200_PEER_FLAG_BYTES) return -4;
+    ctx->peers = *peers;
+    ctx->peer_pending = false;
+    if (ctx->graph_exec) { cudaGraphExecDestroy(ctx->graph_exec); ctx->graph_exec = nullptr; ctx->graph_key = 0; }
+    ctx->pending_key = 0;
+    return 0;
+}
+
 static void * reg_get_proc_address(ggml_backend_reg_t, const char * name) {
+    if (strcmp(name, "ggml_backend_b200_set_peers") == 0) return (void *) b200_set_peers;
     if (strcmp(name, "ggml_backend_split_buffer_type") == 0) return (void *) split_buffer_type;
     if (strcmp(name, "ggml_backend_get_features") == 0) return (void *) get_features;
     if (strcmp(name, "ggml_backend_b200_get_stream") == 0) return (void *) b200_get_stream;

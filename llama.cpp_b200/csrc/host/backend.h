@@ -2,6 +2,7 @@
 #pragma once
 
 #include "ggml_compat.h"
+#include "ggml-b200.h"
 
 #include <cstring>
 #include <mutex>
@@ -70,6 +71,16 @@ struct BackendCtx {
     uint64_t     scratch_generation = 0;
 
     unsigned *   fa_tickets = nullptr;     // zero-initialised counters of the decode attention kernel
+
+    // row-split over several processes: where the peers' arenas are mapped, and whether slices have been
+    // stored to the peers since the last barrier
+    ggml_b200_peers peers = {};
+    bool         peer_pending = false;
+    const ggml_b200_row_slice * row_slice_of(const ggml_tensor * node) const {
+        if (peers.n_ranks < 2 || node->op != GGML_OP_MUL_MAT || !node->extra) return nullptr;
+        const ggml_b200_row_slice * rs = (const ggml_b200_row_slice *) node->extra;
+        return rs->magic == GGML_B200_ROW_SLICE_MAGIC ? rs : nullptr;
+    }
 
     LaunchCtx launch_ctx() const { return LaunchCtx{stream, dev->device, dev->sm_count, status_dev, use_pdl, fa_tickets}; }
     void *    get_scratch(size_t bytes);   // grows (after a stream sync) when needed

@@ -128,12 +128,57 @@ static bool act_cacheable(const ggml_tensor * X) {
     return X->type == GGML_TYPE_F32 && t_contiguous(X) && X->ne[1] * X->ne[2] * X->ne[3] <= 8;
 }
 
+// ---- row-split over processes (include/ggml-b200.h) ----
+// byte distances from this rank's arena to each peer's mapping of its own arena
+static int peer_deltas(const BackendCtx * ctx, int64_t * delta) {
+    int n = 0;
+    const char * mine = (const char *) ctx->peers.arena[ctx->peers.rank];
+    for (int r = 0; r < ctx->peers.n_ranks; ++r) if (r != ctx->peers.rank) delta[n++] = (const char *) ctx->peers.arena[r] - mine;
+    return n;
+}
+static bool in_arena(const BackendCtx * ctx, const void * p, size_t bytes) {
+    const char * mine = (const char *) ctx->peers.arena[ctx->peers.rank];
+    return (const char *) p >= mine + GGML_B200_PEER_FLAG_BYTES && (const char *) p + bytes <= mine + ctx->peers.arena_bytes;
+}
+// stores the [ne0 x ne1] slice `dst` into the same place of every peer's arena
+static bool push_slice(BackendCtx * ctx, const ggml_tensor * dst) {
+    PeerPush p = {};
+    int64_t delta[MAX_PEERS - 1];
+    p.n_peer = peer_deltas(ctx, delta);
+    p.src = (const char *) dst->data;
+    for (int i = 0; i < p.n_peer; ++i) p.peer_dst[i] = (char *) dst->data + delta[i];
+    p.col_bytes = dst->ne[0] * 4; p.col_stride = (int64_t) dst->nb[1]; p.ncols = dst->ne[1];
+    p.shift = (p.col_bytes % 16 == 0 && p.col_stride % 16 == 0 && (uintptr_t) dst->data % 16 == 0) ? 4 : 2;
+    RUN(launch_peer_push(p, ctx->launch_ctx()));
+    return true;
+}
+static bool peer_barrier(BackendCtx * ctx) {
+    PeerBarrier b = {};
+    char * mine = (char *) ctx->peers.arena[ctx->peers.rank];
+    b.local_flags = (unsigned *) mine; b.epoch = (unsigned *) (mine + 64);
+    for (int r = 0; r < ctx->peers.n_ranks; ++r) b.peer_flags[r] = (unsigned *) ctx->peers.arena[r];
+    b.rank = ctx->peers.rank; b.n_ranks = ctx->peers.n_ranks; b.status = ctx->status_dev;
+    RUN(launch_peer_barrier(b, ctx->launch_ctx()));
+    ctx->peer_pending = false;
+    return true;
+}
+
 static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_tensor * ids, ggml_tensor * const * extra = nullptr, int n_extra = 0) {
     const ggml_tensor * W = dst->src[0];
     const ggml_tensor * X = dst->src[1];
     const LaunchCtx lc = ctx->launch_ctx();
+    const bool sliced = !ids && ctx->row_slice_of(dst) != nullptr;
+    if (sliced) {
+        const size_t span = (size_t) (dst->ne[1] - 1) * dst->nb[1] + (size_t) dst->ne[0] * 4;
+        if (dst->ne[2] != 1 || dst->ne[3] != 1 || !in_arena(ctx, dst->data, span)) {
+            B200_LOG_ERROR("ggml-b200: row-sliced MUL_MAT %s lies outside the peer arena or has batch dims\n", dst->name);
+            return false;
+        }
+        ctx->peer_pending = true;
+    }
     if (!ids && is_float_type(W->type)) {
         RUN(launch_matmul_f(to_desc(W), to_desc(X), to_desc(dst), lc));
+        if (sliced && !push_slice(ctx, dst)) return false;
         return true;
     }
     const int64_t K = W->ne[0], M = W->ne[1];
@@ -151,6 +196,7 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
             RUN(launch_mmq_tc(W->type, w, W->nb[1], (const float *) x, X->nb[1], (float *) d, dst->nb[1], M, ne11, K, ws, lc));
             ctx->n_launches++;
         }
+        if (sliced && !push_slice(ctx, dst)) return false;
         return true;
     }
     void * xq = nullptr;
@@ -181,11 +227,21 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
         a.r2 = (int) (ne12 / W->ne[2]); a.r3 = (int) (ne13 / W->ne[3]);
         a.dst_nb1 = dst->nb[1]; a.dst_nb2 = dst->nb[2]; a.dst_nb3 = dst->nb[3];
         a.x_ncols = (int) ne11; a.xq_ne12 = (int) ne12;
+        bool pushed = true;
         for (int64_t n0 = 0; n0 < ne11; n0 += 8) {
             a.N = (int) (ne11 - n0 < 8 ? ne11 - n0 : 8);
             a.x_col0 = (int) n0;
             a.dst = (float *) ((char *) dst->data + n0 * dst->nb[1]);
+            a.n_peer = 0;
+            if (sliced) {
+                if (mmvq_stores_to_peers(a)) a.n_peer = peer_deltas(ctx, a.peer_delta);   // the kernel writes the peer copies itself
+                else pushed = false;
+            }
             RUN(launch_mmvq(a, lc.stream));
+        }
+        if (sliced && !pushed) {
+            if (!push_slice(ctx, dst)) return false;
+            for (int i = 0; i < n_extra; ++i) if (!push_slice(ctx, extra[i])) return false;
         }
     } else {
         // MUL_MAT_ID (ggml_mul_mat_id, ggml/src/ggml.c:2735-2759): one mat-vec per (slot e, token t),
@@ -285,7 +341,8 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
         case GGML_OP_MUL_MAT: {
             ggml_tensor * extra[2]; int n_extra = 0;
             if (group_head_ok(dst) && !buft_is_split(dst->src[0]->buffer ? dst->src[0]->buffer->buft : nullptr)) {
-                while (n_extra < 2 && i + 1 + n_extra < g->n_nodes && groupable_mul_mat(dst, g->nodes[i + 1 + n_extra])) {
+                while (n_extra < 2 && i + 1 + n_extra < g->n_nodes && groupable_mul_mat(dst, g->nodes[i + 1 + n_extra]) &&
+                       (ctx->row_slice_of(dst) != nullptr) == (ctx->row_slice_of(g->nodes[i + 1 + n_extra]) != nullptr)) {
                     extra[n_extra] = g->nodes[i + 1 + n_extra]; ctx->act_cache_invalidate(extra[n_extra]->data); ++n_extra;
                 }
             }
@@ -444,16 +501,34 @@ static int next_exec(const ggml_cgraph * g, int i) {
 
 static bool run_all(BackendCtx * ctx, ggml_cgraph * cgraph) {
     ctx->act_cache_clear();
+    std::vector<const void *> pending_full;            // full results whose slices are in flight to the peers
     for (int i = 0; i < cgraph->n_nodes;) {
         ggml_tensor * node = cgraph->nodes[i];
         if (is_noop(node)) { ++i; continue; }
+        const ggml_b200_row_slice * rs = ctx->row_slice_of(node);
+        if (ctx->peer_pending) {
+            // slices stored to the peers become readable after a barrier; consecutive sliced MUL_MATs that
+            // do not read one of the pending results share one
+            bool need = rs == nullptr;
+            if (rs) {
+                const ggml_tensor * x = node->src[1];
+                for (const void * f : pending_full) if (x->data == f || (x->view_src && x->view_src->data == f)) need = true;
+            }
+            if (need) { if (!peer_barrier(ctx)) return false; pending_full.clear(); }
+        }
+        if (rs) { pending_full.push_back(rs->full_data); ctx->act_cache_invalidate(rs->full_data); }
         ctx->act_cache_invalidate(node->data);
         if (node->op == GGML_OP_CPY && node->src[1]) ctx->act_cache_invalidate(node->src[1]->data);
         if (i + 1 < cgraph->n_nodes) ctx->act_cache_invalidate(cgraph->nodes[i + 1]->data);   // it may be fused into this launch
         const int used = run_node(ctx, cgraph, i);
         if (used == 0) return false;
+        for (int j = 1; j < used; ++j) {               // grouped sliced MUL_MATs ran with the head
+            const ggml_b200_row_slice * r2 = ctx->row_slice_of(cgraph->nodes[i + j]);
+            if (r2) { pending_full.push_back(r2->full_data); ctx->act_cache_invalidate(r2->full_data); }
+        }
         i += used;
     }
+    if (ctx->peer_pending && !peer_barrier(ctx)) return false;
     return true;
 }
 

@@ -25,7 +25,8 @@ using namespace b200;
 
 thread_local std::string g_error;
 
-struct Weight { std::string name; ggml_tensor t; size_t offset; };
+// a weight tensor as this rank stores it: all of it, or (row-split) the rows [row_low, row_low + t.ne[1]) of full_rows
+struct Weight { std::string name; ggml_tensor t; size_t offset; int64_t full_rows, row_low; bool split; };
 
 constexpr size_t ALIGN = 128;
 inline size_t align_up(size_t x) { return (x + ALIGN - 1) & ~(ALIGN - 1); }
@@ -52,6 +53,11 @@ struct b200_llama {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     uint64_t (*launch_count_fn)(ggml_backend_t) = nullptr;
 
+    int n_ranks = 1, rank = 0;                         // row-split over processes (one per GPU)
+    std::vector<ggml_b200_row_slice> slices; size_t slices_used = 0;   // node->extra of sliced MUL_MATs
+    void * peer_arena[GGML_B200_MAX_PEERS] = {};       // peers' compute buffers mapped here (CUDA IPC)
+    int (*status_fn)(ggml_backend_t) = nullptr;
+
     std::vector<Weight> weights;                       // fixed order, see add_weights()
     std::vector<ggml_tensor> k_l, v_l;                 // per-layer KV cache tensors (F16, 1-D)
 
@@ -68,7 +74,7 @@ struct b200_llama {
     std::vector<float> mask_host;
     std::vector<int32_t> pos_host;
 
-    int last_n_nodes = 0; double last_ms = 0.0; size_t weight_bytes = 0;
+    int last_n_nodes = 0; double last_ms = 0.0; size_t weight_bytes = 0, arena_bytes = 0;
 
     // ---- tensor constructors ----
     ggml_tensor * raw() {
@@ -132,6 +138,25 @@ struct b200_llama {
         return node(t);
     }
     ggml_tensor * mul_mat(ggml_tensor * w, ggml_tensor * x) { return op2(GGML_OP_MUL_MAT, w, x, GGML_TYPE_F32, w->ne[1], x->ne[1], x->ne[2], x->ne[3]); }
+    // MUL_MAT with weight i.  Row-split: this rank computes its rows of the full result in place (a strided
+    // view of it) and the backend completes the rest from the peers (include/ggml-b200.h); the full tensor
+    // is what the rest of the graph reads.
+    ggml_tensor * mul_mat_w(int i, ggml_tensor * x) {
+        const Weight & w = weights[(size_t) i];
+        if (!w.split) return mul_mat(W(i), x);
+        ggml_tensor * full = new_tensor(GGML_TYPE_F32, w.full_rows, x->ne[1]);
+        ggml_tensor * t = view_of(full, (size_t) w.row_low * 4);
+        t->view_src = nullptr; t->view_offs = 0;                   // an op result in its own right, not a VIEW
+        t->ne[0] = w.t.ne[1]; t->ne[1] = x->ne[1]; t->ne[2] = 1; t->ne[3] = 1;
+        t->nb[0] = 4; t->nb[1] = full->nb[1]; t->nb[2] = full->nb[2]; t->nb[3] = full->nb[3];
+        t->op = GGML_OP_MUL_MAT; t->src[0] = W(i); t->src[1] = x;
+        B200_ASSERT(slices_used < slices.size());
+        ggml_b200_row_slice * rs = &slices[slices_used++];
+        rs->magic = GGML_B200_ROW_SLICE_MAGIC; rs->full_data = full->data; rs->full_rows = w.full_rows; rs->row_low = w.row_low;
+        t->extra = rs;
+        node(t);
+        return full;
+    }
     ggml_tensor * add(ggml_tensor * a, ggml_tensor * b) { return op2(GGML_OP_ADD, a, b, a->type, a->ne[0], a->ne[1], a->ne[2], a->ne[3]); }
     ggml_tensor * mul(ggml_tensor * a, ggml_tensor * b) { return op2(GGML_OP_MUL, a, b, a->type, a->ne[0], a->ne[1], a->ne[2], a->ne[3]); }
     ggml_tensor * get_rows(ggml_tensor * a, ggml_tensor * idx) { return op2(GGML_OP_GET_ROWS, a, idx, GGML_TYPE_F32, a->ne[0], idx->ne[0], idx->ne[1], idx->ne[2]); }
@@ -176,8 +201,14 @@ struct b200_llama {
 
     // ---- model ----
     static bool use_more_bits(int il, int n) { return il < n / 8 || il >= 7 * n / 8 || (il - n / 8) % 3 == 2; }
-    void add_weight(const std::string & name, ggml_type type, int64_t n0, int64_t n1) {
+    void add_weight(const std::string & name, ggml_type type, int64_t n0, int64_t n1, bool split = false) {
         Weight w; w.name = name; memset(&w.t, 0, sizeof(w.t));
+        w.full_rows = n1; w.row_low = 0; w.split = split && n_ranks > 1;
+        if (w.split) {
+            int64_t lo = 0, hi = n1;
+            b200_row_split_range(n1, rank, n_ranks, &lo, &hi);
+            w.row_low = lo; n1 = hi - lo;
+        }
         set_contig(&w.t, type, n0, n1, 1, 1);
         snprintf(w.t.name, sizeof(w.t.name), "%s", name.c_str());
         w.offset = 0;
@@ -189,25 +220,25 @@ struct b200_llama {
         const int E = cfg.n_embd, F = cfg.n_ff, KV = n_embd_kv;
         add_weight("token_embd.weight", GGML_TYPE_Q4_K, E, cfg.n_vocab);
         add_weight("output_norm.weight", GGML_TYPE_F32, E, 1);
-        add_weight("output.weight", GGML_TYPE_Q6_K, E, cfg.n_vocab);
+        add_weight("output.weight", GGML_TYPE_Q6_K, E, cfg.n_vocab, true);
         for (int il = 0; il < cfg.n_layer; ++il) {
             const std::string p = "blk." + std::to_string(il) + ".";
             const ggml_type more = use_more_bits(il, cfg.n_layer) ? GGML_TYPE_Q6_K : GGML_TYPE_Q4_K;
             add_weight(p + "attn_norm.weight", GGML_TYPE_F32, E, 1);
-            add_weight(p + "attn_q.weight", GGML_TYPE_Q4_K, E, E);
-            add_weight(p + "attn_k.weight", GGML_TYPE_Q4_K, E, KV);
-            add_weight(p + "attn_v.weight", more, E, KV);
-            add_weight(p + "attn_output.weight", GGML_TYPE_Q4_K, E, E);
+            add_weight(p + "attn_q.weight", GGML_TYPE_Q4_K, E, E, true);
+            add_weight(p + "attn_k.weight", GGML_TYPE_Q4_K, E, KV, true);
+            add_weight(p + "attn_v.weight", more, E, KV, true);
+            add_weight(p + "attn_output.weight", GGML_TYPE_Q4_K, E, E, true);
             add_weight(p + "ffn_norm.weight", GGML_TYPE_F32, E, 1);
-            add_weight(p + "ffn_gate.weight", GGML_TYPE_Q4_K, E, F);
-            add_weight(p + "ffn_up.weight", GGML_TYPE_Q4_K, E, F);
-            add_weight(p + "ffn_down.weight", more, F, E);
+            add_weight(p + "ffn_gate.weight", GGML_TYPE_Q4_K, E, F, true);
+            add_weight(p + "ffn_up.weight", GGML_TYPE_Q4_K, E, F, true);
+            add_weight(p + "ffn_down.weight", more, F, E, true);
         }
     }
     ggml_tensor * W(int i) { return &weights[(size_t) i].t; }
 
     void build_graph(int n_tokens, int pos0) {
-        pool_used = 0; nodes.clear();
+        pool_used = 0; nodes.clear(); slices_used = 0;
         rg_global.reset(); rg_layer[0].reset(); rg_layer[1].reset();
         const int n_kv = std::min<int>(cfg.n_ctx, (pos0 + n_tokens + 255) / 256 * 256);
         const int n_pad = (n_tokens + 63) / 64 * 64;
@@ -228,9 +259,9 @@ struct b200_llama {
             const int wb = W_L0 + il * W_PER_LAYER;
             ggml_tensor * inpSA = inpL;
             ggml_tensor * cur = mul(rms_norm(inpL, eps), W(wb + 0));
-            ggml_tensor * Q = mul_mat(W(wb + 1), cur);
-            ggml_tensor * K = mul_mat(W(wb + 2), cur);
-            ggml_tensor * V = mul_mat(W(wb + 3), cur);
+            ggml_tensor * Q = mul_mat_w(wb + 1, cur);
+            ggml_tensor * K = mul_mat_w(wb + 2, cur);
+            ggml_tensor * V = mul_mat_w(wb + 3, cur);
             Q = rope(reshape(Q, head_dim, cfg.n_head, n_tokens), inp_pos);
             K = rope(reshape(K, head_dim, cfg.n_head_kv, n_tokens), inp_pos);
             // KV store: F32 -> F16 into the cache rows [pos0, pos0 + n_tokens)
@@ -245,18 +276,18 @@ struct b200_llama {
                 cur   = get_rows(cur, inp_out_ids);
                 inpSA = get_rows(inpSA, inp_out_ids);
             }
-            cur = mul_mat(W(wb + 4), cur);
+            cur = mul_mat_w(wb + 4, cur);
             ggml_tensor * ffn_inp = add(cur, inpSA);
             cur = mul(rms_norm(ffn_inp, eps), W(wb + 5));
-            ggml_tensor * up   = mul_mat(W(wb + 7), cur);
-            ggml_tensor * gate = mul_mat(W(wb + 6), cur);
+            ggml_tensor * up   = mul_mat_w(wb + 7, cur);
+            ggml_tensor * gate = mul_mat_w(wb + 6, cur);
             cur = mul(silu(gate), up);
-            cur = mul_mat(W(wb + 8), cur);
+            cur = mul_mat_w(wb + 8, cur);
             inpL = add(cur, ffn_inp);
         }
         cur_region = &rg_global;
         ggml_tensor * cur = mul(rms_norm(inpL, eps), W(W_OUT_NORM));
-        logits = mul_mat(W(W_OUT), cur);
+        logits = mul_mat_w(W_OUT, cur);
 
         graph = {};
         graph.size = (int) nodes.size(); graph.n_nodes = (int) nodes.size(); graph.nodes = nodes.data();
@@ -292,6 +323,10 @@ API b200_llama * b200_llama_create(void * reg_, int32_t device_index, const b200
     std::unique_ptr<b200_llama> m(new b200_llama);
     m->cfg = *cfg;
     if (cfg->n_embd % cfg->n_head || cfg->n_head % cfg->n_head_kv || cfg->n_embd % 256 || cfg->n_ff % 256) { g_error = "unsupported model shape"; return nullptr; }
+    m->n_ranks = cfg->n_ranks > 1 ? cfg->n_ranks : 1;
+    m->rank = m->n_ranks > 1 ? cfg->rank : 0;
+    if (m->n_ranks > GGML_B200_MAX_PEERS || m->rank < 0 || m->rank >= m->n_ranks) { g_error = "bad rank / n_ranks"; return nullptr; }
+    if (m->n_ranks > 1 && reg_) { g_error = "row-split needs the B200 backend"; return nullptr; }
     m->head_dim = cfg->n_embd / cfg->n_head;
     m->n_embd_kv = m->head_dim * cfg->n_head_kv;
     m->reg = reg_ ? (ggml_backend_reg_t) reg_ : ggml_backend_init();
@@ -310,6 +345,7 @@ API b200_llama * b200_llama_create(void * reg_, int32_t device_index, const b200
         auto gs = (void * (*)(ggml_backend_t)) m->reg->iface.get_proc_address(m->reg, "ggml_backend_b200_get_stream");
         m->stream = (cudaStream_t) gs(m->backend);
         m->launch_count_fn = (uint64_t (*)(ggml_backend_t)) m->reg->iface.get_proc_address(m->reg, "ggml_backend_b200_get_launch_count");
+        m->status_fn = (int (*)(ggml_backend_t)) m->reg->iface.get_proc_address(m->reg, "ggml_backend_b200_get_status");
         B200_CUDA_CHECK(cudaEventCreate(&m->ev0));
         B200_CUDA_CHECK(cudaEventCreate(&m->ev1));
     }
@@ -341,22 +377,29 @@ API b200_llama * b200_llama_create(void * reg_, int32_t device_index, const b200
     }
 
     // compute buffer: size it with a dry run of the largest graph
-    m->pool.resize((size_t) cfg->n_layer * 64 + 64);
+    m->pool.resize((size_t) cfg->n_layer * 80 + 64);
+    m->slices.resize((size_t) cfg->n_layer * 7 + 1);
     m->nodes.reserve(m->pool.size());
     m->build_graph(cfg->n_ubatch, cfg->n_ctx - cfg->n_ubatch);
+    // The compute buffer is the arena the peers map in row-split mode: its first bytes hold the barrier
+    // flags (zero to begin with), and every rank lays it out identically.
     const size_t sg = align_up(m->rg_global.peak) + ALIGN, sl = align_up(std::max(m->rg_layer[0].peak, m->rg_layer[1].peak)) + ALIGN;
-    m->buf_c = alloc_buffer(m.get(), sg + 2 * sl, "compute");
+    const size_t fl = GGML_B200_PEER_FLAG_BYTES;
+    m->buf_c = alloc_buffer(m.get(), fl + sg + 2 * sl, "compute");
     if (!m->buf_c) { free_buffer(m->buf_w); free_buffer(m->buf_kv); return nullptr; }
+    m->buf_c->iface.clear(m->buf_c, 0);
     char * cbase = (char *) m->buf_c->iface.get_base(m->buf_c);
-    m->rg_global.base = cbase; m->rg_global.cap = sg;
-    m->rg_layer[0].base = cbase + sg; m->rg_layer[0].cap = sl;
-    m->rg_layer[1].base = cbase + sg + sl; m->rg_layer[1].cap = sl;
+    m->rg_global.base = cbase + fl; m->rg_global.cap = sg;
+    m->rg_layer[0].base = cbase + fl + sg; m->rg_layer[0].cap = sl;
+    m->rg_layer[1].base = cbase + fl + sg + sl; m->rg_layer[1].cap = sl;
+    m->arena_bytes = fl + sg + 2 * sl;
     return m.release();
 }
 
 API void b200_llama_free(b200_llama * m) {
     if (!m) return;
     if (m->backend->iface.synchronize) m->backend->iface.synchronize(m->backend);
+    for (int r = 0; r < m->n_ranks; ++r) if (r != m->rank && m->peer_arena[r]) cudaIpcCloseMemHandle(m->peer_arena[r]);
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
     free_buffer(m->buf_c); free_buffer(m->buf_kv); free_buffer(m->buf_w);
@@ -420,8 +463,63 @@ API int32_t b200_llama_decode(b200_llama * m, const int32_t * tokens, int32_t n_
     }
     if (m->backend->iface.synchronize) m->backend->iface.synchronize(m->backend);
     m->last_n_nodes = m->graph.n_nodes;
+    if (m->n_ranks > 1 && m->status_fn) {              // a rank that stopped answering shows up as a barrier that gave up
+        const int dev_status = m->status_fn(m->backend);
+        if (dev_status != 0) { g_error = "device status " + std::to_string(dev_status) + " (3 = a peer did not reach the barrier in time)"; return -3; }
+    }
     if (m->is_b200) { float ms = 0; B200_CUDA_CHECK(cudaEventElapsedTime(&ms, m->ev0, m->ev1)); m->last_ms = ms; }
     else m->last_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    return 0;
+}
+
+API void b200_row_split_range(int64_t n_rows, int32_t rank, int32_t n_ranks, int64_t * row_low, int64_t * row_high) {
+    // equal shares, boundaries rounded down to a multiple of 128 rows, the last rank takes the remainder
+    // (get_row_split with the MMQ tile height as rounding, ggml/src/ggml-cuda/ggml-cuda.cu:725-742)
+    const int64_t R = 128;
+    auto bound = [&](int r) -> int64_t {
+        if (r <= 0) return 0;
+        if (r >= n_ranks) return n_rows;
+        const int64_t b = n_rows * r / n_ranks;
+        return b - b % R;
+    };
+    if (n_ranks < 1) n_ranks = 1;
+    *row_low = bound(rank); *row_high = bound(rank + 1);
+}
+
+API int32_t b200_llama_tensor_rows(const b200_llama * m, int32_t i, int64_t * row_low, int64_t * full_rows) {
+    if (i < 0 || (size_t) i >= m->weights.size()) return -1;
+    if (row_low) *row_low = m->weights[(size_t) i].row_low;
+    if (full_rows) *full_rows = m->weights[(size_t) i].full_rows;
+    return 0;
+}
+
+API int32_t b200_llama_ipc_handle(b200_llama * m, void * handle_out) {
+    if (!m->is_b200) { g_error = "not the B200 backend"; return -1; }
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, m->buf_c->iface.get_base(m->buf_c));
+    if (e != cudaSuccess) { cudaGetLastError(); g_error = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e); return -2; }
+    static_assert(sizeof(h) == B200_LLAMA_IPC_HANDLE_BYTES, "handle size");
+    memcpy(handle_out, &h, sizeof(h));
+    return 0;
+}
+
+API int32_t b200_llama_attach_peers(b200_llama * m, const void * handles) {
+    if (m->n_ranks < 2) return 0;
+    ggml_b200_peers pr = {};
+    pr.rank = m->rank; pr.n_ranks = m->n_ranks; pr.arena_bytes = m->arena_bytes;
+    for (int r = 0; r < m->n_ranks; ++r) {
+        if (r == m->rank) { pr.arena[r] = m->buf_c->iface.get_base(m->buf_c); continue; }
+        if (!m->peer_arena[r]) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, (const char *) handles + (size_t) r * sizeof(h), sizeof(h));
+            const cudaError_t e = cudaIpcOpenMemHandle(&m->peer_arena[r], h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) { cudaGetLastError(); m->peer_arena[r] = nullptr; g_error = std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e); return -2; }
+        }
+        pr.arena[r] = m->peer_arena[r];
+    }
+    auto fn = (int (*)(ggml_backend_t, const ggml_b200_peers *)) m->reg->iface.get_proc_address(m->reg, "ggml_backend_b200_set_peers");
+    const int rc = fn ? fn(m->backend, &pr) : -100;
+    if (rc != 0) { g_error = "ggml_backend_b200_set_peers failed: " + std::to_string(rc); return -3; }
     return 0;
 }
 

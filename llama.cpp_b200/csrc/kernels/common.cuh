@@ -215,7 +215,7 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ void pdl_enter() { pdl_launch_dependents(); pdl_wait(); }
 
 // error codes written to the device status word by kernels that give up a wait
-enum : int { ERR_NONE = 0, ERR_MBAR_TIMEOUT = 1, ERR_BAD_ARG = 2 };
+enum : int { ERR_NONE = 0, ERR_MBAR_TIMEOUT = 1, ERR_BAD_ARG = 2, ERR_PEER_TIMEOUT = 3 };
 
 static thread_local cudaError_t launch_err = cudaSuccess;   // result of the most recent launch_k in this translation unit
 

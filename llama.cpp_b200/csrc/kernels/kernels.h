@@ -27,6 +27,21 @@ struct LaunchCtx {
 };
 static constexpr int FATTN_DEC_TICKETS = 4096;
 
+// ---- row-split exchange over peer memory (peer.cu) ----
+static constexpr int MAX_PEERS = 8;                    // ranks per node
+struct PeerPush {                                      // copy a [ncols][col_bytes] slab (column stride col_stride) to every peer
+    const char * src; char * peer_dst[MAX_PEERS - 1]; int n_peer;
+    int64_t col_bytes, col_stride, ncols; int shift;   // shift: 4 = 16-byte elements, 2 = 4-byte elements
+};
+struct PeerBarrier {
+    unsigned * epoch;                                  // this rank's epoch counter (device memory)
+    unsigned * local_flags;                            // [MAX_PEERS], slot r written by rank r
+    unsigned * peer_flags[MAX_PEERS];                  // the flag arrays of the other ranks (mapped)
+    int rank, n_ranks; int * status;
+};
+cudaError_t launch_peer_push(const PeerPush & p, const LaunchCtx & c);
+cudaError_t launch_peer_barrier(const PeerBarrier & b, const LaunchCtx & c);
+
 // ---- quantized mat-vec (mmvq.cu) ----
 struct MmvqArgs {
     int type;
@@ -39,6 +54,8 @@ struct MmvqArgs {
     int * status; int sm_count, device, use_pdl;
     // up to two more weight matrices of the same type, K and row stride that share Xq (direct Q4_K/Q5_K kernel only)
     int n_extra; const void * extra_W[2]; float * extra_dst[2]; int64_t extra_dst_nb1[2]; int extra_M[2];
+    // row-split: every result is also stored at dst + peer_delta[i] (the same place in each peer's mapped arena)
+    int n_peer; int64_t peer_delta[MAX_PEERS - 1];
 };
 bool        mmvq_type_supported(int type);
 size_t      act128_bytes(int64_t K, int64_t ncols);
@@ -46,6 +63,9 @@ size_t      act128_bytes(int64_t K, int64_t ncols);
 cudaError_t launch_quantize_act128(const float * x, int64_t ne11, int64_t ne12, int64_t ne13,
                                    int64_t s11, int64_t s12, int64_t s13, void * y, int K, cudaStream_t stream, int use_pdl = 0);
 cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream);
+// true when the kernel launch_mmvq picks writes the peer copies itself (n_peer, peer_delta); otherwise
+// the caller pushes the slab with launch_peer_push
+bool        mmvq_stores_to_peers(const MmvqArgs & a);
 // direct 128-bit-coalesced variant for Q4_K / Q5_K (mmvq_k.cu); launch_mmvq routes to it when applicable
 bool        mmvq_k_applicable(const MmvqArgs & a);
 cudaError_t launch_mmvq_k(const MmvqArgs & a, cudaStream_t stream);

@@ -565,6 +565,9 @@ cudaError_t launch_quantize_act128(const float * x, int64_t ne11, int64_t ne12, 
                     x, ne11, ne12, s11, s12, s13, (blk_act128 *) y, K, nblk, ncols);
 }
 
+// do the kernels launch_mmvq picks for these arguments honour n_peer / peer_delta?
+bool mmvq_stores_to_peers(const MmvqArgs & a) { return mmvq_k_applicable(a) || mmvq_q6k_applicable(a); }
+
 cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream) {
     if (mmvq_k_applicable(a)) return launch_mmvq_k(a, stream);
     if (mmvq_q6k_applicable(a)) return launch_mmvq_q6k(a, stream);

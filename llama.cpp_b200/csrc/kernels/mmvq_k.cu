@@ -35,6 +35,7 @@ struct MkParams {
     int m_end[3], nmat;
     int M, K;
     int x_col0;
+    int n_peer; int64_t peer_delta[MAX_PEERS - 1];   // row-split: results also go to dst + peer_delta[i]
 };
 // (no dynamic indexing into the parameter arrays: that would move them to local memory)
 __device__ __forceinline__ const uint8_t * mk_row_ptr(const MkParams & p, int row, int & mat, int & local) {
@@ -85,6 +86,10 @@ __global__ void __launch_bounds__(MK_WARPS * 32, OCC) mmvq_k_kernel(const MkPara
     const int sh16 = 16 * (j & 1);
     const uint32_t mk1 = low ? 0x3F3Fu : 0x0F0Fu, mk2 = low ? 0u : 0x3030u;
     const int niter = (nsb + 7) >> 3;
+    // result stores: lane 0 writes this GPU's dst, lane q + 1 the copy in peer q's arena (row-split)
+    bool storer = lane == 0; int64_t st_delta = 0;
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS - 1; ++q) if (q < p.n_peer && lane == q + 1) { storer = true; st_delta = p.peer_delta[q]; }
 
     auto load = [&](MkBuf<T> & B, int row, int it0) {
         int mat, lrow;
@@ -160,7 +165,7 @@ __global__ void __launch_bounds__(MK_WARPS * 32, OCC) mmvq_k_kernel(const MkPara
 #pragma unroll
             for (int n = 0; n < N; ++n) {
                 const float v = warp_sum(acc[n]);
-                if (lane == 0) ((float *) ((uint8_t *) d0 + (int64_t) n * nb1))[lrow] = v;
+                if (storer) ((float *) ((uint8_t *) d0 + (int64_t) n * nb1 + st_delta))[lrow] = v;
                 acc[n] = 0.0f;
             }
         }
@@ -257,6 +262,7 @@ cudaError_t launch_mmvq_k(const MmvqArgs & a, cudaStream_t stream) {
     }
     if (p.nmat < 2) p.m_end[1] = 0x7fffffff;        // row >= m_end[1] never holds
     p.M = p.m_end[p.nmat - 1]; p.K = a.K; p.x_col0 = a.x_col0;
+    p.n_peer = a.n_peer; for (int i = 0; i < a.n_peer; ++i) p.peer_delta[i] = a.peer_delta[i];
     if (a.type == T_Q4_K) return launch_mk_t<T_Q4_K>(p, a.N, a.sm_count, a.device, a.use_pdl, stream);
     return launch_mk_t<T_Q5_K>(p, a.N, a.sm_count, a.device, a.use_pdl, stream);
 }

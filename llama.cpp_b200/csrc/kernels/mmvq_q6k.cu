@@ -25,6 +25,7 @@ struct Q6Params {
     const uint8_t * Xq; int64_t xq_col_bytes;
     float * dst;        int64_t dst_nb1;
     int M, K, x_col0;
+    int n_peer; int64_t peer_delta[MAX_PEERS - 1];   // row-split: results also go to dst + peer_delta[i]
 };
 
 // NW consecutive 32-bit words at a 2-byte aligned shared-memory address
@@ -54,6 +55,9 @@ __global__ void __launch_bounds__(Q6_WARPS * 32, 2) mmvq_q6k_kernel(const Q6Para
     const int nruns = (nsb + Q6_RUN_BLOCKS - 1) / Q6_RUN_BLOCKS;
     const int row_stride = gridDim.x * Q6_WARPS;
     int row = blockIdx.x * Q6_WARPS + warp;
+    bool storer = lane == 0; int64_t st_delta = 0;
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS - 1; ++q) if (q < p.n_peer && lane == q + 1) { storer = true; st_delta = p.peer_delta[q]; }
 
     uint4 v[Q6_VECS_PER_LANE];
     auto load_run = [&](int r, int run) {
@@ -137,9 +141,9 @@ __global__ void __launch_bounds__(Q6_WARPS * 32, 2) mmvq_q6k_kernel(const Q6Para
         }
 #pragma unroll
         for (int n = 0; n < N; ++n) acc[n] = warp_sum(acc[n]);
-        if (lane == 0) {
+        if (storer) {                     // lane 0: this GPU's dst; lane q + 1: the copy in peer q's arena
 #pragma unroll
-            for (int n = 0; n < N; ++n) ((float *) ((uint8_t *) p.dst + (int64_t) n * p.dst_nb1))[row] = acc[n];
+            for (int n = 0; n < N; ++n) ((float *) ((uint8_t *) p.dst + (int64_t) n * p.dst_nb1 + st_delta))[row] = acc[n];
         }
         row += row_stride;
     }
@@ -187,6 +191,7 @@ cudaError_t launch_mmvq_q6k(const MmvqArgs & a, cudaStream_t stream) {
     p.Xq = (const uint8_t *) a.Xq; p.xq_col_bytes = (int64_t) ((a.K + 127) / 128) * 160;
     p.dst = a.dst; p.dst_nb1 = a.dst_nb1;
     p.M = a.M; p.K = a.K; p.x_col0 = a.x_col0;
+    p.n_peer = a.n_peer; for (int i = 0; i < a.n_peer; ++i) p.peer_delta[i] = a.peer_delta[i];
     switch (a.N) {
         case 1: return launch_q6k_n<1>(p, a.sm_count, a.device, a.use_pdl, stream);
         case 2: return launch_q6k_n<2>(p, a.sm_count, a.device, a.use_pdl, stream);

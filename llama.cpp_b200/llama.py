@@ -11,7 +11,10 @@ from . import B200Error, lib
 class Config(C.Structure):
     _fields_ = [("n_layer", C.c_int32), ("n_embd", C.c_int32), ("n_head", C.c_int32), ("n_head_kv", C.c_int32),
                 ("n_ff", C.c_int32), ("n_vocab", C.c_int32), ("n_ctx", C.c_int32), ("n_ubatch", C.c_int32),
-                ("rope_theta", C.c_float), ("rms_eps", C.c_float), ("n_threads", C.c_int32)]
+                ("rope_theta", C.c_float), ("rms_eps", C.c_float), ("n_threads", C.c_int32),
+                ("n_ranks", C.c_int32), ("rank", C.c_int32)]
+
+IPC_HANDLE_BYTES = 64
 
 
 LLAMA3_8B = dict(n_layer=32, n_embd=4096, n_head=32, n_head_kv=8, n_ff=14336, n_vocab=128256, rope_theta=500000.0, rms_eps=1e-5)
@@ -43,6 +46,9 @@ def _bind():
         l.b200_llama_launch_count.argtypes = [vp]
         l.b200_llama_weight_bytes.restype = C.c_size_t
         l.b200_llama_weight_bytes.argtypes = [vp]
+        l.b200_llama_tensor_rows.argtypes = [vp, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+        l.b200_llama_ipc_handle.argtypes = [vp, vp]
+        l.b200_llama_attach_peers.argtypes = [vp, vp]
         _bound = True
     return l
 
@@ -51,11 +57,15 @@ class Llama:
     """A Llama-architecture model evaluated through a ggml backend's C-ABI.
 
     reg: address of a ggml_backend_reg (another backend library's ggml_backend_init() result) or None for the B200 plugin.
+    rank / n_ranks: row-split over n_ranks processes with one GPU each; after construction (and before the first
+    decode) every rank calls attach_peers() with a gather function, e.g. the one row_split.gather_bytes builds
+    on torch.distributed.
     """
 
-    def __init__(self, n_ctx: int, n_ubatch: int, reg: int | None = None, device_index: int = 0, n_threads: int = 0, **arch):
+    def __init__(self, n_ctx: int, n_ubatch: int, reg: int | None = None, device_index: int = 0, n_threads: int = 0,
+                 rank: int = 0, n_ranks: int = 1, **arch):
         self.l = _bind()
-        self.cfg = Config(n_ctx=n_ctx, n_ubatch=n_ubatch, n_threads=n_threads, **arch)
+        self.cfg = Config(n_ctx=n_ctx, n_ubatch=n_ubatch, n_threads=n_threads, n_ranks=n_ranks, rank=rank, **arch)
         self.h = self.l.b200_llama_create(reg, device_index, C.byref(self.cfg))
         if not self.h:
             raise B200Error(f"b200_llama_create failed: {self.l.b200_llama_error().decode()}")
@@ -70,10 +80,27 @@ class Llama:
         out = []
         name = C.create_string_buffer(128)
         t, n0, n1, nb = C.c_int32(), C.c_int64(), C.c_int64(), C.c_size_t()
+        lo, full = C.c_int64(), C.c_int64()
         for i in range(self.l.b200_llama_n_tensors(self.h)):
             self.l.b200_llama_tensor_info(self.h, i, name, 128, C.byref(t), C.byref(n0), C.byref(n1), C.byref(nb))
-            out.append(dict(index=i, name=name.value.decode(), type=t.value, ne0=n0.value, ne1=n1.value, nbytes=nb.value))
+            self.l.b200_llama_tensor_rows(self.h, i, C.byref(lo), C.byref(full))
+            # ne1 rows starting at row_low of a full_rows-row tensor are stored on this rank
+            out.append(dict(index=i, name=name.value.decode(), type=t.value, ne0=n0.value, ne1=n1.value, nbytes=nb.value,
+                            row_low=lo.value, full_rows=full.value))
         return out
+
+    def attach_peers(self, gather):
+        """gather(handle: bytes) -> list of every rank's bytes in rank order (a collective call)."""
+        if self.cfg.n_ranks < 2:
+            return
+        h = C.create_string_buffer(IPC_HANDLE_BYTES)
+        if self.l.b200_llama_ipc_handle(self.h, h) != 0:
+            raise B200Error(self.l.b200_llama_error().decode())
+        allh = gather(h.raw)
+        if len(allh) != self.cfg.n_ranks or any(len(x) != IPC_HANDLE_BYTES for x in allh):
+            raise B200Error("attach_peers: gather must return one handle per rank")
+        if self.l.b200_llama_attach_peers(self.h, b"".join(allh)) != 0:
+            raise B200Error(self.l.b200_llama_error().decode())
 
     def set_tensor(self, i: int, data: np.ndarray):
         data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)

@@ -1,0 +1,180 @@
+#!/usr/bin/env python
+"""Per-op timing of the hot-path kernels through the flat C-ABI, cold cache.
+
+The counterpart of the reference's `test-backend-ops perf` (tests/test-backend-ops.cpp:681-693) for the
+ops this backend accelerates.  Each case cycles through enough distinct copies of its large operand
+(>= 600 MB in total, several times the L2) that every launch reads it from HBM, and is timed with CUDA
+events on the launching stream.  Bytes and flops follow the reference's accounting
+(tests/test-backend-ops.cpp:1924-1927 for MUL_MAT, :3141-3146 for FLASH_ATTN_EXT).
+
+  python llama.cpp_b200/microbench.py mul_mat --type q4_K -k 4096 -m 14336 -n 1
+  python llama.cpp_b200/microbench.py mul_mat --type q4_K -k 4096 -m 14336 -n 512
+  python llama.cpp_b200/microbench.py flash_attn --n-kv 32768 --n-q 1
+  python llama.cpp_b200/microbench.py sweep          # the projection shapes of Llama-3-8B
+
+`--copies C --reps R` bound the work (for a profiler capture: `--copies 4 --reps 1`).
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+QK_TYPES = ("q4_0", "q8_0", "q4_K", "q5_K", "q6_K")
+
+
+def _weights(pkg, torch, qtype, k, m, copies):
+    """`copies` distinct device copies of one synthetic quantized [k x m] weight matrix."""
+    from llama_cpp_b200 import synth
+    l = pkg.lib()
+    t = pkg.TYPES[qtype]
+    rb = int(l.b200_row_size(t, k))
+    rows = min(m, 4096)
+    if qtype in ("q4_K", "q6_K"):
+        base = torch.from_numpy(synth.make_tensor(t, k, rows, 1, device="cuda")).cuda()
+    elif qtype == "q5_K":       # a Q4_K block with 32 random high-bit bytes spliced in after its 16-byte header
+        q4 = torch.from_numpy(synth.make_tensor(pkg.TYPES["q4_K"], k, rows, 1, device="cuda")).cuda().reshape(-1, 144)
+        qh = torch.randint(0, 256, (q4.shape[0], 32), dtype=torch.uint8, device="cuda")
+        base = torch.cat([q4[:, :16], qh, q4[:, 16:]], 1).reshape(-1)
+    else:                       # Q4_0 / Q8_0 through the device quantizers (CPY F32 -> quantized)
+        import numpy as np
+        x = (0.02 * torch.randn(rows, k, device="cuda")).cpu().numpy()
+        base = torch.from_numpy(pkg.quantize_rows(qtype, x).reshape(-1)).cuda()
+    w = torch.empty((copies, rb * m + 256), dtype=torch.uint8, device="cuda")
+    for c in range(copies):
+        for r0 in range(0, m, 4096):
+            n = min(4096, m - r0)
+            w[c, r0 * rb:(r0 + n) * rb] = base[:n * rb]
+    return w, rb, t
+
+
+def _time(torch, run, reps, graph=True):
+    """Average device milliseconds of run(), replayed from a CUDA graph so host launch cost is excluded."""
+    run()
+    torch.cuda.synchronize()
+    replay = run
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            run()
+        replay = g.replay
+        replay()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def bench_mul_mat(pkg, torch, qtype, k, m, n, copies=None, reps=20):
+    l = pkg.lib()
+    rb = int(l.b200_row_size(pkg.TYPES[qtype], k))
+    copies = copies or max(2, int(600e6 // (rb * m)) + 1)
+    w, rb, t = _weights(pkg, torch, qtype, k, m, copies)
+    x = torch.randn(n, k, device="cuda")
+    dst = torch.empty(n, m, device="cuda")
+    if n <= 8:          # decode: activations quantized once, then the mat-vec kernel alone
+        xq = torch.empty(int(l.b200_act_bytes(k, n)), dtype=torch.uint8, device="cuda")
+        assert l.b200_quantize_act(x.data_ptr(), k, k, n, xq.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+
+        def run():
+            s = torch.cuda.current_stream().cuda_stream
+            for c in range(copies):
+                rc = l.b200_mul_mat_vec_q(t, w[c].data_ptr(), rb, m, k, xq.data_ptr(), n, dst.data_ptr(), m, s)
+                assert rc == 0, l.b200_last_error()
+        graph = True
+    else:               # prefill: the whole MUL_MAT (activation conversion + tensor-core GEMM)
+        sb = int(l.b200_mul_mat_q_scratch_bytes(t, m, k, n))
+        sc = torch.empty(sb + 256, dtype=torch.uint8, device="cuda")
+
+        def run():
+            s = torch.cuda.current_stream().cuda_stream
+            for c in range(copies):
+                rc = l.b200_mul_mat_q(t, w[c].data_ptr(), rb, m, k, x.data_ptr(), k, n, dst.data_ptr(), m, sc.data_ptr(), sb, s)
+                assert rc == 0, l.b200_last_error()
+        graph = False
+    us = _time(torch, run, reps, graph) * 1e3 / copies
+    nbytes = rb * m + 4 * k * n + 4 * m * n
+    flops = 2.0 * m * n * k
+    print(f"MUL_MAT {qtype:5s} K={k:6d} M={m:7d} N={n:4d}  {us:9.2f} us  {nbytes / us / 1e3:8.1f} GB/s  {flops / us / 1e6:8.1f} TFLOP/s"
+          f"  ({copies} copies, {rb * m / 1e6:.1f} MB each)", flush=True)
+    return us
+
+
+def bench_flash_attn(pkg, torch, n_kv, n_q, n_head=32, n_head_kv=8, d=128, copies=None, reps=20):
+    l = pkg.lib()
+    kv_bytes = 2 * 2 * d * n_kv * n_head_kv
+    copies = copies or max(2, int(600e6 // kv_bytes) + 1)
+    # cache layout of the reference's KV views: a token's heads are adjacent (nb1 = n_head_kv * d * 2, nb2 = d * 2)
+    kc = torch.randn(copies, n_kv, n_head_kv, d, device="cuda").half()
+    vc = torch.randn(copies, n_kv, n_head_kv, d, device="cuda").half()
+    q = torch.randn(n_head, n_q, d, device="cuda")
+    n_pad = (n_q + 63) // 64 * 64
+    mask = torch.full((n_pad, n_kv), float("-inf"), device="cuda", dtype=torch.float16)
+    qi = torch.arange(n_q, device="cuda")[:, None]
+    ki = torch.arange(n_kv, device="cuda")[None, :]
+    mask[:n_q] = torch.where(ki <= n_kv - n_q + qi, 0.0, float("-inf")).half()
+    dst = torch.empty(n_q, n_head, d, device="cuda")
+    sb = int(l.b200_flash_attn_scratch_bytes(d, n_q, n_head, n_kv))
+    sc = torch.empty(sb + 256, dtype=torch.uint8, device="cuda")
+
+    def run():
+        s = torch.cuda.current_stream().cuda_stream
+        for c in range(copies):
+            rc = l.b200_flash_attn(q.data_ptr(), d * 4, n_q * d * 4, kc[c].data_ptr(), n_head_kv * d * 2, d * 2,
+                                   vc[c].data_ptr(), n_head_kv * d * 2, d * 2, mask.data_ptr(), n_kv * 2, dst.data_ptr(),
+                                   d, n_q, n_head, n_kv, n_head_kv, d ** -0.5, 0.0, 0.0, sc.data_ptr(), sb, s)
+            assert rc == 0, l.b200_last_error()
+    us = _time(torch, run, reps, graph=n_q <= 8) * 1e3 / copies
+    nbytes = kv_bytes + 2 * 4 * d * n_q * n_head + 2 * n_kv * n_q
+    flops = 4.0 * n_head * n_q * d * n_kv
+    print(f"FLASH_ATTN_EXT D={d} heads {n_head}/{n_head_kv} n_kv={n_kv:6d} n_q={n_q:4d}  {us:9.2f} us  {nbytes / us / 1e3:8.1f} GB/s"
+          f"  {flops / us / 1e6:8.1f} TFLOP/s  ({copies} copies)", flush=True)
+    return us
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("op", choices=["mul_mat", "flash_attn", "sweep"])
+    ap.add_argument("--type", default="q4_K", choices=QK_TYPES)
+    ap.add_argument("-k", type=int, default=4096)
+    ap.add_argument("-m", type=int, default=14336)
+    ap.add_argument("-n", type=int, default=1)
+    ap.add_argument("--n-kv", type=int, default=4096)
+    ap.add_argument("--n-q", type=int, default=1)
+    ap.add_argument("--copies", type=int, default=None)
+    ap.add_argument("--reps", type=int, default=20)
+    a = ap.parse_args()
+    pkg = entry.load_package()
+    import torch
+    if pkg.device_count() < 1:
+        raise SystemExit("no sm_100 device visible: these kernels have no CPU fallback")
+    if a.op == "mul_mat":
+        bench_mul_mat(pkg, torch, a.type, a.k, a.m, a.n, a.copies, a.reps)
+    elif a.op == "flash_attn":
+        bench_flash_attn(pkg, torch, a.n_kv, a.n_q, copies=a.copies, reps=a.reps)
+    else:
+        shapes = [(4096, 4096), (4096, 14336), (14336, 4096)]
+        for n in (1, 8, 32, 128, 512):
+            for qt in ("q4_K", "q6_K", "q8_0"):
+                for k, m in shapes:
+                    bench_mul_mat(pkg, torch, qt, k, m, n, reps=a.reps if n <= 8 else 5)
+        for qt in ("q4_K", "q6_K", "q8_0"):
+            for n in (1, 512):
+                bench_mul_mat(pkg, torch, qt, 4096, 128256, n, copies=2, reps=5)
+        bench_mul_mat(pkg, torch, "q4_0", 4096, 4096, 1)
+        bench_mul_mat(pkg, torch, "q4_0", 4096, 4096, 512, reps=5)
+        for n_kv in (512, 4096, 32768):
+            for n_q in (1, 512):
+                bench_flash_attn(pkg, torch, n_kv, n_q, reps=a.reps if n_q == 1 else 5)
+
+
+if __name__ == "__main__":
+    main()

@@ -38,7 +38,7 @@ import __graft_entry__ as entry  # noqa: E402
 
 N_PROMPT, N_GEN = 512, 128
 CPU_PROMPT, CPU_GEN = 128, 16
-METRIC = "llama3-8b-q4_k_m tg128 tokens/s (pp512+tg128 per step)"
+METRIC = "llama3-8b-q4_k_m tg128 tokens/s (pp512+tg128 per step)"   # --model 70b replaces the model name
 
 
 def log(*a):
@@ -200,25 +200,40 @@ def time_cpu(m, tokens, steps, warmup):
     return steps * CPU_PROMPT / pp_s, steps * CPU_GEN / tg_s, (pp_s + tg_s) / steps
 
 
+def emit(line: str):
+    """The one JSON line goes to the process's original stdout; everything else any library prints
+    (NCCL's version banner, for one) was redirected to stderr at start-up."""
+    os.write(_REAL_STDOUT, (line + "\n").encode())
+
+
+_REAL_STDOUT = 1
+
+
 def main():
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--model", default="8b", choices=["8b", "70b"],
+                    help="8b: the configuration the metric is quoted on; 70b: the row-split parity configuration (no CPU baseline)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     pkg = entry.load_package()   # registers the package under the alias llama_cpp_b200
     from llama_cpp_b200 import llama
-    arch = dict(llama.LLAMA3_8B)
+    arch = dict(llama.LLAMA3_8B if args.model == "8b" else llama.LLAMA3_70B)
     cores = os.cpu_count() or 1
     rng = np.random.default_rng(1234)
     tokens = rng.integers(0, arch["n_vocab"], N_PROMPT + N_GEN).astype(np.int32)
-    config = {"workload": "llama3-8b-arch q4_k_m pp512+tg128 (BASELINE configs[3])", "n_prompt": N_PROMPT, "n_gen": N_GEN,
-              "flash_attn": True, "kv_type": "f16", "l2": "working set 4.6 GB of weights per token >> L2, no flush needed"}
+    config = {"workload": f"llama3-{args.model}-arch q4_k_m pp512+tg128 (BASELINE configs[{3 if args.model == '8b' else 4}])", "n_prompt": N_PROMPT, "n_gen": N_GEN,
+              "flash_attn": True, "kv_type": "f16", "l2": "every token re-reads all weights (4.6 GB for 8b, 42 GB for 70b) >> L2, no flush needed"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -229,7 +244,7 @@ def main():
         pp_tps, tg_tps, step_s = time_cpu(m, tokens, args.steps, min(args.warmup, 1))
         m.close()
         sample = f"pp{CPU_PROMPT}+tg{CPU_GEN} per step on the reference ggml CPU backend, {cores} threads"
-        print(json.dumps({"impl": "reference", "metric": METRIC, "value": tg_tps, "unit": "tokens/s", "n_gpus": args.gpus,
+        emit(json.dumps({"impl": "reference", "metric": METRIC, "value": tg_tps, "unit": "tokens/s", "n_gpus": args.gpus,
                           "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
                           "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4/6 dot, f32 accumulate", "data": "synthetic",
                           "config": dict(config, sample=sample), "pp_tokens_per_s": pp_tps,
@@ -265,7 +280,7 @@ def main():
 
     m = llama.Llama(n_ctx=1024, n_ubatch=N_PROMPT, device_index=local, rank=rank, n_ranks=world, **arch)
     cpu = None
-    if not args.no_cpu_baseline and rank == 0 and world == 1:
+    if not args.no_cpu_baseline and rank == 0 and world == 1 and args.model == "8b":
         try:
             cpu = cpu_model(arch, cores)
         except Exception as e:  # the baseline is reported, never required for the GPU number
@@ -325,7 +340,7 @@ def main():
                         "sample": f"pp{CPU_PROMPT}+tg{CPU_GEN} on the reference ggml CPU backend, {cores} threads",
                         "pp_tokens_per_s": c_pp, "logits_nmse_vs_b200": nmse}
         cpu.close()
-    out = {"metric": METRIC, "value": tg_tps_dev, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+    out = {"metric": METRIC.replace("8b", args.model), "value": tg_tps_dev, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
            "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
            "dtype": "int8 x int4/6 dot, f32 accumulate", "data": "synthetic", "config": config,
            "pp512_tokens_per_s": pp_tps_dev, "tg128_tokens_per_s": tg_tps_dev,
@@ -336,7 +351,7 @@ def main():
     m.close()
     if dist is not None:
         dist.destroy_process_group()
-    print(json.dumps(out))
+    emit(json.dumps(out))
 
 
 if __name__ == "__main__":

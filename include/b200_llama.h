@@ -38,8 +38,9 @@ typedef struct b200_llama_config {
 
 /* reg: a ggml_backend_reg_t (as returned by a backend library's ggml_backend_init), or NULL for
  * this library's own B200 registry.  Weight tensor types follow the reference's Q4_K_M mixture
- * (src/llama-quant.cpp:129-131, 235-236, 291-298): Q4_K, with Q6_K for output.weight and for
- * attn_v / ffn_down on the "more bits" layers.  Returns NULL on failure (b200_llama_error()). */
+ * (src/llama-quant.cpp:129-131, 235-243, 291-298): Q4_K, with Q6_K for output.weight and for
+ * attn_v / ffn_down on the "more bits" layers; an 80-layer (70B-class) model keeps the other attn_v
+ * tensors at Q5_K.  Returns NULL on failure (b200_llama_error()). */
 b200_llama * b200_llama_create(void * reg, int32_t device_index, const b200_llama_config * cfg);
 void         b200_llama_free(b200_llama * m);
 const char * b200_llama_error(void);

@@ -224,10 +224,13 @@ struct b200_llama {
         for (int il = 0; il < cfg.n_layer; ++il) {
             const std::string p = "blk." + std::to_string(il) + ".";
             const ggml_type more = use_more_bits(il, cfg.n_layer) ? GGML_TYPE_Q6_K : GGML_TYPE_Q4_K;
+            // 70B-class models (80 layers, 8 query heads per KV head) keep attn_v at 5 bits or more:
+            // src/llama-quant.cpp:238-243
+            const ggml_type v_type = (cfg.n_layer == 80 && more == GGML_TYPE_Q4_K) ? GGML_TYPE_Q5_K : more;
             add_weight(p + "attn_norm.weight", GGML_TYPE_F32, E, 1);
             add_weight(p + "attn_q.weight", GGML_TYPE_Q4_K, E, E, true);
             add_weight(p + "attn_k.weight", GGML_TYPE_Q4_K, E, KV, true);
-            add_weight(p + "attn_v.weight", more, E, KV, true);
+            add_weight(p + "attn_v.weight", v_type, E, KV, true);
             add_weight(p + "attn_output.weight", GGML_TYPE_Q4_K, E, E, true);
             add_weight(p + "ffn_norm.weight", GGML_TYPE_F32, E, 1);
             add_weight(p + "ffn_gate.weight", GGML_TYPE_Q4_K, E, F, true);

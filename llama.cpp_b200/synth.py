@@ -45,6 +45,40 @@ def quantize_q4_K(x: torch.Tensor) -> torch.Tensor:
     return out.reshape(R, nb * 144)
 
 
+def quantize_q5_K(x: torch.Tensor) -> torch.Tensor:
+    """x float32 [rows, K] (K % 256 == 0) -> uint8 [rows, K/256*176]: Q4_K's layout with 32 levels, the fifth
+    bit of value l of sub-block s in bit s of qh[l] (dequantize_row_q5_K, ggml/src/ggml-quants.c:1482-1508)."""
+    R, K = x.shape
+    nb = K // 256
+    xb = x.reshape(R, nb, 8, 32)
+    mn = xb.amin(-1).clamp(max=0.0)
+    mx = xb.amax(-1)
+    scale_f = (mx - mn) / 31.0
+    min_f = -mn
+    d16 = _f16_round(scale_f.amax(-1) / 63.0)
+    dmin16 = _f16_round(min_f.amax(-1) / 63.0)
+    d, dmin = d16.float().unsqueeze(-1), dmin16.float().unsqueeze(-1)
+    sc = torch.where(d > 0, torch.round(scale_f / d.clamp(min=1e-30)), torch.zeros_like(scale_f)).clamp(0, 63)
+    m = torch.where(dmin > 0, torch.round(min_f / dmin.clamp(min=1e-30)), torch.zeros_like(min_f)).clamp(0, 63)
+    eff_s, eff_m = (d * sc).unsqueeze(-1), (dmin * m).unsqueeze(-1)
+    q = torch.where(eff_s > 0, torch.round((xb + eff_m) / eff_s.clamp(min=1e-30)), torch.zeros_like(xb)).clamp(0, 31).to(torch.uint8)
+    sc, m = sc.to(torch.uint8), m.to(torch.uint8)
+    out = torch.empty(R, nb, 176, dtype=torch.uint8, device=x.device)
+    out[..., 0:2] = d16.view(torch.uint8).reshape(R, nb, 2)
+    out[..., 2:4] = dmin16.view(torch.uint8).reshape(R, nb, 2)
+    out[..., 4:8] = sc[..., 0:4] | ((sc[..., 4:8] >> 4) << 6)
+    out[..., 8:12] = m[..., 0:4] | ((m[..., 4:8] >> 4) << 6)
+    out[..., 12:16] = (sc[..., 4:8] & 0xF) | ((m[..., 4:8] & 0xF) << 4)
+    hi = (q >> 4) & 1                                              # [R, nb, 8, 32]
+    qh = torch.zeros(R, nb, 32, dtype=torch.uint8, device=x.device)
+    for sblk in range(8):
+        qh |= hi[:, :, sblk, :] << sblk
+    out[..., 16:48] = qh
+    qq = (q & 0xF).reshape(R, nb, 4, 2, 32)
+    out[..., 48:176] = (qq[..., 0, :] | (qq[..., 1, :] << 4)).reshape(R, nb, 128)
+    return out.reshape(R, nb * 176)
+
+
 def quantize_q6_K(x: torch.Tensor) -> torch.Tensor:
     """x float32 [rows, K] (K % 256 == 0) -> uint8 [rows, K/256*210]."""
     R, K = x.shape
@@ -70,12 +104,12 @@ def quantize_q6_K(x: torch.Tensor) -> torch.Tensor:
     return out.reshape(R, nb * 210)
 
 
-QUANTIZERS = {12: quantize_q4_K, 14: quantize_q6_K}
+QUANTIZERS = {12: quantize_q4_K, 13: quantize_q5_K, 14: quantize_q6_K}
 
 
 def make_tensor(ggml_type: int, ne0: int, ne1: int, seed: int, device: str | torch.device = "cpu", sigma: float = 0.02,
                 rows_per_chunk: int = 8192) -> np.ndarray:
-    """Random-init tensor [ne1 rows, ne0] as host bytes in the given ggml type (0 F32, 12 Q4_K, 14 Q6_K).
+    """Random-init tensor [ne1 rows, ne0] as host bytes in the given ggml type (0 F32, 12 Q4_K, 13 Q5_K, 14 Q6_K).
     1-row F32 tensors (norm weights) are 1 + N(0, sigma)."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)

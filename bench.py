@@ -220,9 +220,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--n-prompt", type=int, default=512, help="prompt tokens per step (smaller only for profiler captures)")
+    ap.add_argument("--n-gen", type=int, default=128, help="generated tokens per step (smaller only for profiler captures)")
+    ap.add_argument("--no-roofline", action="store_true", help="skip the separate mat-vec roofline pass (profiler captures)")
     ap.add_argument("--model", default="8b", choices=["8b", "70b"],
                     help="8b: the configuration the metric is quoted on; 70b: the row-split parity configuration (no CPU baseline)")
     args = ap.parse_args()
+    global N_PROMPT, N_GEN
+    N_PROMPT, N_GEN = args.n_prompt, args.n_gen
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -322,7 +327,7 @@ def main():
         dist.destroy_process_group()
         return
     peak, peak_kind = measured_peaks()
-    algo, gemv_ms, n_mats = gemv_roofline(pkg, m, torch)
+    algo, gemv_ms, n_mats = (0, 1.0, 1) if args.no_roofline else gemv_roofline(pkg, m, torch)
     achieved = algo / (gemv_ms / 1e3) / 1e9
     roofline = {"bound": "hbm", "kernel": "mmvq_kernel (decode mat-vec)", "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
                 "unit": "GB/s", "frac": achieved / peak, "traffic": None, "launches_per_pass": n_mats,

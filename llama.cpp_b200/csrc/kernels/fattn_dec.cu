@@ -84,43 +84,57 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
         float mx[FD_RT];
 #pragma unroll
         for (int rr = 0; rr < FD_RT; ++rr) mx[rr] = -INFINITY;
-        for (int kb = 0; kb < nkeys; kb += 4) {
-            const int kl = kb + kq, key = kw0 + kl;
-            float acc[FD_RT] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (kl < nkeys) {
-                const char * kr = kbase + (int64_t) key * p.k_nb1;
+        // 16 keys per step: each 8-lane group fetches its 4 keys' chunks before any arithmetic, so four
+        // K rows per lane are in flight instead of one
+        for (int kb = 0; kb < nkeys; kb += 16) {
+            uint4 kreg[4][D / 64];
 #pragma unroll
-                for (int c = 0; c < D / 64; ++c) {                // D/8 16-byte chunks per row, 8 lanes -> D/64 chunks each
-                    const int chunk = c * 8 + sub;
-                    const uint4 kv = __ldg((const uint4 *) (kr + chunk * 16));
-                    const __half2 * kh = (const __half2 *) &kv;
+            for (int u = 0; u < 4; ++u) {
+                const int kl = kb + u * 4 + kq;
+                if (kl < nkeys) {
+                    const char * kr = kbase + (int64_t) (kw0 + kl) * p.k_nb1;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 kf = __half22float2(kh[e]);
-                        const int d = chunk * 8 + 2 * e;
+                    for (int c = 0; c < D / 64; ++c) kreg[u][c] = __ldg((const uint4 *) (kr + (c * 8 + sub) * 16));
+                }
+            }
 #pragma unroll
-                        for (int rr = 0; rr < FD_RT; ++rr) acc[rr] += kf.x * qs[rr][d] + kf.y * qs[rr][d + 1];
+            for (int u = 0; u < 4; ++u) {
+                const int kl = kb + u * 4 + kq, key = kw0 + kl;
+                if (kb + u * 4 >= nkeys) break;                   // warp-uniform
+                float acc[FD_RT] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (kl < nkeys) {
+#pragma unroll
+                    for (int c = 0; c < D / 64; ++c) {            // D/8 16-byte chunks per row, 8 lanes -> D/64 chunks each
+                        const int chunk = c * 8 + sub;
+                        const __half2 * kh = (const __half2 *) &kreg[u][c];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 kf = __half22float2(kh[e]);
+                            const int d = chunk * 8 + 2 * e;
+#pragma unroll
+                            for (int rr = 0; rr < FD_RT; ++rr) acc[rr] += kf.x * qs[rr][d] + kf.y * qs[rr][d + 1];
+                        }
                     }
                 }
-            }
-#pragma unroll
-            for (int rr = 0; rr < FD_RT; ++rr) {
-                acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 1);
-                acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 2);
-                acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 4);
-            }
-            if (sub == 0 && kl < nkeys) {
-                float4 sv;
-                float * s4 = (float *) &sv;
 #pragma unroll
                 for (int rr = 0; rr < FD_RT; ++rr) {
-                    float s = acc[rr] * p.scale;
-                    if (p.softcap != 0.0f) s = p.softcap * tanhf(s);
-                    if (mrow[rr]) s += slope[rr] * __half2float(mrow[rr][key]);
-                    s4[rr] = s;
-                    mx[rr] = fmaxf(mx[rr], s);
+                    acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 1);
+                    acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 2);
+                    acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 4);
                 }
-                *(float4 *) ps[warp][kl] = sv;
+                if (sub == 0 && kl < nkeys) {
+                    float4 sv;
+                    float * s4 = (float *) &sv;
+#pragma unroll
+                    for (int rr = 0; rr < FD_RT; ++rr) {
+                        float s = acc[rr] * p.scale;
+                        if (p.softcap != 0.0f) s = p.softcap * tanhf(s);
+                        if (mrow[rr]) s += slope[rr] * __half2float(mrow[rr][key]);
+                        s4[rr] = s;
+                        mx[rr] = fmaxf(mx[rr], s);
+                    }
+                    *(float4 *) ps[warp][kl] = sv;
+                }
             }
         }
         __syncwarp();
@@ -212,7 +226,7 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
             __threadfence();
             const float * base = p.ws + (((int64_t) i3 * p.n_head_kv + hk) * p.n_splits) * R * (D + 2);
             // per (row, split) weights exp(m_s - M) / L, computed once into shared memory (reusing ps)
-            float * wgt = &ps[0][0][0];                               // R * n_splits floats (<= 64 * 512 fits: 4096 floats)
+            float * wgt = &ps[0][0][0];                               // R * n_splits floats, at most the 4096 of ps[] (fd_pick_splits)
             for (int r = threadIdx.x; r < R; r += blockDim.x) {
                 float M = -INFINITY;
                 for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, base[((int64_t) s * R + r) * (D + 2) + D]);
@@ -260,20 +274,22 @@ bool fattn_dec_applicable(const TensorD & q, const TensorD & k, const TensorD & 
     return true;
 }
 
-static int fd_pick_splits(int64_t n_head_kv_total, int64_t n_kv, int sm_count) {
-    int64_t want = ((int64_t) sm_count * 2 + n_head_kv_total - 1) / n_head_kv_total;
-    const int64_t max_by_kv = (n_kv + 63) / 64;                       // at least 64 keys per CTA
+static int fd_pick_splits(int64_t n_head_kv_total, int64_t n_kv, int sm_count, int64_t R) {
+    int64_t want = ((int64_t) sm_count * 4 + n_head_kv_total - 1) / n_head_kv_total;
+    const int64_t max_by_kv = (n_kv + 63) / 64;                       // at least 64 keys per CTA (16 per warp: one score step)
     int64_t s = want < max_by_kv ? want : max_by_kv;
     const int64_t min_by_cap = (n_kv + FD_WARPS * FD_MAX_KEYS_PER_WARP - 1) / (FD_WARPS * FD_MAX_KEYS_PER_WARP);
     if (s < min_by_cap) s = min_by_cap;
-    if (s > 64) s = s > min_by_cap ? (min_by_cap > 64 ? min_by_cap : 64) : s;
+    if (s > 128) s = s > min_by_cap ? (min_by_cap > 128 ? min_by_cap : 128) : s;
+    const int64_t cap_by_wgt = (FD_WARPS * FD_MAX_KEYS_PER_WARP * FD_RT) / (R > 0 ? R : 1);   // merge weights live in ps[]
+    if (s > cap_by_wgt) s = cap_by_wgt > min_by_cap ? cap_by_wgt : min_by_cap;
     if (s < 1) s = 1;
     return (int) s;
 }
 
 size_t fattn_dec_workspace_bytes(const TensorD & q, const TensorD & k, int sm_count) {
-    const int splits = fd_pick_splits(k.ne[2] * q.ne[3], k.ne[1], sm_count);
     const int64_t R = (q.ne[2] / k.ne[2]) * q.ne[1];
+    const int splits = fd_pick_splits(k.ne[2] * q.ne[3], k.ne[1], sm_count, R);
     return (size_t) q.ne[3] * k.ne[2] * splits * R * (q.ne[0] + 2) * 4 + 256;
 }
 
@@ -287,7 +303,7 @@ cudaError_t launch_fattn_dec(const TensorD & q, const TensorD & k, const TensorD
     p.dst = (float *) dst.data; p.ws = (float *) partials; p.tickets = (unsigned *) tickets;
     p.n_q = (int) q.ne[1]; p.n_kv = (int) k.ne[1]; p.n_head = (int) q.ne[2]; p.n_head_kv = (int) k.ne[2];
     p.gqa = (int) (q.ne[2] / k.ne[2]); p.q3_per_k3 = (int) (q.ne[3] / k.ne[3]);
-    p.n_splits = fd_pick_splits(k.ne[2] * q.ne[3], k.ne[1], c.sm_count);
+    p.n_splits = fd_pick_splits(k.ne[2] * q.ne[3], k.ne[1], c.sm_count, (int64_t) p.gqa * p.n_q);
     p.kv_per_split = (int) ((k.ne[1] + p.n_splits - 1) / p.n_splits);
     p.scale = fp.scale; p.softcap = fp.logit_softcap; p.max_bias = fp.max_bias;
     if (p.softcap != 0.0f) p.scale /= p.softcap;

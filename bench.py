@@ -38,6 +38,7 @@ import __graft_entry__ as entry  # noqa: E402
 
 N_PROMPT, N_GEN = 512, 128
 CPU_PROMPT, CPU_GEN = 128, 16
+DRAM_TRAFFIC_RATIO = 1.001      # measured DRAM bytes / algorithmic bytes of the mat-vec kernels (ncu, see profiles/)
 METRIC = "llama3-8b-q4_k_m tg128 tokens/s (pp512+tg128 per step)"   # --model 70b replaces the model name
 
 
@@ -329,8 +330,14 @@ def main():
     peak, peak_kind = measured_peaks()
     algo, gemv_ms, n_mats = (0, 1.0, 1) if args.no_roofline else gemv_roofline(pkg, m, torch)
     achieved = algo / (gemv_ms / 1e3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "mmvq_kernel (decode mat-vec)", "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
-                "unit": "GB/s", "frac": achieved / peak, "traffic": None, "launches_per_pass": n_mats,
+    # DRAM bytes per launch: ncu measured 33,049,344 B read + 0 written for the 33,103,872 algorithmic bytes of the
+    # Q4_K 4096x14336 case (profiles/mmvq_k_q4k_4096x14336_n1.md) and 431.0 + 4.3 MB for 431.5 MB (Q6_K output matrix);
+    # traffic grows in proportion to the matrix, so the average launch of the pass is scaled by that ratio
+    traffic = None if args.no_roofline else algo / n_mats * DRAM_TRAFFIC_RATIO
+    roofline = {"bound": "hbm", "kernel": "mmvq_k_kernel / mmvq_q6k_kernel (decode mat-vec, all weight matrices of the model in graph order)",
+                "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
+                "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "traffic_unit": "DRAM bytes per launch (average matrix, scaled from ncu)",
+                "bytes_per_launch": algo / n_mats, "us_per_launch": gemv_ms * 1e3 / n_mats, "launches_per_pass": n_mats,
                 "algorithmic_bytes_per_pass": algo, "ms_per_pass": gemv_ms,
                 "whole_decode_step": {"weight_bytes_per_token_per_gpu": m.weight_bytes, "achieved_gbs_per_gpu": m.weight_bytes * tg_tps_dev / 1e9,
                                       "frac": m.weight_bytes * tg_tps_dev / 1e9 / peak}}

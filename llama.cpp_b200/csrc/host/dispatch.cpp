@@ -358,8 +358,21 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
             const size_t ws = fattn_workspace_bytes(qd, kd, lc.sm_count);
             void * wsp = ws ? ctx->get_scratch(ws) : nullptr;
             if (ctx->capture_failed) return fail();
+            // decode: when the attention output goes straight into a quantized MUL_MAT (wo), the kernel also
+            // writes its int8 activation blocks (one head row of 128 values = one block)
+            void * act = nullptr;
+            if (ctx->use_fusion && lc.fa_tickets && a->ne[0] == 128 && a->ne[3] == 1 && fattn_dec_applicable(qd, kd, vd, mask ? &md : nullptr)) {
+                const int j = next_exec(g, i + 1);
+                const ggml_tensor * mm = j >= 0 ? g->nodes[j] : nullptr;
+                if (mm && mm->op == GGML_OP_MUL_MAT && mm->src[1]->data == dst->data && mmvq_type_supported(mm->src[0]->type) &&
+                    act_cacheable(mm->src[1]) && mm->src[1]->ne[0] == dst->ne[0] * dst->ne[1] && mm->src[1]->ne[1] == dst->ne[2]) {
+                    BackendCtx::ActEntry * e = ctx->act_cache_take(dst->data, mm->src[1]->ne[0], mm->src[1]->ne[1]);
+                    if (!e) return fail();
+                    act = e->q;
+                }
+            }
             int nk = 1;
-            RUN0(launch_fattn(qd, kd, vd, mask ? &md : nullptr, dd, fp, wsp, lc, &nk));
+            RUN0(launch_fattn(qd, kd, vd, mask ? &md : nullptr, dd, fp, wsp, lc, &nk, act));
             ctx->n_launches += nk - 1;                               // second kernel: split-KV combine or mask-tile flags
             return 1;
         }

@@ -188,12 +188,12 @@ static cudaError_t fattn_launch_d(const FaK & p, int64_t rows, int n3, const Lau
 }
 
 cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
-                         const FattnParams & fp, void * workspace, const LaunchCtx & c, int * n_kernels) {
+                         const FattnParams & fp, void * workspace, const LaunchCtx & c, int * n_kernels, void * act128_out) {
     const int64_t D = q.ne[0], rows = q.ne[1] * q.ne[2] * q.ne[3];
     if (rows == 0) return cudaSuccess;
     if (c.fa_tickets && fattn_dec_applicable(q, k, v, mask)) {
         if (n_kernels) *n_kernels = 1;
-        return launch_fattn_dec(q, k, v, mask, dst, fp, c.fa_tickets, workspace, c);
+        return launch_fattn_dec(q, k, v, mask, dst, fp, c.fa_tickets, workspace, c, act128_out);
     }
     if (fattn_mma_applicable(q, k, v, mask)) {
         if (n_kernels) *n_kernels = mask ? 2 : 1;

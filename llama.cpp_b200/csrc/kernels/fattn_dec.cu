@@ -30,7 +30,21 @@ struct FdParams {
     int n_q, n_kv, n_head, n_head_kv, gqa, q3_per_k3;
     int n_splits, kv_per_split;
     float scale, softcap, max_bias, m0, m1; int n_head_log2;
+    blk_act128 * act_out;    // optional (D = 128, one query batch): int8 blocks of dst for the MUL_MAT that reads it
 };
+
+// One output row (query iq, head) of D = 128 values is exactly one blk_act128 of the [n_head * D] activation
+// column iq; thread d holds value v.  Same arithmetic as quantize_act128_kernel: a scale per 32 values (a warp).
+__device__ __forceinline__ void fd_emit_act(blk_act128 * blk, int d, float v) {
+    const float amax = warp_max(fabsf(v));
+    const float dd = amax / 127.0f, id = amax > 0.0f ? 127.0f / amax : 0.0f;
+    const int q = __float2int_rn(v * id);
+    int qsum = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
+    blk->q[d] = (int8_t) q;
+    if ((d & 31) == 0) blk->ds[d >> 5] = make_float2(dd, dd * (float) qsum);
+}
 
 template <int D>
 __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams p) {
@@ -208,7 +222,9 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
             }
             if (p.n_splits == 1) {
                 const int iq = r / p.gqa, head = hk * p.gqa + r % p.gqa;
-                p.dst[(((int64_t) i3 * p.n_q + iq) * p.n_head + head) * D + d] = acc / L;
+                const float val = acc / L;
+                p.dst[(((int64_t) i3 * p.n_q + iq) * p.n_head + head) * D + d] = val;
+                if (D == 128 && p.act_out) fd_emit_act(p.act_out + (int64_t) iq * p.n_head + head, d, val);   // r is uniform per pass
             } else {
                 part[(int64_t) r * (D + 2) + d] = acc;
                 if (d == 0) { part[(int64_t) r * (D + 2) + D] = M; part[(int64_t) r * (D + 2) + D + 1] = L; }
@@ -252,7 +268,9 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
                 }
                 for (; s < p.n_splits; ++s) acc0 += base[((int64_t) s * R + r) * (D + 2) + d] * wgt[r * p.n_splits + s];
                 const int iq = r / p.gqa, head = hk * p.gqa + r % p.gqa;
-                p.dst[(((int64_t) i3 * p.n_q + iq) * p.n_head + head) * D + d] = (acc0 + acc1) + (acc2 + acc3);
+                const float val = (acc0 + acc1) + (acc2 + acc3);
+                p.dst[(((int64_t) i3 * p.n_q + iq) * p.n_head + head) * D + d] = val;
+                if (D == 128 && p.act_out) fd_emit_act(p.act_out + (int64_t) iq * p.n_head + head, d, val);
             }
             if (threadIdx.x == 0) p.tickets[i3 * p.n_head_kv + hk] = 0;      // ready for the next launch
         }
@@ -294,8 +312,9 @@ size_t fattn_dec_workspace_bytes(const TensorD & q, const TensorD & k, int sm_co
 }
 
 cudaError_t launch_fattn_dec(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
-                             const FattnParams & fp, void * tickets, void * partials, const LaunchCtx & c) {
+                             const FattnParams & fp, void * tickets, void * partials, const LaunchCtx & c, void * act128_out) {
     FdParams p = {};
+    p.act_out = (q.ne[0] == 128 && q.ne[3] == 1) ? (blk_act128 *) act128_out : nullptr;
     p.q = (const char *) q.data; p.q_nb1 = q.nb[1]; p.q_nb2 = q.nb[2]; p.q_nb3 = q.nb[3];
     p.k = (const char *) k.data; p.k_nb1 = k.nb[1]; p.k_nb2 = k.nb[2]; p.k_nb3 = k.nb[3];
     p.v = (const char *) v.data; p.v_nb1 = v.nb[1]; p.v_nb2 = v.nb[2]; p.v_nb3 = v.nb[3];

@@ -145,8 +145,9 @@ cudaError_t launch_fattn_mma(const TensorD & q, const TensorD & k, const TensorD
 bool        fattn_dec_applicable(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask);
 size_t      fattn_dec_workspace_bytes(const TensorD & q, const TensorD & k, int sm_count);
 cudaError_t launch_fattn_dec(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
-                             const FattnParams & fp, void * tickets, void * partials, const LaunchCtx & c);
+                             const FattnParams & fp, void * tickets, void * partials, const LaunchCtx & c, void * act128_out = nullptr);
 cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
-                         const FattnParams & fp, void * workspace, const LaunchCtx & c, int * n_kernels = nullptr);
+                         const FattnParams & fp, void * workspace, const LaunchCtx & c, int * n_kernels = nullptr,
+                         void * act128_out = nullptr);   // honoured only when fattn_dec_applicable() (blk_act128 of dst, D = 128)
 
 }  // namespace b200

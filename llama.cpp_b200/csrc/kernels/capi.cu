@@ -176,8 +176,15 @@ static void fa_descs(const float * q, int64_t q_nb1, int64_t q_nb2, const void *
 API size_t b200_flash_attn_scratch_bytes(int64_t D, int64_t n_q, int64_t n_head, int64_t n_kv) {
     int dev = 0, sm = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev); else cudaGetLastError();
-    TensorD qd = desc(nullptr, T_F32, D, n_q, n_head, 0, 0), kd = desc(nullptr, T_F16, D, n_kv, 1, 0, 0);
-    return fattn_workspace_bytes(qd, kd, sm);
+    // the number of KV heads is not an argument: take the largest need over every grouping of the query heads
+    size_t need = 0;
+    for (int64_t hkv = 1; hkv <= n_head; ++hkv) {
+        if (n_head % hkv) continue;
+        TensorD qd = desc(nullptr, T_F32, D, n_q, n_head, 0, 0), kd = desc(nullptr, T_F16, D, n_kv, hkv, 0, 0);
+        const size_t b = fattn_workspace_bytes(qd, kd, sm);
+        if (b > need) need = b;
+    }
+    return need;
 }
 
 API int b200_flash_attn(const float * q, int64_t q_nb1, int64_t q_nb2, const void * k, int64_t k_nb1, int64_t k_nb2,

@@ -73,14 +73,20 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
     for (int r0 = 0; r0 < R; r0 += FD_RT) {
         // rows r0 .. r0+3: row r = iq * gqa + hg  ->  query iq, head hk * gqa + hg
         __syncthreads();
-        for (int i = threadIdx.x; i < FD_RT * D; i += blockDim.x) {
-            const int rr = i / D, d = i % D, r = r0 + rr;
-            float v = 0.0f;
-            if (r < R) {
-                const int iq = r / p.gqa, head = hk * p.gqa + r % p.gqa;
-                v = *(const float *) (p.q + (int64_t) iq * p.q_nb1 + (int64_t) head * p.q_nb2 + (int64_t) i3 * p.q_nb3 + d * 4);
+        {
+            constexpr int NT = FD_WARPS * 32, QI = FD_RT * D / NT;      // all loads are issued before the first store
+            float qv[QI];
+#pragma unroll
+            for (int it = 0; it < QI; ++it) {
+                const int i = threadIdx.x + it * NT, rr = i / D, d = i % D, r = r0 + rr;
+                qv[it] = 0.0f;
+                if (r < R) {
+                    const int iq = r / p.gqa, head = hk * p.gqa + r % p.gqa;
+                    qv[it] = *(const float *) (p.q + (int64_t) iq * p.q_nb1 + (int64_t) head * p.q_nb2 + (int64_t) i3 * p.q_nb3 + d * 4);
+                }
             }
-            qs[rr][d] = v;
+#pragma unroll
+            for (int it = 0; it < QI; ++it) { const int i = threadIdx.x + it * NT; qs[i / D][i % D] = qv[it]; }
         }
         __syncthreads();
 
@@ -102,6 +108,7 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
         // K rows per lane are in flight instead of one
         for (int kb = 0; kb < nkeys; kb += 16) {
             uint4 kreg[4][D / 64];
+            __half mval[4][FD_RT];                                // mask values of the same keys, fetched with them
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int kl = kb + u * 4 + kq;
@@ -109,11 +116,13 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
                     const char * kr = kbase + (int64_t) (kw0 + kl) * p.k_nb1;
 #pragma unroll
                     for (int c = 0; c < D / 64; ++c) kreg[u][c] = __ldg((const uint4 *) (kr + (c * 8 + sub) * 16));
+#pragma unroll
+                    for (int rr = 0; rr < FD_RT; ++rr) mval[u][rr] = mrow[rr] ? mrow[rr][kw0 + kl] : __float2half(0.0f);
                 }
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int kl = kb + u * 4 + kq, key = kw0 + kl;
+                const int kl = kb + u * 4 + kq;
                 if (kb + u * 4 >= nkeys) break;                   // warp-uniform
                 float acc[FD_RT] = {0.0f, 0.0f, 0.0f, 0.0f};
                 if (kl < nkeys) {
@@ -143,7 +152,7 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
                     for (int rr = 0; rr < FD_RT; ++rr) {
                         float s = acc[rr] * p.scale;
                         if (p.softcap != 0.0f) s = p.softcap * tanhf(s);
-                        if (mrow[rr]) s += slope[rr] * __half2float(mrow[rr][key]);
+                        if (mrow[rr]) s += slope[rr] * __half2float(mval[u][rr]);
                         s4[rr] = s;
                         mx[rr] = fmaxf(mx[rr], s);
                     }
@@ -241,19 +250,31 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
         if (ticket_sh == (unsigned) p.n_splits - 1) {
             __threadfence();
             const float * base = p.ws + (((int64_t) i3 * p.n_head_kv + hk) * p.n_splits) * R * (D + 2);
-            // per (row, split) weights exp(m_s - M) / L, computed once into shared memory (reusing ps)
-            float * wgt = &ps[0][0][0];                               // R * n_splits floats, at most the 4096 of ps[] (fd_pick_splits)
-            for (int r = threadIdx.x; r < R; r += blockDim.x) {
+            // per (row, split) weights exp(m_s - M) / L in shared memory (reusing ps): all (max, sum) pairs are
+            // fetched in one parallel pass, then one warp per row reduces over the splits
+            float * wgt = &ps[0][0][0];                               // R * n_splits floats, at most half of ps[] (fd_pick_splits)
+            float * wl  = wgt + FD_WARPS * FD_MAX_KEYS_PER_WARP * FD_RT / 2;   // the sums, same indexing, in the upper half
+            const int RS = R * p.n_splits;
+            for (int idx = threadIdx.x; idx < RS; idx += blockDim.x) {
+                const int s_ = idx / R, r = idx - s_ * R;
+                const float * ps_ = base + ((int64_t) s_ * R + r) * (D + 2);
+                wgt[r * p.n_splits + s_] = ps_[D];
+                wl[r * p.n_splits + s_]  = ps_[D + 1];
+            }
+            __syncthreads();
+            for (int r = warp; r < R; r += FD_WARPS) {
                 float M = -INFINITY;
-                for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, base[((int64_t) s * R + r) * (D + 2) + D]);
+                for (int s_ = lane; s_ < p.n_splits; s_ += 32) M = fmaxf(M, wgt[r * p.n_splits + s_]);
+                M = warp_max(M);
                 float L = 0.0f;
-                for (int s = 0; s < p.n_splits; ++s) {
-                    const float * ps_ = base + ((int64_t) s * R + r) * (D + 2);
-                    const float f = (ps_[D] == -INFINITY) ? 0.0f : expf(ps_[D] - M);
-                    wgt[r * p.n_splits + s] = f; L += ps_[D + 1] * f;
+                for (int s_ = lane; s_ < p.n_splits; s_ += 32) {
+                    const float m_s = wgt[r * p.n_splits + s_];
+                    const float f = (m_s == -INFINITY) ? 0.0f : expf(m_s - M);
+                    wgt[r * p.n_splits + s_] = f; L += wl[r * p.n_splits + s_] * f;
                 }
+                L = warp_sum(L);
                 const float inv = 1.0f / L;
-                for (int s = 0; s < p.n_splits; ++s) wgt[r * p.n_splits + s] *= inv;
+                for (int s_ = lane; s_ < p.n_splits; s_ += 32) wgt[r * p.n_splits + s_] *= inv;
             }
             __syncthreads();
             for (int i = threadIdx.x; i < R * D; i += blockDim.x) {
@@ -299,7 +320,7 @@ static int fd_pick_splits(int64_t n_head_kv_total, int64_t n_kv, int sm_count, i
     const int64_t min_by_cap = (n_kv + FD_WARPS * FD_MAX_KEYS_PER_WARP - 1) / (FD_WARPS * FD_MAX_KEYS_PER_WARP);
     if (s < min_by_cap) s = min_by_cap;
     if (s > 128) s = s > min_by_cap ? (min_by_cap > 128 ? min_by_cap : 128) : s;
-    const int64_t cap_by_wgt = (FD_WARPS * FD_MAX_KEYS_PER_WARP * FD_RT) / (R > 0 ? R : 1);   // merge weights live in ps[]
+    const int64_t cap_by_wgt = (FD_WARPS * FD_MAX_KEYS_PER_WARP * FD_RT / 2) / (R > 0 ? R : 1);   // merge weights and sums share ps[]
     if (s > cap_by_wgt) s = cap_by_wgt > min_by_cap ? cap_by_wgt : min_by_cap;
     if (s < 1) s = 1;
     return (int) s;

@@ -88,6 +88,36 @@ def test_mul_mat_llama_shapes(b200, oracle, golden, qt, k, m, n):
     assert oracle.nmse(2.0 * got, got2) <= 1e-9
 
 
+@pytest.mark.parametrize("qt,k,m", [("q4_0", 4096, 4096), ("q4_K", 4096, 14336), ("q6_K", 14336, 4096), ("q8_0", 4096, 4096), ("q4_K", 4096, 4096)])
+@pytest.mark.parametrize("n", [32, 128, 512])
+def test_mul_mat_llama_shapes_prefill(b200, oracle, golden, qt, k, m, n):
+    """The batch sizes that take the tensor-core GEMM, at full Llama-3-8B shapes; the oracle (scalar C) is
+    evaluated on a sample of weight rows and token columns."""
+    w = quantized_weights(oracle, golden, qt, m, k, seed=0)
+    x = np.random.default_rng(20 + n).standard_normal((n, k)).astype(np.float32)
+    got = b200.mul_mat_q(qt, w, x)
+    assert got.shape == (n, m) and np.isfinite(got).all()
+    rows = np.random.default_rng(4).choice(m, 48, replace=False)
+    cols = np.random.default_rng(5).choice(n, 16, replace=False)
+    want = oracle.mul_mat(qt, w[rows], x[cols])
+    assert oracle.nmse(want, got[np.ix_(cols, rows)]) <= NMSE_MM
+    # every token column is independent of its neighbours: the same column alone gives the same values
+    alone = b200.mul_mat_q(qt, w, x[cols[:1]])
+    assert oracle.nmse(alone[0], got[cols[0]]) <= NMSE_MM
+
+
+@pytest.mark.parametrize("qt", ["q4_K", "q6_K", "q8_0"])
+def test_mul_mat_vocab_shape(b200, oracle, golden, qt):
+    """[K=4096, M=128256], the output matrix: one column, oracle on a sample of rows incl. the first and last."""
+    k, m = 4096, 128256
+    block = quantized_weights(oracle, golden, qt, 4096, k, seed=2)       # 4096 distinct rows, repeated down the matrix
+    w = np.ascontiguousarray(np.tile(block, (32, 1))[:m])
+    x = np.random.default_rng(31).standard_normal((1, k)).astype(np.float32)
+    got = b200.mul_mat_q(qt, w, x)
+    rows = np.concatenate([[0, 1, m - 2, m - 1], np.random.default_rng(6).choice(m, 92, replace=False)])
+    assert oracle.nmse(oracle.mul_mat(qt, w[rows], x), got[:, rows]) <= NMSE_MM
+
+
 def test_mul_mat_zero_and_edge_inputs(b200, oracle, golden):
     w = golden["mul_mat.w.q4_K"]
     x = np.zeros((2, 512), np.float32)
@@ -124,6 +154,24 @@ def test_flash_attn_vs_oracle(b200, oracle, n_q, n_kv, d):
     assert oracle.nmse(oracle.flash_attn(q, k, v, mask, 1.0 / np.sqrt(d)), got) <= NMSE_MM
     got = b200.flash_attn(q, k, v, None, 1.0 / np.sqrt(d), softcap=10.0)
     assert oracle.nmse(oracle.flash_attn(q, k, v, None, 1.0 / np.sqrt(d), softcap=10.0), got) <= NMSE_MM
+
+
+@pytest.mark.parametrize("n_kv", [512, 4096])
+def test_flash_attn_prefill_512_queries(b200, oracle, n_kv):
+    """Config-3 prefill shape (32 Q heads / 8 KV heads, D=128, 512 queries, causal): the oracle is evaluated
+    for one KV head's group of query heads on a sample of query rows."""
+    rng = np.random.default_rng(n_kv)
+    nh, nhkv, d, n_q = 32, 8, 128, 512
+    q = rng.standard_normal((nh, n_q, d)).astype(np.float32)
+    k = rng.standard_normal((nhkv, n_kv, d)).astype(np.float16)
+    v = rng.standard_normal((nhkv, n_kv, d)).astype(np.float16)
+    mask = causal_mask(n_q, n_kv)
+    got = b200.flash_attn(q, k, v, mask, 1.0 / np.sqrt(d))           # [n_q, n_head, d]
+    assert np.isfinite(got).all()
+    rows = np.sort(np.random.default_rng(7).choice(n_q, 24, replace=False))
+    heads = [4, 5, 6, 7]                                             # the group of KV head 1
+    want = oracle.flash_attn(q[heads][:, rows], k[1:2], v[1:2], mask[rows], 1.0 / np.sqrt(d))
+    assert oracle.nmse(want, got[rows][:, heads]) <= NMSE_MM
 
 
 def test_flash_attn_decode_32k_properties(b200, oracle):

@@ -53,6 +53,12 @@ int    b200_mul_mat_q(int type, const void * W, int64_t w_row_stride_bytes, int6
  * quantize_q8_1, ggml/src/ggml-cuda/quantize.cu:4-38) writing b200_act_bytes(K, N) bytes, and the mat-vec
  * kernel on activations quantized earlier (mul_mat_vec_q, ggml/src/ggml-cuda/mmvq.cu:50-130).          */
 size_t b200_act_bytes(int64_t K, int64_t N);
+/* Programmatic dependent launch for the device-pointer entry points (off by default; the ggml backend
+ * has it on by default): the mat-vec kernels request their first weight rows before waiting for the kernel
+ * launched just before them on the stream (griddepcontrol), so consecutive launches overlap head and tail.
+ * Only turn it on when no weight operand is written by the kernel launched immediately before it on the
+ * same stream.  No reference counterpart. */
+void   b200_set_dependent_launch(int on);
 int    b200_quantize_act(const float * X, int64_t x_col_stride_elems, int64_t K, int64_t N, void * xq, void * stream);
 int    b200_mul_mat_vec_q(int type, const void * W, int64_t w_row_stride_bytes, int64_t M, int64_t K,
                           const void * xq, int64_t N, float * dst, int64_t dst_col_stride_elems, void * stream);

@@ -27,7 +27,7 @@ BLOCK = {"f32": (1, 4), "f16": (1, 2), "q4_0": (32, 18), "q4_1": (32, 20), "q5_0
 EXPORTS = [
     "b200_device_count", "b200_last_error", "b200_row_size",
     "b200_mul_mat_q_scratch_bytes", "b200_mul_mat_q", "b200_mul_mat_q_host",
-    "b200_act_bytes", "b200_quantize_act", "b200_mul_mat_vec_q",
+    "b200_act_bytes", "b200_quantize_act", "b200_mul_mat_vec_q", "b200_set_dependent_launch",
     "b200_mul_mat_q_noalloc", "b200_noalloc_last_error",
     "b200_flash_attn_scratch_bytes", "b200_flash_attn", "b200_flash_attn_host",
     "b200_dequantize_rows_host", "b200_get_rows_host", "b200_quantize_rows_host", "b200_f32_to_f16_host",

@@ -216,7 +216,11 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
     MmvqArgs a = {};
     a.type = W->type; a.W = W->data; a.w_nb1 = W->nb[1]; a.w_nb2 = W->nb[2]; a.w_nb3 = W->nb[3];
     a.Xq = xq; a.M = (int) M; a.K = (int) K;
-    a.status = lc.status; a.sm_count = lc.sm_count; a.device = lc.device; a.use_pdl = lc.use_pdl;
+    a.status = lc.status; a.sm_count = lc.sm_count; a.device = lc.device;
+    // the mat-vec kernels fetch weights before they wait for their predecessor: only safe when the weights
+    // are not produced inside this graph
+    const bool w_is_leaf = W->op == GGML_OP_NONE && (!W->view_src || W->view_src->op == GGML_OP_NONE);
+    a.use_pdl = w_is_leaf ? lc.use_pdl : 0;
     for (int i = 0; i < n_extra; ++i) {             // grouped launch: more weight matrices on the same activations
         a.extra_W[i] = extra[i]->src[0]->data; a.extra_dst[i] = (float *) extra[i]->data;
         a.extra_dst_nb1[i] = extra[i]->nb[1]; a.extra_M[i] = (int) extra[i]->src[0]->ne[1];

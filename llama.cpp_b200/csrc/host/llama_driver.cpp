@@ -71,8 +71,12 @@ struct b200_llama {
 
     // inputs / outputs of the current graph
     ggml_tensor * inp_tokens = nullptr, * inp_pos = nullptr, * inp_mask = nullptr, * inp_out_ids = nullptr, * logits = nullptr;
-    std::vector<float> mask_host;
-    std::vector<int32_t> pos_host;
+    // host staging of the per-call inputs and of the logits: page-locked on the B200 backend, so the copies
+    // inside b200_llama_decode are true asynchronous DMA transfers
+    float * mask_host = nullptr; int32_t * pos_host = nullptr, * tok_host = nullptr; float * logits_stage = nullptr;
+    size_t mask_cap = 0;
+    bool host_pinned = false;
+    void host_free(void * q) { if (!q) return; if (host_pinned) cudaFreeHost(q); else free(q); }
 
     int last_n_nodes = 0; double last_ms = 0.0; size_t weight_bytes = 0, arena_bytes = 0;
 
@@ -396,6 +400,19 @@ API b200_llama * b200_llama_create(void * reg_, int32_t device_index, const b200
     m->rg_layer[0].base = cbase + fl + sg; m->rg_layer[0].cap = sl;
     m->rg_layer[1].base = cbase + fl + sg + sl; m->rg_layer[1].cap = sl;
     m->arena_bytes = fl + sg + 2 * sl;
+    {
+        const size_t n_pad = ((size_t) cfg->n_ubatch + 63) / 64 * 64;
+        m->mask_cap = (size_t) cfg->n_ctx * n_pad;
+        void * probe = nullptr;
+        m->host_pinned = m->is_b200 && cudaMallocHost(&probe, 64) == cudaSuccess;
+        if (probe) cudaFreeHost(probe); else cudaGetLastError();
+        auto take = [&](size_t n) -> void * { void * q = nullptr; if (m->host_pinned) { if (cudaMallocHost(&q, n) != cudaSuccess) { cudaGetLastError(); q = nullptr; } } else q = malloc(n); return q; };
+        m->mask_host = (float *) take(m->mask_cap * 4);
+        m->pos_host = (int32_t *) take((size_t) cfg->n_ubatch * 4);
+        m->tok_host = (int32_t *) take((size_t) cfg->n_ubatch * 4);
+        m->logits_stage = (float *) take((size_t) cfg->n_vocab * 4);
+        if (!m->mask_host || !m->pos_host || !m->tok_host || !m->logits_stage) { g_error = "host staging allocation failed"; b200_llama_free(m.release()); return nullptr; }
+    }
     return m.release();
 }
 
@@ -405,6 +422,7 @@ API void b200_llama_free(b200_llama * m) {
     for (int r = 0; r < m->n_ranks; ++r) if (r != m->rank && m->peer_arena[r]) cudaIpcCloseMemHandle(m->peer_arena[r]);
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
+    m->host_free(m->mask_host); m->host_free(m->pos_host); m->host_free(m->tok_host); m->host_free(m->logits_stage);
     free_buffer(m->buf_c); free_buffer(m->buf_kv); free_buffer(m->buf_w);
     m->backend->iface.free(m->backend);
     delete m;
@@ -441,18 +459,18 @@ API int32_t b200_llama_decode(b200_llama * m, const int32_t * tokens, int32_t n_
     // inputs: positions, causal mask (0 where key <= query position, -inf elsewhere and in pad rows;
     // llama_set_inputs, src/llama-context.cpp:129-203), index of the output row
     const int64_t n_kv = m->inp_mask->ne[0], n_pad = m->inp_mask->ne[1];
-    m->pos_host.resize((size_t) n_tokens);
-    for (int i = 0; i < n_tokens; ++i) m->pos_host[(size_t) i] = pos0 + i;
-    m->mask_host.assign((size_t) (n_kv * n_pad), -INFINITY);
+    for (int i = 0; i < n_tokens; ++i) { m->pos_host[i] = pos0 + i; m->tok_host[i] = tokens[i]; }
+    const size_t mask_n = (size_t) (n_kv * n_pad);
+    for (size_t i = 0; i < mask_n; ++i) m->mask_host[i] = -INFINITY;
     for (int i = 0; i < n_tokens; ++i) {
-        float * row = m->mask_host.data() + (size_t) i * (size_t) n_kv;
+        float * row = m->mask_host + (size_t) i * (size_t) n_kv;
         const int lim = std::min<int64_t>(n_kv, pos0 + i + 1);
         for (int j = 0; j < lim; ++j) row[j] = 0.0f;
     }
     const int32_t out_id = n_tokens - 1;
-    upload(m, m->inp_tokens, tokens, (size_t) n_tokens * 4);
-    upload(m, m->inp_pos, m->pos_host.data(), (size_t) n_tokens * 4);
-    upload(m, m->inp_mask, m->mask_host.data(), m->mask_host.size() * 4);
+    upload(m, m->inp_tokens, m->tok_host, (size_t) n_tokens * 4);
+    upload(m, m->inp_pos, m->pos_host, (size_t) n_tokens * 4);
+    upload(m, m->inp_mask, m->mask_host, mask_n * 4);
     upload(m, m->inp_out_ids, &out_id, 4);
 
     const auto t0 = std::chrono::steady_clock::now();
@@ -461,10 +479,11 @@ API int32_t b200_llama_decode(b200_llama * m, const int32_t * tokens, int32_t n_
     if (m->is_b200) B200_CUDA_CHECK(cudaEventRecord(m->ev1, m->stream));
     if (st != GGML_STATUS_SUCCESS) { g_error = "graph_compute failed"; return -2; }
     if (logits_host) {
-        if (m->backend->iface.get_tensor_async) m->backend->iface.get_tensor_async(m->backend, m->logits, logits_host, 0, (size_t) m->cfg.n_vocab * 4);
-        else m->logits->buffer->iface.get_tensor(m->logits->buffer, m->logits, logits_host, 0, (size_t) m->cfg.n_vocab * 4);
+        if (m->backend->iface.get_tensor_async) m->backend->iface.get_tensor_async(m->backend, m->logits, m->logits_stage, 0, (size_t) m->cfg.n_vocab * 4);
+        else m->logits->buffer->iface.get_tensor(m->logits->buffer, m->logits, m->logits_stage, 0, (size_t) m->cfg.n_vocab * 4);
     }
     if (m->backend->iface.synchronize) m->backend->iface.synchronize(m->backend);
+    if (logits_host) memcpy(logits_host, m->logits_stage, (size_t) m->cfg.n_vocab * 4);
     m->last_n_nodes = m->graph.n_nodes;
     if (m->n_ranks > 1 && m->status_fn) {              // a rank that stopped answering shows up as a barrier that gave up
         const int dev_status = m->status_fn(m->backend);

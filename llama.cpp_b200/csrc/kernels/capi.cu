@@ -45,6 +45,7 @@ API size_t b200_row_size(int type, int64_t k) {
 struct ApiDev { int sm_count = 0; int * status = nullptr; unsigned * tickets = nullptr; bool ready = false; };
 static ApiDev g_dev[64];
 
+static int g_flat_pdl = 0;      // programmatic dependent launch for the device-pointer entry points (b200_set_dependent_launch)
 static int get_ctx(void * stream, LaunchCtx & lc) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return fail(B200_E_NO_DEVICE, "no CUDA device"); }
@@ -60,9 +61,11 @@ static int get_ctx(void * stream, LaunchCtx & lc) {
         CK(cudaMemset(d.tickets, 0, sizeof(unsigned) * FATTN_DEC_TICKETS));
         d.ready = true;
     }
-    lc.stream = (cudaStream_t) stream; lc.device = dev; lc.sm_count = d.sm_count; lc.status = d.status; lc.use_pdl = 0; lc.fa_tickets = d.tickets;
+    lc.stream = (cudaStream_t) stream; lc.device = dev; lc.sm_count = d.sm_count; lc.status = d.status; lc.use_pdl = g_flat_pdl; lc.fa_tickets = d.tickets;
     return 0;
 }
+API void b200_set_dependent_launch(int on) { g_flat_pdl = on ? 1 : 0; }
+
 static int check_status(const LaunchCtx & lc) {
     int st = 0;
     CK(cudaMemcpy(&st, lc.status, sizeof(int), cudaMemcpyDeviceToHost));
@@ -110,7 +113,7 @@ API int b200_mul_mat_q(int type, const void * W, int64_t w_nb1, int64_t M, int64
     a.type = type; a.W = W; a.w_nb1 = w_nb1; a.Xq = scratch; a.M = (int) M; a.K = (int) K;
     a.ne12 = 1; a.ne13 = 1; a.r2 = 1; a.r3 = 1; a.x_ncols = (int) N; a.xq_ne12 = 1;
     a.dst_nb1 = dst_stride * 4;
-    a.status = lc.status; a.sm_count = lc.sm_count; a.device = lc.device; a.use_pdl = 0;
+    a.status = lc.status; a.sm_count = lc.sm_count; a.device = lc.device; a.use_pdl = lc.use_pdl;
     for (int64_t n0 = 0; n0 < N; n0 += 8) {
         a.N = (int) (N - n0 < 8 ? N - n0 : 8);
         a.x_col0 = (int) n0;
@@ -138,7 +141,7 @@ API int b200_mul_mat_vec_q(int type, const void * W, int64_t w_nb1, int64_t M, i
     a.type = type; a.W = W; a.w_nb1 = w_nb1; a.Xq = xq; a.M = (int) M; a.K = (int) K; a.N = (int) N;
     a.ne12 = 1; a.ne13 = 1; a.r2 = 1; a.r3 = 1; a.x_ncols = (int) N; a.xq_ne12 = 1; a.x_col0 = 0;
     a.dst = dst; a.dst_nb1 = dst_stride * 4;
-    a.status = lc.status; a.sm_count = lc.sm_count; a.device = lc.device; a.use_pdl = 0;
+    a.status = lc.status; a.sm_count = lc.sm_count; a.device = lc.device; a.use_pdl = lc.use_pdl;
     CK(launch_mmvq(a, lc.stream));
     return 0;
 }

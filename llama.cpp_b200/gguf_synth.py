@@ -1,0 +1,123 @@
+#!/usr/bin/env python
+"""Writes a synthetic Llama-architecture model as a GGUF file the unmodified reference can load.
+
+The file format is GGUF version 3 (ggml/include/gguf.h:41-46 and the layout comment at its top: header, key/value
+metadata, tensor infos, padding to `general.alignment` = 32, tensor data).  Weights are random-init (seeded
+N(0, 0.02)), already quantized to the reference's Q4_K_M tensor-type mixture (src/llama-quant.cpp:129-131, 235-243,
+291-298) by this package's own quantizers, i.e. the same bytes `bench.py` feeds through the C-ABI driver.  The
+tokenizer section says `no_vocab`, which makes libllama create `<arch>.vocab_size` dummy tokens
+(src/llama-vocab.cpp:1350-1368): all that llama-bench, which feeds random token ids, needs.
+
+    python llama.cpp_b200/gguf_synth.py /tmp/llama3-8b-q4_k_m.gguf --model 8b
+    GGML_BACKEND_PATH=llama.cpp_b200/lib/libggml-b200.so oracle/_ref/llama-bench -m /tmp/llama3-8b-q4_k_m.gguf \
+        -p 512 -n 128 -fa 1 -ngl 99
+"""
+from __future__ import annotations
+
+import argparse
+import struct
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent
+ALIGN = 32
+T_F32, T_Q4_K, T_Q5_K, T_Q6_K = 0, 12, 13, 14
+# gguf_type ids (ggml/include/gguf.h:53-68)
+G_U32, G_F32, G_STR = 4, 6, 8
+
+
+def use_more_bits(il: int, n: int) -> bool:        # src/llama-quant.cpp:129-131
+    return il < n // 8 or il >= 7 * n // 8 or (il - n // 8) % 3 == 2
+
+
+def tensor_list(arch: dict):
+    """(name, ggml type, ne0, ne1) in file order; 1-D tensors have ne1 = 1."""
+    E, F, L = arch["n_embd"], arch["n_ff"], arch["n_layer"]
+    KV = E // arch["n_head"] * arch["n_head_kv"]
+    out = [("token_embd.weight", T_Q4_K, E, arch["n_vocab"]), ("output_norm.weight", T_F32, E, 1),
+           ("output.weight", T_Q6_K, E, arch["n_vocab"])]
+    for il in range(L):
+        more = T_Q6_K if use_more_bits(il, L) else T_Q4_K
+        v_type = T_Q5_K if (L == 80 and more == T_Q4_K) else more        # 70B-class: src/llama-quant.cpp:238-243
+        p = f"blk.{il}."
+        out += [(p + "attn_norm.weight", T_F32, E, 1), (p + "attn_q.weight", T_Q4_K, E, E), (p + "attn_k.weight", T_Q4_K, E, KV),
+                (p + "attn_v.weight", v_type, E, KV), (p + "attn_output.weight", T_Q4_K, E, E), (p + "ffn_norm.weight", T_F32, E, 1),
+                (p + "ffn_gate.weight", T_Q4_K, E, F), (p + "ffn_up.weight", T_Q4_K, E, F), (p + "ffn_down.weight", more, F, E)]
+    return out
+
+
+def row_bytes(t: int, ne0: int) -> int:
+    return {T_F32: 4 * ne0, T_Q4_K: ne0 // 256 * 144, T_Q5_K: ne0 // 256 * 176, T_Q6_K: ne0 // 256 * 210}[t]
+
+
+def _s(x: str) -> bytes:
+    b = x.encode()
+    return struct.pack("<Q", len(b)) + b
+
+
+def _kv(key: str, gtype: int, value) -> bytes:
+    head = _s(key) + struct.pack("<I", gtype)
+    if gtype == G_U32:
+        return head + struct.pack("<I", value)
+    if gtype == G_F32:
+        return head + struct.pack("<f", value)
+    return head + _s(value)
+
+
+def write_llama_gguf(path, arch: dict, n_ctx_train: int = 8192, seed_base: int = 1000, device: str = "cpu", make_tensor=None) -> int:
+    """Returns the number of bytes written.  make_tensor(type, ne0, ne1, seed, device) -> flat uint8 array."""
+    if make_tensor is None:
+        from llama_cpp_b200 import synth
+        make_tensor = synth.make_tensor
+    a = "llama"
+    head_dim = arch["n_embd"] // arch["n_head"]
+    kvs = [_kv("general.architecture", G_STR, a), _kv("general.name", G_STR, "synthetic llama (random init)"),
+           _kv("general.file_type", G_U32, 15),                       # LLAMA_FTYPE_MOSTLY_Q4_K_M
+           _kv("general.alignment", G_U32, ALIGN),
+           _kv(f"{a}.context_length", G_U32, n_ctx_train), _kv(f"{a}.embedding_length", G_U32, arch["n_embd"]),
+           _kv(f"{a}.block_count", G_U32, arch["n_layer"]), _kv(f"{a}.feed_forward_length", G_U32, arch["n_ff"]),
+           _kv(f"{a}.attention.head_count", G_U32, arch["n_head"]), _kv(f"{a}.attention.head_count_kv", G_U32, arch["n_head_kv"]),
+           _kv(f"{a}.attention.layer_norm_rms_epsilon", G_F32, arch["rms_eps"]), _kv(f"{a}.rope.freq_base", G_F32, arch["rope_theta"]),
+           _kv(f"{a}.rope.dimension_count", G_U32, head_dim), _kv(f"{a}.vocab_size", G_U32, arch["n_vocab"]),
+           _kv("tokenizer.ggml.model", G_STR, "no_vocab")]
+    tensors = tensor_list(arch)
+    infos, off = [], 0
+    for name, t, ne0, ne1 in tensors:
+        dims = [ne0] if ne1 == 1 and t == T_F32 else [ne0, ne1]
+        infos.append(_s(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", t, off))
+        off += (row_bytes(t, ne0) * ne1 + ALIGN - 1) // ALIGN * ALIGN
+    header = b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(kvs)) + b"".join(kvs) + b"".join(infos)
+    header += b"\0" * (-len(header) % ALIGN)
+    written = 0
+    with open(path, "wb") as f:
+        f.write(header)
+        written += len(header)
+        for i, (name, t, ne0, ne1) in enumerate(tensors):
+            data = np.ascontiguousarray(make_tensor(t, ne0, ne1, seed=seed_base + i, device=device)).view(np.uint8).reshape(-1)
+            assert data.size == row_bytes(t, ne0) * ne1, name
+            f.write(data.tobytes())
+            f.write(b"\0" * (-data.size % ALIGN))
+            written += data.size + (-data.size % ALIGN)
+    return written
+
+
+def main():
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as entry
+    entry.load_package()
+    from llama_cpp_b200 import llama
+    import torch
+    ap = argparse.ArgumentParser()
+    ap.add_argument("path")
+    ap.add_argument("--model", default="8b", choices=["8b", "70b", "tiny"])
+    a = ap.parse_args()
+    arch = {"8b": llama.LLAMA3_8B, "70b": llama.LLAMA3_70B,
+            "tiny": dict(n_layer=4, n_embd=1024, n_head=8, n_head_kv=2, n_ff=2048, n_vocab=2048, rope_theta=500000.0, rms_eps=1e-5)}[a.model]
+    n = write_llama_gguf(a.path, arch, device="cuda" if torch.cuda.is_available() else "cpu")
+    print(f"wrote {a.path}: {n / 1e9:.2f} GB")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,41 @@
+"""Drop-in check at the application level: the reference's own, unmodified llama-bench + libllama (built by
+oracle/ref.mk) load libggml-b200.so through GGML_BACKEND_PATH, offload a synthetic Llama model (written by
+llama.cpp_b200/gguf_synth.py) to device B200_0 and run prefill and decode through it."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+REF = ROOT / "oracle" / "_ref"
+TINY = dict(n_layer=4, n_embd=1024, n_head=8, n_head_kv=2, n_ff=2048, n_vocab=2048, rope_theta=500000.0, rms_eps=1e-5)
+
+
+def run_llama_bench(model, *args, plugin=True, timeout=900):
+    if not (REF / "llama-bench").exists():
+        pytest.skip("oracle/_ref/llama-bench not built (make -f oracle/ref.mk all)")
+    env = dict(os.environ)
+    if plugin:
+        env["GGML_BACKEND_PATH"] = str(ROOT / "llama.cpp_b200" / "lib" / "libggml-b200.so")
+    r = subprocess.run([str(REF / "llama-bench"), "-m", str(model), "-o", "json", *args], cwd=REF, env=env, capture_output=True, text=True,
+                       timeout=timeout)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    return json.loads(r.stdout), r.stderr
+
+
+def test_reference_llama_bench_runs_on_the_plugin(tmp_path, b200):
+    from llama_cpp_b200 import gguf_synth
+    model = tmp_path / "tiny.gguf"
+    gguf_synth.write_llama_gguf(model, TINY, device="cuda")
+    res, log = run_llama_bench(model, "-p", "64", "-n", "16", "-fa", "1", "-ngl", "99", "-r", "2")
+    assert len(res) == 2
+    for r in res:
+        assert "B200" in r["backends"], r
+        assert r["n_gpu_layers"] == 99 and r["flash_attn"] and r["avg_ts"] > 0
+    # the same file on the reference CPU backend alone (no plugin): the loader and the graph are the reference's own
+    cpu, _ = run_llama_bench(model, "-p", "64", "-n", "16", "-fa", "1", "-ngl", "0", "-r", "1", "-t", "4", plugin=False)
+    assert all(r["avg_ts"] > 0 for r in cpu)

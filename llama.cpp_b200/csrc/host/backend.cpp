@@ -219,6 +219,10 @@ static void backend_free(ggml_backend_t backend) {
     BackendCtx * ctx = (BackendCtx *) backend->context;
     set_device(ctx->dev->device);
     cudaStreamSynchronize(ctx->stream);
+    if (getenv("GGML_B200_VERBOSE"))
+        fprintf(stderr, "ggml-b200: %s: graph_compute calls: %llu replayed from a CUDA graph, %llu captured, %llu run directly; %llu kernel launches\n",
+                ctx->name.c_str(), (unsigned long long) ctx->n_replay, (unsigned long long) ctx->n_capture, (unsigned long long) ctx->n_direct,
+                (unsigned long long) ctx->n_launches);
     if (ctx->scratch) cudaFree(ctx->scratch);
     for (auto & e : ctx->act_cache) if (e.q) cudaFree(e.q);
     if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);

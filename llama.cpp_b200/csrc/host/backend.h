@@ -65,6 +65,7 @@ struct BackendCtx {
     uint64_t     graph_key = 0, pending_key = 0;
     cudaGraphExec_t graph_exec = nullptr;
     uint64_t     graph_launches = 0;       // kernels inside the instantiated graph
+    uint64_t     n_replay = 0, n_capture = 0, n_direct = 0;   // graph_compute calls by how they were executed
     int64_t *    dyn_host = nullptr, * dyn_dev = nullptr;
     int          dyn_used = 0;
     static constexpr int DYN_CAP = 1024;
@@ -76,6 +77,8 @@ struct BackendCtx {
     // stored to the peers since the last barrier
     ggml_b200_peers peers = {};
     bool         peer_pending = false;
+    std::vector<const void *> pending_full;   // full results whose slices are in flight to the peers
+    std::vector<uint8_t> node_done;            // per graph node: already executed ahead of its position (hoisted into a grouped launch)
     const ggml_b200_row_slice * row_slice_of(const ggml_tensor * node) const {
         if (peers.n_ranks < 2 || node->op != GGML_OP_MUL_MAT || !node->extra) return nullptr;
         const ggml_b200_row_slice * rs = (const ggml_b200_row_slice *) node->extra;

@@ -175,6 +175,10 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
             return false;
         }
         ctx->peer_pending = true;
+        ctx->pending_full.push_back(ctx->row_slice_of(dst)->full_data); ctx->act_cache_invalidate(ctx->row_slice_of(dst)->full_data);
+        for (int i = 0; i < n_extra; ++i) if (const ggml_b200_row_slice * r2 = ctx->row_slice_of(extra[i])) {
+            ctx->pending_full.push_back(r2->full_data); ctx->act_cache_invalidate(r2->full_data);
+        }
     }
     if (!ids && is_float_type(W->type)) {
         RUN(launch_matmul_f(to_desc(W), to_desc(X), to_desc(dst), lc));
@@ -273,6 +277,18 @@ static bool feeds_quant_mul_mat(const ggml_cgraph * g, int from, const ggml_tens
 
 static bool is_noop(const ggml_tensor * node);
 
+// do the byte ranges spanned by two tensors intersect?
+static bool t_overlap(const ggml_tensor * a, const ggml_tensor * b) {
+    if (!a->data || !b->data) return false;
+    auto extent = [](const ggml_tensor * t) {
+        size_t e = (size_t) (t->ne[0] / t_blck(t->type)) * t->nb[0];
+        for (int d = 1; d < 4; ++d) e += (size_t) (t->ne[d] - 1) * t->nb[d];
+        return e;
+    };
+    const char * a0 = (const char *) a->data, * b0 = (const char *) b->data;
+    return a0 < b0 + extent(b) && b0 < a0 + extent(a);
+}
+
 // Can MUL_MAT node `n` ride along with `first` in one grouped mat-vec launch?
 static bool groupable_mul_mat(const ggml_tensor * first, const ggml_tensor * n) {
     if (n->op != GGML_OP_MUL_MAT || n->src[1] != first->src[1]) return false;
@@ -289,7 +305,7 @@ static bool group_head_ok(const ggml_tensor * n) {
     if ((size_t) x->ne[1] * ((w->ne[0] + 127) / 128) * 160 > 200 * 1024) return false;      // must fit the direct kernel's activation smem
     return ((uintptr_t) w->data & 15) == 0 && (w->nb[1] & 15) == 0 && t_contiguous(n) && x->type == GGML_TYPE_F32 && t_contiguous(x);
 }
-static int next_exec(const ggml_cgraph * g, int i);
+static int next_exec(const BackendCtx * ctx, const ggml_cgraph * g, int i);
 
 static RopeParams rope_params_of(const ggml_tensor * dst) {
     RopeParams rp;
@@ -301,17 +317,16 @@ static RopeParams rope_params_of(const ggml_tensor * dst) {
 
 // ROPE(Q), ROPE(K), CPY(K -> cache view), CPY(V -> cache view) as emitted per layer (src/llama.cpp:1511-1531,
 // :157-199), possibly with view-only nodes in between.  On a match returns the index of the last node.
-static int match_rope_kv(const ggml_cgraph * g, int i, const ggml_tensor ** ropek, const ggml_tensor ** cpyk, const ggml_tensor ** cpyv) {
+struct RopeKvMatch { int rk = -1, ck = -1, cv = -1; };    // node indices of ROPE(K), CPY(K), CPY(V); cv < 0: V is stored separately
+static bool match_rope_kv(const BackendCtx * ctx, const ggml_cgraph * g, int i, RopeKvMatch * m) {
     const ggml_tensor * rq = g->nodes[i];
-    const int j1 = next_exec(g, i + 1); if (j1 < 0) return -1;
+    const int j1 = next_exec(ctx, g, i + 1); if (j1 < 0) return false;
     const ggml_tensor * rk = g->nodes[j1];
-    if (rk->op != GGML_OP_ROPE || rk->src[1] != rq->src[1] || rk->src[2] != rq->src[2]) return -1;
-    if (memcmp(rk->op_params, rq->op_params, sizeof(rq->op_params)) != 0) return -1;
+    if (rk->op != GGML_OP_ROPE || rk->src[1] != rq->src[1] || rk->src[2] != rq->src[2]) return false;
+    if (memcmp(rk->op_params, rq->op_params, sizeof(rq->op_params)) != 0) return false;
     auto plain = [](const ggml_tensor * t) { return t->type == GGML_TYPE_F32 && t_contiguous(t) && t_contiguous(t->src[0]) && t->ne[3] == 1; };
-    if (!plain(rq) || !plain(rk) || rq->ne[0] != rk->ne[0] || rq->ne[2] != rk->ne[2] || (rq->ne[0] & 1)) return -1;
-    if (op_param_i32(rq, 2) & ~GGML_ROPE_TYPE_NEOX) return -1;
-    const int j2 = next_exec(g, j1 + 1); if (j2 < 0) return -1;
-    const ggml_tensor * ck = g->nodes[j2];
+    if (!plain(rq) || !plain(rk) || rq->ne[0] != rk->ne[0] || rq->ne[2] != rk->ne[2] || (rq->ne[0] & 1)) return false;
+    if (op_param_i32(rq, 2) & ~GGML_ROPE_TYPE_NEOX) return false;
     auto cache_store = [](const ggml_tensor * c, const ggml_tensor * from) {
         if (c->op != GGML_OP_CPY || c->src[0]->type != GGML_TYPE_F32 || !t_contiguous(c->src[0])) return false;
         if (from && c->src[0] != from) return false;
@@ -319,12 +334,27 @@ static int match_rope_kv(const ggml_cgraph * g, int i, const ggml_tensor ** rope
         return out->type == GGML_TYPE_F16 && t_contiguous(out) && out->view_src && out->view_src->data &&
                t_nelements(out) == t_nelements(c->src[0]) && (t_nelements(out) & 1) == 0 && ((uintptr_t) out->data & 3) == 0;
     };
-    if (!cache_store(ck, rk)) return -1;
-    const int j3 = next_exec(g, j2 + 1); if (j3 < 0) return -1;
-    const ggml_tensor * cv = g->nodes[j3];
-    if (!cache_store(cv, nullptr) || ((uintptr_t) cv->src[0]->data & 7)) return -1;
-    *ropek = rk; *cpyk = ck; *cpyv = cv;
-    return j3;
+    // CPY(K): normally next; libllama's order puts MUL_MAT(V) before it (src/llama.cpp:1511-1540, :157-199).  The
+    // store may run ahead of a mat-mul it does not depend on: its source stays alive until its own position and
+    // its destination is the cache.
+    int j2 = next_exec(ctx, g, j1 + 1);
+    const ggml_tensor * jumped = nullptr;
+    if (j2 >= 0 && g->nodes[j2]->op == GGML_OP_MUL_MAT && g->nodes[j2]->src[0]->op == GGML_OP_NONE) {
+        jumped = g->nodes[j2];
+        j2 = next_exec(ctx, g, j2 + 1);
+    }
+    if (j2 < 0) return false;
+    const ggml_tensor * ck = g->nodes[j2];
+    if (!cache_store(ck, rk)) return false;
+    if (jumped && (t_overlap(jumped, ck->src[1]) || t_overlap(jumped->src[1], ck->src[1]))) return false;
+    m->rk = j1; m->ck = j2; m->cv = -1;
+    const int j3 = next_exec(ctx, g, j2 + 1);
+    if (j3 >= 0) {
+        const ggml_tensor * cv = g->nodes[j3];
+        // V rides along when it has been computed already (not the result of the mat-mul that was jumped over)
+        if (cache_store(cv, nullptr) && !((uintptr_t) cv->src[0]->data & 7) && !(jumped && (cv->src[0] == jumped || cv->src[0]->view_src == jumped))) m->cv = j3;
+    }
+    return true;
 }
 
 // Executes node i, fusing it with its successor where the graph allows:
@@ -343,14 +373,36 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
     ggml_tensor * next = i + 1 < g->n_nodes ? g->nodes[i + 1] : nullptr;
     switch (dst->op) {
         case GGML_OP_MUL_MAT: {
+            // Mat-vecs on the same activations go out as one grouped launch.  libllama emits them interleaved with
+            // their consumers (MUL_MAT q, ROPE q, MUL_MAT k, ROPE k, MUL_MAT v: src/llama.cpp:1511-1540), so the
+            // group also takes members from a little further down the graph: such a node depends only on the shared
+            // activations and a weight leaf, and it may run early if its output does not alias anything the nodes
+            // it jumps over touch (ggml-alloc reuses freed memory).
             ggml_tensor * extra[2]; int n_extra = 0;
-            if (group_head_ok(dst) && !buft_is_split(dst->src[0]->buffer ? dst->src[0]->buffer->buft : nullptr)) {
-                while (n_extra < 2 && i + 1 + n_extra < g->n_nodes && groupable_mul_mat(dst, g->nodes[i + 1 + n_extra]) &&
-                       (ctx->row_slice_of(dst) != nullptr) == (ctx->row_slice_of(g->nodes[i + 1 + n_extra]) != nullptr)) {
-                    extra[n_extra] = g->nodes[i + 1 + n_extra]; ctx->act_cache_invalidate(extra[n_extra]->data); ++n_extra;
+            if (ctx->use_fusion && group_head_ok(dst) && !buft_is_split(dst->src[0]->buffer ? dst->src[0]->buffer->buft : nullptr)) {
+                const bool sliced = ctx->row_slice_of(dst) != nullptr;
+                const ggml_tensor * jumped[16]; int n_jumped = 0;
+                for (int j = i + 1; j < g->n_nodes && n_extra < 2 && n_jumped < 16; ++j) {
+                    ggml_tensor * n = g->nodes[j];
+                    if (is_noop(n) || ctx->node_done[(size_t) j]) continue;
+                    if (n->op == GGML_OP_FLASH_ATTN_EXT) break;
+                    const bool member = groupable_mul_mat(dst, n) && n->src[0]->op == GGML_OP_NONE &&
+                                        (ctx->row_slice_of(n) != nullptr) == sliced;
+                    bool clear = member;
+                    for (int q = 0; q < n_jumped && clear; ++q) {
+                        if (t_overlap(n, jumped[q])) clear = false;
+                        for (int s_ = 0; s_ < GGML_MAX_SRC && jumped[q]->src[s_] && clear; ++s_) if (t_overlap(n, jumped[q]->src[s_])) clear = false;
+                    }
+                    if (member && clear) {
+                        extra[n_extra++] = n; ctx->node_done[(size_t) j] = 1;
+                        ctx->act_cache_invalidate(n->data);
+                    } else {
+                        if (n->op == GGML_OP_MUL_MAT && n->src[1] != dst->src[1]) break;     // a different stage of the layer
+                        jumped[n_jumped++] = n;
+                    }
                 }
             }
-            return run_mul_mat(ctx, dst, nullptr, extra, n_extra) ? 1 + n_extra : 0;
+            return run_mul_mat(ctx, dst, nullptr, extra, n_extra) ? 1 : 0;
         }
         case GGML_OP_MUL_MAT_ID: return run_mul_mat(ctx, dst, dst->src[2]) ? 1 : 0;
         case GGML_OP_FLASH_ATTN_EXT: {
@@ -366,7 +418,7 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
             // writes its int8 activation blocks (one head row of 128 values = one block)
             void * act = nullptr;
             if (ctx->use_fusion && lc.fa_tickets && a->ne[0] == 128 && a->ne[3] == 1 && fattn_dec_applicable(qd, kd, vd, mask ? &md : nullptr)) {
-                const int j = next_exec(g, i + 1);
+                const int j = next_exec(ctx, g, i + 1);
                 const ggml_tensor * mm = j >= 0 ? g->nodes[j] : nullptr;
                 if (mm && mm->op == GGML_OP_MUL_MAT && mm->src[1]->data == dst->data && mmvq_type_supported(mm->src[0]->type) &&
                     act_cacheable(mm->src[1]) && mm->src[1]->ne[0] == dst->ne[0] * dst->ne[1] && mm->src[1]->ne[1] == dst->ne[2]) {
@@ -389,7 +441,8 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
                     if (!e) return fail();
                     act = e->q;
                 }
-                RUN0(launch_rms_norm_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), op_param_f32(dst, 0), act, (float *) dst->data, nullptr, nullptr, lc));
+                RUN0(launch_rms_norm_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), op_param_f32(dst, 0), act,
+                                         dst->data == next->data ? nullptr : (float *) dst->data, nullptr, nullptr, lc));
                 return 2;
             }
             RUN0(launch_rms_norm(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc));
@@ -406,14 +459,14 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
                 t_contiguous(a) && t_contiguous(b) && t_contiguous(dst) && t_contiguous(rn) && t_contiguous(mu) &&
                 mu->type == GGML_TYPE_F32 && mu->src[1]->type == GGML_TYPE_F32 && mu->src[1]->nb[0] == 4 && t_can_repeat(mu->src[1], rn)) {
                 void * act = nullptr;
+                ctx->act_cache_invalidate(rn->data);          // (the MUL is often computed in place of the norm's output)
                 if (act_cacheable(mu) && mu->ne[0] % 128 == 0 && feeds_quant_mul_mat(g, i + 3, mu)) {
                     ctx->act_cache_invalidate(mu->data);
                     BackendCtx::ActEntry * e = ctx->act_cache_take(mu->data, mu->ne[0], mu->ne[1] * mu->ne[2] * mu->ne[3]);
                     if (!e) return fail();
                     act = e->q;
                 }
-                ctx->act_cache_invalidate(rn->data);
-                RUN0(launch_rms_norm_mul(to_desc(a), to_desc(mu->src[1]), to_desc(mu), op_param_f32(rn, 0), act, (float *) rn->data,
+                RUN0(launch_rms_norm_mul(to_desc(a), to_desc(mu->src[1]), to_desc(mu), op_param_f32(rn, 0), act, rn->data == mu->data ? nullptr : (float *) rn->data,
                                          (const float *) b->data, (float *) dst->data, lc));
                 return 3;
             }
@@ -425,16 +478,21 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
         case GGML_OP_DIV: RUN0(launch_bin_bcast(BIN_DIV, to_desc(a), to_desc(b), to_desc(dst), lc)); return 1;
         case GGML_OP_UNARY: {
             const int uop = op_param_i32(dst, 0);
-            if (uop == GGML_UNARY_OP_SILU && next && next->op == GGML_OP_MUL && next->src[0] == dst && next->type == GGML_TYPE_F32 &&
+            const int jn = next_exec(ctx, g, i + 1);           // skips a mat-mul that was hoisted into an earlier group
+            ggml_tensor * next = jn >= 0 ? g->nodes[jn] : nullptr;
+            if (ctx->use_fusion && uop == GGML_UNARY_OP_SILU && next && next->op == GGML_OP_MUL && next->src[0] == dst && next->type == GGML_TYPE_F32 &&
                 next->src[1]->type == GGML_TYPE_F32 && t_same_shape(next->src[1], dst) && t_contiguous(next->src[1]) && t_contiguous(next)) {
                 void * act = nullptr;
-                if (act_cacheable(next) && next->ne[0] % 128 == 0 && feeds_quant_mul_mat(g, i + 2, next)) {
+                ctx->act_cache_invalidate(next->data);
+                if (act_cacheable(next) && next->ne[0] % 128 == 0 && feeds_quant_mul_mat(g, jn + 1, next)) {
                     BackendCtx::ActEntry * e = ctx->act_cache_take(next->data, next->ne[0], next->ne[1] * next->ne[2] * next->ne[3]);
                     if (!e) return fail();
                     act = e->q;
                 }
-                RUN0(launch_silu_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), act, (float *) dst->data, lc));
-                return 2;
+                // the intermediate silu(gate) is skipped when the product is computed in place of it
+                RUN0(launch_silu_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), act, dst->data == next->data ? nullptr : (float *) dst->data, lc));
+                ctx->node_done[(size_t) jn] = 1;
+                return 1;
             }
             RUN0(launch_unary(unary_to_unop(uop), to_desc(a), to_desc(dst), lc));
             return 1;
@@ -449,26 +507,32 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
         case GGML_OP_ROPE: {
             const RopeParams rp = rope_params_of(dst);
             const ggml_tensor * ff = dst->src[2];
-            const ggml_tensor * rk = nullptr, * ck = nullptr, * cv = nullptr;
-            const int last = ctx->use_fusion ? match_rope_kv(g, i, &rk, &ck, &cv) : -1;
-            if (last >= 0 && (!ctx->capturing || ctx->dyn_used + 2 <= BackendCtx::DYN_CAP)) {
+            RopeKvMatch m;
+            if (ctx->use_fusion && match_rope_kv(ctx, g, i, &m) && (!ctx->capturing || ctx->dyn_used + 2 <= BackendCtx::DYN_CAP)) {
+                const ggml_tensor * rk = g->nodes[m.rk], * ck = g->nodes[m.ck], * cv = m.cv >= 0 ? g->nodes[m.cv] : nullptr;
                 RopeKvLaunch l = {};
                 l.q_src = (const float *) a->data; l.q_dst = (float *) dst->data;
                 l.k_src = (const float *) rk->src[0]->data; l.k_dst = (float *) rk->data;
-                l.v_src = (const float *) cv->src[0]->data; l.v_elems = t_nelements(cv->src[0]);
                 l.hd = dst->ne[0]; l.n_head = dst->ne[1]; l.n_head_kv = rk->ne[1]; l.n_tok = dst->ne[2];
-                const ggml_tensor * ko = ck->src[1], * vo = cv->src[1];
-                l.k_cache = ko->view_src->data; l.v_cache = vo->view_src->data;
+                const ggml_tensor * ko = ck->src[1];
+                l.k_cache = ko->view_src->data;
                 l.k_off = (const char *) ko->data - (const char *) ko->view_src->data;
-                l.v_off = (const char *) vo->data - (const char *) vo->view_src->data;
+                if (cv) {
+                    const ggml_tensor * vo = cv->src[1];
+                    l.v_src = (const float *) cv->src[0]->data; l.v_elems = t_nelements(cv->src[0]);
+                    l.v_cache = vo->view_src->data;
+                    l.v_off = (const char *) vo->data - (const char *) vo->view_src->data;
+                }
                 if (ctx->capturing) {                   // same slot order as the CPY nodes appear in the graph
                     ctx->dyn_host[ctx->dyn_used] = l.k_off; l.k_off_dev = ctx->dyn_dev + ctx->dyn_used++;
-                    ctx->dyn_host[ctx->dyn_used] = l.v_off; l.v_off_dev = ctx->dyn_dev + ctx->dyn_used++;
+                    if (cv) { ctx->dyn_host[ctx->dyn_used] = l.v_off; l.v_off_dev = ctx->dyn_dev + ctx->dyn_used++; }
                 }
                 l.pos = (const int32_t *) b->data; l.ff = ff ? (const float *) ff->data : nullptr;
-                for (int j = i; j <= last; ++j) ctx->act_cache_invalidate(g->nodes[j]->data);
+                ctx->act_cache_invalidate(rk->data);
+                ctx->node_done[(size_t) m.rk] = 1; ctx->node_done[(size_t) m.ck] = 1;
+                if (cv) ctx->node_done[(size_t) m.cv] = 1;
                 RUN0(launch_rope_kv(l, rp, lc));
-                return last - i + 1;
+                return 1;
             }
             RUN0(launch_rope(to_desc(a), (const int32_t *) b->data, ff ? (const float *) ff->data : nullptr, to_desc(dst), rp, lc));
             return 1;
@@ -511,17 +575,19 @@ static bool is_noop(const ggml_tensor * node) {
            node->op == GGML_OP_PERMUTE || node->op == GGML_OP_TRANSPOSE;
 }
 
-static int next_exec(const ggml_cgraph * g, int i) {
-    for (; i < g->n_nodes; ++i) if (!is_noop(g->nodes[i])) return i;
+static int next_exec(const BackendCtx * ctx, const ggml_cgraph * g, int i) {
+    for (; i < g->n_nodes; ++i) if (!is_noop(g->nodes[i]) && !(i < (int) ctx->node_done.size() && ctx->node_done[(size_t) i])) return i;
     return -1;
 }
 
 static bool run_all(BackendCtx * ctx, ggml_cgraph * cgraph) {
     ctx->act_cache_clear();
-    std::vector<const void *> pending_full;            // full results whose slices are in flight to the peers
+    std::vector<const void *> & pending_full = ctx->pending_full;
+    pending_full.clear();
+    ctx->node_done.assign((size_t) cgraph->n_nodes, 0);
     for (int i = 0; i < cgraph->n_nodes;) {
         ggml_tensor * node = cgraph->nodes[i];
-        if (is_noop(node)) { ++i; continue; }
+        if (is_noop(node) || ctx->node_done[(size_t) i]) { ++i; continue; }
         const ggml_b200_row_slice * rs = ctx->row_slice_of(node);
         if (ctx->peer_pending) {
             // slices stored to the peers become readable after a barrier; consecutive sliced MUL_MATs that
@@ -533,19 +599,19 @@ static bool run_all(BackendCtx * ctx, ggml_cgraph * cgraph) {
             }
             if (need) { if (!peer_barrier(ctx)) return false; pending_full.clear(); }
         }
-        if (rs) { pending_full.push_back(rs->full_data); ctx->act_cache_invalidate(rs->full_data); }
         ctx->act_cache_invalidate(node->data);
         if (node->op == GGML_OP_CPY && node->src[1]) ctx->act_cache_invalidate(node->src[1]->data);
         if (i + 1 < cgraph->n_nodes) ctx->act_cache_invalidate(cgraph->nodes[i + 1]->data);   // it may be fused into this launch
+        const uint64_t l0 = ctx->n_launches;
         const int used = run_node(ctx, cgraph, i);
         if (used == 0) return false;
-        for (int j = 1; j < used; ++j) {               // grouped sliced MUL_MATs ran with the head
-            const ggml_b200_row_slice * r2 = ctx->row_slice_of(cgraph->nodes[i + j]);
-            if (r2) { pending_full.push_back(r2->full_data); ctx->act_cache_invalidate(r2->full_data); }
-        }
+        if (ctx->trace > 0)
+            fprintf(stderr, "ggml-b200 trace: node %4d op %2d %-24s ne [%lld %lld %lld] nodes %d launches %llu\n", i, (int) node->op, node->name,
+                    (long long) node->ne[0], (long long) node->ne[1], (long long) node->ne[2], used, (unsigned long long) (ctx->n_launches - l0));
         i += used;
     }
     if (ctx->peer_pending && !peer_barrier(ctx)) return false;
+    if (ctx->trace > 0) ctx->trace--;                  // GGML_B200_TRACE=n: the first n graphs
     return true;
 }
 
@@ -596,10 +662,11 @@ enum ggml_status graph_compute(BackendCtx * ctx, ggml_cgraph * cgraph) {
     int n_dyn = 0;
     const uint64_t key = ctx->use_graphs ? graph_signature(ctx, cgraph, &n_dyn) : 0;
     if (key == 0) {
-        ctx->pending_key = 0;
+        ctx->pending_key = 0; ctx->n_direct++;
         return run_all(ctx, cgraph) ? GGML_STATUS_SUCCESS : GGML_STATUS_FAILED;
     }
     if (key == ctx->graph_key && ctx->graph_exec) {
+        ctx->n_replay++;
         // replay: refresh the token-dependent offsets, then one graph launch
         int k = 0;
         for (int i = 0; i < cgraph->n_nodes; ++i) {
@@ -615,10 +682,11 @@ enum ggml_status graph_compute(BackendCtx * ctx, ggml_cgraph * cgraph) {
     if (key != ctx->pending_key) {
         // first sighting of this graph: run it directly (this also performs any lazy allocation and
         // per-kernel attribute set-up); capture if it comes back
-        ctx->pending_key = key;
+        ctx->pending_key = key; ctx->n_direct++;
         return run_all(ctx, cgraph) ? GGML_STATUS_SUCCESS : GGML_STATUS_FAILED;
     }
     // second sighting: capture
+    ctx->n_capture++;
     if (ctx->graph_exec) { cudaGraphExecDestroy(ctx->graph_exec); ctx->graph_exec = nullptr; ctx->graph_key = 0; }
     ctx->capturing = true; ctx->capture_failed = false; ctx->dyn_used = 0;
     const uint64_t launches_before = ctx->n_launches;

@@ -347,8 +347,9 @@ cudaError_t launch_clamp(const TensorD & src, const TensorD & dst, float lo, flo
 
 // silu(gate) * up on contiguous F32 rows, optionally emitting activation blocks
 template <bool EMIT>
-__global__ void silu_mul_kernel(const float * __restrict__ g, const float * __restrict__ u, float * __restrict__ y,
-                                int64_t n0, int64_t rows, blk_act128 * act, float * __restrict__ silu_out) {
+// (no __restrict__: graph allocators compute silu in place of gate and the product in place of either operand)
+__global__ void silu_mul_kernel(const float * g, const float * u, float * y,
+                                int64_t n0, int64_t rows, blk_act128 * act, float * silu_out) {
     pdl_enter();
     const int64_t npad = (n0 + 127) & ~(int64_t) 127;
     const int64_t per_row = npad / 4;

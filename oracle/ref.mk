@@ -66,7 +66,7 @@ CPU_LIBS := $(foreach v,$(VARIANTS),$(OUT)/libggml-cpu-$(v).so)
 .PHONY: all core tools clean
 all: core tools
 core: $(OUT)/libggml-base.so $(OUT)/libggml.so $(CPU_LIBS) $(OUT)/test-backend-ops $(OUT)/test-quantize-fns
-tools: $(OUT)/libllama.so $(OUT)/llama-bench $(OUT)/llama-quantize
+tools: $(OUT)/libllama.so $(OUT)/llama-bench $(OUT)/llama-quantize $(OUT)/llama-logits
 
 # ---- ggml-base ----
 $(OBJ)/base/%.o: $(REF)/ggml/src/%.c
@@ -127,6 +127,10 @@ $(OUT)/llama-bench: $(REF)/examples/llama-bench/llama-bench.cpp $(OUT)/libcommon
 	$(CXX) $(COPT) $(XSTD) $(TOOL_DEFS) $(TOOL_INC) $< -o $@ $(OUT)/libcommon.a -L$(OUT) -lllama -lggml -lggml-base -lpthread $(RPATH)
 $(OUT)/llama-quantize: $(REF)/examples/quantize/quantize.cpp $(OUT)/libcommon.a $(OUT)/libllama.so
 	$(CXX) $(COPT) $(XSTD) $(TOOL_DEFS) $(TOOL_INC) $< -o $@ $(OUT)/libcommon.a -L$(OUT) -lllama -lggml -lggml-base -lpthread $(RPATH)
+
+# test tool of this repository (tests/native/llama_logits.cpp): libllama's public API only
+$(OUT)/llama-logits: tests/native/llama_logits.cpp $(OUT)/libllama.so
+	$(CXX) $(COPT) $(XSTD) $(TOOL_DEFS) $(TOOL_INC) $< -o $@ -L$(OUT) -lllama -lggml -lggml-base -lpthread $(RPATH)
 
 clean:
 	rm -rf $(OUT)

@@ -637,7 +637,10 @@ static uint64_t graph_signature(BackendCtx * ctx, const ggml_cgraph * g, int * n
         const ggml_tensor * n = g->nodes[i];
         if (is_noop(n)) continue;
         ++exec_nodes;
-        if ((n->op == GGML_OP_MUL_MAT || n->op == GGML_OP_MUL_MAT_ID) && n->src[1]->ne[1] * n->src[1]->ne[2] * n->src[1]->ne[3] > 8) return 0;
+        // only small batches are worth replaying; dim 1 of the activation operand is the token count (for MUL_MAT_ID
+        // dim 2), the attention products of the non-flash path batch over heads in dims 2 and 3
+        if (n->op == GGML_OP_MUL_MAT && n->src[1]->ne[1] > 8) return 0;
+        if (n->op == GGML_OP_MUL_MAT_ID && n->src[1]->ne[2] > 8) return 0;
         const ggml_tensor * dd = dyn_cpy_dst(n);
         h = mix(h, (uint64_t) n->op | ((uint64_t) n->type << 32));
         h = mix(h, dd ? (uint64_t) (uintptr_t) dd->view_src->data : (uint64_t) (uintptr_t) n->data);

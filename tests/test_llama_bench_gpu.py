@@ -41,27 +41,30 @@ def test_reference_llama_bench_runs_on_the_plugin(tmp_path, b200):
     assert all(r["avg_ts"] > 0 for r in cpu)
 
 
-def run_logits(model, out, ngl, plugin, n_prompt=37, n_gen=4):
+def run_logits(model, out, ngl, plugin, n_prompt=37, n_gen=6, fa=1):
     if not (REF / "llama-logits").exists():
         pytest.skip("oracle/_ref/llama-logits not built (make -f oracle/ref.mk tools)")
     env = dict(os.environ)
     if plugin:
         env["GGML_BACKEND_PATH"] = str(ROOT / "llama.cpp_b200" / "lib" / "libggml-b200.so")
-    r = subprocess.run([str(REF / "llama-logits"), str(model), str(out), str(ngl), str(n_prompt), str(n_gen), "5"], cwd=REF, env=env,
+    r = subprocess.run([str(REF / "llama-logits"), str(model), str(out), str(ngl), str(n_prompt), str(n_gen), "5", str(fa)], cwd=REF, env=env,
                        capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
     import numpy as np
     return np.fromfile(out, dtype=np.float32).reshape(n_gen + 1, -1), r.stderr
 
 
-def test_libllama_logits_plugin_vs_reference_cpu(tmp_path, b200, oracle):
+@pytest.mark.parametrize("fa", [1, 0])
+def test_libllama_logits_plugin_vs_reference_cpu(tmp_path, b200, oracle, fa):
     """libllama itself (loader, graph builder, scheduler: all the reference's) evaluates the same tokens on the
-    reference CPU backend and on the plugin; the logits agree within the per-op criterion times the depth."""
+    reference CPU backend and on the plugin; the logits agree within the per-op criterion times the depth.
+    fa=1: FLASH_ATTN_EXT; fa=0: llama-bench's default path (K.q and V.p as F16 MUL_MATs, SOFT_MAX, transposed V
+    cache).  Six generated tokens: the decode graph runs directly, is captured, and is then replayed."""
     from llama_cpp_b200 import gguf_synth
     model = tmp_path / "tiny.gguf"
     gguf_synth.write_llama_gguf(model, TINY, device="cuda")
-    cpu, _ = run_logits(model, tmp_path / "cpu.bin", 0, plugin=False)
-    gpu, log = run_logits(model, tmp_path / "gpu.bin", 99, plugin=True)
+    cpu, _ = run_logits(model, tmp_path / "cpu.bin", 0, plugin=False, fa=fa)
+    gpu, log = run_logits(model, tmp_path / "gpu.bin", 99, plugin=True, fa=fa)
     assert "B200" in log                                   # the layers were offloaded to the device
     n_mul_mat = 7 * TINY["n_layer"] + 1
     for a, b in zip(cpu, gpu):

@@ -68,7 +68,7 @@ bool device_supports_op(DeviceCtx * dev, const ggml_tensor * op) {
             const ggml_tensor * mask = op->src[3];
             if (a->type != GGML_TYPE_F32 || op->type != GGML_TYPE_F32) return false;
             if (!fattn_supported(a->ne[0], b->type, v->type) || v->ne[0] != a->ne[0] || b->ne[0] != a->ne[0]) return false;
-            if (a->nb[0] != 4 || b->nb[0] != 2 || v->nb[0] != 2) return false;
+            if (a->nb[0] != 4 || b->nb[0] != t_size(b->type) || v->nb[0] != t_size(v->type)) return false;
             if (mask && (mask->type != GGML_TYPE_F16 || mask->nb[0] != 2)) return false;
             return true;
         }
@@ -417,7 +417,8 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
             // decode: when the attention output goes straight into a quantized MUL_MAT (wo), the kernel also
             // writes its int8 activation blocks (one head row of 128 values = one block)
             void * act = nullptr;
-            if (ctx->use_fusion && lc.fa_tickets && a->ne[0] == 128 && a->ne[3] == 1 && fattn_dec_applicable(qd, kd, vd, mask ? &md : nullptr)) {
+            if (ctx->use_fusion && lc.fa_tickets && a->ne[0] == 128 && a->ne[3] == 1 && kd.type == GGML_TYPE_F16 && vd.type == GGML_TYPE_F16 &&
+                fattn_dec_applicable(qd, kd, vd, mask ? &md : nullptr)) {
                 const int j = next_exec(ctx, g, i + 1);
                 const ggml_tensor * mm = j >= 0 ? g->nodes[j] : nullptr;
                 if (mm && mm->op == GGML_OP_MUL_MAT && mm->src[1]->data == dst->data && mmvq_type_supported(mm->src[0]->type) &&

@@ -31,7 +31,7 @@ struct FaK {
     float scale, softcap, max_bias, m0, m1; int n_head_log2;
 };
 
-template <int D>
+template <int D, int KT, int VT>
 __global__ void __launch_bounds__(FA_WARPS * 32) fattn_vec_kernel(const FaK p) {
     pdl_enter();
     constexpr int DPL = (D + 31) / 32;            // head-dim elements per lane
@@ -69,12 +69,19 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fattn_vec_kernel(const FaK p) {
         if (j < kv1) {
             const float mv = mrow ? slope * __half2float(mrow[j]) : 0.0f;
             if (mv != -INFINITY) {
-                const __half2 * kr = (const __half2 *) (kbase + (int64_t) j * p.k_nb1);
                 float acc = 0.0f;
+                if (KT == T_F16) {
+                    const __half2 * kr = (const __half2 *) (kbase + (int64_t) j * p.k_nb1);
 #pragma unroll 8
-                for (int d2 = 0; d2 < D / 2; ++d2) {
-                    const float2 kk = __half22float2(kr[d2]);
-                    acc += kk.x * qs[2 * d2] + kk.y * qs[2 * d2 + 1];
+                    for (int d2 = 0; d2 < D / 2; ++d2) {
+                        const float2 kk = __half22float2(kr[d2]);
+                        acc += kk.x * qs[2 * d2] + kk.y * qs[2 * d2 + 1];
+                    }
+                } else {
+                    // quantized K cache (Q8_0 / Q4_0 blocks of 32 along the head dimension): dequantized on the fly
+                    const uint8_t * kr = (const uint8_t *) (kbase + (int64_t) j * p.k_nb1);
+#pragma unroll 8
+                    for (int d = 0; d < D; ++d) acc += dequant_elem<KT>(kr, d) * qs[d];
                 }
                 s = acc * p.scale;
                 if (p.softcap != 0.0f) s = p.softcap * tanhf(s);
@@ -92,11 +99,11 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fattn_vec_kernel(const FaK p) {
         for (int jj = 0; jj < 32; ++jj) {
             const float pp = __shfl_sync(0xffffffffu, pj, jj);
             if (pp == 0.0f) continue;             // warp-uniform; also covers rows past kv1
-            const __half * vr = (const __half *) (vbase + (int64_t) (base + jj) * p.v_nb1);
+            const uint8_t * vr = (const uint8_t *) (vbase + (int64_t) (base + jj) * p.v_nb1);
 #pragma unroll
             for (int i = 0; i < DPL; ++i) {
                 const int d = lane + 32 * i;
-                if (d < D) o[i] += pp * __half2float(vr[d]);
+                if (d < D) o[i] += pp * dequant_elem<VT>(vr, d);
             }
         }
     }
@@ -150,8 +157,14 @@ __global__ void fattn_combine_kernel(const float * __restrict__ ws, float * __re
     }
 }
 
+static inline bool t_is_q(int t) { return t == T_Q8_0 || t == T_Q4_0; }
+// F16 K/V everywhere; a quantized KV cache (-ctk/-ctv q8_0, q4_0: 32-value blocks along the head dimension,
+// reference kernels ggml/src/ggml-cuda/fattn-common.cuh:55-...) goes through the vec kernel
 bool fattn_supported(int64_t D, int kt, int vt) {
-    if (kt != T_F16 || vt != T_F16) return false;
+    auto ok = [](int t) { return t == T_F16 || t == T_BF16 || t == T_Q8_0 || t == T_Q4_0; };
+    if (!ok(kt) || !ok(vt)) return false;
+    if ((kt == T_BF16 || vt == T_BF16) && kt != vt) return false;
+    if ((t_is_q(kt) || t_is_q(vt)) && D % 32 != 0) return false;
     return D == 64 || D == 80 || D == 96 || D == 112 || D == 128 || D == 256;
 }
 
@@ -175,9 +188,18 @@ size_t fattn_workspace_bytes(const TensorD & q, const TensorD & k, int sm_count)
 }
 
 template <int D>
-static cudaError_t fattn_launch_d(const FaK & p, int64_t rows, int n3, const LaunchCtx & c) {
+static cudaError_t fattn_launch_d(const FaK & p, int kt, int vt, int64_t rows, int n3, const LaunchCtx & c) {
     dim3 grid((unsigned) p.n_splits, (unsigned) p.n_head, (unsigned) (p.n_q * n3));
-    (void) (launch_err = launch_k(c.use_pdl, c.stream, fattn_vec_kernel<D>, dim3(grid), dim3(FA_WARPS * 32), 0, p));
+    void (*kern)(FaK) = nullptr;
+#define FA_PICK(K_, V_) if (kt == K_ && vt == V_) kern = fattn_vec_kernel<D, K_, V_>
+    FA_PICK(T_F16, T_F16); FA_PICK(T_BF16, T_BF16);
+    if (D % 32 == 0) {
+        FA_PICK(T_Q8_0, T_Q8_0); FA_PICK(T_Q4_0, T_Q4_0); FA_PICK(T_Q8_0, T_F16); FA_PICK(T_F16, T_Q8_0);
+        FA_PICK(T_Q4_0, T_F16); FA_PICK(T_F16, T_Q4_0); FA_PICK(T_Q8_0, T_Q4_0); FA_PICK(T_Q4_0, T_Q8_0);
+    }
+#undef FA_PICK
+    if (!kern) return cudaErrorInvalidValue;
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, kern, dim3(grid), dim3(FA_WARPS * 32), 0, p));
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (p.n_splits > 1) {
@@ -191,11 +213,12 @@ cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v
                          const FattnParams & fp, void * workspace, const LaunchCtx & c, int * n_kernels, void * act128_out) {
     const int64_t D = q.ne[0], rows = q.ne[1] * q.ne[2] * q.ne[3];
     if (rows == 0) return cudaSuccess;
-    if (c.fa_tickets && fattn_dec_applicable(q, k, v, mask)) {
+    const bool f16_kv = k.type == T_F16 && v.type == T_F16;          // the two fast kernels stream F16 only
+    if (f16_kv && c.fa_tickets && fattn_dec_applicable(q, k, v, mask)) {
         if (n_kernels) *n_kernels = 1;
         return launch_fattn_dec(q, k, v, mask, dst, fp, c.fa_tickets, workspace, c, act128_out);
     }
-    if (fattn_mma_applicable(q, k, v, mask)) {
+    if (f16_kv && fattn_mma_applicable(q, k, v, mask)) {
         if (n_kernels) *n_kernels = mask ? 2 : 1;
         return launch_fattn_mma(q, k, v, mask, dst, fp, workspace, c);
     }
@@ -218,12 +241,12 @@ cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v
     p.m1 = powf(2.0f, -(fp.max_bias / 2.0f) / (float) nh2);
     const int n3 = (int) q.ne[3];
     switch (D) {
-        case 64:  return fattn_launch_d<64>(p, rows, n3, c);
-        case 80:  return fattn_launch_d<80>(p, rows, n3, c);
-        case 96:  return fattn_launch_d<96>(p, rows, n3, c);
-        case 112: return fattn_launch_d<112>(p, rows, n3, c);
-        case 128: return fattn_launch_d<128>(p, rows, n3, c);
-        case 256: return fattn_launch_d<256>(p, rows, n3, c);
+        case 64:  return fattn_launch_d<64>(p, k.type, v.type, rows, n3, c);
+        case 80:  return fattn_launch_d<80>(p, k.type, v.type, rows, n3, c);
+        case 96:  return fattn_launch_d<96>(p, k.type, v.type, rows, n3, c);
+        case 112: return fattn_launch_d<112>(p, k.type, v.type, rows, n3, c);
+        case 128: return fattn_launch_d<128>(p, k.type, v.type, rows, n3, c);
+        case 256: return fattn_launch_d<256>(p, k.type, v.type, rows, n3, c);
     }
     return cudaErrorInvalidValue;
 }

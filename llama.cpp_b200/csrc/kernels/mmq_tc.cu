@@ -100,6 +100,7 @@ __device__ __forceinline__ __half2 bytes01_h2(uint32_t v) { return __hsub2(u32_a
 __device__ __forceinline__ __half2 bytes23_h2(uint32_t v) { return __hsub2(u32_as_h2(__byte_perm(v, 0x64646464u, 0x4342)), u32_as_h2(0x64006400u)); }
 
 template <int T> struct Deq32 {                     // generic path: element-wise through the bit-exact dequantizer
+    static constexpr int KPR = 1;                                   // k-steps covered by one Raw
     struct Raw { const uint8_t * row; int k; };
     static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) { r.row = row; r.k = k; }
     static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
@@ -110,6 +111,7 @@ template <int T> struct Deq32 {                     // generic path: element-wis
 
 // Q4_K: k .. k+31 is one sub-block sb = (k >> 5) & 7: nibble (sb & 1) of qs bytes [32 (sb >> 1), +32)
 template <> struct Deq32<T_Q4_K> {
+    static constexpr int KPR = 1;                                   // k-steps covered by one Raw
     struct Raw { uint4 hd, qa, qb; int sb; };
     static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
         const uint8_t * b = row + (k >> 8) * 144;
@@ -138,28 +140,34 @@ template <> struct Deq32<T_Q4_K> {
 
 // Q6_K: k .. k+31 is group t = (k >> 5) & 3 of half n128 = (k >> 7) & 1 (ggml-quants.c:1690-1719);
 // blocks are only 2-byte aligned, so the bytes come in as aligned words plus a funnel shift
+// Q6_K: the 32 ql bytes and 32 qh bytes a thread reads hold its weights of TWO k-steps (sub-block groups t and
+// t + 2 are the low and high nibbles of the same bytes), so one Raw is loaded per pair of k-steps.
 template <> struct Deq32<T_Q6_K> {
-    struct Raw { uint32_t ql[9], qh[9], scd[2]; uint32_t sh; int t, n128; uint32_t scsh; };
-    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
+    static constexpr int KPR = 2;
+    struct Raw { uint32_t ql[9], qh[9], sc[2], d; uint32_t sh; int t0; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {      // k: first k-step of the pair
         const uint8_t * b = row + (k >> 8) * 210;
-        r.n128 = (k >> 7) & 1; r.t = (k >> 5) & 3;
-        const uint8_t * pl = b + r.n128 * 64 + (r.t & 1) * 32;          // 32 bytes of ql
-        const uint8_t * ph = b + 128 + r.n128 * 32;                     // 32 bytes of qh
+        const int n128 = (k >> 7) & 1;
+        r.t0 = (k >> 5) & 1;                                            // the pair is (t0, t0 + 2)
+        const uint8_t * pl = b + n128 * 64 + r.t0 * 32;                 // 32 bytes of ql
+        const uint8_t * ph = b + 128 + n128 * 32;                       // 32 bytes of qh
         const uint32_t * al = (const uint32_t *) ((uintptr_t) pl & ~(uintptr_t) 3);
         const uint32_t * ah = (const uint32_t *) ((uintptr_t) ph & ~(uintptr_t) 3);
         r.sh = ((uint32_t) (uintptr_t) pl & 3u) * 8u;                   // pl and ph have the same alignment (offsets differ by a multiple of 4)
 #pragma unroll
         for (int i = 0; i < 9; ++i) { r.ql[i] = __ldg(al + i); r.qh[i] = __ldg(ah + i); }
-        const uint8_t * ps = b + 192 + r.n128 * 8 + 2 * r.t;           // scales[2t], scales[2t+1]; then d at b+208
-        r.scd[0] = *(const uint16_t *) ps;
-        r.scd[1] = *(const uint16_t *) (b + 208);
+        const uint8_t * ps = b + 192 + n128 * 8 + 2 * r.t0;            // scales[2t], scales[2t+1] for t = t0 and t0 + 2; d at b+208
+        r.sc[0] = *(const uint16_t *) ps;
+        r.sc[1] = *(const uint16_t *) (ps + 4);
+        r.d = *(const uint16_t *) (b + 208);
     }
-    static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
-        const float d = __half2float(__ushort_as_half((unsigned short) r.scd[1]));
-        const __half2 dlo = __float2half2_rn(d * (float) (int) (int8_t) (r.scd[0] & 0xff));
-        const __half2 dhi = __float2half2_rn(d * (float) (int) (int8_t) (r.scd[0] >> 8));
+    static __device__ __forceinline__ void get(const Raw & r, int sub, uint32_t (&out)[16]) {
+        const float d = __half2float(__ushort_as_half((unsigned short) r.d));
+        const uint32_t scw = sub ? r.sc[1] : r.sc[0];
+        const __half2 dlo = __float2half2_rn(d * (float) (int) (int8_t) (scw & 0xff));
+        const __half2 dhi = __float2half2_rn(d * (float) (int) (int8_t) (scw >> 8));
         const __half2 off = u32_as_h2(0x50005000u);                     // 32.0 in F16
-        const int hs = 2 * r.t, ns = (r.t & 2) ? 4 : 0;
+        const int hs = 2 * (r.t0 + 2 * sub), ns = sub ? 4 : 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const uint32_t L = __funnelshift_r(r.ql[i], r.ql[i + 1], r.sh), H = __funnelshift_r(r.qh[i], r.qh[i + 1], r.sh);
@@ -173,6 +181,7 @@ template <> struct Deq32<T_Q6_K> {
 
 // Q4_0 / Q8_0: one 32-value block per thread and k-step
 template <> struct Deq32<T_Q4_0> {
+    static constexpr int KPR = 1;                                   // k-steps covered by one Raw
     struct Raw { uint32_t w[4]; uint32_t d; };
     static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
         const uint16_t * b = (const uint16_t *) (row + (k >> 5) * 18);
@@ -193,6 +202,7 @@ template <> struct Deq32<T_Q4_0> {
     }
 };
 template <> struct Deq32<T_Q8_0> {
+    static constexpr int KPR = 1;                                   // k-steps covered by one Raw
     struct Raw { uint32_t w[8]; uint32_t d; };
     static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
         const uint16_t * b = (const uint16_t *) (row + (k >> 5) * 34);
@@ -272,9 +282,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         const uint8_t * wrow = p.W + (int64_t) (wrow_ok ? m0 + r : 0) * p.w_nb1;
         // raw quant bytes of the next TC_PF k-steps are kept in flight in registers (HBM latency is several
         // k-steps long); weights do not depend on the previous kernel, so the first loads precede the wait
-        typename Deq32<T>::Raw raw[TC_PF];
+        constexpr int KPR = Deq32<T>::KPR;                              // k-steps covered by one Raw
+        constexpr int NRAW = TC_PF / KPR;
+        typename Deq32<T>::Raw raw[NRAW];
 #pragma unroll
-        for (int u = 0; u < TC_PF; ++u) if (u < ksteps) Deq32<T>::load(wrow, u * TC_BK + h * 32, raw[u]);
+        for (int u = 0; u < NRAW; ++u) if (u * KPR < ksteps) Deq32<T>::load(wrow, u * KPR * TC_BK + h * 32, raw[u]);
         pdl_wait();
         bool ok = true;
         for (int ks0 = 0; ks0 < ksteps && ok; ks0 += TC_PF) {
@@ -292,8 +304,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
                     tma_load_2d(sa + TC_BM * TC_BK * 2, &xmap, ks * TC_BK, n0, &full_bar[s]);
                 }
                 uint32_t wv[16];
-                Deq32<T>::get(raw[u], wv);
-                if (ks + TC_PF < ksteps) Deq32<T>::load(wrow, (ks + TC_PF) * TC_BK + h * 32, raw[u]);
+                const int ru = u / KPR, sub = u % KPR;        // constants once the loop is unrolled
+                if constexpr (KPR == 1) Deq32<T>::get(raw[ru], wv); else Deq32<T>::get(raw[ru], sub, wv);
+                // the Raw is free after its last k-step: refill it with the one NRAW pairs ahead
+                if (sub == KPR - 1 && ks + 1 + (NRAW - 1) * KPR < ksteps) Deq32<T>::load(wrow, (ks + 1 + (NRAW - 1) * KPR) * TC_BK + h * 32, raw[ru]);
                 if (!wrow_ok) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) wv[i] = 0;

@@ -224,6 +224,7 @@ static void backend_free(ggml_backend_t backend) {
                 ctx->name.c_str(), (unsigned long long) ctx->n_replay, (unsigned long long) ctx->n_capture, (unsigned long long) ctx->n_direct,
                 (unsigned long long) ctx->n_launches);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->tc_xh) cudaFree(ctx->tc_xh);
     for (auto & e : ctx->act_cache) if (e.q) cudaFree(e.q);
     if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
     if (ctx->dyn_dev) cudaFree(ctx->dyn_dev);

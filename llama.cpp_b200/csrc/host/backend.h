@@ -51,9 +51,11 @@ struct BackendCtx {
     struct ActEntry { const void * src_data = nullptr; int64_t K = 0, ncols = 0; void * q = nullptr; size_t cap = 0; };
     ActEntry     act_cache[2];
     int          act_next = 0;
-    void         act_cache_clear() { act_cache[0].src_data = act_cache[1].src_data = nullptr; }
+    // F16 copy of the activations of the most recent tensor-core MUL_MAT (q/k/v and gate/up convert once)
+    void *       tc_xh = nullptr; size_t tc_xh_cap = 0; const void * tc_x_data = nullptr; int64_t tc_x_k = 0, tc_x_n = 0;
+    void         act_cache_clear() { act_cache[0].src_data = act_cache[1].src_data = nullptr; tc_x_data = nullptr; }
     // a node that writes memory starting at `data` makes blocks quantized from the old contents stale
-    void         act_cache_invalidate(const void * data) { for (ActEntry & e : act_cache) if (e.src_data == data) e.src_data = nullptr; }
+    void         act_cache_invalidate(const void * data) { for (ActEntry & e : act_cache) if (e.src_data == data) e.src_data = nullptr; if (tc_x_data == data) tc_x_data = nullptr; }
     ActEntry *   act_cache_find(const void * src_data, int64_t K, int64_t ncols);
     ActEntry *   act_cache_take(const void * src_data, int64_t K, int64_t ncols);   // may allocate (never while capturing)
 

@@ -189,16 +189,35 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
     const int64_t ne11 = X->ne[1], ne12 = X->ne[2], ne13 = X->ne[3];
     if (!ids && ctx->use_tc && mmq_tc_supported(W->type, M, ne11, K) && mmq_tc_ptr_ok(W->type, W->data, W->nb[1], X->data, X->nb[1]) &&
         W->nb[2] % 16 == 0 && W->nb[3] % 16 == 0 && X->nb[2] % 8 == 0 && X->nb[3] % 8 == 0) {
-        // prefill: tensor-core GEMM per 2-D slice (weights broadcast over the batch dims)
-        void * ws = ctx->get_scratch(mmq_tc_workspace_bytes(ne11, K));
+        // prefill: tensor-core GEMM per 2-D slice (weights broadcast over the batch dims).  The F16 copy of the
+        // activations is kept for the next mat-mul that reads the same tensor (wq/wk/wv, gate/up).
+        const size_t need = mmq_tc_workspace_bytes(ne11, K);
+        const bool single = ne12 * ne13 == 1;
+        void * ws = nullptr;
+        bool have = false;
+        if (single) {
+            if (need > ctx->tc_xh_cap) {
+                B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+                if (ctx->tc_xh) B200_CUDA_CHECK(cudaFree(ctx->tc_xh));
+                size_t cap = ctx->tc_xh_cap ? ctx->tc_xh_cap : (size_t) 4 << 20;
+                while (cap < need) cap *= 2;
+                B200_CUDA_CHECK(cudaMalloc(&ctx->tc_xh, cap));
+                ctx->tc_xh_cap = cap; ctx->tc_x_data = nullptr;
+            }
+            ws = ctx->tc_xh;
+            have = ctx->tc_x_data == X->data && ctx->tc_x_k == K && ctx->tc_x_n == ne11;
+            ctx->tc_x_data = X->data; ctx->tc_x_k = K; ctx->tc_x_n = ne11;
+        } else {
+            ws = ctx->get_scratch(need);
+        }
         if (ctx->capture_failed) return false;
         const int64_t r2 = ne12 / W->ne[2], r3 = ne13 / W->ne[3];
         for (int64_t i13 = 0; i13 < ne13; ++i13) for (int64_t i12 = 0; i12 < ne12; ++i12) {
             const char * w = (const char *) W->data + (i12 / r2) * W->nb[2] + (i13 / r3) * W->nb[3];
             const char * x = (const char *) X->data + i12 * X->nb[2] + i13 * X->nb[3];
             char * d = (char *) dst->data + i12 * dst->nb[2] + i13 * dst->nb[3];
-            RUN(launch_mmq_tc(W->type, w, W->nb[1], (const float *) x, X->nb[1], (float *) d, dst->nb[1], M, ne11, K, ws, lc));
-            ctx->n_launches++;
+            RUN(launch_mmq_tc(W->type, w, W->nb[1], (const float *) x, X->nb[1], (float *) d, dst->nb[1], M, ne11, K, ws, lc, have));
+            if (!have) ctx->n_launches++;
         }
         if (sliced && !push_slice(ctx, dst)) return false;
         return true;
@@ -461,8 +480,8 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
                 mu->type == GGML_TYPE_F32 && mu->src[1]->type == GGML_TYPE_F32 && mu->src[1]->nb[0] == 4 && t_can_repeat(mu->src[1], rn)) {
                 void * act = nullptr;
                 ctx->act_cache_invalidate(rn->data);          // (the MUL is often computed in place of the norm's output)
+                ctx->act_cache_invalidate(mu->data);          // written by this launch: cached conversions of its old contents are stale
                 if (act_cacheable(mu) && mu->ne[0] % 128 == 0 && feeds_quant_mul_mat(g, i + 3, mu)) {
-                    ctx->act_cache_invalidate(mu->data);
                     BackendCtx::ActEntry * e = ctx->act_cache_take(mu->data, mu->ne[0], mu->ne[1] * mu->ne[2] * mu->ne[3]);
                     if (!e) return fail();
                     act = e->q;

@@ -426,9 +426,9 @@ static cudaError_t launch_tc_t(const TcParams & p, int device, int use_pdl, cuda
 }
 
 cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float * X, int64_t x_nb1, float * dst, int64_t dst_nb1,
-                          int64_t M, int64_t N, int64_t K, void * workspace, const LaunchCtx & c) {
+                          int64_t M, int64_t N, int64_t K, void * workspace, const LaunchCtx & c, bool preconverted) {
     __half * xh = (__half *) workspace;
-    {
+    if (!preconverted) {                 // (the caller may keep the F16 copy of X for the next mat-mul on the same activations)
         const int64_t total = N * K / 2;
         int64_t g = (total + 255) / 256; if (g > (int64_t) c.sm_count * 8) g = (int64_t) c.sm_count * 8;
         cudaError_t e = launch_k(c.use_pdl, c.stream, tc_convert_x_kernel, dim3((unsigned) g), dim3(256), 0, X, x_nb1, xh, K, N);

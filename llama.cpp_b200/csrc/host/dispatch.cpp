@@ -296,6 +296,35 @@ static bool feeds_quant_mul_mat(const ggml_cgraph * g, int from, const ggml_tens
 
 static bool is_noop(const ggml_tensor * node);
 
+// Prefill: when `t` (F32, dense rows, more than 8 of them) is the activation operand of a tensor-core MUL_MAT a few
+// nodes on, its producer also writes the F16 copy that GEMM reads; returns where to write it, or null.
+static void * tc_f16_out_for(BackendCtx * ctx, const ggml_cgraph * g, int from, const ggml_tensor * t) {
+    if (!ctx->use_tc || t->type != GGML_TYPE_F32 || !t_contiguous(t) || t->ne[1] <= 8 || t->ne[2] != 1 || t->ne[3] != 1) return nullptr;
+    bool feeds = false;
+    for (int i = from; i < g->n_nodes && i < from + 8 && !feeds; ++i) {
+        const ggml_tensor * n = g->nodes[i];
+        if (n->op != GGML_OP_MUL_MAT || n->src[1] != t) continue;
+        const ggml_tensor * W = n->src[0];
+        feeds = !is_float_type(W->type) && mmq_tc_supported(W->type, W->ne[1], t->ne[1], W->ne[0]) &&
+                mmq_tc_ptr_ok(W->type, W->data, W->nb[1], t->data, t->nb[1]) && W->nb[2] % 16 == 0 && W->nb[3] % 16 == 0;
+    }
+    if (!feeds) return nullptr;
+    const size_t need = mmq_tc_workspace_bytes(t->ne[1], t->ne[0]);
+    if (need > ctx->tc_xh_cap) {
+        if (ctx->capturing) return nullptr;
+        B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+        if (ctx->tc_xh) B200_CUDA_CHECK(cudaFree(ctx->tc_xh));
+        size_t cap = ctx->tc_xh_cap ? ctx->tc_xh_cap : (size_t) 4 << 20;
+        while (cap < need) cap *= 2;
+        B200_CUDA_CHECK(cudaMalloc(&ctx->tc_xh, cap));
+        ctx->tc_xh_cap = cap;
+    }
+    ctx->tc_x_data = t->data; ctx->tc_x_k = t->ne[0]; ctx->tc_x_n = t->ne[1];
+    return ctx->tc_xh;
+}
+
+
+
 // do the byte ranges spanned by two tensors intersect?
 static bool t_overlap(const ggml_tensor * a, const ggml_tensor * b) {
     if (!a->data || !b->data) return false;
@@ -461,8 +490,9 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
                     if (!e) return fail();
                     act = e->q;
                 }
+                void * h16 = tc_f16_out_for(ctx, g, i + 2, next);
                 RUN0(launch_rms_norm_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), op_param_f32(dst, 0), act,
-                                         dst->data == next->data ? nullptr : (float *) dst->data, nullptr, nullptr, lc));
+                                         dst->data == next->data ? nullptr : (float *) dst->data, nullptr, nullptr, lc, h16));
                 return 2;
             }
             RUN0(launch_rms_norm(to_desc(a), to_desc(dst), op_param_f32(dst, 0), lc));
@@ -486,8 +516,9 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
                     if (!e) return fail();
                     act = e->q;
                 }
+                void * h16 = tc_f16_out_for(ctx, g, i + 3, mu);
                 RUN0(launch_rms_norm_mul(to_desc(a), to_desc(mu->src[1]), to_desc(mu), op_param_f32(rn, 0), act, rn->data == mu->data ? nullptr : (float *) rn->data,
-                                         (const float *) b->data, (float *) dst->data, lc));
+                                         (const float *) b->data, (float *) dst->data, lc, h16));
                 return 3;
             }
             RUN0(launch_bin_bcast(BIN_ADD, to_desc(a), to_desc(b), to_desc(dst), lc));
@@ -510,7 +541,8 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
                     act = e->q;
                 }
                 // the intermediate silu(gate) is skipped when the product is computed in place of it
-                RUN0(launch_silu_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), act, dst->data == next->data ? nullptr : (float *) dst->data, lc));
+                void * h16 = tc_f16_out_for(ctx, g, jn + 1, next);
+                RUN0(launch_silu_mul(to_desc(a), to_desc(next->src[1]), to_desc(next), act, dst->data == next->data ? nullptr : (float *) dst->data, lc, h16));
                 ctx->node_done[(size_t) jn] = 1;
                 return 1;
             }

@@ -82,7 +82,7 @@ __device__ __forceinline__ void emit_act128(const float (&v)[4], int64_t k0, int
 // ---------------------------------------------------------------------------
 template <bool HAS_W, bool EMIT>
 __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const TensorD dst, float eps, blk_act128 * act, float * norm_out,
-                                const float * addend, float * sum_out) {
+                                const float * addend, float * sum_out, __half * h16) {
     pdl_enter();
     __shared__ float sh[32];
     const int64_t row = blockIdx.x;
@@ -119,6 +119,10 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
         if (in && yn) *(float4 *) (yn + k0) = make_float4(o[0], o[1], o[2], o[3]);
         if (HAS_W) { o[0] *= wv.x; o[1] *= wv.y; o[2] *= wv.z; o[3] *= wv.w; }
         if (in) *(float4 *) (y + k0) = make_float4(o[0], o[1], o[2], o[3]);
+        if (in && h16) {                                          // F16 copy for a tensor-core mat-mul (dense rows of n)
+            __half2 * hp = (__half2 *) (h16 + row * n + k0);
+            hp[0] = __floats2half2_rn(o[0], o[1]); hp[1] = __floats2half2_rn(o[2], o[3]);
+        }
         if (EMIT && k0 < npad) emit_act128(o, k0, npad, col);     // whole warps take this branch together (npad % 128 == 0)
         return;
     }
@@ -141,6 +145,7 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
             if (yn) yn[i] = v;
             if (HAS_W) v *= wr[i % w.ne[0]];
             y[i] = v;
+            if (h16) h16[row * n + i] = __float2half_rn(v);
         }
     } else {
         // 4 consecutive values per thread so that 8 threads cover one 32-value group
@@ -154,6 +159,7 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
                     if (yn) yn[k0 + i] = v[i];
                     if (HAS_W) v[i] *= wr[(k0 + i) % w.ne[0]];
                     y[k0 + i] = v[i];
+                    if (h16) h16[row * n + k0 + i] = __float2half_rn(v[i]);
                 }
             }
             emit_act128(v, k0, npad, col);
@@ -166,15 +172,15 @@ static int row_block(int64_t n) { return n >= 4096 ? 1024 : (n >= 1024 ? 512 : (
 cudaError_t launch_rms_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c) {
     const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
     if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
-    (void) (launch_err = launch_k(c.use_pdl, c.stream, rms_norm_kernel<false, false>, dim3((unsigned) rows), dim3(row_block(src.ne[0])), 0, src, src, dst, eps, nullptr, nullptr, nullptr, nullptr));
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, rms_norm_kernel<false, false>, dim3((unsigned) rows), dim3(row_block(src.ne[0])), 0, src, src, dst, eps, nullptr, nullptr, nullptr, nullptr, nullptr));
     return B200_LAUNCH_CHECK();
 }
 cudaError_t launch_rms_norm_mul(const TensorD & src, const TensorD & w, const TensorD & dst, float eps, void * act, float * norm_out,
-                                const float * addend, float * sum_out, const LaunchCtx & c) {
+                                const float * addend, float * sum_out, const LaunchCtx & c, void * f16_out) {
     const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
     if (rows == 0 || src.ne[0] == 0) return cudaSuccess;
-    if (act) (void) (launch_err = launch_k(c.use_pdl, c.stream, rms_norm_kernel<true, true>, dim3((unsigned) rows), dim3(row_block(src.ne[0])), 0, src, w, dst, eps, (blk_act128 *) act, norm_out, addend, sum_out));
-    else     (void) (launch_err = launch_k(c.use_pdl, c.stream, rms_norm_kernel<true, false>, dim3((unsigned) rows), dim3(row_block(src.ne[0])), 0, src, w, dst, eps, nullptr, norm_out, addend, sum_out));
+    if (act) (void) (launch_err = launch_k(c.use_pdl, c.stream, rms_norm_kernel<true, true>, dim3((unsigned) rows), dim3(row_block(src.ne[0])), 0, src, w, dst, eps, (blk_act128 *) act, norm_out, addend, sum_out, (__half *) f16_out));
+    else     (void) (launch_err = launch_k(c.use_pdl, c.stream, rms_norm_kernel<true, false>, dim3((unsigned) rows), dim3(row_block(src.ne[0])), 0, src, w, dst, eps, nullptr, norm_out, addend, sum_out, (__half *) f16_out));
     return B200_LAUNCH_CHECK();
 }
 
@@ -349,7 +355,7 @@ cudaError_t launch_clamp(const TensorD & src, const TensorD & dst, float lo, flo
 template <bool EMIT>
 // (no __restrict__: graph allocators compute silu in place of gate and the product in place of either operand)
 __global__ void silu_mul_kernel(const float * g, const float * u, float * y,
-                                int64_t n0, int64_t rows, blk_act128 * act, float * silu_out) {
+                                int64_t n0, int64_t rows, blk_act128 * act, float * silu_out, __half * h16) {
     pdl_enter();
     const int64_t npad = (n0 + 127) & ~(int64_t) 127;
     const int64_t per_row = npad / 4;
@@ -368,20 +374,21 @@ __global__ void silu_mul_kernel(const float * g, const float * u, float * y,
                     if (silu_out) silu_out[row * n0 + k0 + i] = sa;
                     v[i] = sa * u[row * n0 + k0 + i];
                     y[row * n0 + k0 + i] = v[i];
+                    if (h16) h16[row * n0 + k0 + i] = __float2half_rn(v[i]);
                 }
             }
         }
         if (EMIT) emit_act128(v, t < total ? k0 : npad, npad, act + (t < total ? row : 0) * (npad >> 7));
     }
 }
-cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const TensorD & dst, void * act, float * silu_out, const LaunchCtx & c) {
+cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const TensorD & dst, void * act, float * silu_out, const LaunchCtx & c, void * f16_out) {
     const int64_t n0 = gate.ne[0], rows = nelem(gate) / (n0 ? n0 : 1);
     if (n0 == 0 || rows == 0) return cudaSuccess;
     const int64_t threads = ((n0 + 127) / 128 * 32) * rows;
     if (act) (void) (launch_err = launch_k(c.use_pdl, c.stream, silu_mul_kernel<true>, dim3(grid_for(threads, 256, c.sm_count)), dim3(256), 0, 
-                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, (blk_act128 *) act, silu_out));
+                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, (blk_act128 *) act, silu_out, (__half *) f16_out));
     else     (void) (launch_err = launch_k(c.use_pdl, c.stream, silu_mul_kernel<false>, dim3(grid_for(threads, 256, c.sm_count)), dim3(256), 0, 
-                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, nullptr, silu_out));
+                 (const float *) gate.data, (const float *) up.data, (float *) dst.data, n0, rows, nullptr, silu_out, (__half *) f16_out));
     return B200_LAUNCH_CHECK();
 }
 

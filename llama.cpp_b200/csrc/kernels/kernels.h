@@ -94,13 +94,16 @@ cudaError_t launch_rms_norm(const TensorD & src, const TensorD & dst, float eps,
 // y = rms_norm(x) * w   (w broadcast like ggml MUL's src1); optionally also emits blk_act128 of y
 // norm_out (optional): contiguous rows receiving the plain rms_norm(x).  addend/sum_out (optional, contiguous
 // rows): the input becomes src + addend, which is also written to sum_out (fused residual add)
+// f16_out (optional): dense [rows][ne0] F16 copy of dst, the operand format of the tensor-core mat-mul
 cudaError_t launch_rms_norm_mul(const TensorD & src, const TensorD & w, const TensorD & dst, float eps,
-                                void * act128_out, float * norm_out, const float * addend, float * sum_out, const LaunchCtx & c);
+                                void * act128_out, float * norm_out, const float * addend, float * sum_out, const LaunchCtx & c,
+                                void * f16_out = nullptr);
 cudaError_t launch_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c);
 cudaError_t launch_bin_bcast(int op, const TensorD & a, const TensorD & b, const TensorD & dst, const LaunchCtx & c);
 cudaError_t launch_unary(int op, const TensorD & src, const TensorD & dst, const LaunchCtx & c);
 // dst = silu(gate) * up, optionally also emitting blk_act128 of dst
-cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const TensorD & dst, void * act128_out, float * silu_out, const LaunchCtx & c);
+cudaError_t launch_silu_mul(const TensorD & gate, const TensorD & up, const TensorD & dst, void * act128_out, float * silu_out, const LaunchCtx & c,
+                            void * f16_out = nullptr);
 cudaError_t launch_scale(const TensorD & src, const TensorD & dst, float scale, const LaunchCtx & c);
 cudaError_t launch_clamp(const TensorD & src, const TensorD & dst, float lo, float hi, const LaunchCtx & c);
 

@@ -74,11 +74,13 @@ def test_slice_rows():
         row_split.slice_rows(data[:-1], 10, 0, 1)
 
 
-def test_two_gloo_ranks_gather_equals_unsplit(tmp_path, oracle):
+@pytest.mark.parametrize("world", [2, 4])
+def test_gloo_ranks_gather_equals_unsplit(tmp_path, oracle, world):
+    """1000 rows over 2 ranks ([0, 384), [384, 1000)) and over 4 ([0, 128), [128, 384), [384, 640), [640, 1000))."""
     sys.path.insert(0, str(ROOT / "tests"))
     import rank_worker as w
     out = tmp_path / "gathered.npy"
-    run_ranks(2, "cpu_gather", out, timeout=300)
+    run_ranks(world, "cpu_gather", out, timeout=300)
     c = w.CPU_CASE
     rng = np.random.default_rng(c["seed"])
     wq = oracle.quantize_rows("q8_0", rng.standard_normal((c["m"], c["k"])).astype(np.float32) * 0.02)

@@ -69,6 +69,9 @@ bool        mmvq_stores_to_peers(const MmvqArgs & a);
 // direct 128-bit-coalesced variant for Q4_K / Q5_K (mmvq_k.cu); launch_mmvq routes to it when applicable
 bool        mmvq_k_applicable(const MmvqArgs & a);
 cudaError_t launch_mmvq_k(const MmvqArgs & a, cudaStream_t stream);
+// warp-staged variant for Q4_0 / Q8_0 (mmvq_q32.cu)
+bool        mmvq_q32_applicable(const MmvqArgs & a);
+cudaError_t launch_mmvq_q32(const MmvqArgs & a, cudaStream_t stream);
 // warp-staged variant for Q6_K (mmvq_q6k.cu)
 bool        mmvq_q6k_applicable(const MmvqArgs & a);
 cudaError_t launch_mmvq_q6k(const MmvqArgs & a, cudaStream_t stream);

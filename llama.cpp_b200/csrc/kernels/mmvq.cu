@@ -566,11 +566,12 @@ cudaError_t launch_quantize_act128(const float * x, int64_t ne11, int64_t ne12, 
 }
 
 // do the kernels launch_mmvq picks for these arguments honour n_peer / peer_delta?
-bool mmvq_stores_to_peers(const MmvqArgs & a) { return mmvq_k_applicable(a) || mmvq_q6k_applicable(a); }
+bool mmvq_stores_to_peers(const MmvqArgs & a) { return mmvq_k_applicable(a) || mmvq_q6k_applicable(a) || mmvq_q32_applicable(a); }
 
 cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream) {
     if (mmvq_k_applicable(a)) return launch_mmvq_k(a, stream);
     if (mmvq_q6k_applicable(a)) return launch_mmvq_q6k(a, stream);
+    if (mmvq_q32_applicable(a)) return launch_mmvq_q32(a, stream);
     MmvqParams p = {};
     p.W = (const uint8_t *) a.W; p.w_nb1 = a.w_nb1; p.w_nb2 = a.w_nb2; p.w_nb3 = a.w_nb3;
     p.Xq = (const uint8_t *) a.Xq; p.xq_col_bytes = (int64_t) ((a.K + 127) / 128) * 160;

@@ -180,15 +180,24 @@ template <> struct Deq32<T_Q6_K> {
 };
 
 // Q4_0 / Q8_0: one 32-value block per thread and k-step
+// A block {fp16 d, NQ words of quants} at a 2-byte aligned address: read as aligned 32-bit words (at most two bytes past the
+// block; every buffer has tail slack) and realigned with one funnel shift per word.
+template <int NQ>
+__device__ __forceinline__ void load_block32(const uint8_t * pb, uint32_t (&q)[NQ], uint32_t & d) {
+    const uint32_t * al = (const uint32_t *) ((uintptr_t) pb & ~(uintptr_t) 3);
+    const bool odd = ((uintptr_t) pb & 2) != 0;                     // block starts in the upper half of al[0]
+    uint32_t w[NQ + 1];
+#pragma unroll
+    for (int i = 0; i < NQ + 1; ++i) w[i] = __ldg(al + i);
+    d = odd ? (w[0] >> 16) : (w[0] & 0xffffu);
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) q[i] = odd ? w[i + 1] : __funnelshift_r(w[i], w[i + 1], 16);
+}
+
 template <> struct Deq32<T_Q4_0> {
     static constexpr int KPR = 1;                                   // k-steps covered by one Raw
     struct Raw { uint32_t w[4]; uint32_t d; };
-    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
-        const uint16_t * b = (const uint16_t *) (row + (k >> 5) * 18);
-        r.d = b[0];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) r.w[i] = (uint32_t) b[1 + 2 * i] | ((uint32_t) b[2 + 2 * i] << 16);
-    }
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) { load_block32<4>(row + (k >> 5) * 18, r.w, r.d); }
     static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
         const __half2 d = __half2half2(__ushort_as_half((unsigned short) r.d)), off = u32_as_h2(0x48004800u);   // 8.0
 #pragma unroll
@@ -204,12 +213,7 @@ template <> struct Deq32<T_Q4_0> {
 template <> struct Deq32<T_Q8_0> {
     static constexpr int KPR = 1;                                   // k-steps covered by one Raw
     struct Raw { uint32_t w[8]; uint32_t d; };
-    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
-        const uint16_t * b = (const uint16_t *) (row + (k >> 5) * 34);
-        r.d = b[0];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) r.w[i] = (uint32_t) b[1 + 2 * i] | ((uint32_t) b[2 + 2 * i] << 16);
-    }
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) { load_block32<8>(row + (k >> 5) * 34, r.w, r.d); }
     static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
         const __half2 d = __half2half2(__ushort_as_half((unsigned short) r.d)), off = u32_as_h2(0x58005800u);   // 128.0
 #pragma unroll

@@ -210,13 +210,16 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
         } else {
             ws = ctx->get_scratch(need);
         }
+        const size_t pbytes = single ? mmq_tc_partial_bytes(M, ne11, K, lc.sm_count) : 0;     // split-K partial tiles
+        void * partials = pbytes ? ctx->get_scratch(pbytes) : nullptr;
         if (ctx->capture_failed) return false;
         const int64_t r2 = ne12 / W->ne[2], r3 = ne13 / W->ne[3];
         for (int64_t i13 = 0; i13 < ne13; ++i13) for (int64_t i12 = 0; i12 < ne12; ++i12) {
             const char * w = (const char *) W->data + (i12 / r2) * W->nb[2] + (i13 / r3) * W->nb[3];
             const char * x = (const char *) X->data + i12 * X->nb[2] + i13 * X->nb[3];
             char * d = (char *) dst->data + i12 * dst->nb[2] + i13 * dst->nb[3];
-            RUN(launch_mmq_tc(W->type, w, W->nb[1], (const float *) x, X->nb[1], (float *) d, dst->nb[1], M, ne11, K, ws, lc, have));
+            RUN(launch_mmq_tc(W->type, w, W->nb[1], (const float *) x, X->nb[1], (float *) d, dst->nb[1], M, ne11, K, ws, lc, have, partials));
+            if (partials) ctx->n_launches++;
             if (!have) ctx->n_launches++;
         }
         if (sliced && !push_slice(ctx, dst)) return false;

@@ -94,7 +94,7 @@ static TensorD desc(void * data, int type, int64_t ne0, int64_t ne1, int64_t ne2
 API size_t b200_mul_mat_q_scratch_bytes(int type, int64_t M, int64_t K, int64_t N) {
     (void) M;
     size_t s = act128_bytes(K, N);
-    if (mmq_tc_supported(type, M, N, K)) { const size_t t = mmq_tc_workspace_bytes(N, K); if (t > s) s = t; }
+    if (mmq_tc_supported(type, M, N, K)) { const size_t t = mmq_tc_workspace_bytes(N, K) + mmq_tc_partial_bytes(M, N, K, 148); if (t > s) s = t; }
     return s;
 }
 
@@ -105,7 +105,8 @@ API int b200_mul_mat_q(int type, const void * W, int64_t w_nb1, int64_t M, int64
     if (scratch_bytes < b200_mul_mat_q_scratch_bytes(type, M, K, N)) return fail(B200_E_SCRATCH, "scratch buffer too small");
     LaunchCtx lc; int rc = get_ctx(stream, lc); if (rc) return rc;
     if (mmq_tc_supported(type, M, N, K) && mmq_tc_ptr_ok(type, W, w_nb1, X, x_stride * 4)) {
-        CK(launch_mmq_tc(type, W, w_nb1, X, x_stride * 4, dst, dst_stride * 4, M, N, K, scratch, lc));
+        void * partials = mmq_tc_partial_bytes(M, N, K, lc.sm_count) ? (char *) scratch + mmq_tc_workspace_bytes(N, K) : nullptr;
+        CK(launch_mmq_tc(type, W, w_nb1, X, x_stride * 4, dst, dst_stride * 4, M, N, K, scratch, lc, false, partials));
         return 0;
     }
     CK(launch_quantize_act128(X, N, 1, 1, x_stride, 0, 0, scratch, (int) K, lc.stream));

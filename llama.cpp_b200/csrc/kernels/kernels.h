@@ -86,7 +86,10 @@ size_t      mmq_tc_workspace_bytes(int64_t N, int64_t K);
 bool        mmq_tc_ptr_ok(int type, const void * W, int64_t w_nb1, const void * X, int64_t x_nb1_bytes);
 cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float * X, int64_t x_nb1,
                           float * dst, int64_t dst_nb1, int64_t M, int64_t N, int64_t K,
-                          void * workspace, const LaunchCtx & c, bool preconverted = false);   // preconverted: workspace already holds X as F16
+                          void * workspace, const LaunchCtx & c, bool preconverted = false,    // preconverted: workspace already holds X as F16
+                          void * partials = nullptr);   // mmq_tc_partial_bytes() of scratch enables split-K when the output has few tiles
+int         mmq_tc_ksplit(int64_t M, int64_t N, int64_t K, int sm_count);
+size_t      mmq_tc_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count);
 
 // ---- glue ops (glue.cu) ----
 enum BinOp { BIN_ADD = 0, BIN_SUB = 1, BIN_MUL = 2, BIN_DIV = 3 };

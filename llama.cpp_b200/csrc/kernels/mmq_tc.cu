@@ -243,6 +243,9 @@ struct TcParams {
     float * dst; int64_t dst_nb1;      // bytes between token columns
     int M, N, K;
     int * status;
+    // split-K (few output tiles): CTA z handles k-steps [z * kps, z * kps + kps) and writes its partial [N][M] tile
+    // set into part + z * M * N; tc_reduce_kernel then sums the splits in order
+    int ksplit, kps; float * part;
 };
 
 __device__ __forceinline__ void tma_load_2d(void * smem_dst, const CUtensorMap * tmap, int x, int y, uint64_t * bar) {
@@ -263,7 +266,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;    // adjacent CTAs share one weight tile (L2 reuse)
-    const int ksteps = p.K / TC_BK;
+    const int ks_begin = (int) blockIdx.z * p.kps;                  // split-K: this CTA's range of k-steps
+    const int ksteps = min(p.kps, p.K / TC_BK - ks_begin);
+    const int k_base = ks_begin * TC_BK;
     constexpr int MMA_WARP = TC_PRODUCERS / 32;
 
     if (tid == 0) {
@@ -290,7 +295,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         constexpr int NRAW = TC_PF / KPR;
         typename Deq32<T>::Raw raw[NRAW];
 #pragma unroll
-        for (int u = 0; u < NRAW; ++u) if (u * KPR < ksteps) Deq32<T>::load(wrow, u * KPR * TC_BK + h * 32, raw[u]);
+        for (int u = 0; u < NRAW; ++u) if (u * KPR < ksteps) Deq32<T>::load(wrow, k_base + u * KPR * TC_BK + h * 32, raw[u]);
         pdl_wait();
         bool ok = true;
         for (int ks0 = 0; ks0 < ksteps && ok; ks0 += TC_PF) {
@@ -305,13 +310,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
                 uint8_t * sa = smem + (size_t) s * TC_STAGE_BYTES;      // A: weights 128 x 64 F16
                 if (tid == 0) {                                         // B: activations 128 x 64 F16 by TMA (rows past N read as zero)
                     mbar_arrive_expect_tx(&full_bar[s], TC_BN * TC_BK * 2);
-                    tma_load_2d(sa + TC_BM * TC_BK * 2, &xmap, ks * TC_BK, n0, &full_bar[s]);
+                    tma_load_2d(sa + TC_BM * TC_BK * 2, &xmap, k_base + ks * TC_BK, n0, &full_bar[s]);
                 }
                 uint32_t wv[16];
                 const int ru = u / KPR, sub = u % KPR;        // constants once the loop is unrolled
                 if constexpr (KPR == 1) Deq32<T>::get(raw[ru], wv); else Deq32<T>::get(raw[ru], sub, wv);
                 // the Raw is free after its last k-step: refill it with the one NRAW pairs ahead
-                if (sub == KPR - 1 && ks + 1 + (NRAW - 1) * KPR < ksteps) Deq32<T>::load(wrow, (ks + 1 + (NRAW - 1) * KPR) * TC_BK + h * 32, raw[ru]);
+                if (sub == KPR - 1 && ks + 1 + (NRAW - 1) * KPR < ksteps) Deq32<T>::load(wrow, k_base + (ks + 1 + (NRAW - 1) * KPR) * TC_BK + h * 32, raw[ru]);
                 if (!wrow_ok) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) wv[i] = 0;
@@ -331,6 +336,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
             tc_fence_after();
             const int quad = warp & 3, chalf = warp >> 2;               // lane quadrant; which 64 of the 128 columns
             const int m = m0 + quad * 32 + lane;
+            char * out = p.ksplit > 1 ? (char *) (p.part + (int64_t) blockIdx.z * p.M * p.N) : (char *) p.dst;
+            const int64_t out_nb1 = p.ksplit > 1 ? (int64_t) p.M * 4 : p.dst_nb1;
 #pragma unroll 1
             for (int c0 = chalf * 64; c0 < chalf * 64 + 64; c0 += 32) {
                 uint32_t v[32];
@@ -340,7 +347,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int n = n0 + c0 + i;
-                        if (n < p.N) *(float *) ((char *) p.dst + (int64_t) n * p.dst_nb1 + (int64_t) m * 4) = __uint_as_float(v[i]);
+                        if (n < p.N) *(float *) (out + (int64_t) n * out_nb1 + (int64_t) m * 4) = __uint_as_float(v[i]);
                     }
                 }
             }
@@ -405,6 +412,33 @@ static encode_tiled_fn get_encode_tiled() {
     return fn;
 }
 
+// sums the split-K partials in split order (deterministic)
+__global__ void tc_reduce_kernel(const float * __restrict__ part, float * dst, int64_t dst_nb1, int M, int N, int ksplit) {
+    pdl_enter();
+    const int64_t total = (int64_t) M * N;
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
+        float acc = part[i];
+        for (int z = 1; z < ksplit; ++z) acc += part[(int64_t) z * total + i];
+        const int64_t n = i / M, m = i - n * M;
+        *(float *) ((char *) dst + n * dst_nb1 + m * 4) = acc;
+    }
+}
+
+// With few output tiles (small M or N) the K range is divided over several CTAs so that the GPU is filled; every
+// split keeps at least 8 k-steps and an even number of them (the Q6_K producer works on pairs).
+int mmq_tc_ksplit(int64_t M, int64_t N, int64_t K, int sm_count) {
+    const int64_t tiles = ((M + TC_BM - 1) / TC_BM) * ((N + TC_BN - 1) / TC_BN);
+    const int64_t ksteps = K / TC_BK;
+    int64_t s = sm_count / (tiles > 0 ? tiles : 1);
+    if (s > 8) s = 8;
+    while (s > 1 && (ksteps / s < 8)) --s;
+    return s < 2 ? 1 : (int) s;
+}
+size_t mmq_tc_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count) {
+    const int s = mmq_tc_ksplit(M, N, K, sm_count);
+    return s > 1 ? (size_t) s * M * N * 4 + 256 : 0;
+}
+
 template <int T>
 static cudaError_t launch_tc_t(const TcParams & p, int device, int use_pdl, cudaStream_t stream) {
     auto kern = mmq_tc_kernel<T>;
@@ -425,12 +459,16 @@ static cudaError_t launch_tc_t(const TcParams & p, int device, int use_pdl, cuda
     if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *) p.Xh, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    dim3 grid((unsigned) ((p.N + TC_BN - 1) / TC_BN), (unsigned) ((p.M + TC_BM - 1) / TC_BM));
-    return launch_k(use_pdl, stream, kern, grid, dim3(TC_THREADS), smem, p, xmap);
+    dim3 grid((unsigned) ((p.N + TC_BN - 1) / TC_BN), (unsigned) ((p.M + TC_BM - 1) / TC_BM), (unsigned) p.ksplit);
+    cudaError_t e = launch_k(use_pdl, stream, kern, grid, dim3(TC_THREADS), smem, p, xmap);
+    if (e != cudaSuccess || p.ksplit == 1) return e;
+    const int64_t total = (int64_t) p.M * p.N;
+    int64_t g = (total + 255) / 256; if (g > 148 * 8) g = 148 * 8;
+    return launch_k(use_pdl, stream, tc_reduce_kernel, dim3((unsigned) g), dim3(256), 0, (const float *) p.part, p.dst, p.dst_nb1, p.M, p.N, p.ksplit);
 }
 
 cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float * X, int64_t x_nb1, float * dst, int64_t dst_nb1,
-                          int64_t M, int64_t N, int64_t K, void * workspace, const LaunchCtx & c, bool preconverted) {
+                          int64_t M, int64_t N, int64_t K, void * workspace, const LaunchCtx & c, bool preconverted, void * partials) {
     __half * xh = (__half *) workspace;
     if (!preconverted) {                 // (the caller may keep the F16 copy of X for the next mat-mul on the same activations)
         const int64_t total = N * K / 2;
@@ -441,6 +479,11 @@ cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float *
     TcParams p;
     p.W = (const uint8_t *) W; p.w_nb1 = w_nb1; p.Xh = xh; p.dst = dst; p.dst_nb1 = dst_nb1;
     p.M = (int) M; p.N = (int) N; p.K = (int) K; p.status = c.status;
+    p.ksplit = partials ? mmq_tc_ksplit(M, N, K, c.sm_count) : 1;
+    const int ksteps = (int) (K / TC_BK);
+    p.kps = (ksteps + p.ksplit - 1) / p.ksplit; p.kps += p.kps & 1;          // even
+    p.ksplit = (ksteps + p.kps - 1) / p.kps;                                   // splits that actually have work
+    p.part = (float *) partials;
     switch (type) {
         case T_Q4_0: return launch_tc_t<T_Q4_0>(p, c.device, c.use_pdl, c.stream);
         case T_Q4_1: return launch_tc_t<T_Q4_1>(p, c.device, c.use_pdl, c.stream);

@@ -17,7 +17,7 @@ namespace b200 {
 enum : int {
     T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8,
     T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14,
-    T_I32 = 26, T_BF16 = 30,
+    T_IQ4_NL = 20, T_I32 = 26, T_BF16 = 30,
 };
 
 #pragma pack(push, 1)
@@ -29,10 +29,14 @@ struct blk_q8_0 { uint16_t d; int8_t qs[32]; };                                 
 struct blk_q4_K { uint16_t d; uint16_t dmin; uint8_t scales[12]; uint8_t qs[128]; };        // 144 B / 256 w
 struct blk_q5_K { uint16_t d; uint16_t dmin; uint8_t scales[12]; uint8_t qh[32]; uint8_t qs[128]; }; // 176 B
 struct blk_q6_K { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; uint16_t d; };        // 210 B / 256 w
+struct blk_q2_K { uint8_t scales[16]; uint8_t qs[64]; uint16_t d; uint16_t dmin; };         // 84 B / 256 w
+struct blk_q3_K { uint8_t hmask[32]; uint8_t qs[64]; uint8_t scales[12]; uint16_t d; };     // 110 B / 256 w
+struct blk_iq4_nl { uint16_t d; uint8_t qs[16]; };                                          // 18 B / 32 w
 #pragma pack(pop)
 static_assert(sizeof(blk_q4_0) == 18 && sizeof(blk_q4_1) == 20 && sizeof(blk_q5_0) == 22, "block size");
 static_assert(sizeof(blk_q5_1) == 24 && sizeof(blk_q8_0) == 34, "block size");
 static_assert(sizeof(blk_q4_K) == 144 && sizeof(blk_q5_K) == 176 && sizeof(blk_q6_K) == 210, "block size");
+static_assert(sizeof(blk_q2_K) == 84 && sizeof(blk_q3_K) == 110 && sizeof(blk_iq4_nl) == 18, "block size");
 
 // Activation blocks produced on the device for the integer dot products:
 // 128 consecutive values of one activation column = 4 groups of 32 int8 plus,
@@ -44,8 +48,8 @@ static_assert(sizeof(blk_act128) == 160, "activation block size");
 __host__ __device__ inline int type_block_elems(int t) {
     switch (t) {
         case T_F32: case T_F16: case T_BF16: case T_I32: return 1;
-        case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: return 32;
-        case T_Q4_K: case T_Q5_K: case T_Q6_K: return 256;
+        case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: case T_IQ4_NL: return 32;
+        case T_Q2_K: case T_Q3_K: case T_Q4_K: case T_Q5_K: case T_Q6_K: return 256;
         default: return 0;
     }
 }
@@ -55,6 +59,7 @@ __host__ __device__ inline int type_block_bytes(int t) {
         case T_F16: case T_BF16: return 2;
         case T_Q4_0: return 18; case T_Q4_1: return 20; case T_Q5_0: return 22; case T_Q5_1: return 24;
         case T_Q8_0: return 34; case T_Q4_K: return 144; case T_Q5_K: return 176; case T_Q6_K: return 210;
+        case T_Q2_K: return 84; case T_Q3_K: return 110; case T_IQ4_NL: return 18;
         default: return 0;
     }
 }
@@ -78,6 +83,7 @@ __device__ __forceinline__ void k4_scale_min(int j, const uint8_t * q, int & sc,
 // fused multiply-add, so that results are bit-identical to the CPU code:
 //   q4_0 ggml-quants.c:255-273   q4_1 :275-294   q5_0 :296-320   q5_1 :322-347
 //   q8_0 :349-363   q4_K :1280-1302   q5_K :1482-1507   q6_K :1690-1719
+//   q2_K :712-744   q3_K :1056-1106   iq4_nl :2434-2451
 template <int T> __device__ __forceinline__ float dequant_elem(const uint8_t * row, int64_t i);
 
 template <> __device__ __forceinline__ float dequant_elem<T_F32>(const uint8_t * row, int64_t i) {
@@ -150,6 +156,44 @@ template <> __device__ __forceinline__ float dequant_elem<T_Q6_K>(const uint8_t 
     const int q  = (int) (int8_t) (lo | (hi << 4)) - 32;
     const int sc = b->scales[n * 8 + (l >> 4) + 2 * grp];
     return __fmul_rn(__fmul_rn(h2f(b->d), (float) sc), (float) q);
+}
+
+// Q2_K: 16 sub-blocks of 16 weights; scales[s] = 4-bit scale | 4-bit min << 4; weight l of the 128-half n, 32-run j
+// is bits [2j, 2j+2) of qs[32 n + l]
+template <> __device__ __forceinline__ float dequant_elem<T_Q2_K>(const uint8_t * row, int64_t i) {
+    const blk_q2_K * b = (const blk_q2_K *) row + (i >> 8);
+    const int r = i & 255, n = r >> 7, j = (r & 127) >> 5, l = r & 31;
+    const uint8_t sc = b->scales[n * 8 + 2 * j + (l >> 4)];
+    const float dl = __fmul_rn(h2f(b->d), (float) (sc & 0xF));
+    const float ml = __fmul_rn(h2f(b->dmin), (float) (sc >> 4));
+    const int q = (b->qs[n * 32 + l] >> (2 * j)) & 3;
+    return __fsub_rn(__fmul_rn(dl, (float) q), ml);
+}
+// 6-bit scale s (0..15) of a Q3_K super-block, before the -32 offset (the aux[] shuffle of ggml-quants.c:1075-1080)
+__device__ __forceinline__ int q3k_scale(const uint8_t * scales, int s) {
+    const int lo = s < 8 ? (scales[s] & 0xF) : (scales[s - 8] >> 4);
+    const int hi = (scales[8 + (s & 3)] >> (2 * (s >> 2))) & 3;
+    return lo | (hi << 4);
+}
+// Q3_K: low 2 bits as Q2_K, third bit in hmask[l] bit (4 n + j); a clear bit subtracts 4
+template <> __device__ __forceinline__ float dequant_elem<T_Q3_K>(const uint8_t * row, int64_t i) {
+    const blk_q3_K * b = (const blk_q3_K *) row + (i >> 8);
+    const int r = i & 255, n = r >> 7, j = (r & 127) >> 5, l = r & 31;
+    const float dl = __fmul_rn(h2f(b->d), (float) (q3k_scale(b->scales, n * 8 + 2 * j + (l >> 4)) - 32));
+    const int q = ((b->qs[n * 32 + l] >> (2 * j)) & 3) - (((b->hmask[l] >> (4 * n + j)) & 1) ? 0 : 4);
+    return __fmul_rn(dl, (float) q);
+}
+// IQ4_NL: Q4_0 layout with the nibble mapped through the 16-entry non-linear table of the format
+// (kvalues_iq4nl, ggml-quants.c:2434), held here as two 64-bit words of int8
+__device__ __forceinline__ int iq4nl_value(int idx) {
+    const uint64_t t = idx < 8 ? 0xF6EADDCFBFAD9881ull : 0x7159453526190D01ull;
+    return (int) (int8_t) (t >> (8 * (idx & 7)));
+}
+template <> __device__ __forceinline__ float dequant_elem<T_IQ4_NL>(const uint8_t * row, int64_t i) {
+    const blk_iq4_nl * b = (const blk_iq4_nl *) row + (i >> 5);
+    const int j = i & 31;
+    const int q = j < 16 ? (b->qs[j] & 0x0F) : (b->qs[j - 16] >> 4);
+    return __fmul_rn(h2f(b->d), (float) iq4nl_value(q));
 }
 
 // ---------------------------------------------------------------------------

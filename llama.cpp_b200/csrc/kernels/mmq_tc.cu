@@ -493,6 +493,9 @@ cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float *
         case T_Q4_K: return launch_tc_t<T_Q4_K>(p, c.device, c.use_pdl, c.stream);
         case T_Q5_K: return launch_tc_t<T_Q5_K>(p, c.device, c.use_pdl, c.stream);
         case T_Q6_K: return launch_tc_t<T_Q6_K>(p, c.device, c.use_pdl, c.stream);
+        case T_Q2_K: return launch_tc_t<T_Q2_K>(p, c.device, c.use_pdl, c.stream);
+        case T_Q3_K: return launch_tc_t<T_Q3_K>(p, c.device, c.use_pdl, c.stream);
+        case T_IQ4_NL: return launch_tc_t<T_IQ4_NL>(p, c.device, c.use_pdl, c.stream);
     }
     return cudaErrorInvalidValue;
 }

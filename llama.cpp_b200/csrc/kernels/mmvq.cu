@@ -323,6 +323,89 @@ template <> struct WT<T_Q6_K> {
     }
 };
 
+// Q2_K: a unit is the 32 weights of (128-half n, bit pair j): bits [2j, 2j+2) of 32 consecutive qs bytes, two
+// 16-weight sub-blocks with a 4-bit scale and a 4-bit min each (ggml-quants.c:712-744); the mins need the
+// activation sums of the two 16-value halves, taken here with a dot against ones.
+template <> struct WT<T_Q2_K> {
+    static constexpr int UNIT = 32, BLK_ELEMS = 256, BLK_BYTES = 84;
+    template <int N> static __device__ __forceinline__ void dot(const uint8_t * row, int u, const ActView & xv, float (&acc)[N]) {
+        const uint8_t * b = row + (u >> 3) * 84;
+        const int n128 = (u >> 2) & 1, j = u & 3;
+        const int sc0 = b[n128 * 8 + 2 * j], sc1 = b[n128 * 8 + 2 * j + 1];
+        const float d = h2f(*(const uint16_t *) (b + 80)), dmin = h2f(*(const uint16_t *) (b + 82));
+        uint32_t w[8];
+        lds_words<8>(b + 16 + n128 * 32, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = (w[i] >> (2 * j)) & 0x03030303u;
+#pragma unroll
+        for (int n = 0; n < N; ++n) {
+            const int * xq = xv.q32(n, u);
+            int s0 = 0, s1 = 0, x0 = 0, x1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                s0 = __dp4a((int) w[i], xq[i], s0);         x0 = __dp4a(0x01010101, xq[i], x0);
+                s1 = __dp4a((int) w[i + 4], xq[i + 4], s1); x1 = __dp4a(0x01010101, xq[i + 4], x1);
+            }
+            acc[n] += xv.ds(n, u).x * (d * (float) ((sc0 & 15) * s0 + (sc1 & 15) * s1) - dmin * (float) ((sc0 >> 4) * x0 + (sc1 >> 4) * x1));
+        }
+    }
+};
+
+// Q3_K: the same unit; the third bit of weight l is bit (4 n + j) of hmask[l], a clear bit subtracts 4, and the
+// 6-bit scales carry an offset of 32 (ggml-quants.c:1056-1106)
+template <> struct WT<T_Q3_K> {
+    static constexpr int UNIT = 32, BLK_ELEMS = 256, BLK_BYTES = 110;
+    template <int N> static __device__ __forceinline__ void dot(const uint8_t * row, int u, const ActView & xv, float (&acc)[N]) {
+        const uint8_t * b = row + (u >> 3) * 110;
+        const int n128 = (u >> 2) & 1, j = u & 3;
+        const int sc0 = q3k_scale(b + 96, n128 * 8 + 2 * j) - 32, sc1 = q3k_scale(b + 96, n128 * 8 + 2 * j + 1) - 32;
+        const float d = h2f(*(const uint16_t *) (b + 108));
+        uint32_t w[8], h[8];
+        lds_words<8>(b + 32 + n128 * 32, w);
+        lds_words<8>(b, h);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            w[i] = __vsub4(((w[i] >> (2 * j)) & 0x03030303u) | (((h[i] >> (4 * n128 + j)) & 0x01010101u) << 2), 0x04040404u);
+#pragma unroll
+        for (int n = 0; n < N; ++n) {
+            const int * xq = xv.q32(n, u);
+            int s0 = 0, s1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { s0 = __dp4a((int) w[i], xq[i], s0); s1 = __dp4a((int) w[i + 4], xq[i + 4], s1); }
+            acc[n] += d * xv.ds(n, u).x * (float) (sc0 * s0 + sc1 * s1);
+        }
+    }
+};
+
+// IQ4_NL: Q4_0 layout, nibbles looked up in the 16-entry table of the format (ggml-quants.c:2434): four lookups
+// at once with two byte permutes over the table halves and a select on bit 3 of each index
+__device__ __forceinline__ uint32_t iq4nl_lut4(uint32_t idx) {          // idx: four byte lanes, each 0..15
+    const uint32_t s = idx & 0x07070707u, t = s | (s >> 4);
+    const uint32_t sel = (t & 0xFFu) | ((t >> 8) & 0xFF00u);
+    const uint32_t lo = __byte_perm(0xBFAD9881u, 0xF6EADDCFu, sel), hi = __byte_perm(0x26190D01u, 0x71594535u, sel);
+    const uint32_t m = ((idx >> 3) & 0x01010101u) * 0xFFu;
+    return (lo & ~m) | (hi & m);
+}
+template <> struct WT<T_IQ4_NL> {
+    static constexpr int UNIT = 32, BLK_ELEMS = 32, BLK_BYTES = 18;
+    template <int N> static __device__ __forceinline__ void dot(const uint8_t * row, int u, const ActView & xv, float (&acc)[N]) {
+        const uint8_t * b = row + u * 18;
+        const float dw = h2f(*(const uint16_t *) b);
+        uint32_t w[4], lo[4], hi[4];
+        lds_words<4>(b + 2, w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { lo[i] = iq4nl_lut4(w[i] & 0x0F0F0F0Fu); hi[i] = iq4nl_lut4((w[i] >> 4) & 0x0F0F0F0Fu); }
+#pragma unroll
+        for (int n = 0; n < N; ++n) {
+            const int * xq = xv.q32(n, u);
+            int s = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { s = __dp4a((int) lo[i], xq[i], s); s = __dp4a((int) hi[i], xq[i + 4], s); }
+            acc[n] += dw * xv.ds(n, u).x * (float) s;
+        }
+    }
+};
+
 // ---------------------------------------------------------------------------
 // the streaming kernel
 // ---------------------------------------------------------------------------
@@ -489,7 +572,7 @@ static cudaError_t launch_mmvq_tn(const MmvqParams & p0, int sm_count, cudaStrea
     // chunks) stays near 44 KB and 4 stages fit one CTA
     const int units_total   = p.K / W::UNIT;
     const int units_per_256 = 256 / W::UNIT;
-    const int unit_w_bytes  = W::BLK_BYTES * W::UNIT / W::BLK_ELEMS;
+    const int unit_w_bytes  = (W::BLK_BYTES * W::UNIT + W::BLK_ELEMS - 1) / W::BLK_ELEMS;   // Q2_K, Q3_K, Q6_K: fractional, rounded up
     const int per_unit      = MMVQ_WARPS * unit_w_bytes + N * (W::UNIT * 160 / 128);
     int cu = (44 * 1024 - MMVQ_WARPS * 48) / per_unit;
     const int cu_cap = 2304 / unit_w_bytes;            // ~2.25 KB per row segment is plenty
@@ -498,7 +581,7 @@ static cudaError_t launch_mmvq_tn(const MmvqParams & p0, int sm_count, cudaStrea
     if (cu < 32) cu = 32;
     if (cu > units_total) cu = ((units_total + units_per_256 - 1) / units_per_256) * units_per_256;
     p.chunk_units = cu;
-    const int seg_bytes = cu * unit_w_bytes;
+    const int seg_bytes = (cu * W::BLK_BYTES * W::UNIT + W::BLK_ELEMS - 1) / W::BLK_ELEMS;
     p.slot_bytes  = ((seg_bytes + 15 + 15) & ~15) + 16;
     p.xslot_bytes = ((cu * W::UNIT + 127) / 128) * 160;
     const size_t smem = (size_t) MMVQ_STAGES * (MMVQ_WARPS * p.slot_bytes + N * p.xslot_bytes);
@@ -546,8 +629,8 @@ static cudaError_t launch_mmvq_t(const MmvqParams & p, int sm, cudaStream_t st) 
 
 bool mmvq_type_supported(int type) {
     switch (type) {
-        case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0:
-        case T_Q4_K: case T_Q5_K: case T_Q6_K: return true;
+        case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: case T_IQ4_NL:
+        case T_Q2_K: case T_Q3_K: case T_Q4_K: case T_Q5_K: case T_Q6_K: return true;
         default: return false;
     }
 }
@@ -589,6 +672,9 @@ cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream) {
         case T_Q4_K: return launch_mmvq_t<T_Q4_K>(p, a.sm_count, stream);
         case T_Q5_K: return launch_mmvq_t<T_Q5_K>(p, a.sm_count, stream);
         case T_Q6_K: return launch_mmvq_t<T_Q6_K>(p, a.sm_count, stream);
+        case T_Q2_K: return launch_mmvq_t<T_Q2_K>(p, a.sm_count, stream);
+        case T_Q3_K: return launch_mmvq_t<T_Q3_K>(p, a.sm_count, stream);
+        case T_IQ4_NL: return launch_mmvq_t<T_IQ4_NL>(p, a.sm_count, stream);
         default: return cudaErrorInvalidValue;
     }
 }

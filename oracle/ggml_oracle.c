@@ -20,7 +20,7 @@
 
 #define EXPORT __attribute__((visibility("default")))
 
-enum { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14 };
+enum { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ4_NL = 20 };
 
 /* ---- IEEE half <-> float (ggml_compute_fp16_to_fp32 / fp32_to_fp16, ggml/src/ggml-impl.h:330-400) ---- */
 static float h2f(uint16_t h) {
@@ -73,6 +73,9 @@ typedef struct { uint16_t d, s; int8_t qs[32]; } blk_q8_1;
 typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qs[128]; } blk_q4_K;
 typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qh[32]; uint8_t qs[128]; } blk_q5_K;
 typedef struct { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; uint16_t d; } blk_q6_K;
+typedef struct { uint8_t scales[16]; uint8_t qs[64]; uint16_t d, dmin; } blk_q2_K;
+typedef struct { uint8_t hmask[32]; uint8_t qs[64]; uint8_t scales[12]; uint16_t d; } blk_q3_K;
+typedef struct { uint16_t d; uint8_t qs[16]; } blk_iq4_nl;
 typedef struct { float d; int8_t qs[256]; int16_t bsums[16]; } blk_q8_K;
 #pragma pack(pop)
 
@@ -82,6 +85,7 @@ EXPORT int64_t oracle_row_size(int type, int64_t k) {      /* ggml_row_size, ggm
         case T_Q4_0: return k / 32 * 18; case T_Q4_1: return k / 32 * 20; case T_Q5_0: return k / 32 * 22;
         case T_Q5_1: return k / 32 * 24; case T_Q8_0: return k / 32 * 34;
         case T_Q4_K: return k / 256 * 144; case T_Q5_K: return k / 256 * 176; case T_Q6_K: return k / 256 * 210;
+        case T_Q2_K: return k / 256 * 84; case T_Q3_K: return k / 256 * 110; case T_IQ4_NL: return k / 32 * 18;
     }
     return 0;
 }
@@ -92,7 +96,16 @@ static void scale_min_k4(int j, const uint8_t * q, uint8_t * d, uint8_t * m) {
     else { *d = (uint8_t) ((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4)); *m = (uint8_t) ((q[j + 4] >> 4) | ((q[j] >> 6) << 4)); }
 }
 
-/* ---- dequantize_row_* (ggml/src/ggml-quants.c: q4_0 255, q4_1 275, q5_0 296, q5_1 322, q8_0 349,
+/* 6-bit scale s of a Q3_K super-block before its offset of 32: low nibble from scales[0..7], two high bits from
+ * scales[8..11] (what the word shuffle at ggml/src/ggml-quants.c:1075-1080 produces, element by element) */
+static int q3k_scale6(const uint8_t * sc, int s) {
+    const int lo = s < 8 ? (sc[s] & 0xF) : (sc[s - 8] >> 4);
+    return lo | (((sc[8 + (s & 3)] >> (2 * (s >> 2))) & 3) << 4);
+}
+/* the non-linear 4-bit code book of IQ4_NL (kvalues_iq4nl, ggml/src/ggml-quants.c:2434) */
+static const int8_t iq4nl_values[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+/* ---- dequantize_row_* (ggml/src/ggml-quants.c: q2_K 712, q3_K 1056, iq4_nl 2436, q4_0 255, q4_1 275, q5_0 296, q5_1 322, q8_0 349,
  *      q4_K 1280, q5_K 1482, q6_K 1690) ---- */
 EXPORT int oracle_dequantize_row(int type, const void * src, float * y, int64_t k) {
     switch (type) {
@@ -120,6 +133,24 @@ EXPORT int oracle_dequantize_row(int type, const void * src, float * y, int64_t 
             return 0; }
         case T_Q8_0: { const blk_q8_0 * x = src;
             for (int64_t i = 0; i < k / 32; ++i) { const float d = h2f(x[i].d); for (int j = 0; j < 32; ++j) y[i*32 + j] = (float) x[i].qs[j] * d; }
+            return 0; }
+        case T_Q2_K: { const blk_q2_K * x = src;
+            for (int64_t i = 0; i < k / 256; ++i) { const float d = h2f(x[i].d), min = h2f(x[i].dmin);
+                for (int e = 0; e < 256; ++e) { const int n = e >> 7, j = (e & 127) >> 5, l = e & 31;
+                    const uint8_t sc = x[i].scales[n * 8 + 2 * j + (l >> 4)];
+                    const float dl = d * (float) (sc & 0xF), ml = min * (float) (sc >> 4);
+                    y[i*256 + e] = dl * (float) ((x[i].qs[n * 32 + l] >> (2 * j)) & 3) - ml; } }
+            return 0; }
+        case T_Q3_K: { const blk_q3_K * x = src;
+            for (int64_t i = 0; i < k / 256; ++i) { const float d = h2f(x[i].d);
+                for (int e = 0; e < 256; ++e) { const int n = e >> 7, j = (e & 127) >> 5, l = e & 31;
+                    const float dl = d * (float) (q3k_scale6(x[i].scales, n * 8 + 2 * j + (l >> 4)) - 32);
+                    const int q = ((x[i].qs[n * 32 + l] >> (2 * j)) & 3) - (((x[i].hmask[l] >> (4 * n + j)) & 1) ? 0 : 4);
+                    y[i*256 + e] = dl * (float) q; } }
+            return 0; }
+        case T_IQ4_NL: { const blk_iq4_nl * x = src;
+            for (int64_t i = 0; i < k / 32; ++i) { const float d = h2f(x[i].d);
+                for (int j = 0; j < 16; ++j) { y[i*32 + j] = d * (float) iq4nl_values[x[i].qs[j] & 0xF]; y[i*32 + j + 16] = d * (float) iq4nl_values[x[i].qs[j] >> 4]; } }
             return 0; }
         case T_Q4_K: { const blk_q4_K * x = src;
             for (int64_t i = 0; i < k / 256; ++i) { const uint8_t * q = x[i].qs; const float d = h2f(x[i].d), min = h2f(x[i].dmin);
@@ -258,6 +289,33 @@ static float vec_dot(int type, int64_t k, const void * vx, const void * vy) {
             for (int64_t i = 0; i < k / 32; ++i) { int s = 0; for (int j = 0; j < 32; ++j) s += x[i].qs[j] * y[i].qs[j];
                 sumf += (float) s * (h2f(x[i].d) * h2f(y[i].d)); }
             return sumf; }
+        case T_Q2_K: { const blk_q2_K * x = vx; const blk_q8_K * y = vy;            /* scalar form, ggml-cpu-quants.c:5058-5096 */
+            for (int64_t i = 0; i < k / 256; ++i) {
+                int mins = 0, isum = 0;
+                for (int sb = 0; sb < 16; ++sb) mins += y[i].bsums[sb] * (x[i].scales[sb] >> 4);
+                for (int sb = 0; sb < 16; ++sb) { const int n = sb >> 3, j = (sb & 7) >> 1, half = sb & 1;
+                    int part = 0;
+                    for (int l = 0; l < 16; ++l) part += y[i].qs[sb * 16 + l] * ((x[i].qs[n * 32 + half * 16 + l] >> (2 * j)) & 3);
+                    isum += (x[i].scales[sb] & 0xF) * part; }
+                const float dall = y[i].d * h2f(x[i].d), dmin = y[i].d * h2f(x[i].dmin);
+                sumf += dall * (float) isum - dmin * (float) mins; }
+            return sumf; }
+        case T_Q3_K: { const blk_q3_K * x = vx; const blk_q8_K * y = vy;            /* scalar form, ggml-cpu-quants.c:6041-6108: eight running sums */
+            float sums[8] = {0};
+            for (int64_t i = 0; i < k / 256; ++i) {
+                int32_t part[8] = {0};
+                for (int e = 0; e < 256; ++e) { const int n = e >> 7, j = (e & 127) >> 5, l = e & 31;
+                    const int q = ((x[i].qs[n * 32 + l] >> (2 * j)) & 3) - (((x[i].hmask[l] >> (4 * n + j)) & 1) ? 0 : 4);
+                    part[e & 7] += (q3k_scale6(x[i].scales, e >> 4) - 32) * (y[i].qs[e] * q); }
+                const float d = h2f(x[i].d) * y[i].d;
+                for (int l = 0; l < 8; ++l) sums[l] += d * (float) part[l]; }
+            for (int l = 0; l < 8; ++l) sumf += sums[l];
+            return sumf; }
+        case T_IQ4_NL: { const blk_iq4_nl * x = vx; const blk_q8_0 * y = vy;        /* ggml-cpu-quants.c:11188 (scalar tail) */
+            for (int64_t i = 0; i < k / 32; ++i) { int s0 = 0, s1 = 0;
+                for (int j = 0; j < 16; ++j) { s0 += y[i].qs[j] * iq4nl_values[x[i].qs[j] & 0xF]; s1 += y[i].qs[j + 16] * iq4nl_values[x[i].qs[j] >> 4]; }
+                sumf += h2f(y[i].d) * h2f(x[i].d) * (float) (s0 + s1); }
+            return sumf; }
         case T_Q4_K: case T_Q5_K: {
             const blk_q8_K * y = vy;
             for (int64_t i = 0; i < k / 256; ++i) {
@@ -304,13 +362,13 @@ EXPORT int oracle_mul_mat(int type, const void * W, int64_t M, int64_t K, const 
     const int64_t wrs = oracle_row_size(type, K);
     if (!wrs) return -1;
     int64_t yrs;
-    if (type == T_Q4_0 || type == T_Q5_0 || type == T_Q8_0) yrs = K / 32 * (int64_t) sizeof(blk_q8_0);
+    if (type == T_Q4_0 || type == T_Q5_0 || type == T_Q8_0 || type == T_IQ4_NL) yrs = K / 32 * (int64_t) sizeof(blk_q8_0);
     else if (type == T_Q4_1 || type == T_Q5_1) yrs = K / 32 * (int64_t) sizeof(blk_q8_1);
     else yrs = K / 256 * (int64_t) sizeof(blk_q8_K);
     uint8_t * yq = malloc((size_t) yrs);
     if (!yq) return -2;
     for (int64_t n = 0; n < N; ++n) {
-        if (type == T_Q4_0 || type == T_Q5_0 || type == T_Q8_0) oracle_quantize_row(T_Q8_0, X + n * K, yq, K);
+        if (type == T_Q4_0 || type == T_Q5_0 || type == T_Q8_0 || type == T_IQ4_NL) oracle_quantize_row(T_Q8_0, X + n * K, yq, K);
         else if (type == T_Q4_1 || type == T_Q5_1) quantize_row_q8_1(X + n * K, (blk_q8_1 *) yq, K);
         else quantize_row_q8_K(X + n * K, (blk_q8_K *) yq, K);
         for (int64_t m = 0; m < M; ++m) dst[n * M + m] = vec_dot(type, K, (const uint8_t *) W + m * wrs, yq);

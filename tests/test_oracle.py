@@ -4,7 +4,7 @@ present, against the reference libraries directly.  CPU only."""
 import numpy as np
 import pytest
 
-QT = ["q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q4_K", "q5_K", "q6_K"]
+QT = ["q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q2_K", "q3_K", "q4_K", "q5_K", "q6_K", "iq4_nl"]
 SIMPLE_QT = ["q4_0", "q4_1", "q5_0", "q5_1", "q8_0"]
 
 
@@ -80,6 +80,7 @@ def test_dequantize_vs_reference_quantizer_output(oracle, qt):
     x = rng.standard_normal((3, 1024)).astype(np.float32) * 0.02
     q = oracle.ref_quantize_rows(qt, x)
     dq = oracle.dequantize_rows(qt, q, 1024)
-    # reconstruction error bound used by the reference (tests/test-quantize-fns.cpp:17-25), scaled to sigma
+    # reconstruction error bound used by the reference (tests/test-quantize-fns.cpp:17-25, :152-158), scaled to
+    # sigma: the 2-bit and 3-bit formats are allowed 3.75x and 2x the default
     rmse = float(np.sqrt(np.mean((dq - x) ** 2)))
-    assert rmse < 0.02 * 0.2
+    assert rmse < 0.02 * 0.2 * {"q2_K": 3.75, "q3_K": 2.0}.get(qt, 1.0)

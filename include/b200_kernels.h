@@ -7,7 +7,7 @@
  * Conventions
  *  - `type` arguments are ggml_type values (ggml/include/ggml.h:351-392):
  *    0 F32, 1 F16, 2 Q4_0, 3 Q4_1, 6 Q5_0, 7 Q5_1, 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, 13 Q5_K, 14 Q6_K,
- *    20 IQ4_NL.
+ *    20 IQ4_NL, 23 IQ4_XS.
  *  - Matrices use ggml's layout: a weight matrix W[K, M] is M rows of K values,
  *    each row a run of quantized blocks (ggml/src/ggml-common.h:161-328);
  *    activations X[K, N] are N contiguous F32 columns; dst[M, N] is N columns of M.

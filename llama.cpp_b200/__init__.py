@@ -20,10 +20,10 @@ LIB_PATH = PKG_DIR / "lib" / "libggml-b200.so"
 
 # ggml_type numbers (ggml/include/ggml.h:351-392)
 TYPES = {"f32": 0, "f16": 1, "q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8,
-         "q2_K": 10, "q3_K": 11, "q4_K": 12, "q5_K": 13, "q6_K": 14, "iq4_nl": 20, "i32": 26, "bf16": 30}
+         "q2_K": 10, "q3_K": 11, "q4_K": 12, "q5_K": 13, "q6_K": 14, "iq4_nl": 20, "iq4_xs": 23, "i32": 26, "bf16": 30}
 BLOCK = {"f32": (1, 4), "f16": (1, 2), "q4_0": (32, 18), "q4_1": (32, 20), "q5_0": (32, 22), "q5_1": (32, 24),
          "q8_0": (32, 34), "q2_K": (256, 84), "q3_K": (256, 110), "q4_K": (256, 144), "q5_K": (256, 176), "q6_K": (256, 210),
-         "iq4_nl": (32, 18)}
+         "iq4_nl": (32, 18), "iq4_xs": (256, 136)}
 
 EXPORTS = [
     "b200_device_count", "b200_last_error", "b200_row_size",

@@ -17,7 +17,7 @@ namespace b200 {
 enum : int {
     T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8,
     T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14,
-    T_IQ4_NL = 20, T_I32 = 26, T_BF16 = 30,
+    T_IQ4_NL = 20, T_IQ4_XS = 23, T_I32 = 26, T_BF16 = 30,
 };
 
 #pragma pack(push, 1)
@@ -32,11 +32,12 @@ struct blk_q6_K { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; uint16_t d
 struct blk_q2_K { uint8_t scales[16]; uint8_t qs[64]; uint16_t d; uint16_t dmin; };         // 84 B / 256 w
 struct blk_q3_K { uint8_t hmask[32]; uint8_t qs[64]; uint8_t scales[12]; uint16_t d; };     // 110 B / 256 w
 struct blk_iq4_nl { uint16_t d; uint8_t qs[16]; };                                          // 18 B / 32 w
+struct blk_iq4_xs { uint16_t d; uint16_t scales_h; uint8_t scales_l[4]; uint8_t qs[128]; }; // 136 B / 256 w
 #pragma pack(pop)
 static_assert(sizeof(blk_q4_0) == 18 && sizeof(blk_q4_1) == 20 && sizeof(blk_q5_0) == 22, "block size");
 static_assert(sizeof(blk_q5_1) == 24 && sizeof(blk_q8_0) == 34, "block size");
 static_assert(sizeof(blk_q4_K) == 144 && sizeof(blk_q5_K) == 176 && sizeof(blk_q6_K) == 210, "block size");
-static_assert(sizeof(blk_q2_K) == 84 && sizeof(blk_q3_K) == 110 && sizeof(blk_iq4_nl) == 18, "block size");
+static_assert(sizeof(blk_q2_K) == 84 && sizeof(blk_q3_K) == 110 && sizeof(blk_iq4_nl) == 18 && sizeof(blk_iq4_xs) == 136, "block size");
 
 // Activation blocks produced on the device for the integer dot products:
 // 128 consecutive values of one activation column = 4 groups of 32 int8 plus,
@@ -49,7 +50,7 @@ __host__ __device__ inline int type_block_elems(int t) {
     switch (t) {
         case T_F32: case T_F16: case T_BF16: case T_I32: return 1;
         case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: case T_IQ4_NL: return 32;
-        case T_Q2_K: case T_Q3_K: case T_Q4_K: case T_Q5_K: case T_Q6_K: return 256;
+        case T_Q2_K: case T_Q3_K: case T_Q4_K: case T_Q5_K: case T_Q6_K: case T_IQ4_XS: return 256;
         default: return 0;
     }
 }
@@ -59,7 +60,7 @@ __host__ __device__ inline int type_block_bytes(int t) {
         case T_F16: case T_BF16: return 2;
         case T_Q4_0: return 18; case T_Q4_1: return 20; case T_Q5_0: return 22; case T_Q5_1: return 24;
         case T_Q8_0: return 34; case T_Q4_K: return 144; case T_Q5_K: return 176; case T_Q6_K: return 210;
-        case T_Q2_K: return 84; case T_Q3_K: return 110; case T_IQ4_NL: return 18;
+        case T_Q2_K: return 84; case T_Q3_K: return 110; case T_IQ4_NL: return 18; case T_IQ4_XS: return 136;
         default: return 0;
     }
 }
@@ -83,7 +84,7 @@ __device__ __forceinline__ void k4_scale_min(int j, const uint8_t * q, int & sc,
 // fused multiply-add, so that results are bit-identical to the CPU code:
 //   q4_0 ggml-quants.c:255-273   q4_1 :275-294   q5_0 :296-320   q5_1 :322-347
 //   q8_0 :349-363   q4_K :1280-1302   q5_K :1482-1507   q6_K :1690-1719
-//   q2_K :712-744   q3_K :1056-1106   iq4_nl :2434-2451
+//   q2_K :712-744   q3_K :1056-1106   iq4_nl :2434-2451   iq4_xs :2453-2475
 template <int T> __device__ __forceinline__ float dequant_elem(const uint8_t * row, int64_t i);
 
 template <> __device__ __forceinline__ float dequant_elem<T_F32>(const uint8_t * row, int64_t i) {
@@ -194,6 +195,20 @@ template <> __device__ __forceinline__ float dequant_elem<T_IQ4_NL>(const uint8_
     const int j = i & 31;
     const int q = j < 16 ? (b->qs[j] & 0x0F) : (b->qs[j - 16] >> 4);
     return __fmul_rn(h2f(b->d), (float) iq4nl_value(q));
+}
+
+// IQ4_XS: eight 32-weight sub-blocks in IQ4_NL coding, each with a 6-bit scale (offset 32): low nibble in
+// scales_l, two high bits in scales_h
+__device__ __forceinline__ int iq4xs_scale(const uint8_t * blk, int ib) {
+    const int h = blk[2] | (blk[3] << 8);
+    return (((blk[4 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF) | (((h >> (2 * ib)) & 3) << 4)) - 32;
+}
+template <> __device__ __forceinline__ float dequant_elem<T_IQ4_XS>(const uint8_t * row, int64_t i) {
+    const uint8_t * b = row + (i >> 8) * 136;
+    const int r = i & 255, ib = r >> 5, j = r & 31;
+    const float dl = __fmul_rn(h2f(*(const uint16_t *) b), (float) iq4xs_scale(b, ib));
+    const uint8_t byte = b[8 + ib * 16 + (j & 15)];
+    return __fmul_rn(dl, (float) iq4nl_value(j < 16 ? (byte & 0x0F) : (byte >> 4)));
 }
 
 // ---------------------------------------------------------------------------

@@ -710,7 +710,7 @@ __global__ void get_rows_kernel(const TensorD src, const TensorD idx, const Tens
 }
 bool get_rows_supported(int t) {
     switch (t) {
-        case T_F32: case T_F16: case T_BF16: case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: case T_IQ4_NL:
+        case T_F32: case T_F16: case T_BF16: case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: case T_IQ4_NL: case T_IQ4_XS:
         case T_Q2_K: case T_Q3_K: case T_Q4_K: case T_Q5_K: case T_Q6_K: return true;
         default: return false;
     }
@@ -722,7 +722,7 @@ cudaError_t launch_get_rows(const TensorD & src, const TensorD & idx, const Tens
     dim3 grid((unsigned) gx, (unsigned) idx.ne[0], (unsigned) (idx.ne[1] * idx.ne[2]));
 #define GR(T) case T: (void) (launch_err = launch_k(c.use_pdl, c.stream, get_rows_kernel<T>, dim3(grid), dim3(block), 0, src, idx, dst)); break;
     switch (src.type) {
-        GR(T_F32) GR(T_F16) GR(T_BF16) GR(T_Q4_0) GR(T_Q4_1) GR(T_Q5_0) GR(T_Q5_1) GR(T_Q8_0) GR(T_Q4_K) GR(T_Q5_K) GR(T_Q6_K) GR(T_Q2_K) GR(T_Q3_K) GR(T_IQ4_NL)
+        GR(T_F32) GR(T_F16) GR(T_BF16) GR(T_Q4_0) GR(T_Q4_1) GR(T_Q5_0) GR(T_Q5_1) GR(T_Q8_0) GR(T_Q4_K) GR(T_Q5_K) GR(T_Q6_K) GR(T_Q2_K) GR(T_Q3_K) GR(T_IQ4_NL) GR(T_IQ4_XS)
         default: return cudaErrorInvalidValue;
     }
 #undef GR

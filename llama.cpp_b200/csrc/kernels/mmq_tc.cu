@@ -496,6 +496,7 @@ cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float *
         case T_Q2_K: return launch_tc_t<T_Q2_K>(p, c.device, c.use_pdl, c.stream);
         case T_Q3_K: return launch_tc_t<T_Q3_K>(p, c.device, c.use_pdl, c.stream);
         case T_IQ4_NL: return launch_tc_t<T_IQ4_NL>(p, c.device, c.use_pdl, c.stream);
+        case T_IQ4_XS: return launch_tc_t<T_IQ4_XS>(p, c.device, c.use_pdl, c.stream);
     }
     return cudaErrorInvalidValue;
 }

@@ -406,6 +406,28 @@ template <> struct WT<T_IQ4_NL> {
     }
 };
 
+// IQ4_XS: a unit is one 32-weight sub-block (16 qs bytes) with its own 6-bit scale (ggml-quants.c:2453-2475)
+template <> struct WT<T_IQ4_XS> {
+    static constexpr int UNIT = 32, BLK_ELEMS = 256, BLK_BYTES = 136;
+    template <int N> static __device__ __forceinline__ void dot(const uint8_t * row, int u, const ActView & xv, float (&acc)[N]) {
+        const uint8_t * b = row + (u >> 3) * 136;
+        const int ib = u & 7;
+        const float dl = h2f(*(const uint16_t *) b) * (float) iq4xs_scale(b, ib);
+        uint32_t w[4], lo[4], hi[4];
+        lds_words<4>(b + 8 + ib * 16, w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { lo[i] = iq4nl_lut4(w[i] & 0x0F0F0F0Fu); hi[i] = iq4nl_lut4((w[i] >> 4) & 0x0F0F0F0Fu); }
+#pragma unroll
+        for (int n = 0; n < N; ++n) {
+            const int * xq = xv.q32(n, u);
+            int s = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { s = __dp4a((int) lo[i], xq[i], s); s = __dp4a((int) hi[i], xq[i + 4], s); }
+            acc[n] += dl * xv.ds(n, u).x * (float) s;
+        }
+    }
+};
+
 // ---------------------------------------------------------------------------
 // the streaming kernel
 // ---------------------------------------------------------------------------
@@ -629,7 +651,7 @@ static cudaError_t launch_mmvq_t(const MmvqParams & p, int sm, cudaStream_t st) 
 
 bool mmvq_type_supported(int type) {
     switch (type) {
-        case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: case T_IQ4_NL:
+        case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: case T_IQ4_NL: case T_IQ4_XS:
         case T_Q2_K: case T_Q3_K: case T_Q4_K: case T_Q5_K: case T_Q6_K: return true;
         default: return false;
     }
@@ -675,6 +697,7 @@ cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream) {
         case T_Q2_K: return launch_mmvq_t<T_Q2_K>(p, a.sm_count, stream);
         case T_Q3_K: return launch_mmvq_t<T_Q3_K>(p, a.sm_count, stream);
         case T_IQ4_NL: return launch_mmvq_t<T_IQ4_NL>(p, a.sm_count, stream);
+        case T_IQ4_XS: return launch_mmvq_t<T_IQ4_XS>(p, a.sm_count, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -20,7 +20,7 @@
 
 #define EXPORT __attribute__((visibility("default")))
 
-enum { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ4_NL = 20 };
+enum { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ4_NL = 20, T_IQ4_XS = 23 };
 
 /* ---- IEEE half <-> float (ggml_compute_fp16_to_fp32 / fp32_to_fp16, ggml/src/ggml-impl.h:330-400) ---- */
 static float h2f(uint16_t h) {
@@ -76,6 +76,7 @@ typedef struct { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; uint16_t d;
 typedef struct { uint8_t scales[16]; uint8_t qs[64]; uint16_t d, dmin; } blk_q2_K;
 typedef struct { uint8_t hmask[32]; uint8_t qs[64]; uint8_t scales[12]; uint16_t d; } blk_q3_K;
 typedef struct { uint16_t d; uint8_t qs[16]; } blk_iq4_nl;
+typedef struct { uint16_t d, scales_h; uint8_t scales_l[4]; uint8_t qs[128]; } blk_iq4_xs;
 typedef struct { float d; int8_t qs[256]; int16_t bsums[16]; } blk_q8_K;
 #pragma pack(pop)
 
@@ -85,7 +86,7 @@ EXPORT int64_t oracle_row_size(int type, int64_t k) {      /* ggml_row_size, ggm
         case T_Q4_0: return k / 32 * 18; case T_Q4_1: return k / 32 * 20; case T_Q5_0: return k / 32 * 22;
         case T_Q5_1: return k / 32 * 24; case T_Q8_0: return k / 32 * 34;
         case T_Q4_K: return k / 256 * 144; case T_Q5_K: return k / 256 * 176; case T_Q6_K: return k / 256 * 210;
-        case T_Q2_K: return k / 256 * 84; case T_Q3_K: return k / 256 * 110; case T_IQ4_NL: return k / 32 * 18;
+        case T_Q2_K: return k / 256 * 84; case T_Q3_K: return k / 256 * 110; case T_IQ4_NL: return k / 32 * 18; case T_IQ4_XS: return k / 256 * 136;
     }
     return 0;
 }
@@ -105,7 +106,12 @@ static int q3k_scale6(const uint8_t * sc, int s) {
 /* the non-linear 4-bit code book of IQ4_NL (kvalues_iq4nl, ggml/src/ggml-quants.c:2434) */
 static const int8_t iq4nl_values[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 
-/* ---- dequantize_row_* (ggml/src/ggml-quants.c: q2_K 712, q3_K 1056, iq4_nl 2436, q4_0 255, q4_1 275, q5_0 296, q5_1 322, q8_0 349,
+/* 6-bit scale of sub-block ib of an IQ4_XS super-block, offset removed (ggml/src/ggml-quants.c:2465) */
+static int iq4xs_scale(const blk_iq4_xs * b, int ib) {
+    return (((b->scales_l[ib / 2] >> (4 * (ib % 2))) & 0xF) | (((b->scales_h >> (2 * ib)) & 3) << 4)) - 32;
+}
+
+/* ---- dequantize_row_* (ggml/src/ggml-quants.c: q2_K 712, q3_K 1056, iq4_nl 2436, iq4_xs 2453, q4_0 255, q4_1 275, q5_0 296, q5_1 322, q8_0 349,
  *      q4_K 1280, q5_K 1482, q6_K 1690) ---- */
 EXPORT int oracle_dequantize_row(int type, const void * src, float * y, int64_t k) {
     switch (type) {
@@ -151,6 +157,11 @@ EXPORT int oracle_dequantize_row(int type, const void * src, float * y, int64_t 
         case T_IQ4_NL: { const blk_iq4_nl * x = src;
             for (int64_t i = 0; i < k / 32; ++i) { const float d = h2f(x[i].d);
                 for (int j = 0; j < 16; ++j) { y[i*32 + j] = d * (float) iq4nl_values[x[i].qs[j] & 0xF]; y[i*32 + j + 16] = d * (float) iq4nl_values[x[i].qs[j] >> 4]; } }
+            return 0; }
+        case T_IQ4_XS: { const blk_iq4_xs * x = src;
+            for (int64_t i = 0; i < k / 256; ++i) { const float d = h2f(x[i].d);
+                for (int ib = 0; ib < 8; ++ib) { const float dl = d * (float) iq4xs_scale(&x[i], ib); const uint8_t * qs = x[i].qs + 16 * ib;
+                    for (int j = 0; j < 16; ++j) { y[i*256 + ib*32 + j] = dl * (float) iq4nl_values[qs[j] & 0xF]; y[i*256 + ib*32 + j + 16] = dl * (float) iq4nl_values[qs[j] >> 4]; } } }
             return 0; }
         case T_Q4_K: { const blk_q4_K * x = src;
             for (int64_t i = 0; i < k / 256; ++i) { const uint8_t * q = x[i].qs; const float d = h2f(x[i].d), min = h2f(x[i].dmin);
@@ -315,6 +326,12 @@ static float vec_dot(int type, int64_t k, const void * vx, const void * vy) {
             for (int64_t i = 0; i < k / 32; ++i) { int s0 = 0, s1 = 0;
                 for (int j = 0; j < 16; ++j) { s0 += y[i].qs[j] * iq4nl_values[x[i].qs[j] & 0xF]; s1 += y[i].qs[j + 16] * iq4nl_values[x[i].qs[j] >> 4]; }
                 sumf += h2f(y[i].d) * h2f(x[i].d) * (float) (s0 + s1); }
+            return sumf; }
+        case T_IQ4_XS: { const blk_iq4_xs * x = vx; const blk_q8_K * y = vy;        /* scalar form, ggml-cpu-quants.c:11646-11676 */
+            for (int64_t i = 0; i < k / 256; ++i) { const float dd = h2f(x[i].d) * y[i].d;
+                for (int ib = 0; ib < 8; ++ib) { const uint8_t * qs = x[i].qs + 16 * ib; const int8_t * q8 = y[i].qs + 32 * ib; int s0 = 0, s1 = 0;
+                    for (int j = 0; j < 16; ++j) { s0 += q8[j] * iq4nl_values[qs[j] & 0xF]; s1 += q8[j + 16] * iq4nl_values[qs[j] >> 4]; }
+                    sumf += dd * (float) iq4xs_scale(&x[i], ib) * (float) (s0 + s1); } }
             return sumf; }
         case T_Q4_K: case T_Q5_K: {
             const blk_q8_K * y = vy;

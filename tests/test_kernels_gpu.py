@@ -8,7 +8,7 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
-QT = ["q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q2_K", "q3_K", "q4_K", "q5_K", "q6_K", "iq4_nl"]
+QT = ["q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q2_K", "q3_K", "q4_K", "q5_K", "q6_K", "iq4_nl", "iq4_xs"]
 SIMPLE_QT = ["q4_0", "q4_1", "q5_0", "q5_1", "q8_0"]
 NMSE_MM = 5e-4
 

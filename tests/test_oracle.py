@@ -4,7 +4,7 @@ present, against the reference libraries directly.  CPU only."""
 import numpy as np
 import pytest
 
-QT = ["q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q2_K", "q3_K", "q4_K", "q5_K", "q6_K", "iq4_nl"]
+QT = ["q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q2_K", "q3_K", "q4_K", "q5_K", "q6_K", "iq4_nl", "iq4_xs"]
 SIMPLE_QT = ["q4_0", "q4_1", "q5_0", "q5_1", "q8_0"]
 
 

@@ -45,6 +45,38 @@ b200_llama * b200_llama_create(void * reg, int32_t device_index, const b200_llam
 void         b200_llama_free(b200_llama * m);
 const char * b200_llama_error(void);
 
+/* ---- model files ------------------------------------------------------------------------------
+ * b200_llama_load_gguf: the step before the hot path.  Reads a GGUF file of a Llama-architecture model (the
+ * reference's on-disk format, ggml/include/gguf.h:1-68; its loader: src/llama-model-loader.cpp, ggml/src/gguf.cpp),
+ * takes the hyper-parameters from its `llama.*` keys and the type of every weight from its tensor infos, and
+ * copies the tensor data from the read-only file mapping into the backend's weight buffer -- on the B200
+ * backend in 32 MB chunks through two pinned staging buffers and asynchronous host-to-device copies, each
+ * rank only its own rows when n_ranks > 1.  A file without output.weight uses the token embeddings for the
+ * output projection.  Rejected with an error: other architectures, expert tensors, rope scaling or frequency
+ * factors, partial rotary dimensions, tensor types this backend has no kernel for.
+ * b200_gguf_*: the reader by itself (metadata and tensor directory of any GGUF file, version 2 or 3). */
+typedef struct b200_gguf b200_gguf;
+b200_llama * b200_llama_load_gguf(void * reg, int32_t device_index, const char * path, int32_t n_ctx, int32_t n_ubatch,
+                                  int32_t n_threads, int32_t n_ranks, int32_t rank);
+void         b200_llama_get_config(const b200_llama * m, b200_llama_config * cfg);
+b200_gguf *  b200_gguf_open(const char * path);            /* NULL on failure: b200_gguf_error() */
+void         b200_gguf_close(b200_gguf * g);
+const char * b200_gguf_error(void);
+uint32_t     b200_gguf_version(const b200_gguf * g);
+uint32_t     b200_gguf_alignment(const b200_gguf * g);
+uint64_t     b200_gguf_data_offset(const b200_gguf * g);   /* file offset of the tensor data section */
+int64_t      b200_gguf_n_kv(const b200_gguf * g);
+int64_t      b200_gguf_n_tensors(const b200_gguf * g);
+/* key i in file order with its gguf_type; for arrays (type 9) also the element type and count */
+int32_t      b200_gguf_key(const b200_gguf * g, int64_t i, char * key, size_t key_cap, uint32_t * type, uint32_t * elem_type, uint64_t * count);
+int32_t      b200_gguf_get_u32(const b200_gguf * g, const char * key, uint32_t * value);     /* 0 if present and integral */
+int32_t      b200_gguf_get_f32(const b200_gguf * g, const char * key, float * value);
+int32_t      b200_gguf_get_str(const b200_gguf * g, const char * key, char * value, size_t value_cap);
+int32_t      b200_gguf_tensor_info(const b200_gguf * g, int64_t i, char * name, size_t name_cap, int32_t * type, int32_t * n_dims,
+                                   int64_t * ne /* [4] */, uint64_t * offset, size_t * nbytes);
+int64_t      b200_gguf_find_tensor(const b200_gguf * g, const char * name);                  /* index or -1 */
+const void * b200_gguf_tensor_data(const b200_gguf * g, int64_t i);                          /* inside the mapping */
+
 /* weight tensors, in a fixed order; names follow the GGUF convention ("blk.0.attn_q.weight") */
 int32_t      b200_llama_n_tensors(const b200_llama * m);
 int32_t      b200_llama_tensor_info(const b200_llama * m, int32_t i, char * name, size_t name_cap,

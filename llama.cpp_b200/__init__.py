@@ -38,6 +38,10 @@ EXPORTS = [
     "b200_llama_set_tensor", "b200_llama_tensor_data", "b200_llama_decode", "b200_llama_last_n_nodes",
     "b200_llama_last_compute_ms", "b200_llama_launch_count", "b200_llama_weight_bytes",
     "b200_row_split_range", "b200_llama_tensor_rows", "b200_llama_ipc_handle", "b200_llama_attach_peers",
+    "b200_llama_load_gguf", "b200_llama_get_config",
+    "b200_gguf_open", "b200_gguf_close", "b200_gguf_error", "b200_gguf_version", "b200_gguf_alignment", "b200_gguf_data_offset",
+    "b200_gguf_n_kv", "b200_gguf_n_tensors", "b200_gguf_key", "b200_gguf_get_u32", "b200_gguf_get_f32", "b200_gguf_get_str",
+    "b200_gguf_tensor_info", "b200_gguf_find_tensor", "b200_gguf_tensor_data",
 ]
 
 

@@ -12,9 +12,11 @@
 #include "backend.h"
 #include "ggml-impl.h"
 #include "b200_llama.h"
+#include "gguf_load.h"
 
 #include <chrono>
 #include <cmath>
+#include <map>
 #include <memory>
 
 extern "C" ggml_backend_reg_t ggml_backend_init(void);
@@ -205,7 +207,10 @@ struct b200_llama {
 
     // ---- model ----
     static bool use_more_bits(int il, int n) { return il < n / 8 || il >= 7 * n / 8 || (il - n / 8) % 3 == 2; }
+    // tensor types found in a model file replace the synthetic model's Q4_K_M mixture
+    const std::map<std::string, int> * type_override = nullptr;
     void add_weight(const std::string & name, ggml_type type, int64_t n0, int64_t n1, bool split = false) {
+        if (type_override) { auto it = type_override->find(name); if (it != type_override->end()) type = (ggml_type) it->second; }
         Weight w; w.name = name; memset(&w.t, 0, sizeof(w.t));
         w.full_rows = n1; w.row_low = 0; w.split = split && n_ranks > 1;
         if (w.split) {
@@ -326,9 +331,16 @@ extern "C" {
 
 API const char * b200_llama_error(void) { return g_error.c_str(); }
 
+static b200_llama * create_impl(void * reg_, int32_t device_index, const b200_llama_config * cfg, const std::map<std::string, int> * types);
+
 API b200_llama * b200_llama_create(void * reg_, int32_t device_index, const b200_llama_config * cfg) {
+    return create_impl(reg_, device_index, cfg, nullptr);
+}
+
+static b200_llama * create_impl(void * reg_, int32_t device_index, const b200_llama_config * cfg, const std::map<std::string, int> * types) {
     std::unique_ptr<b200_llama> m(new b200_llama);
     m->cfg = *cfg;
+    m->type_override = types;
     if (cfg->n_embd % cfg->n_head || cfg->n_head % cfg->n_head_kv || cfg->n_embd % 256 || cfg->n_ff % 256) { g_error = "unsupported model shape"; return nullptr; }
     m->n_ranks = cfg->n_ranks > 1 ? cfg->n_ranks : 1;
     m->rank = m->n_ranks > 1 ? cfg->rank : 0;
@@ -359,6 +371,7 @@ API b200_llama * b200_llama_create(void * reg_, int32_t device_index, const b200
 
     // weights: one buffer, tensors at 128-byte aligned offsets
     m->add_weights();
+    m->type_override = nullptr;
     size_t off = 0;
     for (Weight & w : m->weights) { off = align_up(off); w.offset = off; off += t_nbytes(&w.t); m->weight_bytes += t_nbytes(&w.t); }
     m->weight_bytes -= t_nbytes(&m->weights[b200_llama::W_TOK].t);   // embeddings: only the gathered rows are read
@@ -427,6 +440,105 @@ API void b200_llama_free(b200_llama * m) {
     m->backend->iface.free(m->backend);
     delete m;
 }
+
+// ---- model files ---------------------------------------------------------------------------
+// Host bytes -> weight buffer.  On the B200 backend the bytes go through two pinned staging buffers so that
+// the copy out of the page cache (the file mapping) overlaps the asynchronous host-to-device transfer of the
+// previous chunk; other backends take the mapping directly through set_tensor.
+namespace {
+struct Uploader {
+    b200_llama * m;
+    static constexpr size_t CHUNK = (size_t) 32 << 20;
+    void * stage[2] = {nullptr, nullptr};
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    cudaStream_t stream = nullptr;
+    int next = 0;
+    bool pinned = false;
+    explicit Uploader(b200_llama * m_) : m(m_) {
+        if (!m->is_b200) return;
+        pinned = cudaMallocHost(&stage[0], CHUNK) == cudaSuccess && cudaMallocHost(&stage[1], CHUNK) == cudaSuccess &&
+                 cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&done[0], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&done[1], cudaEventDisableTiming) == cudaSuccess;
+        if (!pinned) cudaGetLastError();
+    }
+    ~Uploader() {
+        if (stream) { cudaStreamSynchronize(stream); cudaStreamDestroy(stream); }
+        for (int b = 0; b < 2; ++b) { if (done[b]) cudaEventDestroy(done[b]); if (stage[b]) cudaFreeHost(stage[b]); }
+    }
+    bool put(ggml_tensor * t, const uint8_t * src, size_t n) {
+        if (!pinned) { m->buf_w->iface.set_tensor(m->buf_w, t, src, 0, n); return true; }
+        for (size_t off = 0; off < n; off += CHUNK) {
+            const size_t len = std::min(CHUNK, n - off);
+            const int b = next; next ^= 1;
+            if (cudaEventSynchronize(done[b]) != cudaSuccess) return false;       // the buffer's previous transfer has left it
+            memcpy(stage[b], src + off, len);
+            if (cudaMemcpyAsync((char *) t->data + off, stage[b], len, cudaMemcpyHostToDevice, stream) != cudaSuccess) return false;
+            if (cudaEventRecord(done[b], stream) != cudaSuccess) return false;
+        }
+        return true;
+    }
+    bool finish() { return !pinned || cudaStreamSynchronize(stream) == cudaSuccess; }
+};
+}  // namespace
+
+API b200_llama * b200_llama_load_gguf(void * reg_, int32_t device_index, const char * path, int32_t n_ctx, int32_t n_ubatch,
+                                      int32_t n_threads, int32_t n_ranks, int32_t rank) {
+    GgufFile f;
+    if (!f.open(path, g_error)) return nullptr;
+    std::string arch;
+    if (!f.get_str("general.architecture", arch) || arch != "llama") { g_error = std::string(path) + ": architecture '" + arch + "' is not llama"; return nullptr; }
+    auto key = [&](const char * k) { return arch + "." + k; };
+    b200_llama_config cfg = {};
+    uint32_t n_layer = 0, n_embd = 0, n_head = 0, n_head_kv = 0, n_ff = 0, n_vocab = 0, n_rot = 0, n_expert = 0;
+    if (!f.get_u32(key("block_count"), n_layer) || !f.get_u32(key("embedding_length"), n_embd) || !f.get_u32(key("attention.head_count"), n_head) ||
+        !f.get_u32(key("feed_forward_length"), n_ff) || n_head == 0) {
+        g_error = std::string(path) + ": missing llama hyper-parameters (block_count, embedding_length, feed_forward_length, attention.head_count)";
+        return nullptr;
+    }
+    if (!f.get_u32(key("attention.head_count_kv"), n_head_kv)) n_head_kv = n_head;
+    const GgufTensor * tok = f.find("token_embd.weight");
+    if (!tok) { g_error = std::string(path) + ": no token_embd.weight"; return nullptr; }
+    if (!f.get_u32(key("vocab_size"), n_vocab)) n_vocab = (uint32_t) tok->ne[1];
+    if (f.get_u32(key("rope.dimension_count"), n_rot) && n_rot != n_embd / n_head) { g_error = "partial rotary dimensions are not supported by this driver"; return nullptr; }
+    if (f.get_u32(key("expert_count"), n_expert) && n_expert > 0) { g_error = "mixture-of-experts files are not supported by this driver"; return nullptr; }
+    if (f.find("rope_freqs.weight")) { g_error = "rope frequency factors (rope_freqs.weight) are not supported by this driver"; return nullptr; }
+    std::string scaling;
+    if (f.get_str(key("rope.scaling.type"), scaling) && scaling != "none") { g_error = "rope scaling '" + scaling + "' is not supported by this driver"; return nullptr; }
+    cfg.n_layer = (int32_t) n_layer; cfg.n_embd = (int32_t) n_embd; cfg.n_head = (int32_t) n_head; cfg.n_head_kv = (int32_t) n_head_kv;
+    cfg.n_ff = (int32_t) n_ff; cfg.n_vocab = (int32_t) n_vocab;
+    cfg.n_ctx = n_ctx; cfg.n_ubatch = n_ubatch; cfg.n_threads = n_threads; cfg.n_ranks = n_ranks; cfg.rank = rank;
+    cfg.rope_theta = 10000.0f; cfg.rms_eps = 1e-5f;                     // defaults of the reference's loader (src/llama-model.cpp)
+    f.get_f32(key("rope.freq_base"), cfg.rope_theta);
+    f.get_f32(key("attention.layer_norm_rms_epsilon"), cfg.rms_eps);
+
+    // tensor types as stored; a file without output.weight ties it to the token embeddings (src/llama-model.cpp: output = tok_embd)
+    std::map<std::string, int> types;
+    for (const GgufTensor & t : f.tensors) types[t.name] = t.type;
+    const bool tied = !f.find("output.weight");
+    if (tied) types["output.weight"] = tok->type;
+    b200_llama * m = create_impl(reg_, device_index, &cfg, &types);
+    if (!m) return nullptr;
+
+    Uploader up(m);
+    for (Weight & w : m->weights) {
+        const GgufTensor * t = f.find(tied && w.name == "output.weight" ? "token_embd.weight" : w.name);
+        std::string why;
+        if (!t) why = "is missing";
+        else if (t->type != (int32_t) w.t.type) why = "has an unexpected type";
+        else if (t->ne[0] != w.t.ne[0] || t->ne[1] != w.full_rows || t->ne[2] != 1 || t->ne[3] != 1) why = "has an unexpected shape";
+        else if (w.full_rows == 1 ? t->type != GGML_TYPE_F32
+                                  : !(t->type == GGML_TYPE_F32 || t->type == GGML_TYPE_F16 || t->type == GGML_TYPE_BF16 || mmvq_type_supported(t->type)))
+            why = "has a type this backend does not compute with";
+        if (!why.empty()) { g_error = std::string(path) + ": tensor " + w.name + " " + why; b200_llama_free(m); return nullptr; }
+        const size_t row = t_row_size(t->type, t->ne[0]);
+        if (!up.put(&w.t, f.data(*t) + (size_t) w.row_low * row, t_nbytes(&w.t))) { g_error = "upload of " + w.name + " failed"; b200_llama_free(m); return nullptr; }
+    }
+    if (!up.finish()) { g_error = "weight upload failed"; b200_llama_free(m); return nullptr; }
+    return m;
+}
+
+API void b200_llama_get_config(const b200_llama * m, b200_llama_config * cfg) { *cfg = m->cfg; }
 
 API int32_t b200_llama_n_tensors(const b200_llama * m) { return (int32_t) m->weights.size(); }
 

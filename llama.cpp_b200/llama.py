@@ -49,6 +49,9 @@ def _bind():
         l.b200_llama_tensor_rows.argtypes = [vp, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         l.b200_llama_ipc_handle.argtypes = [vp, vp]
         l.b200_llama_attach_peers.argtypes = [vp, vp]
+        l.b200_llama_load_gguf.restype = vp
+        l.b200_llama_load_gguf.argtypes = [vp, C.c_int32, C.c_char_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
+        l.b200_llama_get_config.argtypes = [vp, C.POINTER(Config)]
         _bound = True
     return l
 
@@ -70,6 +73,21 @@ class Llama:
         if not self.h:
             raise B200Error(f"b200_llama_create failed: {self.l.b200_llama_error().decode()}")
         self.logits = np.empty(self.cfg.n_vocab, dtype=np.float32)
+
+    @classmethod
+    def from_gguf(cls, path, n_ctx: int, n_ubatch: int, reg: int | None = None, device_index: int = 0, n_threads: int = 0,
+                  rank: int = 0, n_ranks: int = 1) -> "Llama":
+        """Loads a Llama-architecture GGUF file: hyper-parameters and tensor types from the file, weights copied
+        into the backend's buffer (this rank's rows only when n_ranks > 1)."""
+        self = cls.__new__(cls)
+        self.l = _bind()
+        self.h = self.l.b200_llama_load_gguf(reg, device_index, str(path).encode(), n_ctx, n_ubatch, n_threads, n_ranks, rank)
+        if not self.h:
+            raise B200Error(f"b200_llama_load_gguf failed: {self.l.b200_llama_error().decode()}")
+        self.cfg = Config()
+        self.l.b200_llama_get_config(self.h, C.byref(self.cfg))
+        self.logits = np.empty(self.cfg.n_vocab, dtype=np.float32)
+        return self
 
     def close(self):
         if self.h:

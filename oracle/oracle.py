@@ -226,3 +226,36 @@ def ref_cpu_backend_reg() -> int:
         best.ggml_backend_init.restype = C.c_void_p
         _cpu_lib = best
     return int(_cpu_lib.ggml_backend_init())
+
+
+def ref_gguf_directory(path) -> dict:
+    """What the reference's own GGUF reader (gguf_init_from_file, ggml/src/gguf.cpp:288) sees in a file:
+    version, alignment, data offset, keys with their types, tensors with type, offset and size."""
+    l = ref_base()
+
+    class Params(C.Structure):
+        _fields_ = [("no_alloc", C.c_bool), ("ctx", C.c_void_p)]
+
+    vp, i64 = C.c_void_p, C.c_int64
+    l.gguf_init_from_file.restype = vp
+    l.gguf_init_from_file.argtypes = [C.c_char_p, Params]
+    for fn, rt in (("gguf_get_version", C.c_uint32), ("gguf_get_alignment", C.c_size_t), ("gguf_get_data_offset", C.c_size_t),
+                   ("gguf_get_n_kv", i64), ("gguf_get_n_tensors", i64)):
+        getattr(l, fn).restype = rt
+        getattr(l, fn).argtypes = [vp]
+    for fn, rt in (("gguf_get_key", C.c_char_p), ("gguf_get_kv_type", C.c_int), ("gguf_get_tensor_name", C.c_char_p),
+                   ("gguf_get_tensor_offset", C.c_size_t), ("gguf_get_tensor_type", C.c_int), ("gguf_get_tensor_size", C.c_size_t)):
+        getattr(l, fn).restype = rt
+        getattr(l, fn).argtypes = [vp, i64]
+    l.gguf_free.argtypes = [vp]
+    g = l.gguf_init_from_file(str(path).encode(), Params(True, None))
+    if not g:
+        return None
+    try:
+        return dict(version=l.gguf_get_version(g), alignment=l.gguf_get_alignment(g), data_offset=l.gguf_get_data_offset(g),
+                    keys=[(l.gguf_get_key(g, i).decode(), l.gguf_get_kv_type(g, i)) for i in range(l.gguf_get_n_kv(g))],
+                    tensors=[dict(name=l.gguf_get_tensor_name(g, i).decode(), type=l.gguf_get_tensor_type(g, i),
+                                  offset=l.gguf_get_tensor_offset(g, i), nbytes=l.gguf_get_tensor_size(g, i))
+                             for i in range(l.gguf_get_n_tensors(g))])
+    finally:
+        l.gguf_free(g)

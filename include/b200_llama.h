@@ -50,8 +50,8 @@ const char * b200_llama_error(void);
  * reference's on-disk format, ggml/include/gguf.h:1-68; its loader: src/llama-model-loader.cpp, ggml/src/gguf.cpp),
  * takes the hyper-parameters from its `llama.*` keys and the type of every weight from its tensor infos, and
  * copies the tensor data from the read-only file mapping into the backend's weight buffer -- on the B200
- * backend in 32 MB chunks through two pinned staging buffers and asynchronous host-to-device copies, each
- * rank only its own rows when n_ranks > 1.  A file without output.weight uses the token embeddings for the
+ * backend in 16 MB chunks that a few worker threads stage through pinned buffers into asynchronous
+ * host-to-device copies, each rank only its own rows when n_ranks > 1.  A file without output.weight uses the token embeddings for the
  * output projection.  Rejected with an error: other architectures, expert tensors, rope scaling or frequency
  * factors, partial rotary dimensions, tensor types this backend has no kernel for.
  * b200_gguf_*: the reader by itself (metadata and tensor directory of any GGUF file, version 2 or 3). */

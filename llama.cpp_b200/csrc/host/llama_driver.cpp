@@ -16,8 +16,10 @@
 
 #include <chrono>
 #include <cmath>
+#include <atomic>
 #include <map>
 #include <memory>
+#include <thread>
 
 extern "C" ggml_backend_reg_t ggml_backend_init(void);
 
@@ -442,43 +444,62 @@ API void b200_llama_free(b200_llama * m) {
 }
 
 // ---- model files ---------------------------------------------------------------------------
-// Host bytes -> weight buffer.  On the B200 backend the bytes go through two pinned staging buffers so that
-// the copy out of the page cache (the file mapping) overlaps the asynchronous host-to-device transfer of the
-// previous chunk; other backends take the mapping directly through set_tensor.
+// Host bytes -> weight buffer.  On the B200 backend the tensors are cut into 16 MB jobs that a few worker
+// threads pull from a shared counter; each worker copies its job out of the page cache (the file mapping)
+// into one of its two pinned staging buffers and queues an asynchronous host-to-device transfer on its own
+// stream, so page-cache reads, staging copies and DMA of different jobs overlap.  Other backends take the
+// mapping directly through set_tensor.
 namespace {
 struct Uploader {
+    struct Job { char * dst; const uint8_t * src; size_t len; };
+    static constexpr size_t CHUNK = (size_t) 16 << 20;
     b200_llama * m;
-    static constexpr size_t CHUNK = (size_t) 32 << 20;
-    void * stage[2] = {nullptr, nullptr};
-    cudaEvent_t done[2] = {nullptr, nullptr};
-    cudaStream_t stream = nullptr;
-    int next = 0;
-    bool pinned = false;
-    explicit Uploader(b200_llama * m_) : m(m_) {
-        if (!m->is_b200) return;
-        pinned = cudaMallocHost(&stage[0], CHUNK) == cudaSuccess && cudaMallocHost(&stage[1], CHUNK) == cudaSuccess &&
-                 cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) == cudaSuccess &&
-                 cudaEventCreateWithFlags(&done[0], cudaEventDisableTiming) == cudaSuccess &&
-                 cudaEventCreateWithFlags(&done[1], cudaEventDisableTiming) == cudaSuccess;
-        if (!pinned) cudaGetLastError();
+    std::vector<Job> jobs;
+    explicit Uploader(b200_llama * m_) : m(m_) {}
+    void put(ggml_tensor * t, const uint8_t * src, size_t n) {
+        if (!m->is_b200) { m->buf_w->iface.set_tensor(m->buf_w, t, src, 0, n); return; }
+        for (size_t off = 0; off < n; off += CHUNK) jobs.push_back({(char *) t->data + off, src + off, std::min(CHUNK, n - off)});
     }
-    ~Uploader() {
-        if (stream) { cudaStreamSynchronize(stream); cudaStreamDestroy(stream); }
-        for (int b = 0; b < 2; ++b) { if (done[b]) cudaEventDestroy(done[b]); if (stage[b]) cudaFreeHost(stage[b]); }
-    }
-    bool put(ggml_tensor * t, const uint8_t * src, size_t n) {
-        if (!pinned) { m->buf_w->iface.set_tensor(m->buf_w, t, src, 0, n); return true; }
-        for (size_t off = 0; off < n; off += CHUNK) {
-            const size_t len = std::min(CHUNK, n - off);
-            const int b = next; next ^= 1;
-            if (cudaEventSynchronize(done[b]) != cudaSuccess) return false;       // the buffer's previous transfer has left it
-            memcpy(stage[b], src + off, len);
-            if (cudaMemcpyAsync((char *) t->data + off, stage[b], len, cudaMemcpyHostToDevice, stream) != cudaSuccess) return false;
-            if (cudaEventRecord(done[b], stream) != cudaSuccess) return false;
+    static bool worker(int device, const std::vector<Job> * jobs, std::atomic<size_t> * next, std::atomic<bool> * failed) {
+        void * stage[2] = {nullptr, nullptr};
+        cudaEvent_t done[2] = {nullptr, nullptr};
+        cudaStream_t stream = nullptr;
+        bool ok = cudaSetDevice(device) == cudaSuccess &&
+                  cudaMallocHost(&stage[0], CHUNK) == cudaSuccess && cudaMallocHost(&stage[1], CHUNK) == cudaSuccess &&
+                  cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&done[0], cudaEventDisableTiming) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&done[1], cudaEventDisableTiming) == cudaSuccess;
+        int b = 0;
+        while (ok && !failed->load()) {
+            const size_t i = next->fetch_add(1);
+            if (i >= jobs->size()) break;
+            const Job & j = (*jobs)[i];
+            ok = cudaEventSynchronize(done[b]) == cudaSuccess;                     // this buffer's previous transfer has left it
+            if (!ok) break;
+            memcpy(stage[b], j.src, j.len);
+            ok = cudaMemcpyAsync(j.dst, stage[b], j.len, cudaMemcpyHostToDevice, stream) == cudaSuccess &&
+                 cudaEventRecord(done[b], stream) == cudaSuccess;
+            b ^= 1;
         }
-        return true;
+        if (stream) { ok = cudaStreamSynchronize(stream) == cudaSuccess && ok; cudaStreamDestroy(stream); }
+        for (int k = 0; k < 2; ++k) { if (done[k]) cudaEventDestroy(done[k]); if (stage[k]) cudaFreeHost(stage[k]); }
+        if (!ok) { cudaGetLastError(); failed->store(true); }
+        return ok;
     }
-    bool finish() { return !pinned || cudaStreamSynchronize(stream) == cudaSuccess; }
+    bool finish() {
+        if (jobs.empty()) return true;
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess) return false;
+        unsigned hw = std::thread::hardware_concurrency();
+        const size_t n_threads = std::max<size_t>(1, std::min(std::min<size_t>(8, hw ? hw / 2 : 1), jobs.size()));
+        std::atomic<size_t> next{0};
+        std::atomic<bool> failed{false};
+        std::vector<std::thread> pool;
+        for (size_t t = 1; t < n_threads; ++t) pool.emplace_back(worker, device, &jobs, &next, &failed);
+        worker(device, &jobs, &next, &failed);
+        for (std::thread & t : pool) t.join();
+        return !failed.load();
+    }
 };
 }  // namespace
 
@@ -532,7 +553,7 @@ API b200_llama * b200_llama_load_gguf(void * reg_, int32_t device_index, const c
             why = "has a type this backend does not compute with";
         if (!why.empty()) { g_error = std::string(path) + ": tensor " + w.name + " " + why; b200_llama_free(m); return nullptr; }
         const size_t row = t_row_size(t->type, t->ne[0]);
-        if (!up.put(&w.t, f.data(*t) + (size_t) w.row_low * row, t_nbytes(&w.t))) { g_error = "upload of " + w.name + " failed"; b200_llama_free(m); return nullptr; }
+        up.put(&w.t, f.data(*t) + (size_t) w.row_low * row, t_nbytes(&w.t));
     }
     if (!up.finish()) { g_error = "weight upload failed"; b200_llama_free(m); return nullptr; }
     return m;

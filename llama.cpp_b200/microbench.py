@@ -11,6 +11,7 @@ events on the launching stream.  Bytes and flops follow the reference's accounti
   python llama.cpp_b200/microbench.py mul_mat --type q4_K -k 4096 -m 14336 -n 512
   python llama.cpp_b200/microbench.py flash_attn --n-kv 32768 --n-q 1
   python llama.cpp_b200/microbench.py sweep          # the projection shapes of Llama-3-8B
+  python llama.cpp_b200/microbench.py load --path /tmp/m.gguf     # model-file load time (file mapping -> HBM)
 
 `--copies C --reps R` bound the work (for a profiler capture: `--copies 4 --reps 1`).
 """
@@ -140,9 +141,28 @@ def bench_flash_attn(pkg, torch, n_kv, n_q, n_head=32, n_head_kv=8, d=128, copie
     return us
 
 
+def bench_load(pkg, path, reps=3):
+    """Wall time of b200_llama_load_gguf (parse, allocate, copy every tensor to the device) and one decoded token."""
+    import time
+    import numpy as np
+    from llama_cpp_b200 import llama
+    size = Path(path).stat().st_size
+    for r in range(reps):
+        t0 = time.perf_counter()
+        m = llama.Llama.from_gguf(path, n_ctx=1024, n_ubatch=512)
+        t1 = time.perf_counter()
+        logits = m.decode(np.array([1], dtype=np.int32), 0)
+        t2 = time.perf_counter()
+        assert np.isfinite(logits).all()
+        m.close()
+        print(f"LOAD {path}  {size / 1e9:.2f} GB  load {t1 - t0:7.3f} s  {size / (t1 - t0) / 1e9:6.2f} GB/s  first token {1e3 * (t2 - t1):7.1f} ms"
+              f"  ({'page cache warm' if r else 'first pass'})", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["mul_mat", "flash_attn", "sweep"])
+    ap.add_argument("op", choices=["mul_mat", "flash_attn", "sweep", "load"])
+    ap.add_argument("--path", default=None, help="load: a Llama-architecture GGUF file (llama.cpp_b200/gguf_synth.py writes one)")
     ap.add_argument("--type", default="q4_K", choices=QK_TYPES)
     ap.add_argument("-k", type=int, default=4096)
     ap.add_argument("-m", type=int, default=14336)
@@ -156,7 +176,9 @@ def main():
     import torch
     if pkg.device_count() < 1:
         raise SystemExit("no sm_100 device visible: these kernels have no CPU fallback")
-    if a.op == "mul_mat":
+    if a.op == "load":
+        bench_load(pkg, a.path, reps=min(a.reps, 3))
+    elif a.op == "mul_mat":
         bench_mul_mat(pkg, torch, a.type, a.k, a.m, a.n, a.copies, a.reps)
     elif a.op == "flash_attn":
         bench_flash_attn(pkg, torch, a.n_kv, a.n_q, copies=a.copies, reps=a.reps)

@@ -168,7 +168,7 @@ def test_load_into_driver_on_b200(b200, tiny_gguf):
 
 @pytest.mark.gpu
 def test_load_large_tensor_through_staging(b200, tmp_path):
-    """A tensor larger than one 32 MB staging chunk (and not a multiple of it) arrives intact: the loaded model's
+    """Tensors of several staging chunks (and not a multiple of the chunk size), spread over the upload workers, arrive intact: the loaded model's
     logits equal those of the tensor-by-tensor model."""
     from llama_cpp_b200 import gguf_synth, llama
     arch = dict(n_layer=1, n_embd=1024, n_head=8, n_head_kv=2, n_ff=2048, n_vocab=70016, rope_theta=10000.0, rms_eps=1e-6)

@@ -52,8 +52,9 @@ const char * b200_llama_error(void);
  * copies the tensor data from the read-only file mapping into the backend's weight buffer -- on the B200
  * backend in 16 MB chunks that a few worker threads stage through pinned buffers into asynchronous
  * host-to-device copies, each rank only its own rows when n_ranks > 1.  A file without output.weight uses the token embeddings for the
- * output projection.  Rejected with an error: other architectures, expert tensors, rope scaling or frequency
- * factors, partial rotary dimensions, tensor types this backend has no kernel for.
+ * output projection; rope_freqs.weight (Llama-3.1 files), when present, becomes the frequency-factor operand of
+ * every ROPE.  Rejected with an error: other architectures, expert tensors, a rope.scaling.type other than
+ * none, partial rotary dimensions, tensor types this backend has no kernel for.
  * b200_gguf_*: the reader by itself (metadata and tensor directory of any GGUF file, version 2 or 3). */
 typedef struct b200_gguf b200_gguf;
 b200_llama * b200_llama_load_gguf(void * reg, int32_t device_index, const char * path, int32_t n_ctx, int32_t n_ubatch,

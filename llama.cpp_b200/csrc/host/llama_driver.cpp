@@ -185,6 +185,7 @@ struct b200_llama {
         const float f[6] = {cfg.rope_theta, 1.0f, 0.0f, 1.0f, 32.0f, 1.0f};   // base, scale, ext, attn, beta_fast, beta_slow
         memcpy(params + 5, f, sizeof(f));
         memcpy(t->op_params, params, sizeof(params));
+        if (w_rope_ff >= 0) t->src[2] = W(w_rope_ff);                // per-frequency divisors (Llama-3.1 files), ggml_rope_ext's `c`
         return t;
     }
     ggml_tensor * cpy(ggml_tensor * a, ggml_tensor * b) {          // result is a view of b
@@ -248,7 +249,13 @@ struct b200_llama {
             add_weight(p + "ffn_up.weight", GGML_TYPE_Q4_K, E, F, true);
             add_weight(p + "ffn_down.weight", more, F, E, true);
         }
+        // optional, last: rope frequency factors of a model file (src/llama-model.cpp: rope_freqs, one tensor shared by the layers)
+        if (type_override && type_override->count("rope_freqs.weight")) {
+            add_weight("rope_freqs.weight", GGML_TYPE_F32, head_dim / 2, 1);
+            w_rope_ff = (int) weights.size() - 1;
+        }
     }
+    int w_rope_ff = -1;
     ggml_tensor * W(int i) { return &weights[(size_t) i].t; }
 
     void build_graph(int n_tokens, int pos0) {
@@ -523,7 +530,6 @@ API b200_llama * b200_llama_load_gguf(void * reg_, int32_t device_index, const c
     if (!f.get_u32(key("vocab_size"), n_vocab)) n_vocab = (uint32_t) tok->ne[1];
     if (f.get_u32(key("rope.dimension_count"), n_rot) && n_rot != n_embd / n_head) { g_error = "partial rotary dimensions are not supported by this driver"; return nullptr; }
     if (f.get_u32(key("expert_count"), n_expert) && n_expert > 0) { g_error = "mixture-of-experts files are not supported by this driver"; return nullptr; }
-    if (f.find("rope_freqs.weight")) { g_error = "rope frequency factors (rope_freqs.weight) are not supported by this driver"; return nullptr; }
     std::string scaling;
     if (f.get_str(key("rope.scaling.type"), scaling) && scaling != "none") { g_error = "rope scaling '" + scaling + "' is not supported by this driver"; return nullptr; }
     cfg.n_layer = (int32_t) n_layer; cfg.n_embd = (int32_t) n_embd; cfg.n_head = (int32_t) n_head; cfg.n_head_kv = (int32_t) n_head_kv;

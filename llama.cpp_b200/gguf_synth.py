@@ -32,7 +32,7 @@ def use_more_bits(il: int, n: int) -> bool:        # src/llama-quant.cpp:129-131
     return il < n // 8 or il >= 7 * n // 8 or (il - n // 8) % 3 == 2
 
 
-def tensor_list(arch: dict):
+def tensor_list(arch: dict, rope_freqs: bool = False):
     """(name, ggml type, ne0, ne1) in file order; 1-D tensors have ne1 = 1."""
     E, F, L = arch["n_embd"], arch["n_ff"], arch["n_layer"]
     KV = E // arch["n_head"] * arch["n_head_kv"]
@@ -45,6 +45,8 @@ def tensor_list(arch: dict):
         out += [(p + "attn_norm.weight", T_F32, E, 1), (p + "attn_q.weight", T_Q4_K, E, E), (p + "attn_k.weight", T_Q4_K, E, KV),
                 (p + "attn_v.weight", v_type, E, KV), (p + "attn_output.weight", T_Q4_K, E, E), (p + "ffn_norm.weight", T_F32, E, 1),
                 (p + "ffn_gate.weight", T_Q4_K, E, F), (p + "ffn_up.weight", T_Q4_K, E, F), (p + "ffn_down.weight", more, F, E)]
+    if rope_freqs:                                                        # as Llama-3.1 conversions carry it
+        out.append(("rope_freqs.weight", T_F32, E // arch["n_head"] // 2, 1))
     return out
 
 
@@ -66,8 +68,10 @@ def _kv(key: str, gtype: int, value) -> bytes:
     return head + _s(value)
 
 
-def write_llama_gguf(path, arch: dict, n_ctx_train: int = 8192, seed_base: int = 1000, device: str = "cpu", make_tensor=None) -> int:
-    """Returns the number of bytes written.  make_tensor(type, ne0, ne1, seed, device) -> flat uint8 array."""
+def write_llama_gguf(path, arch: dict, n_ctx_train: int = 8192, seed_base: int = 1000, device: str = "cpu", make_tensor=None,
+                     rope_freqs: np.ndarray | None = None) -> int:
+    """Returns the number of bytes written.  make_tensor(type, ne0, ne1, seed, device) -> flat uint8 array.
+    rope_freqs: head_dim / 2 frequency factors written as rope_freqs.weight (none by default)."""
     if make_tensor is None:
         from llama_cpp_b200 import synth
         make_tensor = synth.make_tensor
@@ -82,7 +86,7 @@ def write_llama_gguf(path, arch: dict, n_ctx_train: int = 8192, seed_base: int =
            _kv(f"{a}.attention.layer_norm_rms_epsilon", G_F32, arch["rms_eps"]), _kv(f"{a}.rope.freq_base", G_F32, arch["rope_theta"]),
            _kv(f"{a}.rope.dimension_count", G_U32, head_dim), _kv(f"{a}.vocab_size", G_U32, arch["n_vocab"]),
            _kv("tokenizer.ggml.model", G_STR, "no_vocab")]
-    tensors = tensor_list(arch)
+    tensors = tensor_list(arch, rope_freqs is not None)
     infos, off = [], 0
     for name, t, ne0, ne1 in tensors:
         dims = [ne0] if ne1 == 1 and t == T_F32 else [ne0, ne1]
@@ -95,7 +99,10 @@ def write_llama_gguf(path, arch: dict, n_ctx_train: int = 8192, seed_base: int =
         f.write(header)
         written += len(header)
         for i, (name, t, ne0, ne1) in enumerate(tensors):
-            data = np.ascontiguousarray(make_tensor(t, ne0, ne1, seed=seed_base + i, device=device)).view(np.uint8).reshape(-1)
+            if name == "rope_freqs.weight":
+                data = np.ascontiguousarray(rope_freqs, dtype=np.float32).view(np.uint8).reshape(-1)
+            else:
+                data = np.ascontiguousarray(make_tensor(t, ne0, ne1, seed=seed_base + i, device=device)).view(np.uint8).reshape(-1)
             assert data.size == row_bytes(t, ne0) * ne1, name
             f.write(data.tobytes())
             f.write(b"\0" * (-data.size % ALIGN))

@@ -141,6 +141,28 @@ def test_load_into_driver_on_reference_cpu_backend(b200, oracle, tiny_gguf):
         a.close(); b.close()
 
 
+def test_rope_frequency_factors_from_file(b200, oracle, tiny_gguf, tmp_path):
+    """rope_freqs.weight becomes the third operand of every ROPE: factors of one change nothing (bit for bit),
+    other factors change the logits."""
+    if not oracle.ref_available():
+        pytest.skip("reference build (oracle/_ref) not present")
+    from llama_cpp_b200 import gguf_synth, llama
+    reg = oracle.ref_cpu_backend_reg()
+    hd2 = TINY["n_embd"] // TINY["n_head"] // 2
+    ones, ramp = tmp_path / "ones.gguf", tmp_path / "ramp.gguf"
+    gguf_synth.write_llama_gguf(ones, TINY, seed_base=500, rope_freqs=np.ones(hd2, np.float32))
+    gguf_synth.write_llama_gguf(ramp, TINY, seed_base=500, rope_freqs=np.linspace(1.0, 8.0, hd2).astype(np.float32))
+    outs = []
+    for p in (tiny_gguf, ones, ramp):
+        m = llama.Llama.from_gguf(p, n_ctx=512, n_ubatch=64, reg=reg, n_threads=2)
+        assert [t["name"] for t in m.tensors()][-1] == ("blk.1.ffn_down.weight" if p == tiny_gguf else "rope_freqs.weight")
+        outs.append(_logits(m))
+        m.close()
+    for x, y in zip(outs[0], outs[1]):
+        assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
+    assert oracle.nmse(outs[0][1], outs[2][1]) > 1e-6
+
+
 def test_load_rejects_unsupported_models(b200, oracle, tiny_gguf, tmp_path):
     from llama_cpp_b200 import llama
     raw = tiny_gguf.read_bytes()
@@ -164,6 +186,23 @@ def test_load_into_driver_on_b200(b200, tiny_gguf):
         assert a.launch_count > 0
     finally:
         a.close(); b.close()
+
+
+@pytest.mark.gpu
+def test_rope_frequency_factors_b200_matches_reference_cpu_backend(b200, oracle, tmp_path):
+    if not oracle.ref_available():
+        pytest.skip("reference build (oracle/_ref) not present")
+    from llama_cpp_b200 import gguf_synth, llama
+    arch = dict(n_layer=2, n_embd=1024, n_head=8, n_head_kv=2, n_ff=2048, n_vocab=2048, rope_theta=500000.0, rms_eps=1e-5)
+    path = tmp_path / "ff.gguf"
+    gguf_synth.write_llama_gguf(path, arch, seed_base=40, rope_freqs=np.linspace(1.0, 8.0, 64).astype(np.float32))
+    cpu = llama.Llama.from_gguf(path, n_ctx=512, n_ubatch=64, reg=oracle.ref_cpu_backend_reg(), n_threads=8)
+    gpu = llama.Llama.from_gguf(path, n_ctx=512, n_ubatch=64)
+    try:
+        for x, y in zip(_logits(cpu), _logits(gpu)):
+            assert oracle.nmse(x, y) <= 5e-4 * (7 * arch["n_layer"] + 1)       # per-op criterion x chained MUL_MATs
+    finally:
+        cpu.close(); gpu.close()
 
 
 @pytest.mark.gpu

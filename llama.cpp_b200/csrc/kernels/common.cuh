@@ -190,6 +190,14 @@ __device__ __forceinline__ int iq4nl_value(int idx) {
     const uint64_t t = idx < 8 ? 0xF6EADDCFBFAD9881ull : 0x7159453526190D01ull;
     return (int) (int8_t) (t >> (8 * (idx & 7)));
 }
+// four table lookups at once: two byte permutes over the table halves and a select on bit 3 of each index
+__device__ __forceinline__ uint32_t iq4nl_lut4(uint32_t idx) {          // idx: four byte lanes, each 0..15
+    const uint32_t s = idx & 0x07070707u, t = s | (s >> 4);
+    const uint32_t sel = (t & 0xFFu) | ((t >> 8) & 0xFF00u);
+    const uint32_t lo = __byte_perm(0xBFAD9881u, 0xF6EADDCFu, sel), hi = __byte_perm(0x26190D01u, 0x71594535u, sel);
+    const uint32_t m = ((idx >> 3) & 0x01010101u) * 0xFFu;
+    return (lo & ~m) | (hi & m);
+}
 template <> __device__ __forceinline__ float dequant_elem<T_IQ4_NL>(const uint8_t * row, int64_t i) {
     const blk_iq4_nl * b = (const blk_iq4_nl *) row + (i >> 5);
     const int j = i & 31;

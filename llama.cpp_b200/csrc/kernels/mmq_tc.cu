@@ -138,6 +138,45 @@ template <> struct Deq32<T_Q4_K> {
     }
 };
 
+// Q5_K: as Q4_K plus bit sb of qh[l] as the fifth bit.  A thread's consecutive k-steps are sub-blocks sb and sb + 2 of
+// the same super-block: they share the header and the 32 qh bytes, so one Raw is loaded per pair of k-steps.
+template <> struct Deq32<T_Q5_K> {
+    static constexpr int KPR = 2;
+    struct Raw { uint4 hd, ha, hb, qa[2], qb[2]; int sb0; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {      // k: first k-step of the pair
+        const uint8_t * b = row + (k >> 8) * 176;
+        r.sb0 = (k >> 5) & 7;
+        r.hd = __ldg((const uint4 *) b);
+        r.ha = __ldg((const uint4 *) (b + 16));
+        r.hb = __ldg((const uint4 *) (b + 32));
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            const int o = 48 + 32 * ((r.sb0 + 2 * s) >> 1);
+            r.qa[s] = __ldg((const uint4 *) (b + o));
+            r.qb[s] = __ldg((const uint4 *) (b + o + 16));
+        }
+    }
+    static __device__ __forceinline__ void get(const Raw & r, int sub, uint32_t (&out)[16]) {
+        const int sb = r.sb0 + 2 * sub;
+        const float2 dm = __half22float2(u32_as_h2(r.hd.x));
+        const uint32_t s0 = r.hd.y, s1 = r.hd.z, s2 = r.hd.w;
+        int sc, m;
+        if (sb < 4) { sc = (s0 >> (8 * sb)) & 63; m = (s1 >> (8 * sb)) & 63; }
+        else { const int t = sb - 4; sc = ((s2 >> (8 * t)) & 0xF) | (((s0 >> (8 * t + 6)) & 3) << 4); m = ((s2 >> (8 * t + 4)) & 0xF) | (((s1 >> (8 * t + 6)) & 3) << 4); }
+        const __half2 ds = __float2half2_rn(dm.x * (float) sc), nm = __float2half2_rn(-dm.y * (float) m);
+        const uint4 qa = sub ? r.qa[1] : r.qa[0], qb = sub ? r.qb[1] : r.qb[0];
+        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+        const uint32_t h[8] = {r.ha.x, r.ha.y, r.ha.z, r.ha.w, r.hb.x, r.hb.y, r.hb.z, r.hb.w};
+        const int sh = (sb & 1) * 4;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t v = ((w[i] >> sh) & 0x0F0F0F0Fu) | (((h[i] >> sb) & 0x01010101u) << 4);      // 4 values 0..31
+            out[2 * i]     = h2_as_u32(__hfma2(bytes01_h2(v), ds, nm));
+            out[2 * i + 1] = h2_as_u32(__hfma2(bytes23_h2(v), ds, nm));
+        }
+    }
+};
+
 // Q6_K: k .. k+31 is group t = (k >> 5) & 3 of half n128 = (k >> 7) & 1 (ggml-quants.c:1690-1719);
 // blocks are only 2-byte aligned, so the bytes come in as aligned words plus a funnel shift
 // Q6_K: the 32 ql bytes and 32 qh bytes a thread reads hold its weights of TWO k-steps (sub-block groups t and
@@ -221,6 +260,120 @@ template <> struct Deq32<T_Q8_0> {
             const uint32_t u = r.w[i] ^ 0x80808080u;
             out[2 * i]     = h2_as_u32(__hmul2(__hsub2(bytes01_h2(u), off), d));
             out[2 * i + 1] = h2_as_u32(__hmul2(__hsub2(bytes23_h2(u), off), d));
+        }
+    }
+};
+
+// IQ4_NL: the Q4_0 block with its nibbles mapped through the code book; table values are signed bytes
+template <> struct Deq32<T_IQ4_NL> {
+    static constexpr int KPR = 1;
+    struct Raw { uint32_t w[4]; uint32_t d; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) { load_block32<4>(row + (k >> 5) * 18, r.w, r.d); }
+    static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
+        const __half2 d = __half2half2(__ushort_as_half((unsigned short) r.d)), off = u32_as_h2(0x58005800u);   // 128.0
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t lo = iq4nl_lut4(r.w[i] & 0x0F0F0F0Fu) ^ 0x80808080u, hi = iq4nl_lut4((r.w[i] >> 4) & 0x0F0F0F0Fu) ^ 0x80808080u;
+            out[2 * i]         = h2_as_u32(__hmul2(__hsub2(bytes01_h2(lo), off), d));
+            out[2 * i + 1]     = h2_as_u32(__hmul2(__hsub2(bytes23_h2(lo), off), d));
+            out[8 + 2 * i]     = h2_as_u32(__hmul2(__hsub2(bytes01_h2(hi), off), d));
+            out[8 + 2 * i + 1] = h2_as_u32(__hmul2(__hsub2(bytes23_h2(hi), off), d));
+        }
+    }
+};
+// IQ4_XS: blocks of 136 bytes are 8-byte aligned; a k-step is sub-block ib: 16 qs bytes and a 6-bit scale
+template <> struct Deq32<T_IQ4_XS> {
+    static constexpr int KPR = 1;
+    struct Raw { uint2 hd, q0, q1; int ib; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
+        const uint8_t * b = row + (k >> 8) * 136;
+        r.ib = (k >> 5) & 7;
+        r.hd = __ldg((const uint2 *) b);
+        r.q0 = __ldg((const uint2 *) (b + 8 + 16 * r.ib));
+        r.q1 = __ldg((const uint2 *) (b + 16 + 16 * r.ib));
+    }
+    static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
+        const int ls = (int) (((r.hd.y >> (4 * r.ib)) & 0xF) | ((((r.hd.x >> 16) >> (2 * r.ib)) & 3) << 4)) - 32;   // scales_l nibble, scales_h pair
+        const __half2 d = __float2half2_rn(__half2float(__ushort_as_half((unsigned short) (r.hd.x & 0xffffu))) * (float) ls);
+        const __half2 off = u32_as_h2(0x58005800u);
+        const uint32_t w[4] = {r.q0.x, r.q0.y, r.q1.x, r.q1.y};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t lo = iq4nl_lut4(w[i] & 0x0F0F0F0Fu) ^ 0x80808080u, hi = iq4nl_lut4((w[i] >> 4) & 0x0F0F0F0Fu) ^ 0x80808080u;
+            out[2 * i]         = h2_as_u32(__hmul2(__hsub2(bytes01_h2(lo), off), d));
+            out[2 * i + 1]     = h2_as_u32(__hmul2(__hsub2(bytes23_h2(lo), off), d));
+            out[8 + 2 * i]     = h2_as_u32(__hmul2(__hsub2(bytes01_h2(hi), off), d));
+            out[8 + 2 * i + 1] = h2_as_u32(__hmul2(__hsub2(bytes23_h2(hi), off), d));
+        }
+    }
+};
+// Q2_K: blocks of 84 bytes are 4-byte aligned.  A thread's consecutive k-steps are bit pairs j and j + 2 of the same 32
+// qs bytes (128-half n128), so one Raw serves a pair of k-steps; each k-step has two 16-weight sub-blocks with a 4-bit
+// scale and a 4-bit min.
+template <> struct Deq32<T_Q2_K> {
+    static constexpr int KPR = 2;
+    struct Raw { uint32_t q[8], sc[2], dm; int j0; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {      // k: first k-step of the pair
+        const uint8_t * b = row + (k >> 8) * 84;
+        const int n128 = (k >> 7) & 1;
+        r.j0 = (k >> 5) & 1;                                            // the pair is (j0, j0 + 2)
+        const uint32_t * pq = (const uint32_t *) (b + 16 + 32 * n128);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r.q[i] = __ldg(pq + i);
+        r.sc[0] = *(const uint16_t *) (b + 8 * n128 + 2 * r.j0);        // scales[8 n + 2 j], [.. + 1]
+        r.sc[1] = *(const uint16_t *) (b + 8 * n128 + 2 * r.j0 + 4);
+        r.dm = __ldg((const uint32_t *) (b + 80));
+    }
+    static __device__ __forceinline__ void get(const Raw & r, int sub, uint32_t (&out)[16]) {
+        const float2 dm = __half22float2(u32_as_h2(r.dm));
+        const uint32_t scw = sub ? r.sc[1] : r.sc[0];
+        const __half2 d0 = __float2half2_rn(dm.x * (float) (scw & 0xF)),        m0 = __float2half2_rn(-dm.y * (float) ((scw >> 4) & 0xF));
+        const __half2 d1 = __float2half2_rn(dm.x * (float) ((scw >> 8) & 0xF)), m1 = __float2half2_rn(-dm.y * (float) (scw >> 12));
+        const int sh = 2 * (r.j0 + 2 * sub);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t v = (r.q[i] >> sh) & 0x03030303u;
+            out[2 * i]     = h2_as_u32(__hfma2(bytes01_h2(v), i < 4 ? d0 : d1, i < 4 ? m0 : m1));
+            out[2 * i + 1] = h2_as_u32(__hfma2(bytes23_h2(v), i < 4 ? d0 : d1, i < 4 ? m0 : m1));
+        }
+    }
+};
+// Q3_K: blocks of 110 bytes are 2-byte aligned: the 32 qs bytes and the 32 hmask bytes come in as aligned words plus a
+// funnel shift (both at the same alignment: their offsets differ by a multiple of 4).  Pairs of k-steps as for Q2_K.
+template <> struct Deq32<T_Q3_K> {
+    static constexpr int KPR = 2;
+    struct Raw { uint32_t q[9], hm[9]; uint32_t s0, s1, s2; uint32_t d, sh; int j0, n128; };
+    static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) {
+        const uint8_t * b = row + (k >> 8) * 110;
+        r.n128 = (k >> 7) & 1;
+        r.j0 = (k >> 5) & 1;
+        const uint8_t * pq = b + 32 + 32 * r.n128;
+        const uint32_t * aq = (const uint32_t *) ((uintptr_t) pq & ~(uintptr_t) 3);
+        const uint32_t * ah = (const uint32_t *) ((uintptr_t) b & ~(uintptr_t) 3);
+        r.sh = ((uint32_t) (uintptr_t) b & 3u) * 8u;
+#pragma unroll
+        for (int i = 0; i < 9; ++i) { r.q[i] = __ldg(aq + i); r.hm[i] = __ldg(ah + i); }
+        const uint16_t * ps = (const uint16_t *) (b + 96);              // the 12 scale bytes as three words
+        r.s0 = ps[0] | ((uint32_t) ps[1] << 16); r.s1 = ps[2] | ((uint32_t) ps[3] << 16); r.s2 = ps[4] | ((uint32_t) ps[5] << 16);
+        r.d = ps[6];
+    }
+    static __device__ __forceinline__ int scale6(const Raw & r, int s) {
+        auto byte = [&](int t) { return ((t < 4 ? r.s0 : (t < 8 ? r.s1 : r.s2)) >> (8 * (t & 3))) & 0xFFu; };
+        const uint32_t lo = s < 8 ? (byte(s) & 0xF) : (byte(s - 8) >> 4);
+        return (int) (lo | (((byte(8 + (s & 3)) >> (2 * (s >> 2))) & 3) << 4)) - 32;
+    }
+    static __device__ __forceinline__ void get(const Raw & r, int sub, uint32_t (&out)[16]) {
+        const int j = r.j0 + 2 * sub;
+        const float d = __half2float(__ushort_as_half((unsigned short) r.d));
+        const __half2 d0 = __float2half2_rn(d * (float) scale6(r, 8 * r.n128 + 2 * j)), d1 = __float2half2_rn(d * (float) scale6(r, 8 * r.n128 + 2 * j + 1));
+        const __half2 off = u32_as_h2(0x44004400u);                     // 4.0
+        const int hb = 4 * r.n128 + j;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t Q = __funnelshift_r(r.q[i], r.q[i + 1], r.sh), H = __funnelshift_r(r.hm[i], r.hm[i + 1], r.sh);
+            const uint32_t v = ((Q >> (2 * j)) & 0x03030303u) | (((H >> hb) & 0x01010101u) << 2);          // 0..7, value = v - 4
+            out[2 * i]     = h2_as_u32(__hmul2(__hsub2(bytes01_h2(v), off), i < 4 ? d0 : d1));
+            out[2 * i + 1] = h2_as_u32(__hmul2(__hsub2(bytes23_h2(v), off), i < 4 ? d0 : d1));
         }
     }
 };

@@ -377,15 +377,7 @@ template <> struct WT<T_Q3_K> {
     }
 };
 
-// IQ4_NL: Q4_0 layout, nibbles looked up in the 16-entry table of the format (ggml-quants.c:2434): four lookups
-// at once with two byte permutes over the table halves and a select on bit 3 of each index
-__device__ __forceinline__ uint32_t iq4nl_lut4(uint32_t idx) {          // idx: four byte lanes, each 0..15
-    const uint32_t s = idx & 0x07070707u, t = s | (s >> 4);
-    const uint32_t sel = (t & 0xFFu) | ((t >> 8) & 0xFF00u);
-    const uint32_t lo = __byte_perm(0xBFAD9881u, 0xF6EADDCFu, sel), hi = __byte_perm(0x26190D01u, 0x71594535u, sel);
-    const uint32_t m = ((idx >> 3) & 0x01010101u) * 0xFFu;
-    return (lo & ~m) | (hi & m);
-}
+// IQ4_NL: Q4_0 layout, nibbles looked up in the 16-entry table of the format with iq4nl_lut4
 template <> struct WT<T_IQ4_NL> {
     static constexpr int UNIT = 32, BLK_ELEMS = 32, BLK_BYTES = 18;
     template <int N> static __device__ __forceinline__ void dot(const uint8_t * row, int u, const ActView & xv, float (&acc)[N]) {

@@ -25,7 +25,9 @@ ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
 import __graft_entry__ as entry  # noqa: E402
 
-QK_TYPES = ("q4_0", "q8_0", "q4_K", "q5_K", "q6_K")
+QK_TYPES = ("q4_0", "q8_0", "q4_K", "q5_K", "q6_K", "q2_K", "q3_K", "iq4_nl", "iq4_xs")
+# byte offsets of the F16 scale fields inside one block of the types filled with random bytes below
+_SCALE_FIELDS = {"q2_K": (84, (80, 82)), "q3_K": (110, (108,)), "iq4_nl": (18, (0,)), "iq4_xs": (136, (0,))}
 
 
 def _weights(pkg, torch, qtype, k, m, copies):
@@ -41,6 +43,13 @@ def _weights(pkg, torch, qtype, k, m, copies):
         q4 = torch.from_numpy(synth.make_tensor(pkg.TYPES["q4_K"], k, rows, 1, device="cuda")).cuda().reshape(-1, 144)
         qh = torch.randint(0, 256, (q4.shape[0], 32), dtype=torch.uint8, device="cuda")
         base = torch.cat([q4[:, :16], qh, q4[:, 16:]], 1).reshape(-1)
+    elif qtype in _SCALE_FIELDS:   # timing only: random quant bytes, block scales set to small positive F16 numbers
+        bb, fields = _SCALE_FIELDS[qtype]
+        blk = torch.randint(0, 256, (rows * rb // bb, bb), dtype=torch.uint8, device="cuda")
+        for f in fields:
+            blk[:, f] = torch.randint(0, 256, (blk.shape[0],), dtype=torch.uint8, device="cuda")
+            blk[:, f + 1] = 0x1C        # F16 0x1Cxx: about 4e-3 .. 8e-3
+        base = blk.reshape(-1)
     else:                       # Q4_0 / Q8_0 through the device quantizers (CPY F32 -> quantized)
         import numpy as np
         x = (0.02 * torch.randn(rows, k, device="cuda")).cpu().numpy()
@@ -193,6 +202,9 @@ def main():
                 bench_mul_mat(pkg, torch, qt, 4096, 128256, n, copies=2, reps=5)
         bench_mul_mat(pkg, torch, "q4_0", 4096, 4096, 1)
         bench_mul_mat(pkg, torch, "q4_0", 4096, 4096, 512, reps=5)
+        for qt in ("q2_K", "q3_K", "iq4_nl", "iq4_xs", "q5_K"):       # types served by the generic kernels
+            for n in (1, 512):
+                bench_mul_mat(pkg, torch, qt, 4096, 14336, n, reps=a.reps if n == 1 else 5)
         for n_kv in (512, 4096, 32768):
             for n_q in (1, 512):
                 bench_flash_attn(pkg, torch, n_kv, n_q, reps=a.reps if n_q == 1 else 5)

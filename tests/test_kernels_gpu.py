@@ -88,7 +88,8 @@ def test_mul_mat_llama_shapes(b200, oracle, golden, qt, k, m, n):
     assert oracle.nmse(2.0 * got, got2) <= 1e-9
 
 
-@pytest.mark.parametrize("qt,k,m", [("q4_0", 4096, 4096), ("q4_K", 4096, 14336), ("q6_K", 14336, 4096), ("q8_0", 4096, 4096), ("q4_K", 4096, 4096)])
+@pytest.mark.parametrize("qt,k,m", [("q4_0", 4096, 4096), ("q4_K", 4096, 14336), ("q6_K", 14336, 4096), ("q8_0", 4096, 4096), ("q4_K", 4096, 4096),
+                                    ("q5_K", 8192, 1024), ("q2_K", 4096, 4096), ("q3_K", 4096, 4096), ("iq4_nl", 4096, 4096), ("iq4_xs", 4096, 4096)])
 @pytest.mark.parametrize("n", [32, 128, 512])
 def test_mul_mat_llama_shapes_prefill(b200, oracle, golden, qt, k, m, n):
     """The batch sizes that take the tensor-core GEMM, at full Llama-3-8B shapes; the oracle (scalar C) is

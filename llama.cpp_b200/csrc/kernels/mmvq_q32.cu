@@ -1,5 +1,6 @@
 // Decode mat-vec for the 32-weight block formats Q4_0 (18-byte blocks: fp16 d + 16 nibble bytes,
-// ggml/src/ggml-common.h:161-166) and Q8_0 (34-byte blocks: fp16 d + 32 int8, :203-208).
+// ggml/src/ggml-common.h:161-166), Q8_0 (34-byte blocks: fp16 d + 32 int8, :203-208) and IQ4_NL (the Q4_0 layout with
+// the nibbles mapped through the format's 16-entry code book, :398-403).
 //
 // The blocks are only 2-byte aligned, but 128 of them (4096 weights; 2304 or 4352 bytes) are a 16-byte multiple,
 // so a warp fetches such a run of its weight row with fully coalesced 128-bit loads into registers, parks it in a
@@ -45,7 +46,7 @@ __device__ __forceinline__ int dp4a_us32(uint32_t a, int b, int c) {   // unsign
 
 template <int T, int N>
 __global__ void __launch_bounds__(Q32_WARPS * 32, 2) mmvq_q32_kernel(const Q32Params p) {
-    constexpr int BS = (T == T_Q4_0) ? 18 : 34;                    // block bytes
+    constexpr int BS = (T == T_Q8_0) ? 34 : 18;                    // block bytes (Q4_0 and IQ4_NL: 18)
     constexpr int RUN_BYTES = Q32_RUN_BLOCKS * BS;                 // 2304 / 4352
     constexpr int VPL = (RUN_BYTES / 16 + 31) / 32;                // uint4 per lane: 5 / 9
     constexpr int LW = 4 * BS / 4;                                 // 32-bit words of a lane's four blocks: 18 / 34
@@ -119,6 +120,11 @@ __global__ void __launch_bounds__(Q32_WARPS * 32, 2) mmvq_q32_kernel(const Q32Pa
                     uint32_t q[(BS - 2) / 4];
 #pragma unroll
                     for (int i = 0; i < (BS - 2) / 4; ++i) q[i] = word_at<OFF + 2>(w, i);
+                    uint32_t nl[8];                                // IQ4_NL: the nibbles mapped through the code book, once per block
+                    if (T == T_IQ4_NL) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) { nl[i] = iq4nl_lut4(q[i] & 0x0F0F0F0Fu); nl[4 + i] = iq4nl_lut4((q[i] >> 4) & 0x0F0F0F0Fu); }
+                    }
 #pragma unroll
                     for (int n = 0; n < N; ++n) {
                         const uint8_t * ab = acts + n * col_bytes + a_base;
@@ -132,6 +138,13 @@ __global__ void __launch_bounds__(Q32_WARPS * 32, 2) mmvq_q32_kernel(const Q32Pa
                             s = dp4a_us32((q[0] >> 4) & 0x0F0F0F0Fu, (int) x1.x, s); s = dp4a_us32((q[1] >> 4) & 0x0F0F0F0Fu, (int) x1.y, s);
                             s = dp4a_us32((q[2] >> 4) & 0x0F0F0F0Fu, (int) x1.z, s); s = dp4a_us32((q[3] >> 4) & 0x0F0F0F0Fu, (int) x1.w, s);
                             acc[n] += d * (ds.x * (float) s - 8.0f * ds.y);
+                        } else if (T == T_IQ4_NL) {
+                            int s = 0;
+                            s = __dp4a((int) nl[0], (int) x0.x, s); s = __dp4a((int) nl[1], (int) x0.y, s);
+                            s = __dp4a((int) nl[2], (int) x0.z, s); s = __dp4a((int) nl[3], (int) x0.w, s);
+                            s = __dp4a((int) nl[4], (int) x1.x, s); s = __dp4a((int) nl[5], (int) x1.y, s);
+                            s = __dp4a((int) nl[6], (int) x1.z, s); s = __dp4a((int) nl[7], (int) x1.w, s);
+                            acc[n] += d * ds.x * (float) s;
                         } else {
                             int s = 0;
                             s = __dp4a((int) q[0], (int) x0.x, s); s = __dp4a((int) q[1], (int) x0.y, s);
@@ -158,7 +171,7 @@ __global__ void __launch_bounds__(Q32_WARPS * 32, 2) mmvq_q32_kernel(const Q32Pa
 
 template <int T, int N>
 static cudaError_t launch_q32_tn(const Q32Params & p, int sm_count, int device, int use_pdl, cudaStream_t stream) {
-    constexpr int BS = (T == T_Q4_0) ? 18 : 34;
+    constexpr int BS = (T == T_Q8_0) ? 34 : 18;
     const size_t smem = (size_t) N * ((p.K + 127) / 128) * 160 + (size_t) Q32_WARPS * (Q32_RUN_BLOCKS * BS + 16);
     auto kern = mmvq_q32_kernel<T, N>;
     static unsigned attr_mask = 0;
@@ -202,9 +215,9 @@ static cudaError_t launch_q32_t(const Q32Params & p, int N, int sm, int dev, int
 
 // needs 16-byte aligned rows made of whole 8-block groups and whole activation blocks, no batching / expert indirection
 bool mmvq_q32_applicable(const MmvqArgs & a) {
-    if ((a.type != T_Q4_0 && a.type != T_Q8_0) || a.ids || a.ne12 * a.ne13 != 1) return false;
+    if ((a.type != T_Q4_0 && a.type != T_Q8_0 && a.type != T_IQ4_NL) || a.ids || a.ne12 * a.ne13 != 1) return false;
     if (((uintptr_t) a.W & 15) || (a.w_nb1 & 15) || (a.K % 256) != 0) return false;
-    const int bs = a.type == T_Q4_0 ? 18 : 34;
+    const int bs = a.type == T_Q8_0 ? 34 : 18;
     if ((size_t) a.N * ((a.K + 127) / 128) * 160 + (size_t) Q32_WARPS * (Q32_RUN_BLOCKS * bs + 16) > 200 * 1024) return false;
     return true;
 }
@@ -217,6 +230,7 @@ cudaError_t launch_mmvq_q32(const MmvqArgs & a, cudaStream_t stream) {
     p.M = a.M; p.K = a.K; p.x_col0 = a.x_col0;
     p.n_peer = a.n_peer; for (int i = 0; i < a.n_peer; ++i) p.peer_delta[i] = a.peer_delta[i];
     if (a.type == T_Q4_0) return launch_q32_t<T_Q4_0>(p, a.N, a.sm_count, a.device, a.use_pdl, stream);
+    if (a.type == T_IQ4_NL) return launch_q32_t<T_IQ4_NL>(p, a.N, a.sm_count, a.device, a.use_pdl, stream);
     return launch_q32_t<T_Q8_0>(p, a.N, a.sm_count, a.device, a.use_pdl, stream);
 }
 

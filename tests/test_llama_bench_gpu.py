@@ -69,3 +69,29 @@ def test_libllama_logits_plugin_vs_reference_cpu(tmp_path, b200, oracle, fa):
     n_mul_mat = 7 * TINY["n_layer"] + 1
     for a, b in zip(cpu, gpu):
         assert oracle.nmse(a, b) <= 5e-4 * n_mul_mat
+
+
+def test_gguf_loader_and_driver_agree_with_libllama(tmp_path, b200, oracle):
+    """The same model file evaluated twice on the B200 kernels: by the reference's libllama (its loader, its graph)
+    through the plugin, and by this package's own GGUF loader and graph driver.  Same tokens (std::mt19937 and
+    numpy's RandomState are the same generator).  The two graphs are not node for node the same (views, batching,
+    which kernel serves an op), so the bound is the per-op criterion of test-backend-ops, 5e-4, once -- not times
+    the depth as against the CPU backend; a wrong hyper-parameter, tensor placement or rope convention in the loader
+    gives an NMSE near 1."""
+    import numpy as np
+    from llama_cpp_b200 import gguf_synth, llama
+    model = tmp_path / "tiny.gguf"
+    gguf_synth.write_llama_gguf(model, TINY, device="cuda")
+    n_prompt, n_gen, seed = 37, 6, 5
+    ref, log = run_logits(model, tmp_path / "gpu.bin", 99, plugin=True, n_prompt=n_prompt, n_gen=n_gen, fa=1)
+    assert "B200" in log
+    toks = (np.random.RandomState(seed).randint(0, 2 ** 32, size=n_prompt + n_gen, dtype=np.uint64) % TINY["n_vocab"]).astype(np.int32)
+    m = llama.Llama.from_gguf(model, n_ctx=512, n_ubatch=64)
+    try:
+        mine = [m.decode(toks[:n_prompt], 0).copy()]
+        for i in range(n_gen):
+            mine.append(m.decode(toks[n_prompt + i:n_prompt + i + 1], n_prompt + i).copy())
+    finally:
+        m.close()
+    for a, b in zip(ref, mine):
+        assert oracle.nmse(a, b) <= 5e-4

@@ -9,7 +9,8 @@
 // dequantized to F16 on its way into shared memory (exact up to the F16 rounding of d*q), and one
 // FP32 accumulator in TMEM runs over the whole K with tcgen05.mma kind::f16.
 //
-// CTA = 9 warps, one 128 (weight rows) x 128 (tokens) output tile:
+// CTA = 9 warps, one 128 (weight rows) x 128 or 256 (tokens) output tile (256 when that still gives every SM a CTA:
+// a weight tile is then dequantized half as often):
 //   warps 0-7  producers: thread (r, h) dequantizes 32 consecutive weights of weight row r per k-step
 //              (raw quant bytes of the next k-step are prefetched into registers first) and writes them
 //              as F16 in the canonical K-major SWIZZLE_128B layout (row r at r*128 B, 16-byte chunk c at
@@ -30,10 +31,8 @@ namespace b200 {
 
 static constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
 static constexpr int TC_STAGES = 4;
-static constexpr int TC_STAGE_BYTES = (TC_BM + TC_BN) * TC_BK * 2;      // 32 KB
 static constexpr int TC_PRODUCERS = 256;
 static constexpr int TC_THREADS = TC_PRODUCERS + 32;
-static constexpr int TC_TMEM_COLS = 128;
 static constexpr int TC_PF = 4;                                        // k-steps of raw weight bytes in flight per producer thread
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
@@ -407,8 +406,11 @@ __device__ __forceinline__ void tma_load_2d(void * smem_dst, const CUtensorMap *
         :: "r"(smem_u32(smem_dst)), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 
-template <int T>
+// BN: token columns per CTA, 128 or 256.  The wide tile halves the number of times a weight tile is dequantized (the
+// producers, not the tensor core, bound this kernel) and is used when it still leaves every SM a CTA.
+template <int T, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap xmap) {
+    constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;            // 32 KB / 48 KB
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     pdl_launch_dependents();          // the next kernel may start its prologue (its weight prefetch) right away
     // operand stages must be 1024-byte aligned for the 128-byte swizzle pattern
@@ -418,7 +420,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;    // adjacent CTAs share one weight tile (L2 reuse)
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;    // adjacent CTAs share one weight tile (L2 reuse)
     const int ks_begin = (int) blockIdx.z * p.kps;                  // split-K: this CTA's range of k-steps
     const int ksteps = min(p.kps, p.K / TC_BK - ks_begin);
     const int k_base = ks_begin * TC_BK;
@@ -431,7 +433,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == MMA_WARP) tmem_alloc(&tmem_base_sh, TC_TMEM_COLS);
+    if (warp == MMA_WARP) tmem_alloc(&tmem_base_sh, BN);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -460,9 +462,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
                 const uint32_t round = (uint32_t) (ks / TC_STAGES);
                 if (ks >= TC_STAGES && !mbar_wait(&empty_bar[s], (round - 1) & 1)) { ok = false; break; }
                 if (*(volatile int *) &abort_flag) { ok = false; break; }
-                uint8_t * sa = smem + (size_t) s * TC_STAGE_BYTES;      // A: weights 128 x 64 F16
+                uint8_t * sa = smem + (size_t) s * STAGE_BYTES;      // A: weights 128 x 64 F16
                 if (tid == 0) {                                         // B: activations 128 x 64 F16 by TMA (rows past N read as zero)
-                    mbar_arrive_expect_tx(&full_bar[s], TC_BN * TC_BK * 2);
+                    mbar_arrive_expect_tx(&full_bar[s], BN * TC_BK * 2);
                     tma_load_2d(sa + TC_BM * TC_BK * 2, &xmap, k_base + ks * TC_BK, n0, &full_bar[s]);
                 }
                 uint32_t wv[16];
@@ -487,12 +489,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         // ------------------------------ epilogue ------------------------------
         if (ok && mbar_wait(&accum_bar, 0)) {
             tc_fence_after();
-            const int quad = warp & 3, chalf = warp >> 2;               // lane quadrant; which 64 of the 128 columns
+            const int quad = warp & 3, chalf = warp >> 2;               // lane quadrant; which half of the BN columns
             const int m = m0 + quad * 32 + lane;
             char * out = p.ksplit > 1 ? (char *) (p.part + (int64_t) blockIdx.z * p.M * p.N) : (char *) p.dst;
             const int64_t out_nb1 = p.ksplit > 1 ? (int64_t) p.M * 4 : p.dst_nb1;
 #pragma unroll 1
-            for (int c0 = chalf * 64; c0 < chalf * 64 + 64; c0 += 32) {
+            for (int c0 = chalf * (BN / 2); c0 < chalf * (BN / 2) + BN / 2; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t) (quad * 32) << 16) + (uint32_t) c0, v);
                 tmem_ld_wait();
@@ -509,7 +511,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         }
     } else {
         // ------------------------------ MMA issuer ------------------------------
-        constexpr uint32_t idesc = umma_idesc_f16(TC_BM, TC_BN);
+        constexpr uint32_t idesc = umma_idesc_f16(TC_BM, BN);
         bool ok = true;
         for (int ks = 0; ks < ksteps && ok; ++ks) {
             const int s = ks % TC_STAGES;
@@ -518,7 +520,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
             if (*(volatile int *) &abort_flag) { ok = false; break; }
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t a_addr = smem_u32(smem + (size_t) s * TC_STAGE_BYTES);
+                const uint32_t a_addr = smem_u32(smem + (size_t) s * STAGE_BYTES);
                 const uint32_t b_addr = a_addr + TC_BM * TC_BK * 2;
 #pragma unroll
                 for (int kk = 0; kk < TC_BK / 16; ++kk) {
@@ -534,7 +536,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, TC_TMEM_COLS); }
+    if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, BN); }
 }
 
 bool mmq_tc_supported(int type, int64_t M, int64_t N, int64_t K) {
@@ -592,32 +594,40 @@ size_t mmq_tc_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count) {
     return s > 1 ? (size_t) s * M * N * 4 + 256 : 0;
 }
 
-template <int T>
-static cudaError_t launch_tc_t(const TcParams & p, int device, int use_pdl, cudaStream_t stream) {
-    auto kern = mmq_tc_kernel<T>;
-    const size_t smem = (size_t) TC_STAGES * TC_STAGE_BYTES + 1024;
+template <int T, int BN>
+static cudaError_t launch_tc_tb(const TcParams & p, int device, int use_pdl, cudaStream_t stream) {
+    auto kern = mmq_tc_kernel<T, BN>;
+    const size_t smem = (size_t) TC_STAGES * (TC_BM + BN) * TC_BK * 2 + 1024;
     static unsigned attr_mask = 0;
     if (!(attr_mask & (1u << device))) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         if (e != cudaSuccess) return e;
         attr_mask |= 1u << device;
     }
-    // tensor map of the F16 activations [N][K]: boxes of 64 (k) x 128 (tokens), 128-byte swizzle, zero fill
+    // tensor map of the F16 activations [N][K]: boxes of 64 (k) x BN (tokens), 128-byte swizzle, zero fill
     encode_tiled_fn enc = get_encode_tiled();
     if (!enc) return cudaErrorNotSupported;
     CUtensorMap xmap;
     const cuuint64_t gdim[2] = {(cuuint64_t) p.K, (cuuint64_t) p.N};
     const cuuint64_t gstr[1] = {(cuuint64_t) p.K * 2};
-    const cuuint32_t box[2] = {TC_BK, TC_BN}, estr[2] = {1, 1};
+    const cuuint32_t box[2] = {TC_BK, BN}, estr[2] = {1, 1};
     if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *) p.Xh, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    dim3 grid((unsigned) ((p.N + TC_BN - 1) / TC_BN), (unsigned) ((p.M + TC_BM - 1) / TC_BM), (unsigned) p.ksplit);
+    dim3 grid((unsigned) ((p.N + BN - 1) / BN), (unsigned) ((p.M + TC_BM - 1) / TC_BM), (unsigned) p.ksplit);
     cudaError_t e = launch_k(use_pdl, stream, kern, grid, dim3(TC_THREADS), smem, p, xmap);
     if (e != cudaSuccess || p.ksplit == 1) return e;
     const int64_t total = (int64_t) p.M * p.N;
     int64_t g = (total + 255) / 256; if (g > 148 * 8) g = 148 * 8;
     return launch_k(use_pdl, stream, tc_reduce_kernel, dim3((unsigned) g), dim3(256), 0, (const float *) p.part, p.dst, p.dst_nb1, p.M, p.N, p.ksplit);
+}
+
+// 256 token columns per CTA when there is no split-K and the wide tiles still give every SM one
+template <int T>
+static cudaError_t launch_tc_t(const TcParams & p, int device, int use_pdl, cudaStream_t stream, int sm_count) {
+    const int64_t wide_tiles = (int64_t) ((p.M + TC_BM - 1) / TC_BM) * ((p.N + 255) / 256);
+    if (p.ksplit == 1 && p.N >= 256 && wide_tiles >= sm_count) return launch_tc_tb<T, 256>(p, device, use_pdl, stream);
+    return launch_tc_tb<T, TC_BN>(p, device, use_pdl, stream);
 }
 
 cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float * X, int64_t x_nb1, float * dst, int64_t dst_nb1,
@@ -638,18 +648,18 @@ cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float *
     p.ksplit = (ksteps + p.kps - 1) / p.kps;                                   // splits that actually have work
     p.part = (float *) partials;
     switch (type) {
-        case T_Q4_0: return launch_tc_t<T_Q4_0>(p, c.device, c.use_pdl, c.stream);
-        case T_Q4_1: return launch_tc_t<T_Q4_1>(p, c.device, c.use_pdl, c.stream);
-        case T_Q5_0: return launch_tc_t<T_Q5_0>(p, c.device, c.use_pdl, c.stream);
-        case T_Q5_1: return launch_tc_t<T_Q5_1>(p, c.device, c.use_pdl, c.stream);
-        case T_Q8_0: return launch_tc_t<T_Q8_0>(p, c.device, c.use_pdl, c.stream);
-        case T_Q4_K: return launch_tc_t<T_Q4_K>(p, c.device, c.use_pdl, c.stream);
-        case T_Q5_K: return launch_tc_t<T_Q5_K>(p, c.device, c.use_pdl, c.stream);
-        case T_Q6_K: return launch_tc_t<T_Q6_K>(p, c.device, c.use_pdl, c.stream);
-        case T_Q2_K: return launch_tc_t<T_Q2_K>(p, c.device, c.use_pdl, c.stream);
-        case T_Q3_K: return launch_tc_t<T_Q3_K>(p, c.device, c.use_pdl, c.stream);
-        case T_IQ4_NL: return launch_tc_t<T_IQ4_NL>(p, c.device, c.use_pdl, c.stream);
-        case T_IQ4_XS: return launch_tc_t<T_IQ4_XS>(p, c.device, c.use_pdl, c.stream);
+        case T_Q4_0: return launch_tc_t<T_Q4_0>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_Q4_1: return launch_tc_t<T_Q4_1>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_Q5_0: return launch_tc_t<T_Q5_0>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_Q5_1: return launch_tc_t<T_Q5_1>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_Q8_0: return launch_tc_t<T_Q8_0>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_Q4_K: return launch_tc_t<T_Q4_K>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_Q5_K: return launch_tc_t<T_Q5_K>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_Q6_K: return launch_tc_t<T_Q6_K>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_Q2_K: return launch_tc_t<T_Q2_K>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_Q3_K: return launch_tc_t<T_Q3_K>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_IQ4_NL: return launch_tc_t<T_IQ4_NL>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_IQ4_XS: return launch_tc_t<T_IQ4_XS>(p, c.device, c.use_pdl, c.stream, c.sm_count);
     }
     return cudaErrorInvalidValue;
 }

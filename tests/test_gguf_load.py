@@ -105,10 +105,10 @@ def test_reader_rejects_malformed_files(b200, tiny_gguf, tmp_path):
         gguf.GGUF(tmp_path / "does_not_exist.gguf")
 
 
-def _from_tensors(b200, reg, path, **kw):
+def _from_tensors(b200, reg, path, arch=TINY):
     """The same model built tensor by tensor from the file's bytes."""
     from llama_cpp_b200 import gguf, llama
-    m = llama.Llama(n_ctx=512, n_ubatch=64, reg=reg, n_threads=2, **kw, **TINY)
+    m = llama.Llama(n_ctx=512, n_ubatch=64, reg=reg, n_threads=2, **arch)
     with gguf.GGUF(path) as g:
         for t in m.tensors():
             i = g.find(t["name"])
@@ -213,14 +213,11 @@ def test_load_large_tensor_through_staging(b200, tmp_path):
     arch = dict(n_layer=1, n_embd=1024, n_head=8, n_head_kv=2, n_ff=2048, n_vocab=70016, rope_theta=10000.0, rms_eps=1e-6)
     path = tmp_path / "wide.gguf"
     gguf_synth.write_llama_gguf(path, arch, seed_base=9, device="cuda")
-    global TINY
-    saved, TINY = TINY, arch
+    a = llama.Llama.from_gguf(path, n_ctx=512, n_ubatch=64)
+    b = _from_tensors(b200, None, path, arch)
     try:
-        a = llama.Llama.from_gguf(path, n_ctx=512, n_ubatch=64)
-        b = _from_tensors(b200, None, path)
         assert abs(a.cfg.rms_eps - 1e-6) < 1e-12 and a.cfg.n_vocab == 70016
         for x, y in zip(_logits(a), _logits(b)):
             assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
-        a.close(); b.close()
     finally:
-        TINY = saved
+        a.close(); b.close()

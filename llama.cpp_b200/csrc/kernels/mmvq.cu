@@ -641,6 +641,178 @@ static cudaError_t launch_mmvq_t(const MmvqParams & p, int sm, cudaStream_t st) 
     }
 }
 
+// ---------------------------------------------------------------------------
+// warp-staged kernel for the K-block types without a kernel of their own (Q2_K, Q3_K, IQ4_XS)
+// ---------------------------------------------------------------------------
+// One warp per weight row at a time, no block-wide barriers in the loop: the warp fetches a run of up to 32
+// super-blocks of its row with coalesced 128-bit loads from the enclosing 16-byte aligned window into registers,
+// parks it in a warp-private shared-memory buffer, and every lane takes units (32 weights) from there with the same
+// WT<T>::dot as the ring kernel.  The next run (of this row or of the warp's next row) is loaded while the
+// current one is decoded; weight loads are issued before the dependency wait.  All activation columns sit in
+// shared memory for the life of the CTA.
+static constexpr int STG_WARPS = 8;
+static constexpr int STG_RUN_BLOCKS = 32;
+
+struct StagedParams {
+    const uint8_t * W;  int64_t w_nb1;
+    const uint8_t * Xq; int64_t xq_col_bytes;
+    float * dst;        int64_t dst_nb1;
+    int M, K, x_col0;
+    int n_peer; int64_t peer_delta[MAX_PEERS - 1];                 // row-split: results also go to dst + peer_delta[i]
+};
+
+template <int T, int N>
+__global__ void __launch_bounds__(STG_WARPS * 32, 2) mmvq_staged_kernel(const StagedParams p) {
+    using W = WT<T>;
+    constexpr int BB = W::BLK_BYTES;
+    constexpr int RUN_BYTES = STG_RUN_BLOCKS * BB;
+    constexpr int STAGE_BYTES = (RUN_BYTES + 15 + 15) / 16 * 16 + 16;      // misalignment in front, 16 bytes of slack behind
+    constexpr int VPL = (STAGE_BYTES / 16 + 31) / 32;                      // uint4 per lane
+    constexpr int UPB = 256 / W::UNIT;                                     // units per super-block
+    extern __shared__ __align__(128) uint8_t smem[];
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nblk = p.K >> 8;
+    const int col_bytes = ((p.K + 127) >> 7) * 160;
+    uint8_t * acts  = smem;                                                // [N][col_bytes]
+    uint8_t * stage = smem + (size_t) N * col_bytes + (size_t) warp * STAGE_BYTES;
+
+    const int nruns = (nblk + STG_RUN_BLOCKS - 1) / STG_RUN_BLOCKS;
+    const int row_stride = gridDim.x * STG_WARPS;
+    int row = blockIdx.x * STG_WARPS + warp;
+    bool storer = lane == 0; int64_t st_delta = 0;
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS - 1; ++q) if (q < p.n_peer && lane == q + 1) { storer = true; st_delta = p.peer_delta[q]; }
+
+    uint4 v[VPL];
+    auto run_src = [&](int r, int run) { return p.W + (int64_t) r * p.w_nb1 + (int64_t) run * RUN_BYTES; };
+    auto run_vecs = [&](const uint8_t * a, int run) {
+        const int bytes = min(STG_RUN_BLOCKS, nblk - run * STG_RUN_BLOCKS) * BB;
+        return (int) ((((uintptr_t) a & 15) + bytes + 15) >> 4);
+    };
+    auto load_run = [&](int r, int run) {
+        const uint8_t * a = run_src(r, run);
+        const uint4 * src = (const uint4 *) ((uintptr_t) a & ~(uintptr_t) 15);
+        const int nvec = run_vecs(a, run);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int idx = i * 32 + lane;
+            if (idx < nvec) v[i] = __ldg(src + idx);
+        }
+    };
+    auto store_run = [&](int r, int run) {
+        const int nvec = run_vecs(run_src(r, run), run);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int idx = i * 32 + lane;
+            if (idx < nvec) ((uint4 *) stage)[idx] = v[i];
+        }
+    };
+
+    if (row < p.M) load_run(row, 0);
+    pdl_wait();
+    for (int n = 0; n < N; ++n) {
+        const uint4 * src = (const uint4 *) (p.Xq + (int64_t) (p.x_col0 + n) * p.xq_col_bytes);
+        uint4 * dstp = (uint4 *) (acts + n * col_bytes);
+        for (int i = threadIdx.x; i < col_bytes / 16; i += blockDim.x) dstp[i] = src[i];
+    }
+    __syncthreads();
+    const ActView xv { acts, col_bytes };
+
+    while (row < p.M) {
+        float acc[N];
+#pragma unroll
+        for (int n = 0; n < N; ++n) acc[n] = 0.0f;
+        for (int run = 0; run < nruns; ++run) {
+            __syncwarp();
+            store_run(row, run);
+            __syncwarp();
+            if (run + 1 < nruns) load_run(row, run + 1);
+            else if (row + row_stride < p.M) load_run(row + row_stride, 0);
+            // dot() addresses units from the start of the row: hand it the address the row would have if all of it were staged
+            const uint8_t * vrow = stage + ((uintptr_t) run_src(row, run) & 15) - (size_t) run * RUN_BYTES;
+            const int u_end = min((run + 1) * STG_RUN_BLOCKS, nblk) * UPB;
+            for (int u = run * STG_RUN_BLOCKS * UPB + lane; u < u_end; u += 32) W::template dot<N>(vrow, u, xv, acc);
+        }
+#pragma unroll
+        for (int n = 0; n < N; ++n) acc[n] = warp_sum(acc[n]);
+        if (storer) {                     // lane 0: this GPU's dst; lane q + 1: the copy in peer q's arena
+#pragma unroll
+            for (int n = 0; n < N; ++n) ((float *) ((uint8_t *) p.dst + (int64_t) n * p.dst_nb1 + st_delta))[row] = acc[n];
+        }
+        row += row_stride;
+    }
+}
+
+template <int T>
+static size_t staged_smem_bytes(int N, int K) {
+    constexpr int STAGE_BYTES = (STG_RUN_BLOCKS * WT<T>::BLK_BYTES + 15 + 15) / 16 * 16 + 16;
+    return (size_t) N * ((K + 127) / 128) * 160 + (size_t) STG_WARPS * STAGE_BYTES;
+}
+
+template <int T, int N>
+static cudaError_t launch_staged_tn(const StagedParams & p, int sm_count, int device, int use_pdl, cudaStream_t stream) {
+    const size_t smem = staged_smem_bytes<T>(N, p.K);
+    auto kern = mmvq_staged_kernel<T, N>;
+    static unsigned attr_mask = 0;
+    if (smem > 48 * 1024 && !(attr_mask & (1u << device))) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_mask |= 1u << device;
+    }
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    int ctas_per_sm = (int) ((220 * 1024) / (smem + 1024));
+    if (ctas_per_sm > 3) ctas_per_sm = 3;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    int64_t grid = (int64_t) sm_count * ctas_per_sm;
+    const int64_t need = ((int64_t) p.M + STG_WARPS - 1) / STG_WARPS;
+    if (grid > need) grid = need;
+    if (grid < 1) grid = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned) grid); cfg.blockDim = dim3(STG_WARPS * 32);
+    cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+template <int T>
+static cudaError_t launch_staged_t(const StagedParams & p, int N, int sm, int dev, int pdl, cudaStream_t st) {
+    switch (N) {
+        case 1: return launch_staged_tn<T, 1>(p, sm, dev, pdl, st);
+        case 2: return launch_staged_tn<T, 2>(p, sm, dev, pdl, st);
+        case 3: return launch_staged_tn<T, 3>(p, sm, dev, pdl, st);
+        case 4: return launch_staged_tn<T, 4>(p, sm, dev, pdl, st);
+        case 5: return launch_staged_tn<T, 5>(p, sm, dev, pdl, st);
+        case 6: return launch_staged_tn<T, 6>(p, sm, dev, pdl, st);
+        case 7: return launch_staged_tn<T, 7>(p, sm, dev, pdl, st);
+        case 8: return launch_staged_tn<T, 8>(p, sm, dev, pdl, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+// plain 2-D weights (no batching, no expert indirection), whole super-blocks, activations that fit shared memory
+static bool mmvq_staged_applicable(const MmvqArgs & a) {
+    if ((a.type != T_Q2_K && a.type != T_Q3_K && a.type != T_IQ4_XS) || a.ids || a.ne12 * a.ne13 != 1) return false;
+    if ((a.K % 256) != 0 || a.N < 1 || a.N > 8) return false;
+    const size_t smem = a.type == T_Q2_K ? staged_smem_bytes<T_Q2_K>(a.N, a.K) : a.type == T_Q3_K ? staged_smem_bytes<T_Q3_K>(a.N, a.K) : staged_smem_bytes<T_IQ4_XS>(a.N, a.K);
+    return smem <= 200 * 1024;
+}
+
+static cudaError_t launch_mmvq_staged(const MmvqArgs & a, cudaStream_t stream) {
+    StagedParams p = {};
+    p.W = (const uint8_t *) a.W; p.w_nb1 = a.w_nb1;
+    p.Xq = (const uint8_t *) a.Xq; p.xq_col_bytes = (int64_t) ((a.K + 127) / 128) * 160;
+    p.dst = a.dst; p.dst_nb1 = a.dst_nb1;
+    p.M = a.M; p.K = a.K; p.x_col0 = a.x_col0;
+    p.n_peer = a.n_peer; for (int i = 0; i < a.n_peer; ++i) p.peer_delta[i] = a.peer_delta[i];
+    if (a.type == T_Q2_K) return launch_staged_t<T_Q2_K>(p, a.N, a.sm_count, a.device, a.use_pdl, stream);
+    if (a.type == T_Q3_K) return launch_staged_t<T_Q3_K>(p, a.N, a.sm_count, a.device, a.use_pdl, stream);
+    return launch_staged_t<T_IQ4_XS>(p, a.N, a.sm_count, a.device, a.use_pdl, stream);
+}
+
 bool mmvq_type_supported(int type) {
     switch (type) {
         case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: case T_IQ4_NL: case T_IQ4_XS:
@@ -663,12 +835,13 @@ cudaError_t launch_quantize_act128(const float * x, int64_t ne11, int64_t ne12, 
 }
 
 // do the kernels launch_mmvq picks for these arguments honour n_peer / peer_delta?
-bool mmvq_stores_to_peers(const MmvqArgs & a) { return mmvq_k_applicable(a) || mmvq_q6k_applicable(a) || mmvq_q32_applicable(a); }
+bool mmvq_stores_to_peers(const MmvqArgs & a) { return mmvq_k_applicable(a) || mmvq_q6k_applicable(a) || mmvq_q32_applicable(a) || mmvq_staged_applicable(a); }
 
 cudaError_t launch_mmvq(const MmvqArgs & a, cudaStream_t stream) {
     if (mmvq_k_applicable(a)) return launch_mmvq_k(a, stream);
     if (mmvq_q6k_applicable(a)) return launch_mmvq_q6k(a, stream);
     if (mmvq_q32_applicable(a)) return launch_mmvq_q32(a, stream);
+    if (mmvq_staged_applicable(a)) return launch_mmvq_staged(a, stream);
     MmvqParams p = {};
     p.W = (const uint8_t *) a.W; p.w_nb1 = a.w_nb1; p.w_nb2 = a.w_nb2; p.w_nb3 = a.w_nb3;
     p.Xq = (const uint8_t *) a.Xq; p.xq_col_bytes = (int64_t) ((a.K + 127) / 128) * 160;

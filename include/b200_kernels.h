@@ -81,15 +81,50 @@ int    b200_mul_mat_q_host(int type, const void * W, int64_t M, int64_t K, const
  *    message from b200_noalloc_last_error().
  *  - The first call on each device looks up the array's device address (with that device
  *    current) and clears a status word; make that first call before any stream capture begins.
+ *    With CUDA's lazy module loading the driver also materialises the array and each kernel
+ *    variant (weight type, N) the first time it is used, so "allocates nothing" holds from the
+ *    second call of a given (device, type, N) on: warm each combination up once at start-up.
+ *    The first call is serialised per device, so several host threads may race to make it.
  *  - All calls on a device share the one array, which keeps whatever the last call wrote.  The
  *    kernels overwrite the part they use before reading it, so no clearing is needed between
  *    calls; but two calls that overlap on the GPU (different streams, no ordering) race on it.
- *  - Asynchronous on `stream`; same arithmetic and results as b200_mul_mat_q for N <= 8.        */
+ *  - Asynchronous on `stream`; same arithmetic and results as b200_mul_mat_q for N <= 8.
+ *  - Arguments the kernels could fault on (null or misaligned pointers, strides shorter than
+ *    a row) are rejected with B200_E_BAD_ARG before anything is launched.
+ *  - A kernel that gives up a bounded wait leaves garbage in dst and records it in a status
+ *    word; the launching call has long returned 0 by then.  b200_noalloc_status(stream)
+ *    synchronises the stream, returns B200_E_DEVICE_WAIT if that happened since the last
+ *    check (0 otherwise) and clears the word.  It allocates nothing either.                  */
 #define B200_NOALLOC_SCRATCH_BYTES (1u << 20)
 int          b200_mul_mat_q_noalloc(int type, const void * W, int64_t w_row_stride_bytes, int64_t M, int64_t K,
                                     const float * X, int64_t x_col_stride_elems, int64_t N,
                                     float * dst, int64_t dst_col_stride_elems, void * stream);
+int          b200_noalloc_status(void * stream);
 const char * b200_noalloc_last_error(void);
+
+/* ---- single phases of the persistent decode-step kernel -------------------
+ * The ggml backend runs a whole run of Llama layers for one token as ONE cooperative launch
+ * (csrc/kernels/decode_step.cu) instead of one launch per graph node (the reference's walk,
+ * ggml/src/ggml-cuda/ggml-cuda.cu:2691-2765).  These host-buffer entry points run one phase of that
+ * kernel at a time so that each can be checked against the oracle of the op sequence it replaces:
+ *  - mul_mat:   dst[M] = W . y with y = x (+ x_add), or rms_norm(x (+ x_add), eps) * norm_w when norm_w is set
+ *               (ADD, RMS_NORM, MUL, MUL_MAT of src/llama.cpp:1476-1640); sum_out (optional) receives x + x_add
+ *  - gate_up:   dst[M] = silu(Wg . x) * (Wu . x)            (MUL_MAT x2, UNARY(SILU), MUL)
+ *  - qkv:       q_out = rope(Wq . y), k_row = f16(rope(Wk . y)), v_row = f16(Wv . y) for one token at
+ *               position pos; head size 128, adjacent-pair rotation (MUL_MAT x3, ROPE x2, CPY x2)
+ *  - attention: FLASH_ATTN_EXT for one query token over contiguous F16 K/V [n_head_kv][n_kv][128], split into
+ *               n_slices KV slices that the kernel merges in slice order
+ * Weight types: Q4_K, Q5_K, Q6_K (K a multiple of 256; of 2048 for Q6_K).                                   */
+int          b200_decode_step_mul_mat_host(int type, const void * W, int64_t M, int64_t K, const float * x, const float * x_add,
+                                           const float * norm_w, float eps, float * dst, float * sum_out);
+int          b200_decode_step_gate_up_host(int type, const void * Wg, const void * Wu, int64_t M, int64_t K, const float * x, float * dst);
+int          b200_decode_step_qkv_host(int type_qk, int type_v, const void * Wq, const void * Wk, const void * Wv, int64_t n_head,
+                                       int64_t n_head_kv, int64_t K, const float * x, const float * norm_w, float eps, int32_t pos,
+                                       int n_dims, float freq_base, const float * freq_factors, float * q_out, void * k_row_f16,
+                                       void * v_row_f16);
+int          b200_decode_step_attention_host(const float * q, const void * k_f16, const void * v_f16, const void * mask_f16,
+                                             int64_t n_kv, int64_t n_head, int64_t n_head_kv, float scale, int n_slices, float * dst);
+const char * b200_decode_step_last_error(void);
 
 /* ---- FLASH_ATTN_EXT -------------------------------------------------------
  * GGML_OP_FLASH_ATTN_EXT (ggml_flash_attn_ext, ggml/src/ggml.c:4306-4345; CPU

@@ -29,7 +29,9 @@ EXPORTS = [
     "b200_device_count", "b200_last_error", "b200_row_size",
     "b200_mul_mat_q_scratch_bytes", "b200_mul_mat_q", "b200_mul_mat_q_host",
     "b200_act_bytes", "b200_quantize_act", "b200_mul_mat_vec_q", "b200_set_dependent_launch",
-    "b200_mul_mat_q_noalloc", "b200_noalloc_last_error",
+    "b200_mul_mat_q_noalloc", "b200_noalloc_last_error", "b200_noalloc_status",
+    "b200_decode_step_mul_mat_host", "b200_decode_step_gate_up_host", "b200_decode_step_qkv_host",
+    "b200_decode_step_attention_host", "b200_decode_step_last_error",
     "b200_flash_attn_scratch_bytes", "b200_flash_attn", "b200_flash_attn_host",
     "b200_dequantize_rows_host", "b200_get_rows_host", "b200_quantize_rows_host", "b200_f32_to_f16_host",
     "b200_rms_norm_host", "b200_rope_host", "b200_silu_mul_host", "b200_soft_max_host",
@@ -83,6 +85,12 @@ def lib() -> C.CDLL:
         l.b200_mul_mat_vec_q.argtypes = [C.c_int, vp, i64, i64, i64, vp, i64, vp, i64, vp]
         l.b200_mul_mat_q_noalloc.argtypes = [C.c_int, vp, i64, i64, i64, vp, i64, i64, vp, i64, vp]
         l.b200_noalloc_last_error.restype = C.c_char_p
+        l.b200_noalloc_status.argtypes = [vp]
+        l.b200_decode_step_last_error.restype = C.c_char_p
+        l.b200_decode_step_mul_mat_host.argtypes = [C.c_int, vp, i64, i64, vp, vp, vp, f32, vp, vp]
+        l.b200_decode_step_gate_up_host.argtypes = [C.c_int, vp, vp, i64, i64, vp, vp]
+        l.b200_decode_step_qkv_host.argtypes = [C.c_int, C.c_int, vp, vp, vp, i64, i64, i64, vp, vp, f32, C.c_int32, C.c_int, f32, vp, vp, vp, vp]
+        l.b200_decode_step_attention_host.argtypes = [vp, vp, vp, vp, i64, i64, i64, f32, C.c_int, vp]
         l.b200_flash_attn_scratch_bytes.restype = sz
         l.b200_flash_attn_scratch_bytes.argtypes = [i64, i64, i64, i64]
         l.b200_flash_attn.argtypes = [vp, i64, i64, vp, i64, i64, vp, i64, i64, vp, i64, vp,
@@ -142,6 +150,60 @@ def flash_attn(q: np.ndarray, k: np.ndarray, v: np.ndarray, mask: np.ndarray | N
         assert mask.shape == (nq, nkv)
     out = np.empty((nq, nh, d), dtype=np.float32)
     _check(lib().b200_flash_attn_host(_p(q), _p(k), _p(v), _p(mask), _p(out), d, nq, nh, nkv, nhkv, scale, max_bias, softcap))
+    return out
+
+
+def _check_ds(rc: int) -> None:
+    if rc != 0:
+        raise B200Error(f"decode-step phase failed (code {rc}): {lib().b200_decode_step_last_error().decode()}")
+
+
+def decode_step_mul_mat(qtype: str, w: np.ndarray, x: np.ndarray, x_add: np.ndarray | None = None,
+                        norm_w: np.ndarray | None = None, eps: float = 1e-5):
+    """One mat-vec phase of the persistent decode-step kernel: w uint8 [M, row_size(K)], x f32 [K].
+    Returns (dst [M], x + x_add or None)."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    k, m = x.size, w.shape[0]
+    assert w.shape[1] == row_size(qtype, k)
+    xa = None if x_add is None else np.ascontiguousarray(x_add, dtype=np.float32).reshape(-1)
+    nw = None if norm_w is None else np.ascontiguousarray(norm_w, dtype=np.float32).reshape(-1)
+    out = np.empty(m, dtype=np.float32)
+    s = None if xa is None else np.empty(k, dtype=np.float32)
+    _check_ds(lib().b200_decode_step_mul_mat_host(TYPES[qtype], _p(w), m, k, _p(x), _p(xa), _p(nw), eps, _p(out), _p(s)))
+    return out, s
+
+
+def decode_step_gate_up(qtype: str, wg: np.ndarray, wu: np.ndarray, x: np.ndarray) -> np.ndarray:
+    wg = np.ascontiguousarray(wg, dtype=np.uint8); wu = np.ascontiguousarray(wu, dtype=np.uint8)
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    out = np.empty(wg.shape[0], dtype=np.float32)
+    _check_ds(lib().b200_decode_step_gate_up_host(TYPES[qtype], _p(wg), _p(wu), wg.shape[0], x.size, _p(x), _p(out)))
+    return out
+
+
+def decode_step_qkv(qt_qk: str, qt_v: str, wq, wk, wv, n_head: int, n_head_kv: int, x, norm_w, eps: float, pos: int,
+                    n_dims: int, freq_base: float, freq_factors=None):
+    """Returns (q f32 [n_head, 128], k f16 [n_head_kv, 128], v f16 [n_head_kv, 128])."""
+    wq, wk, wv = (np.ascontiguousarray(a, dtype=np.uint8) for a in (wq, wk, wv))
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    nw = np.ascontiguousarray(norm_w, dtype=np.float32).reshape(-1)
+    ff = None if freq_factors is None else np.ascontiguousarray(freq_factors, dtype=np.float32)
+    q = np.empty((n_head, 128), dtype=np.float32)
+    k = np.empty((n_head_kv, 128), dtype=np.float16); v = np.empty((n_head_kv, 128), dtype=np.float16)
+    _check_ds(lib().b200_decode_step_qkv_host(TYPES[qt_qk], TYPES[qt_v], _p(wq), _p(wk), _p(wv), n_head, n_head_kv, x.size, _p(x), _p(nw), eps,
+                                             pos, n_dims, freq_base, _p(ff), _p(q), _p(k), _p(v)))
+    return q, k, v
+
+
+def decode_step_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, mask: np.ndarray | None, scale: float, n_slices: int) -> np.ndarray:
+    """q f32 [n_head, 128]; k, v f16 [n_head_kv, n_kv, 128]; mask f16 [n_kv] or None; returns f32 [n_head, 128]."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    k = np.ascontiguousarray(k, dtype=np.float16); v = np.ascontiguousarray(v, dtype=np.float16)
+    m = None if mask is None else np.ascontiguousarray(mask, dtype=np.float16).reshape(-1)
+    nh, nhkv, nkv = q.shape[0], k.shape[0], k.shape[1]
+    out = np.empty((nh, 128), dtype=np.float32)
+    _check_ds(lib().b200_decode_step_attention_host(_p(q), _p(k), _p(v), _p(m), nkv, nh, nhkv, scale, n_slices, _p(out)))
     return out
 
 

@@ -220,15 +220,18 @@ static void backend_free(ggml_backend_t backend) {
     set_device(ctx->dev->device);
     cudaStreamSynchronize(ctx->stream);
     if (getenv("GGML_B200_VERBOSE"))
-        fprintf(stderr, "ggml-b200: %s: graph_compute calls: %llu replayed from a CUDA graph, %llu captured, %llu run directly; %llu kernel launches\n",
+        fprintf(stderr, "ggml-b200: %s: graph_compute calls: %llu replayed from a CUDA graph, %llu captured, %llu run directly; %llu kernel launches, %llu of them persistent decode steps\n",
                 ctx->name.c_str(), (unsigned long long) ctx->n_replay, (unsigned long long) ctx->n_capture, (unsigned long long) ctx->n_direct,
-                (unsigned long long) ctx->n_launches);
+                (unsigned long long) ctx->n_launches, (unsigned long long) ctx->n_mega);
+    decode_step_print_timing(ctx);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->tc_xh) cudaFree(ctx->tc_xh);
     for (auto & e : ctx->act_cache) if (e.q) cudaFree(e.q);
     if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
     if (ctx->dyn_dev) cudaFree(ctx->dyn_dev);
     if (ctx->fa_tickets) cudaFree(ctx->fa_tickets);
+    if (ctx->mega_arena) cudaFree(ctx->mega_arena);
+    if (ctx->mega_copy_stream) cudaStreamDestroy(ctx->mega_copy_stream);
     free(ctx->dyn_host);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
@@ -350,6 +353,10 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t dev, const char * /*pa
     ctx->use_graphs = getenv("GGML_B200_GRAPHS") ? atoi(getenv("GGML_B200_GRAPHS")) : 1;
     ctx->use_fusion = getenv("GGML_B200_FUSE") ? atoi(getenv("GGML_B200_FUSE")) : 1;
     ctx->use_tc = getenv("GGML_B200_TC") ? atoi(getenv("GGML_B200_TC")) : 1;
+    ctx->use_mega = getenv("GGML_B200_MEGA") ? atoi(getenv("GGML_B200_MEGA")) : 1;
+    if (getenv("GGML_B200_MEGA_MAX_BLOCKS")) ctx->mega_max_blocks = atoi(getenv("GGML_B200_MEGA_MAX_BLOCKS"));
+    if (ctx->mega_max_blocks < 1) ctx->mega_max_blocks = 1;
+    ctx->mega_timing = getenv("GGML_B200_MEGA_TIMING") ? atoi(getenv("GGML_B200_MEGA_TIMING")) : 0;
     const char * pdl = getenv("GGML_B200_PDL");
     ctx->use_pdl = pdl ? atoi(pdl) : 1;
     ctx->trace = getenv("GGML_B200_TRACE") ? atoi(getenv("GGML_B200_TRACE")) : 0;

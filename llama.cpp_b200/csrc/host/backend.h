@@ -75,6 +75,16 @@ struct BackendCtx {
 
     unsigned *   fa_tickets = nullptr;     // zero-initialised counters of the decode attention kernel
 
+    // persistent decode step (decode_plan.cpp): scratch, phase lists and barrier words of the single-launch path
+    int          use_mega = 1;             // GGML_B200_MEGA=0 keeps one launch per node (group)
+    int          mega_max_blocks = 1 << 30;   // GGML_B200_MEGA_MAX_BLOCKS: cut the persistent launch after this many blocks (debugging aid)
+    int          mega_ops_used = 0;        // per graph_compute call: phases already placed in the arena's parameter region
+    int          mega_timing = 0, mega_last_ops = 0;
+    bool         mega_tried = false;       // per graph_compute call: a failed match is not retried at every node
+    void *       mega_arena = nullptr;
+    cudaStream_t mega_copy_stream = nullptr;
+    uint64_t     n_mega = 0;               // persistent launches so far
+
     // row-split over several processes: where the peers' arenas are mapped, and whether slices have been
     // stored to the peers since the last barrier
     ggml_b200_peers peers = {};
@@ -97,6 +107,10 @@ bool buffer_is_ours(ggml_backend_buffer_t buf);
 bool buft_is_ours(ggml_backend_buffer_type_t buft);
 bool buft_is_split(ggml_backend_buffer_type_t buft);
 ggml_backend_buffer_type_t split_buffer_type(int main_device, const float * tensor_split);
+
+// decode_plan.cpp
+int              try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i);
+void             decode_step_print_timing(BackendCtx * ctx);
 
 // dispatch.cpp
 bool             device_supports_op(DeviceCtx * dev, const ggml_tensor * op);

@@ -640,9 +640,17 @@ static bool run_all(BackendCtx * ctx, ggml_cgraph * cgraph) {
     std::vector<const void *> & pending_full = ctx->pending_full;
     pending_full.clear();
     ctx->node_done.assign((size_t) cgraph->n_nodes, 0);
+    ctx->mega_tried = false; ctx->mega_ops_used = 0;
     for (int i = 0; i < cgraph->n_nodes;) {
         ggml_tensor * node = cgraph->nodes[i];
         if (is_noop(node) || ctx->node_done[(size_t) i]) { ++i; continue; }
+        // single-token Llama layers: one persistent launch for the whole run of layers (decode_plan.cpp)
+        if (ctx->use_mega && ctx->use_fusion && !ctx->mega_tried && ctx->peers.n_ranks < 2 && !ctx->peer_pending &&
+            (node->op == GGML_OP_ADD || node->op == GGML_OP_RMS_NORM) && node->ne[1] == 1 && node->ne[2] == 1 && node->ne[3] == 1) {
+            const int next = try_decode_step(ctx, cgraph, i);
+            if (next > i) { i = next; continue; }
+            ctx->mega_tried = true;
+        }
         const ggml_b200_row_slice * rs = ctx->row_slice_of(node);
         if (ctx->peer_pending) {
             // slices stored to the peers become readable after a barrier; consecutive sliced MUL_MATs that

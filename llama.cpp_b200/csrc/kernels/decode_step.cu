@@ -1,0 +1,903 @@
+// Persistent decode step: a run of Llama layers for ONE token in a single cooperative launch.
+//
+// The node-per-launch walk of a decode graph (the reference's ggml_backend_cuda_graph_compute,
+// ggml/src/ggml-cuda/ggml-cuda.cu:2691-2765, and this backend's own per-node path) spends most of a
+// token in launch ramps and tails: each of the ~300 kernels streams a few MB and the next one cannot
+// start fetching until it is scheduled.  Here one CTA per SM stays resident for the whole token and
+// walks a list of phases prepared by the host (csrc/host/decode_plan.cpp):
+//
+//   mat-vec phase   every CTA first builds the int8 activation blocks of the shared input in its own
+//                   shared memory -- directly from x, or from rms_norm(x [+ residual]) * w -- then each
+//                   warp computes whole weight rows.  Results are stored, or consumed in registers:
+//                   adjacent row pairs of wq/wk are rotated (ROPE) and K/V rows go straight into the
+//                   F16 cache; row r of gate and row r of up are computed by the same warp, which
+//                   stores silu(gate) * up.
+//   attention phase (KV head, KV slice) work items as in fattn_dec.cu: all query heads of a KV head
+//                   share the K/V reads; the last CTA of a head merges the slices in a fixed order.
+//
+// Phases are separated by grid-wide barriers (bounded spins; a give-up sets the status word and the
+// kernel drains and returns).  Weight streaming does not stop at a barrier: every warp owns a ring of
+// DS_NSLOT shared-memory slots filled by cp.async.bulk (plain, non-multicast, local memory) and keeps
+// requesting the units of its FUTURE rows -- across phase boundaries, because the schedule of a warp
+// is a pure function of the phase list -- while it waits for activations.  HBM therefore sees one
+// nearly continuous stream of weight reads per token instead of ~150 separate ramps.
+//
+// Arithmetic of the dot products: vec_dot_q4_K_q8_1 / q5_K / q6_K (ggml/src/ggml-cuda/vecdotq.cuh:357-496,
+// 671-787) restated for these layouts, identical to mmvq_k.cu / mmvq_q6k.cu; activation blocks as
+// quantize_act128_kernel (mmvq.cu); rms_norm, rope and silu as in glue.cu; attention as fattn_dec.cu.
+#include "common.cuh"
+#include "kernels.h"
+#include <math.h>
+#include <string.h>
+#include <vector>
+
+namespace b200 {
+
+static constexpr int DS_WARPS = 12, DS_THREADS = DS_WARPS * 32;
+static constexpr int DS_NSLOT = 3, DS_SLOT = 4608;               // per-warp ring: 3 slots of 32 Q4_K super-blocks
+static constexpr int DS_ACT_STRIDE = 336;                         // shared-memory bytes per 256 activation values: 256 int8, 8 x {d, s}, 16 pad
+static constexpr int DS_ACT_BYTES = 38912;                        // activation blocks of one column (K <= 29440) / attention scratch
+static constexpr int DS_MAX_K = (DS_ACT_BYTES / DS_ACT_STRIDE) * 256;
+static constexpr int DS_IN_V4 = 4;                                // 4-value groups per thread and pass of the input stage
+static constexpr int DS_SPIN_LIMIT = 1 << 22;
+
+// what a warp needs to walk the rows of one mat-vec phase, kept in shared memory for all phases of the launch
+struct alignas(8) DsMvDesc {
+    uint64_t W[3];
+    uint32_t nb1[3];            // row stride in bytes
+    uint32_t m_end[3];          // cumulative row counts of the concatenated row space (unused: 0xffffffff)
+    uint32_t ngroups;           // work items of the phase; a group is one row, or two (mode bit 1)
+    uint8_t  type[3], nseg[3], seg_blk[3], last_blk[3];   // per matrix: segments per row, blocks per segment / in the last one
+    uint8_t  mode;              // bit 0: member j of a group is row g of matrix j (gate/up); else rows R*g+j of the row space;
+                                // bit 1: two rows per group; bit 2: both rows of a group travel in one ring slot
+    uint8_t  pad[3];
+};
+static_assert(sizeof(DsMvDesc) == 72, "descriptor size");
+
+// shared-memory layout
+static constexpr int DS_OFF_RING = DS_ACT_BYTES;
+static constexpr int DS_OFF_BAR  = DS_OFF_RING + DS_WARPS * DS_NSLOT * DS_SLOT;
+static constexpr int DS_OFF_OP   = DS_OFF_BAR + DS_WARPS * DS_NSLOT * 8;
+static constexpr int DS_OP_BYTES = (int) sizeof(DsOp);
+static_assert(sizeof(DsOp) % 16 == 0, "phase parameters are copied in 16-byte pieces");
+static constexpr int DS_OFF_MISC = DS_OFF_OP + 2 * DS_OP_BYTES;     // two copies: the next phase's parameters are fetched during the current one
+struct DsMisc {
+    float red[32];
+    float2 rope_cs[64];
+    __half * kc; __half * vc;
+    volatile int dead;
+    unsigned ticket;
+};
+static constexpr int DS_OFF_DESC = DS_OFF_MISC + (int) ((sizeof(DsMisc) + 15) / 16 * 16);
+static constexpr int DS_SMEM_LIMIT = 232448;                      // 227 KB opt-in maximum per CTA
+
+struct DsParams {
+    const DsOp * ops; int n_ops;
+    const DsMvDesc * descs; int n_mv;
+    unsigned * sync;            // [0] barrier arrivals, [1] exit arrivals, [2] give-up flag
+    int * status;
+    unsigned long long * timing;   // optional: per phase {start, input stage done, rows done, barrier passed} of CTA 0, in ns
+};
+
+__device__ __forceinline__ unsigned long long ds_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned ds_ld_acquire(const unsigned * p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void ds_red_release(unsigned * p, unsigned v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void ds_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void ds_give_up(const DsParams & p, DsMisc * misc, int code) {
+    misc->dead = 1;
+    atomicExch(&p.sync[2], 1u);
+    atomicCAS(p.status, ERR_NONE, code);
+}
+
+// Grid-wide barrier: arrival number `target` of the monotonically increasing counter releases the phase.
+__device__ __forceinline__ void ds_grid_barrier(const DsParams & p, DsMisc * misc, unsigned target) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        ds_red_release(&p.sync[0], 1u);
+        if (!misc->dead) {
+            int spins = 0;
+            while (ds_ld_acquire(&p.sync[0]) < target) {
+                if (++spins >= DS_SPIN_LIMIT) { ds_give_up(p, misc, ERR_MBAR_TIMEOUT); break; }
+                if ((spins & 255) == 0 && ds_ld_acquire(&p.sync[2])) { misc->dead = 1; break; }
+            }
+        }
+        __threadfence();
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ int ds_blk_bytes(int type) { return type == T_Q4_K ? 144 : (type == T_Q5_K ? 176 : 210); }
+
+// ---------------------------------------------------------------------------
+// dot products of one ring slot (a run of super-blocks of one weight row) with the activation blocks
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int ds_dp4a_us(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Q4_K / Q5_K: one lane per super-block (256 weights).  The 12 scale bytes are decoded once per block, every
+// load is 128 bits wide, and with a lane stride of 144 / 176 bytes (weights) and DS_ACT_STRIDE (activations) the
+// eight lanes of a quarter warp hit eight different bank groups.  `ab` is the activation block of the same 256 values.
+template <int T>
+__device__ __forceinline__ float ds_dot_blk(const uint8_t * blk, const uint8_t * ab) {
+    constexpr int QS_OFF = (T == T_Q4_K) ? 16 : 48;
+    const uint4 hd = *(const uint4 *) blk;
+    const float2 dm = __half22float2(*(const __half2 *) &hd.x);                 // {d, dmin}
+    // 6-bit scales and mins of the 8 sub-blocks as bytes (get_scale_min_k4, ggml/src/ggml-quants.c:631-638)
+    const uint32_t sc_lo = hd.y & 0x3f3f3f3fu, mn_lo = hd.z & 0x3f3f3f3fu;
+    const uint32_t sc_hi = (hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u);
+    const uint32_t mn_hi = ((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u);
+    uint32_t hb[8];
+    if (T == T_Q5_K) {
+        const uint4 h0 = *(const uint4 *) (blk + 16), h1 = *(const uint4 *) (blk + 32);
+        hb[0] = h0.x; hb[1] = h0.y; hb[2] = h0.z; hb[3] = h0.w; hb[4] = h1.x; hb[5] = h1.y; hb[6] = h1.z; hb[7] = h1.w;
+    }
+    float accE = 0.0f, accO = 0.0f, accM = 0.0f;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {                      // 64 weights: low nibbles = sub-block 2r, high nibbles = 2r+1
+        const uint4 q0 = *(const uint4 *) (blk + QS_OFF + 32 * r), q1 = *(const uint4 *) (blk + QS_OFF + 32 * r + 16);
+        const uint4 xa = *(const uint4 *) (ab + 64 * r), xb = *(const uint4 *) (ab + 64 * r + 16);
+        const uint4 xc = *(const uint4 *) (ab + 64 * r + 32), xd = *(const uint4 *) (ab + 64 * r + 48);
+        const float4 ds = *(const float4 *) (ab + 256 + 16 * r);              // {d, s} of sub-blocks 2r, 2r+1
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { lo[i] = w[i] & 0x0F0F0F0Fu; hi[i] = (T == T_Q5_K) ? (w[i] >> 4) & 0x0F0F0F0Fu : w[i] & 0xF0F0F0F0u; }
+        if (T == T_Q5_K) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t t = hb[i] >> (2 * r);
+                lo[i] |= (t << 4) & 0x10101010u;
+                hi[i] |= (t << 3) & 0x10101010u;
+            }
+        }
+        int t0 = ds_dp4a_us(lo[0], (int) xa.x, 0); t0 = ds_dp4a_us(lo[1], (int) xa.y, t0);
+        t0 = ds_dp4a_us(lo[2], (int) xa.z, t0);    t0 = ds_dp4a_us(lo[3], (int) xa.w, t0);
+        t0 = ds_dp4a_us(lo[4], (int) xb.x, t0);    t0 = ds_dp4a_us(lo[5], (int) xb.y, t0);
+        t0 = ds_dp4a_us(lo[6], (int) xb.z, t0);    t0 = ds_dp4a_us(lo[7], (int) xb.w, t0);
+        int t1 = ds_dp4a_us(hi[0], (int) xc.x, 0); t1 = ds_dp4a_us(hi[1], (int) xc.y, t1);
+        t1 = ds_dp4a_us(hi[2], (int) xc.z, t1);    t1 = ds_dp4a_us(hi[3], (int) xc.w, t1);
+        t1 = ds_dp4a_us(hi[4], (int) xd.x, t1);    t1 = ds_dp4a_us(hi[5], (int) xd.y, t1);
+        t1 = ds_dp4a_us(hi[6], (int) xd.z, t1);    t1 = ds_dp4a_us(hi[7], (int) xd.w, t1);
+        const uint32_t scw = (r < 2 ? sc_lo : sc_hi) >> (16 * (r & 1)), mnw = (r < 2 ? mn_lo : mn_hi) >> (16 * (r & 1));
+        // |sc * t| <= 63 * 32 * 240 * 127 < 2^26: exact in int32 (Q4_K keeps the high nibbles in place, value * 16)
+        accE += ds.x * (float) ((int) (scw & 0xff) * t0);
+        accO += ds.z * (float) ((int) ((scw >> 8) & 0xff) * t1);
+        accM += ds.y * (float) (mnw & 0xff) + ds.w * (float) ((mnw >> 8) & 0xff);
+    }
+    return dm.x * (accE + (T == T_Q5_K ? 1.0f : 0.0625f) * accO) - dm.y * accM;
+}
+
+// NW consecutive 32-bit words at a 2-byte aligned shared-memory address
+template <int NW>
+__device__ __forceinline__ void ds_lds_run(const uint8_t * p, uint32_t (&out)[NW]) {
+    const uint32_t * base = (const uint32_t *) ((uintptr_t) p & ~(uintptr_t) 3);
+    const uint32_t sh = ((uint32_t) (uintptr_t) p & 3u) * 8u;
+    uint32_t prev = base[0];
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+        const uint32_t next = base[i + 1];
+        out[i] = __funnelshift_r(prev, next, sh);
+        prev = next;
+    }
+}
+
+// Q6_K: lane l owns half (l & 1) of super-block l >> 1 (a slot holds at most 16 super-blocks)
+__device__ __forceinline__ float ds_dot_q6k(const uint8_t * slot, int nblk, const uint8_t * acts, int lane) {
+    const int b = lane >> 1, n128 = lane & 1;
+    float acc = 0.0f;
+    if (b < nblk) {
+        const uint8_t * blk = slot + b * 210;
+        uint32_t ql[16], qh[8], scw[2];
+        ds_lds_run<16>(blk + n128 * 64, ql);
+        ds_lds_run<8>(blk + 128 + n128 * 32, qh);
+        ds_lds_run<2>(blk + 192 + n128 * 8, scw);
+        const float d = h2f(*(const uint16_t *) (blk + 208));
+        const uint8_t * ab = acts + b * DS_ACT_STRIDE + n128 * 128;       // 128 int8 of this half; its {d, s} pairs follow the block's 256 int8
+        const uint8_t * dsb = acts + b * DS_ACT_STRIDE + 256 + n128 * 32;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            int q[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t L = (t & 1) ? ql[8 + i] : ql[i];
+                const uint32_t nib = (t & 2) ? (L >> 4) & 0x0F0F0F0Fu : L & 0x0F0F0F0Fu;
+                const uint32_t hb = t == 0 ? (qh[i] << 4) : t == 1 ? (qh[i] << 2) : t == 2 ? qh[i] : (qh[i] >> 2);
+                q[i] = (int) __vsubss4(nib | (hb & 0x30303030u), 0x20202020u);
+            }
+            const int sc_lo = (int) (int8_t) ((scw[(2 * t) >> 2] >> (8 * ((2 * t) & 3))) & 0xff);
+            const int sc_hi = (int) (int8_t) ((scw[(2 * t + 1) >> 2] >> (8 * ((2 * t + 1) & 3))) & 0xff);
+            const uint4 x0 = *(const uint4 *) (ab + t * 32);
+            const uint4 x1 = *(const uint4 *) (ab + t * 32 + 16);
+            const float dx = *(const float *) (dsb + t * 8);
+            int s0 = __dp4a(q[0], (int) x0.x, 0); s0 = __dp4a(q[1], (int) x0.y, s0);
+            s0 = __dp4a(q[2], (int) x0.z, s0);    s0 = __dp4a(q[3], (int) x0.w, s0);
+            int s1 = __dp4a(q[4], (int) x1.x, 0); s1 = __dp4a(q[5], (int) x1.y, s1);
+            s1 = __dp4a(q[6], (int) x1.z, s1);    s1 = __dp4a(q[7], (int) x1.w, s1);
+            acc += d * dx * (float) (sc_lo * s0 + sc_hi * s1);
+        }
+    }
+    return acc;
+}
+
+// ---------------------------------------------------------------------------
+// input stage of a mat-vec phase: x (+ residual) [-> rms_norm * w] -> int8 activation blocks in shared memory
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float ds_block_sum(float v, float * red) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float r = lane < DS_WARPS ? red[lane] : 0.0f;
+    return warp_sum(r);
+}
+
+// x = in0 (+ in1) -> [rms_norm(x) * w] -> blk_act128 in shared memory.  A thread handles four consecutive values
+// at a time (one 128-bit load per operand), eight neighbouring threads form a 32-value quantization group; DS_IN_V4
+// such quads per thread and pass.  With rms_norm the vector is read twice (sum of squares, then normalise and
+// quantize): it sits in L2, and short code matters more here than the second read.
+__device__ __forceinline__ float4 ds_ld4(const float * p) { return __ldcg((const float4 *) p); }
+
+__device__ __forceinline__ void ds_input_stage(const DsOp & o, uint8_t * acts, float * red) {
+    const int tid = threadIdx.x;
+    const int K = o.K;
+    const bool writer = blockIdx.x == 0, norm = o.in_kind == DS_IN_NORM;
+    const float * __restrict__ in0 = o.in0;
+    const float * __restrict__ in1 = o.in1;
+    float scale = 1.0f;
+    if (norm) {
+        float ss = 0.0f;
+#pragma unroll 1
+        for (int base = 0; base < K; base += DS_IN_V4 * DS_THREADS * 4) {
+            float4 xv[DS_IN_V4];
+#pragma unroll
+            for (int k = 0; k < DS_IN_V4; ++k) {
+                const int i = base + (k * DS_THREADS + tid) * 4;
+                xv[k] = i < K ? ds_ld4(in0 + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+            if (in1) {
+#pragma unroll
+                for (int k = 0; k < DS_IN_V4; ++k) {
+                    const int i = base + (k * DS_THREADS + tid) * 4;
+                    if (i < K) { const float4 r = ds_ld4(in1 + i); xv[k].x += r.x; xv[k].y += r.y; xv[k].z += r.z; xv[k].w += r.w; }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < DS_IN_V4; ++k) ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
+        }
+        ss = ds_block_sum(ss, red);
+        scale = rsqrtf(ss / (float) K + o.eps);
+    }
+#pragma unroll 1
+    for (int base = 0; base < K; base += DS_IN_V4 * DS_THREADS * 4) {
+        float4 xv[DS_IN_V4], wv[DS_IN_V4];
+#pragma unroll
+        for (int k = 0; k < DS_IN_V4; ++k) {
+            const int i = base + (k * DS_THREADS + tid) * 4;
+            xv[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f); wv[k] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+            if (i < K) { xv[k] = ds_ld4(in0 + i); if (norm) wv[k] = __ldg((const float4 *) (o.norm_w + i)); }
+        }
+        if (in1) {
+#pragma unroll
+            for (int k = 0; k < DS_IN_V4; ++k) {
+                const int i = base + (k * DS_THREADS + tid) * 4;
+                if (i < K) { const float4 r = ds_ld4(in1 + i); xv[k].x += r.x; xv[k].y += r.y; xv[k].z += r.z; xv[k].w += r.w; }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < DS_IN_V4; ++k) {
+            const int i = base + (k * DS_THREADS + tid) * 4;
+            if (base + (k * DS_THREADS + (tid & ~31)) * 4 < K) {          // warp-uniform: K is a multiple of 128
+                float4 y = xv[k];
+                if (writer && in1 && o.sum_out) *(float4 *) (o.sum_out + i) = y;
+                if (norm) { y.x = y.x * scale * wv[k].x; y.y = y.y * scale * wv[k].y; y.z = y.z * scale * wv[k].z; y.w = y.w * scale * wv[k].w; }
+                if (writer && o.y_out) *(float4 *) (o.y_out + i) = y;
+                float amax = fmaxf(fmaxf(fabsf(y.x), fabsf(y.y)), fmaxf(fabsf(y.z), fabsf(y.w)));
+#pragma unroll
+                for (int s = 4; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+                const float d = amax * (1.0f / 127.0f), id = amax > 0.0f ? __fdividef(127.0f, amax) : 0.0f;
+                const int q0 = __float2int_rn(y.x * id), q1 = __float2int_rn(y.y * id), q2 = __float2int_rn(y.z * id), q3 = __float2int_rn(y.w * id);
+                int qsum = q0 + q1 + q2 + q3;
+#pragma unroll
+                for (int s = 4; s > 0; s >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, s);
+                uint8_t * blk = acts + (i >> 8) * DS_ACT_STRIDE;
+                *(uint32_t *) (blk + (i & 255)) = (uint32_t) (q0 & 0xff) | ((uint32_t) (q1 & 0xff) << 8) | ((uint32_t) (q2 & 0xff) << 16) | ((uint32_t) (q3 & 0xff) << 24);
+                if ((tid & 7) == 0) *(float2 *) (blk + 256 + ((i & 255) >> 5) * 8) = make_float2(d, d * (float) qsum);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void ds_rope_cs(const DsOp & o, float theta_extrap, int i0, float & c, float & s) {
+    // YaRN mix of interpolated and extrapolated angles (ggml-cpu.c:9275-9306), as rope_cs in glue.cu
+    const float theta_interp = o.freq_scale * theta_extrap;
+    float theta = theta_interp, mscale = o.attn_factor;
+    if (o.ext_factor != 0.0f) {
+        const float y = ((float) (i0 / 2) - o.corr0) / fmaxf(0.001f, o.corr1 - o.corr0);
+        const float ramp_mix = (1.0f - fminf(1.0f, fmaxf(0.0f, y))) * o.ext_factor;
+        theta = theta_interp * (1.0f - ramp_mix) + theta_extrap * ramp_mix;
+        mscale *= 1.0f + 0.1f * logf(1.0f / o.freq_scale);
+    }
+    c = cosf(theta) * mscale;
+    s = sinf(theta) * mscale;
+}
+
+__device__ __forceinline__ void ds_matvec_input(const DsOp & o, uint8_t * acts, DsMisc * misc) {
+    if (o.epilogue == DS_EP_ROPE_KV) {
+        const int tid = threadIdx.x;
+        if (tid < o.n_dims / 2 && tid < 64) {
+            const float theta_base = (float) __ldg(o.pos) * powf(o.theta_scale, (float) tid);
+            const float f = o.ff ? __ldg(o.ff + tid) : 1.0f;
+            float c, s;
+            ds_rope_cs(o, theta_base / f, 2 * tid, c, s);
+            misc->rope_cs[tid] = make_float2(c, s);
+        }
+        if (tid == 64) {
+            misc->kc = (__half *) ((char *) o.k_cache + (o.k_off_dev ? __ldg(o.k_off_dev) : o.k_off));
+            misc->vc = (__half *) ((char *) o.v_cache + (o.v_off_dev ? __ldg(o.v_off_dev) : o.v_off));
+        }
+    }
+    ds_input_stage(o, acts, misc->red);
+    __syncthreads();
+}
+
+// ---------------------------------------------------------------------------
+// weight streaming: the schedule of one warp over all mat-vec phases of the launch
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void ds_map(const DsMvDesc & d, uint32_t g, int j, int & mat, uint32_t & row) {
+    if (d.mode & 1) { mat = j; row = g; return; }
+    const uint32_t v = (d.mode & 2) ? 2 * g + j : g;
+    mat = v >= d.m_end[1] ? 2 : (v >= d.m_end[0] ? 1 : 0);
+    row = v - (mat ? d.m_end[mat - 1] : 0u);
+}
+
+// A unit is what one ring slot holds: a run of super-blocks of one weight row, or (mode bit 2) both rows of a group
+// back to back.  The fetch cursor walks the units of this warp in exactly the order the compute loop consumes them.
+struct DsFetch {
+    int mv;                     // mat-vec phase being fetched (n_mv: nothing left)
+    uint32_t g; int j, s;       // group, member, segment of the next unit
+    const uint8_t * src;        // first part of the next unit
+    const uint8_t * src2;       // second part (mode bit 2), or null when both rows are one contiguous run
+    int nseg; uint32_t seg_b, last_b;
+};
+
+__device__ __forceinline__ void ds_fetch_enter(DsFetch & f, const DsMvDesc * descs) {
+    const DsMvDesc & d = descs[f.mv];
+    int mat; uint32_t row;
+    ds_map(d, f.g, f.j, mat, row);
+    const int bb = ds_blk_bytes(d.type[mat]);
+    f.nseg = d.nseg[mat]; f.seg_b = (uint32_t) d.seg_blk[mat] * bb; f.last_b = (uint32_t) d.last_blk[mat] * bb;
+    f.src = (const uint8_t *) d.W[mat] + (uint64_t) row * d.nb1[mat];
+    f.src2 = nullptr;
+    f.s = 0;
+    if (d.mode & 4) {
+        int mat2; uint32_t row2;
+        ds_map(d, f.g, 1, mat2, row2);
+        const uint8_t * second = (const uint8_t *) d.W[mat2] + (uint64_t) row2 * d.nb1[mat2];
+        if (second == f.src + f.last_b) f.last_b *= 2;          // adjacent rows: one copy brings both
+        else f.src2 = second;
+    }
+}
+// positions f on the first unit of this warp at or after phase f.mv
+__device__ __forceinline__ void ds_fetch_seek(DsFetch & f, const DsMvDesc * descs, int n_mv, uint32_t gw) {
+    while (f.mv < n_mv && gw >= descs[f.mv].ngroups) ++f.mv;
+    if (f.mv < n_mv) { f.g = gw; f.j = 0; ds_fetch_enter(f, descs); }
+}
+__device__ __forceinline__ void ds_fetch_advance(DsFetch & f, const DsMvDesc * descs, int n_mv, uint32_t gw, uint32_t G) {
+    if (++f.s < f.nseg) { f.src += f.seg_b; return; }
+    const DsMvDesc & d = descs[f.mv];
+    if ((d.mode & 6) == 2 && f.j == 0) { f.j = 1; ds_fetch_enter(f, descs); return; }
+    f.j = 0; f.g += G;
+    if (f.g < d.ngroups) { ds_fetch_enter(f, descs); return; }
+    ++f.mv;
+    ds_fetch_seek(f, descs, n_mv, gw);
+}
+
+// ---------------------------------------------------------------------------
+// attention phase (one query token, head size 128, F16 K/V), after fattn_dec.cu
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, DsMisc * misc, unsigned long long * dbg) {
+#define DBG(k) do { if (dbg && blockIdx.x == 0 && threadIdx.x == 0) dbg[k] = ds_now(); } while (0)
+    DBG(0);
+    constexpr int D = 128, RT = 4, CH = 16, DPL = 4;
+    float (*qs)[D] = (float (*)[D]) scratch;                                     // [RT][D]
+    float * ps_all = (float *) (scratch + RT * D * 4);                           // [DS_WARPS][CH][RT]
+    float * w_m = ps_all + DS_WARPS * CH * RT;                                   // [DS_WARPS][RT]
+    float * w_l = w_m + DS_WARPS * RT;
+    float * w_o = w_l + DS_WARPS * RT;                                           // [DS_WARPS][RT][D]
+    static_assert((RT * D + DS_WARPS * CH * RT + 2 * DS_WARPS * RT + DS_WARPS * RT * D) * 4 <= DS_ACT_BYTES, "attention scratch");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gqa = o.n_head / o.n_head_kv;
+    const int n_items = o.n_head_kv * o.n_slices;
+    float * ps = ps_all + warp * CH * RT;
+    const __half * mrow = (const __half *) o.mask;
+
+#pragma unroll 1
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const int hk = item / o.n_slices, split = item - hk * o.n_slices;
+        const char * kbase = o.k + (int64_t) hk * o.k_nb2;
+        const char * vbase = o.v + (int64_t) hk * o.v_nb2;
+        const int kv0 = split * o.kv_per_slice, kv1 = min(o.n_kv, kv0 + o.kv_per_slice);
+        const int per_warp = (max(kv1 - kv0, 0) + DS_WARPS - 1) / DS_WARPS;
+        const int kw0 = kv0 + warp * per_warp, kw1 = min(kv1, kw0 + per_warp);
+        const int nkeys = max(kw1 - kw0, 0);
+        float * part = o.partials + ((int64_t) hk * o.n_slices + split) * gqa * (D + 2);
+
+#pragma unroll 1
+        for (int r0 = 0; r0 < gqa; r0 += RT) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < RT * D; i += DS_THREADS) {
+                const int rr = i / D, d = i % D, r = r0 + rr;
+                qs[rr][d] = r < gqa ? __ldcg(o.q + (int64_t) (hk * gqa + r) * D + d) : 0.0f;
+            }
+            __syncthreads();
+            DBG(1);
+
+            const int sub = lane & 7, kq = lane >> 3;
+            float m_run[RT], l_part[RT], oacc[RT][DPL];
+#pragma unroll
+            for (int rr = 0; rr < RT; ++rr) {
+                m_run[rr] = -INFINITY; l_part[rr] = 0.0f;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) oacc[rr][i] = 0.0f;
+            }
+#pragma unroll 1
+            for (int kb = 0; kb < nkeys; kb += CH) {
+                const int nk = min(CH, nkeys - kb);
+                // K rows of 4 keys per 8-lane group and this lane's part of all 16 V rows are requested together
+                uint4 kreg[4][2];
+                float mval[4];
+                uint2 vreg[CH];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int kl = kb + u * 4 + kq;
+                    mval[u] = 0.0f;
+                    if (kl < nkeys) {
+                        const char * kr = kbase + (int64_t) (kw0 + kl) * o.k_nb1;
+                        kreg[u][0] = __ldcg((const uint4 *) (kr + sub * 16));
+                        kreg[u][1] = __ldcg((const uint4 *) (kr + (8 + sub) * 16));
+                        if (mrow) mval[u] = __half2float(__ldg(mrow + kw0 + kl));
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < CH; ++t) {
+                    const int kl = min(kb + t, nkeys - 1);
+                    vreg[t] = __ldcg((const uint2 *) (vbase + (int64_t) (kw0 + kl) * o.v_nb1 + lane * 8));
+                }
+                float cmax[RT];
+#pragma unroll
+                for (int rr = 0; rr < RT; ++rr) cmax[rr] = -INFINITY;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int kl = kb + u * 4 + kq;
+                    float acc[RT] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    if (kl < nkeys) {
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const int chunk = c * 8 + sub;
+                            const __half2 * kh = (const __half2 *) &kreg[u][c];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 kf = __half22float2(kh[e]);
+                                const int d = chunk * 8 + 2 * e;
+#pragma unroll
+                                for (int rr = 0; rr < RT; ++rr) acc[rr] += kf.x * qs[rr][d] + kf.y * qs[rr][d + 1];
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int rr = 0; rr < RT; ++rr) {
+                        acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 1);
+                        acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 2);
+                        acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 4);
+                    }
+                    if (kl < nkeys) {
+                        float4 sv;
+                        float * s4 = (float *) &sv;
+#pragma unroll
+                        for (int rr = 0; rr < RT; ++rr) {
+                            const float s = acc[rr] * o.scale + mval[u];
+                            s4[rr] = s;
+                            cmax[rr] = fmaxf(cmax[rr], s);
+                        }
+                        if (sub == 0) *(float4 *) (ps + (u * 4 + kq) * RT) = sv;
+                    }
+                }
+                float fac[RT], m_new[RT];
+#pragma unroll
+                for (int rr = 0; rr < RT; ++rr) {
+                    cmax[rr] = warp_max(cmax[rr]);
+                    m_new[rr] = fmaxf(m_run[rr], cmax[rr]);
+                    fac[rr] = (m_run[rr] == -INFINITY) ? 0.0f : expf(m_run[rr] - m_new[rr]);
+                    m_run[rr] = m_new[rr];
+                }
+                __syncwarp();
+                // lane t turns the scores of key t into probabilities
+                {
+                    float4 sv = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (lane < nk) sv = *(float4 *) (ps + lane * RT);
+                    float * s4 = (float *) &sv;
+#pragma unroll
+                    for (int rr = 0; rr < RT; ++rr) {
+                        const float e = (lane >= nk || m_new[rr] == -INFINITY || s4[rr] == -INFINITY) ? 0.0f : expf(s4[rr] - m_new[rr]);
+                        s4[rr] = e;
+                        l_part[rr] = l_part[rr] * fac[rr] + e;
+                    }
+                    if (lane < nk) *(float4 *) (ps + lane * RT) = sv;
+                }
+                __syncwarp();
+#pragma unroll
+                for (int rr = 0; rr < RT; ++rr)
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) oacc[rr][i] *= fac[rr];
+#pragma unroll
+                for (int t = 0; t < CH; ++t) {
+                    if (t < nk) {
+                        const float4 pv = *(const float4 *) (ps + t * RT);
+                        const float2 a = __half22float2(*(const __half2 *) &vreg[t].x), b2 = __half22float2(*(const __half2 *) &vreg[t].y);
+                        const float vf[4] = {a.x, a.y, b2.x, b2.y};
+                        const float pr[RT] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+                        for (int rr = 0; rr < RT; ++rr)
+#pragma unroll
+                            for (int i = 0; i < DPL; ++i) oacc[rr][i] += pr[rr] * vf[i];
+                    }
+                }
+                __syncwarp();
+            }
+            DBG(2);
+            // ---- merge the warps of the CTA ----
+#pragma unroll
+            for (int rr = 0; rr < RT; ++rr) {
+                const float l = warp_sum(l_part[rr]);
+                if (lane == 0) { w_m[warp * RT + rr] = m_run[rr]; w_l[warp * RT + rr] = l; }
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) w_o[(warp * RT + rr) * D + lane * DPL + i] = oacc[rr][i];
+            }
+            __syncthreads();
+            for (int i = threadIdx.x; i < RT * D; i += DS_THREADS) {
+                const int rr = i / D, d = i % D, r = r0 + rr;
+                if (r >= gqa) continue;
+                float M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < DS_WARPS; ++w) M = fmaxf(M, w_m[w * RT + rr]);
+                float L = 0.0f, acc = 0.0f;
+#pragma unroll
+                for (int w = 0; w < DS_WARPS; ++w) {
+                    const float f = (w_m[w * RT + rr] == -INFINITY) ? 0.0f : expf(w_m[w * RT + rr] - M);
+                    L += w_l[w * RT + rr] * f; acc += w_o[(w * RT + rr) * D + d] * f;
+                }
+                if (o.n_slices == 1) {
+                    o.out[(int64_t) (hk * gqa + r) * D + d] = acc / L;
+                } else {
+                    part[(int64_t) r * (D + 2) + d] = acc;
+                    if (d == 0) { part[(int64_t) r * (D + 2) + D] = M; part[(int64_t) r * (D + 2) + D + 1] = L; }
+                }
+            }
+        }
+
+        DBG(3);
+        if (o.n_slices > 1) {
+            // ---- the last CTA of this KV head merges the slices, in slice order ----
+            __threadfence();
+            __syncthreads();
+            DBG(4);
+            if (threadIdx.x == 0) misc->ticket = atomicAdd(&o.tickets[hk], 1u);
+            __syncthreads();
+            DBG(5);
+            if (misc->ticket == (unsigned) o.n_slices - 1) {
+                __threadfence();
+                const float * base = o.partials + (int64_t) hk * o.n_slices * gqa * (D + 2);
+                for (int i = threadIdx.x; i < gqa * D; i += DS_THREADS) {
+                    const int r = i / D, d = i % D;
+                    float M = -INFINITY;
+                    for (int s = 0; s < o.n_slices; ++s) M = fmaxf(M, __ldcg(base + ((int64_t) s * gqa + r) * (D + 2) + D));
+                    float L = 0.0f, acc = 0.0f;
+                    for (int s = 0; s < o.n_slices; ++s) {
+                        const float * ps_ = base + ((int64_t) s * gqa + r) * (D + 2);
+                        const float m_s = __ldcg(ps_ + D);
+                        const float f = (m_s == -INFINITY) ? 0.0f : expf(m_s - M);
+                        L += __ldcg(ps_ + D + 1) * f; acc += __ldcg(ps_ + d) * f;
+                    }
+                    o.out[(int64_t) (hk * gqa + r) * D + d] = acc / L;
+                }
+                if (threadIdx.x == 0) o.tickets[hk] = 0;                    // ready for the next use
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid_constant__ DsParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t *  acts  = smem;
+    uint64_t * bars  = (uint64_t *) (smem + DS_OFF_BAR);
+    DsOp *     s_op  = (DsOp *) (smem + DS_OFF_OP);
+    DsMisc *   misc  = (DsMisc *) (smem + DS_OFF_MISC);
+    DsMvDesc * descs = (DsMvDesc *) (smem + DS_OFF_DESC);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint8_t *  ring = smem + DS_OFF_RING + warp * DS_NSLOT * DS_SLOT;
+    uint64_t * bar  = bars + warp * DS_NSLOT;
+    const uint32_t G = gridDim.x * DS_WARPS, gw = (uint32_t) warp * gridDim.x + blockIdx.x;
+
+    for (int i = tid; i < p.n_mv * (int) (sizeof(DsMvDesc) / 8); i += DS_THREADS) ((uint64_t *) descs)[i] = __ldg((const uint64_t *) p.descs + i);
+    if (tid == 0) { misc->dead = 0; misc->ticket = 0; }
+    if (lane == 0) for (int s = 0; s < DS_NSLOT; ++s) mbar_init(&bar[s], 1);
+    mbar_fence_init();
+    __syncthreads();
+
+    // ---- start the weight stream of this warp ----
+    DsFetch f; f.mv = 0; f.g = 0; f.j = 0; f.s = 0; f.src = nullptr; f.src2 = nullptr; f.nseg = 0; f.seg_b = 0; f.last_b = 0;
+    ds_fetch_seek(f, descs, p.n_mv, gw);
+    int f_slot = 0;
+    unsigned pending = 0;                       // slots with a copy in flight
+    auto fetch_issue = [&]() {
+        if (f.mv >= p.n_mv) return;
+        const uint32_t bytes = (f.s == f.nseg - 1) ? f.last_b : f.seg_b;
+        if (lane == 0) {
+            uint8_t * dst = ring + f_slot * DS_SLOT;
+            ds_fence_proxy_async();
+            if (f.src2) {
+                mbar_arrive_expect_tx(&bar[f_slot], 2 * bytes);
+                bulk_g2s(dst, f.src, bytes, &bar[f_slot]);
+                bulk_g2s(dst + bytes, f.src2, bytes, &bar[f_slot]);
+            } else {
+                mbar_arrive_expect_tx(&bar[f_slot], bytes);
+                bulk_g2s(dst, f.src, bytes, &bar[f_slot]);
+            }
+        }
+        pending |= 1u << f_slot;
+        f_slot = f_slot + 1 == DS_NSLOT ? 0 : f_slot + 1;
+        ds_fetch_advance(f, descs, p.n_mv, gw, G);
+    };
+#pragma unroll
+    for (int s = 0; s < DS_NSLOT; ++s) fetch_issue();
+
+    int c_slot = 0; unsigned c_par = 0;         // parity bit per slot
+    // waits for the unit in slot c_slot; returns its address
+    auto unit_wait = [&]() -> const uint8_t * {
+        bool ok = mbar_try_wait(&bar[c_slot], (c_par >> c_slot) & 1u);
+        if (!ok && !misc->dead) {
+            for (int it = 0; it < DS_SPIN_LIMIT && !ok; ++it) {
+                ok = mbar_try_wait(&bar[c_slot], (c_par >> c_slot) & 1u);
+                if (!ok && (it & 1023) == 1023 && misc->dead) break;
+            }
+            if (!ok && !misc->dead) { ds_give_up(p, misc, ERR_MBAR_TIMEOUT); f.mv = p.n_mv; }
+        }
+        if (ok) { pending &= ~(1u << c_slot); c_par ^= 1u << c_slot; }
+        return ring + c_slot * DS_SLOT;
+    };
+    // hands the slot back to the stream
+    auto unit_done = [&]() {
+        c_slot = c_slot + 1 == DS_NSLOT ? 0 : c_slot + 1;
+        __syncwarp();
+        if (misc->dead) f.mv = p.n_mv;
+        fetch_issue();
+    };
+
+    for (int i = tid; i < DS_OP_BYTES / 16; i += DS_THREADS) ((uint4 *) s_op)[i] = __ldg((const uint4 *) p.ops + i);
+    __syncthreads();
+    int mv = 0;
+    unsigned phase = 0;
+#pragma unroll 1
+    for (int op = 0; op < p.n_ops; ++op) {
+        const DsOp & o = s_op[op & 1];
+        // the next phase's parameters travel while this phase runs (they become visible at the phase's barrier)
+        uint4 next_op = make_uint4(0, 0, 0, 0);
+        const bool carries = op + 1 < p.n_ops && tid < DS_OP_BYTES / 16;
+        if (carries) next_op = __ldg((const uint4 *) (p.ops + op + 1) + tid);
+        const bool stamp = p.timing && blockIdx.x == 0 && tid == 0;
+        if (stamp) p.timing[op * 4 + 0] = ds_now();
+        if (o.kind == DS_OP_MATVEC) {
+            ds_matvec_input(o, acts, misc);
+            if (stamp) p.timing[op * 4 + 1] = ds_now();
+            const DsMvDesc & d = descs[mv];
+            const int R = (d.mode & 2) ? 2 : 1;
+            const bool both = (d.mode & 4) != 0;
+#pragma unroll 1
+            for (uint32_t g = gw; g < d.ngroups; g += G) {
+                float acc[2] = {0.0f, 0.0f};
+                int mat0; uint32_t row0;
+                ds_map(d, g, 0, mat0, row0);
+                // `both`: the two rows of the group share one slot, lanes [0, nb) take the first row, [nb, 2 nb) the second
+                const int nb = d.last_blk[mat0];
+                const int n_member = both ? 1 : R;
+#pragma unroll 1
+                for (int j = 0; j < n_member; ++j) {
+                    int mat; uint32_t row;
+                    ds_map(d, g, j, mat, row);
+                    const int type = d.type[mat], nseg = d.nseg[mat], seg_blk = d.seg_blk[mat];
+                    float a = 0.0f;
+#pragma unroll 1
+                    for (int s = 0; s < nseg; ++s) {
+                        const int nblk = s == nseg - 1 ? d.last_blk[mat] : seg_blk;
+                        const uint8_t * slot = unit_wait();
+                        const uint8_t * ap = acts + (size_t) s * seg_blk * DS_ACT_STRIDE;
+                        if (type == T_Q6_K) a += ds_dot_q6k(slot, nblk, ap, lane);
+                        else if (lane < (both ? 2 * nb : nblk)) {
+                            const uint8_t * al = ap + ((both && lane >= nb) ? lane - nb : lane) * DS_ACT_STRIDE;
+                            if (type == T_Q4_K) a += ds_dot_blk<T_Q4_K>(slot + lane * 144, al);
+                            else                a += ds_dot_blk<T_Q5_K>(slot + lane * 176, al);
+                        }
+                        unit_done();
+                    }
+                    if (both) { acc[0] = warp_sum(lane < nb ? a : 0.0f); acc[1] = warp_sum(lane < nb ? 0.0f : a); }
+                    else acc[j] = warp_sum(a);
+                }
+                if (lane == 0) {
+                    if (o.epilogue == DS_EP_STORE) {
+                        o.dst[mat0][row0] = acc[0];
+                        if (R == 2) o.dst[mat0][row0 + 1] = acc[1];
+                    } else if (o.epilogue == DS_EP_SILU_MUL) {
+                        const float sa = acc[0] / (1.0f + expf(-acc[0]));
+                        if (o.dst[0]) o.dst[0][g] = acc[0];
+                        if (o.dst[1]) o.dst[1][g] = acc[1];
+                        if (o.silu_out) o.silu_out[g] = sa;
+                        o.act_out[g] = sa * acc[1];
+                    } else {
+                        if (o.dst[mat0]) { o.dst[mat0][row0] = acc[0]; o.dst[mat0][row0 + 1] = acc[1]; }
+                        if (mat0 == 2) {
+                            ((__half2 *) misc->vc)[row0 >> 1] = __floats2half2_rn(acc[0], acc[1]);
+                        } else {
+                            const int ip = (int) (row0 % (uint32_t) o.head_dim) >> 1;
+                            float o0 = acc[0], o1 = acc[1];
+                            if (2 * ip < o.n_dims) {
+                                const float2 cs = misc->rope_cs[ip];
+                                o0 = acc[0] * cs.x - acc[1] * cs.y; o1 = acc[0] * cs.y + acc[1] * cs.x;
+                            }
+                            if (mat0 == 0) { o.q_rope[row0] = o0; o.q_rope[row0 + 1] = o1; }
+                            else {
+                                if (o.k_rope) { o.k_rope[row0] = o0; o.k_rope[row0 + 1] = o1; }
+                                ((__half2 *) misc->kc)[row0 >> 1] = __floats2half2_rn(o0, o1);
+                            }
+                        }
+                    }
+                }
+            }
+            ++mv;
+        } else if (o.kind == DS_OP_ATTN) {
+            if (stamp) p.timing[op * 4 + 1] = ds_now();
+            ds_attention(o, acts, misc, p.timing ? p.timing + 4000 : nullptr);
+        }
+        if (carries) ((uint4 *) (s_op + ((op + 1) & 1)))[tid] = next_op;
+        if (stamp) p.timing[op * 4 + 2] = ds_now();
+        ds_grid_barrier(p, misc, ++phase * gridDim.x);
+        if (stamp) p.timing[op * 4 + 3] = ds_now();
+    }
+
+    // ---- drain: nothing may still be writing into this CTA's shared memory when it exits ----
+    for (int s = 0; s < DS_NSLOT; ++s) {
+        if (pending & (1u << s)) {
+            bool ok = false;
+            for (int it = 0; it < (1 << 20) && !ok; ++it) ok = mbar_try_wait(&bar[s], (c_par >> s) & 1u);
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned n = atomicAdd(&p.sync[1], 1u);
+        if (n == gridDim.x - 1) {                 // everyone is past the last barrier: reset for the next launch
+            p.sync[0] = 0; p.sync[2] = 0;
+            __threadfence();
+            p.sync[1] = 0;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+int64_t decode_step_max_k() { return DS_MAX_K; }
+
+bool decode_step_type_ok(int type, int64_t K, int64_t w_nb1, const void * W) {
+    if (type != T_Q4_K && type != T_Q5_K && type != T_Q6_K) return false;
+    if (K <= 0 || K > DS_MAX_K || K % 256) return false;
+    if (type == T_Q6_K && K % 2048) return false;                 // runs of 8 super-blocks are the 16-byte multiples
+    if (((uintptr_t) W & 15) || (w_nb1 & 15) || w_nb1 <= 0 || w_nb1 > 0xffffffffll) return false;
+    return true;
+}
+
+static size_t ds_smem_bytes(int n_mv) { return (size_t) DS_OFF_DESC + (size_t) n_mv * sizeof(DsMvDesc); }
+
+int decode_step_max_matvecs(int) { return (int) ((DS_SMEM_LIMIT - DS_OFF_DESC) / sizeof(DsMvDesc)); }
+
+size_t decode_step_work_bytes(int n_ops) { return (size_t) (n_ops > 0 ? n_ops : 1) * sizeof(DsMvDesc); }
+
+static int ds_count_mv(const DsOp * ops, int n_ops) {
+    int n = 0;
+    for (int i = 0; i < n_ops; ++i) if (ops[i].kind == DS_OP_MATVEC) ++n;
+    return n;
+}
+
+static bool ds_make_desc(const DsOp & o, DsMvDesc & d) {
+    memset(&d, 0, sizeof(d));
+    const bool zip = o.epilogue == DS_EP_SILU_MUL;
+    // plain results are computed two rows at a time as well when every matrix has an even number of rows
+    bool pair = o.epilogue != DS_EP_STORE;
+    if (!pair) { pair = true; for (int i = 0; i < o.nmat; ++i) if (o.M[i] & 1) pair = false; }
+    d.mode = (uint8_t) ((zip ? 1 : 0) | (pair ? 2 : 0));
+    uint32_t total = 0;
+    for (int i = 0; i < 3; ++i) {
+        d.m_end[i] = 0xffffffffu;
+        if (i >= o.nmat) { d.type[i] = (uint8_t) o.type[0]; d.nseg[i] = 1; d.seg_blk[i] = d.last_blk[i] = 1; continue; }
+        if (!decode_step_type_ok(o.type[i], o.K, o.w_nb1[i], o.W[i]) || o.M[i] <= 0) return false;
+        if (pair && !zip && (o.M[i] & 1)) return false;
+        const int nblk = o.K / 256;
+        const int cap = o.type[i] == T_Q4_K ? 32 : (o.type[i] == T_Q5_K ? 24 : 16);       // super-blocks per ring slot
+        const int nseg = (nblk + cap - 1) / cap;
+        d.W[i] = (uint64_t) (uintptr_t) o.W[i]; d.nb1[i] = (uint32_t) o.w_nb1[i];
+        d.type[i] = (uint8_t) o.type[i]; d.nseg[i] = (uint8_t) nseg;
+        d.seg_blk[i] = (uint8_t) (nseg > 1 ? cap : nblk); d.last_blk[i] = (uint8_t) (nblk - (nseg - 1) * cap);
+        total += (uint32_t) o.M[i];
+        d.m_end[i] = total;
+    }
+    for (int i = o.nmat; i < 3; ++i) d.m_end[i] = 0xffffffffu;
+    if (zip) { if (o.nmat != 2 || o.M[0] != o.M[1]) return false; d.ngroups = (uint32_t) o.M[0]; }
+    else d.ngroups = pair ? total / 2 : total;
+    // short rows of the one-lane-per-block types: both rows of a pair share a slot (every matrix the same type)
+    if (pair) {
+        bool both = true;
+        for (int i = 0; i < o.nmat; ++i) if (o.type[i] != o.type[0] || o.type[i] == T_Q6_K || o.K / 256 > 16 || (o.type[i] == T_Q5_K && o.K / 256 > 12)) both = false;
+        if (both) d.mode |= 4;
+    }
+    return true;
+}
+
+cudaError_t decode_step_prepare(const DsOp * ops, int n_ops, void * work, cudaStream_t copy_stream) {
+    std::vector<DsMvDesc> descs;
+    for (int i = 0; i < n_ops; ++i) {
+        if (ops[i].kind != DS_OP_MATVEC) continue;
+        DsMvDesc d;
+        if (!ds_make_desc(ops[i], d)) return cudaErrorInvalidValue;
+        descs.push_back(d);
+    }
+    if (ds_smem_bytes((int) descs.size()) > (size_t) DS_SMEM_LIMIT) return cudaErrorInvalidValue;
+    if (descs.empty()) return cudaSuccess;
+    // synchronous with respect to the host buffer: the vector dies at return
+    cudaError_t e = cudaMemcpyAsync(work, descs.data(), descs.size() * sizeof(DsMvDesc), cudaMemcpyHostToDevice, copy_stream);
+    if (e != cudaSuccess) return e;
+    return cudaStreamSynchronize(copy_stream);
+}
+
+cudaError_t launch_decode_step(const DsOp * ops_dev, const DsOp * ops, int n_ops, const void * work, unsigned * sync, const LaunchCtx & c,
+                               unsigned long long * timing) {
+    DsParams p = {};
+    p.ops = ops_dev; p.n_ops = n_ops;
+    p.descs = (const DsMvDesc *) work; p.n_mv = ds_count_mv(ops, n_ops);
+    p.sync = sync; p.status = c.status; p.timing = timing;
+    const size_t smem = ds_smem_bytes(p.n_mv);
+    if (smem > (size_t) DS_SMEM_LIMIT) return cudaErrorInvalidValue;
+    static unsigned long long attr_mask = 0;
+    if (!(attr_mask & (1ull << (c.device & 63)))) {
+        cudaError_t e = cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DS_SMEM_LIMIT);
+        if (e != cudaSuccess) return e;
+        attr_mask |= 1ull << (c.device & 63);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned) c.sm_count); cfg.blockDim = dim3(DS_THREADS);
+    cfg.dynamicSmemBytes = smem; cfg.stream = c.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeCooperative;
+    at[0].val.cooperative = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, decode_step_kernel, p);
+}
+
+}  // namespace b200

@@ -140,6 +140,53 @@ cudaError_t launch_get_rows(const TensorD & src, const TensorD & idx, const Tens
 cudaError_t launch_soft_max(const TensorD & src, const TensorD * mask, const TensorD & dst, float scale, float max_bias,
                             const LaunchCtx & c);
 
+// ---- persistent decode step (decode_step.cu) ----
+// One cooperative launch runs a whole sequence of Llama layers for a single token: every phase is either
+// a group of mat-vecs that share their input (with the producer of that input fused in front and the
+// consumer of the results fused behind) or the attention over the KV cache; phases are separated by
+// grid-wide barriers, and every warp keeps streaming the weights of the phases ahead into its own
+// shared-memory ring while it waits.
+enum { DS_OP_MATVEC = 1, DS_OP_ATTN = 2 };
+enum { DS_IN_PLAIN = 0, DS_IN_NORM = 1 };                       // mat-vec input: x, or rms_norm(x) * w
+enum { DS_EP_STORE = 0, DS_EP_ROPE_KV = 1, DS_EP_SILU_MUL = 2 }; // what happens to the mat-vec results
+struct alignas(16) DsOp {
+    int kind;
+    // ---- DS_OP_MATVEC ----
+    int in_kind, K, nmat, epilogue;
+    const float * in0; const float * in1;        // x = in0 (+ in1 when set)
+    const float * norm_w; float eps;             // DS_IN_NORM
+    float * sum_out;                             // receives x when in1 is set
+    float * y_out;                               // optional: receives the (normalised) mat-vec input
+    const void * W[3]; int type[3]; int M[3]; int64_t w_nb1[3];
+    float * dst[3];                              // DS_EP_STORE: results; other epilogues: optional raw results
+    // DS_EP_ROPE_KV: matrices wq, wk, wv; rows are rotated in adjacent pairs (ggml's normal rope mode)
+    float * q_rope; float * k_rope;              // rotated Q (required), rotated K as F32 (optional)
+    void * k_cache; void * v_cache;              // viewed cache tensors; rows go to base + offset as F16
+    int64_t k_off, v_off; const int64_t * k_off_dev; const int64_t * v_off_dev;   // byte offsets: immediate, or read from device memory
+    const int32_t * pos; const float * ff;
+    int head_dim, n_dims; float freq_scale, ext_factor, attn_factor, theta_scale, corr0, corr1;
+    // DS_EP_SILU_MUL: matrices gate, up
+    float * act_out; float * silu_out;           // silu(gate) * up (required), silu(gate) (optional)
+    // ---- DS_OP_ATTN (one query token, head size 128, F16 K/V) ----
+    const float * q;                             // [n_head][128]
+    const char * k; const char * v; int64_t k_nb1, k_nb2, v_nb1, v_nb2;
+    const void * mask;                           // F16 [n_kv] or null
+    int n_kv, n_head, n_head_kv; float scale;
+    float * partials; unsigned * tickets;        // split-KV partial results and per-KV-head counters (zero between uses)
+    float * out;                                 // [n_head][128]
+    int n_slices, kv_per_slice;
+};
+bool        decode_step_type_ok(int type, int64_t K, int64_t w_nb1, const void * W);
+// How many mat-vec ops one launch can hold (their descriptors live in shared memory), given the largest K
+int         decode_step_max_matvecs(int device);
+int64_t     decode_step_max_k();
+// `ops` (host copy) describes the same ops as `ops_dev`; `work` is device memory of decode_step_work_bytes(n_ops)
+// that this call fills (asynchronously, on `copy_stream`) with the mat-vec descriptors; sync: 4 zero words
+size_t      decode_step_work_bytes(int n_ops);
+cudaError_t decode_step_prepare(const DsOp * ops, int n_ops, void * work, cudaStream_t copy_stream);
+cudaError_t launch_decode_step(const DsOp * ops_dev, const DsOp * ops, int n_ops, const void * work, unsigned * sync, const LaunchCtx & c,
+                               unsigned long long * timing = nullptr);   // optional: 4 time stamps per phase written by CTA 0
+
 // ---- flash attention (fattn.cu) ----
 struct FattnParams { float scale, max_bias, logit_softcap; };
 bool        fattn_supported(int64_t head_dim, int k_type, int v_type);

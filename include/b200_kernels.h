@@ -113,7 +113,8 @@ const char * b200_noalloc_last_error(void);
  *  - qkv:       q_out = rope(Wq . y), k_row = f16(rope(Wk . y)), v_row = f16(Wv . y) for one token at
  *               position pos; head size 128, adjacent-pair rotation (MUL_MAT x3, ROPE x2, CPY x2)
  *  - attention: FLASH_ATTN_EXT for one query token over contiguous F16 K/V [n_head_kv][n_kv][128], split into
- *               n_slices KV slices that the kernel merges in slice order
+ *               n_slices KV slices, merged in slice order either by the attention phase itself or
+ *               (merge_in_next_phase, 2..8 slices) by the input stage of the mat-vec phase that follows
  * Weight types: Q4_K, Q5_K, Q6_K (K a multiple of 256; of 2048 for Q6_K).                                   */
 int          b200_decode_step_mul_mat_host(int type, const void * W, int64_t M, int64_t K, const float * x, const float * x_add,
                                            const float * norm_w, float eps, float * dst, float * sum_out);
@@ -123,7 +124,8 @@ int          b200_decode_step_qkv_host(int type_qk, int type_v, const void * Wq,
                                        int n_dims, float freq_base, const float * freq_factors, float * q_out, void * k_row_f16,
                                        void * v_row_f16);
 int          b200_decode_step_attention_host(const float * q, const void * k_f16, const void * v_f16, const void * mask_f16,
-                                             int64_t n_kv, int64_t n_head, int64_t n_head_kv, float scale, int n_slices, float * dst);
+                                             int64_t n_kv, int64_t n_head, int64_t n_head_kv, float scale, int n_slices,
+                                             int merge_in_next_phase, float * dst);
 const char * b200_decode_step_last_error(void);
 
 /* ---- FLASH_ATTN_EXT -------------------------------------------------------

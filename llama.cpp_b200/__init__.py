@@ -90,7 +90,7 @@ def lib() -> C.CDLL:
         l.b200_decode_step_mul_mat_host.argtypes = [C.c_int, vp, i64, i64, vp, vp, vp, f32, vp, vp]
         l.b200_decode_step_gate_up_host.argtypes = [C.c_int, vp, vp, i64, i64, vp, vp]
         l.b200_decode_step_qkv_host.argtypes = [C.c_int, C.c_int, vp, vp, vp, i64, i64, i64, vp, vp, f32, C.c_int32, C.c_int, f32, vp, vp, vp, vp]
-        l.b200_decode_step_attention_host.argtypes = [vp, vp, vp, vp, i64, i64, i64, f32, C.c_int, vp]
+        l.b200_decode_step_attention_host.argtypes = [vp, vp, vp, vp, i64, i64, i64, f32, C.c_int, C.c_int, vp]
         l.b200_flash_attn_scratch_bytes.restype = sz
         l.b200_flash_attn_scratch_bytes.argtypes = [i64, i64, i64, i64]
         l.b200_flash_attn.argtypes = [vp, i64, i64, vp, i64, i64, vp, i64, i64, vp, i64, vp,
@@ -196,14 +196,15 @@ def decode_step_qkv(qt_qk: str, qt_v: str, wq, wk, wv, n_head: int, n_head_kv: i
     return q, k, v
 
 
-def decode_step_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, mask: np.ndarray | None, scale: float, n_slices: int) -> np.ndarray:
+def decode_step_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, mask: np.ndarray | None, scale: float, n_slices: int,
+                          merge_in_next_phase: bool = False) -> np.ndarray:
     """q f32 [n_head, 128]; k, v f16 [n_head_kv, n_kv, 128]; mask f16 [n_kv] or None; returns f32 [n_head, 128]."""
     q = np.ascontiguousarray(q, dtype=np.float32)
     k = np.ascontiguousarray(k, dtype=np.float16); v = np.ascontiguousarray(v, dtype=np.float16)
     m = None if mask is None else np.ascontiguousarray(mask, dtype=np.float16).reshape(-1)
     nh, nhkv, nkv = q.shape[0], k.shape[0], k.shape[1]
     out = np.empty((nh, 128), dtype=np.float32)
-    _check_ds(lib().b200_decode_step_attention_host(_p(q), _p(k), _p(v), _p(m), nkv, nh, nhkv, scale, n_slices, _p(out)))
+    _check_ds(lib().b200_decode_step_attention_host(_p(q), _p(k), _p(v), _p(m), nkv, nh, nhkv, scale, n_slices, int(merge_in_next_phase), _p(out)))
     return out
 
 

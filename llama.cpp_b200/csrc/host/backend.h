@@ -83,7 +83,7 @@ struct BackendCtx {
     bool         mega_tried = false;       // per graph_compute call: a failed match is not retried at every node
     void *       mega_arena = nullptr;
     cudaStream_t mega_copy_stream = nullptr;
-    uint64_t     n_mega = 0;               // persistent launches so far
+    uint64_t     n_mega = 0, graph_megas = 0;   // persistent launches so far; of them inside the instantiated CUDA graph
 
     // row-split over several processes: where the peers' arenas are mapped, and whether slices have been
     // stored to the peers since the last barrier
@@ -115,5 +115,6 @@ void             decode_step_print_timing(BackendCtx * ctx);
 // dispatch.cpp
 bool             device_supports_op(DeviceCtx * dev, const ggml_tensor * op);
 enum ggml_status graph_compute(BackendCtx * ctx, ggml_cgraph * cgraph);
+bool             run_single_node(BackendCtx * ctx, ggml_cgraph * g, int i);   // executes node i alone (no fusion with its neighbours)
 
 }  // namespace b200

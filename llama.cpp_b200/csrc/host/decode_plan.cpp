@@ -13,6 +13,7 @@
 #include "backend.h"
 #include "ggml-impl.h"
 
+#include <algorithm>
 #include <unordered_map>
 #include <unordered_set>
 
@@ -25,7 +26,8 @@ constexpr size_t MEGA_VEC_FLOATS = 32768;
 constexpr int    MEGA_N_VEC = 9;
 constexpr size_t MEGA_PARTIAL_BYTES = (size_t) 4 << 20;
 constexpr size_t MEGA_OFF_SYNC = 0, MEGA_OFF_TICKETS = 256, MEGA_OFF_OPS = 1024;
-constexpr size_t MEGA_OPS_REGION = (size_t) MEGA_MAX_OPS * (sizeof(DsOp) + 128);
+constexpr size_t MEGA_WORK_PER_OP = 160;                                          // >= decode_step_work_bytes(1)
+constexpr size_t MEGA_OPS_REGION = (size_t) MEGA_MAX_OPS * (sizeof(DsOp) + MEGA_WORK_PER_OP);
 constexpr size_t MEGA_OFF_VEC = MEGA_OFF_OPS + 2 * MEGA_OPS_REGION;
 constexpr size_t MEGA_OFF_PARTIALS = MEGA_OFF_VEC + MEGA_N_VEC * MEGA_VEC_FLOATS * 4;
 constexpr size_t MEGA_OFF_TIMING = MEGA_OFF_PARTIALS + MEGA_PARTIAL_BYTES;       // GGML_B200_MEGA_TIMING: 4 time stamps per phase
@@ -65,7 +67,9 @@ struct Matcher {
     std::unordered_map<const ggml_tensor *, int> index_of;
     std::vector<uint8_t> taken;                                        // per node: consumed by the plan
     std::vector<Block> blocks;
-    int last = -1;
+    int last = -1, n_matvec = 0;
+    const char * why = "";                                              // for GGML_B200_TRACE: the check that ended the match
+    int why_line = 0;
 
     bool exec(int i) const {
         const ggml_tensor * n = g->nodes[i];
@@ -111,35 +115,37 @@ struct Matcher {
         return decode_step_type_ok((int) W->type, K, (int64_t) W->nb[1], W->data);
     }
 
+    bool no(int line) { why_line = line; return false; }
+
     // [ADD] RMS_NORM MUL {MUL_MAT ...} starting at exec node `at`
     bool match_head(int at, Block & b) {
         const ggml_tensor * n = g->nodes[at];
         if (n->op == GGML_OP_ADD) {
-            if (!is_vec(n) || !t_contiguous(n) || !n->src[0] || !n->src[1] || !is_vec(n->src[0]) || !is_vec(n->src[1])) return false;
-            if (n->src[0]->ne[0] != n->ne[0] || n->src[1]->ne[0] != n->ne[0] || !t_contiguous(n->src[0]) || !t_contiguous(n->src[1])) return false;
+            if (!is_vec(n) || !t_contiguous(n) || !n->src[0] || !n->src[1] || !is_vec(n->src[0]) || !is_vec(n->src[1])) return no(__LINE__);
+            if (n->src[0]->ne[0] != n->ne[0] || n->src[1]->ne[0] != n->ne[0] || !t_contiguous(n->src[0]) || !t_contiguous(n->src[1])) return no(__LINE__);
             b.add = n;
             // its consumers: the RMS_NORM, and (later) the next residual ADD
             const ggml_tensor * rn = nullptr;
             for (int u : users_of(n)) if (g->nodes[u]->op == GGML_OP_RMS_NORM) rn = g->nodes[u];
-            if (!rn) return false;
+            if (!rn) return no(__LINE__);
             n = rn;
         }
-        if (n->op != GGML_OP_RMS_NORM || !is_vec(n) || !t_contiguous(n) || !n->src[0] || !is_vec(n->src[0]) || !t_contiguous(n->src[0])) return false;
-        if (b.add && root_of(n->src[0]) != b.add) return false;
+        if (n->op != GGML_OP_RMS_NORM || !is_vec(n) || !t_contiguous(n) || !n->src[0] || !is_vec(n->src[0]) || !t_contiguous(n->src[0])) return no(__LINE__);
+        if (b.add && root_of(n->src[0]) != b.add) return no(__LINE__);
         b.rn = n;
         const ggml_tensor * mu = sole_user(n, GGML_OP_MUL);
-        if (!mu || !is_vec(mu) || !t_contiguous(mu)) return false;
+        if (!mu || !is_vec(mu) || !t_contiguous(mu)) return no(__LINE__);
         const ggml_tensor * w = root_of(mu->src[0]) == n ? mu->src[1] : mu->src[0];
-        if ((root_of(mu->src[0]) != n && root_of(mu->src[1]) != n) || !w || w->type != GGML_TYPE_F32 || !t_contiguous(w) || t_nelements(w) != n->ne[0] || w->op != GGML_OP_NONE) return false;
+        if ((root_of(mu->src[0]) != n && root_of(mu->src[1]) != n) || !w || w->type != GGML_TYPE_F32 || !t_contiguous(w) || t_nelements(w) != n->ne[0] || w->op != GGML_OP_NONE) return no(__LINE__);
         b.mu = mu;
         const int64_t E = n->ne[0];
-        if (E % 128 || E > 8448) return false;
+        if (E % 128) return no(__LINE__);
         const std::vector<int> & mms = users_of(mu);
-        if (mms.empty() || mms.size() > 3) return false;
+        if (mms.empty() || mms.size() > 3) return no(__LINE__);
         int k = 0;
         for (int u : mms) {
             const ggml_tensor * mm = g->nodes[u];
-            if (!weight_ok(mm, E) || root_of(mm->src[1]) != mu) return false;
+            if (!weight_ok(mm, E) || root_of(mm->src[1]) != mu) return no(__LINE__);
             b.mm[k++] = mm;
         }
         b.kind = k == 3 ? 0 : (k == 2 ? 1 : 2);
@@ -151,52 +157,52 @@ struct Matcher {
         for (int i = 0; i < 3; ++i) {
             const ggml_tensor * mm = b.mm[i];
             if (const ggml_tensor * r = sole_user(mm, GGML_OP_ROPE)) {
-                if (root_of(r->src[0]) != mm) return false;
+                if (root_of(r->src[0]) != mm) return no(__LINE__);
                 if (sole_user(r, GGML_OP_FLASH_ATTN_EXT)) { q = mm; b.rope_q = r; }
                 else if (sole_user(r, GGML_OP_CPY))       { k = mm; b.rope_k = r; }
-                else return false;
+                else return no(__LINE__);
             } else if (sole_user(mm, GGML_OP_CPY)) v = mm;
-            else return false;
+            else return no(__LINE__);
         }
-        if (!q || !k || !v) return false;
+        if (!q || !k || !v) return no(__LINE__);
         b.mm[0] = q; b.mm[1] = k; b.mm[2] = v;
         const ggml_tensor * rq = b.rope_q, * rk = b.rope_k;
-        if (rq->type != GGML_TYPE_F32 || rk->type != GGML_TYPE_F32 || !t_contiguous(rq) || !t_contiguous(rk)) return false;
-        if (rq->src[1] != rk->src[1] || rq->src[2] != rk->src[2] || memcmp(rq->op_params, rk->op_params, sizeof(rq->op_params)) != 0) return false;
-        if (op_param_i32(rq, 2) != 0) return false;                        // adjacent-pair rotation only
+        if (rq->type != GGML_TYPE_F32 || rk->type != GGML_TYPE_F32 || !t_contiguous(rq) || !t_contiguous(rk)) return no(__LINE__);
+        if (rq->src[1] != rk->src[1] || rq->src[2] != rk->src[2] || memcmp(rq->op_params, rk->op_params, sizeof(rq->op_params)) != 0) return no(__LINE__);
+        if (op_param_i32(rq, 2) != 0) return no(__LINE__);                        // adjacent-pair rotation only
         const int64_t hd = rq->ne[0];
         const int n_dims = op_param_i32(rq, 1);
-        if (hd != 128 || rk->ne[0] != hd || n_dims <= 0 || n_dims > hd || (n_dims & 1)) return false;
-        if (rq->ne[2] != 1 || rk->ne[2] != 1 || rq->ne[3] != 1 || rk->ne[3] != 1) return false;
-        if (!rq->src[1] || rq->src[1]->type != GGML_TYPE_I32) return false;
-        if (rq->src[2] && (rq->src[2]->type != GGML_TYPE_F32 || t_nelements(rq->src[2]) < n_dims / 2)) return false;
-        if (q->ne[0] != hd * rq->ne[1] || k->ne[0] != hd * rk->ne[1] || v->ne[0] != k->ne[0]) return false;
+        if (hd != 128 || rk->ne[0] != hd || n_dims <= 0 || n_dims > hd || (n_dims & 1)) return no(__LINE__);
+        if (rq->ne[2] != 1 || rk->ne[2] != 1 || rq->ne[3] != 1 || rk->ne[3] != 1) return no(__LINE__);
+        if (!rq->src[1] || rq->src[1]->type != GGML_TYPE_I32) return no(__LINE__);
+        if (rq->src[2] && (rq->src[2]->type != GGML_TYPE_F32 || t_nelements(rq->src[2]) < n_dims / 2)) return no(__LINE__);
+        if (q->ne[0] != hd * rq->ne[1] || k->ne[0] != hd * rk->ne[1] || v->ne[0] != k->ne[0]) return no(__LINE__);
 
         b.cpy_k = sole_user(rk, GGML_OP_CPY); b.cpy_v = sole_user(v, GGML_OP_CPY);
         auto store_ok = [&](const ggml_tensor * c, const ggml_tensor * from) {
-            if (!c || root_of(c->src[0]) != from || !c->src[1]) return false;
+            if (!c || root_of(c->src[0]) != from || !c->src[1]) return no(__LINE__);
             const ggml_tensor * out = c->src[1];
             return out->type == GGML_TYPE_F16 && t_contiguous(out) && out->view_src && out->view_src->data && out->view_src->op == GGML_OP_NONE &&
                    t_nelements(out) == from->ne[0] * from->ne[1] * from->ne[2] && ((uintptr_t) out->data & 3) == 0;
         };
-        if (!store_ok(b.cpy_k, rk) || !store_ok(b.cpy_v, v)) return false;
+        if (!store_ok(b.cpy_k, rk) || !store_ok(b.cpy_v, v)) return no(__LINE__);
         b.cpy_k_idx = idx(b.cpy_k); b.cpy_v_idx = idx(b.cpy_v);
 
         const ggml_tensor * fa = sole_user(rq, GGML_OP_FLASH_ATTN_EXT);
-        if (!fa || root_of(fa->src[0]) != rq || fa->type != GGML_TYPE_F32 || !t_contiguous(fa)) return false;
+        if (!fa || root_of(fa->src[0]) != rq || fa->type != GGML_TYPE_F32 || !t_contiguous(fa)) return no(__LINE__);
         const ggml_tensor * K = fa->src[1], * V = fa->src[2], * mask = fa->src[3];
-        if (!K || !V || K->type != GGML_TYPE_F16 || V->type != GGML_TYPE_F16 || K->nb[0] != 2 || V->nb[0] != 2) return false;
-        if (K->ne[0] != hd || V->ne[0] != hd || K->ne[1] != V->ne[1] || K->ne[2] != rk->ne[1] || V->ne[2] != K->ne[2] || K->ne[3] != 1 || V->ne[3] != 1) return false;
-        if (root_of(K) != b.cpy_k->src[1]->view_src || root_of(V) != b.cpy_v->src[1]->view_src) return false;
+        if (!K || !V || K->type != GGML_TYPE_F16 || V->type != GGML_TYPE_F16 || K->nb[0] != 2 || V->nb[0] != 2) return no(__LINE__);
+        if (K->ne[0] != hd || V->ne[0] != hd || K->ne[1] != V->ne[1] || K->ne[2] != rk->ne[1] || V->ne[2] != K->ne[2] || K->ne[3] != 1 || V->ne[3] != 1) return no(__LINE__);
+        if (root_of(K) != b.cpy_k->src[1]->view_src || root_of(V) != b.cpy_v->src[1]->view_src) return no(__LINE__);
         auto al16 = [](const ggml_tensor * t) { return ((uintptr_t) t->data & 15) == 0 && (t->nb[1] & 15) == 0 && (t->nb[2] & 15) == 0; };
-        if (!al16(K) || !al16(V) || K->ne[1] < 1 || K->ne[1] > 1 << 20) return false;
-        if (fa->src[0]->ne[1] != 1 || fa->src[0]->ne[2] != rq->ne[1] || fa->src[0]->ne[3] != 1) return false;
-        if (rq->ne[1] % rk->ne[1] || rk->ne[1] > 64 || rq->ne[1] / rk->ne[1] > 16) return false;
-        if (mask && (mask->type != GGML_TYPE_F16 || mask->nb[0] != 2 || mask->ne[0] < K->ne[1] || root_of(mask) == nullptr)) return false;
-        if (op_param_f32(fa, 1) != 0.0f || op_param_f32(fa, 2) != 0.0f) return false;   // no ALiBi, no soft-capping
+        if (!al16(K) || !al16(V) || K->ne[1] < 1 || K->ne[1] > 1 << 20) return no(__LINE__);
+        if (fa->src[0]->ne[1] != 1 || fa->src[0]->ne[2] != rq->ne[1] || fa->src[0]->ne[3] != 1) return no(__LINE__);
+        if (rq->ne[1] % rk->ne[1] || rk->ne[1] > 64 || rq->ne[1] / rk->ne[1] > 16) return no(__LINE__);
+        if (mask && (mask->type != GGML_TYPE_F16 || mask->nb[0] != 2 || mask->ne[0] < K->ne[1] || root_of(mask) == nullptr)) return no(__LINE__);
+        if (op_param_f32(fa, 1) != 0.0f || op_param_f32(fa, 2) != 0.0f) return no(__LINE__);   // no ALiBi, no soft-capping
         b.fa = fa;
         const ggml_tensor * wo = sole_user(fa, GGML_OP_MUL_MAT);
-        if (!wo || root_of(wo->src[1]) != fa || !weight_ok(wo, fa->ne[0] * fa->ne[1])) return false;
+        if (!wo || root_of(wo->src[1]) != fa || !weight_ok(wo, fa->ne[0] * fa->ne[1])) return no(__LINE__);
         b.wo = wo;
         return true;
     }
@@ -206,20 +212,20 @@ struct Matcher {
         for (int i = 0; i < 2; ++i) {
             const ggml_tensor * mm = b.mm[i];
             if (const ggml_tensor * s = sole_user(mm, GGML_OP_UNARY)) {
-                if (op_param_i32(s, 0) != GGML_UNARY_OP_SILU || !is_vec(s) || !t_contiguous(s)) return false;
+                if (op_param_i32(s, 0) != GGML_UNARY_OP_SILU || !is_vec(s) || !t_contiguous(s)) return no(__LINE__);
                 gate = mm; b.silu = s;
             } else if (sole_user(mm, GGML_OP_MUL)) up = mm;
-            else return false;
+            else return no(__LINE__);
         }
-        if (!gate || !up || gate->ne[0] != up->ne[0]) return false;
+        if (!gate || !up || gate->ne[0] != up->ne[0]) return no(__LINE__);
         b.mm[0] = gate; b.mm[1] = up;
         const ggml_tensor * m3 = sole_user(b.silu, GGML_OP_MUL);
-        if (!m3 || m3 != sole_user(up, GGML_OP_MUL) || !is_vec(m3) || !t_contiguous(m3)) return false;
+        if (!m3 || m3 != sole_user(up, GGML_OP_MUL) || !is_vec(m3) || !t_contiguous(m3)) return no(__LINE__);
         const ggml_tensor * r0 = root_of(m3->src[0]), * r1 = root_of(m3->src[1]);
-        if (!((r0 == b.silu && r1 == up) || (r0 == up && r1 == b.silu))) return false;
+        if (!((r0 == b.silu && r1 == up) || (r0 == up && r1 == b.silu))) return no(__LINE__);
         b.mul3 = m3;
         const ggml_tensor * down = sole_user(m3, GGML_OP_MUL_MAT);
-        if (!down || root_of(down->src[1]) != m3 || !weight_ok(down, m3->ne[0])) return false;
+        if (!down || root_of(down->src[1]) != m3 || !weight_ok(down, m3->ne[0])) return no(__LINE__);
         b.down = down;
         return true;
     }
@@ -227,7 +233,7 @@ struct Matcher {
     // marks the nodes of block b as consumed; false if one of them is not available
     bool claim(const Block & b) {
         const ggml_tensor * all[] = {b.add, b.rn, b.mu, b.mm[0], b.mm[1], b.mm[2], b.rope_q, b.rope_k, b.cpy_k, b.cpy_v, b.fa, b.wo, b.silu, b.mul3, b.down};
-        for (const ggml_tensor * t : all) if (t && !take(t)) return false;
+        for (const ggml_tensor * t : all) if (t && !take(t)) return no(__LINE__);
         return true;
     }
 
@@ -248,7 +254,9 @@ struct Matcher {
             bool ok = match_head(at, b);
             if (ok && b.kind == 0) ok = match_attention(b);
             else if (ok && b.kind == 1) ok = match_ffn(b);
+            if (ok && n_matvec + (b.kind == 2 ? 1 : 2) > decode_step_max_matvecs(0)) ok = false;   // the rest goes into the next launch
             if (ok) ok = claim(b);
+            if (ok) n_matvec += b.kind == 2 ? 1 : 2;
             if (!ok) { taken = taken_before; last = last_before; break; }
             blocks.push_back(b);
             if (b.kind == 2 || (int) blocks.size() >= ctx->mega_max_blocks) break;
@@ -287,14 +295,29 @@ int try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i) {
     if ((n0->op != GGML_OP_ADD && n0->op != GGML_OP_RMS_NORM) || !is_vec(n0)) return 0;
     Matcher m{ctx, g, i};
     m.run();
+    if (ctx->trace > 0) fprintf(stderr, "ggml-b200 trace: decode-step match at node %d (%s): %zu blocks, stopped by the check at decode_plan.cpp:%d\n", i, n0->name, m.blocks.size(), m.why_line);
     // worth a launch from two whole layers on
     if ((int) m.blocks.size() < (ctx->mega_max_blocks < 4 ? ctx->mega_max_blocks : 4)) return 0;
-    // every executable node inside the covered range must belong to the plan
+    // Every executable node inside the covered range must belong to the plan.  libllama's node order also puts
+    // nodes there that only prepare inputs (the F32 -> F16 cast of the attention mask sits between the first
+    // layer's cache stores and its attention): a copy or row gather whose operands are produced outside the range
+    // (or by another such node) runs ahead of the persistent launch.  It writes its own tensor, which the
+    // allocator keeps apart from everything still live at its original position.
+    std::vector<int> hoisted;
     for (int j = i; j <= m.last; ++j) {
         if (!m.exec(j) || m.taken[(size_t) j] || ctx->node_done[(size_t) j]) continue;
+        const ggml_tensor * n = g->nodes[j];
         // an identity row selection is skipped when everything that reads it is inside the plan
-        if (is_identity_rows(g->nodes[j]) && !(g->nodes[j]->flags & GGML_TENSOR_FLAG_OUTPUT) && !m.visible(root_of(g->nodes[j]))) { m.taken[(size_t) j] = 1; continue; }
-        return 0;
+        if (is_identity_rows(n) && !(n->flags & GGML_TENSOR_FLAG_OUTPUT) && !m.visible(root_of(n))) { m.taken[(size_t) j] = 1; continue; }
+        bool ok = n->op == GGML_OP_CPY || n->op == GGML_OP_CONT || n->op == GGML_OP_DUP || n->op == GGML_OP_GET_ROWS;
+        if (ok && n->op == GGML_OP_CPY && n->src[1] && n->src[1]->view_src) ok = false;          // stores into views (the KV cache) stay in order
+        for (int s_ = 0; s_ < GGML_MAX_SRC && ok; ++s_) {
+            if (!n->src[s_] || n->src[s_] == n) continue;                  // (a cast names itself as its destination operand)
+            const int ri = m.idx(root_of(n->src[s_]));
+            if (ri >= i && std::find(hoisted.begin(), hoisted.end(), ri) == hoisted.end()) ok = false;
+        }
+        if (!ok) { if (ctx->trace > 0) fprintf(stderr, "ggml-b200 trace: node %d (%s) inside the range is not part of the plan\n", j, n->name); return 0; }
+        hoisted.push_back(j);
     }
     char * arena = (char *) mega_arena(ctx);
     if (!arena) return 0;
@@ -381,6 +404,14 @@ int try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i) {
             };
             o.corr0 = fmaxf(0.0f, floorf(corr_dim(beta_fast)));
             o.corr1 = fminf((float) o.n_dims - 1.0f, ceilf(corr_dim(beta_slow)));
+            {
+                const ggml_tensor * K = b.fa->src[1], * V = b.fa->src[2];
+                const int64_t kb = (int64_t) K->ne[1] * (int64_t) K->nb[1];
+                if ((int64_t) K->nb[2] * K->ne[2] == (int64_t) K->nb[1] && (int64_t) V->nb[2] * V->ne[2] == (int64_t) V->nb[1] && K->nb[1] == V->nb[1] &&
+                    kb <= ((int64_t) 8 << 20) && kb % 16 == 0) {
+                    o.pf_k = (const char *) K->data; o.pf_v = (const char *) V->data; o.pf_bytes = kb;
+                }
+            }
             ops.push_back(o);
 
             DsOp a; memset(&a, 0, sizeof(a));
@@ -392,13 +423,15 @@ int try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i) {
             a.mask = mask ? mask->data : nullptr;
             a.n_kv = (int) K->ne[1]; a.n_head = (int) rq->ne[1]; a.n_head_kv = (int) K->ne[2];
             a.scale = op_param_f32(b.fa, 0);
-            int slices = (a.n_kv + 191) / 192;
+            int slices = (a.n_kv + 63) / 64;                                // 4 keys per warp: short contexts are latency, not bandwidth
+            if (slices > DS_MAX_MERGE_SLICES && a.n_kv <= 4096) slices = DS_MAX_MERGE_SLICES;
             const int max_slices = lc.sm_count / a.n_head_kv;
             if (slices > max_slices) slices = max_slices;
             if (slices < 1) slices = 1;
             a.n_slices = slices; a.kv_per_slice = (a.n_kv + slices - 1) / slices;
             a.partials = (float *) (arena + MEGA_OFF_PARTIALS); a.tickets = (unsigned *) (arena + MEGA_OFF_TICKETS);
-            const size_t pn = (size_t) a.n_head_kv * slices * (size_t) (a.n_head / a.n_head_kv) * 130 * 4;
+            const size_t pn = (size_t) a.n_head_kv * slices * (size_t) (a.n_head / a.n_head_kv) * DS_PARTIAL_STRIDE * 4;
+            a.consumer_merge = slices > 1 && slices <= DS_MAX_MERGE_SLICES;                   // few slices: the wo phase merges them while it builds its input
             if (pn > partial_need) partial_need = pn;
             a.out = place(b.fa, vec[V_AO]);
             ops.push_back(a);
@@ -406,6 +439,10 @@ int try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i) {
             DsOp c; memset(&c, 0, sizeof(c));
             c.kind = DS_OP_MATVEC; c.in_kind = DS_IN_PLAIN; c.K = (int) b.wo->src[0]->ne[0]; c.nmat = 1; c.epilogue = DS_EP_STORE;
             c.in0 = a.out;
+            if (a.consumer_merge) {
+                c.in_kind = DS_IN_ATTN; c.in0 = a.partials; c.in_slices = a.n_slices; c.in_gqa = a.n_head / a.n_head_kv;
+                c.y_out = m.visible(b.fa) ? (float *) b.fa->data : nullptr;
+            }
             const ggml_tensor * W = b.wo->src[0];
             c.W[0] = W->data; c.type[0] = (int) W->type; c.M[0] = (int) W->ne[1]; c.w_nb1[0] = (int64_t) W->nb[1];
             c.dst[0] = place(b.wo, vec[V_WO]);
@@ -455,17 +492,21 @@ int try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i) {
         }
     }
 
+    for (int j : hoisted) {
+        if (!run_single_node(ctx, g, j)) return 0;
+        ctx->node_done[(size_t) j] = 1;
+    }
     // Phase lists and descriptors live in the arena: region 0 for direct runs, region 1 for the launches recorded
     // in the CUDA graph; every plan of one graph takes its own part of the region (a graph matched in pieces has
     // several), and the part is rewritten only when the graph is run directly / captured again.
     if (ctx->mega_ops_used + (int) ops.size() > MEGA_MAX_OPS) return 0;
     char * region = arena + MEGA_OFF_OPS + (ctx->capturing ? MEGA_OPS_REGION : 0);
     DsOp * ops_dev = (DsOp *) region + ctx->mega_ops_used;
-    void * work = region + (size_t) MEGA_MAX_OPS * sizeof(DsOp) + (size_t) ctx->mega_ops_used * 128;
+    void * work = region + (size_t) MEGA_MAX_OPS * sizeof(DsOp) + (size_t) ctx->mega_ops_used * MEGA_WORK_PER_OP;
     if (!ctx->capturing && ctx->mega_ops_used == 0) B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));   // an earlier direct run may still read region 0
     ctx->mega_ops_used += (int) ops.size();
     if (cudaMemcpyAsync(ops_dev, ops.data(), ops.size() * sizeof(DsOp), cudaMemcpyHostToDevice, ctx->mega_copy_stream) != cudaSuccess ||
-        decode_step_prepare(ops.data(), (int) ops.size(), work, ctx->mega_copy_stream) != cudaSuccess) {
+        decode_step_prepare(ops.data(), (int) ops.size(), lc.sm_count, work, ctx->mega_copy_stream) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }

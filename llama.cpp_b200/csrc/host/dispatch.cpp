@@ -625,6 +625,15 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
 #undef RUN0
 }
 
+bool run_single_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
+    const int fusion = ctx->use_fusion;
+    ctx->use_fusion = 0;
+    ctx->act_cache_invalidate(g->nodes[i]->data);
+    const int used = run_node(ctx, g, i);
+    ctx->use_fusion = fusion;
+    return used == 1;
+}
+
 static bool is_noop(const ggml_tensor * node) {
     return t_empty(node) || node->op == GGML_OP_NONE || node->op == GGML_OP_RESHAPE || node->op == GGML_OP_VIEW ||
            node->op == GGML_OP_PERMUTE || node->op == GGML_OP_TRANSPOSE;
@@ -742,7 +751,7 @@ enum ggml_status graph_compute(BackendCtx * ctx, ggml_cgraph * cgraph) {
         }
         if (k) B200_CUDA_CHECK(cudaMemcpyAsync(ctx->dyn_dev, ctx->dyn_host, sizeof(int64_t) * k, cudaMemcpyHostToDevice, ctx->stream));
         B200_CUDA_CHECK(cudaGraphLaunch(ctx->graph_exec, ctx->stream));
-        ctx->n_launches += ctx->graph_launches;
+        ctx->n_launches += ctx->graph_launches; ctx->n_mega += ctx->graph_megas;
         return GGML_STATUS_SUCCESS;
     }
     if (key != ctx->pending_key) {
@@ -755,7 +764,7 @@ enum ggml_status graph_compute(BackendCtx * ctx, ggml_cgraph * cgraph) {
     ctx->n_capture++;
     if (ctx->graph_exec) { cudaGraphExecDestroy(ctx->graph_exec); ctx->graph_exec = nullptr; ctx->graph_key = 0; }
     ctx->capturing = true; ctx->capture_failed = false; ctx->dyn_used = 0;
-    const uint64_t launches_before = ctx->n_launches;
+    const uint64_t launches_before = ctx->n_launches, megas_before = ctx->n_mega;
     B200_CUDA_CHECK(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
     const bool ok = run_all(ctx, cgraph);
     cudaGraph_t graph = nullptr;
@@ -778,7 +787,7 @@ enum ggml_status graph_compute(BackendCtx * ctx, ggml_cgraph * cgraph) {
         return run_all(ctx, cgraph) ? GGML_STATUS_SUCCESS : GGML_STATUS_FAILED;
     }
     cudaGraphDestroy(graph);
-    ctx->graph_exec = exec; ctx->graph_key = key; ctx->graph_launches = captured;
+    ctx->graph_exec = exec; ctx->graph_key = key; ctx->graph_launches = captured; ctx->graph_megas = ctx->n_mega - megas_before;
     if (ctx->dyn_used) B200_CUDA_CHECK(cudaMemcpyAsync(ctx->dyn_dev, ctx->dyn_host, sizeof(int64_t) * ctx->dyn_used, cudaMemcpyHostToDevice, ctx->stream));
     B200_CUDA_CHECK(cudaGraphLaunch(ctx->graph_exec, ctx->stream));
     ctx->n_launches += captured;

@@ -40,7 +40,7 @@ int run_phases(const std::vector<DsOp> & ops) {
         cudaGetLastError();
         return ds_fail(B200_E_SCRATCH, "device allocation failed");
     }
-    cudaError_t e = decode_step_prepare(ops.data(), (int) ops.size(), d_work.p, nullptr);
+    cudaError_t e = decode_step_prepare(ops.data(), (int) ops.size(), sm, d_work.p, nullptr);
     if (e != cudaSuccess) { cudaGetLastError(); return ds_fail(B200_E_UNSUPPORTED, "shape or type not handled by the decode-step kernel"); }
     LaunchCtx lc = {};
     lc.stream = nullptr; lc.device = dev; lc.sm_count = sm; lc.status = (int *) d_status.p;
@@ -121,13 +121,13 @@ API int b200_decode_step_qkv_host(int type_qk, int type_v, const void * Wq, cons
 }
 
 API int b200_decode_step_attention_host(const float * q, const void * k_f16, const void * v_f16, const void * mask_f16, int64_t n_kv,
-                                        int64_t n_head, int64_t n_head_kv, float scale, int n_slices, float * dst) {
+                                        int64_t n_head, int64_t n_head_kv, float scale, int n_slices, int merge_in_next_phase, float * dst) {
     const int64_t D = 128;
     if (n_kv <= 0 || n_head <= 0 || n_head_kv <= 0 || n_head % n_head_kv || n_head_kv > 64 || n_slices < 1 || n_slices > 128) return ds_fail(B200_E_BAD_ARG, "bad shape");
     const int64_t gqa = n_head / n_head_kv;
     Dev dq, dk, dv, dm, dd, dp, dt;
     if (!dq.put(q, n_head * D * 4) || !dk.put(k_f16, n_head_kv * n_kv * D * 2) || !dv.put(v_f16, n_head_kv * n_kv * D * 2) ||
-        (mask_f16 && !dm.put(mask_f16, n_kv * 2)) || !dd.alloc(n_head * D * 4) || !dp.alloc((size_t) n_head_kv * n_slices * gqa * (D + 2) * 4) || !dt.alloc(256)) {
+        (mask_f16 && !dm.put(mask_f16, n_kv * 2)) || !dd.alloc(n_head * D * 4) || !dp.alloc((size_t) n_head_kv * n_slices * gqa * DS_PARTIAL_STRIDE * 4) || !dt.alloc(256)) {
         cudaGetLastError();
         return ds_fail(B200_E_SCRATCH, "device allocation failed");
     }
@@ -140,7 +140,20 @@ API int b200_decode_step_attention_host(const float * q, const void * k_f16, con
     a.n_kv = (int) n_kv; a.n_head = (int) n_head; a.n_head_kv = (int) n_head_kv; a.scale = scale;
     a.n_slices = n_slices; a.kv_per_slice = (int) ((n_kv + n_slices - 1) / n_slices);
     a.partials = (float *) dp.p; a.tickets = (unsigned *) dt.p; a.out = (float *) dd.p;
-    if (int rc = run_phases({a})) return rc;
+    if (n_slices > 1 && n_slices <= DS_MAX_MERGE_SLICES && merge_in_next_phase) {
+        // the slices are merged by the input stage of a following mat-vec phase; an identity-free way to observe the
+        // merged vector is that phase's optional copy of its input (y_out); the mat-vec itself multiplies a tiny
+        // all-zero Q4_K matrix
+        a.consumer_merge = 1;
+        Dev dw, dz;
+        const int64_t K = n_head * D;
+        if (!dw.alloc((size_t) 2 * (K / 256) * 144) || !dz.alloc(16)) { cudaGetLastError(); return ds_fail(B200_E_SCRATCH, "device allocation failed"); }
+        DsOp c; memset(&c, 0, sizeof(c));
+        c.kind = DS_OP_MATVEC; c.in_kind = DS_IN_ATTN; c.K = (int) K; c.nmat = 1; c.epilogue = DS_EP_STORE;
+        c.in0 = a.partials; c.in_slices = n_slices; c.in_gqa = (int) gqa; c.y_out = (float *) dd.p;
+        c.W[0] = dw.p; c.type[0] = T_Q4_K; c.M[0] = 2; c.w_nb1[0] = (K / 256) * 144; c.dst[0] = (float *) dz.p;
+        if (int rc = run_phases({a, c})) return rc;
+    } else if (int rc = run_phases({a})) return rc;
     if (!dd.get(dst, n_head * D * 4)) { cudaGetLastError(); return ds_fail(B200_E_BAD_ARG, "copy back failed"); }
     return 0;
 }

@@ -33,26 +33,30 @@
 
 namespace b200 {
 
-static constexpr int DS_WARPS = 12, DS_THREADS = DS_WARPS * 32;
-static constexpr int DS_NSLOT = 3, DS_SLOT = 4608;               // per-warp ring: 3 slots of 32 Q4_K super-blocks
+static constexpr int DS_WARPS = 16, DS_THREADS = DS_WARPS * 32;
+static constexpr int DS_NSLOT = 2, DS_SLOT = 4608;               // per-warp ring: slots of 32 Q4_K super-blocks (one being computed on, the rest in flight)
 static constexpr int DS_ACT_STRIDE = 336;                         // shared-memory bytes per 256 activation values: 256 int8, 8 x {d, s}, 16 pad
-static constexpr int DS_ACT_BYTES = 38912;                        // activation blocks of one column (K <= 29440) / attention scratch
-static constexpr int DS_MAX_K = (DS_ACT_BYTES / DS_ACT_STRIDE) * 256;
-static constexpr int DS_IN_V4 = 4;                                // 4-value groups per thread and pass of the input stage
+static constexpr int DS_MAX_K = 28672;
+static constexpr int DS_BS16_OFF = DS_MAX_K / 256 * DS_ACT_STRIDE;    // int16 sums of 16 activations each (the -32 of Q6_K weights folds into them)
+static constexpr int DS_ACT_BYTES = (DS_BS16_OFF + DS_MAX_K / 8 + 255) / 256 * 256;   // activation blocks of one column / attention scratch
+static constexpr int DS_PSTRIDE = 132;                            // floats per (head, slice, row) attention partial: O[128], max, sum, pad
 static constexpr int DS_SPIN_LIMIT = 1 << 22;
 
-// what a warp needs to walk the rows of one mat-vec phase, kept in shared memory for all phases of the launch
-struct alignas(8) DsMvDesc {
-    uint64_t W[3];
-    uint32_t nb1[3];            // row stride in bytes
-    uint32_t m_end[3];          // cumulative row counts of the concatenated row space (unused: 0xffffffff)
-    uint32_t ngroups;           // work items of the phase; a group is one row, or two (mode bit 1)
-    uint8_t  type[3], nseg[3], seg_blk[3], last_blk[3];   // per matrix: segments per row, blocks per segment / in the last one
-    uint8_t  mode;              // bit 0: member j of a group is row g of matrix j (gate/up); else rows R*g+j of the row space;
-                                // bit 1: two rows per group; bit 2: both rows of a group travel in one ring slot
-    uint8_t  pad[3];
+// The rows of all mat-vec phases of a launch as a flat list of parts: one part per weight matrix of a phase (the
+// gate/up pair is one part).  A group is the work item of a warp: one row, or two rows (adjacent rows of a matrix, or
+// row r of gate and row r of up).  Group g of a phase belongs to warp g mod (warps of the grid).
+struct alignas(16) DsPart {
+    uint64_t W0, W1;            // the matrix; W1: the partner matrix of a gate/up pair
+    uint32_t nb1;               // row stride in bytes
+    uint32_t g_begin, g_end;    // groups of this part, in the numbering of its phase
+    uint32_t first_mod;         // g_begin mod (warps of the grid): a warp finds its first group without a division
+    uint16_t seg_b, last_b;     // bytes of a full / of the last segment of a row
+    uint8_t  type, nseg, seg_blk, last_blk;   // segments per row, super-blocks per full / last segment
+    uint8_t  mode;              // bit 0: gate/up pair; bit 1: two rows per group; bit 2: both rows travel in one ring slot
+    uint8_t  mat;               // index of the matrix within its phase
+    uint16_t phase;             // index of the mat-vec phase within the launch
 };
-static_assert(sizeof(DsMvDesc) == 72, "descriptor size");
+static_assert(sizeof(DsPart) == 48, "part size");
 
 // shared-memory layout
 static constexpr int DS_OFF_RING = DS_ACT_BYTES;
@@ -73,7 +77,7 @@ static constexpr int DS_SMEM_LIMIT = 232448;                      // 227 KB opt-
 
 struct DsParams {
     const DsOp * ops; int n_ops;
-    const DsMvDesc * descs; int n_mv;
+    const DsPart * parts; int n_parts;
     unsigned * sync;            // [0] barrier arrivals, [1] exit arrivals, [2] give-up flag
     int * status;
     unsigned long long * timing;   // optional: per phase {start, input stage done, rows done, barrier passed} of CTA 0, in ns
@@ -91,6 +95,23 @@ __device__ __forceinline__ unsigned ds_ld_acquire(const unsigned * p) {
 }
 __device__ __forceinline__ void ds_red_release(unsigned * p, unsigned v) {
     asm volatile("red.release.gpu.global.add.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+// mbarrier / bulk-copy operations on shared-memory addresses that were converted once
+__device__ __forceinline__ bool ds_try_wait(uint32_t bar_s, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar_s), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void ds_expect_tx(uint32_t bar_s, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar_s), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ds_bulk(uint32_t dst_s, const void * src, uint32_t bytes, uint32_t bar_s) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(dst_s), "l"(src), "r"(bytes), "r"(bar_s) : "memory");
 }
 __device__ __forceinline__ void ds_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -165,14 +186,16 @@ __device__ __forceinline__ float ds_dot_blk(const uint8_t * blk, const uint8_t *
                 hi[i] |= (t << 3) & 0x10101010u;
             }
         }
-        int t0 = ds_dp4a_us(lo[0], (int) xa.x, 0); t0 = ds_dp4a_us(lo[1], (int) xa.y, t0);
-        t0 = ds_dp4a_us(lo[2], (int) xa.z, t0);    t0 = ds_dp4a_us(lo[3], (int) xa.w, t0);
-        t0 = ds_dp4a_us(lo[4], (int) xb.x, t0);    t0 = ds_dp4a_us(lo[5], (int) xb.y, t0);
-        t0 = ds_dp4a_us(lo[6], (int) xb.z, t0);    t0 = ds_dp4a_us(lo[7], (int) xb.w, t0);
-        int t1 = ds_dp4a_us(hi[0], (int) xc.x, 0); t1 = ds_dp4a_us(hi[1], (int) xc.y, t1);
-        t1 = ds_dp4a_us(hi[2], (int) xc.z, t1);    t1 = ds_dp4a_us(hi[3], (int) xc.w, t1);
-        t1 = ds_dp4a_us(hi[4], (int) xd.x, t1);    t1 = ds_dp4a_us(hi[5], (int) xd.y, t1);
-        t1 = ds_dp4a_us(hi[6], (int) xd.z, t1);    t1 = ds_dp4a_us(hi[7], (int) xd.w, t1);
+        // four independent chains of four dependent dp4a each
+        int t0 = ds_dp4a_us(lo[0], (int) xa.x, 0), u0 = ds_dp4a_us(lo[4], (int) xb.x, 0);
+        int t1 = ds_dp4a_us(hi[0], (int) xc.x, 0), u1 = ds_dp4a_us(hi[4], (int) xd.x, 0);
+        t0 = ds_dp4a_us(lo[1], (int) xa.y, t0); u0 = ds_dp4a_us(lo[5], (int) xb.y, u0);
+        t1 = ds_dp4a_us(hi[1], (int) xc.y, t1); u1 = ds_dp4a_us(hi[5], (int) xd.y, u1);
+        t0 = ds_dp4a_us(lo[2], (int) xa.z, t0); u0 = ds_dp4a_us(lo[6], (int) xb.z, u0);
+        t1 = ds_dp4a_us(hi[2], (int) xc.z, t1); u1 = ds_dp4a_us(hi[6], (int) xd.z, u1);
+        t0 = ds_dp4a_us(lo[3], (int) xa.w, t0); u0 = ds_dp4a_us(lo[7], (int) xb.w, u0);
+        t1 = ds_dp4a_us(hi[3], (int) xc.w, t1); u1 = ds_dp4a_us(hi[7], (int) xd.w, u1);
+        t0 += u0; t1 += u1;
         const uint32_t scw = (r < 2 ? sc_lo : sc_hi) >> (16 * (r & 1)), mnw = (r < 2 ? mn_lo : mn_hi) >> (16 * (r & 1));
         // |sc * t| <= 63 * 32 * 240 * 127 < 2^26: exact in int32 (Q4_K keeps the high nibbles in place, value * 16)
         accE += ds.x * (float) ((int) (scw & 0xff) * t0);
@@ -196,8 +219,10 @@ __device__ __forceinline__ void ds_lds_run(const uint8_t * p, uint32_t (&out)[NW
     }
 }
 
-// Q6_K: lane l owns half (l & 1) of super-block l >> 1 (a slot holds at most 16 super-blocks)
-__device__ __forceinline__ float ds_dot_q6k(const uint8_t * slot, int nblk, const uint8_t * acts, int lane) {
+// Q6_K: lane l owns half (l & 1) of super-block l >> 1 (a slot holds at most 16 super-blocks).  The 6-bit values
+// stay unsigned (0..63): sum (q - 32) x = sum q x - 32 sum x, and the sums of x over the 16-value sub-blocks come
+// ready-made from the input stage (bs16), so no per-byte subtraction is needed.
+__device__ __forceinline__ float ds_dot_q6k(const uint8_t * slot, int nblk, const uint8_t * acts, const uint8_t * bs16, int lane) {
     const int b = lane >> 1, n128 = lane & 1;
     float acc = 0.0f;
     if (b < nblk) {
@@ -209,27 +234,31 @@ __device__ __forceinline__ float ds_dot_q6k(const uint8_t * slot, int nblk, cons
         const float d = h2f(*(const uint16_t *) (blk + 208));
         const uint8_t * ab = acts + b * DS_ACT_STRIDE + n128 * 128;       // 128 int8 of this half; its {d, s} pairs follow the block's 256 int8
         const uint8_t * dsb = acts + b * DS_ACT_STRIDE + 256 + n128 * 32;
+        const uint4 bsv = *(const uint4 *) (bs16 + b * 32 + n128 * 16);   // eight int16 sums
+        const uint32_t bsw[4] = {bsv.x, bsv.y, bsv.z, bsv.w};
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            int q[8];
+        for (int t = 0; t < 4; ++t) {                                     // 32 values: words 0..3 sub-block 2t, words 4..7 sub-block 2t+1
+            uint32_t q[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const uint32_t L = (t & 1) ? ql[8 + i] : ql[i];
                 const uint32_t nib = (t & 2) ? (L >> 4) & 0x0F0F0F0Fu : L & 0x0F0F0F0Fu;
                 const uint32_t hb = t == 0 ? (qh[i] << 4) : t == 1 ? (qh[i] << 2) : t == 2 ? qh[i] : (qh[i] >> 2);
-                q[i] = (int) __vsubss4(nib | (hb & 0x30303030u), 0x20202020u);
+                q[i] = nib | (hb & 0x30303030u);
             }
             const int sc_lo = (int) (int8_t) ((scw[(2 * t) >> 2] >> (8 * ((2 * t) & 3))) & 0xff);
             const int sc_hi = (int) (int8_t) ((scw[(2 * t + 1) >> 2] >> (8 * ((2 * t + 1) & 3))) & 0xff);
             const uint4 x0 = *(const uint4 *) (ab + t * 32);
             const uint4 x1 = *(const uint4 *) (ab + t * 32 + 16);
             const float dx = *(const float *) (dsb + t * 8);
-            int s0 = __dp4a(q[0], (int) x0.x, 0); s0 = __dp4a(q[1], (int) x0.y, s0);
-            s0 = __dp4a(q[2], (int) x0.z, s0);    s0 = __dp4a(q[3], (int) x0.w, s0);
-            int s1 = __dp4a(q[4], (int) x1.x, 0); s1 = __dp4a(q[5], (int) x1.y, s1);
-            s1 = __dp4a(q[6], (int) x1.z, s1);    s1 = __dp4a(q[7], (int) x1.w, s1);
-            acc += d * dx * (float) (sc_lo * s0 + sc_hi * s1);
+            int s0 = ds_dp4a_us(q[0], (int) x0.x, 0); s0 = ds_dp4a_us(q[1], (int) x0.y, s0);
+            s0 = ds_dp4a_us(q[2], (int) x0.z, s0);    s0 = ds_dp4a_us(q[3], (int) x0.w, s0);
+            int s1 = ds_dp4a_us(q[4], (int) x1.x, 0); s1 = ds_dp4a_us(q[5], (int) x1.y, s1);
+            s1 = ds_dp4a_us(q[6], (int) x1.z, s1);    s1 = ds_dp4a_us(q[7], (int) x1.w, s1);
+            const int b0 = (int) (int16_t) (bsw[t] & 0xffffu), b1 = (int) bsw[t] >> 16;
+            acc += dx * (float) (sc_lo * (s0 - 32 * b0) + sc_hi * (s1 - 32 * b1));
         }
+        acc *= d;
     }
     return acc;
 }
@@ -247,80 +276,135 @@ __device__ __forceinline__ float ds_block_sum(float v, float * red) {
     return warp_sum(r);
 }
 
-// x = in0 (+ in1) -> [rms_norm(x) * w] -> blk_act128 in shared memory.  A thread handles four consecutive values
-// at a time (one 128-bit load per operand), eight neighbouring threads form a 32-value quantization group; DS_IN_V4
-// such quads per thread and pass.  With rms_norm the vector is read twice (sum of squares, then normalise and
-// quantize): it sits in L2, and short code matters more here than the second read.
+// Input stage: the shared input vector of a mat-vec phase becomes int8 activation blocks in shared memory.  A thread
+// handles four consecutive values at a time (one 128-bit load per operand), eight neighbouring threads form a
+// 32-value quantization group.  Quad q of a pass belongs to thread q mod DS_THREADS.
 __device__ __forceinline__ float4 ds_ld4(const float * p) { return __ldcg((const float4 *) p); }
 
-__device__ __forceinline__ void ds_input_stage(const DsOp & o, uint8_t * acts, float * red) {
+// quantizes the quad y (values i .. i+3) and stores it; all 32 lanes of a warp call this together
+__device__ __forceinline__ void ds_quant_quad(const float4 y, int i, uint8_t * acts) {
     const int tid = threadIdx.x;
-    const int K = o.K;
-    const bool writer = blockIdx.x == 0, norm = o.in_kind == DS_IN_NORM;
+    float amax = fmaxf(fmaxf(fabsf(y.x), fabsf(y.y)), fmaxf(fabsf(y.z), fabsf(y.w)));
+#pragma unroll
+    for (int s = 4; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+    const float d = amax * (1.0f / 127.0f), id = amax > 0.0f ? __fdividef(127.0f, amax) : 0.0f;
+    const int q0 = __float2int_rn(y.x * id), q1 = __float2int_rn(y.y * id), q2 = __float2int_rn(y.z * id), q3 = __float2int_rn(y.w * id);
+    int qsum = q0 + q1 + q2 + q3;
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);                // 16 values: what a Q6_K sub-block multiplies
+    if ((tid & 3) == 0) *(int16_t *) (acts + DS_BS16_OFF + (i >> 4) * 2) = (int16_t) qsum;
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 4);
+    uint8_t * blk = acts + (i >> 8) * DS_ACT_STRIDE;
+    *(uint32_t *) (blk + (i & 255)) = (uint32_t) (q0 & 0xff) | ((uint32_t) (q1 & 0xff) << 8) | ((uint32_t) (q2 & 0xff) << 16) | ((uint32_t) (q3 & 0xff) << 24);
+    if ((tid & 7) == 0) *(float2 *) (blk + 256 + ((i & 255) >> 5) * 8) = make_float2(d, d * (float) qsum);
+}
+
+// x = in0 (+ in1), optionally rms-normalised and weighted.  NORM: the whole vector (K <= VQ * 4 * DS_THREADS) is
+// held in registers between the sum of squares and the output, so it is read once.  Otherwise the vector is
+// processed in passes of VQ quads per thread.
+template <int VQ, bool NORM>
+__device__ __forceinline__ void ds_input_x(const DsOp & o, uint8_t * acts, float * red) {
+    const int tid = threadIdx.x, K = o.K;
+    const bool writer = blockIdx.x == 0;
     const float * __restrict__ in0 = o.in0;
     const float * __restrict__ in1 = o.in1;
+    const bool one_pass = K <= VQ * DS_THREADS * 4;
     float scale = 1.0f;
-    if (norm) {
+    if (NORM && !one_pass) {                     // longer than the registers hold: sum of squares first, second read below
         float ss = 0.0f;
 #pragma unroll 1
-        for (int base = 0; base < K; base += DS_IN_V4 * DS_THREADS * 4) {
-            float4 xv[DS_IN_V4];
+        for (int base = 0; base < K; base += VQ * DS_THREADS * 4) {
 #pragma unroll
-            for (int k = 0; k < DS_IN_V4; ++k) {
+            for (int k = 0; k < VQ; ++k) {
                 const int i = base + (k * DS_THREADS + tid) * 4;
-                xv[k] = i < K ? ds_ld4(in0 + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            }
-            if (in1) {
-#pragma unroll
-                for (int k = 0; k < DS_IN_V4; ++k) {
-                    const int i = base + (k * DS_THREADS + tid) * 4;
-                    if (i < K) { const float4 r = ds_ld4(in1 + i); xv[k].x += r.x; xv[k].y += r.y; xv[k].z += r.z; xv[k].w += r.w; }
+                if (i < K) {
+                    float4 x = ds_ld4(in0 + i);
+                    if (in1) { const float4 r = ds_ld4(in1 + i); x.x += r.x; x.y += r.y; x.z += r.z; x.w += r.w; }
+                    ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
                 }
             }
-#pragma unroll
-            for (int k = 0; k < DS_IN_V4; ++k) ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
         }
         ss = ds_block_sum(ss, red);
         scale = rsqrtf(ss / (float) K + o.eps);
     }
 #pragma unroll 1
-    for (int base = 0; base < K; base += DS_IN_V4 * DS_THREADS * 4) {
-        float4 xv[DS_IN_V4], wv[DS_IN_V4];
+    for (int base = 0; base < K; base += VQ * DS_THREADS * 4) {
+        float4 xv[VQ], wv[NORM ? VQ : 1];
 #pragma unroll
-        for (int k = 0; k < DS_IN_V4; ++k) {
+        for (int k = 0; k < VQ; ++k) {
             const int i = base + (k * DS_THREADS + tid) * 4;
-            xv[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f); wv[k] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-            if (i < K) { xv[k] = ds_ld4(in0 + i); if (norm) wv[k] = __ldg((const float4 *) (o.norm_w + i)); }
+            xv[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (i < K) { xv[k] = ds_ld4(in0 + i); if (NORM) wv[k] = __ldg((const float4 *) (o.norm_w + i)); }
         }
         if (in1) {
 #pragma unroll
-            for (int k = 0; k < DS_IN_V4; ++k) {
+            for (int k = 0; k < VQ; ++k) {
                 const int i = base + (k * DS_THREADS + tid) * 4;
-                if (i < K) { const float4 r = ds_ld4(in1 + i); xv[k].x += r.x; xv[k].y += r.y; xv[k].z += r.z; xv[k].w += r.w; }
+                if (i < K) {
+                    const float4 r = ds_ld4(in1 + i);
+                    xv[k].x += r.x; xv[k].y += r.y; xv[k].z += r.z; xv[k].w += r.w;
+                    if (writer && o.sum_out) *(float4 *) (o.sum_out + i) = xv[k];
+                }
             }
         }
+        if (NORM && one_pass) {
+            float ss = 0.0f;
 #pragma unroll
-        for (int k = 0; k < DS_IN_V4; ++k) {
+            for (int k = 0; k < VQ; ++k) ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
+            ss = ds_block_sum(ss, red);
+            scale = rsqrtf(ss / (float) K + o.eps);
+        }
+#pragma unroll
+        for (int k = 0; k < VQ; ++k) {
             const int i = base + (k * DS_THREADS + tid) * 4;
             if (base + (k * DS_THREADS + (tid & ~31)) * 4 < K) {          // warp-uniform: K is a multiple of 128
                 float4 y = xv[k];
-                if (writer && in1 && o.sum_out) *(float4 *) (o.sum_out + i) = y;
-                if (norm) { y.x = y.x * scale * wv[k].x; y.y = y.y * scale * wv[k].y; y.z = y.z * scale * wv[k].z; y.w = y.w * scale * wv[k].w; }
+                if (NORM) { y.x = y.x * scale * wv[k].x; y.y = y.y * scale * wv[k].y; y.z = y.z * scale * wv[k].z; y.w = y.w * scale * wv[k].w; }
                 if (writer && o.y_out) *(float4 *) (o.y_out + i) = y;
-                float amax = fmaxf(fmaxf(fabsf(y.x), fabsf(y.y)), fmaxf(fabsf(y.z), fabsf(y.w)));
-#pragma unroll
-                for (int s = 4; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
-                const float d = amax * (1.0f / 127.0f), id = amax > 0.0f ? __fdividef(127.0f, amax) : 0.0f;
-                const int q0 = __float2int_rn(y.x * id), q1 = __float2int_rn(y.y * id), q2 = __float2int_rn(y.z * id), q3 = __float2int_rn(y.w * id);
-                int qsum = q0 + q1 + q2 + q3;
-#pragma unroll
-                for (int s = 4; s > 0; s >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, s);
-                uint8_t * blk = acts + (i >> 8) * DS_ACT_STRIDE;
-                *(uint32_t *) (blk + (i & 255)) = (uint32_t) (q0 & 0xff) | ((uint32_t) (q1 & 0xff) << 8) | ((uint32_t) (q2 & 0xff) << 16) | ((uint32_t) (q3 & 0xff) << 24);
-                if ((tid & 7) == 0) *(float2 *) (blk + 256 + ((i & 255) >> 5) * 8) = make_float2(d, d * (float) qsum);
+                ds_quant_quad(y, i, acts);
             }
         }
     }
+}
+
+// The input is the attention output, still in KV slices: (max, sum, unnormalised O) per (head, slice), merged here in
+// slice order (what the last CTA of a head would otherwise do after a fence and a ticket).
+__device__ __forceinline__ void ds_input_attn(const DsOp & o, uint8_t * acts) {
+    constexpr int D = 128, MAXS = DS_MAX_MERGE_SLICES;
+    const int tid = threadIdx.x, K = o.K, ns = o.in_slices, gqa = o.in_gqa;
+    const bool writer = blockIdx.x == 0;
+#pragma unroll 1
+    for (int base = 0; base < K; base += DS_THREADS * 4) {
+        const int i = base + tid * 4;
+        if (base + (tid & ~31) * 4 < K) {                                  // warp-uniform
+            const int h = i / D, d = i - h * D, hk = h / gqa, r = h - hk * gqa;
+            const float * p0 = o.in0 + ((int64_t) hk * ns * gqa + r) * DS_PSTRIDE;
+            float ms[MAXS]; float M = -INFINITY;
+#pragma unroll
+            for (int s = 0; s < MAXS; ++s) { ms[s] = s < ns ? __ldcg(p0 + (int64_t) s * gqa * DS_PSTRIDE + D) : -INFINITY; M = fmaxf(M, ms[s]); }
+            float L = 0.0f; float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int s = 0; s < MAXS; ++s) {
+                if (s < ns) {
+                    const float * ps = p0 + (int64_t) s * gqa * DS_PSTRIDE;
+                    const float f = (ms[s] == -INFINITY) ? 0.0f : expf(ms[s] - M);
+                    const float4 v = ds_ld4(ps + d);
+                    L += __ldcg(ps + D + 1) * f;
+                    acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+                }
+            }
+            const float inv = 1.0f / L;
+            const float4 y = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+            if (writer && o.y_out) *(float4 *) (o.y_out + i) = y;
+            ds_quant_quad(y, i, acts);
+        }
+    }
+}
+
+__device__ __forceinline__ void ds_input_stage(const DsOp & o, uint8_t * acts, float * red) {
+    if (o.in_kind == DS_IN_NORM) ds_input_x<3, true>(o, acts, red);
+    else if (o.in_kind == DS_IN_ATTN) ds_input_attn(o, acts);
+    else ds_input_x<7, false>(o, acts, red);                        // 14336 values (Llama-3-8B's feed-forward width) in one pass
 }
 
 __device__ __forceinline__ void ds_rope_cs(const DsOp & o, float theta_extrap, int i0, float & c, float & s) {
@@ -337,9 +421,23 @@ __device__ __forceinline__ void ds_rope_cs(const DsOp & o, float theta_extrap, i
     s = sinf(theta) * mscale;
 }
 
+__device__ __forceinline__ void ds_prefetch_l2(const char * p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(p), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void ds_matvec_input(const DsOp & o, uint8_t * acts, DsMisc * misc) {
     if (o.epilogue == DS_EP_ROPE_KV) {
         const int tid = threadIdx.x;
+        // The attention phase that follows reads this layer's K/V rows while the weight stream keeps HBM's queues
+        // full; asking for them now, two barriers ahead, puts them into L2 by then.
+        if ((tid & 31) == 0 && o.pf_bytes > 0) {
+            const int64_t CH = 4096, step = (int64_t) gridDim.x * DS_WARPS * CH;
+            for (int64_t off = ((int64_t) (tid >> 5) * gridDim.x + blockIdx.x) * CH; off < o.pf_bytes; off += step) {
+                const uint32_t n = (uint32_t) (o.pf_bytes - off < CH ? o.pf_bytes - off : CH);
+                ds_prefetch_l2(o.pf_k + off, n);
+                ds_prefetch_l2(o.pf_v + off, n);
+            }
+        }
         if (tid < o.n_dims / 2 && tid < 64) {
             const float theta_base = (float) __ldg(o.pos) * powf(o.theta_scale, (float) tid);
             const float f = o.ff ? __ldg(o.ff + tid) : 1.0f;
@@ -359,53 +457,51 @@ __device__ __forceinline__ void ds_matvec_input(const DsOp & o, uint8_t * acts, 
 // ---------------------------------------------------------------------------
 // weight streaming: the schedule of one warp over all mat-vec phases of the launch
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void ds_map(const DsMvDesc & d, uint32_t g, int j, int & mat, uint32_t & row) {
-    if (d.mode & 1) { mat = j; row = g; return; }
-    const uint32_t v = (d.mode & 2) ? 2 * g + j : g;
-    mat = v >= d.m_end[1] ? 2 : (v >= d.m_end[0] ? 1 : 0);
-    row = v - (mat ? d.m_end[mat - 1] : 0u);
-}
-
 // A unit is what one ring slot holds: a run of super-blocks of one weight row, or (mode bit 2) both rows of a group
-// back to back.  The fetch cursor walks the units of this warp in exactly the order the compute loop consumes them.
-struct DsFetch {
-    int mv;                     // mat-vec phase being fetched (n_mv: nothing left)
-    uint32_t g; int j, s;       // group, member, segment of the next unit
-    const uint8_t * src;        // first part of the next unit
-    const uint8_t * src2;       // second part (mode bit 2), or null when both rows are one contiguous run
-    int nseg; uint32_t seg_b, last_b;
+// back to back.  Both cursors of a warp -- the one that requests units and the one that computes on them -- walk the
+// parts in the same order; everything they need of the current part sits in registers.
+struct DsCursor {
+    int part;                   // current part (n_parts: nothing left)
+    uint32_t g, g_end;          // current group of this warp, end of the part
+    int j, s;                   // row of the group, segment of the row
+    const uint8_t * row;        // first row of the current group
+    const uint8_t * src;        // next unit
+    uint64_t g_stride;          // bytes from a group of this warp to its next one
+    int64_t  pair_off;          // from the first to the second row of a group
+    uint32_t seg_b, last_b; int nseg, mode;
 };
 
-__device__ __forceinline__ void ds_fetch_enter(DsFetch & f, const DsMvDesc * descs) {
-    const DsMvDesc & d = descs[f.mv];
-    int mat; uint32_t row;
-    ds_map(d, f.g, f.j, mat, row);
-    const int bb = ds_blk_bytes(d.type[mat]);
-    f.nseg = d.nseg[mat]; f.seg_b = (uint32_t) d.seg_blk[mat] * bb; f.last_b = (uint32_t) d.last_blk[mat] * bb;
-    f.src = (const uint8_t *) d.W[mat] + (uint64_t) row * d.nb1[mat];
-    f.src2 = nullptr;
-    f.s = 0;
-    if (d.mode & 4) {
-        int mat2; uint32_t row2;
-        ds_map(d, f.g, 1, mat2, row2);
-        const uint8_t * second = (const uint8_t *) d.W[mat2] + (uint64_t) row2 * d.nb1[mat2];
-        if (second == f.src + f.last_b) f.last_b *= 2;          // adjacent rows: one copy brings both
-        else f.src2 = second;
-    }
+// loads part `c.part` and positions the cursor on this warp's first group in it; false if the warp has none
+__device__ __forceinline__ bool ds_cursor_enter(DsCursor & c, const DsPart * parts, uint32_t gw, uint32_t G) {
+    const DsPart & P = parts[c.part];
+    const uint4 a = *(const uint4 *) &P, b = *(const uint4 *) ((const uint8_t *) &P + 16), d = *(const uint4 *) ((const uint8_t *) &P + 32);
+    const uint64_t W0 = (uint64_t) a.x | ((uint64_t) a.y << 32), W1 = (uint64_t) a.z | ((uint64_t) a.w << 32);
+    const uint32_t nb1 = b.x, g_begin = b.y, first_mod = b.w;
+    c.g_end = b.z;
+    c.g = g_begin + (gw >= first_mod ? gw - first_mod : gw + G - first_mod);
+    if (c.g >= c.g_end) return false;
+    c.seg_b = d.x & 0xffffu; c.last_b = d.x >> 16;
+    c.nseg = (d.y >> 8) & 0xff; c.mode = d.z & 0xff;
+    const uint32_t rows_per_group = (c.mode & 3) == 2 ? 2u : 1u;           // adjacent rows of one matrix
+    c.g_stride = (uint64_t) G * rows_per_group * nb1;
+    c.pair_off = (c.mode & 1) ? (int64_t) (W1 - W0) : (int64_t) nb1;
+    c.row = (const uint8_t *) W0 + (uint64_t) (c.g - g_begin) * rows_per_group * nb1;
+    c.src = c.row; c.j = 0; c.s = 0;
+    return true;
 }
-// positions f on the first unit of this warp at or after phase f.mv
-__device__ __forceinline__ void ds_fetch_seek(DsFetch & f, const DsMvDesc * descs, int n_mv, uint32_t gw) {
-    while (f.mv < n_mv && gw >= descs[f.mv].ngroups) ++f.mv;
-    if (f.mv < n_mv) { f.g = gw; f.j = 0; ds_fetch_enter(f, descs); }
+__device__ __forceinline__ void ds_cursor_seek(DsCursor & c, const DsPart * parts, int n_parts, uint32_t gw, uint32_t G) {
+    while (c.part < n_parts && !ds_cursor_enter(c, parts, gw, G)) ++c.part;
 }
-__device__ __forceinline__ void ds_fetch_advance(DsFetch & f, const DsMvDesc * descs, int n_mv, uint32_t gw, uint32_t G) {
-    if (++f.s < f.nseg) { f.src += f.seg_b; return; }
-    const DsMvDesc & d = descs[f.mv];
-    if ((d.mode & 6) == 2 && f.j == 0) { f.j = 1; ds_fetch_enter(f, descs); return; }
-    f.j = 0; f.g += G;
-    if (f.g < d.ngroups) { ds_fetch_enter(f, descs); return; }
-    ++f.mv;
-    ds_fetch_seek(f, descs, n_mv, gw);
+// steps to the next unit of this warp
+__device__ __forceinline__ void ds_cursor_advance(DsCursor & c, const DsPart * parts, int n_parts, uint32_t gw, uint32_t G) {
+    if (++c.s < c.nseg) { c.src += c.seg_b; return; }
+    c.s = 0;
+    if ((c.mode & 6) == 2 && c.j == 0) { c.j = 1; c.src = c.row + c.pair_off; return; }
+    c.j = 0;
+    c.g += G;
+    if (c.g < c.g_end) { c.row += c.g_stride; c.src = c.row; return; }
+    ++c.part;
+    ds_cursor_seek(c, parts, n_parts, gw, G);
 }
 
 // ---------------------------------------------------------------------------
@@ -414,7 +510,7 @@ __device__ __forceinline__ void ds_fetch_advance(DsFetch & f, const DsMvDesc * d
 __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, DsMisc * misc, unsigned long long * dbg) {
 #define DBG(k) do { if (dbg && blockIdx.x == 0 && threadIdx.x == 0) dbg[k] = ds_now(); } while (0)
     DBG(0);
-    constexpr int D = 128, RT = 4, CH = 16, DPL = 4;
+    constexpr int D = 128, RT = 4, CH = 4, KU = CH / 4, DPL = 4;
     float (*qs)[D] = (float (*)[D]) scratch;                                     // [RT][D]
     float * ps_all = (float *) (scratch + RT * D * 4);                           // [DS_WARPS][CH][RT]
     float * w_m = ps_all + DS_WARPS * CH * RT;                                   // [DS_WARPS][RT]
@@ -436,7 +532,7 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
         const int per_warp = (max(kv1 - kv0, 0) + DS_WARPS - 1) / DS_WARPS;
         const int kw0 = kv0 + warp * per_warp, kw1 = min(kv1, kw0 + per_warp);
         const int nkeys = max(kw1 - kw0, 0);
-        float * part = o.partials + ((int64_t) hk * o.n_slices + split) * gqa * (D + 2);
+        float * part = o.partials + ((int64_t) hk * o.n_slices + split) * gqa * DS_PSTRIDE;
 
 #pragma unroll 1
         for (int r0 = 0; r0 < gqa; r0 += RT) {
@@ -459,12 +555,12 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
 #pragma unroll 1
             for (int kb = 0; kb < nkeys; kb += CH) {
                 const int nk = min(CH, nkeys - kb);
-                // K rows of 4 keys per 8-lane group and this lane's part of all 16 V rows are requested together
-                uint4 kreg[4][2];
-                float mval[4];
+                // the K rows of this 8-lane group and this lane's part of all V rows of the chunk are requested together
+                uint4 kreg[KU][2];
+                float mval[KU];
                 uint2 vreg[CH];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < KU; ++u) {
                     const int kl = kb + u * 4 + kq;
                     mval[u] = 0.0f;
                     if (kl < nkeys) {
@@ -483,7 +579,7 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
 #pragma unroll
                 for (int rr = 0; rr < RT; ++rr) cmax[rr] = -INFINITY;
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < KU; ++u) {
                     const int kl = kb + u * 4 + kq;
                     float acc[RT] = {0.0f, 0.0f, 0.0f, 0.0f};
                     if (kl < nkeys) {
@@ -585,14 +681,14 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
                 if (o.n_slices == 1) {
                     o.out[(int64_t) (hk * gqa + r) * D + d] = acc / L;
                 } else {
-                    part[(int64_t) r * (D + 2) + d] = acc;
-                    if (d == 0) { part[(int64_t) r * (D + 2) + D] = M; part[(int64_t) r * (D + 2) + D + 1] = L; }
+                    part[(int64_t) r * DS_PSTRIDE + d] = acc;
+                    if (d == 0) { part[(int64_t) r * DS_PSTRIDE + D] = M; part[(int64_t) r * DS_PSTRIDE + D + 1] = L; }
                 }
             }
         }
 
         DBG(3);
-        if (o.n_slices > 1) {
+        if (o.n_slices > 1 && !o.consumer_merge) {
             // ---- the last CTA of this KV head merges the slices, in slice order ----
             __threadfence();
             __syncthreads();
@@ -602,14 +698,14 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
             DBG(5);
             if (misc->ticket == (unsigned) o.n_slices - 1) {
                 __threadfence();
-                const float * base = o.partials + (int64_t) hk * o.n_slices * gqa * (D + 2);
+                const float * base = o.partials + (int64_t) hk * o.n_slices * gqa * DS_PSTRIDE;
                 for (int i = threadIdx.x; i < gqa * D; i += DS_THREADS) {
                     const int r = i / D, d = i % D;
                     float M = -INFINITY;
-                    for (int s = 0; s < o.n_slices; ++s) M = fmaxf(M, __ldcg(base + ((int64_t) s * gqa + r) * (D + 2) + D));
+                    for (int s = 0; s < o.n_slices; ++s) M = fmaxf(M, __ldcg(base + ((int64_t) s * gqa + r) * DS_PSTRIDE + D));
                     float L = 0.0f, acc = 0.0f;
                     for (int s = 0; s < o.n_slices; ++s) {
-                        const float * ps_ = base + ((int64_t) s * gqa + r) * (D + 2);
+                        const float * ps_ = base + ((int64_t) s * gqa + r) * DS_PSTRIDE;
                         const float m_s = __ldcg(ps_ + D);
                         const float f = (m_s == -INFINITY) ? 0.0f : expf(m_s - M);
                         L += __ldcg(ps_ + D + 1) * f; acc += __ldcg(ps_ + d) * f;
@@ -631,70 +727,73 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
     uint64_t * bars  = (uint64_t *) (smem + DS_OFF_BAR);
     DsOp *     s_op  = (DsOp *) (smem + DS_OFF_OP);
     DsMisc *   misc  = (DsMisc *) (smem + DS_OFF_MISC);
-    DsMvDesc * descs = (DsMvDesc *) (smem + DS_OFF_DESC);
+    DsPart *   parts = (DsPart *) (smem + DS_OFF_DESC);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t *  ring = smem + DS_OFF_RING + warp * DS_NSLOT * DS_SLOT;
     uint64_t * bar  = bars + warp * DS_NSLOT;
     const uint32_t G = gridDim.x * DS_WARPS, gw = (uint32_t) warp * gridDim.x + blockIdx.x;
+    const int n_parts = p.n_parts;
 
-    for (int i = tid; i < p.n_mv * (int) (sizeof(DsMvDesc) / 8); i += DS_THREADS) ((uint64_t *) descs)[i] = __ldg((const uint64_t *) p.descs + i);
+    for (int i = tid; i < n_parts * (int) (sizeof(DsPart) / 16); i += DS_THREADS) ((uint4 *) parts)[i] = __ldg((const uint4 *) p.parts + i);
+    for (int i = tid; i < DS_OP_BYTES / 16; i += DS_THREADS) ((uint4 *) s_op)[i] = __ldg((const uint4 *) p.ops + i);
     if (tid == 0) { misc->dead = 0; misc->ticket = 0; }
     if (lane == 0) for (int s = 0; s < DS_NSLOT; ++s) mbar_init(&bar[s], 1);
     mbar_fence_init();
     __syncthreads();
 
-    // ---- start the weight stream of this warp ----
-    DsFetch f; f.mv = 0; f.g = 0; f.j = 0; f.s = 0; f.src = nullptr; f.src2 = nullptr; f.nseg = 0; f.seg_b = 0; f.last_b = 0;
-    ds_fetch_seek(f, descs, p.n_mv, gw);
-    int f_slot = 0;
-    unsigned pending = 0;                       // slots with a copy in flight
+    // ---- the weight stream of this warp: f requests units, c (below) computes on them, in the same order ----
+    DsCursor f;
+    f.part = 0;
+    ds_cursor_seek(f, parts, n_parts, gw, G);
+    const uint32_t ring_s = smem_u32(ring), bar_s = smem_u32(bar);
+    uint32_t f_off = 0, f_bar = bar_s;          // slot being filled next: byte offset in the ring, its mbarrier
+    unsigned n_fetched = 0, n_done = 0;
+    bool warp_dead = false;                     // this warp gave up a wait: it neither requests nor waits any more
     auto fetch_issue = [&]() {
-        if (f.mv >= p.n_mv) return;
+        if (f.part >= n_parts) return;
         const uint32_t bytes = (f.s == f.nseg - 1) ? f.last_b : f.seg_b;
         if (lane == 0) {
-            uint8_t * dst = ring + f_slot * DS_SLOT;
             ds_fence_proxy_async();
-            if (f.src2) {
-                mbar_arrive_expect_tx(&bar[f_slot], 2 * bytes);
-                bulk_g2s(dst, f.src, bytes, &bar[f_slot]);
-                bulk_g2s(dst + bytes, f.src2, bytes, &bar[f_slot]);
+            if (f.mode & 4) {                   // both rows of the group: adjacent in memory (one copy) or not (two)
+                ds_expect_tx(f_bar, 2 * bytes);
+                if (f.pair_off == (int64_t) bytes) ds_bulk(ring_s + f_off, f.src, 2 * bytes, f_bar);
+                else { ds_bulk(ring_s + f_off, f.src, bytes, f_bar); ds_bulk(ring_s + f_off + bytes, f.src + f.pair_off, bytes, f_bar); }
             } else {
-                mbar_arrive_expect_tx(&bar[f_slot], bytes);
-                bulk_g2s(dst, f.src, bytes, &bar[f_slot]);
+                ds_expect_tx(f_bar, bytes);
+                ds_bulk(ring_s + f_off, f.src, bytes, f_bar);
             }
         }
-        pending |= 1u << f_slot;
-        f_slot = f_slot + 1 == DS_NSLOT ? 0 : f_slot + 1;
-        ds_fetch_advance(f, descs, p.n_mv, gw, G);
+        ++n_fetched;
+        f_off += DS_SLOT; f_bar += 8;
+        if (f_off == DS_NSLOT * DS_SLOT) { f_off = 0; f_bar = bar_s; }
+        ds_cursor_advance(f, parts, n_parts, gw, G);
     };
 #pragma unroll
     for (int s = 0; s < DS_NSLOT; ++s) fetch_issue();
 
-    int c_slot = 0; unsigned c_par = 0;         // parity bit per slot
-    // waits for the unit in slot c_slot; returns its address
+    uint32_t c_off = 0, c_bar = bar_s, c_par = 0;   // slot being consumed; parities of all slots (bit = slot)
+    uint32_t c_bit = 1;
+    // waits for the unit in the current slot; returns its address
     auto unit_wait = [&]() -> const uint8_t * {
-        bool ok = mbar_try_wait(&bar[c_slot], (c_par >> c_slot) & 1u);
-        if (!ok && !misc->dead) {
-            for (int it = 0; it < DS_SPIN_LIMIT && !ok; ++it) {
-                ok = mbar_try_wait(&bar[c_slot], (c_par >> c_slot) & 1u);
-                if (!ok && (it & 1023) == 1023 && misc->dead) break;
-            }
-            if (!ok && !misc->dead) { ds_give_up(p, misc, ERR_MBAR_TIMEOUT); f.mv = p.n_mv; }
+        if (!ds_try_wait(c_bar, (c_par & c_bit) ? 1u : 0u) && !warp_dead) {
+            bool ok = false;
+            for (int it = 0; it < DS_SPIN_LIMIT && !ok; ++it) ok = ds_try_wait(c_bar, (c_par & c_bit) ? 1u : 0u);
+            if (!ok) { ds_give_up(p, misc, ERR_MBAR_TIMEOUT); warp_dead = true; f.part = n_parts; }
         }
-        if (ok) { pending &= ~(1u << c_slot); c_par ^= 1u << c_slot; }
-        return ring + c_slot * DS_SLOT;
+        return ring + c_off;
     };
     // hands the slot back to the stream
     auto unit_done = [&]() {
-        c_slot = c_slot + 1 == DS_NSLOT ? 0 : c_slot + 1;
+        if (!warp_dead) { c_par ^= c_bit; ++n_done; }
+        c_off += DS_SLOT; c_bar += 8; c_bit <<= 1;
+        if (c_off == DS_NSLOT * DS_SLOT) { c_off = 0; c_bar = bar_s; c_bit = 1; }
         __syncwarp();
-        if (misc->dead) f.mv = p.n_mv;
         fetch_issue();
     };
 
-    for (int i = tid; i < DS_OP_BYTES / 16; i += DS_THREADS) ((uint4 *) s_op)[i] = __ldg((const uint4 *) p.ops + i);
-    __syncthreads();
+    DsCursor c;                                 // only part / g / g_end of it are used: the compute loop has its own nest
+    c.part = 0;
     int mv = 0;
     unsigned phase = 0;
 #pragma unroll 1
@@ -709,64 +808,73 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
         if (o.kind == DS_OP_MATVEC) {
             ds_matvec_input(o, acts, misc);
             if (stamp) p.timing[op * 4 + 1] = ds_now();
-            const DsMvDesc & d = descs[mv];
-            const int R = (d.mode & 2) ? 2 : 1;
-            const bool both = (d.mode & 4) != 0;
+            const int epilogue = o.epilogue;
 #pragma unroll 1
-            for (uint32_t g = gw; g < d.ngroups; g += G) {
-                float acc[2] = {0.0f, 0.0f};
-                int mat0; uint32_t row0;
-                ds_map(d, g, 0, mat0, row0);
-                // `both`: the two rows of the group share one slot, lanes [0, nb) take the first row, [nb, 2 nb) the second
-                const int nb = d.last_blk[mat0];
-                const int n_member = both ? 1 : R;
+            for (; c.part < n_parts && parts[c.part].phase == mv; ++c.part) {
+                if (!ds_cursor_enter(c, parts, gw, G)) continue;
+                const DsPart & P = parts[c.part];
+                const int type = P.type, nseg = P.nseg, seg_blk = P.seg_blk, last_blk = P.last_blk, mode = P.mode, mat = P.mat;
+                const uint32_t g_begin = P.g_begin, g_end = c.g_end;
+                const bool both = (mode & 4) != 0;
+                const int n_member = both ? 1 : ((mode & 2) ? 2 : 1);
+                float * const dst = o.dst[mat];
 #pragma unroll 1
-                for (int j = 0; j < n_member; ++j) {
-                    int mat; uint32_t row;
-                    ds_map(d, g, j, mat, row);
-                    const int type = d.type[mat], nseg = d.nseg[mat], seg_blk = d.seg_blk[mat];
-                    float a = 0.0f;
+                for (uint32_t g = c.g; g < g_end; g += G) {
+                    float acc0 = 0.0f, acc1 = 0.0f;
 #pragma unroll 1
-                    for (int s = 0; s < nseg; ++s) {
-                        const int nblk = s == nseg - 1 ? d.last_blk[mat] : seg_blk;
-                        const uint8_t * slot = unit_wait();
-                        const uint8_t * ap = acts + (size_t) s * seg_blk * DS_ACT_STRIDE;
-                        if (type == T_Q6_K) a += ds_dot_q6k(slot, nblk, ap, lane);
-                        else if (lane < (both ? 2 * nb : nblk)) {
-                            const uint8_t * al = ap + ((both && lane >= nb) ? lane - nb : lane) * DS_ACT_STRIDE;
-                            if (type == T_Q4_K) a += ds_dot_blk<T_Q4_K>(slot + lane * 144, al);
-                            else                a += ds_dot_blk<T_Q5_K>(slot + lane * 176, al);
-                        }
-                        unit_done();
-                    }
-                    if (both) { acc[0] = warp_sum(lane < nb ? a : 0.0f); acc[1] = warp_sum(lane < nb ? 0.0f : a); }
-                    else acc[j] = warp_sum(a);
-                }
-                if (lane == 0) {
-                    if (o.epilogue == DS_EP_STORE) {
-                        o.dst[mat0][row0] = acc[0];
-                        if (R == 2) o.dst[mat0][row0 + 1] = acc[1];
-                    } else if (o.epilogue == DS_EP_SILU_MUL) {
-                        const float sa = acc[0] / (1.0f + expf(-acc[0]));
-                        if (o.dst[0]) o.dst[0][g] = acc[0];
-                        if (o.dst[1]) o.dst[1][g] = acc[1];
-                        if (o.silu_out) o.silu_out[g] = sa;
-                        o.act_out[g] = sa * acc[1];
-                    } else {
-                        if (o.dst[mat0]) { o.dst[mat0][row0] = acc[0]; o.dst[mat0][row0 + 1] = acc[1]; }
-                        if (mat0 == 2) {
-                            ((__half2 *) misc->vc)[row0 >> 1] = __floats2half2_rn(acc[0], acc[1]);
-                        } else {
-                            const int ip = (int) (row0 % (uint32_t) o.head_dim) >> 1;
-                            float o0 = acc[0], o1 = acc[1];
-                            if (2 * ip < o.n_dims) {
-                                const float2 cs = misc->rope_cs[ip];
-                                o0 = acc[0] * cs.x - acc[1] * cs.y; o1 = acc[0] * cs.y + acc[1] * cs.x;
+                    for (int j = 0; j < n_member; ++j) {
+                        float a = 0.0f;
+#pragma unroll 1
+                        for (int sg = 0; sg < nseg; ++sg) {
+                            const int nblk = sg == nseg - 1 ? last_blk : seg_blk;
+                            const uint8_t * slot = unit_wait();
+                            const uint8_t * ap = acts + sg * seg_blk * DS_ACT_STRIDE;
+                            if (type == T_Q6_K) a += ds_dot_q6k(slot, nblk, ap, acts + DS_BS16_OFF + sg * seg_blk * 32, lane);
+                            else if (lane < (both ? 2 * nblk : nblk)) {
+                                // `both`: lanes [0, nblk) take the first row of the group, [nblk, 2 nblk) the second
+                                const uint8_t * al = ap + ((both && lane >= nblk) ? lane - nblk : lane) * DS_ACT_STRIDE;
+                                if (type == T_Q4_K) a += ds_dot_blk<T_Q4_K>(slot + lane * 144, al);
+                                else                a += ds_dot_blk<T_Q5_K>(slot + lane * 176, al);
                             }
-                            if (mat0 == 0) { o.q_rope[row0] = o0; o.q_rope[row0 + 1] = o1; }
-                            else {
-                                if (o.k_rope) { o.k_rope[row0] = o0; o.k_rope[row0 + 1] = o1; }
-                                ((__half2 *) misc->kc)[row0 >> 1] = __floats2half2_rn(o0, o1);
+                            unit_done();
+                        }
+                        if (both) {
+                            if (last_blk == 16) {           // halves of the warp: four butterfly steps, then lane 0 fetches the other half's sum
+                                a += __shfl_xor_sync(0xffffffffu, a, 8); a += __shfl_xor_sync(0xffffffffu, a, 4);
+                                a += __shfl_xor_sync(0xffffffffu, a, 2); a += __shfl_xor_sync(0xffffffffu, a, 1);
+                                acc0 = a; acc1 = __shfl_sync(0xffffffffu, a, 16);
+                            } else { acc0 = warp_sum(lane < last_blk ? a : 0.0f); acc1 = warp_sum(lane < last_blk ? 0.0f : a); }
+                        } else if (j == 0) acc0 = warp_sum(a);
+                        else acc1 = warp_sum(a);
+                    }
+                    if (lane == 0) {
+                        const uint32_t lg = g - g_begin;
+                        if (epilogue == DS_EP_STORE) {
+                            if (mode & 2) { dst[2 * lg] = acc0; dst[2 * lg + 1] = acc1; }
+                            else dst[lg] = acc0;
+                        } else if (epilogue == DS_EP_SILU_MUL) {
+                            const float sa = acc0 / (1.0f + expf(-acc0));
+                            if (o.dst[0]) o.dst[0][lg] = acc0;
+                            if (o.dst[1]) o.dst[1][lg] = acc1;
+                            if (o.silu_out) o.silu_out[lg] = sa;
+                            o.act_out[lg] = sa * acc1;
+                        } else {
+                            const uint32_t row0 = 2 * lg;
+                            if (dst) { dst[row0] = acc0; dst[row0 + 1] = acc1; }
+                            if (mat == 2) {
+                                ((__half2 *) misc->vc)[lg] = __floats2half2_rn(acc0, acc1);
+                            } else {
+                                const int ip = (int) (row0 % (uint32_t) o.head_dim) >> 1;
+                                float o0 = acc0, o1 = acc1;
+                                if (2 * ip < o.n_dims) {
+                                    const float2 cs = misc->rope_cs[ip];
+                                    o0 = acc0 * cs.x - acc1 * cs.y; o1 = acc0 * cs.y + acc1 * cs.x;
+                                }
+                                if (mat == 0) { o.q_rope[row0] = o0; o.q_rope[row0 + 1] = o1; }
+                                else {
+                                    if (o.k_rope) { o.k_rope[row0] = o0; o.k_rope[row0 + 1] = o1; }
+                                    ((__half2 *) misc->kc)[lg] = __floats2half2_rn(o0, o1);
+                                }
                             }
                         }
                     }
@@ -784,11 +892,12 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
     }
 
     // ---- drain: nothing may still be writing into this CTA's shared memory when it exits ----
-    for (int s = 0; s < DS_NSLOT; ++s) {
-        if (pending & (1u << s)) {
-            bool ok = false;
-            for (int it = 0; it < (1 << 20) && !ok; ++it) ok = mbar_try_wait(&bar[s], (c_par >> s) & 1u);
-        }
+    for (; n_done < n_fetched; ++n_done) {
+        bool ok = false;
+        for (int it = 0; it < (1 << 20) && !ok; ++it) ok = ds_try_wait(c_bar, (c_par & c_bit) ? 1u : 0u);
+        c_par ^= c_bit;
+        c_off += DS_SLOT; c_bar += 8; c_bit <<= 1;
+        if (c_off == DS_NSLOT * DS_SLOT) { c_off = 0; c_bar = bar_s; c_bit = 1; }
     }
     __syncthreads();
     if (tid == 0) {
@@ -814,64 +923,64 @@ bool decode_step_type_ok(int type, int64_t K, int64_t w_nb1, const void * W) {
     return true;
 }
 
-static size_t ds_smem_bytes(int n_mv) { return (size_t) DS_OFF_DESC + (size_t) n_mv * sizeof(DsMvDesc); }
+static size_t ds_smem_bytes(int n_parts) { return (size_t) DS_OFF_DESC + (size_t) n_parts * sizeof(DsPart); }
 
-int decode_step_max_matvecs(int) { return (int) ((DS_SMEM_LIMIT - DS_OFF_DESC) / sizeof(DsMvDesc)); }
+int decode_step_max_matvecs(int) { return (int) ((DS_SMEM_LIMIT - DS_OFF_DESC) / sizeof(DsPart) / 3); }
 
-size_t decode_step_work_bytes(int n_ops) { return (size_t) (n_ops > 0 ? n_ops : 1) * sizeof(DsMvDesc); }
+size_t decode_step_work_bytes(int n_ops) { return (size_t) (n_ops > 0 ? n_ops : 1) * 3 * sizeof(DsPart); }
 
-static int ds_count_mv(const DsOp * ops, int n_ops) {
-    int n = 0;
-    for (int i = 0; i < n_ops; ++i) if (ops[i].kind == DS_OP_MATVEC) ++n;
-    return n;
-}
-
-static bool ds_make_desc(const DsOp & o, DsMvDesc & d) {
-    memset(&d, 0, sizeof(d));
+// the parts of one mat-vec phase (at most three)
+static bool ds_make_parts(const DsOp & o, int phase, uint32_t grid_warps, std::vector<DsPart> & out) {
     const bool zip = o.epilogue == DS_EP_SILU_MUL;
     // plain results are computed two rows at a time as well when every matrix has an even number of rows
     bool pair = o.epilogue != DS_EP_STORE;
-    if (!pair) { pair = true; for (int i = 0; i < o.nmat; ++i) if (o.M[i] & 1) pair = false; }
-    d.mode = (uint8_t) ((zip ? 1 : 0) | (pair ? 2 : 0));
-    uint32_t total = 0;
-    for (int i = 0; i < 3; ++i) {
-        d.m_end[i] = 0xffffffffu;
-        if (i >= o.nmat) { d.type[i] = (uint8_t) o.type[0]; d.nseg[i] = 1; d.seg_blk[i] = d.last_blk[i] = 1; continue; }
-        if (!decode_step_type_ok(o.type[i], o.K, o.w_nb1[i], o.W[i]) || o.M[i] <= 0) return false;
-        if (pair && !zip && (o.M[i] & 1)) return false;
-        const int nblk = o.K / 256;
-        const int cap = o.type[i] == T_Q4_K ? 32 : (o.type[i] == T_Q5_K ? 24 : 16);       // super-blocks per ring slot
-        const int nseg = (nblk + cap - 1) / cap;
-        d.W[i] = (uint64_t) (uintptr_t) o.W[i]; d.nb1[i] = (uint32_t) o.w_nb1[i];
-        d.type[i] = (uint8_t) o.type[i]; d.nseg[i] = (uint8_t) nseg;
-        d.seg_blk[i] = (uint8_t) (nseg > 1 ? cap : nblk); d.last_blk[i] = (uint8_t) (nblk - (nseg - 1) * cap);
-        total += (uint32_t) o.M[i];
-        d.m_end[i] = total;
+    if (!pair) {
+        pair = true;
+        for (int i = 0; i < o.nmat; ++i) if ((o.M[i] & 1) || o.type[i] == T_Q6_K || o.K / 256 > (o.type[i] == T_Q4_K ? 16 : 12)) pair = false;   // only rows that share a slot
     }
-    for (int i = o.nmat; i < 3; ++i) d.m_end[i] = 0xffffffffu;
-    if (zip) { if (o.nmat != 2 || o.M[0] != o.M[1]) return false; d.ngroups = (uint32_t) o.M[0]; }
-    else d.ngroups = pair ? total / 2 : total;
-    // short rows of the one-lane-per-block types: both rows of a pair share a slot (every matrix the same type)
-    if (pair) {
-        bool both = true;
-        for (int i = 0; i < o.nmat; ++i) if (o.type[i] != o.type[0] || o.type[i] == T_Q6_K || o.K / 256 > 16 || (o.type[i] == T_Q5_K && o.K / 256 > 12)) both = false;
-        if (both) d.mode |= 4;
+    if (o.nmat < 1 || o.nmat > 3 || (zip && (o.nmat != 2 || o.M[0] != o.M[1]))) return false;
+    uint32_t g = 0;
+    for (int i = 0; i < (zip ? 1 : o.nmat); ++i) {
+        const int type = o.type[i];
+        if (!decode_step_type_ok(type, o.K, o.w_nb1[i], o.W[i]) || o.M[i] <= 0) return false;
+        if (zip && (!decode_step_type_ok(o.type[1], o.K, o.w_nb1[1], o.W[1]) || o.type[1] != type || o.w_nb1[1] != o.w_nb1[0])) return false;
+        if (pair && !zip && (o.M[i] & 1)) return false;
+        const int nblk = o.K / 256, bb = type == T_Q4_K ? 144 : (type == T_Q5_K ? 176 : 210);
+        const int cap = type == T_Q4_K ? 32 : (type == T_Q5_K ? 24 : 16);       // super-blocks per ring slot
+        const int nseg = (nblk + cap - 1) / cap;
+        DsPart P; memset(&P, 0, sizeof(P));
+        P.W0 = (uint64_t) (uintptr_t) o.W[i]; P.W1 = zip ? (uint64_t) (uintptr_t) o.W[1] : 0;
+        P.nb1 = (uint32_t) o.w_nb1[i];
+        P.g_begin = g; g += (uint32_t) (pair && !zip ? o.M[i] / 2 : o.M[i]); P.g_end = g;
+        P.first_mod = P.g_begin % grid_warps;
+        P.type = (uint8_t) type; P.nseg = (uint8_t) nseg;
+        P.seg_blk = (uint8_t) (nseg > 1 ? cap : nblk); P.last_blk = (uint8_t) (nblk - (nseg - 1) * cap);
+        P.seg_b = (uint16_t) (P.seg_blk * bb); P.last_b = (uint16_t) (P.last_blk * bb);
+        // short rows of the one-lane-per-block types: both rows of a pair share a ring slot
+        const bool both = pair && type != T_Q6_K && nblk <= (type == T_Q4_K ? 16 : 12);
+        P.mode = (uint8_t) ((zip ? 1 : 0) | (pair ? 2 : 0) | (both ? 4 : 0));
+        P.mat = (uint8_t) i; P.phase = (uint16_t) phase;
+        out.push_back(P);
     }
     return true;
 }
 
-cudaError_t decode_step_prepare(const DsOp * ops, int n_ops, void * work, cudaStream_t copy_stream) {
-    std::vector<DsMvDesc> descs;
+static bool ds_all_parts(const DsOp * ops, int n_ops, int sm_count, std::vector<DsPart> & parts) {
+    int phase = 0;
     for (int i = 0; i < n_ops; ++i) {
         if (ops[i].kind != DS_OP_MATVEC) continue;
-        DsMvDesc d;
-        if (!ds_make_desc(ops[i], d)) return cudaErrorInvalidValue;
-        descs.push_back(d);
+        if (!ds_make_parts(ops[i], phase++, (uint32_t) sm_count * DS_WARPS, parts)) return false;
     }
-    if (ds_smem_bytes((int) descs.size()) > (size_t) DS_SMEM_LIMIT) return cudaErrorInvalidValue;
-    if (descs.empty()) return cudaSuccess;
+    return phase < 65536;
+}
+
+cudaError_t decode_step_prepare(const DsOp * ops, int n_ops, int sm_count, void * work, cudaStream_t copy_stream) {
+    std::vector<DsPart> parts;
+    if (!ds_all_parts(ops, n_ops, sm_count, parts)) return cudaErrorInvalidValue;
+    if (ds_smem_bytes((int) parts.size()) > (size_t) DS_SMEM_LIMIT) return cudaErrorInvalidValue;
+    if (parts.empty()) return cudaSuccess;
     // synchronous with respect to the host buffer: the vector dies at return
-    cudaError_t e = cudaMemcpyAsync(work, descs.data(), descs.size() * sizeof(DsMvDesc), cudaMemcpyHostToDevice, copy_stream);
+    cudaError_t e = cudaMemcpyAsync(work, parts.data(), parts.size() * sizeof(DsPart), cudaMemcpyHostToDevice, copy_stream);
     if (e != cudaSuccess) return e;
     return cudaStreamSynchronize(copy_stream);
 }
@@ -880,9 +989,14 @@ cudaError_t launch_decode_step(const DsOp * ops_dev, const DsOp * ops, int n_ops
                                unsigned long long * timing) {
     DsParams p = {};
     p.ops = ops_dev; p.n_ops = n_ops;
-    p.descs = (const DsMvDesc *) work; p.n_mv = ds_count_mv(ops, n_ops);
+    p.parts = (const DsPart *) work;
+    {
+        std::vector<DsPart> parts;
+        if (!ds_all_parts(ops, n_ops, c.sm_count, parts)) return cudaErrorInvalidValue;
+        p.n_parts = (int) parts.size();
+    }
     p.sync = sync; p.status = c.status; p.timing = timing;
-    const size_t smem = ds_smem_bytes(p.n_mv);
+    const size_t smem = ds_smem_bytes(p.n_parts);
     if (smem > (size_t) DS_SMEM_LIMIT) return cudaErrorInvalidValue;
     static unsigned long long attr_mask = 0;
     if (!(attr_mask & (1ull << (c.device & 63)))) {

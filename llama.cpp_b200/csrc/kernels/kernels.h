@@ -127,6 +127,7 @@ struct RopeKvLaunch {
     void * k_cache; void * v_cache; int64_t k_off, v_off;        // view bases and byte offsets
     const int64_t * k_off_dev; const int64_t * v_off_dev;        // if set, offsets are read from device memory instead
     const int32_t * pos; const float * ff;
+    const char * pf_k; const char * pf_v; int64_t pf_bytes;   // optional: this layer's K / V rows, to be brought into L2 ahead of the attention phase
 };
 cudaError_t launch_rope_kv(const RopeKvLaunch & l, const RopeParams & rp, const LaunchCtx & c);
 
@@ -147,7 +148,7 @@ cudaError_t launch_soft_max(const TensorD & src, const TensorD * mask, const Ten
 // grid-wide barriers, and every warp keeps streaming the weights of the phases ahead into its own
 // shared-memory ring while it waits.
 enum { DS_OP_MATVEC = 1, DS_OP_ATTN = 2 };
-enum { DS_IN_PLAIN = 0, DS_IN_NORM = 1 };                       // mat-vec input: x, or rms_norm(x) * w
+enum { DS_IN_PLAIN = 0, DS_IN_NORM = 1, DS_IN_ATTN = 2 };       // mat-vec input: x, rms_norm(x) * w, or attention partials to merge
 enum { DS_EP_STORE = 0, DS_EP_ROPE_KV = 1, DS_EP_SILU_MUL = 2 }; // what happens to the mat-vec results
 struct alignas(16) DsOp {
     int kind;
@@ -156,6 +157,7 @@ struct alignas(16) DsOp {
     const float * in0; const float * in1;        // x = in0 (+ in1 when set)
     const float * norm_w; float eps;             // DS_IN_NORM
     float * sum_out;                             // receives x when in1 is set
+    int in_slices, in_gqa;                       // DS_IN_ATTN: in0 = partials of the attention phase [n_head_kv][in_slices][in_gqa][DS partial stride]
     float * y_out;                               // optional: receives the (normalised) mat-vec input
     const void * W[3]; int type[3]; int M[3]; int64_t w_nb1[3];
     float * dst[3];                              // DS_EP_STORE: results; other epilogues: optional raw results
@@ -164,6 +166,7 @@ struct alignas(16) DsOp {
     void * k_cache; void * v_cache;              // viewed cache tensors; rows go to base + offset as F16
     int64_t k_off, v_off; const int64_t * k_off_dev; const int64_t * v_off_dev;   // byte offsets: immediate, or read from device memory
     const int32_t * pos; const float * ff;
+    const char * pf_k; const char * pf_v; int64_t pf_bytes;   // optional: this layer's K / V rows, to be brought into L2 ahead of the attention phase
     int head_dim, n_dims; float freq_scale, ext_factor, attn_factor, theta_scale, corr0, corr1;
     // DS_EP_SILU_MUL: matrices gate, up
     float * act_out; float * silu_out;           // silu(gate) * up (required), silu(gate) (optional)
@@ -175,7 +178,10 @@ struct alignas(16) DsOp {
     float * partials; unsigned * tickets;        // split-KV partial results and per-KV-head counters (zero between uses)
     float * out;                                 // [n_head][128]
     int n_slices, kv_per_slice;
+    int consumer_merge;                          // the slices are merged by the input stage of the next phase (DS_IN_ATTN), not here
 };
+static constexpr int DS_MAX_MERGE_SLICES = 16;   // most KV slices the input stage of the next phase merges (consumer_merge)
+static constexpr int DS_PARTIAL_STRIDE = 132;    // floats per (KV head, slice, query row) partial: O[128], max, sum, padding
 bool        decode_step_type_ok(int type, int64_t K, int64_t w_nb1, const void * W);
 // How many mat-vec ops one launch can hold (their descriptors live in shared memory), given the largest K
 int         decode_step_max_matvecs(int device);
@@ -183,7 +189,7 @@ int64_t     decode_step_max_k();
 // `ops` (host copy) describes the same ops as `ops_dev`; `work` is device memory of decode_step_work_bytes(n_ops)
 // that this call fills (asynchronously, on `copy_stream`) with the mat-vec descriptors; sync: 4 zero words
 size_t      decode_step_work_bytes(int n_ops);
-cudaError_t decode_step_prepare(const DsOp * ops, int n_ops, void * work, cudaStream_t copy_stream);
+cudaError_t decode_step_prepare(const DsOp * ops, int n_ops, int sm_count, void * work, cudaStream_t copy_stream);
 cudaError_t launch_decode_step(const DsOp * ops_dev, const DsOp * ops, int n_ops, const void * work, unsigned * sync, const LaunchCtx & c,
                                unsigned long long * timing = nullptr);   // optional: 4 time stamps per phase written by CTA 0
 

@@ -93,9 +93,10 @@ def test_qkv_rope_phase(b200, oracle, qt_v, pos, n_dims, ff):
     assert oracle.nmse(want_v, vv.astype(np.float32)) <= NMSE_MM + 1e-6
 
 
-@pytest.mark.parametrize("n_kv,n_slices", [(256, 1), (256, 2), (768, 4), (4096, 18), (1000, 3)])
+@pytest.mark.parametrize("n_kv,n_slices,next_merges", [(256, 1, False), (256, 2, False), (256, 2, True), (768, 4, True), (4096, 18, False),
+                                                       (1000, 3, False), (2048, 8, True), (768, 12, True), (1024, 16, True)])
 @pytest.mark.parametrize("n_head,n_head_kv", [(32, 8), (16, 2)])
-def test_attention_phase(b200, oracle, n_kv, n_slices, n_head, n_head_kv):
+def test_attention_phase(b200, oracle, n_kv, n_slices, next_merges, n_head, n_head_kv):
     rng = np.random.default_rng(n_kv + n_slices)
     q = rng.standard_normal((n_head, 128)).astype(np.float32)
     k = rng.standard_normal((n_head_kv, n_kv, 128)).astype(np.float16)
@@ -103,7 +104,7 @@ def test_attention_phase(b200, oracle, n_kv, n_slices, n_head, n_head_kv):
     n_valid = n_kv - 37                                           # causal: the tail of the padded cache is masked out
     mask = np.zeros(n_kv, dtype=np.float16); mask[n_valid:] = -np.inf
     scale = 1.0 / np.sqrt(128.0)
-    got = b200.decode_step_attention(q, k, v, mask, scale, n_slices)
+    got = b200.decode_step_attention(q, k, v, mask, scale, n_slices, merge_in_next_phase=next_merges)
     # exact attention in float64
     kq = np.einsum("hd,hkd->hk", q.astype(np.float64), np.repeat(k, n_head // n_head_kv, axis=0).astype(np.float64)) * scale
     kq[:, n_valid:] = -np.inf

@@ -356,6 +356,9 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t dev, const char * /*pa
     ctx->use_mega = getenv("GGML_B200_MEGA") ? atoi(getenv("GGML_B200_MEGA")) : 1;
     if (getenv("GGML_B200_MEGA_MAX_BLOCKS")) ctx->mega_max_blocks = atoi(getenv("GGML_B200_MEGA_MAX_BLOCKS"));
     if (ctx->mega_max_blocks < 1) ctx->mega_max_blocks = 1;
+    if (getenv("GGML_B200_MEGA_KEYS")) ctx->mega_keys_per_slice = atoi(getenv("GGML_B200_MEGA_KEYS"));
+    if (ctx->mega_keys_per_slice < 16) ctx->mega_keys_per_slice = 16;
+    if (getenv("GGML_B200_MEGA_CMERGE")) ctx->mega_consumer_merge = atoi(getenv("GGML_B200_MEGA_CMERGE"));
     ctx->mega_timing = getenv("GGML_B200_MEGA_TIMING") ? atoi(getenv("GGML_B200_MEGA_TIMING")) : 0;
     const char * pdl = getenv("GGML_B200_PDL");
     ctx->use_pdl = pdl ? atoi(pdl) : 1;

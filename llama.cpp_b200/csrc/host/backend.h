@@ -80,6 +80,8 @@ struct BackendCtx {
     int          mega_max_blocks = 1 << 30;   // GGML_B200_MEGA_MAX_BLOCKS: cut the persistent launch after this many blocks (debugging aid)
     int          mega_ops_used = 0;        // per graph_compute call: phases already placed in the arena's parameter region
     int          mega_timing = 0, mega_last_ops = 0;
+    int          mega_keys_per_slice = 128; // GGML_B200_MEGA_KEYS: keys of the KV cache per attention work item
+    int          mega_consumer_merge = 16;  // GGML_B200_MEGA_CMERGE: up to this many KV slices are merged by the next phase's input stage
     bool         mega_tried = false;       // per graph_compute call: a failed match is not retried at every node
     void *       mega_arena = nullptr;
     cudaStream_t mega_copy_stream = nullptr;

@@ -423,15 +423,14 @@ int try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i) {
             a.mask = mask ? mask->data : nullptr;
             a.n_kv = (int) K->ne[1]; a.n_head = (int) rq->ne[1]; a.n_head_kv = (int) K->ne[2];
             a.scale = op_param_f32(b.fa, 0);
-            int slices = (a.n_kv + 63) / 64;                                // 4 keys per warp: short contexts are latency, not bandwidth
-            if (slices > DS_MAX_MERGE_SLICES && a.n_kv <= 4096) slices = DS_MAX_MERGE_SLICES;
+            int slices = (a.n_kv + ctx->mega_keys_per_slice - 1) / ctx->mega_keys_per_slice;     // short contexts are latency, not bandwidth: few keys per warp
             const int max_slices = lc.sm_count / a.n_head_kv;
             if (slices > max_slices) slices = max_slices;
             if (slices < 1) slices = 1;
             a.n_slices = slices; a.kv_per_slice = (a.n_kv + slices - 1) / slices;
             a.partials = (float *) (arena + MEGA_OFF_PARTIALS); a.tickets = (unsigned *) (arena + MEGA_OFF_TICKETS);
             const size_t pn = (size_t) a.n_head_kv * slices * (size_t) (a.n_head / a.n_head_kv) * DS_PARTIAL_STRIDE * 4;
-            a.consumer_merge = slices > 1 && slices <= DS_MAX_MERGE_SLICES;                   // few slices: the wo phase merges them while it builds its input
+            a.consumer_merge = slices > 1 && slices <= ctx->mega_consumer_merge && slices <= DS_MAX_MERGE_SLICES;                   // few slices: the wo phase merges them while it builds its input
             if (pn > partial_need) partial_need = pn;
             a.out = place(b.fa, vec[V_AO]);
             ops.push_back(a);
@@ -535,11 +534,6 @@ void decode_step_print_timing(BackendCtx * ctx) {
     std::vector<unsigned long long> t((size_t) ctx->mega_last_ops * 4);
     if (cudaMemcpy(t.data(), (char *) ctx->mega_arena + MEGA_OFF_TIMING, t.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return; }
     fprintf(stderr, "ggml-b200: persistent decode step, per phase (ns, CTA 0): start-of-phase offset | input stage | rows | barrier\n");
-    {
-        unsigned long long a[8];
-        if (cudaMemcpy(a, (char *) ctx->mega_arena + MEGA_OFF_TIMING + 4000 * 8, sizeof(a), cudaMemcpyDeviceToHost) == cudaSuccess)
-            fprintf(stderr, "  attention (last): q %llu | keys %llu | merge %llu | fence %llu | ticket %llu\n", a[1] - a[0], a[2] - a[1], a[3] - a[2], a[4] - a[3], a[5] - a[4]);
-    }
     for (int i = 0; i < ctx->mega_last_ops; ++i) {
         const unsigned long long * q = &t[(size_t) i * 4];
         fprintf(stderr, "  phase %3d  +%8llu | %6llu | %6llu | %6llu\n", i, q[0] - t[0], q[1] - q[0], q[2] - q[1], q[3] - q[2]);

@@ -507,9 +507,7 @@ __device__ __forceinline__ void ds_cursor_advance(DsCursor & c, const DsPart * p
 // ---------------------------------------------------------------------------
 // attention phase (one query token, head size 128, F16 K/V), after fattn_dec.cu
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, DsMisc * misc, unsigned long long * dbg) {
-#define DBG(k) do { if (dbg && blockIdx.x == 0 && threadIdx.x == 0) dbg[k] = ds_now(); } while (0)
-    DBG(0);
+__device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, DsMisc * misc) {
     constexpr int D = 128, RT = 4, CH = 4, KU = CH / 4, DPL = 4;
     float (*qs)[D] = (float (*)[D]) scratch;                                     // [RT][D]
     float * ps_all = (float *) (scratch + RT * D * 4);                           // [DS_WARPS][CH][RT]
@@ -542,7 +540,6 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
                 qs[rr][d] = r < gqa ? __ldcg(o.q + (int64_t) (hk * gqa + r) * D + d) : 0.0f;
             }
             __syncthreads();
-            DBG(1);
 
             const int sub = lane & 7, kq = lane >> 3;
             float m_run[RT], l_part[RT], oacc[RT][DPL];
@@ -656,7 +653,6 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
                 }
                 __syncwarp();
             }
-            DBG(2);
             // ---- merge the warps of the CTA ----
 #pragma unroll
             for (int rr = 0; rr < RT; ++rr) {
@@ -687,15 +683,12 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
             }
         }
 
-        DBG(3);
         if (o.n_slices > 1 && !o.consumer_merge) {
             // ---- the last CTA of this KV head merges the slices, in slice order ----
             __threadfence();
             __syncthreads();
-            DBG(4);
             if (threadIdx.x == 0) misc->ticket = atomicAdd(&o.tickets[hk], 1u);
             __syncthreads();
-            DBG(5);
             if (misc->ticket == (unsigned) o.n_slices - 1) {
                 __threadfence();
                 const float * base = o.partials + (int64_t) hk * o.n_slices * gqa * DS_PSTRIDE;
@@ -883,7 +876,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
             ++mv;
         } else if (o.kind == DS_OP_ATTN) {
             if (stamp) p.timing[op * 4 + 1] = ds_now();
-            ds_attention(o, acts, misc, p.timing ? p.timing + 4000 : nullptr);
+            ds_attention(o, acts, misc);
         }
         if (carries) ((uint4 *) (s_op + ((op + 1) & 1)))[tid] = next_op;
         if (stamp) p.timing[op * 4 + 2] = ds_now();

@@ -2,21 +2,26 @@
 """Benchmark: Llama-3-8B architecture, Q4_K_M, pp512 + tg128 per step, through the B200 ggml backend.
 
 One step = what one repetition of the reference's llama-bench does (examples/llama-bench/llama-bench.cpp:
-1430-1468): a 512-token prompt evaluated as one batch at an empty KV cache, then 128 single-token decodes.
-Weights are random-init (seeded N(0, 0.02), quantized to the Q4_K_M tensor-type mixture); token ids are
-uniform random, as llama-bench feeds them.  The model (4.6 GB of weights) is far larger than L2, so every
-timed token re-reads it from HBM; no L2 flush is needed.
+1430-1468): a 512-token prompt evaluated as one batch at an empty KV cache, then 128 single-token decodes
+(here they continue from the prompt, i.e. at KV positions 512..639; llama-bench's own tg test starts from an
+empty cache).  Weights are random-init (seeded N(0, 0.02), quantized to the Q4_K_M tensor-type mixture); token
+ids are uniform random, as llama-bench feeds them.  The model (4.6 GB of weights) is far larger than L2, so
+every timed token re-reads it from HBM; no L2 flush is needed.
 
   value      tg128 tokens/s from the device time of graph_compute (CUDA events on the backend's stream;
              inputs already resident), summed over the 128 decodes of each timed step
   e2e        the same tokens/s by host clock around the driver's decode call: token ids and mask copied
              host->device, logits copied device->host, every token
-  roofline   the decode mat-vec kernel alone, launched through the flat C-ABI over every weight matrix of
-             the model in order (cold L2), bracketed by CUDA events: algorithmic bytes / duration
+  roofline   the persistent decode-step kernel (one launch per token): weight bytes + attended K/V bytes of a
+             token over the CUDA-event time of the token's graph, against the measured HBM copy bandwidth
+  llama_bench  the reference's own, unmodified llama-bench + libllama driving the plugin on the same
+             architecture (a GGUF written by llama.cpp_b200/gguf_synth.py): the number a user of the drop-in gets
   cpu_baseline  the reference's ggml CPU backend (oracle/_ref) running the same graph on the same weights
-             on a bounded sample (pp128 + tg16), all host cores
+             on a bounded sample (pp128 + tg16), one thread per physical core
 
-`--impl reference` times only the reference CPU backend on the bounded sample and prints the same line.
+`--impl reference` runs the stock reference path alone: oracle/_ref/llama-bench -ngl 0 (the reference's CPU
+backend, its own graph builder and scheduler) at pp512 + tg128 on a GGUF of the same architecture, one thread
+per physical core; it neither loads this repository's library nor touches a GPU.
 """
 from __future__ import annotations
 
@@ -37,8 +42,12 @@ sys.path.insert(0, str(ROOT))
 import __graft_entry__ as entry  # noqa: E402
 
 N_PROMPT, N_GEN = 512, 128
+LLAMA3_8B = dict(n_layer=32, n_embd=4096, n_head=32, n_head_kv=8, n_ff=14336, n_vocab=128256, rope_theta=500000.0, rms_eps=1e-5)
+LLAMA3_70B = dict(n_layer=80, n_embd=8192, n_head=64, n_head_kv=8, n_ff=28672, n_vocab=128256, rope_theta=500000.0, rms_eps=1e-5)
 CPU_PROMPT, CPU_GEN = 128, 16
-DRAM_TRAFFIC_RATIO = 1.001      # measured DRAM bytes / algorithmic bytes of the mat-vec kernels (ncu, see profiles/)
+# DRAM bytes moved per algorithmic byte by the decode-step kernel, from an ncu capture (dram__bytes_read.sum +
+# dram__bytes_write.sum) of an 8-layer model with the same layer shapes; traffic grows with the number of layers
+DRAM_TRAFFIC_RATIO = 1.02
 METRIC = "llama3-8b-q4_k_m tg128 tokens/s (pp512+tg128 per step)"   # --model 70b replaces the model name
 
 
@@ -52,6 +61,60 @@ def measured_peaks():
         d = json.loads(p.read_text())
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def physical_cores() -> int:
+    """Cores x sockets as lscpu reports them (hyper-threads do not count); falls back to the logical CPU count."""
+    try:
+        out = subprocess.run(["lscpu"], capture_output=True, text=True, timeout=10).stdout
+        f = {l.split(":")[0].strip(): l.split(":")[1].strip() for l in out.splitlines() if ":" in l}
+        n = int(f["Core(s) per socket"]) * int(f["Socket(s)"])
+        if n > 0:
+            return min(n, os.cpu_count() or n)
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+REF_DIR = ROOT / "oracle" / "_ref"
+
+
+def synth_gguf(arch_name: str, arch: dict, device: str, share_layers: bool) -> Path:
+    """The synthetic model as a GGUF file under the system's temporary directory (written once per machine)."""
+    import tempfile
+    from llama_cpp_b200 import gguf_synth
+    path = Path(tempfile.gettempdir()) / f"b200-bench-llama3-{arch_name}-q4_k_m{'-shared' if share_layers else ''}.gguf"
+    if not path.exists():
+        t0 = time.time()
+        tmp = path.with_suffix(".part")
+        n = gguf_synth.write_llama_gguf(tmp, arch, device=device, share_layers=share_layers)
+        tmp.rename(path)
+        log(f"[bench] wrote {path} ({n / 1e9:.2f} GB) in {time.time() - t0:.1f} s")
+    return path
+
+
+def run_llama_bench(gguf: Path, n_prompt: int, n_gen: int, reps: int, keep: int, plugin: bool, threads: int):
+    """The reference's llama-bench (built unmodified by oracle/ref.mk).  Runs `reps` repetitions after llama-bench's own
+    warm-up run and averages the last `keep`.  Returns {"pp": tokens/s, "tg": tokens/s} or raises."""
+    exe = REF_DIR / "llama-bench"
+    if not exe.exists():
+        raise RuntimeError("oracle/_ref/llama-bench is not built (make -f oracle/ref.mk all)")
+    env = {k: v for k, v in os.environ.items() if k != "GGML_BACKEND_PATH"}
+    cmd = [str(exe), "-m", str(gguf), "-p", str(n_prompt), "-n", str(n_gen), "-fa", "1", "-r", str(reps), "-o", "json"]
+    if plugin:
+        env["GGML_BACKEND_PATH"] = str(ROOT / "llama.cpp_b200" / "lib" / "libggml-b200.so")
+        cmd += ["-ngl", "99"]
+    else:
+        cmd += ["-ngl", "0", "-t", str(threads)]
+    r = subprocess.run(cmd, cwd=REF_DIR, env=env, capture_output=True, text=True, timeout=3000)
+    if r.returncode != 0:
+        raise RuntimeError(f"llama-bench failed: {(r.stdout + r.stderr)[-500:]}")
+    out = {}
+    for t in json.loads(r.stdout):
+        ts = t["samples_ts"][-keep:]
+        out["pp" if t["n_prompt"] else "tg"] = float(np.mean(ts))
+        out["backends"] = t.get("backends")
+    return out
 
 
 class ClockSampler:
@@ -228,7 +291,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--n-prompt", type=int, default=512, help="prompt tokens per step (smaller only for profiler captures)")
     ap.add_argument("--n-gen", type=int, default=128, help="generated tokens per step (smaller only for profiler captures)")
-    ap.add_argument("--no-roofline", action="store_true", help="skip the separate mat-vec roofline pass (profiler captures)")
+    ap.add_argument("--no-roofline", action="store_true", help="skip the separate per-op mat-vec pass (profiler captures)")
+    ap.add_argument("--no-llama-bench", action="store_true", help="skip the run of the reference's llama-bench on the plugin")
     ap.add_argument("--model", default="8b", choices=["8b", "70b"],
                     help="8b: the configuration the metric is quoted on; 70b: the row-split parity configuration (no CPU baseline)")
     args = ap.parse_args()
@@ -237,32 +301,39 @@ def main():
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    pkg = entry.load_package()   # registers the package under the alias llama_cpp_b200
-    from llama_cpp_b200 import llama
-    arch = dict(llama.LLAMA3_8B if args.model == "8b" else llama.LLAMA3_70B)
-    cores = os.cpu_count() or 1
+    arch = dict(LLAMA3_8B if args.model == "8b" else LLAMA3_70B)
+    cores = physical_cores()
     rng = np.random.default_rng(1234)
     tokens = rng.integers(0, arch["n_vocab"], N_PROMPT + N_GEN).astype(np.int32)
-    config = {"workload": f"llama3-{args.model}-arch q4_k_m pp512+tg128 (BASELINE configs[{3 if args.model == '8b' else 4}])", "n_prompt": N_PROMPT, "n_gen": N_GEN,
+    config = {"workload": f"llama3-{args.model}-arch q4_k_m pp512+tg128, random-init weights, uniform-random token ids", "n_prompt": N_PROMPT, "n_gen": N_GEN,
               "flash_attn": True, "kv_type": "f16", "l2": "every token re-reads all weights (4.6 GB for 8b, 42 GB for 70b) >> L2, no flush needed"}
 
     if args.impl == "reference":
         if rank != 0:
             return
-        import torch
-        m = cpu_model(arch, cores)
-        fill_weights([m], "cuda" if torch.cuda.is_available() else "cpu")
-        pp_tps, tg_tps, step_s = time_cpu(m, tokens, args.steps, min(args.warmup, 1))
-        m.close()
-        sample = f"pp{CPU_PROMPT}+tg{CPU_GEN} per step on the reference ggml CPU backend, {cores} threads"
-        emit(json.dumps({"impl": "reference", "metric": METRIC, "value": tg_tps, "unit": "tokens/s", "n_gpus": args.gpus,
-                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
-                          "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4/6 dot, f32 accumulate", "data": "synthetic",
-                          "config": dict(config, sample=sample), "pp_tokens_per_s": pp_tps,
-                          "cpu_baseline": {"value": tg_tps, "unit": "tokens/s", "cores": cores, "kind": "reference", "sample": sample},
-                          "e2e": {"value": tg_tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        entry.load_package()                           # the Python package only (synthetic weights, GGUF writer): the CUDA library is never opened here
+        try:
+            gguf = synth_gguf(args.model, arch, "cpu", share_layers=True)
+            warm = max(args.warmup, 1)
+            t0 = time.perf_counter()
+            res = run_llama_bench(gguf, N_PROMPT, N_GEN, reps=args.steps + warm - 1, keep=args.steps, plugin=False, threads=cores)
+            wall = time.perf_counter() - t0
+        except Exception as e:
+            emit(json.dumps({"impl": "reference", "unavailable": f"the reference's llama-bench could not be run here: {e}"[:300]}))
+            return
+        sample = (f"oracle/_ref/llama-bench -ngl 0 -fa 1 -t {cores} -p {N_PROMPT} -n {N_GEN}: the reference's CPU backend, {cores} threads "
+                  f"(one per physical core), last {args.steps} of {args.steps + warm - 1} repetitions after llama-bench's own warm-up run; "
+                  "synthetic GGUF of the same architecture whose layers share one set of random weights")
+        emit(json.dumps({"impl": "reference", "metric": METRIC.replace("8b", args.model), "value": res["tg"], "unit": "tokens/s", "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": warm, "ms_per_step": (N_PROMPT / res["pp"] + N_GEN / res["tg"]) * 1e3,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4/6 dot, f32 accumulate",
+                          "data": "synthetic", "config": config, "pp512_tokens_per_s": res["pp"], "tg128_tokens_per_s": res["tg"], "wall_s": wall,
+                          "cpu_baseline": {"value": res["tg"], "unit": "tokens/s", "cores": cores, "kind": "reference", "sample": sample},
+                          "e2e": {"value": res["tg"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
+    pkg = entry.load_package()   # registers the package under the alias llama_cpp_b200
+    from llama_cpp_b200 import llama
     import torch
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if pkg.device_count() <= local:
@@ -319,6 +390,10 @@ def main():
     launches = m.launch_count - launches0
     # the slowest rank sets the job's time (device times by CUDA events on each rank's stream)
     pp_wall, tg_wall, pp_dev, tg_dev, wall = max_over_ranks(pp_wall, tg_wall, pp_dev, tg_dev, wall)
+    l_a = m.launch_count
+    m.decode(tokens[N_PROMPT:N_PROMPT + 1], N_PROMPT, want_logits=False)
+    launches_per_token = m.launch_count - l_a
+    nodes_per_token = m.last_n_nodes
     logits = m.decode(tokens[:8], 0).copy()
     assert np.isfinite(logits).all(), "non-finite logits"
 
@@ -333,19 +408,40 @@ def main():
         dist.destroy_process_group()
         return
     peak, peak_kind = measured_peaks()
-    algo, gemv_ms, n_mats = (0, 1.0, 1) if args.no_roofline else gemv_roofline(pkg, m, torch)
-    achieved = algo / (gemv_ms / 1e3) / 1e9
-    # DRAM bytes per launch: ncu measured 33,049,344 B read + 0 written for the 33,103,872 algorithmic bytes of the
-    # Q4_K 4096x14336 case (profiles/mmvq_k_q4k_4096x14336_n1.md) and 431.0 + 4.3 MB for 431.5 MB (Q6_K output matrix);
-    # traffic grows in proportion to the matrix, so the average launch of the pass is scaled by that ratio
-    traffic = None if args.no_roofline else algo / n_mats * DRAM_TRAFFIC_RATIO
-    roofline = {"bound": "hbm", "kernel": "mmvq_k_kernel / mmvq_q6k_kernel (decode mat-vec, all weight matrices of the model in graph order)",
-                "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
-                "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "traffic_unit": "DRAM bytes per launch (average matrix, scaled from ncu)",
-                "bytes_per_launch": algo / n_mats, "us_per_launch": gemv_ms * 1e3 / n_mats, "launches_per_pass": n_mats,
-                "algorithmic_bytes_per_pass": algo, "ms_per_pass": gemv_ms,
+    # The dominant kernel is the persistent decode step: one launch per token that reads every weight matrix once and
+    # the attended part of the KV cache.  Its duration is the CUDA-event time of the token's graph on the backend's
+    # stream (the graph also holds the token's embedding-row gather and the mask cast: two launches, < 1 % of the time).
+    n_embd_kv = arch["n_embd"] // arch["n_head"] * arch["n_head_kv"]
+    kv_bytes = sum(2 * 2 * n_embd_kv * (N_PROMPT + i + 1) for i in range(N_GEN)) / N_GEN * arch["n_layer"]     # K and V rows up to the token, F16
+    bytes_per_token = m.weight_bytes + kv_bytes
+    ms_per_token = tg_dev / n_tg
+    achieved = bytes_per_token / (ms_per_token / 1e3) / 1e9
+    persistent = launches_per_token <= 16
+    roofline = {"bound": "hbm",
+                "kernel": ("decode_step_kernel (one persistent launch per token: all layers' mat-vecs, norms, rope, KV store, attention)" if persistent
+                           else "the token's graph of per-op kernels (mmvq_*, fattn_dec, glue)"),
+                "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": bytes_per_token * DRAM_TRAFFIC_RATIO if persistent else None,
+                "traffic_unit": "DRAM bytes per launch (ncu capture of an 8-layer model of the same layer shapes, scaled by layers)",
+                "bytes_per_launch": bytes_per_token, "weight_bytes_per_token": m.weight_bytes, "kv_bytes_per_token": kv_bytes,
+                "us_per_launch": ms_per_token * 1e3, "launches_per_token": launches_per_token,
                 "whole_decode_step": {"weight_bytes_per_token_per_gpu": m.weight_bytes, "achieved_gbs_per_gpu": m.weight_bytes * tg_tps_dev / 1e9,
                                       "frac": m.weight_bytes * tg_tps_dev / 1e9 / peak}}
+    if not args.no_roofline:
+        algo, gemv_ms, n_mats = gemv_roofline(pkg, m, torch)
+        roofline["per_op_mat_vec_kernels"] = {"what": "the one-kernel-per-op decode mat-vec (mmvq_k / mmvq_q6k), every weight matrix in graph order, cold L2",
+                                              "achieved": algo / (gemv_ms / 1e3) / 1e9, "frac": algo / (gemv_ms / 1e3) / 1e9 / peak,
+                                              "launches_per_pass": n_mats, "ms_per_pass": gemv_ms}
+    # the drop-in path: the reference's own llama-bench + libllama on the plugin, same architecture
+    llama_bench = None
+    if world == 1 and args.model == "8b" and not args.no_llama_bench:
+        try:
+            gguf = synth_gguf(args.model, arch, "cuda", share_layers=False)
+            lb = run_llama_bench(gguf, N_PROMPT, N_GEN, reps=3, keep=3, plugin=True, threads=cores)
+            llama_bench = {"pp512_tokens_per_s": lb["pp"], "tg128_tokens_per_s": lb["tg"], "backends": lb.get("backends"),
+                           "command": "oracle/_ref/llama-bench -p 512 -n 128 -fa 1 -ngl 99 -r 3 with GGML_BACKEND_PATH=libggml-b200.so"}
+        except Exception as e:
+            log(f"[bench] llama-bench through the plugin unavailable: {e}")
     cpu_baseline = None
     if cpu is not None:
         c_pp, c_tg, _ = time_cpu(cpu, tokens, 1, 1)
@@ -362,7 +458,8 @@ def main():
            "dtype": "int8 x int4/6 dot, f32 accumulate", "data": "synthetic", "config": config,
            "pp512_tokens_per_s": pp_tps_dev, "tg128_tokens_per_s": tg_tps_dev,
            "e2e": {"value": tg_tps_e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "pp512_tokens_per_s": pp_tps_e2e},
-           "gpu_launches": launches * world, "graph_nodes_per_token": m.last_n_nodes, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline}
+           "gpu_launches": launches * world, "launches_per_token": launches_per_token, "graph_nodes_per_token": nodes_per_token, "clocks": clocks,
+           "roofline": roofline, "llama_bench": llama_bench, "cpu_baseline": cpu_baseline}
     if dist is not None:
         sync_all()
     m.close()

@@ -181,7 +181,7 @@ BackendCtx::ActEntry * BackendCtx::act_cache_find(const void * src_data, int64_t
     return nullptr;
 }
 BackendCtx::ActEntry * BackendCtx::act_cache_take(const void * src_data, int64_t K, int64_t ncols) {
-    act_cache_invalidate(src_data);
+    act_cache_invalidate(src_data, (size_t) K * (size_t) ncols * 4);
     ActEntry & e = act_cache[act_next];
     act_next ^= 1;
     const size_t need = act128_bytes(K, ncols);
@@ -195,7 +195,7 @@ BackendCtx::ActEntry * BackendCtx::act_cache_take(const void * src_data, int64_t
         e.cap = cap;
         scratch_generation++;
     }
-    e.src_data = src_data; e.K = K; e.ncols = ncols;
+    e.src_data = src_data; e.K = K; e.ncols = ncols; e.src_bytes = (size_t) K * (size_t) ncols * 4;
     return &e;
 }
 

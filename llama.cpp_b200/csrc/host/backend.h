@@ -48,14 +48,20 @@ struct BackendCtx {
     // int8 activation blocks of recent MUL_MAT inputs, so that mat-muls sharing an input (wq/wk/wv,
     // gate/up) quantize it once and producers (rms_norm*w, silu*up) can emit it directly; valid only
     // within one graph_compute call
-    struct ActEntry { const void * src_data = nullptr; int64_t K = 0, ncols = 0; void * q = nullptr; size_t cap = 0; };
+    struct ActEntry { const void * src_data = nullptr; int64_t K = 0, ncols = 0; void * q = nullptr; size_t cap = 0; size_t src_bytes = 0; };
     ActEntry     act_cache[2];
     int          act_next = 0;
     // F16 copy of the activations of the most recent tensor-core MUL_MAT (q/k/v and gate/up convert once)
-    void *       tc_xh = nullptr; size_t tc_xh_cap = 0; const void * tc_x_data = nullptr; int64_t tc_x_k = 0, tc_x_n = 0;
+    void *       tc_xh = nullptr; size_t tc_xh_cap = 0; const void * tc_x_data = nullptr; int64_t tc_x_k = 0, tc_x_n = 0; size_t tc_x_bytes = 0;
     void         act_cache_clear() { act_cache[0].src_data = act_cache[1].src_data = nullptr; tc_x_data = nullptr; }
-    // a node that writes memory starting at `data` makes blocks quantized from the old contents stale
-    void         act_cache_invalidate(const void * data) { for (ActEntry & e : act_cache) if (e.src_data == data) e.src_data = nullptr; if (tc_x_data == data) tc_x_data = nullptr; }
+    // a node that writes the bytes [data, data + bytes) makes conversions of anything overlapping them stale: an entry
+    // is keyed by the start of its source, but a write into a view of that source (or a larger tensor the allocator
+    // placed over it) starts elsewhere
+    void         act_cache_invalidate(const void * data, size_t bytes) {
+        const char * w0 = (const char *) data, * w1 = w0 + (bytes ? bytes : 1);
+        for (ActEntry & e : act_cache) if (e.src_data && w0 < (const char *) e.src_data + e.src_bytes && (const char *) e.src_data < w1) e.src_data = nullptr;
+        if (tc_x_data && w0 < (const char *) tc_x_data + tc_x_bytes && (const char *) tc_x_data < w1) tc_x_data = nullptr;
+    }
     ActEntry *   act_cache_find(const void * src_data, int64_t K, int64_t ncols);
     ActEntry *   act_cache_take(const void * src_data, int64_t K, int64_t ncols);   // may allocate (never while capturing)
 

@@ -123,6 +123,14 @@ bool device_supports_op(DeviceCtx * dev, const ggml_tensor * op) {
         ctx->n_launches++;                                                                  \
     } while (0)
 
+// the bytes a tensor spans, from its data pointer
+static size_t t_extent(const ggml_tensor * t) {
+    size_t e = (size_t) (t->ne[0] / t_blck(t->type)) * t->nb[0];
+    for (int d = 1; d < 4; ++d) e += (size_t) (t->ne[d] > 0 ? t->ne[d] - 1 : 0) * t->nb[d];
+    return e;
+}
+static void invalidate_written(BackendCtx * ctx, const ggml_tensor * t) { if (t && t->data) ctx->act_cache_invalidate(t->data, t_extent(t)); }
+
 // can the int8 activation blocks of X be produced/kept in the per-graph cache?
 static bool act_cacheable(const ggml_tensor * X) {
     return X->type == GGML_TYPE_F32 && t_contiguous(X) && X->ne[1] * X->ne[2] * X->ne[3] <= 8;
@@ -175,9 +183,11 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
             return false;
         }
         ctx->peer_pending = true;
-        ctx->pending_full.push_back(ctx->row_slice_of(dst)->full_data); ctx->act_cache_invalidate(ctx->row_slice_of(dst)->full_data);
+        ctx->pending_full.push_back(ctx->row_slice_of(dst)->full_data);
+        ctx->act_cache_invalidate(ctx->row_slice_of(dst)->full_data, (size_t) (dst->ne[1] - 1) * dst->nb[1] + (size_t) ctx->row_slice_of(dst)->full_rows * 4);
         for (int i = 0; i < n_extra; ++i) if (const ggml_b200_row_slice * r2 = ctx->row_slice_of(extra[i])) {
-            ctx->pending_full.push_back(r2->full_data); ctx->act_cache_invalidate(r2->full_data);
+            ctx->pending_full.push_back(r2->full_data);
+            ctx->act_cache_invalidate(r2->full_data, (size_t) (extra[i]->ne[1] - 1) * extra[i]->nb[1] + (size_t) r2->full_rows * 4);
         }
     }
     if (!ids && is_float_type(W->type)) {
@@ -206,7 +216,7 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
             }
             ws = ctx->tc_xh;
             have = ctx->tc_x_data == X->data && ctx->tc_x_k == K && ctx->tc_x_n == ne11;
-            ctx->tc_x_data = X->data; ctx->tc_x_k = K; ctx->tc_x_n = ne11;
+            ctx->tc_x_data = X->data; ctx->tc_x_k = K; ctx->tc_x_n = ne11; ctx->tc_x_bytes = (size_t) K * (size_t) ne11 * 4;
         } else {
             ws = ctx->get_scratch(need);
         }
@@ -322,7 +332,7 @@ static void * tc_f16_out_for(BackendCtx * ctx, const ggml_cgraph * g, int from, 
         B200_CUDA_CHECK(cudaMalloc(&ctx->tc_xh, cap));
         ctx->tc_xh_cap = cap;
     }
-    ctx->tc_x_data = t->data; ctx->tc_x_k = t->ne[0]; ctx->tc_x_n = t->ne[1];
+    ctx->tc_x_data = t->data; ctx->tc_x_k = t->ne[0]; ctx->tc_x_n = t->ne[1]; ctx->tc_x_bytes = (size_t) t->ne[0] * (size_t) t->ne[1] * 4;
     return ctx->tc_xh;
 }
 
@@ -446,9 +456,10 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
                     }
                     if (member && clear) {
                         extra[n_extra++] = n; ctx->node_done[(size_t) j] = 1;
-                        ctx->act_cache_invalidate(n->data);
+                        invalidate_written(ctx, n);
                     } else {
                         if (n->op == GGML_OP_MUL_MAT && n->src[1] != dst->src[1]) break;     // a different stage of the layer
+                        if (t_overlap(n, dst->src[1]) || (n->op == GGML_OP_CPY && n->src[1] && t_overlap(n->src[1], dst->src[1]))) break;   // it rewrites the shared input (in place, through a view): later mat-muls must see that
                         jumped[n_jumped++] = n;
                     }
                 }
@@ -512,8 +523,8 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
                 t_contiguous(a) && t_contiguous(b) && t_contiguous(dst) && t_contiguous(rn) && t_contiguous(mu) &&
                 mu->type == GGML_TYPE_F32 && mu->src[1]->type == GGML_TYPE_F32 && mu->src[1]->nb[0] == 4 && t_can_repeat(mu->src[1], rn)) {
                 void * act = nullptr;
-                ctx->act_cache_invalidate(rn->data);          // (the MUL is often computed in place of the norm's output)
-                ctx->act_cache_invalidate(mu->data);          // written by this launch: cached conversions of its old contents are stale
+                invalidate_written(ctx, rn);          // (the MUL is often computed in place of the norm's output)
+                invalidate_written(ctx, mu);          // written by this launch: cached conversions of its old contents are stale
                 if (act_cacheable(mu) && mu->ne[0] % 128 == 0 && feeds_quant_mul_mat(g, i + 3, mu)) {
                     BackendCtx::ActEntry * e = ctx->act_cache_take(mu->data, mu->ne[0], mu->ne[1] * mu->ne[2] * mu->ne[3]);
                     if (!e) return fail();
@@ -537,7 +548,7 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
             if (ctx->use_fusion && uop == GGML_UNARY_OP_SILU && next && next->op == GGML_OP_MUL && next->src[0] == dst && next->type == GGML_TYPE_F32 &&
                 next->src[1]->type == GGML_TYPE_F32 && t_same_shape(next->src[1], dst) && t_contiguous(next->src[1]) && t_contiguous(next)) {
                 void * act = nullptr;
-                ctx->act_cache_invalidate(next->data);
+                invalidate_written(ctx, next);
                 if (act_cacheable(next) && next->ne[0] % 128 == 0 && feeds_quant_mul_mat(g, jn + 1, next)) {
                     BackendCtx::ActEntry * e = ctx->act_cache_take(next->data, next->ne[0], next->ne[1] * next->ne[2] * next->ne[3]);
                     if (!e) return fail();
@@ -583,7 +594,7 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
                     if (cv) { ctx->dyn_host[ctx->dyn_used] = l.v_off; l.v_off_dev = ctx->dyn_dev + ctx->dyn_used++; }
                 }
                 l.pos = (const int32_t *) b->data; l.ff = ff ? (const float *) ff->data : nullptr;
-                ctx->act_cache_invalidate(rk->data);
+                invalidate_written(ctx, rk);
                 ctx->node_done[(size_t) m.rk] = 1; ctx->node_done[(size_t) m.ck] = 1;
                 if (cv) ctx->node_done[(size_t) m.cv] = 1;
                 RUN0(launch_rope_kv(l, rp, lc));
@@ -628,7 +639,7 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
 bool run_single_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
     const int fusion = ctx->use_fusion;
     ctx->use_fusion = 0;
-    ctx->act_cache_invalidate(g->nodes[i]->data);
+    invalidate_written(ctx, g->nodes[i]);
     const int used = run_node(ctx, g, i);
     ctx->use_fusion = fusion;
     return used == 1;
@@ -671,9 +682,9 @@ static bool run_all(BackendCtx * ctx, ggml_cgraph * cgraph) {
             }
             if (need) { if (!peer_barrier(ctx)) return false; pending_full.clear(); }
         }
-        ctx->act_cache_invalidate(node->data);
-        if (node->op == GGML_OP_CPY && node->src[1]) ctx->act_cache_invalidate(node->src[1]->data);
-        if (i + 1 < cgraph->n_nodes) ctx->act_cache_invalidate(cgraph->nodes[i + 1]->data);   // it may be fused into this launch
+        invalidate_written(ctx, node);
+        if (node->op == GGML_OP_CPY) invalidate_written(ctx, node->src[1]);
+        if (i + 1 < cgraph->n_nodes) invalidate_written(ctx, cgraph->nodes[i + 1]);   // it may be fused into this launch
         const uint64_t l0 = ctx->n_launches;
         const int used = run_node(ctx, cgraph, i);
         if (used == 0) return false;

@@ -69,9 +69,12 @@ def _kv(key: str, gtype: int, value) -> bytes:
 
 
 def write_llama_gguf(path, arch: dict, n_ctx_train: int = 8192, seed_base: int = 1000, device: str = "cpu", make_tensor=None,
-                     rope_freqs: np.ndarray | None = None) -> int:
+                     rope_freqs: np.ndarray | None = None, share_layers: bool = False) -> int:
     """Returns the number of bytes written.  make_tensor(type, ne0, ne1, seed, device) -> flat uint8 array.
-    rope_freqs: head_dim / 2 frequency factors written as rope_freqs.weight (none by default)."""
+    rope_freqs: head_dim / 2 frequency factors written as rope_freqs.weight (none by default).
+    share_layers: every layer gets the bytes of the first layer that has the same tensor (name suffix, type, shape):
+    for timing runs on hosts where quantizing 8 billion random weights on the CPU would take minutes; speed does
+    not depend on the values."""
     if make_tensor is None:
         from llama_cpp_b200 import synth
         make_tensor = synth.make_tensor
@@ -95,14 +98,20 @@ def write_llama_gguf(path, arch: dict, n_ctx_train: int = 8192, seed_base: int =
     header = b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(kvs)) + b"".join(kvs) + b"".join(infos)
     header += b"\0" * (-len(header) % ALIGN)
     written = 0
+    shared = {}
     with open(path, "wb") as f:
         f.write(header)
         written += len(header)
         for i, (name, t, ne0, ne1) in enumerate(tensors):
+            key = (name.split(".", 2)[-1] if name.startswith("blk.") else name, t, ne0, ne1)
             if name == "rope_freqs.weight":
                 data = np.ascontiguousarray(rope_freqs, dtype=np.float32).view(np.uint8).reshape(-1)
+            elif share_layers and key in shared:
+                data = shared[key]
             else:
                 data = np.ascontiguousarray(make_tensor(t, ne0, ne1, seed=seed_base + i, device=device)).view(np.uint8).reshape(-1)
+                if share_layers:
+                    shared[key] = data
             assert data.size == row_bytes(t, ne0) * ne1, name
             f.write(data.tobytes())
             f.write(b"\0" * (-data.size % ALIGN))

@@ -66,7 +66,7 @@ CPU_LIBS := $(foreach v,$(VARIANTS),$(OUT)/libggml-cpu-$(v).so)
 .PHONY: all core tools clean
 all: core tools
 core: $(OUT)/libggml-base.so $(OUT)/libggml.so $(CPU_LIBS) $(OUT)/test-backend-ops $(OUT)/test-quantize-fns
-tools: $(OUT)/libllama.so $(OUT)/llama-bench $(OUT)/llama-quantize $(OUT)/llama-logits
+tools: $(OUT)/libllama.so $(OUT)/llama-bench $(OUT)/llama-quantize $(OUT)/llama-logits $(OUT)/graph-cases
 
 # ---- ggml-base ----
 $(OBJ)/base/%.o: $(REF)/ggml/src/%.c
@@ -131,6 +131,10 @@ $(OUT)/llama-quantize: $(REF)/examples/quantize/quantize.cpp $(OUT)/libcommon.a 
 # test tool of this repository (tests/native/llama_logits.cpp): libllama's public API only
 $(OUT)/llama-logits: tests/native/llama_logits.cpp $(OUT)/libllama.so
 	$(CXX) $(COPT) $(XSTD) $(TOOL_DEFS) $(TOOL_INC) $< -o $@ -L$(OUT) -lllama -lggml -lggml-base -lpthread $(RPATH)
+
+# test tool of this repository (tests/native/graph_cases.cpp): hand-built graphs on the CPU backend and on a named device
+$(OUT)/graph-cases: tests/native/graph_cases.cpp $(OUT)/libggml.so
+	$(CXX) $(COPT) $(XSTD) $(TOOL_DEFS) -I$(REF)/ggml/include $< -o $@ -L$(OUT) -lggml -lggml-base -lpthread $(RPATH)
 
 clean:
 	rm -rf $(OUT)

@@ -1,0 +1,217 @@
+// Test tool: hand-built ggml graphs with seeded data, computed on the reference's CPU backend (all host threads)
+// and on a named device of whatever backends the registry loads, compared element by element.  It is the checker
+// behind the full-size parity sweeps (every element of every output, not a sample of rows) and behind the
+// graph-level cases that single-op tests cannot express (memory reused inside a graph).  Public ggml API only;
+// built by oracle/ref.mk against the reference headers; test infrastructure.
+//   graph_cases DEVICE SUITE [N_THREADS]
+//   suites: mul_mat (the projection shapes x types x batch sizes), flash_attn, alias
+// One line per case: "CASE <name> nmse=<x> max_abs=<y> n=<elements>"
+#include "ggml.h"
+#include "ggml-backend.h"
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <random>
+#include <string>
+#include <vector>
+
+struct Input { ggml_tensor * t; std::vector<uint8_t> bytes; };
+struct Built { std::vector<Input> inputs; std::vector<ggml_tensor *> outputs; ggml_cgraph * graph; size_t manual_bytes = 0;
+               std::vector<std::pair<ggml_tensor *, size_t>> placement; };   // manual placement: tensor -> offset (alias cases)
+using Builder = std::function<Built(ggml_context *)>;
+
+static std::vector<float> normal(size_t n, float sigma, unsigned seed) {
+    std::mt19937 rng(seed);
+    std::normal_distribution<float> d(0.0f, sigma);
+    std::vector<float> v(n);
+    for (auto & x : v) x = d(rng);
+    return v;
+}
+static std::vector<uint8_t> as_bytes(const std::vector<float> & v) {
+    std::vector<uint8_t> b(v.size() * 4);
+    memcpy(b.data(), v.data(), b.size());
+    return b;
+}
+// `rows` rows of K weights ~ N(0, 0.02): 4096 distinct rows quantized with the reference's quantizer, repeated
+static std::vector<uint8_t> quantized(ggml_type type, int64_t K, int64_t rows, unsigned seed) {
+    const int64_t distinct = rows < 4096 ? rows : 4096;
+    const size_t rb = ggml_row_size(type, K);
+    std::vector<float> w = normal((size_t) distinct * K, 0.02f, seed);
+    std::vector<uint8_t> q(rb * (size_t) distinct), out(rb * (size_t) rows);
+    ggml_quantize_chunk(type, w.data(), q.data(), 0, distinct, K, nullptr);
+    for (int64_t r = 0; r < rows; r += distinct) memcpy(out.data() + (size_t) r * rb, q.data(), rb * (size_t) std::min(distinct, rows - r));
+    return out;
+}
+
+static std::vector<std::vector<float>> run_on(ggml_backend_t backend, const Builder & build) {
+    ggml_init_params ip = {ggml_tensor_overhead() * 64 + ggml_graph_overhead(), nullptr, true};
+    ggml_context * ctx = ggml_init(ip);
+    Built b = build(ctx);
+    ggml_backend_buffer_t buf = nullptr;
+    if (b.manual_bytes) {
+        buf = ggml_backend_alloc_buffer(backend, b.manual_bytes);
+        char * base = (char *) ggml_backend_buffer_get_base(buf);
+        for (auto & pl : b.placement) {
+            if (pl.first->view_src) ggml_backend_view_init(pl.first);
+            else ggml_backend_tensor_alloc(buf, pl.first, base + pl.second);
+        }
+    } else {
+        buf = ggml_backend_alloc_ctx_tensors(ctx, backend);
+    }
+    if (!buf) { fprintf(stderr, "buffer allocation failed\n"); exit(1); }
+    for (auto & in : b.inputs) ggml_backend_tensor_set(in.t, in.bytes.data(), 0, in.bytes.size());
+    if (ggml_backend_graph_compute(backend, b.graph) != GGML_STATUS_SUCCESS) { fprintf(stderr, "graph_compute failed\n"); exit(1); }
+    std::vector<std::vector<float>> outs;
+    for (ggml_tensor * t : b.outputs) {
+        std::vector<float> v((size_t) ggml_nelements(t));
+        ggml_backend_tensor_get(t, v.data(), 0, v.size() * 4);
+        outs.push_back(std::move(v));
+    }
+    ggml_backend_buffer_free(buf);
+    ggml_free(ctx);
+    return outs;
+}
+
+static ggml_backend_t g_cpu, g_dev;
+static int g_fail = 0;
+static void run_case(const std::string & name, const Builder & build) {
+    auto want = run_on(g_cpu, build), got = run_on(g_dev, build);
+    double num = 0, den = 0, mx = 0; size_t n = 0; bool finite = true;
+    for (size_t o = 0; o < want.size(); ++o)
+        for (size_t i = 0; i < want[o].size(); ++i) {
+            const double a = want[o][i], c = got[o][i];
+            if (!std::isfinite(c)) finite = false;
+            num += (a - c) * (a - c); den += a * a; mx = std::max(mx, std::fabs(a - c)); ++n;
+        }
+    printf("CASE %s nmse=%.3e max_abs=%.3e n=%zu%s\n", name.c_str(), den > 0 ? num / den : num, mx, n, finite ? "" : " NONFINITE");
+    fflush(stdout);
+    if (!finite) g_fail = 1;
+}
+
+// ---- suites ----
+static void suite_mul_mat() {
+    const ggml_type types[] = {GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, GGML_TYPE_Q8_0, GGML_TYPE_Q4_0};
+    const int64_t shapes[][2] = {{4096, 4096}, {4096, 14336}, {14336, 4096}, {4096, 128256}};     // K, M
+    const int64_t batches[] = {1, 8, 32, 128, 512};
+    for (ggml_type type : types) for (auto & sh : shapes) for (int64_t N : batches) {
+        if (type == GGML_TYPE_Q4_0 && !(sh[0] == 4096 && sh[1] == 4096 && (N == 1 || N == 512))) continue;      // the single-op configuration
+        const int64_t K = sh[0], M = sh[1];
+        run_case(std::string("mul_mat.") + ggml_type_name(type) + ".k" + std::to_string(K) + ".m" + std::to_string(M) + ".n" + std::to_string(N), [=](ggml_context * ctx) {
+            Built b;
+            ggml_tensor * w = ggml_new_tensor_2d(ctx, type, K, M), * x = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, K, N);
+            ggml_tensor * y = ggml_mul_mat(ctx, w, x);
+            b.graph = ggml_new_graph(ctx);
+            ggml_build_forward_expand(b.graph, y);
+            b.inputs.push_back({w, quantized(type, K, M, 7)});
+            b.inputs.push_back({x, as_bytes(normal((size_t) K * N, 1.0f, 11 + (unsigned) N))});
+            b.outputs = {y};
+            return b;
+        });
+    }
+}
+
+static void suite_flash_attn() {
+    const int64_t D = 128, n_head = 32, n_head_kv = 8;
+    for (int64_t n_kv : {512, 4096, 32768}) for (int64_t n_q : {1, 512}) {
+        run_case("flash_attn.kv" + std::to_string(n_kv) + ".q" + std::to_string(n_q), [=](ggml_context * ctx) {
+            Built b;
+            const int64_t n_pad = (n_q + 63) / 64 * 64;
+            ggml_tensor * q = ggml_new_tensor_3d(ctx, GGML_TYPE_F32, D, n_q, n_head);
+            ggml_tensor * k = ggml_new_tensor_3d(ctx, GGML_TYPE_F16, D, n_kv, n_head_kv), * v = ggml_new_tensor_3d(ctx, GGML_TYPE_F16, D, n_kv, n_head_kv);
+            ggml_tensor * mask = ggml_new_tensor_2d(ctx, GGML_TYPE_F16, n_kv, n_pad);
+            ggml_tensor * y = ggml_flash_attn_ext(ctx, q, k, v, mask, 1.0f / std::sqrt((float) D), 0.0f, 0.0f);
+            ggml_flash_attn_ext_set_prec(y, GGML_PREC_F32);
+            b.graph = ggml_new_graph(ctx);
+            ggml_build_forward_expand(b.graph, y);
+            auto half = [](const std::vector<float> & f) { std::vector<uint8_t> h(f.size() * 2); ggml_fp32_to_fp16_row(f.data(), (ggml_fp16_t *) h.data(), (int64_t) f.size()); return h; };
+            b.inputs.push_back({q, as_bytes(normal((size_t) (D * n_q * n_head), 1.0f, 21))});
+            b.inputs.push_back({k, half(normal((size_t) (D * n_kv * n_head_kv), 1.0f, 22))});
+            b.inputs.push_back({v, half(normal((size_t) (D * n_kv * n_head_kv), 1.0f, 23))});
+            std::vector<float> m((size_t) (n_kv * n_pad), -INFINITY);                 // causal: query i sees keys 0 .. n_kv - n_q + i
+            for (int64_t i = 0; i < n_q; ++i) for (int64_t j = 0; j <= n_kv - n_q + i; ++j) m[(size_t) (i * n_kv + j)] = 0.0f;
+            b.inputs.push_back({mask, half(m)});
+            b.outputs = {y};
+            return b;
+        });
+    }
+}
+
+// graphs whose memory is reused while they run
+static void suite_alias() {
+    const int64_t K = 4096, M = 512;
+    // a mat-mul input is changed in place through a view at a non-zero offset between two mat-muls that read it:
+    // conversions of the input cached by its start address would be stale
+    run_case("alias.inplace_view_between_mul_mats", [=](ggml_context * ctx) {
+        Built b;
+        ggml_tensor * w = ggml_new_tensor_2d(ctx, GGML_TYPE_Q4_K, K, M), * x = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, K, 1);
+        ggml_tensor * c = ggml_new_tensor_1d(ctx, GGML_TYPE_F32, K / 2);
+        ggml_tensor * y1 = ggml_mul_mat(ctx, w, x);
+        ggml_tensor * xv = ggml_view_1d(ctx, x, K / 2, (size_t) (K / 2) * 4);
+        ggml_tensor * upd = ggml_add_inplace(ctx, xv, c);
+        ggml_tensor * y2 = ggml_mul_mat(ctx, w, x);
+        b.graph = ggml_new_graph(ctx);
+        ggml_build_forward_expand(b.graph, y1);
+        ggml_build_forward_expand(b.graph, upd);
+        ggml_build_forward_expand(b.graph, y2);
+        b.inputs.push_back({w, quantized(GGML_TYPE_Q4_K, K, M, 3)});
+        b.inputs.push_back({x, as_bytes(normal((size_t) K, 1.0f, 4))});
+        b.inputs.push_back({c, as_bytes(normal((size_t) K / 2, 1.0f, 5))});
+        b.outputs = {y1, y2};
+        return b;
+    });
+    // q = Wq x ; r = scale(q) ; k = Wk x placed in q's memory (free once r has read it) ; out = r + k.  A backend
+    // that groups the two mat-muls on x into one launch must not let k overwrite q before r has read it.
+    run_case("alias.grouped_mul_mat_into_freed_memory", [=](ggml_context * ctx) {
+        Built b;
+        ggml_tensor * wq = ggml_new_tensor_2d(ctx, GGML_TYPE_Q4_K, K, M), * wk = ggml_new_tensor_2d(ctx, GGML_TYPE_Q4_K, K, M);
+        ggml_tensor * x = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, K, 1);
+        ggml_tensor * q = ggml_mul_mat(ctx, wq, x);
+        ggml_tensor * r = ggml_scale(ctx, q, 0.5f);
+        ggml_tensor * k = ggml_mul_mat(ctx, wk, x);
+        ggml_tensor * out = ggml_add(ctx, r, k);
+        b.graph = ggml_new_graph(ctx);
+        ggml_build_forward_expand(b.graph, q);
+        ggml_build_forward_expand(b.graph, r);
+        ggml_build_forward_expand(b.graph, k);
+        ggml_build_forward_expand(b.graph, out);
+        const size_t wb = ggml_nbytes(wq);
+        size_t off = 0;
+        auto put = [&](ggml_tensor * t, size_t at) { b.placement.push_back({t, at}); };
+        put(wq, off); off += (wb + 255) / 256 * 256;
+        put(wk, off); off += (wb + 255) / 256 * 256;
+        put(x, off); off += (size_t) K * 4;
+        const size_t q_at = off; off += (size_t) M * 4 + 256;
+        put(q, q_at); put(k, q_at);                                            // the same bytes
+        put(r, off); off += (size_t) M * 4 + 256;
+        put(out, off); off += (size_t) M * 4 + 256;
+        b.manual_bytes = off + 4096;
+        b.inputs.push_back({wq, quantized(GGML_TYPE_Q4_K, K, M, 6)});
+        b.inputs.push_back({wk, quantized(GGML_TYPE_Q4_K, K, M, 7)});
+        b.inputs.push_back({x, as_bytes(normal((size_t) K, 1.0f, 8))});
+        b.outputs = {out};
+        return b;
+    });
+}
+
+int main(int argc, char ** argv) {
+    if (argc < 3) { fprintf(stderr, "usage: %s DEVICE SUITE [N_THREADS]\n", argv[0]); return 2; }
+    ggml_backend_load_all();
+    ggml_backend_dev_t cpu_dev = ggml_backend_dev_by_type(GGML_BACKEND_DEVICE_TYPE_CPU), dev = ggml_backend_dev_by_name(argv[1]);
+    if (!cpu_dev || !dev) { fprintf(stderr, "device %s (or the CPU device) not found\n", argv[1]); return 3; }
+    g_cpu = ggml_backend_dev_init(cpu_dev, nullptr); g_dev = ggml_backend_dev_init(dev, nullptr);
+    if (!g_cpu || !g_dev) { fprintf(stderr, "backend init failed\n"); return 3; }
+    if (argc > 3) {
+        auto set_threads = (ggml_backend_set_n_threads_t) ggml_backend_reg_get_proc_address(ggml_backend_dev_backend_reg(cpu_dev), "ggml_backend_set_n_threads");
+        if (set_threads) set_threads(g_cpu, atoi(argv[3]));
+    }
+    const std::string suite = argv[2];
+    if (suite == "mul_mat") suite_mul_mat();
+    else if (suite == "flash_attn") suite_flash_attn();
+    else if (suite == "alias") suite_alias();
+    else { fprintf(stderr, "unknown suite %s\n", argv[2]); return 2; }
+    ggml_backend_free(g_dev); ggml_backend_free(g_cpu);
+    return g_fail;
+}

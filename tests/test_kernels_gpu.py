@@ -212,3 +212,33 @@ def test_glue_ops(b200, oracle, golden):
         assert oracle.nmse(golden[f"rope.y.mode{mode}"], got) <= 1e-7
     big = np.random.default_rng(1).standard_normal((5, 4096)).astype(np.float32)
     assert oracle.nmse(oracle.rms_norm(big, 1e-5), b200.rms_norm(big, 1e-5)) <= 1e-7
+
+
+def test_quantize_act_blocks_bit_exact(b200):
+    """b200_quantize_act against a numpy restatement of the activation block format (160 bytes per 128 values: 128 int8,
+    then per 32 values {d = amax / 127, s = d * sum(q)}), the device-side counterpart of quantize_row_q8_1
+    (ggml/src/ggml-cuda/quantize.cu:4-38)."""
+    torch = pytest.importorskip("torch")
+    l = b200.lib()
+    rng = np.random.default_rng(9)
+    n, k = 3, 4224
+    x = rng.standard_normal((n, k)).astype(np.float32)
+    x[0, 64:96] = 0.0                    # an all-zero group: d = 0, q = 0
+    x[1, 5] = 1.0e4                      # an outlier squeezes its group
+    x[2, 4096:] *= 1.0e-3
+    dx = torch.from_numpy(x).cuda()
+    xq = torch.empty(int(l.b200_act_bytes(k, n)), device="cuda", dtype=torch.uint8)
+    assert l.b200_quantize_act(dx.data_ptr(), k, k, n, xq.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0, l.b200_last_error()
+    torch.cuda.synchronize()
+    blocks = xq.cpu().numpy()[: n * (k // 128) * 160].reshape(n, k // 128, 160)
+    q = blocks[:, :, :128].view(np.int8).reshape(n, k // 32, 32)
+    ds = np.ascontiguousarray(blocks[:, :, 128:]).view(np.float32).reshape(n, k // 32, 2)
+    g = x.reshape(n, k // 32, 32)
+    amax = np.abs(g).max(axis=-1)
+    d = (amax / np.float32(127.0)).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        inv = np.where(amax > 0, np.float32(127.0) / amax, np.float32(0.0)).astype(np.float32)
+    want_q = np.rint(g * inv[..., None]).astype(np.int32)          # round half to even, as __float2int_rn
+    assert np.array_equal(q.astype(np.int32), want_q)
+    assert np.array_equal(ds[..., 0], d)
+    assert np.array_equal(ds[..., 1], d * want_q.sum(axis=-1).astype(np.float32))

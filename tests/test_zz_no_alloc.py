@@ -45,6 +45,48 @@ def test_noalloc_matches_regular_entry_point_twice(b200, oracle, golden):
         assert oracle.nmse(oracle.mul_mat(qt, w, x), out) <= 5e-4
 
 
+def test_noalloc_at_the_scratch_limit_and_eight_columns(b200, oracle):
+    """8 columns of 104832 values need 1,048,320 of the 1,048,576 scratch bytes; one more activation block per column is refused."""
+    torch = pytest.importorskip("torch")
+    l = b200.lib()
+    rng = np.random.default_rng(1)
+    n, m = 8, 16
+    for k, fits in ((104832, True), (104960, False)):
+        w = oracle.quantize_rows("q8_0", (rng.standard_normal((m, k)) * 0.02).astype(np.float32))
+        x = rng.standard_normal((n, k)).astype(np.float32)
+        if fits:
+            ref, out = run_pair(b200, torch, "q8_0", w, x)
+            assert np.array_equal(ref, out)
+            assert oracle.nmse(oracle.mul_mat("q8_0", w, x), out) <= 5e-4
+        else:
+            dw, dx = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+            out = torch.zeros(n, m, device="cuda")
+            rc = l.b200_mul_mat_q_noalloc(b200.TYPES["q8_0"], dw.data_ptr(), b200.row_size("q8_0", k), m, k, dx.data_ptr(), k, n, out.data_ptr(), m, None)
+            assert rc == -4 and b"scratch" in l.b200_noalloc_last_error()
+
+
+def test_noalloc_second_call_allocates_nothing_and_status_is_clean(b200, golden):
+    torch = pytest.importorskip("torch")
+    l = b200.lib()
+    w = np.ascontiguousarray(np.tile(golden["mul_mat.w.q4_K"], (3, 4)))
+    x = np.random.default_rng(2).standard_normal((2, 2048)).astype(np.float32)
+    dw, dx = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+    out = torch.zeros(2, w.shape[0], device="cuda")
+    args = (b200.TYPES["q4_K"], dw.data_ptr(), b200.row_size("q4_K", 2048), w.shape[0], 2048, dx.data_ptr(), 2048, 2, out.data_ptr(), w.shape[0], None)
+    assert l.b200_mul_mat_q_noalloc(*args) == 0           # warm-up: module and kernel variant are materialised here
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    assert l.b200_mul_mat_q_noalloc(*args) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0          # not a byte of device memory taken by the second call
+    assert l.b200_noalloc_status(None) == 0               # no kernel gave up a wait
+    # arguments a kernel would fault on come back as B200_E_BAD_ARG without a launch
+    bad = list(args); bad[5] = dx.data_ptr() + 2
+    assert l.b200_mul_mat_q_noalloc(*bad) == -2
+    bad = list(args); bad[6] = 1024
+    assert l.b200_mul_mat_q_noalloc(*bad) == -2
+
+
 def test_noalloc_rejects_oversize(b200):
     torch = pytest.importorskip("torch")
     l = b200.lib()

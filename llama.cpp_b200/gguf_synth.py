@@ -69,12 +69,14 @@ def _kv(key: str, gtype: int, value) -> bytes:
 
 
 def write_llama_gguf(path, arch: dict, n_ctx_train: int = 8192, seed_base: int = 1000, device: str = "cpu", make_tensor=None,
-                     rope_freqs: np.ndarray | None = None, share_layers: bool = False) -> int:
+                     rope_freqs: np.ndarray | None = None, share_layers: bool = False, dequantize=None) -> int:
     """Returns the number of bytes written.  make_tensor(type, ne0, ne1, seed, device) -> flat uint8 array.
     rope_freqs: head_dim / 2 frequency factors written as rope_freqs.weight (none by default).
     share_layers: every layer gets the bytes of the first layer that has the same tensor (name suffix, type, shape):
     for timing runs on hosts where quantizing 8 billion random weights on the CPU would take minutes; speed does
-    not depend on the values."""
+    not depend on the values.
+    dequantize(type, bytes, ne0) -> float32 [rows, ne0]: when given, every quantized tensor is written as the F32 values
+    its blocks decode to -- the same model with exact weights, for parity checks against an unquantized evaluation."""
     if make_tensor is None:
         from llama_cpp_b200 import synth
         make_tensor = synth.make_tensor
@@ -90,9 +92,12 @@ def write_llama_gguf(path, arch: dict, n_ctx_train: int = 8192, seed_base: int =
            _kv(f"{a}.rope.dimension_count", G_U32, head_dim), _kv(f"{a}.vocab_size", G_U32, arch["n_vocab"]),
            _kv("tokenizer.ggml.model", G_STR, "no_vocab")]
     tensors = tensor_list(arch, rope_freqs is not None)
+    src_types = [t for _, t, _, _ in tensors]
+    if dequantize is not None:
+        tensors = [(name, T_F32, ne0, ne1) for name, _, ne0, ne1 in tensors]
     infos, off = [], 0
     for name, t, ne0, ne1 in tensors:
-        dims = [ne0] if ne1 == 1 and t == T_F32 else [ne0, ne1]
+        dims = [ne0] if ne1 == 1 else [ne0, ne1]
         infos.append(_s(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", t, off))
         off += (row_bytes(t, ne0) * ne1 + ALIGN - 1) // ALIGN * ALIGN
     header = b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(kvs)) + b"".join(kvs) + b"".join(infos)
@@ -109,7 +114,9 @@ def write_llama_gguf(path, arch: dict, n_ctx_train: int = 8192, seed_base: int =
             elif share_layers and key in shared:
                 data = shared[key]
             else:
-                data = np.ascontiguousarray(make_tensor(t, ne0, ne1, seed=seed_base + i, device=device)).view(np.uint8).reshape(-1)
+                data = np.ascontiguousarray(make_tensor(src_types[i], ne0, ne1, seed=seed_base + i, device=device)).view(np.uint8).reshape(-1)
+                if dequantize is not None and src_types[i] != T_F32:
+                    data = np.ascontiguousarray(dequantize(src_types[i], data, ne0), dtype=np.float32).view(np.uint8).reshape(-1)
                 if share_layers:
                     shared[key] = data
             assert data.size == row_bytes(t, ne0) * ne1, name

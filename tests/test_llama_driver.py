@@ -66,3 +66,30 @@ def test_driver_b200_matches_reference_cpu_backend(b200, oracle):
         assert gpu.launch_count > 0
     finally:
         cpu.close(); gpu.close()
+
+
+@pytest.mark.gpu
+def test_quantized_backends_against_exact_evaluation(tmp_path, b200, oracle):
+    """Anchors whole-model parity: the same model with its weights written out as the F32 values the quantized blocks
+    decode to, evaluated by the reference CPU backend with F32 mat-muls, is the exact result both quantized
+    evaluations approximate (the reference CPU backend quantizes activations to Q8_K, per 256 values; this backend to
+    int8 per 32 values).  The device must be no further from exact than the reference CPU backend is."""
+    if not oracle.ref_available():
+        pytest.skip("reference build (oracle/_ref) not present")
+    from llama_cpp_b200 import gguf_synth, llama
+    arch = dict(n_layer=4, n_embd=2048, n_head=16, n_head_kv=4, n_ff=4096, n_vocab=2048, rope_theta=500000.0, rms_eps=1e-5)
+    names = {12: "q4_K", 13: "q5_K", 14: "q6_K"}
+    fq, ff = tmp_path / "q.gguf", tmp_path / "f32.gguf"
+    gguf_synth.write_llama_gguf(fq, arch, device="cuda")
+    gguf_synth.write_llama_gguf(ff, arch, device="cuda", dequantize=lambda t, data, ne0: b200.dequantize_rows(names[t], data, ne0))
+    cpu_reg = oracle.ref_cpu_backend_reg()
+    exact = llama.Llama.from_gguf(ff, n_ctx=512, n_ubatch=64, reg=cpu_reg, n_threads=8)
+    cpu = llama.Llama.from_gguf(fq, n_ctx=512, n_ubatch=64, reg=cpu_reg, n_threads=8)
+    gpu = llama.Llama.from_gguf(fq, n_ctx=512, n_ubatch=64)
+    try:
+        e, c, g = run_tokens(exact, 37, 5), run_tokens(cpu, 37, 5), run_tokens(gpu, 37, 5)
+        for i, (x, y, z) in enumerate(zip(e, c, g)):
+            d_cpu, d_gpu = oracle.nmse(x, y), oracle.nmse(x, z)
+            assert d_gpu <= 1.5 * d_cpu + 1e-5, (i, d_cpu, d_gpu)
+    finally:
+        exact.close(); cpu.close(); gpu.close()

@@ -128,6 +128,14 @@ int          b200_decode_step_attention_host(const float * q, const void * k_f16
                                              int merge_in_next_phase, float * dst);
 const char * b200_decode_step_last_error(void);
 
+/* ---- the bounded wait of the row-split barrier, observable on one GPU ------
+ * No counterpart in the reference (its multi-GPU path synchronises with events inside one process).  The
+ * barrier between the ranks of a row-split run (include/ggml-b200.h) spins on flags the peers write; the spin
+ * is bounded.  This probe runs that kernel as rank 0 of 2 with both flag arrays in local memory: with
+ * peer_arrives = 0 nothing ever writes the flag, the wait runs out after spin_limit polls, *status_out
+ * becomes 3 (ERR_PEER_TIMEOUT) and the kernel returns normally; with peer_arrives = 1 it passes (0).   */
+int b200_peer_barrier_probe_host(int spin_limit, int peer_arrives, int * status_out);
+
 /* ---- FLASH_ATTN_EXT -------------------------------------------------------
  * GGML_OP_FLASH_ATTN_EXT (ggml_flash_attn_ext, ggml/src/ggml.c:4306-4345; CPU
  * semantics ggml/src/ggml-cpu/ggml-cpu.c:10916-11129).  q F32 [D, n_q, n_head],

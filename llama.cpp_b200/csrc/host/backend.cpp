@@ -359,6 +359,7 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t dev, const char * /*pa
     if (getenv("GGML_B200_MEGA_KEYS")) ctx->mega_keys_per_slice = atoi(getenv("GGML_B200_MEGA_KEYS"));
     if (ctx->mega_keys_per_slice < 16) ctx->mega_keys_per_slice = 16;
     if (getenv("GGML_B200_MEGA_CMERGE")) ctx->mega_consumer_merge = atoi(getenv("GGML_B200_MEGA_CMERGE"));
+    if (getenv("GGML_B200_PEER_SPIN_LIMIT")) ctx->peer_spin_limit = atoi(getenv("GGML_B200_PEER_SPIN_LIMIT"));
     ctx->mega_timing = getenv("GGML_B200_MEGA_TIMING") ? atoi(getenv("GGML_B200_MEGA_TIMING")) : 0;
     const char * pdl = getenv("GGML_B200_PDL");
     ctx->use_pdl = pdl ? atoi(pdl) : 1;

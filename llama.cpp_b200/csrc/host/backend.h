@@ -97,6 +97,7 @@ struct BackendCtx {
     // stored to the peers since the last barrier
     ggml_b200_peers peers = {};
     bool         peer_pending = false;
+    int          peer_spin_limit = 0;          // GGML_B200_PEER_SPIN_LIMIT: polls before the cross-GPU barrier gives up (0: default)
     std::vector<const void *> pending_full;   // full results whose slices are in flight to the peers
     std::vector<uint8_t> node_done;            // per graph node: already executed ahead of its position (hoisted into a grouped launch)
     const ggml_b200_row_slice * row_slice_of(const ggml_tensor * node) const {

@@ -165,7 +165,7 @@ static bool peer_barrier(BackendCtx * ctx) {
     char * mine = (char *) ctx->peers.arena[ctx->peers.rank];
     b.local_flags = (unsigned *) mine; b.epoch = (unsigned *) (mine + 64);
     for (int r = 0; r < ctx->peers.n_ranks; ++r) b.peer_flags[r] = (unsigned *) ctx->peers.arena[r];
-    b.rank = ctx->peers.rank; b.n_ranks = ctx->peers.n_ranks; b.status = ctx->status_dev;
+    b.rank = ctx->peers.rank; b.n_ranks = ctx->peers.n_ranks; b.status = ctx->status_dev; b.spin_limit = ctx->peer_spin_limit;
     RUN(launch_peer_barrier(b, ctx->launch_ctx()));
     ctx->peer_pending = false;
     return true;

@@ -137,7 +137,9 @@ bool GgufFile::open(const char * path_, std::string & err) {
             if (d > 0) rows *= t.ne[d];
         }
         if (t.ne[0] % blck) { err = path + ": row length of " + t.name + " is not a multiple of its block size"; return false; }
-        t.nbytes = t_row_size(t.type, t.ne[0]) * (size_t) rows;
+        const size_t row_size = t_row_size(t.type, t.ne[0]);
+        if (row_size && (size_t) rows > SIZE_MAX / row_size) { err = path + ": tensor " + t.name + " is larger than the address space"; return false; }
+        t.nbytes = row_size * (size_t) rows;
         if (t.offset % alignment) { err = path + ": tensor " + t.name + " is not aligned"; return false; }
         if (by_name.count(t.name)) { err = path + ": duplicate tensor " + t.name; return false; }
         by_name[t.name] = tensors.size();

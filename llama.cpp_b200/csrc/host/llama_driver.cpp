@@ -350,6 +350,12 @@ static b200_llama * create_impl(void * reg_, int32_t device_index, const b200_ll
     std::unique_ptr<b200_llama> m(new b200_llama);
     m->cfg = *cfg;
     m->type_override = types;
+    // hyper-parameters may come from a file: nothing below divides by, or sizes a buffer from, an unchecked value
+    if (cfg->n_layer <= 0 || cfg->n_layer > 1024 || cfg->n_embd <= 0 || cfg->n_embd > (1 << 20) || cfg->n_head <= 0 || cfg->n_head_kv <= 0 ||
+        cfg->n_ff <= 0 || cfg->n_ff > (1 << 24) || cfg->n_vocab <= 0 || cfg->n_ctx <= 0 || cfg->n_ubatch <= 0 || cfg->n_ubatch > cfg->n_ctx) {
+        g_error = "model hyper-parameters out of range (layers, widths, heads, vocabulary, context and batch must be positive and sane)";
+        return nullptr;
+    }
     if (cfg->n_embd % cfg->n_head || cfg->n_head % cfg->n_head_kv || cfg->n_embd % 256 || cfg->n_ff % 256) { g_error = "unsupported model shape"; return nullptr; }
     m->n_ranks = cfg->n_ranks > 1 ? cfg->n_ranks : 1;
     m->rank = m->n_ranks > 1 ? cfg->rank : 0;

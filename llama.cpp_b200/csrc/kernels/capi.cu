@@ -1,6 +1,7 @@
 // Flat C-ABI declared in include/b200_kernels.h: thin argument marshalling over
 // the kernel launchers.  The `_host` forms own their device memory for the
-// duration of the call; the device forms allocate nothing.
+// duration of the call; the device forms allocate nothing per call (their first
+// call on a device creates a status word and the attention kernel's counters).
 #include "common.cuh"
 #include "kernels.h"
 #include "b200_kernels.h"
@@ -91,10 +92,16 @@ static TensorD desc(void * data, int type, int64_t ne0, int64_t ne1, int64_t ne2
 // ---------------------------------------------------------------------------
 // MUL_MAT
 // ---------------------------------------------------------------------------
+// The kernels issue 16-byte bulk copies / vector loads from the activation blocks and 4-byte accesses to X and dst:
+// a misaligned caller pointer would raise a sticky device error, so it is refused here, before any launch.
+static bool aligned_to(const void * p, size_t a) { return p && ((uintptr_t) p & (a - 1)) == 0; }
+static constexpr int64_t I32_MAX = 0x7fffffff;
+static constexpr int FLAT_SPLITK_SMS = 148;       // what b200_mul_mat_q_scratch_bytes sizes the split-K partial tiles for
+
 API size_t b200_mul_mat_q_scratch_bytes(int type, int64_t M, int64_t K, int64_t N) {
     (void) M;
     size_t s = act128_bytes(K, N);
-    if (mmq_tc_supported(type, M, N, K)) { const size_t t = mmq_tc_workspace_bytes(N, K) + mmq_tc_partial_bytes(M, N, K, 148); if (t > s) s = t; }
+    if (mmq_tc_supported(type, M, N, K)) { const size_t t = mmq_tc_workspace_bytes(N, K) + mmq_tc_partial_bytes(M, N, K, FLAT_SPLITK_SMS); if (t > s) s = t; }
     return s;
 }
 
@@ -103,10 +110,17 @@ API int b200_mul_mat_q(int type, const void * W, int64_t w_nb1, int64_t M, int64
     if (!mmvq_type_supported(type)) return fail(B200_E_UNSUPPORTED, "weight type not supported");
     if (K <= 0 || M <= 0 || N <= 0 || K % type_block_elems(type) != 0) return fail(B200_E_BAD_ARG, "bad shape");
     if (scratch_bytes < b200_mul_mat_q_scratch_bytes(type, M, K, N)) return fail(B200_E_SCRATCH, "scratch buffer too small");
+    if (M > I32_MAX || K > I32_MAX || x_stride < K || dst_stride < M || w_nb1 < (int64_t) b200_row_size(type, K))
+        return fail(B200_E_BAD_ARG, "strides shorter than a row / column, or a dimension beyond 2^31-1");
+    if (!aligned_to(W, 2) || (w_nb1 & 1) || !aligned_to(X, 4) || !aligned_to(dst, 4) || !aligned_to(scratch, 16))
+        return fail(B200_E_BAD_ARG, "null or misaligned pointer (weights 2, X and dst 4, scratch 16 bytes)");
     LaunchCtx lc; int rc = get_ctx(stream, lc); if (rc) return rc;
     if (mmq_tc_supported(type, M, N, K) && mmq_tc_ptr_ok(type, W, w_nb1, X, x_stride * 4)) {
-        void * partials = mmq_tc_partial_bytes(M, N, K, lc.sm_count) ? (char *) scratch + mmq_tc_workspace_bytes(N, K) : nullptr;
-        CK(launch_mmq_tc(type, W, w_nb1, X, x_stride * 4, dst, dst_stride * 4, M, N, K, scratch, lc, false, partials));
+        // split-K partial tiles: never more than the scratch size function allowed for, whatever this device's SM count
+        LaunchCtx tc = lc;
+        if (tc.sm_count > FLAT_SPLITK_SMS) tc.sm_count = FLAT_SPLITK_SMS;
+        void * partials = mmq_tc_partial_bytes(M, N, K, tc.sm_count) ? (char *) scratch + mmq_tc_workspace_bytes(N, K) : nullptr;
+        CK(launch_mmq_tc(type, W, w_nb1, X, x_stride * 4, dst, dst_stride * 4, M, N, K, scratch, tc, false, partials));
         return 0;
     }
     CK(launch_quantize_act128(X, N, 1, 1, x_stride, 0, 0, scratch, (int) K, lc.stream));
@@ -127,7 +141,8 @@ API int b200_mul_mat_q(int type, const void * W, int64_t w_nb1, int64_t M, int64
 API size_t b200_act_bytes(int64_t K, int64_t N) { return act128_bytes(K, N); }
 
 API int b200_quantize_act(const float * X, int64_t x_stride, int64_t K, int64_t N, void * xq, void * stream) {
-    if (K <= 0 || N <= 0) return fail(B200_E_BAD_ARG, "bad shape");
+    if (K <= 0 || N <= 0 || K > I32_MAX || x_stride < K) return fail(B200_E_BAD_ARG, "bad shape");
+    if (!aligned_to(X, 4) || !aligned_to(xq, 16)) return fail(B200_E_BAD_ARG, "null or misaligned pointer (X 4, xq 16 bytes)");
     LaunchCtx lc; int rc = get_ctx(stream, lc); if (rc) return rc;
     CK(launch_quantize_act128(X, N, 1, 1, x_stride, 0, 0, xq, (int) K, lc.stream));
     return 0;
@@ -137,6 +152,8 @@ API int b200_mul_mat_vec_q(int type, const void * W, int64_t w_nb1, int64_t M, i
                            float * dst, int64_t dst_stride, void * stream) {
     if (!mmvq_type_supported(type)) return fail(B200_E_UNSUPPORTED, "weight type not supported");
     if (K <= 0 || M <= 0 || N <= 0 || N > 8 || K % type_block_elems(type) != 0) return fail(B200_E_BAD_ARG, "bad shape");
+    if (M > I32_MAX || K > I32_MAX || dst_stride < M || w_nb1 < (int64_t) b200_row_size(type, K)) return fail(B200_E_BAD_ARG, "strides shorter than a row / column, or a dimension beyond 2^31-1");
+    if (!aligned_to(W, 2) || (w_nb1 & 1) || !aligned_to(xq, 16) || !aligned_to(dst, 4)) return fail(B200_E_BAD_ARG, "null or misaligned pointer (weights 2, xq 16, dst 4 bytes)");
     LaunchCtx lc; int rc = get_ctx(stream, lc); if (rc) return rc;
     MmvqArgs a = {};
     a.type = type; a.W = W; a.w_nb1 = w_nb1; a.Xq = xq; a.M = (int) M; a.K = (int) K; a.N = (int) N;
@@ -350,5 +367,29 @@ API int b200_soft_max_host(const float * x, int64_t n_rows, int64_t k, const voi
     CK(launch_soft_max(xd, mask ? &md : nullptr, dd_, scale, 0.0f, lc));
     CK(cudaDeviceSynchronize());
     CK(cudaMemcpy(dst, dd.p, nb, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// the bounded wait of the cross-GPU barrier, on one GPU
+// ---------------------------------------------------------------------------
+// Runs the row-split barrier kernel (peer.cu) as rank 0 of 2 with both flag arrays in this GPU's memory.  With
+// peer_arrives the "peer" has already published the epoch and the barrier passes; without, nothing ever writes the
+// flag, the wait runs out after `spin_limit` polls, and the kernel records ERR_PEER_TIMEOUT and returns.
+API int b200_peer_barrier_probe_host(int spin_limit, int peer_arrives, int * status_out) {
+    LaunchCtx lc; int rc = get_ctx(nullptr, lc); if (rc) return rc;
+    DevBuf flags, peer, epoch, status;
+    CK(flags.alloc(256)); CK(peer.alloc(256)); CK(epoch.alloc(16)); CK(status.alloc(16));
+    CK(cudaMemset(flags.p, 0, 256)); CK(cudaMemset(peer.p, 0, 256)); CK(cudaMemset(epoch.p, 0, 16)); CK(cudaMemset(status.p, 0, 16));
+    if (peer_arrives) { const unsigned one = 1; CK(cudaMemcpy((unsigned *) flags.p + 1, &one, 4, cudaMemcpyHostToDevice)); }
+    PeerBarrier b = {};
+    b.epoch = (unsigned *) epoch.p; b.local_flags = (unsigned *) flags.p;
+    b.peer_flags[0] = (unsigned *) flags.p; b.peer_flags[1] = (unsigned *) peer.p;
+    b.rank = 0; b.n_ranks = 2; b.status = (int *) status.p; b.spin_limit = spin_limit;
+    CK(launch_peer_barrier(b, lc));
+    CK(cudaDeviceSynchronize());
+    int st = 0;
+    CK(cudaMemcpy(&st, status.p, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status_out) *status_out = st;
     return 0;
 }

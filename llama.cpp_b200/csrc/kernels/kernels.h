@@ -38,6 +38,7 @@ struct PeerBarrier {
     unsigned * local_flags;                            // [MAX_PEERS], slot r written by rank r
     unsigned * peer_flags[MAX_PEERS];                  // the flag arrays of the other ranks (mapped)
     int rank, n_ranks; int * status;
+    int spin_limit;                                    // polls before the wait gives up (0: the default, a few seconds)
 };
 cudaError_t launch_peer_push(const PeerPush & p, const LaunchCtx & c);
 cudaError_t launch_peer_barrier(const PeerBarrier & b, const LaunchCtx & c);

@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerBarrier b) {
         for (;;) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
             if ((int) (seen - ep) >= 0) break;
-            if (++spins > PEER_SPIN_LIMIT) { atomicMax(b.status, (int) ERR_PEER_TIMEOUT); break; }
+            if (++spins > (b.spin_limit > 0 ? b.spin_limit : PEER_SPIN_LIMIT)) { atomicMax(b.status, (int) ERR_PEER_TIMEOUT); break; }
             __nanosleep(200);
         }
     }

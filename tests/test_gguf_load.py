@@ -173,6 +173,19 @@ def test_load_rejects_unsupported_models(b200, oracle, tiny_gguf, tmp_path):
         llama.Llama.from_gguf(bad, n_ctx=512, n_ubatch=64)
     with pytest.raises(b200.B200Error):
         llama.Llama.from_gguf(tmp_path / "missing.gguf", n_ctx=512, n_ubatch=64)
+    # hyper-parameters a corrupt file may carry: an error, never a division by zero or a wild allocation
+    if oracle.ref_available():
+        reg = oracle.ref_cpu_backend_reg()
+        for key, value in (("llama.attention.head_count_kv", 0), ("llama.block_count", 0), ("llama.embedding_length", 0),
+                           ("llama.feed_forward_length", 0x7fffff00)):
+            i = raw.index(_s(key) + struct.pack("<I", 4))
+            at = i + len(_s(key)) + 4
+            broken = tmp_path / "hp.gguf"
+            broken.write_bytes(raw[:at] + struct.pack("<I", value) + raw[at + 4:])
+            with pytest.raises(b200.B200Error):
+                llama.Llama.from_gguf(broken, n_ctx=512, n_ubatch=64, reg=reg)
+        with pytest.raises(b200.B200Error):
+            llama.Llama.from_gguf(tiny_gguf, n_ctx=0, n_ubatch=64, reg=reg)
 
 
 @pytest.mark.gpu

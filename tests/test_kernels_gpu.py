@@ -242,3 +242,23 @@ def test_quantize_act_blocks_bit_exact(b200):
     assert np.array_equal(q.astype(np.int32), want_q)
     assert np.array_equal(ds[..., 0], d)
     assert np.array_equal(ds[..., 1], d * want_q.sum(axis=-1).astype(np.float32))
+
+
+def test_device_pointer_entry_points_refuse_bad_pointers(b200):
+    """Misaligned or undersized arguments come back as B200_E_BAD_ARG; nothing is launched on them."""
+    torch = pytest.importorskip("torch")
+    l = b200.lib()
+    t, k, m = b200.TYPES["q4_K"], 512, 32
+    w = torch.zeros(m * b200.row_size("q4_K", k), device="cuda", dtype=torch.uint8)
+    x = torch.zeros(k + 8, device="cuda"); d = torch.zeros(m + 8, device="cuda")
+    sb = int(l.b200_mul_mat_q_scratch_bytes(t, m, k, 1))
+    sc = torch.zeros(sb + 64, device="cuda", dtype=torch.uint8)
+    rb = b200.row_size("q4_K", k)
+    ok = (t, w.data_ptr(), rb, m, k, x.data_ptr(), k, 1, d.data_ptr(), m, sc.data_ptr(), sb, None)
+    assert l.b200_mul_mat_q(*ok) == 0
+    for idx, val in ((10, sc.data_ptr() + 4), (5, x.data_ptr() + 2), (8, d.data_ptr() + 1), (6, k - 1), (9, m - 1), (2, rb - 2)):
+        bad = list(ok); bad[idx] = val
+        assert l.b200_mul_mat_q(*bad) == -2, idx
+    assert l.b200_quantize_act(x.data_ptr(), k, k, 1, sc.data_ptr() + 8, None) == -2
+    assert l.b200_mul_mat_vec_q(t, w.data_ptr(), rb, m, k, sc.data_ptr() + 8, 1, d.data_ptr(), m, None) == -2
+    torch.cuda.synchronize()

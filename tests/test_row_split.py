@@ -108,3 +108,18 @@ def test_row_split_two_gpus_matches_one_gpu(tmp_path, b200, oracle):
     assert split.shape == single.shape and np.isfinite(split).all()
     for a, b in zip(split, single):
         assert oracle.nmse(b, a) <= 1e-6                               # same kernels, same per-row arithmetic
+
+
+@pytest.mark.gpu
+def test_barrier_wait_runs_out_and_the_context_stays_usable(b200, oracle, golden):
+    """Failure detection without a fault: the cross-GPU barrier kernel as rank 0 of 2 on one GPU, its peer's flag never
+    written.  The bounded wait gives up after the (test-size) limit, the status word says ERR_PEER_TIMEOUT, the kernel
+    returns; afterwards the same context computes a MUL_MAT correctly and a barrier whose peer has arrived passes."""
+    import ctypes as C
+    l = b200.lib()
+    st = C.c_int(-1)
+    assert l.b200_peer_barrier_probe_host(2000, 0, C.byref(st)) == 0, l.b200_last_error()
+    assert st.value == 3                                         # ERR_PEER_TIMEOUT
+    got = b200.mul_mat_q("q4_K", golden["mul_mat.w.q4_K"], golden["mul_mat.x"])
+    assert oracle.nmse(oracle.mul_mat("q4_K", golden["mul_mat.w.q4_K"], golden["mul_mat.x"]), got) <= 5e-4
+    assert l.b200_peer_barrier_probe_host(2000, 1, C.byref(st)) == 0 and st.value == 0

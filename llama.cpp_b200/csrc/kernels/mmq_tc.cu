@@ -21,8 +21,14 @@
 //              token; warps w and w+4 share a lane quadrant and split the columns) and coalesced stores.
 //   warp 8     one elected thread issues 4 x tcgen05.mma (M128 N128 K16) per k-step from shared-memory
 //              matrix descriptors; tcgen05.commit frees the stage / publishes the accumulator.
-// 4-stage ring of 32 KB stages; every mbarrier wait is bounded and failure is reported through the
-// status word; TMEM (128 columns) is allocated and released by warp 8 on every path.
+//   warp 9     loader (types whose 256-value row chunks are 16-byte multiples: Q4_K, Q5_K, Q8_0, Q4_0, ...): brings the
+//              raw quant bytes of the tile's 128 rows, one 256-deep K chunk at a time, into a double-buffered
+//              shared-memory tile with cp.async.bulk (plain, non-multicast), one copy per row.  The producers then
+//              read their bytes with shared-memory loads: a warp-wide global load of one row per thread touched 32
+//              sectors and the load/store unit, not the tensor core, set the pace.  The other types keep the
+//              producers' own global loads.
+// Ring of 32 KB / 48 KB operand stages; every mbarrier wait is bounded and failure is reported through the
+// status word; TMEM is allocated and released by warp 8 on every path.
 #include "common.cuh"
 #include "kernels.h"
 #include <cuda.h>
@@ -30,9 +36,9 @@
 namespace b200 {
 
 static constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
-static constexpr int TC_STAGES = 4;
 static constexpr int TC_PRODUCERS = 256;
-static constexpr int TC_THREADS = TC_PRODUCERS + 32;
+static constexpr int TC_THREADS = TC_PRODUCERS + 64;                  // + the MMA warp and the loader warp
+static constexpr int TC_CHUNK_K = 256;                                // K values per staged raw chunk (4 k-steps)
 static constexpr int TC_PF = 4;                                        // k-steps of raw weight bytes in flight per producer thread
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
@@ -102,6 +108,7 @@ template <int T> struct Deq32 {                     // generic path: element-wis
     static constexpr int KPR = 1;                                   // k-steps covered by one Raw
     struct Raw { const uint8_t * row; int k; };
     static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) { r.row = row; r.k = k; }
+    static __device__ __forceinline__ void load_s(const uint8_t * b, int k, Raw & r) { r.row = b; r.k = k; }   // dequant_elem reads with plain loads
     static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
 #pragma unroll 4
         for (int i = 0; i < 16; ++i) out[i] = pack_h2(dequant_elem<T>(r.row, r.k + 2 * i), dequant_elem<T>(r.row, r.k + 2 * i + 1));
@@ -118,6 +125,12 @@ template <> struct Deq32<T_Q4_K> {
         r.hd = __ldg((const uint4 *) b);
         r.qa = __ldg((const uint4 *) (b + 16 + 32 * (r.sb >> 1)));
         r.qb = __ldg((const uint4 *) (b + 32 + 32 * (r.sb >> 1)));
+    }
+    static __device__ __forceinline__ void load_s(const uint8_t * b, int k, Raw & r) {       // b: the row's chunk in shared memory
+        r.sb = (k >> 5) & 7;
+        r.hd = *(const uint4 *) b;
+        r.qa = *(const uint4 *) (b + 16 + 32 * (r.sb >> 1));
+        r.qb = *(const uint4 *) (b + 32 + 32 * (r.sb >> 1));
     }
     static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
         const float2 dm = __half22float2(u32_as_h2(r.hd.x));
@@ -153,6 +166,18 @@ template <> struct Deq32<T_Q5_K> {
             const int o = 48 + 32 * ((r.sb0 + 2 * s) >> 1);
             r.qa[s] = __ldg((const uint4 *) (b + o));
             r.qb[s] = __ldg((const uint4 *) (b + o + 16));
+        }
+    }
+    static __device__ __forceinline__ void load_s(const uint8_t * b, int k, Raw & r) {
+        r.sb0 = (k >> 5) & 7;
+        r.hd = *(const uint4 *) b;
+        r.ha = *(const uint4 *) (b + 16);
+        r.hb = *(const uint4 *) (b + 32);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            const int o = 48 + 32 * ((r.sb0 + 2 * s) >> 1);
+            r.qa[s] = *(const uint4 *) (b + o);
+            r.qb[s] = *(const uint4 *) (b + o + 16);
         }
     }
     static __device__ __forceinline__ void get(const Raw & r, int sub, uint32_t (&out)[16]) {
@@ -199,6 +224,21 @@ template <> struct Deq32<T_Q6_K> {
         r.sc[1] = *(const uint16_t *) (ps + 4);
         r.d = *(const uint16_t *) (b + 208);
     }
+    static __device__ __forceinline__ void load_s(const uint8_t * b, int k, Raw & r) {       // b: the row's super-block in shared memory
+        const int n128 = (k >> 7) & 1;
+        r.t0 = (k >> 5) & 1;
+        const uint8_t * pl = b + n128 * 64 + r.t0 * 32;
+        const uint8_t * ph = b + 128 + n128 * 32;
+        const uint32_t * al = (const uint32_t *) ((uintptr_t) pl & ~(uintptr_t) 3);
+        const uint32_t * ah = (const uint32_t *) ((uintptr_t) ph & ~(uintptr_t) 3);
+        r.sh = ((uint32_t) (uintptr_t) pl & 3u) * 8u;
+#pragma unroll
+        for (int i = 0; i < 9; ++i) { r.ql[i] = al[i]; r.qh[i] = ah[i]; }
+        const uint8_t * ps = b + 192 + n128 * 8 + 2 * r.t0;
+        r.sc[0] = *(const uint16_t *) ps;
+        r.sc[1] = *(const uint16_t *) (ps + 4);
+        r.d = *(const uint16_t *) (b + 208);
+    }
     static __device__ __forceinline__ void get(const Raw & r, int sub, uint32_t (&out)[16]) {
         const float d = __half2float(__ushort_as_half((unsigned short) r.d));
         const uint32_t scw = sub ? r.sc[1] : r.sc[0];
@@ -232,10 +272,23 @@ __device__ __forceinline__ void load_block32(const uint8_t * pb, uint32_t (&q)[N
     for (int i = 0; i < NQ; ++i) q[i] = odd ? w[i + 1] : __funnelshift_r(w[i], w[i + 1], 16);
 }
 
+template <int NQ>
+__device__ __forceinline__ void load_block32_s(const uint8_t * pb, uint32_t (&q)[NQ], uint32_t & d) {       // shared memory
+    const uint32_t * al = (const uint32_t *) ((uintptr_t) pb & ~(uintptr_t) 3);
+    const bool odd = ((uintptr_t) pb & 2) != 0;
+    uint32_t w[NQ + 1];
+#pragma unroll
+    for (int i = 0; i < NQ + 1; ++i) w[i] = al[i];
+    d = odd ? (w[0] >> 16) : (w[0] & 0xffffu);
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) q[i] = odd ? w[i + 1] : __funnelshift_r(w[i], w[i + 1], 16);
+}
+
 template <> struct Deq32<T_Q4_0> {
     static constexpr int KPR = 1;                                   // k-steps covered by one Raw
     struct Raw { uint32_t w[4]; uint32_t d; };
     static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) { load_block32<4>(row + (k >> 5) * 18, r.w, r.d); }
+    static __device__ __forceinline__ void load_s(const uint8_t * b, int k, Raw & r) { load_block32_s<4>(b + (k >> 5) * 18, r.w, r.d); }
     static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
         const __half2 d = __half2half2(__ushort_as_half((unsigned short) r.d)), off = u32_as_h2(0x48004800u);   // 8.0
 #pragma unroll
@@ -252,6 +305,7 @@ template <> struct Deq32<T_Q8_0> {
     static constexpr int KPR = 1;                                   // k-steps covered by one Raw
     struct Raw { uint32_t w[8]; uint32_t d; };
     static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) { load_block32<8>(row + (k >> 5) * 34, r.w, r.d); }
+    static __device__ __forceinline__ void load_s(const uint8_t * b, int k, Raw & r) { load_block32_s<8>(b + (k >> 5) * 34, r.w, r.d); }
     static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
         const __half2 d = __half2half2(__ushort_as_half((unsigned short) r.d)), off = u32_as_h2(0x58005800u);   // 128.0
 #pragma unroll
@@ -268,6 +322,7 @@ template <> struct Deq32<T_IQ4_NL> {
     static constexpr int KPR = 1;
     struct Raw { uint32_t w[4]; uint32_t d; };
     static __device__ __forceinline__ void load(const uint8_t * row, int k, Raw & r) { load_block32<4>(row + (k >> 5) * 18, r.w, r.d); }
+    static __device__ __forceinline__ void load_s(const uint8_t * b, int k, Raw & r) { load_block32_s<4>(b + (k >> 5) * 18, r.w, r.d); }
     static __device__ __forceinline__ void get(const Raw & r, uint32_t (&out)[16]) {
         const __half2 d = __half2half2(__ushort_as_half((unsigned short) r.d)), off = u32_as_h2(0x58005800u);   // 128.0
 #pragma unroll
@@ -377,6 +432,20 @@ template <> struct Deq32<T_Q3_K> {
     }
 };
 
+// Staging of raw blocks through shared memory.  SRC: bytes of one row's 256-value chunk; BYTES: bytes per row of the box
+// that is copied (0: not staged).  A tensor copy starts on a 16-byte boundary, so where SRC is not a multiple of 16 the
+// box starts at the boundary below the chunk and is wide enough for every remainder; readers add the remainder.
+template <int T> struct TcChunk { static constexpr int SRC = 0, BYTES = 0; };
+template <> struct TcChunk<T_Q4_K>   { static constexpr int SRC = 144, BYTES = 144; };
+template <> struct TcChunk<T_Q5_K>   { static constexpr int SRC = 176, BYTES = 176; };
+template <> struct TcChunk<T_Q6_K>   { static constexpr int SRC = 210, BYTES = 240; };    // 210 + 14 = 224; 240 spreads rows over 8 banks
+template <> struct TcChunk<T_Q8_0>   { static constexpr int SRC = 272, BYTES = 272; };
+template <> struct TcChunk<T_Q4_0>   { static constexpr int SRC = 144, BYTES = 144; };
+template <> struct TcChunk<T_IQ4_NL> { static constexpr int SRC = 144, BYTES = 144; };
+template <> struct TcChunk<T_Q4_1>   { static constexpr int SRC = 160, BYTES = 160; };
+template <> struct TcChunk<T_Q5_0>   { static constexpr int SRC = 176, BYTES = 176; };
+template <> struct TcChunk<T_Q5_1>   { static constexpr int SRC = 192, BYTES = 192; };
+
 // ---- F32 -> F16 activations (pre-pass) --------------------------------------------------------
 __global__ void tc_convert_x_kernel(const float * __restrict__ x, int64_t x_nb1 /*bytes*/, __half * __restrict__ y, int64_t K, int64_t N) {
     pdl_enter();
@@ -390,6 +459,7 @@ __global__ void tc_convert_x_kernel(const float * __restrict__ x, int64_t x_nb1 
 
 // ---- the GEMM kernel ---------------------------------------------------------------------------
 struct TcParams {
+    int staged;                 // raw blocks come through shared memory by tensor copies (needs 16-byte aligned rows)
     const uint8_t * W; int64_t w_nb1;
     const __half * Xh;                 // [N][K] F16 (read through the tensor map)
     float * dst; int64_t dst_nb1;      // bytes between token columns
@@ -408,14 +478,30 @@ __device__ __forceinline__ void tma_load_2d(void * smem_dst, const CUtensorMap *
 
 // BN: token columns per CTA, 128 or 256.  The wide tile halves the number of times a weight tile is dequantized (the
 // producers, not the tensor core, bound this kernel) and is used when it still leaves every SM a CTA.
+template <int BN> struct TcCfg {
+    static constexpr int STAGES = BN == 256 ? 3 : 4;
+    // (+16: the readers of 2-byte aligned blocks look one word past the last block of a row)
+    template <int T> static __host__ __device__ constexpr int raw_bytes() { return (TC_BM * TcChunk<T>::BYTES + 16 + 127) & ~127; }
+    template <int T> static __host__ __device__ constexpr int raw_bufs() {
+        return TcChunk<T>::BYTES == 0 ? 0 : ((size_t) STAGES * (TC_BM + BN) * TC_BK * 2 + 3 * (size_t) raw_bytes<T>() + 2048 <= 232448 ? 3 : 2);
+    }
+    template <int T> static __host__ __device__ constexpr size_t smem_bytes() { return (size_t) STAGES * (TC_BM + BN) * TC_BK * 2 + (size_t) raw_bufs<T>() * raw_bytes<T>() + 1024; }
+};
+
 template <int T, int BN>
-__global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap xmap) {
+__global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap) {
+    constexpr int STAGES = TcCfg<BN>::STAGES;
     constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;            // 32 KB / 48 KB
+    constexpr int CB = TcChunk<T>::BYTES;                             // raw bytes of one row's 256-value chunk (0: not staged)
+    constexpr bool STAGED = CB > 0;
+    constexpr int RAW_BYTES = TcCfg<BN>::template raw_bytes<T>();     // one raw tile [128 rows][CB], padded to the 128-byte TMA alignment
+    constexpr int NRB = TcCfg<BN>::template raw_bufs<T>();            // raw tiles in flight
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     pdl_launch_dependents();          // the next kernel may start its prologue (its weight prefetch) right away
     // operand stages must be 1024-byte aligned for the 128-byte swizzle pattern
     uint8_t * smem = (uint8_t *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
-    __shared__ uint64_t full_bar[TC_STAGES], empty_bar[TC_STAGES], accum_bar;
+    uint8_t * rawbuf = smem + (size_t) STAGES * STAGE_BYTES;          // the raw tiles
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar, raw_full[3], raw_empty[3];
     __shared__ uint32_t tmem_base_sh;
     __shared__ int abort_flag;
 
@@ -424,11 +510,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
     const int ks_begin = (int) blockIdx.z * p.kps;                  // split-K: this CTA's range of k-steps
     const int ksteps = min(p.kps, p.K / TC_BK - ks_begin);
     const int k_base = ks_begin * TC_BK;
-    constexpr int MMA_WARP = TC_PRODUCERS / 32;
+    constexpr int MMA_WARP = TC_PRODUCERS / 32;                       // the warp after it is the loader
 
     if (tid == 0) {
         // per stage: one arrival per producer warp + 1 arrive.expect_tx for the activation tile
-        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full_bar[s], TC_PRODUCERS / 32 + 1); mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], TC_PRODUCERS / 32 + 1); mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < 3; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], TC_PRODUCERS / 32); }
         mbar_init(&accum_bar, 1);
         abort_flag = 0;
         mbar_fence_init();
@@ -444,44 +531,72 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         const int r = tid & 127, h = tid >> 7;                          // operand row, which 32 of the 64 k-values
         const bool wrow_ok = m0 + r < p.M;
         const uint8_t * wrow = p.W + (int64_t) (wrow_ok ? m0 + r : 0) * p.w_nb1;
-        // raw quant bytes of the next TC_PF k-steps are kept in flight in registers (HBM latency is several
-        // k-steps long); weights do not depend on the previous kernel, so the first loads precede the wait
         constexpr int KPR = Deq32<T>::KPR;                              // k-steps covered by one Raw
-        constexpr int NRAW = TC_PF / KPR;
-        typename Deq32<T>::Raw raw[NRAW];
-#pragma unroll
-        for (int u = 0; u < NRAW; ++u) if (u * KPR < ksteps) Deq32<T>::load(wrow, k_base + u * KPR * TC_BK + h * 32, raw[u]);
-        pdl_wait();
         bool ok = true;
-        for (int ks0 = 0; ks0 < ksteps && ok; ks0 += TC_PF) {
+        // one k-step: the F16 values `wv` of this thread go into stage s, then the warp arrives
+        auto emit = [&](int ks, uint32_t (&wv)[16]) -> bool {
+            const int s = ks % STAGES;
+            const uint32_t round = (uint32_t) (ks / STAGES);
+            if (ks >= STAGES && !mbar_wait(&empty_bar[s], (round - 1) & 1)) return false;
+            if (*(volatile int *) &abort_flag) return false;
+            uint8_t * sa = smem + (size_t) s * STAGE_BYTES;          // A: weights 128 x 64 F16
+            if (tid == 0) {                                             // B: activations BN x 64 F16 by TMA (rows past N read as zero)
+                mbar_arrive_expect_tx(&full_bar[s], BN * TC_BK * 2);
+                tma_load_2d(sa + TC_BM * TC_BK * 2, &xmap, k_base + ks * TC_BK, n0, &full_bar[s]);
+            }
+            if (!wrow_ok) {
 #pragma unroll
-            for (int u = 0; u < TC_PF; ++u) {
-                const int ks = ks0 + u;
-                if (ks >= ksteps || !ok) break;
-                const int s = ks % TC_STAGES;
-                const uint32_t round = (uint32_t) (ks / TC_STAGES);
-                if (ks >= TC_STAGES && !mbar_wait(&empty_bar[s], (round - 1) & 1)) { ok = false; break; }
-                if (*(volatile int *) &abort_flag) { ok = false; break; }
-                uint8_t * sa = smem + (size_t) s * STAGE_BYTES;      // A: weights 128 x 64 F16
-                if (tid == 0) {                                         // B: activations 128 x 64 F16 by TMA (rows past N read as zero)
-                    mbar_arrive_expect_tx(&full_bar[s], BN * TC_BK * 2);
-                    tma_load_2d(sa + TC_BM * TC_BK * 2, &xmap, k_base + ks * TC_BK, n0, &full_bar[s]);
+                for (int i = 0; i < 16; ++i) wv[i] = 0;
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                *(uint4 *) (sa + r * 128 + (((4 * h + c) ^ (r & 7)) << 4)) = make_uint4(wv[4 * c], wv[4 * c + 1], wv[4 * c + 2], wv[4 * c + 3]);
+            fence_async_smem();                                         // make the generic-proxy stores visible to the tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_bar[s]);                   // one arrival per warp: 257 arrivals on one barrier serialise
+            return true;
+        };
+        if constexpr (STAGED) if (p.staged) {
+            // raw quant bytes arrive in shared memory, one 256-deep chunk (4 k-steps) of all 128 rows at a time
+            pdl_wait();
+            for (int c = 0; c * 4 < ksteps && ok; ++c) {
+                const int buf = c % NRB;
+                if (!mbar_wait(&raw_full[buf], (uint32_t) (c / NRB) & 1)) { ok = false; break; }
+                const uint8_t * rrow = rawbuf + (size_t) buf * RAW_BYTES + r * CB + (((k_base / TC_CHUNK_K + c) * TcChunk<T>::SRC) & 15);
+                typename Deq32<T>::Raw raw;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int ks = c * 4 + u;
+                    if (ks >= ksteps || !ok) break;
+                    uint32_t wv[16];
+                    if (u % KPR == 0) Deq32<T>::load_s(rrow, u * TC_BK + h * 32, raw);
+                    if constexpr (KPR == 1) Deq32<T>::get(raw, wv); else Deq32<T>::get(raw, u % KPR, wv);
+                    if (!emit(ks, wv)) ok = false;
                 }
-                uint32_t wv[16];
-                const int ru = u / KPR, sub = u % KPR;        // constants once the loop is unrolled
-                if constexpr (KPR == 1) Deq32<T>::get(raw[ru], wv); else Deq32<T>::get(raw[ru], sub, wv);
-                // the Raw is free after its last k-step: refill it with the one NRAW pairs ahead
-                if (sub == KPR - 1 && ks + 1 + (NRAW - 1) * KPR < ksteps) Deq32<T>::load(wrow, k_base + (ks + 1 + (NRAW - 1) * KPR) * TC_BK + h * 32, raw[ru]);
-                if (!wrow_ok) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) wv[i] = 0;
-                }
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    *(uint4 *) (sa + r * 128 + (((4 * h + c) ^ (r & 7)) << 4)) = make_uint4(wv[4 * c], wv[4 * c + 1], wv[4 * c + 2], wv[4 * c + 3]);
-                fence_async_smem();                                     // make the generic-proxy stores visible to the tensor core
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&full_bar[s]);               // one arrival per warp: 257 arrivals on one barrier serialise
+                if (lane == 0) mbar_arrive(&raw_empty[buf]);            // this warp has read the chunk
+            }
+        }
+        if (!STAGED || !p.staged) {
+            // raw quant bytes of the next TC_PF k-steps are kept in flight in registers (HBM latency is several
+            // k-steps long); weights do not depend on the previous kernel, so the first loads precede the wait
+            constexpr int NRAW = TC_PF / KPR;
+            typename Deq32<T>::Raw raw[NRAW];
+#pragma unroll
+            for (int u = 0; u < NRAW; ++u) if (u * KPR < ksteps) Deq32<T>::load(wrow, k_base + u * KPR * TC_BK + h * 32, raw[u]);
+            pdl_wait();
+            for (int ks0 = 0; ks0 < ksteps && ok; ks0 += TC_PF) {
+#pragma unroll
+                for (int u = 0; u < TC_PF; ++u) {
+                    const int ks = ks0 + u;
+                    if (ks >= ksteps || !ok) break;
+                    uint32_t wv[16];
+                    const int ru = u / KPR, sub = u % KPR;        // constants once the loop is unrolled
+                    if constexpr (KPR == 1) Deq32<T>::get(raw[ru], wv); else Deq32<T>::get(raw[ru], sub, wv);
+                    // the Raw is free after its last k-step: refill it with the one NRAW pairs ahead
+                    if (sub == KPR - 1 && ks + 1 + (NRAW - 1) * KPR < ksteps) Deq32<T>::load(wrow, k_base + (ks + 1 + (NRAW - 1) * KPR) * TC_BK + h * 32, raw[ru]);
+                    if (!emit(ks, wv)) ok = false;
+                }
             }
         }
         if (!ok && lane == 0) { atomicExch(p.status, ERR_MBAR_TIMEOUT); abort_flag = 1; }
@@ -509,13 +624,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         } else if (ok && lane == 0) {
             atomicExch(p.status, ERR_MBAR_TIMEOUT);
         }
-    } else {
+    } else if (warp == MMA_WARP) {
         // ------------------------------ MMA issuer ------------------------------
         constexpr uint32_t idesc = umma_idesc_f16(TC_BM, BN);
         bool ok = true;
         for (int ks = 0; ks < ksteps && ok; ++ks) {
-            const int s = ks % TC_STAGES;
-            const uint32_t round = (uint32_t) (ks / TC_STAGES);
+            const int s = ks % STAGES;
+            const uint32_t round = (uint32_t) (ks / STAGES);
             if (!mbar_wait(&full_bar[s], round & 1)) { ok = false; break; }
             if (*(volatile int *) &abort_flag) { ok = false; break; }
             tc_fence_after();
@@ -533,6 +648,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
             __syncwarp();
         }
         if (!ok && lane == 0) { atomicExch(p.status, ERR_MBAR_TIMEOUT); abort_flag = 1; }
+    } else {
+        // ------------------------------ loader ------------------------------
+        // One tensor copy per chunk: the box is CB bytes (as 32-bit words) of 128 consecutive rows, laid down densely;
+        // rows past M read as zero.  Weights do not depend on the kernel launched before this one, so the first
+        // chunks are requested right away.
+        if constexpr (STAGED) if (p.staged) {
+            const int nchunks = (ksteps + 3) / 4;
+            bool ok = true;
+            if (lane == 0) {
+                int c = 0;
+                for (; c < nchunks; ++c) {
+                    const int buf = c % NRB;
+                    if (c >= NRB && !mbar_wait(&raw_empty[buf], (uint32_t) (c / NRB - 1) & 1)) { ok = false; break; }
+                    if (*(volatile int *) &abort_flag) break;
+                    mbar_arrive_expect_tx(&raw_full[buf], TC_BM * CB);
+                    tma_load_2d(rawbuf + (size_t) buf * RAW_BYTES, &wmap, (((k_base / TC_CHUNK_K + c) * TcChunk<T>::SRC) >> 4) * 4, m0, &raw_full[buf]);
+                }
+                if (!ok) { atomicExch(p.status, ERR_MBAR_TIMEOUT); abort_flag = 1; }
+                // When the kernel gives up, the last copies of this thread may still be in flight: wait (bounded) for
+                // each of them before the CTA's shared memory is released.  In a normal run the producers have waited
+                // for every chunk.
+                if (!ok || *(volatile int *) &abort_flag) {
+                    for (int cc = max(0, c - NRB); cc < c; ++cc) mbar_wait(&raw_full[cc % NRB], (uint32_t) (cc / NRB) & 1);
+                }
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -550,6 +691,13 @@ bool mmq_tc_ptr_ok(int type, const void * W, int64_t w_nb1, const void * X, int6
     if (((uintptr_t) X & 7) || (x_nb1 & 7)) return false;
     if (type == T_Q4_K || type == T_Q5_K) return ((uintptr_t) W & 15) == 0 && (w_nb1 & 15) == 0;
     return ((uintptr_t) W & 1) == 0 && (w_nb1 & 1) == 0;
+}
+// Raw blocks can be staged by tensor copies when whole 256-value chunks tile K, rows start on 16-byte boundaries and a
+// row is a whole number of 32-bit words.
+template <int T> static bool tc_can_stage(const TcParams & p) {
+    if (TcChunk<T>::BYTES == 0 || p.K % TC_CHUNK_K) return false;
+    const int64_t row_bytes = (int64_t) (p.K / TC_CHUNK_K) * TcChunk<T>::SRC;
+    return ((uintptr_t) p.W & 15) == 0 && (p.w_nb1 & 15) == 0 && (row_bytes & 3) == 0 && p.w_nb1 >= row_bytes;
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -595,9 +743,9 @@ size_t mmq_tc_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count) {
 }
 
 template <int T, int BN>
-static cudaError_t launch_tc_tb(const TcParams & p, int device, int use_pdl, cudaStream_t stream) {
+static cudaError_t launch_tc_tb(const TcParams & p_in, int device, int use_pdl, cudaStream_t stream) {
     auto kern = mmq_tc_kernel<T, BN>;
-    const size_t smem = (size_t) TC_STAGES * (TC_BM + BN) * TC_BK * 2 + 1024;
+    const size_t smem = TcCfg<BN>::template smem_bytes<T>();
     static unsigned attr_mask = 0;
     if (!(attr_mask & (1u << device))) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
@@ -607,6 +755,8 @@ static cudaError_t launch_tc_tb(const TcParams & p, int device, int use_pdl, cud
     // tensor map of the F16 activations [N][K]: boxes of 64 (k) x BN (tokens), 128-byte swizzle, zero fill
     encode_tiled_fn enc = get_encode_tiled();
     if (!enc) return cudaErrorNotSupported;
+    TcParams p = p_in;
+    p.staged = tc_can_stage<T>(p) ? 1 : 0;
     CUtensorMap xmap;
     const cuuint64_t gdim[2] = {(cuuint64_t) p.K, (cuuint64_t) p.N};
     const cuuint64_t gstr[1] = {(cuuint64_t) p.K * 2};
@@ -614,8 +764,19 @@ static cudaError_t launch_tc_tb(const TcParams & p, int device, int use_pdl, cud
     if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *) p.Xh, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
+    // tensor map of the raw weight rows as 32-bit words [M][row bytes / 4]: boxes of one 256-value chunk x 128 rows
+    CUtensorMap wmap = xmap;
+    if (p.staged) {
+        constexpr cuuint32_t CW = TcChunk<T>::BYTES / 4;
+        const cuuint64_t wdim[2] = {(cuuint64_t) (p.K / TC_CHUNK_K) * TcChunk<T>::SRC / 4, (cuuint64_t) p.M};
+        const cuuint64_t wstr[1] = {(cuuint64_t) p.w_nb1};
+        const cuuint32_t wbox[2] = {CW, TC_BM};
+        if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void *) p.W, wdim, wstr, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
     dim3 grid((unsigned) ((p.N + BN - 1) / BN), (unsigned) ((p.M + TC_BM - 1) / TC_BM), (unsigned) p.ksplit);
-    cudaError_t e = launch_k(use_pdl, stream, kern, grid, dim3(TC_THREADS), smem, p, xmap);
+    cudaError_t e = launch_k(use_pdl, stream, kern, grid, dim3(TC_THREADS), smem, p, xmap, wmap);
     if (e != cudaSuccess || p.ksplit == 1) return e;
     const int64_t total = (int64_t) p.M * p.N;
     int64_t g = (total + 255) / 256; if (g > 148 * 8) g = 148 * 8;
@@ -644,7 +805,7 @@ cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float *
     p.M = (int) M; p.N = (int) N; p.K = (int) K; p.status = c.status;
     p.ksplit = partials ? mmq_tc_ksplit(M, N, K, c.sm_count) : 1;
     const int ksteps = (int) (K / TC_BK);
-    p.kps = (ksteps + p.ksplit - 1) / p.ksplit; p.kps += p.kps & 1;          // even
+    p.kps = (ksteps + p.ksplit - 1) / p.ksplit; p.kps = (p.kps + 3) & ~3;    // whole 256-value chunks (and pairs of k-steps)
     p.ksplit = (ksteps + p.kps - 1) / p.kps;                                   // splits that actually have work
     p.part = (float *) partials;
     switch (type) {

@@ -36,7 +36,8 @@
 namespace b200 {
 
 static constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
-static constexpr int TC_PRODUCERS = 256;
+static constexpr int TC_GROUP = 256;                                  // threads that dequantize one k-step: 128 rows x two 32-value halves
+static constexpr int TC_PRODUCERS = 2 * TC_GROUP;                      // two groups work on different k-steps at the same time
 static constexpr int TC_THREADS = TC_PRODUCERS + 64;                  // + the MMA warp and the loader warp
 static constexpr int TC_CHUNK_K = 256;                                // K values per staged raw chunk (4 k-steps)
 static constexpr int TC_PF = 4;                                        // k-steps of raw weight bytes in flight per producer thread
@@ -60,6 +61,23 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar_smem) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar_smem) : "memory");
+}
+// bounded wait on the mbarrier at shared-memory address `bar`; the give-up flag of the CTA is looked at only while waiting
+__device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity, const int * abort_flag, int limit = (1 << 22)) {
+    for (int i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (*(const volatile int *) abort_flag) return false;
+    }
+    return false;
+}
 __device__ __forceinline__ void umma_commit(uint64_t * bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
 }
@@ -74,6 +92,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {   // A from tensor memory
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :: "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's lane (lane = 32 * (warp % 4) + lane id)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart
@@ -479,19 +512,21 @@ __device__ __forceinline__ void tma_load_2d(void * smem_dst, const CUtensorMap *
 // BN: token columns per CTA, 128 or 256.  The wide tile halves the number of times a weight tile is dequantized (the
 // producers, not the tensor core, bound this kernel) and is used when it still leaves every SM a CTA.
 template <int BN> struct TcCfg {
-    static constexpr int STAGES = BN == 256 ? 3 : 4;
+    static constexpr int STAGES = 4;
+    static constexpr int TMEM_COLS = BN == 256 ? 512 : 256;          // accumulator (BN columns) + the ring of weight tiles (32 columns each)
     // (+16: the readers of 2-byte aligned blocks look one word past the last block of a row)
     template <int T> static __host__ __device__ constexpr int raw_bytes() { return (TC_BM * TcChunk<T>::BYTES + 16 + 127) & ~127; }
     template <int T> static __host__ __device__ constexpr int raw_bufs() {
-        return TcChunk<T>::BYTES == 0 ? 0 : ((size_t) STAGES * (TC_BM + BN) * TC_BK * 2 + 3 * (size_t) raw_bytes<T>() + 2048 <= 232448 ? 3 : 2);
+        return TcChunk<T>::BYTES == 0 ? 0 : ((size_t) STAGES * BN * TC_BK * 2 + 3 * (size_t) raw_bytes<T>() + 2048 <= 232448 ? 3 : 2);
     }
-    template <int T> static __host__ __device__ constexpr size_t smem_bytes() { return (size_t) STAGES * (TC_BM + BN) * TC_BK * 2 + (size_t) raw_bufs<T>() * raw_bytes<T>() + 1024; }
+    template <int T> static __host__ __device__ constexpr size_t smem_bytes() { return (size_t) STAGES * BN * TC_BK * 2 + (size_t) raw_bufs<T>() * raw_bytes<T>() + 1024; }
 };
 
 template <int T, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap) {
     constexpr int STAGES = TcCfg<BN>::STAGES;
-    constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;            // 32 KB / 48 KB
+    constexpr int STAGE_BYTES = BN * TC_BK * 2;                       // activation tile: 16 KB / 32 KB
+    constexpr uint32_t A_COL0 = BN;                                   // tensor-memory column of the first weight tile
     constexpr int CB = TcChunk<T>::BYTES;                             // raw bytes of one row's 256-value chunk (0: not staged)
     constexpr bool STAGED = CB > 0;
     constexpr int RAW_BYTES = TcCfg<BN>::template raw_bytes<T>();     // one raw tile [128 rows][CB], padded to the 128-byte TMA alignment
@@ -513,14 +548,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
     constexpr int MMA_WARP = TC_PRODUCERS / 32;                       // the warp after it is the loader
 
     if (tid == 0) {
-        // per stage: one arrival per producer warp + 1 arrive.expect_tx for the activation tile
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], TC_PRODUCERS / 32 + 1); mbar_init(&empty_bar[s], 1); }
+        // per stage: one arrival per warp of the producing group + 1 arrive.expect_tx for the activation tile
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], TC_GROUP / 32 + 1); mbar_init(&empty_bar[s], 1); }
         for (int s = 0; s < 3; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], TC_PRODUCERS / 32); }
         mbar_init(&accum_bar, 1);
         abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == MMA_WARP) tmem_alloc(&tmem_base_sh, BN);
+    if (warp == MMA_WARP) tmem_alloc(&tmem_base_sh, TcCfg<BN>::TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -528,7 +563,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
 
     if (warp < MMA_WARP) {
         // ------------------------------ producers ------------------------------
-        const int r = tid & 127, h = tid >> 7;                          // operand row, which 32 of the 64 k-values
+        // Two groups of 8 warps: group g takes the k-step pairs (4c + 2g, 4c + 2g + 1) of every 256-value chunk c, so two
+        // k-steps are being dequantized at any time (one group alone leaves each scheduler two warps and is bound by
+        // instruction latency).  A group is never more than 3 k-steps past its previous one, which keeps its parity waits
+        // on the stage ring within one phase of the tensor core's progress.
+        const int r = tid & 127, h = (tid >> 7) & 1, g = tid >> 8;      // operand row, which 32 of the 64 k-values, group
         const bool wrow_ok = m0 + r < p.M;
         const uint8_t * wrow = p.W + (int64_t) (wrow_ok ? m0 + r : 0) * p.w_nb1;
         constexpr int KPR = Deq32<T>::KPR;                              // k-steps covered by one Raw
@@ -537,21 +576,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         auto emit = [&](int ks, uint32_t (&wv)[16]) -> bool {
             const int s = ks % STAGES;
             const uint32_t round = (uint32_t) (ks / STAGES);
-            if (ks >= STAGES && !mbar_wait(&empty_bar[s], (round - 1) & 1)) return false;
-            if (*(volatile int *) &abort_flag) return false;
-            uint8_t * sa = smem + (size_t) s * STAGE_BYTES;          // A: weights 128 x 64 F16
-            if (tid == 0) {                                             // B: activations BN x 64 F16 by TMA (rows past N read as zero)
+            if (ks >= STAGES && !mbar_wait_or_abort(smem_u32(&empty_bar[s]), (round - 1) & 1, &abort_flag)) return false;
+            tc_fence_after();                                           // the tensor core has finished reading this stage
+            if ((tid & (TC_GROUP - 1)) == 0) {                          // B: activations BN x 64 F16 by TMA (rows past N read as zero)
                 mbar_arrive_expect_tx(&full_bar[s], BN * TC_BK * 2);
-                tma_load_2d(sa + TC_BM * TC_BK * 2, &xmap, k_base + ks * TC_BK, n0, &full_bar[s]);
+                tma_load_2d(smem + (size_t) s * STAGE_BYTES, &xmap, k_base + ks * TC_BK, n0, &full_bar[s]);
             }
             if (!wrow_ok) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) wv[i] = 0;
             }
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                *(uint4 *) (sa + r * 128 + (((4 * h + c) ^ (r & 7)) << 4)) = make_uint4(wv[4 * c], wv[4 * c + 1], wv[4 * c + 2], wv[4 * c + 3]);
-            fence_async_smem();                                         // make the generic-proxy stores visible to the tensor core
+            // A: this thread's 32 F16 weights are 16 columns of its row's lane in tensor memory (two values per column)
+            tmem_st16(tmem_base + ((uint32_t) ((warp & 3) * 32) << 16) + A_COL0 + (uint32_t) (s * (TC_BK / 2) + h * 16), wv);
+            tmem_st_wait();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&full_bar[s]);                   // one arrival per warp: 257 arrivals on one barrier serialise
             return true;
@@ -561,24 +599,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
             pdl_wait();
             for (int c = 0; c * 4 < ksteps && ok; ++c) {
                 const int buf = c % NRB;
-                if (!mbar_wait(&raw_full[buf], (uint32_t) (c / NRB) & 1)) { ok = false; break; }
+                if (!mbar_wait_or_abort(smem_u32(&raw_full[buf]), (uint32_t) (c / NRB) & 1, &abort_flag)) { ok = false; break; }
                 const uint8_t * rrow = rawbuf + (size_t) buf * RAW_BYTES + r * CB + (((k_base / TC_CHUNK_K + c) * TcChunk<T>::SRC) & 15);
                 typename Deq32<T>::Raw raw;
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int ks = c * 4 + u;
+                for (int uu = 0; uu < 2; ++uu) {
+                    const int u = 2 * g + uu, ks = c * 4 + u;
                     if (ks >= ksteps || !ok) break;
                     uint32_t wv[16];
-                    if (u % KPR == 0) Deq32<T>::load_s(rrow, u * TC_BK + h * 32, raw);
-                    if constexpr (KPR == 1) Deq32<T>::get(raw, wv); else Deq32<T>::get(raw, u % KPR, wv);
+                    if (uu % KPR == 0) Deq32<T>::load_s(rrow, u * TC_BK + h * 32, raw);
+                    if constexpr (KPR == 1) Deq32<T>::get(raw, wv); else Deq32<T>::get(raw, uu % KPR, wv);
                     if (!emit(ks, wv)) ok = false;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&raw_empty[buf]);            // this warp has read the chunk
             }
         }
-        if (!STAGED || !p.staged) {
-            // raw quant bytes of the next TC_PF k-steps are kept in flight in registers (HBM latency is several
+        if ((!STAGED || !p.staged) && g == 0) {
+            // (one group only on this path) raw quant bytes of the next TC_PF k-steps are kept in flight in registers (HBM latency is several
             // k-steps long); weights do not depend on the previous kernel, so the first loads precede the wait
             constexpr int NRAW = TC_PF / KPR;
             typename Deq32<T>::Raw raw[NRAW];
@@ -604,12 +642,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         // ------------------------------ epilogue ------------------------------
         if (ok && mbar_wait(&accum_bar, 0)) {
             tc_fence_after();
-            const int quad = warp & 3, chalf = warp >> 2;               // lane quadrant; which half of the BN columns
+            const int quad = warp & 3, cq = warp >> 2;                  // lane quadrant; which quarter of the BN columns
             const int m = m0 + quad * 32 + lane;
             char * out = p.ksplit > 1 ? (char *) (p.part + (int64_t) blockIdx.z * p.M * p.N) : (char *) p.dst;
             const int64_t out_nb1 = p.ksplit > 1 ? (int64_t) p.M * 4 : p.dst_nb1;
 #pragma unroll 1
-            for (int c0 = chalf * (BN / 2); c0 < chalf * (BN / 2) + BN / 2; c0 += 32) {
+            for (int c0 = cq * (BN / 4); c0 < cq * (BN / 4) + BN / 4; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t) (quad * 32) << 16) + (uint32_t) c0, v);
                 tmem_ld_wait();
@@ -626,28 +664,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------ MMA issuer ------------------------------
+        // One thread runs this loop, and every k-step has to pass through it: it is kept to a wait, a fence, four
+        // tcgen05.mma and a commit, with the stage's descriptors derived by one addition (the address field of a
+        // shared-memory descriptor counts 16-byte units, and shared memory is smaller than the field).
         constexpr uint32_t idesc = umma_idesc_f16(TC_BM, BN);
-        bool ok = true;
-        for (int ks = 0; ks < ksteps && ok; ++ks) {
-            const int s = ks % STAGES;
-            const uint32_t round = (uint32_t) (ks / STAGES);
-            if (!mbar_wait(&full_bar[s], round & 1)) { ok = false; break; }
-            if (*(volatile int *) &abort_flag) { ok = false; break; }
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t a_addr = smem_u32(smem + (size_t) s * STAGE_BYTES);
-                const uint32_t b_addr = a_addr + TC_BM * TC_BK * 2;
+        if (lane == 0) {
+            bool ok = true;
+            const uint64_t bdesc0 = umma_smem_desc(smem_u32(smem));
+            const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+            int s = 0; uint32_t ph = 0;
+            for (int ks = 0; ks < ksteps; ++ks) {
+                if (!mbar_wait_or_abort(full0 + 8 * s, ph, &abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t bd = bdesc0 + (uint64_t) (s * (STAGE_BYTES >> 4));
+                const uint32_t ta = tmem_base + A_COL0 + (uint32_t) (s * (TC_BK / 2));
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk) {
-                    // advancing 16 K-elements = 32 bytes inside the 128-byte swizzle atom
-                    umma_f16(tmem_base, umma_smem_desc(a_addr + kk * 32), umma_smem_desc(b_addr + kk * 32), idesc, (ks | kk) != 0);
-                }
-                umma_commit(&empty_bar[s]);                             // frees the stage once these MMAs have read it
-                if (ks == ksteps - 1) umma_commit(&accum_bar);          // accumulator complete
+                for (int kk = 0; kk < TC_BK / 16; ++kk)                 // 16 K-elements: 8 columns of A, 32 bytes of B inside the 128-byte swizzle atom
+                    umma_f16_ts(tmem_base, ta + 8 * kk, bd + 2 * kk, idesc, (ks | kk) != 0);
+                umma_commit_addr(empty0 + 8 * s);                       // frees the stage once these MMAs have read it
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
-            __syncwarp();
+            if (ok) umma_commit(&accum_bar);                            // accumulator complete
+            else { atomicExch(p.status, ERR_MBAR_TIMEOUT); abort_flag = 1; }
         }
-        if (!ok && lane == 0) { atomicExch(p.status, ERR_MBAR_TIMEOUT); abort_flag = 1; }
+        __syncwarp();
     } else {
         // ------------------------------ loader ------------------------------
         // One tensor copy per chunk: the box is CB bytes (as 32-bit words) of 128 consecutive rows, laid down densely;
@@ -677,7 +717,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, BN); }
+    if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, TcCfg<BN>::TMEM_COLS); }
 }
 
 bool mmq_tc_supported(int type, int64_t M, int64_t N, int64_t K) {

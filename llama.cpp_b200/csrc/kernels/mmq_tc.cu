@@ -670,19 +670,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         constexpr uint32_t idesc = umma_idesc_f16(TC_BM, BN);
         if (lane == 0) {
             bool ok = true;
-            const uint64_t bdesc0 = umma_smem_desc(smem_u32(smem));
-            const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
-            int s = 0; uint32_t ph = 0;
-            for (int ks = 0; ks < ksteps; ++ks) {
-                if (!mbar_wait_or_abort(full0 + 8 * s, ph, &abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                const uint64_t bd = bdesc0 + (uint64_t) (s * (STAGE_BYTES >> 4));
-                const uint32_t ta = tmem_base + A_COL0 + (uint32_t) (s * (TC_BK / 2));
+            // every descriptor and address of the loop is a register set up here
+            uint64_t bd[STAGES][TC_BK / 16];
+            uint32_t ta[STAGES][TC_BK / 16];
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk)                 // 16 K-elements: 8 columns of A, 32 bytes of B inside the 128-byte swizzle atom
-                    umma_f16_ts(tmem_base, ta + 8 * kk, bd + 2 * kk, idesc, (ks | kk) != 0);
-                umma_commit_addr(empty0 + 8 * s);                       // frees the stage once these MMAs have read it
-                if (++s == STAGES) { s = 0; ph ^= 1; }
+            for (int s = 0; s < STAGES; ++s)
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk) {               // 16 K-elements: 8 columns of A, 32 bytes of B inside the 128-byte swizzle atom
+                    bd[s][kk] = umma_smem_desc(smem_u32(smem) + s * STAGE_BYTES + kk * 32);
+                    ta[s][kk] = tmem_base + A_COL0 + (uint32_t) (s * (TC_BK / 2) + 8 * kk);
+                }
+            const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+            uint32_t ph = 0, acc = 0;
+            for (int ks0 = 0; ks0 < ksteps && ok; ks0 += STAGES, ph ^= 1) {
+#pragma unroll
+                for (int s = 0; s < STAGES; ++s) {
+                    if (ks0 + s >= ksteps) break;
+                    if (!mbar_wait_or_abort(full0 + 8 * s, ph, &abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    umma_f16_ts(tmem_base, ta[s][0], bd[s][0], idesc, acc);
+                    acc = 1;
+#pragma unroll
+                    for (int kk = 1; kk < TC_BK / 16; ++kk) umma_f16_ts(tmem_base, ta[s][kk], bd[s][kk], idesc, 1);
+                    umma_commit_addr(empty0 + 8 * s);                   // frees the stage once these MMAs have read it
+                }
             }
             if (ok) umma_commit(&accum_bar);                            // accumulator complete
             else { atomicExch(p.status, ERR_MBAR_TIMEOUT); abort_flag = 1; }

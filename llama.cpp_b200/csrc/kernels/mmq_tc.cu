@@ -582,10 +582,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
                 mbar_arrive_expect_tx(&full_bar[s], BN * TC_BK * 2);
                 tma_load_2d(smem + (size_t) s * STAGE_BYTES, &xmap, k_base + ks * TC_BK, n0, &full_bar[s]);
             }
-            if (!wrow_ok) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) wv[i] = 0;
-            }
             // A: this thread's 32 F16 weights are 16 columns of its row's lane in tensor memory (two values per column)
             tmem_st16(tmem_base + ((uint32_t) ((warp & 3) * 32) << 16) + A_COL0 + (uint32_t) (s * (TC_BK / 2) + h * 16), wv);
             tmem_st_wait();
@@ -631,6 +627,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
                     uint32_t wv[16];
                     const int ru = u / KPR, sub = u % KPR;        // constants once the loop is unrolled
                     if constexpr (KPR == 1) Deq32<T>::get(raw[ru], wv); else Deq32<T>::get(raw[ru], sub, wv);
+                    if (!wrow_ok) {                     // (this path reads row 0 in place of rows past M)
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) wv[i] = 0;
+                    }
                     // the Raw is free after its last k-step: refill it with the one NRAW pairs ahead
                     if (sub == KPR - 1 && ks + 1 + (NRAW - 1) * KPR < ksteps) Deq32<T>::load(wrow, k_base + (ks + 1 + (NRAW - 1) * KPR) * TC_BK + h * 32, raw[ru]);
                     if (!emit(ks, wv)) ok = false;

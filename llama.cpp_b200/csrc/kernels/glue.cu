@@ -96,34 +96,46 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
     const int64_t npad = (n + 127) & ~(int64_t) 127;
     blk_act128 * col = EMIT ? act + row * (npad >> 7) : nullptr;
 
-    // fast path (the usual case: one row of a few thousand values): every thread keeps its four values
-    // in registers between the reduction and the output, so the row is read exactly once
-    const bool fast = (n & 3) == 0 && npad <= (int64_t) blockDim.x * 4 && (!HAS_W || w.ne[0] == n) &&
+    // fast path (the usual case: one row of a few thousand values): every thread keeps its values (up to four groups of
+    // four) in registers between the reduction and the output, so the row is read exactly once
+    constexpr int MAXV = 4;
+    const int nv = (int) ((npad / 4 + blockDim.x - 1) / blockDim.x);
+    const bool fast = (n & 3) == 0 && nv <= MAXV && (!HAS_W || w.ne[0] == n) &&
                       (((uintptr_t) x | (uintptr_t) y | (uintptr_t) wr | (uintptr_t) yn | (uintptr_t) addend | (uintptr_t) sum_out) & 15) == 0;
     if (fast) {
-        const int64_t k0 = (int64_t) threadIdx.x * 4;
-        const bool in = k0 < n;
-        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f), wv = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-        if (in) {
-            v = *(const float4 *) (x + k0);
-            if (HAS_W) wv = *(const float4 *) (wr + k0);
-            if (addend) {
-                const float4 a4 = *(const float4 *) (addend + row * n + k0);
-                v.x += a4.x; v.y += a4.y; v.z += a4.z; v.w += a4.w;
-                *(float4 *) (sum_out + row * n + k0) = v;
+        float4 v[MAXV];
+        float part = 0.0f;
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            v[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const int64_t k0 = ((int64_t) j * blockDim.x + threadIdx.x) * 4;
+            if (j < nv && k0 < n) {
+                v[j] = *(const float4 *) (x + k0);
+                if (addend) {
+                    const float4 a4 = *(const float4 *) (addend + row * n + k0);
+                    v[j].x += a4.x; v[j].y += a4.y; v[j].z += a4.z; v[j].w += a4.w;
+                    *(float4 *) (sum_out + row * n + k0) = v[j];
+                }
+                part += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
             }
         }
-        const float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, sh);
+        const float ss = block_sum(part, sh);
         const float scale = rsqrtf(ss / (float) n + eps);
-        float o[4] = {v.x * scale, v.y * scale, v.z * scale, v.w * scale};
-        if (in && yn) *(float4 *) (yn + k0) = make_float4(o[0], o[1], o[2], o[3]);
-        if (HAS_W) { o[0] *= wv.x; o[1] *= wv.y; o[2] *= wv.z; o[3] *= wv.w; }
-        if (in) *(float4 *) (y + k0) = make_float4(o[0], o[1], o[2], o[3]);
-        if (in && h16) {                                          // F16 copy for a tensor-core mat-mul (dense rows of n)
-            __half2 * hp = (__half2 *) (h16 + row * n + k0);
-            hp[0] = __floats2half2_rn(o[0], o[1]); hp[1] = __floats2half2_rn(o[2], o[3]);
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const int64_t k0 = ((int64_t) j * blockDim.x + threadIdx.x) * 4;
+            if (j >= nv) break;
+            const bool in = k0 < n;
+            float o[4] = {v[j].x * scale, v[j].y * scale, v[j].z * scale, v[j].w * scale};
+            if (in && yn) *(float4 *) (yn + k0) = make_float4(o[0], o[1], o[2], o[3]);
+            if (HAS_W && in) { const float4 wv = *(const float4 *) (wr + k0); o[0] *= wv.x; o[1] *= wv.y; o[2] *= wv.z; o[3] *= wv.w; }
+            if (in) *(float4 *) (y + k0) = make_float4(o[0], o[1], o[2], o[3]);
+            if (in && h16) {                                          // F16 copy for a tensor-core mat-mul (dense rows of n)
+                __half2 h0 = __floats2half2_rn(o[0], o[1]), h1 = __floats2half2_rn(o[2], o[3]);
+                *(uint2 *) (h16 + row * n + k0) = make_uint2(*(uint32_t *) &h0, *(uint32_t *) &h1);
+            }
+            if (EMIT && k0 < npad) emit_act128(o, k0, npad, col);     // whole warps take this branch together (npad % 128 == 0)
         }
-        if (EMIT && k0 < npad) emit_act128(o, k0, npad, col);     // whole warps take this branch together (npad % 128 == 0)
         return;
     }
 
@@ -167,7 +179,8 @@ __global__ void rms_norm_kernel(const TensorD src, const TensorD w, const Tensor
     }
 }
 
-static int row_block(int64_t n) { return n >= 4096 ? 1024 : (n >= 1024 ? 512 : (n >= 256 ? 256 : 128)); }
+// threads per row: 16 values each where the row allows it (more rows resident per SM, one short reduction)
+static int row_block(int64_t n) { const int64_t b = ((n + 15) / 16 + 31) & ~(int64_t) 31; return (int) (b < 128 ? 128 : (b > 1024 ? 1024 : b)); }
 
 cudaError_t launch_rms_norm(const TensorD & src, const TensorD & dst, float eps, const LaunchCtx & c) {
     const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
@@ -360,6 +373,22 @@ __global__ void silu_mul_kernel(const float * g, const float * u, float * y,
     const int64_t npad = (n0 + 127) & ~(int64_t) 127;
     const int64_t per_row = npad / 4;
     const int64_t total = per_row * rows;
+    // rows that are whole 128-value blocks at 16-byte aligned addresses: 128-bit loads and stores, no row arithmetic
+    if (n0 == npad && ((((uintptr_t) g | (uintptr_t) u | (uintptr_t) y | (uintptr_t) silu_out) & 15) == 0) && (((uintptr_t) h16 & 7) == 0)) {
+        for (int64_t t = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t) gridDim.x * blockDim.x) {
+            const float4 a4 = ((const float4 *) g)[t], u4 = ((const float4 *) u)[t];
+            const float4 s4 = make_float4(a4.x / (1.0f + expf(-a4.x)), a4.y / (1.0f + expf(-a4.y)), a4.z / (1.0f + expf(-a4.z)), a4.w / (1.0f + expf(-a4.w)));
+            float v[4] = {s4.x * u4.x, s4.y * u4.y, s4.z * u4.z, s4.w * u4.w};
+            if (silu_out) ((float4 *) silu_out)[t] = s4;
+            ((float4 *) y)[t] = make_float4(v[0], v[1], v[2], v[3]);
+            if (h16) {
+                __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+                ((uint2 *) h16)[t] = make_uint2(*(uint32_t *) &h0, *(uint32_t *) &h1);
+            }
+            if (EMIT) { const int64_t row = t / per_row; emit_act128(v, (t - row * per_row) * 4, npad, act + row * (npad >> 7)); }
+        }
+        return;
+    }
     // whole warps stay together (emit_act128 shuffles), so loop bounds are warp-uniform
     const int64_t total_w = (total + 31) & ~(int64_t) 31;
     for (int64_t t = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; t < total_w; t += (int64_t) gridDim.x * blockDim.x) {
@@ -476,41 +505,67 @@ struct RopeKvArgs {
     int hd, n_head, n_head_kv;
     RopeK r;
 };
-__global__ void rope_kv_kernel(const RopeKvArgs a) {
+// Block layout: blocks [0, n_tok * hb) take one token and ROPE_HPB heads of the combined list (query heads, then key
+// heads): the cos / sin pair of every rotation index is computed once per block into shared memory and applied to all its
+// heads.  The blocks after those convert V.
+static constexpr int ROPE_HPB = 8;          // heads per block
+static constexpr int ROPE_MAX_HALF = 256;   // head sizes up to 512
+__global__ void rope_kv_kernel(const RopeKvArgs a, int64_t n_tok, int hb) {
     pdl_enter();
-    const int64_t total = a.q_pairs + a.k_pairs + a.v_pairs;
+    __shared__ float2 cs[ROPE_MAX_HALF];
     const int half_hd = a.hd / 2;
     __half * kc = (__half *) ((char *) a.k_cache + (a.k_off ? *a.k_off : a.k_off_imm));
     __half * vc = (__half *) ((char *) a.v_cache + (a.v_off ? *a.v_off : a.v_off_imm));
-    for (int64_t t = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t) gridDim.x * blockDim.x) {
-        if (t >= a.q_pairs + a.k_pairs) {
-            const int64_t i = t - a.q_pairs - a.k_pairs;
-            const float2 v = ((const float2 *) a.v_src)[i];
-            ((__half2 *) vc)[i] = __floats2half2_rn(v.x, v.y);
-            continue;
+    const int64_t rope_blocks = n_tok * hb;
+    if ((int64_t) blockIdx.x >= rope_blocks) {
+        // V: F32 -> F16 into the cache rows
+        const int64_t nvb = (int64_t) gridDim.x - rope_blocks;
+        const int64_t quads = a.v_pairs / 2;
+        for (int64_t i = ((int64_t) blockIdx.x - rope_blocks) * blockDim.x + threadIdx.x; i < quads; i += nvb * blockDim.x) {
+            const float4 v = ((const float4 *) a.v_src)[i];
+            __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+            ((uint2 *) vc)[i] = make_uint2(*(uint32_t *) &h0, *(uint32_t *) &h1);
         }
-        const bool is_k = t >= a.q_pairs;
-        const int64_t i = is_k ? t - a.q_pairs : t;
-        const int heads = is_k ? a.n_head_kv : a.n_head;
-        const int ip = (int) (i % half_hd);
-        const int64_t rowi = i / half_hd;                       // (token, head) row
-        const int64_t tok = rowi / heads;
+        if ((a.v_pairs & 1) && blockIdx.x == rope_blocks && threadIdx.x == 0) {
+            const float2 v = ((const float2 *) a.v_src)[a.v_pairs - 1];
+            ((__half2 *) vc)[a.v_pairs - 1] = __floats2half2_rn(v.x, v.y);
+        }
+        return;
+    }
+    const int64_t tok = blockIdx.x / hb;
+    const int h0 = (int) (blockIdx.x % hb) * ROPE_HPB;
+    const int h1 = min(h0 + ROPE_HPB, a.n_head + a.n_head_kv);
+    const int half_rot = min(a.r.n_dims / 2, half_hd);
+    const float p = (float) a.pos[tok];
+    for (int ip = threadIdx.x; ip < half_rot; ip += blockDim.x) {
+        const float theta_base = p * powf(a.r.theta_scale, (float) ip);
+        const float f = a.ff ? a.ff[ip] : 1.0f;
+        float c, sn;
+        rope_cs(a.r, theta_base / f, 2 * ip, c, sn);
+        cs[ip] = make_float2(c, sn);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < (h1 - h0) * half_hd; idx += blockDim.x) {
+        const int head = h0 + idx / half_hd, ip = idx % half_hd;
+        const bool is_k = head >= a.n_head;
+        const int64_t rowi = is_k ? tok * a.n_head_kv + (head - a.n_head) : tok * a.n_head + head;
         const float * xs = (is_k ? a.k_src : a.q_src) + rowi * a.hd;
         float *       yd = (is_k ? a.k_dst : a.q_dst) + rowi * a.hd;
         const int i0 = 2 * ip;
         float o0, o1; int ia, ib;
         if (i0 >= a.r.n_dims) { ia = i0; ib = i0 + 1; o0 = xs[ia]; o1 = xs[ib]; }
         else {
-            const float theta_base = (float) a.pos[tok] * powf(a.r.theta_scale, (float) ip);
-            const float f = a.ff ? a.ff[ip] : 1.0f;
-            float c, s;
-            rope_cs(a.r, theta_base / f, i0, c, s);
+            const float2 c = cs[ip];
             ia = a.r.neox ? ip : i0; ib = a.r.neox ? ip + a.r.n_dims / 2 : i0 + 1;
             const float x0 = xs[ia], x1 = xs[ib];
-            o0 = x0 * c - x1 * s; o1 = x0 * s + x1 * c;
+            o0 = x0 * c.x - x1 * c.y; o1 = x0 * c.y + x1 * c.x;
         }
-        yd[ia] = o0; yd[ib] = o1;
-        if (is_k) { kc[rowi * a.hd + ia] = __float2half_rn(o0); kc[rowi * a.hd + ib] = __float2half_rn(o1); }
+        if (ib == ia + 1) *(float2 *) (yd + ia) = make_float2(o0, o1);      // (hd is even and rows are 8-byte aligned)
+        else { yd[ia] = o0; yd[ib] = o1; }
+        if (is_k) {
+            if (ib == ia + 1) *(__half2 *) (kc + rowi * a.hd + ia) = __floats2half2_rn(o0, o1);
+            else { kc[rowi * a.hd + ia] = __float2half_rn(o0); kc[rowi * a.hd + ib] = __float2half_rn(o1); }
+        }
     }
 }
 static RopeK make_ropek(const RopeParams & rp) {
@@ -536,7 +591,10 @@ cudaError_t launch_rope_kv(const RopeKvLaunch & l, const RopeParams & rp, const 
     a.r = make_ropek(rp);
     const int64_t total = a.q_pairs + a.k_pairs + a.v_pairs;
     if (total == 0) return cudaSuccess;
-    (void) (launch_err = launch_k(c.use_pdl, c.stream, rope_kv_kernel, dim3(grid_for(total, 256, c.sm_count)), dim3(256), 0, a));
+    if (l.hd / 2 > ROPE_MAX_HALF || (l.hd & 1)) return cudaErrorInvalidValue;
+    const int hb = (int) ((l.n_head + l.n_head_kv + ROPE_HPB - 1) / ROPE_HPB);
+    int64_t vblocks = (a.v_pairs / 2 + 1023) / 1024; if (vblocks > 4 * c.sm_count) vblocks = 4 * c.sm_count; if (a.v_pairs && vblocks < 1) vblocks = 1;
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, rope_kv_kernel, dim3((unsigned) (l.n_tok * hb + vblocks)), dim3(256), 0, a, (int64_t) l.n_tok, hb));
     return B200_LAUNCH_CHECK();
 }
 

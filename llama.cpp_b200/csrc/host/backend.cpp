@@ -217,8 +217,19 @@ static bool backend_is_ours(ggml_backend_t backend) { return backend && backend-
 
 static void backend_free(ggml_backend_t backend) {
     BackendCtx * ctx = (BackendCtx *) backend->context;
+    for (BackendCtx::SplitPeer & sp : ctx->split_peer) {            // helper instances on the other devices (row-split mat-muls)
+        if (!sp.helper) continue;
+        BackendCtx * h = (BackendCtx *) sp.helper->context;
+        set_device(h->dev->device);
+        cudaStreamSynchronize(h->stream);
+        if (sp.x) cudaFree(sp.x);
+        if (sp.d) cudaFree(sp.d);
+        if (sp.done) cudaEventDestroy(sp.done);
+        backend_free(sp.helper);
+    }
     set_device(ctx->dev->device);
     cudaStreamSynchronize(ctx->stream);
+    if (ctx->split_ready) cudaEventDestroy(ctx->split_ready);
     if (getenv("GGML_B200_VERBOSE"))
         fprintf(stderr, "ggml-b200: %s: graph_compute calls: %llu replayed from a CUDA graph, %llu captured, %llu run directly; %llu kernel launches, %llu of them persistent decode steps\n",
                 ctx->name.c_str(), (unsigned long long) ctx->n_replay, (unsigned long long) ctx->n_capture, (unsigned long long) ctx->n_direct,
@@ -334,6 +345,8 @@ static void dev_get_props(ggml_backend_dev_t dev, ggml_backend_dev_props * props
     props->caps.buffer_from_host_ptr = false;
     props->caps.events = true;
 }
+void free_backend(ggml_backend_t backend) { backend_free(backend); }
+ggml_backend_t init_backend_for(DeviceCtx * d) { return d->dev.iface.init_backend(&d->dev, nullptr); }
 static ggml_backend_t dev_init_backend(ggml_backend_dev_t dev, const char * /*params*/) {
     DeviceCtx * d = (DeviceCtx *) dev->context;
     set_device(d->device);
@@ -373,7 +386,7 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t dev, const char * /*pa
 }
 static bool dev_supports_op(ggml_backend_dev_t dev, const ggml_tensor * op) { return device_supports_op((DeviceCtx *) dev->context, op); }
 static bool dev_supports_buft(ggml_backend_dev_t dev, ggml_backend_buffer_type_t buft) {
-    if (buft_is_split(buft)) return true;
+    if (buft_is_split(buft)) return buft->device == dev;        // a split matrix is consumed by the backend of its main device
     return buft_is_ours(buft) && buft->context == dev->context;
 }
 static bool dev_offload_op(ggml_backend_dev_t, const ggml_tensor * op) {

@@ -29,6 +29,15 @@ struct BufferCtx {
     size_t size;
 };
 
+// row-split buffer type (split.cpp): what hangs off tensor->extra of a matrix stored in it
+static constexpr int SPLIT_MAX_DEVICES = 16;
+static constexpr uint32_t SPLIT_EXTRA_MAGIC = 0xb2005917u;
+struct SplitExtra {
+    uint32_t magic;
+    void *   data[SPLIT_MAX_DEVICES];                   // the device's slice (registry index), null where it has no rows
+    int64_t  row_low[SPLIT_MAX_DEVICES], row_high[SPLIT_MAX_DEVICES];
+};
+
 // per-backend (stream) state
 struct BackendCtx {
     DeviceCtx *  dev = nullptr;
@@ -106,6 +115,13 @@ struct BackendCtx {
         return rs->magic == GGML_B200_ROW_SLICE_MAGIC ? rs : nullptr;
     }
 
+    // MUL_MAT on a matrix of the row-split buffer type: one helper instance (stream, scratch, status word) per other
+    // device, the activations' copy and the result slice on that device, and the events that order the exchange
+    struct SplitPeer { ggml_backend_t helper = nullptr; void * x = nullptr; size_t x_cap = 0; void * d = nullptr; size_t d_cap = 0; cudaEvent_t done = nullptr; };
+    SplitPeer    split_peer[SPLIT_MAX_DEVICES];
+    cudaEvent_t  split_ready = nullptr;        // recorded on this stream when the activations may be read
+    bool         graph_has_split = false;      // per graph_compute call: such a graph is not captured into a CUDA graph
+
     LaunchCtx launch_ctx() const { return LaunchCtx{stream, dev->device, dev->sm_count, status_dev, use_pdl, fa_tickets}; }
     void *    get_scratch(size_t bytes);   // grows (after a stream sync) when needed
 };
@@ -116,6 +132,9 @@ bool buffer_is_ours(ggml_backend_buffer_t buf);
 bool buft_is_ours(ggml_backend_buffer_type_t buft);
 bool buft_is_split(ggml_backend_buffer_type_t buft);
 ggml_backend_buffer_type_t split_buffer_type(int main_device, const float * tensor_split);
+const SplitExtra * split_extra_of(const ggml_tensor * t);      // null unless t lives in a row-split buffer
+ggml_backend_t   init_backend_for(DeviceCtx * d);              // a backend instance on device d (what dev_init_backend returns)
+void             free_backend(ggml_backend_t backend);
 
 // decode_plan.cpp
 int              try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i);

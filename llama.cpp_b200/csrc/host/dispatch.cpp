@@ -42,6 +42,12 @@ bool device_supports_op(DeviceCtx * dev, const ggml_tensor * op) {
         const ggml_tensor * s = op->src[i];
         if (s && s->buffer && buft_is_split(s->buffer->buft) && !(op->op == GGML_OP_MUL_MAT && i == 0)) return false;
     }
+    // ... of a plain 2-D product on contiguous F32 activations (the reference's split path has the same limits:
+    // ggml/src/ggml-cuda/ggml-cuda.cu:3028-3040)
+    if (op->op == GGML_OP_MUL_MAT && op->src[0] && op->src[0]->buffer && buft_is_split(op->src[0]->buffer->buft)) {
+        const ggml_tensor * w = op->src[0], * x = op->src[1];
+        if (w->ne[2] != 1 || w->ne[3] != 1 || x->ne[2] != 1 || x->ne[3] != 1 || x->type != GGML_TYPE_F32 || !t_contiguous(x) || !t_contiguous(op)) return false;
+    }
     const ggml_tensor * a = op->src[0];
     const ggml_tensor * b = op->src[1];
     switch (op->op) {
@@ -351,6 +357,83 @@ static bool t_overlap(const ggml_tensor * a, const ggml_tensor * b) {
 }
 
 // Can MUL_MAT node `n` ride along with `first` in one grouped mat-vec launch?
+// MUL_MAT whose weight matrix lives in the row-split buffer type (split.cpp): every device that holds rows computes
+// its slice of the result on its own stream, from its own copy of the activations, and copies the slice into the
+// result on this (the main) device; this stream then waits for all of them.  The data flow of the reference's
+// ggml_cuda_op_mul_mat with split weights (ggml/src/ggml-cuda/ggml-cuda.cu:1520-1660): activations out by peer copy,
+// slices back by a strided peer copy, events in between.  The mat-mul itself is the ordinary path of this backend, run
+// by a helper instance on each other device.
+static bool run_split_mul_mat(BackendCtx * ctx, const ggml_tensor * dst) {
+    const ggml_tensor * W = dst->src[0];
+    const ggml_tensor * X = dst->src[1];
+    const SplitExtra * e = split_extra_of(W);
+    const int n_dev = (int) devices().size(), me = ctx->dev->index;
+    const int64_t ncols = X->ne[1];
+    const size_t xbytes = (size_t) X->ne[0] * (size_t) ncols * 4;
+    auto slice_tensors = [&](int id, void * x_data, void * d_data, size_t d_nb1, ggml_tensor & Wf, ggml_tensor & Xf, ggml_tensor & Df) {
+        const int64_t rows = e->row_high[id] - e->row_low[id];
+        Wf = *W; Wf.data = e->data[id]; Wf.ne[1] = rows; Wf.nb[2] = Wf.nb[3] = (size_t) rows * W->nb[1]; Wf.buffer = nullptr; Wf.extra = nullptr;
+        Xf = *X; Xf.data = x_data; Xf.buffer = nullptr; Xf.view_src = nullptr; Xf.extra = nullptr;
+        Df = *dst; Df.data = d_data; Df.ne[0] = rows; Df.nb[1] = d_nb1; Df.nb[2] = Df.nb[3] = d_nb1 * (size_t) ncols;
+        Df.src[0] = &Wf; Df.src[1] = &Xf; Df.buffer = nullptr; Df.view_src = nullptr; Df.extra = nullptr;
+    };
+    bool others = false;
+    for (int id = 0; id < n_dev; ++id) if (id != me && e->data[id]) others = true;
+    if (others) {
+        if (!ctx->split_ready) B200_CUDA_CHECK(cudaEventCreateWithFlags(&ctx->split_ready, cudaEventDisableTiming));
+        B200_CUDA_CHECK(cudaEventRecord(ctx->split_ready, ctx->stream));
+    }
+    for (int id = 0; id < n_dev; ++id) {
+        if (id == me || !e->data[id]) continue;
+        BackendCtx::SplitPeer & sp = ctx->split_peer[id];
+        DeviceCtx * d = devices()[(size_t) id];
+        B200_CUDA_CHECK(cudaSetDevice(d->device));
+        if (!sp.helper) {
+            sp.helper = init_backend_for(d);
+            if (!sp.helper) { cudaSetDevice(ctx->dev->device); return false; }
+            B200_CUDA_CHECK(cudaEventCreateWithFlags(&sp.done, cudaEventDisableTiming));
+            // direct copies between the two devices where the machine allows them (the copies work either way)
+            if (cudaDeviceEnablePeerAccess(ctx->dev->device, 0) != cudaSuccess) cudaGetLastError();
+            cudaSetDevice(ctx->dev->device);
+            if (cudaDeviceEnablePeerAccess(d->device, 0) != cudaSuccess) cudaGetLastError();
+            B200_CUDA_CHECK(cudaSetDevice(d->device));
+        }
+        BackendCtx * h = (BackendCtx *) sp.helper->context;
+        const int64_t rows = e->row_high[id] - e->row_low[id];
+        const size_t dbytes = (size_t) rows * (size_t) ncols * 4;
+        auto grow = [&](void *& p, size_t & cap, size_t need) {
+            if (need <= cap) return;
+            B200_CUDA_CHECK(cudaStreamSynchronize(h->stream));
+            if (p) B200_CUDA_CHECK(cudaFree(p));
+            cap = need + need / 2;
+            B200_CUDA_CHECK(cudaMalloc(&p, cap + 256));
+        };
+        grow(sp.x, sp.x_cap, xbytes);
+        grow(sp.d, sp.d_cap, dbytes);
+        B200_CUDA_CHECK(cudaStreamWaitEvent(h->stream, ctx->split_ready, 0));
+        B200_CUDA_CHECK(cudaMemcpyPeerAsync(sp.x, d->device, X->data, ctx->dev->device, xbytes, h->stream));
+        ggml_tensor Wf, Xf, Df;
+        slice_tensors(id, sp.x, sp.d, (size_t) rows * 4, Wf, Xf, Df);
+        h->act_cache_clear();                       // the copy lands at the same address every time, with new contents
+        const bool ok = run_mul_mat(h, &Df, nullptr);
+        ctx->n_launches += 1;
+        if (ok) {
+            B200_CUDA_CHECK(cudaMemcpy2DAsync((char *) dst->data + (size_t) e->row_low[id] * 4, dst->nb[1], sp.d, (size_t) rows * 4,
+                                              (size_t) rows * 4, (size_t) ncols, cudaMemcpyDeviceToDevice, h->stream));
+            B200_CUDA_CHECK(cudaEventRecord(sp.done, h->stream));
+        }
+        if (!ok) { cudaSetDevice(ctx->dev->device); return false; }
+    }
+    B200_CUDA_CHECK(cudaSetDevice(ctx->dev->device));
+    if (e->data[me]) {
+        ggml_tensor Wf, Xf, Df;
+        slice_tensors(me, X->data, (char *) dst->data + (size_t) e->row_low[me] * 4, dst->nb[1], Wf, Xf, Df);
+        if (!run_mul_mat(ctx, &Df, nullptr)) return false;
+    }
+    for (int id = 0; id < n_dev; ++id) if (id != me && e->data[id]) B200_CUDA_CHECK(cudaStreamWaitEvent(ctx->stream, ctx->split_peer[id].done, 0));
+    return true;
+}
+
 static bool groupable_mul_mat(const ggml_tensor * first, const ggml_tensor * n) {
     if (n->op != GGML_OP_MUL_MAT || n->src[1] != first->src[1]) return false;
     const ggml_tensor * w0 = first->src[0], * w = n->src[0];
@@ -439,6 +522,7 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
             // group also takes members from a little further down the graph: such a node depends only on the shared
             // activations and a weight leaf, and it may run early if its output does not alias anything the nodes
             // it jumps over touch (ggml-alloc reuses freed memory).
+            if (split_extra_of(dst->src[0])) return run_split_mul_mat(ctx, dst) ? 1 : 0;
             ggml_tensor * extra[2]; int n_extra = 0;
             if (ctx->use_fusion && group_head_ok(dst) && !buft_is_split(dst->src[0]->buffer ? dst->src[0]->buffer->buft : nullptr)) {
                 const bool sliced = ctx->row_slice_of(dst) != nullptr;
@@ -723,6 +807,7 @@ static uint64_t graph_signature(BackendCtx * ctx, const ggml_cgraph * g, int * n
         // only small batches are worth replaying; dim 1 of the activation operand is the token count (for MUL_MAT_ID
         // dim 2), the attention products of the non-flash path batch over heads in dims 2 and 3
         if (n->op == GGML_OP_MUL_MAT && n->src[1]->ne[1] > 8) return 0;
+        if (n->op == GGML_OP_MUL_MAT && split_extra_of(n->src[0])) return 0;     // work on several devices' streams: not captured
         if (n->op == GGML_OP_MUL_MAT_ID && n->src[1]->ne[2] > 8) return 0;
         const ggml_tensor * dd = dyn_cpy_dst(n);
         h = mix(h, (uint64_t) n->op | ((uint64_t) n->type << 32));
@@ -804,9 +889,5 @@ enum ggml_status graph_compute(BackendCtx * ctx, ggml_cgraph * cgraph) {
     ctx->n_launches += captured;
     return GGML_STATUS_SUCCESS;
 }
-
-// ---- row-split buffer type: provided by split.cpp once built; until then absent ----
-bool buft_is_split(ggml_backend_buffer_type_t) { return false; }
-ggml_backend_buffer_type_t split_buffer_type(int, const float *) { return nullptr; }
 
 }  // namespace b200

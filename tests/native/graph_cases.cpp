@@ -4,7 +4,8 @@
 // graph-level cases that single-op tests cannot express (memory reused inside a graph).  Public ggml API only;
 // built by oracle/ref.mk against the reference headers; test infrastructure.
 //   graph_cases DEVICE SUITE [N_THREADS]
-//   suites: mul_mat (the projection shapes x types x batch sizes), flash_attn, alias
+//   suites: mul_mat (the projection shapes x types x batch sizes), flash_attn, alias, split (weights in the device's
+//   row-split buffer type, ggml_backend_split_buffer_type by name: a scatter / gather round trip and MUL_MAT)
 // One line per case: "CASE <name> nmse=<x> max_abs=<y> n=<elements>"
 #include "ggml.h"
 #include "ggml-backend.h"
@@ -20,7 +21,8 @@
 
 struct Input { ggml_tensor * t; std::vector<uint8_t> bytes; };
 struct Built { std::vector<Input> inputs; std::vector<ggml_tensor *> outputs; ggml_cgraph * graph; size_t manual_bytes = 0;
-               std::vector<std::pair<ggml_tensor *, size_t>> placement; };   // manual placement: tensor -> offset (alias cases)
+               std::vector<std::pair<ggml_tensor *, size_t>> placement;      // manual placement: tensor -> offset (alias cases)
+               std::vector<ggml_tensor *> split; };                           // tensors that go into the row-split buffer type on the device
 using Builder = std::function<Built(ggml_context *)>;
 
 static std::vector<float> normal(size_t n, float sigma, unsigned seed) {
@@ -46,11 +48,22 @@ static std::vector<uint8_t> quantized(ggml_type type, int64_t K, int64_t rows, u
     return out;
 }
 
+static ggml_backend_buffer_type_t g_split_buft = nullptr;      // set by the split suite; used for Built::split on the device only
+static ggml_backend_t g_cpu, g_dev;
+static int g_fail = 0;
+
 static std::vector<std::vector<float>> run_on(ggml_backend_t backend, const Builder & build) {
     ggml_init_params ip = {ggml_tensor_overhead() * 64 + ggml_graph_overhead(), nullptr, true};
     ggml_context * ctx = ggml_init(ip);
     Built b = build(ctx);
     ggml_backend_buffer_t buf = nullptr;
+    std::vector<ggml_backend_buffer_t> split_bufs;
+    if (backend == g_dev && g_split_buft) for (ggml_tensor * w : b.split) {
+        ggml_backend_buffer_t sb = ggml_backend_buft_alloc_buffer(g_split_buft, ggml_backend_buft_get_alloc_size(g_split_buft, w));
+        if (!sb) { fprintf(stderr, "split buffer allocation failed\n"); exit(1); }
+        ggml_backend_tensor_alloc(sb, w, ggml_backend_buffer_get_base(sb));
+        split_bufs.push_back(sb);
+    }
     if (b.manual_bytes) {
         buf = ggml_backend_alloc_buffer(backend, b.manual_bytes);
         char * base = (char *) ggml_backend_buffer_get_base(buf);
@@ -70,13 +83,22 @@ static std::vector<std::vector<float>> run_on(ggml_backend_t backend, const Buil
         ggml_backend_tensor_get(t, v.data(), 0, v.size() * 4);
         outs.push_back(std::move(v));
     }
+    if (backend == g_dev && g_split_buft) for (auto & in : b.inputs) {
+        // what was scattered over the devices reads back as the same bytes
+        bool is_split = false;
+        for (ggml_tensor * w : b.split) if (w == in.t) is_split = true;
+        if (!is_split) continue;
+        std::vector<uint8_t> back(in.bytes.size());
+        ggml_backend_tensor_get(in.t, back.data(), 0, back.size());
+        const bool same = memcmp(back.data(), in.bytes.data(), back.size()) == 0;
+        printf("ROUNDTRIP %s %s bytes=%zu\n", in.t->name, same ? "identical" : "DIFFERENT", back.size());
+        if (!same) g_fail = 1;
+    }
     ggml_backend_buffer_free(buf);
+    for (ggml_backend_buffer_t sb : split_bufs) ggml_backend_buffer_free(sb);
     ggml_free(ctx);
     return outs;
 }
-
-static ggml_backend_t g_cpu, g_dev;
-static int g_fail = 0;
 static void run_case(const std::string & name, const Builder & build) {
     auto want = run_on(g_cpu, build), got = run_on(g_dev, build);
     double num = 0, den = 0, mx = 0; size_t n = 0; bool finite = true;
@@ -196,6 +218,52 @@ static void suite_alias() {
     });
 }
 
+// MUL_MAT with the weights in the row-split buffer type.  Row counts that are not multiples of the 128-row rounding, an
+// uneven split, batch sizes of both the mat-vec and the tensor-core path.
+static void suite_split(ggml_backend_dev_t dev) {
+    typedef ggml_backend_buffer_type_t (*split_fn_t)(int, const float *);
+    ggml_backend_reg_t reg = ggml_backend_dev_backend_reg(dev);
+    split_fn_t fn = (split_fn_t) ggml_backend_reg_get_proc_address(reg, "ggml_backend_split_buffer_type");
+    if (!fn) { printf("SPLIT unavailable: the registry has no ggml_backend_split_buffer_type\n"); g_fail = 1; return; }
+    int main_index = -1;
+    const int n_dev = (int) ggml_backend_reg_dev_count(reg);
+    for (int i = 0; i < n_dev; ++i) if (ggml_backend_reg_dev_get(reg, (size_t) i) == dev) main_index = i;
+    printf("SPLIT devices=%d main=%d\n", n_dev, main_index);
+    float uneven[16] = {0};
+    for (int i = 0; i < n_dev && i < 16; ++i) uneven[i] = i == 0 ? 3.0f : 1.0f;
+    const float * splits[2] = {nullptr, uneven};
+    const ggml_type types[] = {GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, GGML_TYPE_Q8_0, GGML_TYPE_F16};
+    for (int si = 0; si < 2; ++si) {
+        g_split_buft = fn(main_index, splits[si]);
+        if (!g_split_buft) { printf("SPLIT unavailable: the entry point returned NULL\n"); g_fail = 1; return; }
+        printf("SPLIT buffer type %s\n", ggml_backend_buft_name(g_split_buft));
+        for (ggml_type type : types) for (int64_t N : {1, 8, 64, 512}) {
+            const int64_t K = 4096, M = si == 0 ? 4096 : 4096 + 200;
+            run_case(std::string("split.") + (si ? "uneven." : "equal.") + ggml_type_name(type) + ".m" + std::to_string(M) + ".n" + std::to_string(N), [=](ggml_context * ctx) {
+                Built b;
+                ggml_tensor * w = ggml_new_tensor_2d(ctx, type, K, M), * x = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, K, N);
+                ggml_set_name(w, "w");
+                ggml_tensor * y = ggml_mul_mat(ctx, w, x);
+                b.graph = ggml_new_graph(ctx);
+                ggml_build_forward_expand(b.graph, y);
+                if (type == GGML_TYPE_F16) {
+                    std::vector<float> wf = normal((size_t) K * M, 0.02f, 5);
+                    std::vector<uint8_t> wb((size_t) K * M * 2);
+                    ggml_fp32_to_fp16_row(wf.data(), (ggml_fp16_t *) wb.data(), K * M);
+                    b.inputs.push_back({w, wb});
+                } else {
+                    b.inputs.push_back({w, quantized(type, K, M, 7)});
+                }
+                b.inputs.push_back({x, as_bytes(normal((size_t) K * N, 1.0f, 11 + (unsigned) N))});
+                b.outputs = {y};
+                b.split = {w};
+                return b;
+            });
+        }
+    }
+    g_split_buft = nullptr;
+}
+
 int main(int argc, char ** argv) {
     if (argc < 3) { fprintf(stderr, "usage: %s DEVICE SUITE [N_THREADS]\n", argv[0]); return 2; }
     ggml_backend_load_all();
@@ -211,6 +279,7 @@ int main(int argc, char ** argv) {
     if (suite == "mul_mat") suite_mul_mat();
     else if (suite == "flash_attn") suite_flash_attn();
     else if (suite == "alias") suite_alias();
+    else if (suite == "split") suite_split(dev);
     else { fprintf(stderr, "unknown suite %s\n", argv[2]); return 2; }
     ggml_backend_free(g_dev); ggml_backend_free(g_cpu);
     return g_fail;

@@ -3,13 +3,14 @@
 // generated position to a binary file (float32, n_vocab per row).  Run once with -ngl 0 (reference CPU backend)
 // and once with GGML_BACKEND_PATH pointing at libggml-b200.so and -ngl 99: same loader, same graph builder, same
 // scheduler; only the device differs.  Built by oracle/ref.mk against the reference headers; test infrastructure.
-//   llama_logits MODEL.gguf OUT.bin N_GPU_LAYERS N_PROMPT N_GEN SEED [FLASH_ATTN=1]
+//   llama_logits MODEL.gguf OUT.bin N_GPU_LAYERS N_PROMPT N_GEN SEED [FLASH_ATTN=1] [SPLIT_MODE=layer|row|none]
 #include "llama.h"
 #include "ggml-backend.h"
 
 #include <cstdio>
 #include <cstdlib>
 #include <random>
+#include <string>
 #include <vector>
 
 int main(int argc, char ** argv) {
@@ -20,6 +21,10 @@ int main(int argc, char ** argv) {
     llama_backend_init();
     llama_model_params mp = llama_model_default_params();
     mp.n_gpu_layers = ngl;
+    if (argc > 8) {
+        const std::string sm = argv[8];
+        mp.split_mode = sm == "row" ? LLAMA_SPLIT_MODE_ROW : (sm == "none" ? LLAMA_SPLIT_MODE_NONE : LLAMA_SPLIT_MODE_LAYER);
+    }
     llama_model * model = llama_model_load_from_file(argv[1], mp);
     if (!model) { fprintf(stderr, "load failed\n"); return 1; }
     llama_context_params cp = llama_context_default_params();

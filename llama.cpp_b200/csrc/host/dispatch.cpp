@@ -226,17 +226,30 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
         } else {
             ws = ctx->get_scratch(need);
         }
-        const size_t pbytes = single ? mmq_tc_partial_bytes(M, ne11, K, lc.sm_count) : 0;     // split-K partial tiles
+        // a grouped launch: the head and up to two more matrices of the same type and row length on the same activations
+        const void * gW[3] = {W->data, nullptr, nullptr}; float * gD[3] = {(float *) dst->data, nullptr, nullptr};
+        int64_t gM[3] = {M, 0, 0}, gNb[3] = {(int64_t) dst->nb[1], 0, 0};
+        const int n_mats = single ? 1 + n_extra : 1;
+        for (int i = 0; i < n_extra && single; ++i) {
+            gW[1 + i] = extra[i]->src[0]->data; gD[1 + i] = (float *) extra[i]->data;
+            gM[1 + i] = extra[i]->src[0]->ne[1]; gNb[1 + i] = (int64_t) extra[i]->nb[1];
+        }
+        const size_t pbytes = single ? mmq_tc_group_partial_bytes(n_mats, gM, ne11, K, lc.sm_count) : 0;     // partial tiles of the K-divided part
         void * partials = pbytes ? ctx->get_scratch(pbytes) : nullptr;
         if (ctx->capture_failed) return false;
-        const int64_t r2 = ne12 / W->ne[2], r3 = ne13 / W->ne[3];
-        for (int64_t i13 = 0; i13 < ne13; ++i13) for (int64_t i12 = 0; i12 < ne12; ++i12) {
-            const char * w = (const char *) W->data + (i12 / r2) * W->nb[2] + (i13 / r3) * W->nb[3];
-            const char * x = (const char *) X->data + i12 * X->nb[2] + i13 * X->nb[3];
-            char * d = (char *) dst->data + i12 * dst->nb[2] + i13 * dst->nb[3];
-            RUN(launch_mmq_tc(W->type, w, W->nb[1], (const float *) x, X->nb[1], (float *) d, dst->nb[1], M, ne11, K, ws, lc, have, partials));
+        if (single) {
+            RUN(launch_mmq_tc_group(W->type, n_mats, gW, W->nb[1], gM, gD, gNb, (const float *) X->data, X->nb[1], ne11, K, ws, lc, have, partials));
             if (partials) ctx->n_launches++;
             if (!have) ctx->n_launches++;
+        } else {
+            const int64_t r2 = ne12 / W->ne[2], r3 = ne13 / W->ne[3];
+            for (int64_t i13 = 0; i13 < ne13; ++i13) for (int64_t i12 = 0; i12 < ne12; ++i12) {
+                const char * w = (const char *) W->data + (i12 / r2) * W->nb[2] + (i13 / r3) * W->nb[3];
+                const char * x = (const char *) X->data + i12 * X->nb[2] + i13 * X->nb[3];
+                char * d = (char *) dst->data + i12 * dst->nb[2] + i13 * dst->nb[3];
+                RUN(launch_mmq_tc(W->type, w, W->nb[1], (const float *) x, X->nb[1], (float *) d, dst->nb[1], M, ne11, K, ws, lc, false, nullptr));
+                ctx->n_launches++;
+            }
         }
         if (sliced && !push_slice(ctx, dst)) return false;
         return true;
@@ -449,6 +462,20 @@ static bool group_head_ok(const ggml_tensor * n) {
     if ((size_t) x->ne[1] * ((w->ne[0] + 127) / 128) * 160 > 200 * 1024) return false;      // must fit the direct kernel's activation smem
     return ((uintptr_t) w->data & 15) == 0 && (w->nb[1] & 15) == 0 && t_contiguous(n) && x->type == GGML_TYPE_F32 && t_contiguous(x);
 }
+// the same for the tensor-core GEMM (more than 8 tokens): any type it takes, plain 2-D operands
+static bool tc_group_ok(const BackendCtx * ctx, const ggml_tensor * n) {
+    const ggml_tensor * w = n->src[0], * x = n->src[1];
+    if (!ctx->use_tc || is_float_type(w->type) || x->type != GGML_TYPE_F32 || x->ne[1] <= 8) return false;
+    if (x->ne[2] != 1 || x->ne[3] != 1 || w->ne[2] != 1 || w->ne[3] != 1 || n->type != GGML_TYPE_F32 || n->nb[0] != 4) return false;
+    if (!mmq_tc_supported(w->type, w->ne[1], x->ne[1], w->ne[0]) || !mmq_tc_ptr_ok(w->type, w->data, w->nb[1], x->data, x->nb[1])) return false;
+    if (w->nb[2] % 16 || w->nb[3] % 16 || x->nb[2] % 8 || x->nb[3] % 8) return false;      // (what run_mul_mat asks of the tensor-core path)
+    return !buft_is_split(w->buffer ? w->buffer->buft : nullptr);
+}
+static bool tc_groupable(const BackendCtx * ctx, const ggml_tensor * first, const ggml_tensor * n) {
+    if (n->op != GGML_OP_MUL_MAT || n->src[1] != first->src[1] || !tc_group_ok(ctx, n)) return false;
+    const ggml_tensor * w0 = first->src[0], * w = n->src[0];
+    return w->type == w0->type && w->ne[0] == w0->ne[0] && w->nb[1] == w0->nb[1];
+}
 static int next_exec(const BackendCtx * ctx, const ggml_cgraph * g, int i);
 
 static RopeParams rope_params_of(const ggml_tensor * dst) {
@@ -524,14 +551,15 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
             // it jumps over touch (ggml-alloc reuses freed memory).
             if (split_extra_of(dst->src[0])) return run_split_mul_mat(ctx, dst) ? 1 : 0;
             ggml_tensor * extra[2]; int n_extra = 0;
-            if (ctx->use_fusion && group_head_ok(dst) && !buft_is_split(dst->src[0]->buffer ? dst->src[0]->buffer->buft : nullptr)) {
+            const bool tc_head = ctx->use_fusion && ctx->peers.n_ranks < 2 && tc_group_ok(ctx, dst);
+            if ((ctx->use_fusion && group_head_ok(dst) && !buft_is_split(dst->src[0]->buffer ? dst->src[0]->buffer->buft : nullptr)) || tc_head) {
                 const bool sliced = ctx->row_slice_of(dst) != nullptr;
                 const ggml_tensor * jumped[16]; int n_jumped = 0;
                 for (int j = i + 1; j < g->n_nodes && n_extra < 2 && n_jumped < 16; ++j) {
                     ggml_tensor * n = g->nodes[j];
                     if (is_noop(n) || ctx->node_done[(size_t) j]) continue;
                     if (n->op == GGML_OP_FLASH_ATTN_EXT) break;
-                    const bool member = groupable_mul_mat(dst, n) && n->src[0]->op == GGML_OP_NONE &&
+                    const bool member = (tc_head ? tc_groupable(ctx, dst, n) : groupable_mul_mat(dst, n)) && n->src[0]->op == GGML_OP_NONE &&
                                         (ctx->row_slice_of(n) != nullptr) == sliced;
                     bool clear = member;
                     for (int q = 0; q < n_jumped && clear; ++q) {

@@ -119,7 +119,9 @@ API int b200_mul_mat_q(int type, const void * W, int64_t w_nb1, int64_t M, int64
         // split-K partial tiles: never more than the scratch size function allowed for, whatever this device's SM count
         LaunchCtx tc = lc;
         if (tc.sm_count > FLAT_SPLITK_SMS) tc.sm_count = FLAT_SPLITK_SMS;
-        void * partials = mmq_tc_partial_bytes(M, N, K, tc.sm_count) ? (char *) scratch + mmq_tc_workspace_bytes(N, K) : nullptr;
+        const size_t pb = mmq_tc_partial_bytes(M, N, K, tc.sm_count);
+        // (a device with fewer SMs may want more partial tiles than the scratch holds: then K is not divided)
+        void * partials = pb && mmq_tc_workspace_bytes(N, K) + pb <= scratch_bytes ? (char *) scratch + mmq_tc_workspace_bytes(N, K) : nullptr;
         CK(launch_mmq_tc(type, W, w_nb1, X, x_stride * 4, dst, dst_stride * 4, M, N, K, scratch, tc, false, partials));
         return 0;
     }

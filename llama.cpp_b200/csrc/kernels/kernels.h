@@ -89,8 +89,12 @@ cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float *
                           float * dst, int64_t dst_nb1, int64_t M, int64_t N, int64_t K,
                           void * workspace, const LaunchCtx & c, bool preconverted = false,    // preconverted: workspace already holds X as F16
                           void * partials = nullptr);   // mmq_tc_partial_bytes() of scratch enables split-K when the output has few tiles
-int         mmq_tc_ksplit(int64_t M, int64_t N, int64_t K, int sm_count);
 size_t      mmq_tc_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count);
+// up to three weight matrices of one type, row length and row stride on the same activations (wq/wk/wv, gate/up) as ONE launch
+cudaError_t launch_mmq_tc_group(int type, int n_mats, const void * const * W, int64_t w_nb1, const int64_t * M, float * const * dst,
+                                const int64_t * dst_nb1, const float * X, int64_t x_nb1, int64_t N, int64_t K, void * workspace,
+                                const LaunchCtx & c, bool preconverted = false, void * partials = nullptr);
+size_t      mmq_tc_group_partial_bytes(int n_mats, const int64_t * M, int64_t N, int64_t K, int sm_count);
 
 // ---- glue ops (glue.cu) ----
 enum BinOp { BIN_ADD = 0, BIN_SUB = 1, BIN_MUL = 2, BIN_DIV = 3 };

@@ -491,16 +491,24 @@ __global__ void tc_convert_x_kernel(const float * __restrict__ x, int64_t x_nb1 
 }
 
 // ---- the GEMM kernel ---------------------------------------------------------------------------
+static constexpr int TC_MAX_MATS = 3;
 struct TcParams {
     int staged;                 // raw blocks come through shared memory by tensor copies (needs 16-byte aligned rows)
-    const uint8_t * W; int64_t w_nb1;
+    // Up to three weight matrices of one type and row length that share the activations (wq/wk/wv, gate/up) run as one
+    // launch: their 128-row tiles are numbered consecutively, matrix j owning m-tiles [mt0[j], mt0[j + 1]).
+    int n_mats;
+    const uint8_t * W[TC_MAX_MATS]; int64_t w_nb1;
+    float * dst[TC_MAX_MATS]; int64_t dst_nb1[TC_MAX_MATS];      // bytes between token columns
+    int M[TC_MAX_MATS], mt0[TC_MAX_MATS + 1];
     const __half * Xh;                 // [N][K] F16 (read through the tensor map)
-    float * dst; int64_t dst_nb1;      // bytes between token columns
-    int M, N, K;
+    int N, K;
     int * status;
-    // split-K (few output tiles): CTA z handles k-steps [z * kps, z * kps + kps) and writes its partial [N][M] tile
-    // set into part + z * M * N; tc_reduce_kernel then sums the splits in order
-    int ksplit, kps; float * part;
+    // Tiles are numbered with the token tile fastest (neighbouring CTAs share a weight tile in L2).  CTAs [0, n_direct)
+    // compute one whole tile each.  The tiles after those (the part of the output that would not fill another wave of
+    // CTAs, or every tile of a small output) are divided along K: CTA n_direct + r * ksplit + z computes k-steps
+    // [z * kps, z * kps + kps) of tile n_direct + r into the partial tile part + (r * ksplit + z) * 128 * BN, and
+    // tc_reduce_kernel sums the splits in order.
+    int n_tiles_n, n_direct, ksplit, kps; float * part;
 };
 
 __device__ __forceinline__ void tma_load_2d(void * smem_dst, const CUtensorMap * tmap, int x, int y, uint64_t * bar) {
@@ -523,7 +531,8 @@ template <int BN> struct TcCfg {
 };
 
 template <int T, int BN>
-__global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap) {
+__global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap0,
+                                                                const __grid_constant__ CUtensorMap wmap1, const __grid_constant__ CUtensorMap wmap2) {
     constexpr int STAGES = TcCfg<BN>::STAGES;
     constexpr int STAGE_BYTES = BN * TC_BK * 2;                       // activation tile: 16 KB / 32 KB
     constexpr uint32_t A_COL0 = BN;                                   // tensor-memory column of the first weight tile
@@ -541,9 +550,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;    // adjacent CTAs share one weight tile (L2 reuse)
-    const int ks_begin = (int) blockIdx.z * p.kps;                  // split-K: this CTA's range of k-steps
-    const int ksteps = min(p.kps, p.K / TC_BK - ks_begin);
+    // which tile, which part of K
+    const int cta = (int) blockIdx.x;
+    const bool is_split = cta >= p.n_direct;
+    const int tile = is_split ? p.n_direct + (cta - p.n_direct) / p.ksplit : cta;
+    const int zsplit = is_split ? (cta - p.n_direct) % p.ksplit : 0;
+    const int mt = tile / p.n_tiles_n, n0 = (tile - mt * p.n_tiles_n) * BN;
+    const int mat = (p.n_mats > 2 && mt >= p.mt0[2]) ? 2 : ((p.n_mats > 1 && mt >= p.mt0[1]) ? 1 : 0);
+    const int m0 = (mt - p.mt0[mat]) * TC_BM;
+    const int M = p.M[mat];
+    const uint8_t * Wm = p.W[mat];
+    const CUtensorMap * wmap = mat == 0 ? &wmap0 : (mat == 1 ? &wmap1 : &wmap2);
+    const int ks_begin = is_split ? zsplit * p.kps : 0;             // this CTA's range of k-steps
+    const int ksteps = is_split ? min(p.kps, p.K / TC_BK - ks_begin) : p.K / TC_BK;
     const int k_base = ks_begin * TC_BK;
     constexpr int MMA_WARP = TC_PRODUCERS / 32;                       // the warp after it is the loader
 
@@ -568,8 +587,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
         // instruction latency).  A group is never more than 3 k-steps past its previous one, which keeps its parity waits
         // on the stage ring within one phase of the tensor core's progress.
         const int r = tid & 127, h = (tid >> 7) & 1, g = tid >> 8;      // operand row, which 32 of the 64 k-values, group
-        const bool wrow_ok = m0 + r < p.M;
-        const uint8_t * wrow = p.W + (int64_t) (wrow_ok ? m0 + r : 0) * p.w_nb1;
+        const bool wrow_ok = m0 + r < M;
+        const uint8_t * wrow = Wm + (int64_t) (wrow_ok ? m0 + r : 0) * p.w_nb1;
         constexpr int KPR = Deq32<T>::KPR;                              // k-steps covered by one Raw
         bool ok = true;
         // one k-step: the F16 values `wv` of this thread go into stage s, then the warp arrives
@@ -644,18 +663,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
             tc_fence_after();
             const int quad = warp & 3, cq = warp >> 2;                  // lane quadrant; which quarter of the BN columns
             const int m = m0 + quad * 32 + lane;
-            char * out = p.ksplit > 1 ? (char *) (p.part + (int64_t) blockIdx.z * p.M * p.N) : (char *) p.dst;
-            const int64_t out_nb1 = p.ksplit > 1 ? (int64_t) p.M * 4 : p.dst_nb1;
+            // a whole tile goes to its place in the result, a K part to its partial tile [BN][128]
+            char * out = is_split ? (char *) (p.part + (int64_t) (cta - p.n_direct) * TC_BM * BN) - (int64_t) n0 * TC_BM * 4 - (int64_t) m0 * 4
+                                  : (char *) p.dst[mat];
+            const int64_t out_nb1 = is_split ? (int64_t) TC_BM * 4 : p.dst_nb1[mat];
+            const int n_end = is_split ? n0 + BN : p.N, m_end = is_split ? m0 + TC_BM : M;
 #pragma unroll 1
             for (int c0 = cq * (BN / 4); c0 < cq * (BN / 4) + BN / 4; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t) (quad * 32) << 16) + (uint32_t) c0, v);
                 tmem_ld_wait();
-                if (m < p.M) {
+                if (m < m_end) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int n = n0 + c0 + i;
-                        if (n < p.N) *(float *) (out + (int64_t) n * out_nb1 + (int64_t) m * 4) = __uint_as_float(v[i]);
+                        if (n < n_end) *(float *) (out + (int64_t) n * out_nb1 + (int64_t) m * 4) = __uint_as_float(v[i]);
                     }
                 }
             }
@@ -714,7 +736,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
                     if (c >= NRB && !mbar_wait(&raw_empty[buf], (uint32_t) (c / NRB - 1) & 1)) { ok = false; break; }
                     if (*(volatile int *) &abort_flag) break;
                     mbar_arrive_expect_tx(&raw_full[buf], TC_BM * CB);
-                    tma_load_2d(rawbuf + (size_t) buf * RAW_BYTES, &wmap, (((k_base / TC_CHUNK_K + c) * TcChunk<T>::SRC) >> 4) * 4, m0, &raw_full[buf]);
+                    tma_load_2d(rawbuf + (size_t) buf * RAW_BYTES, wmap, (((k_base / TC_CHUNK_K + c) * TcChunk<T>::SRC) >> 4) * 4, m0, &raw_full[buf]);
                 }
                 if (!ok) { atomicExch(p.status, ERR_MBAR_TIMEOUT); abort_flag = 1; }
                 // When the kernel gives up, the last copies of this thread may still be in flight: wait (bounded) for
@@ -748,7 +770,8 @@ bool mmq_tc_ptr_ok(int type, const void * W, int64_t w_nb1, const void * X, int6
 template <int T> static bool tc_can_stage(const TcParams & p) {
     if (TcChunk<T>::BYTES == 0 || p.K % TC_CHUNK_K) return false;
     const int64_t row_bytes = (int64_t) (p.K / TC_CHUNK_K) * TcChunk<T>::SRC;
-    return ((uintptr_t) p.W & 15) == 0 && (p.w_nb1 & 15) == 0 && (row_bytes & 3) == 0 && p.w_nb1 >= row_bytes;
+    for (int j = 0; j < p.n_mats; ++j) if ((uintptr_t) p.W[j] & 15) return false;
+    return (p.w_nb1 & 15) == 0 && (row_bytes & 3) == 0 && p.w_nb1 >= row_bytes;
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -766,32 +789,70 @@ static encode_tiled_fn get_encode_tiled() {
     return fn;
 }
 
-// sums the split-K partials in split order (deterministic)
-__global__ void tc_reduce_kernel(const float * __restrict__ part, float * dst, int64_t dst_nb1, int M, int N, int ksplit) {
+// sums the K parts of the divided tiles in split order (deterministic) into their place in the result
+template <int BN>
+__global__ void tc_reduce_kernel(const TcParams p, int n_split_tiles) {
     pdl_enter();
-    const int64_t total = (int64_t) M * N;
+    const int64_t per_tile = (int64_t) TC_BM * BN, total = per_tile * n_split_tiles;
     for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
-        float acc = part[i];
-        for (int z = 1; z < ksplit; ++z) acc += part[(int64_t) z * total + i];
-        const int64_t n = i / M, m = i - n * M;
-        *(float *) ((char *) dst + n * dst_nb1 + m * 4) = acc;
+        const int r = (int) (i / per_tile);
+        const int e = (int) (i - (int64_t) r * per_tile), nl = e / TC_BM, ml = e - nl * TC_BM;
+        const int tile = p.n_direct + r, mt = tile / p.n_tiles_n, n = (tile - mt * p.n_tiles_n) * BN + nl;
+        const int mat = (p.n_mats > 2 && mt >= p.mt0[2]) ? 2 : ((p.n_mats > 1 && mt >= p.mt0[1]) ? 1 : 0);
+        const int m = (mt - p.mt0[mat]) * TC_BM + ml;
+        if (n >= p.N || m >= p.M[mat]) continue;
+        const float * src = p.part + (int64_t) r * p.ksplit * per_tile + e;
+        float acc = src[0];
+        for (int z = 1; z < p.ksplit; ++z) acc += src[(int64_t) z * per_tile];
+        *(float *) ((char *) p.dst[mat] + (int64_t) n * p.dst_nb1[mat] + (int64_t) m * 4) = acc;
     }
 }
 
-// With few output tiles (small M or N) the K range is divided over several CTAs so that the GPU is filled; every
-// split keeps at least 8 k-steps and an even number of them (the Q6_K producer works on pairs).
-int mmq_tc_ksplit(int64_t M, int64_t N, int64_t K, int sm_count) {
-    const int64_t tiles = ((M + TC_BM - 1) / TC_BM) * ((N + TC_BN - 1) / TC_BN);
-    const int64_t ksteps = K / TC_BK;
-    int64_t s = sm_count / (tiles > 0 ? tiles : 1);
-    if (s > 8) s = 8;
-    while (s > 1 && (ksteps / s < 8)) --s;
-    return s < 2 ? 1 : (int) s;
+// How a product of `m_tiles` 128-row tiles by N tokens is laid over the SMs.  The K range of a tile is divided over several
+// CTAs where whole tiles would leave SMs idle: every tile of a small output, or the tiles left over after the last full
+// wave of a large one (a part keeps at least 8 k-steps, and whole 256-value chunks).
+struct TcPlan { int bn, n_tiles_n, tiles, n_direct, ksplit, kps; double cost; };
+static TcPlan tc_plan_bn(int bn, int64_t m_tiles, int64_t N, int64_t K, int sm_count, bool allow_split) {
+    TcPlan pl;
+    pl.bn = bn; pl.n_tiles_n = (int) ((N + bn - 1) / bn); pl.tiles = (int) (m_tiles * pl.n_tiles_n);
+    const int ksteps = (int) (K / TC_BK);
+    const int full = pl.tiles / sm_count * sm_count, rest = pl.tiles - full;
+    int s = 1;
+    if (allow_split && rest > 0 && rest * 4 < sm_count * 3) {
+        s = sm_count / rest; if (s > 8) s = 8;
+        while (s > 1 && ksteps / s < 8) --s;
+    }
+    pl.kps = ((ksteps + s - 1) / s + 3) & ~3;
+    pl.ksplit = (ksteps + pl.kps - 1) / pl.kps;
+    if (pl.ksplit < 2) { pl.ksplit = 1; pl.kps = ksteps; pl.n_direct = pl.tiles; }
+    else pl.n_direct = full;
+    // estimated time in microseconds, from measurements on B200: a k-step of a CTA (a 128-token tile is bound by the issue
+    // rate of its MMAs, not by their size), a fixed part per wave (set-up, accumulator read-out), and what dividing K adds
+    // (partial tiles written and read back, the summation launch)
+    const double t_k = bn == 256 ? 0.47 : 0.45, fixed = 6.0, split_extra = 15.0;
+    pl.cost = (pl.n_direct + sm_count - 1) / sm_count * (ksteps * t_k + fixed);
+    if (pl.ksplit > 1) pl.cost += pl.kps * t_k + fixed + split_extra;
+    return pl;
 }
-size_t mmq_tc_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count) {
-    const int s = mmq_tc_ksplit(M, N, K, sm_count);
-    return s > 1 ? (size_t) s * M * N * 4 + 256 : 0;
+static TcPlan tc_plan(int64_t m_tiles, int64_t N, int64_t K, int sm_count, bool allow_split) {
+    static const int force_bn = getenv("GGML_B200_TC_BN") ? atoi(getenv("GGML_B200_TC_BN")) : 0;       // tuning aids
+    static const int no_tail = getenv("GGML_B200_TC_NO_SPLIT") ? atoi(getenv("GGML_B200_TC_NO_SPLIT")) : 0;
+    if (no_tail) allow_split = false;
+    const TcPlan a = tc_plan_bn(128, m_tiles, N, K, sm_count, allow_split);
+    if (N < 256 || force_bn == 128) return a;
+    const TcPlan b = tc_plan_bn(256, m_tiles, N, K, sm_count, allow_split);
+    return (force_bn == 256 || b.cost <= a.cost) ? b : a;
 }
+static int64_t m_tiles_of(int n_mats, const int64_t * M) {
+    int64_t t = 0;
+    for (int j = 0; j < n_mats; ++j) t += (M[j] + TC_BM - 1) / TC_BM;
+    return t;
+}
+size_t mmq_tc_group_partial_bytes(int n_mats, const int64_t * M, int64_t N, int64_t K, int sm_count) {
+    const TcPlan pl = tc_plan(m_tiles_of(n_mats, M), N, K, sm_count, true);
+    return pl.ksplit > 1 ? (size_t) (pl.tiles - pl.n_direct) * pl.ksplit * TC_BM * pl.bn * 4 + 256 : 0;
+}
+size_t mmq_tc_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count) { return mmq_tc_group_partial_bytes(1, &M, N, K, sm_count); }
 
 template <int T, int BN>
 static cudaError_t launch_tc_tb(const TcParams & p_in, int device, int use_pdl, cudaStream_t stream) {
@@ -815,35 +876,36 @@ static cudaError_t launch_tc_tb(const TcParams & p_in, int device, int use_pdl, 
     if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *) p.Xh, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    // tensor map of the raw weight rows as 32-bit words [M][row bytes / 4]: boxes of one 256-value chunk x 128 rows
-    CUtensorMap wmap = xmap;
-    if (p.staged) {
+    // per matrix, a tensor map of the raw weight rows as 32-bit words [M][row bytes / 4]: boxes of one 256-value chunk x 128 rows
+    CUtensorMap wmap[TC_MAX_MATS] = {xmap, xmap, xmap};
+    if (p.staged) for (int j = 0; j < p.n_mats; ++j) {
         constexpr cuuint32_t CW = TcChunk<T>::BYTES / 4;
-        const cuuint64_t wdim[2] = {(cuuint64_t) (p.K / TC_CHUNK_K) * TcChunk<T>::SRC / 4, (cuuint64_t) p.M};
+        const cuuint64_t wdim[2] = {(cuuint64_t) (p.K / TC_CHUNK_K) * TcChunk<T>::SRC / 4, (cuuint64_t) p.M[j]};
         const cuuint64_t wstr[1] = {(cuuint64_t) p.w_nb1};
         const cuuint32_t wbox[2] = {CW, TC_BM};
-        if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void *) p.W, wdim, wstr, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        if (enc(&wmap[j], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void *) p.W[j], wdim, wstr, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    dim3 grid((unsigned) ((p.N + BN - 1) / BN), (unsigned) ((p.M + TC_BM - 1) / TC_BM), (unsigned) p.ksplit);
-    cudaError_t e = launch_k(use_pdl, stream, kern, grid, dim3(TC_THREADS), smem, p, xmap, wmap);
+    const int n_split_tiles = p.mt0[p.n_mats] * p.n_tiles_n - p.n_direct;
+    const unsigned grid = (unsigned) (p.n_direct + n_split_tiles * (p.ksplit > 1 ? p.ksplit : 0));
+    cudaError_t e = launch_k(use_pdl, stream, kern, dim3(grid), dim3(TC_THREADS), smem, p, xmap, wmap[0], wmap[1], wmap[2]);
     if (e != cudaSuccess || p.ksplit == 1) return e;
-    const int64_t total = (int64_t) p.M * p.N;
+    const int64_t total = (int64_t) n_split_tiles * TC_BM * BN;
     int64_t g = (total + 255) / 256; if (g > 148 * 8) g = 148 * 8;
-    return launch_k(use_pdl, stream, tc_reduce_kernel, dim3((unsigned) g), dim3(256), 0, (const float *) p.part, p.dst, p.dst_nb1, p.M, p.N, p.ksplit);
+    return launch_k(use_pdl, stream, tc_reduce_kernel<BN>, dim3((unsigned) g), dim3(256), 0, p, n_split_tiles);
 }
 
-// 256 token columns per CTA when there is no split-K and the wide tiles still give every SM one
 template <int T>
-static cudaError_t launch_tc_t(const TcParams & p, int device, int use_pdl, cudaStream_t stream, int sm_count) {
-    const int64_t wide_tiles = (int64_t) ((p.M + TC_BM - 1) / TC_BM) * ((p.N + 255) / 256);
-    if (p.ksplit == 1 && p.N >= 256 && wide_tiles >= sm_count) return launch_tc_tb<T, 256>(p, device, use_pdl, stream);
+static cudaError_t launch_tc_t(const TcParams & p, int bn, int device, int use_pdl, cudaStream_t stream) {
+    if (bn == 256) return launch_tc_tb<T, 256>(p, device, use_pdl, stream);
     return launch_tc_tb<T, TC_BN>(p, device, use_pdl, stream);
 }
 
-cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float * X, int64_t x_nb1, float * dst, int64_t dst_nb1,
-                          int64_t M, int64_t N, int64_t K, void * workspace, const LaunchCtx & c, bool preconverted, void * partials) {
+cudaError_t launch_mmq_tc_group(int type, int n_mats, const void * const * W, int64_t w_nb1, const int64_t * M, float * const * dst,
+                                const int64_t * dst_nb1, const float * X, int64_t x_nb1, int64_t N, int64_t K, void * workspace,
+                                const LaunchCtx & c, bool preconverted, void * partials) {
+    if (n_mats < 1 || n_mats > TC_MAX_MATS) return cudaErrorInvalidValue;
     __half * xh = (__half *) workspace;
     if (!preconverted) {                 // (the caller may keep the F16 copy of X for the next mat-mul on the same activations)
         const int64_t total = N * K / 2;
@@ -851,29 +913,36 @@ cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float *
         cudaError_t e = launch_k(c.use_pdl, c.stream, tc_convert_x_kernel, dim3((unsigned) g), dim3(256), 0, X, x_nb1, xh, K, N);
         if (e != cudaSuccess) return e;
     }
-    TcParams p;
-    p.W = (const uint8_t *) W; p.w_nb1 = w_nb1; p.Xh = xh; p.dst = dst; p.dst_nb1 = dst_nb1;
-    p.M = (int) M; p.N = (int) N; p.K = (int) K; p.status = c.status;
-    p.ksplit = partials ? mmq_tc_ksplit(M, N, K, c.sm_count) : 1;
-    const int ksteps = (int) (K / TC_BK);
-    p.kps = (ksteps + p.ksplit - 1) / p.ksplit; p.kps = (p.kps + 3) & ~3;    // whole 256-value chunks (and pairs of k-steps)
-    p.ksplit = (ksteps + p.kps - 1) / p.kps;                                   // splits that actually have work
+    TcParams p = {};
+    p.n_mats = n_mats; p.w_nb1 = w_nb1; p.Xh = xh; p.N = (int) N; p.K = (int) K; p.status = c.status;
+    int mt = 0;
+    for (int j = 0; j < n_mats; ++j) {
+        p.W[j] = (const uint8_t *) W[j]; p.dst[j] = dst[j]; p.dst_nb1[j] = dst_nb1[j]; p.M[j] = (int) M[j];
+        p.mt0[j] = mt; mt += (int) ((M[j] + TC_BM - 1) / TC_BM);
+    }
+    for (int j = n_mats; j <= TC_MAX_MATS; ++j) p.mt0[j] = mt;
+    const TcPlan pl = tc_plan(mt, N, K, c.sm_count, partials != nullptr);
+    p.n_tiles_n = pl.n_tiles_n; p.n_direct = pl.n_direct; p.ksplit = pl.ksplit; p.kps = pl.kps;
     p.part = (float *) partials;
     switch (type) {
-        case T_Q4_0: return launch_tc_t<T_Q4_0>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_Q4_1: return launch_tc_t<T_Q4_1>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_Q5_0: return launch_tc_t<T_Q5_0>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_Q5_1: return launch_tc_t<T_Q5_1>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_Q8_0: return launch_tc_t<T_Q8_0>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_Q4_K: return launch_tc_t<T_Q4_K>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_Q5_K: return launch_tc_t<T_Q5_K>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_Q6_K: return launch_tc_t<T_Q6_K>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_Q2_K: return launch_tc_t<T_Q2_K>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_Q3_K: return launch_tc_t<T_Q3_K>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_IQ4_NL: return launch_tc_t<T_IQ4_NL>(p, c.device, c.use_pdl, c.stream, c.sm_count);
-        case T_IQ4_XS: return launch_tc_t<T_IQ4_XS>(p, c.device, c.use_pdl, c.stream, c.sm_count);
+        case T_Q4_0: return launch_tc_t<T_Q4_0>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_Q4_1: return launch_tc_t<T_Q4_1>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_Q5_0: return launch_tc_t<T_Q5_0>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_Q5_1: return launch_tc_t<T_Q5_1>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_Q8_0: return launch_tc_t<T_Q8_0>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_Q4_K: return launch_tc_t<T_Q4_K>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_Q5_K: return launch_tc_t<T_Q5_K>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_Q6_K: return launch_tc_t<T_Q6_K>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_Q2_K: return launch_tc_t<T_Q2_K>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_Q3_K: return launch_tc_t<T_Q3_K>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_IQ4_NL: return launch_tc_t<T_IQ4_NL>(p, pl.bn, c.device, c.use_pdl, c.stream);
+        case T_IQ4_XS: return launch_tc_t<T_IQ4_XS>(p, pl.bn, c.device, c.use_pdl, c.stream);
     }
     return cudaErrorInvalidValue;
+}
+cudaError_t launch_mmq_tc(int type, const void * W, int64_t w_nb1, const float * X, int64_t x_nb1, float * dst, int64_t dst_nb1,
+                          int64_t M, int64_t N, int64_t K, void * workspace, const LaunchCtx & c, bool preconverted, void * partials) {
+    return launch_mmq_tc_group(type, 1, &W, w_nb1, &M, &dst, &dst_nb1, X, x_nb1, N, K, workspace, c, preconverted, partials);
 }
 
 }  // namespace b200

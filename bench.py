@@ -47,7 +47,7 @@ LLAMA3_70B = dict(n_layer=80, n_embd=8192, n_head=64, n_head_kv=8, n_ff=28672, n
 CPU_PROMPT, CPU_GEN = 128, 16
 # DRAM bytes moved per algorithmic byte by the decode-step kernel, from an ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum) of an 8-layer model with the same layer shapes; traffic grows with the number of layers
-DRAM_TRAFFIC_RATIO = 1.02
+DRAM_TRAFFIC_RATIO = 1.0247       # 1,531,302,400 DRAM bytes for 1,494,425,600 algorithmic ones
 METRIC = "llama3-8b-q4_k_m tg128 tokens/s (pp512+tg128 per step)"   # --model 70b replaces the model name
 
 
@@ -293,6 +293,7 @@ def main():
     ap.add_argument("--n-gen", type=int, default=128, help="generated tokens per step (smaller only for profiler captures)")
     ap.add_argument("--no-roofline", action="store_true", help="skip the separate per-op mat-vec pass (profiler captures)")
     ap.add_argument("--no-llama-bench", action="store_true", help="skip the run of the reference's llama-bench on the plugin")
+    ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (profiler captures only; the line says so)")
     ap.add_argument("--model", default="8b", choices=["8b", "70b"],
                     help="8b: the configuration the metric is quoted on; 70b: the row-split parity configuration (no CPU baseline)")
     args = ap.parse_args()
@@ -302,11 +303,15 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     arch = dict(LLAMA3_8B if args.model == "8b" else LLAMA3_70B)
+    if args.layers > 0:
+        arch["n_layer"] = args.layers
     cores = physical_cores()
     rng = np.random.default_rng(1234)
     tokens = rng.integers(0, arch["n_vocab"], N_PROMPT + N_GEN).astype(np.int32)
     config = {"workload": f"llama3-{args.model}-arch q4_k_m pp512+tg128, random-init weights, uniform-random token ids", "n_prompt": N_PROMPT, "n_gen": N_GEN,
               "flash_attn": True, "kv_type": "f16", "l2": "every token re-reads all weights (4.6 GB for 8b, 42 GB for 70b) >> L2, no flush needed"}
+    if args.layers > 0:
+        config["layers_cut_to"] = args.layers          # not the benchmark configuration: a profiler capture
 
     if args.impl == "reference":
         if rank != 0:

@@ -218,6 +218,11 @@ cudaError_t launch_fattn(const TensorD & q, const TensorD & k, const TensorD & v
         if (n_kernels) *n_kernels = 1;
         return launch_fattn_dec(q, k, v, mask, dst, fp, c.fa_tickets, workspace, c, act128_out);
     }
+    static const int use_tc = getenv("GGML_B200_FA_TC") ? atoi(getenv("GGML_B200_FA_TC")) : 1;        // 0: keep the mma.sync kernel
+    if (f16_kv && use_tc && fattn_tc_applicable(q, k, v, mask, fp)) {
+        if (n_kernels) *n_kernels = mask ? 2 : 1;
+        return launch_fattn_tc(q, k, v, mask, dst, fp, workspace, c);
+    }
     if (f16_kv && fattn_mma_applicable(q, k, v, mask)) {
         if (n_kernels) *n_kernels = mask ? 2 : 1;
         return launch_fattn_mma(q, k, v, mask, dst, fp, workspace, c);

@@ -249,6 +249,12 @@ static cudaError_t fattn_mma_launch(const FmParams & p, int n3, const LaunchCtx 
     return cudaGetLastError();
 }
 
+cudaError_t launch_fattn_mask_flags(const char * mask, int64_t m_nb1, int n_q, int n_kv, uint8_t * flags, int flags_stride, const LaunchCtx & c) {
+    const int qt = (n_q + FM_BM - 1) / FM_BM, kt = (n_kv + FM_BN - 1) / FM_BN;
+    (void) (launch_err = launch_k(c.use_pdl, c.stream, fattn_mask_flags_kernel, dim3(dim3((unsigned) kt, (unsigned) qt)), dim3(256), 0, mask, m_nb1, n_q, n_kv, flags, flags_stride));
+    return cudaGetLastError();
+}
+
 cudaError_t launch_fattn_mma(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
                              const FattnParams & fp, void * workspace, const LaunchCtx & c) {
     FmParams p = {};

@@ -207,6 +207,13 @@ bool        fattn_mma_applicable(const TensorD & q, const TensorD & k, const Ten
 size_t      fattn_mma_workspace_bytes(const TensorD & q, const TensorD & k);
 cudaError_t launch_fattn_mma(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
                              const FattnParams & fp, void * workspace, const LaunchCtx & c);
+// classifies the 64 x 64 tiles of an F16 mask: 0 mixed, 1 all -inf, 2 all zero (fattn_mma.cu)
+cudaError_t launch_fattn_mask_flags(const char * mask, int64_t m_nb1, int n_q, int n_kv, uint8_t * flags, int flags_stride, const LaunchCtx & c);
+// tcgen05 kernel for batches of queries at head size 128 (fattn_tc.cu): S and O in tensor memory, K/V by tiled tensor copies;
+// workspace: fattn_mma_workspace_bytes()
+bool        fattn_tc_applicable(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const FattnParams & fp);
+cudaError_t launch_fattn_tc(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const TensorD & dst,
+                            const FattnParams & fp, void * workspace, const LaunchCtx & c);
 // n_kernels (optional) receives the number of kernels launched
 // GQA-shared split-KV kernel for decode (fattn_dec.cu); needs LaunchCtx::fa_tickets
 bool        fattn_dec_applicable(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask);

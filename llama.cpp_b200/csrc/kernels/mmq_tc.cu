@@ -31,7 +31,7 @@
 // status word; TMEM is allocated and released by warp 8 on every path.
 #include "common.cuh"
 #include "kernels.h"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace b200 {
 
@@ -41,88 +41,6 @@ static constexpr int TC_PRODUCERS = 2 * TC_GROUP;                      // two gr
 static constexpr int TC_THREADS = TC_PRODUCERS + 64;                  // + the MMA warp and the loader warp
 static constexpr int TC_CHUNK_K = 256;                                // K values per staged raw chunk (4 k-steps)
 static constexpr int TC_PF = 4;                                        // k-steps of raw weight bytes in flight per producer thread
-
-// ---- tcgen05 wrappers -------------------------------------------------------------------------
-__device__ __forceinline__ void tmem_alloc(uint32_t * smem_dst, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit_addr(uint32_t bar_smem) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar_smem) : "memory");
-}
-// bounded wait on the mbarrier at shared-memory address `bar`; the give-up flag of the CTA is looked at only while waiting
-__device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity, const int * abort_flag, int limit = (1 << 22)) {
-    for (int i = 0; i < limit; ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if (*(const volatile int *) abort_flag) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ void umma_commit(uint64_t * bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {   // A from tensor memory
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        :: "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 16 consecutive 32-bit columns of this thread's lane (lane = 32 * (warp % 4) + lane id)
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t) ((smem_addr & 0x3FFFF) >> 4);          // start address
-    d |= (uint64_t) 1 << 16;                               // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t) (1024 >> 4) << 32;                     // stride byte offset between 8-row groups
-    d |= (uint64_t) 1 << 46;                               // descriptor version of this architecture
-    d |= (uint64_t) 2 << 61;                               // SWIZZLE_128B
-    return d;
-}
-// instruction descriptor: F16 x F16 -> F32, both operands K-major, M = 128, N = 128
-__device__ __forceinline__ constexpr uint32_t umma_idesc_f16(int M, int N) {
-    return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t) (N >> 3) << 17) | ((uint32_t) (M >> 4) << 24);
-}
 
 // ---- weight dequantization: 32 consecutive values of one row as F16 ---------------------------
 // Raw<T> holds the quant bytes a thread needs for its 32 values of one k-step; load() only issues the
@@ -511,11 +429,6 @@ struct TcParams {
     int n_tiles_n, n_direct, ksplit, kps; float * part;
 };
 
-__device__ __forceinline__ void tma_load_2d(void * smem_dst, const CUtensorMap * tmap, int x, int y, uint64_t * bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        :: "r"(smem_u32(smem_dst)), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
 
 // BN: token columns per CTA, 128 or 256.  The wide tile halves the number of times a weight tile is dequantized (the
 // producers, not the tensor core, bound this kernel) and is used when it still leaves every SM a CTA.
@@ -772,21 +685,6 @@ template <int T> static bool tc_can_stage(const TcParams & p) {
     const int64_t row_bytes = (int64_t) (p.K / TC_CHUNK_K) * TcChunk<T>::SRC;
     for (int j = 0; j < p.n_mats; ++j) if ((uintptr_t) p.W[j] & 15) return false;
     return (p.w_nb1 & 15) == 0 && (row_bytes & 3) == 0 && p.w_nb1 >= row_bytes;
-}
-
-typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static encode_tiled_fn get_encode_tiled() {
-    static encode_tiled_fn fn = nullptr;
-    if (!fn) {
-        void * p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (encode_tiled_fn) p;
-        else cudaGetLastError();
-    }
-    return fn;
 }
 
 // sums the K parts of the divided tiles in split order (deterministic) into their place in the result

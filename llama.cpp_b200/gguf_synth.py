@@ -8,7 +8,7 @@ N(0, 0.02)), already quantized to the reference's Q4_K_M tensor-type mixture (sr
 tokenizer section says `no_vocab`, which makes libllama create `<arch>.vocab_size` dummy tokens
 (src/llama-vocab.cpp:1350-1368): all that llama-bench, which feeds random token ids, needs.
 
-    python llama.cpp_b200/gguf_synth.py /tmp/llama3-8b-q4_k_m.gguf --model 8b
+    python llama.cpp_b200/gguf_synth.py llama3-8b-q4_k_m.gguf --model 8b
     GGML_BACKEND_PATH=llama.cpp_b200/lib/libggml-b200.so oracle/_ref/llama-bench -m /tmp/llama3-8b-q4_k_m.gguf \
         -p 512 -n 128 -fa 1 -ngl 99
 """

@@ -11,7 +11,7 @@ events on the launching stream.  Bytes and flops follow the reference's accounti
   python llama.cpp_b200/microbench.py mul_mat --type q4_K -k 4096 -m 14336 -n 512
   python llama.cpp_b200/microbench.py flash_attn --n-kv 32768 --n-q 1
   python llama.cpp_b200/microbench.py sweep          # the projection shapes of Llama-3-8B
-  python llama.cpp_b200/microbench.py load --path /tmp/m.gguf     # model-file load time (file mapping -> HBM)
+  python llama.cpp_b200/microbench.py load --path m.gguf     # model-file load time (file mapping -> HBM)
 
 `--copies C --reps R` bound the work (for a profiler capture: `--copies 4 --reps 1`).
 """

@@ -3,14 +3,15 @@
 # lie, into oracle/_ref/.  This is test infrastructure: the resulting CPU
 # backend is the oracle the CUDA path is checked against and the timed CPU
 # baseline.  No reference source is copied; the reference's own build system is
-# not run.  Usage:   make -f oracle/ref.mk REF=/path/to/reference -j8
+# not run.  Usage:   make -f oracle/ref.mk REF=/path/to/reference -j8   (REF defaults to a
+# directory `reference` beside this repository)
 #
 # The ggml libraries are built in the reference's "dynamic backend" mode
 # (GGML_BACKEND_DL): the CPU backend is produced as three loadable variants and
 # the registry picks the best one the host CPU supports, so the same binaries
 # run on the build container and on the GPU box's host.
 
-REF  ?= /root/reference
+REF   ?= $(abspath $(dir $(lastword $(MAKEFILE_LIST)))../../reference)
 OUT  ?= oracle/_ref
 OBJ  := $(OUT)/obj
 CC   ?= gcc

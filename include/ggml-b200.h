@@ -34,7 +34,12 @@ int ggml_backend_score(void);
  * Names answered by reg->iface.get_proc_address:
  *   "ggml_backend_split_buffer_type"  ggml_backend_buffer_type_t (*)(int main_device, const float * tensor_split)
  *                                     (ggml/include/ggml-backend.h:188; libllama asks for it in row-split mode,
- *                                      src/llama-model.cpp:308-326)
+ *                                      src/llama-model.cpp:308-326).  Returns a buffer type that divides the rows of a
+ *                                     matrix over the B200 devices of this process (boundaries rounded down to 128
+ *                                     rows, all-zero tensor_split = equal shares; what ggml_backend_cuda_split_buffer_type
+ *                                     is to the reference, ggml/src/ggml-cuda/ggml-cuda.cu:714-1040); tensors in it are
+ *                                     accepted only as the weight operand of a 2-D MUL_MAT.  NULL for a main_device
+ *                                     outside the registry.
  *   "ggml_backend_get_features"       ggml_backend_feature * (*)(ggml_backend_reg_t)   (ggml-backend.h:196-200)
  *   "ggml_backend_b200_get_stream"       void *   (*)(ggml_backend_t)   the backend's cudaStream_t, for event timing
  *   "ggml_backend_b200_get_launch_count" uint64_t (*)(ggml_backend_t)   kernels launched by graph_compute so far
@@ -48,7 +53,8 @@ int ggml_backend_score(void);
  *
  * The reference splits the rows of a weight matrix over the devices of ONE process through its split
  * buffer type and gathers the dst slices with peer copies (ggml/src/ggml-cuda/ggml-cuda.cu:714-1040,
- * :1520-1660).  Here every rank is its own process with its own backend; each rank's graph holds only
+ * :1520-1660); the buffer type above does the same.  This second form keeps the exchange inside the kernels
+ * and the CUDA graph: every rank is its own process with its own backend; each rank's graph holds only
  * its rows of each split matrix, and a MUL_MAT node says where its slice belongs in the full result:
  *
  *   node->op == GGML_OP_MUL_MAT, node->src[0] = this rank's rows [row_low, row_low + node->ne[0]) of the matrix,

@@ -136,6 +136,15 @@ const char * b200_decode_step_last_error(void);
  * becomes 3 (ERR_PEER_TIMEOUT) and the kernel returns normally; with peer_arrives = 1 it passes (0).   */
 int b200_peer_barrier_probe_host(int spin_limit, int peer_arrives, int * status_out);
 
+/* ---- the int8 form of the prefill GEMM, measured ---------------------------
+ * No counterpart in the reference.  The reference's prefill mat-mul runs int8 MMAs of 32-deep steps and applies the
+ * block scales to each step's int32 result in FP32 (ggml/src/ggml-cuda/mmq.cuh:649-727).  This probe runs that
+ * structure on tcgen05 with nothing else around it (fixed operands in shared memory): per step one 128 x 256 x 32
+ * `kind::i8` MMA into tensor memory, read back by eight warps and folded into FP32 sums with a row and a column scale.
+ * *us_per_kblock = time of one step of one CTA (every SM runs a CTA), *check = one element of the result, *expected =
+ * what it must be.  Used by `microbench.py i8_probe` to put a number on the alternative the product does not take.   */
+int b200_tc_i8_probe_host(int kblocks, int reps, float * us_per_kblock, float * check, float * expected);
+
 /* ---- FLASH_ATTN_EXT -------------------------------------------------------
  * GGML_OP_FLASH_ATTN_EXT (ggml_flash_attn_ext, ggml/src/ggml.c:4306-4345; CPU
  * semantics ggml/src/ggml-cpu/ggml-cpu.c:10916-11129).  q F32 [D, n_q, n_head],

@@ -31,7 +31,7 @@ EXPORTS = [
     "b200_act_bytes", "b200_quantize_act", "b200_mul_mat_vec_q", "b200_set_dependent_launch",
     "b200_mul_mat_q_noalloc", "b200_noalloc_last_error", "b200_noalloc_status",
     "b200_decode_step_mul_mat_host", "b200_decode_step_gate_up_host", "b200_decode_step_qkv_host",
-    "b200_decode_step_attention_host", "b200_decode_step_last_error", "b200_peer_barrier_probe_host",
+    "b200_decode_step_attention_host", "b200_decode_step_last_error", "b200_peer_barrier_probe_host", "b200_tc_i8_probe_host",
     "b200_flash_attn_scratch_bytes", "b200_flash_attn", "b200_flash_attn_host",
     "b200_dequantize_rows_host", "b200_get_rows_host", "b200_quantize_rows_host", "b200_f32_to_f16_host",
     "b200_rms_norm_host", "b200_rope_host", "b200_silu_mul_host", "b200_soft_max_host",
@@ -92,6 +92,7 @@ def lib() -> C.CDLL:
         l.b200_decode_step_qkv_host.argtypes = [C.c_int, C.c_int, vp, vp, vp, i64, i64, i64, vp, vp, f32, C.c_int32, C.c_int, f32, vp, vp, vp, vp]
         l.b200_decode_step_attention_host.argtypes = [vp, vp, vp, vp, i64, i64, i64, f32, C.c_int, C.c_int, vp]
         l.b200_peer_barrier_probe_host.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_int)]
+        l.b200_tc_i8_probe_host.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]
         l.b200_flash_attn_scratch_bytes.restype = sz
         l.b200_flash_attn_scratch_bytes.argtypes = [i64, i64, i64, i64]
         l.b200_flash_attn.argtypes = [vp, i64, i64, vp, i64, i64, vp, i64, i64, vp, i64, vp,

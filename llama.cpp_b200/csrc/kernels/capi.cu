@@ -378,6 +378,13 @@ API int b200_soft_max_host(const float * x, int64_t n_rows, int64_t k, const voi
 // Runs the row-split barrier kernel (peer.cu) as rank 0 of 2 with both flag arrays in this GPU's memory.  With
 // peer_arrives the "peer" has already published the epoch and the barrier passes; without, nothing ever writes the
 // flag, the wait runs out after `spin_limit` polls, and the kernel records ERR_PEER_TIMEOUT and returns.
+API int b200_tc_i8_probe_host(int kblocks, int reps, float * us_per_kblock, float * check, float * expected) {
+    if (kblocks < 1 || kblocks > (1 << 20) || reps < 1 || !us_per_kblock || !check || !expected) return fail(B200_E_BAD_ARG, "bad probe arguments");
+    LaunchCtx lc; int rc = get_ctx(nullptr, lc); if (rc) return rc;
+    CK(launch_tc_i8_probe(kblocks, reps, us_per_kblock, check, expected, lc));
+    return 0;
+}
+
 API int b200_peer_barrier_probe_host(int spin_limit, int peer_arrives, int * status_out) {
     LaunchCtx lc; int rc = get_ctx(nullptr, lc); if (rc) return rc;
     DevBuf flags, peer, epoch, status;

@@ -316,7 +316,7 @@ cudaError_t launch_fattn_tc(const TensorD & q, const TensorD & k, const TensorD 
     p.scale_log2 = fp.scale * 1.4426950408889634f;
     p.status = c.status;
     if (mask) {
-        const int qt = (p.n_q + 63) / 64, kt = (p.n_kv + 63) / 64;
+        const int kt = (p.n_kv + 63) / 64;                        // flags: one byte per 64 x 64 tile of the mask
         p.flags = (const uint8_t *) workspace; p.flags_stride = kt;
         cudaError_t e = launch_fattn_mask_flags(p.mask, p.m_nb1, p.n_q, p.n_kv, (uint8_t *) workspace, kt, c);
         if (e != cudaSuccess) return e;

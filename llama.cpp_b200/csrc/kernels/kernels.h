@@ -96,6 +96,9 @@ cudaError_t launch_mmq_tc_group(int type, int n_mats, const void * const * W, in
                                 const LaunchCtx & c, bool preconverted = false, void * partials = nullptr);
 size_t      mmq_tc_group_partial_bytes(int n_mats, const int64_t * M, int64_t N, int64_t K, int sm_count);
 
+// ---- measurement of the int8 design alternative of the prefill GEMM (tc_i8_probe.cu); not on a product path ----
+cudaError_t launch_tc_i8_probe(int kblocks, int reps, float * us_per_kblock, float * check, float * expected, const LaunchCtx & c);
+
 // ---- glue ops (glue.cu) ----
 enum BinOp { BIN_ADD = 0, BIN_SUB = 1, BIN_MUL = 2, BIN_DIV = 3 };
 enum UnOp  { UN_SILU = 0, UN_GELU, UN_GELU_QUICK, UN_RELU, UN_TANH, UN_SIGMOID, UN_NEG, UN_EXP, UN_ABS, UN_SGN,

@@ -11,6 +11,7 @@ events on the launching stream.  Bytes and flops follow the reference's accounti
   python llama.cpp_b200/microbench.py mul_mat --type q4_K -k 4096 -m 14336 -n 512
   python llama.cpp_b200/microbench.py flash_attn --n-kv 32768 --n-q 1
   python llama.cpp_b200/microbench.py sweep          # the projection shapes of Llama-3-8B
+  python llama.cpp_b200/microbench.py i8_probe -k 4096                # the int8-MMA-plus-drain form of the GEMM, per 32-deep step
   python llama.cpp_b200/microbench.py load --path m.gguf     # model-file load time (file mapping -> HBM)
 
 `--copies C --reps R` bound the work (for a profiler capture: `--copies 4 --reps 1`).
@@ -170,7 +171,7 @@ def bench_load(pkg, path, reps=3):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["mul_mat", "flash_attn", "sweep", "load"])
+    ap.add_argument("op", choices=["mul_mat", "flash_attn", "sweep", "load", "i8_probe"])
     ap.add_argument("--path", default=None, help="load: a Llama-architecture GGUF file (llama.cpp_b200/gguf_synth.py writes one)")
     ap.add_argument("--type", default="q4_K", choices=QK_TYPES)
     ap.add_argument("-k", type=int, default=4096)
@@ -185,7 +186,18 @@ def main():
     import torch
     if pkg.device_count() < 1:
         raise SystemExit("no sm_100 device visible: these kernels have no CPU fallback")
-    if a.op == "load":
+    if a.op == "i8_probe":
+        # the int8 form of the prefill GEMM (one kind::i8 MMA per 32-deep step, drained and scaled in FP32), nothing else
+        import ctypes as C
+        us, chk, exp = C.c_float(), C.c_float(), C.c_float()
+        rc = pkg.lib().b200_tc_i8_probe_host(a.k // 32, a.reps, C.byref(us), C.byref(chk), C.byref(exp))
+        if rc != 0:
+            raise SystemExit(f"probe failed ({rc}): {pkg.lib().b200_last_error().decode()}")
+        steps = a.k // 32
+        print(f"kind::i8 128x256x32 + drain: {us.value:.4f} us per 32-deep step ({us.value * 2:.4f} us per 64 values of K; "
+              f"{2 * 128 * 256 * 32 / us.value / 1e6:.1f} TFLOP/s per SM-resident CTA x 148), K = {a.k} ({steps} steps), "
+              f"element check {chk.value:.3f} (expected {exp.value:.3f})", flush=True)
+    elif a.op == "load":
         bench_load(pkg, a.path, reps=min(a.reps, 3))
     elif a.op == "mul_mat":
         bench_mul_mat(pkg, torch, a.type, a.k, a.m, a.n, a.copies, a.reps)

@@ -733,8 +733,8 @@ static TcPlan tc_plan_bn(int bn, int64_t m_tiles, int64_t N, int64_t K, int sm_c
     return pl;
 }
 static TcPlan tc_plan(int64_t m_tiles, int64_t N, int64_t K, int sm_count, bool allow_split) {
-    static const int force_bn = getenv("GGML_B200_TC_BN") ? atoi(getenv("GGML_B200_TC_BN")) : 0;       // tuning aids
-    static const int no_tail = getenv("GGML_B200_TC_NO_SPLIT") ? atoi(getenv("GGML_B200_TC_NO_SPLIT")) : 0;
+    const char * e_bn = getenv("GGML_B200_TC_BN"), * e_ns = getenv("GGML_B200_TC_NO_SPLIT");            // tuning and test aids (read per call)
+    const int force_bn = e_bn ? atoi(e_bn) : 0, no_tail = e_ns ? atoi(e_ns) : 0;
     if (no_tail) allow_split = false;
     const TcPlan a = tc_plan_bn(128, m_tiles, N, K, sm_count, allow_split);
     if (N < 256 || force_bn == 128) return a;

@@ -90,9 +90,14 @@ def test_gloo_ranks_gather_equals_unsplit(tmp_path, oracle, world):
 
 
 @pytest.mark.gpu
-def test_row_split_two_gpus_matches_one_gpu(tmp_path, b200, oracle):
+def test_row_split_two_gpus_matches_one_gpu(tmp_path, b200, oracle, monkeypatch):
     if b200.device_count() < 2:
         pytest.skip("needs two B200s")
+    # Both runs on the one-launch-per-node path with K undivided, so that every output row is computed by the same kernel
+    # with the same order of sums whether its matrix is whole or one rank's slice (the persistent decode step does not take
+    # row-split graphs, and the tile plan of the tensor-core GEMM depends on the row count).
+    monkeypatch.setenv("GGML_B200_MEGA", "0")
+    monkeypatch.setenv("GGML_B200_TC_NO_SPLIT", "1")
     sys.path.insert(0, str(ROOT / "tests"))
     import rank_worker as w
     from llama_cpp_b200 import llama

@@ -241,6 +241,7 @@ static void backend_free(ggml_backend_t backend) {
     if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
     if (ctx->dyn_dev) cudaFree(ctx->dyn_dev);
     if (ctx->fa_tickets) cudaFree(ctx->fa_tickets);
+    if (ctx->mask16) cudaFree(ctx->mask16);
     if (ctx->mega_arena) cudaFree(ctx->mega_arena);
     if (ctx->mega_copy_stream) cudaStreamDestroy(ctx->mega_copy_stream);
     free(ctx->dyn_host);

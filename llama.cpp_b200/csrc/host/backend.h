@@ -89,6 +89,8 @@ struct BackendCtx {
     uint64_t     scratch_generation = 0;
 
     unsigned *   fa_tickets = nullptr;     // zero-initialised counters of the decode attention kernel
+    // F16 copy of an F32 attention mask (graphs built without FLASH_ATTN_EXT carry it in F32), made once per graph_compute
+    void *       mask16 = nullptr; size_t mask16_cap = 0; const void * mask16_src = nullptr;
 
     // persistent decode step (decode_plan.cpp): scratch, phase lists and barrier words of the single-launch path
     int          use_mega = 1;             // GGML_B200_MEGA=0 keeps one launch per node (group)

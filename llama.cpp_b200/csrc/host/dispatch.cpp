@@ -478,6 +478,56 @@ static bool tc_groupable(const BackendCtx * ctx, const ggml_tensor * first, cons
 }
 static int next_exec(const BackendCtx * ctx, const ggml_cgraph * g, int i);
 
+// Attention as libllama builds it WITHOUT flash attention (llm_build_kqv, src/llama.cpp:601-650): kq = MUL_MAT(K, Q),
+// SOFT_MAX(kq, mask, scale), kqv = MUL_MAT(V^T, p) with V kept transposed in the cache, PERMUTE, CONT.  When those five
+// nodes stand in a row and nothing else reads the intermediates, they are computed as ONE flash-attention launch on the
+// same operands (the score and probability matrices are never materialised): the result of CONT has exactly the
+// [head size, heads, queries] layout FLASH_ATTN_EXT writes.  Returns the number of nodes consumed, 0 for no match.
+struct AttnChain { const ggml_tensor * q, * k, * v, * mask; ggml_tensor * out; float scale; int last; };
+static bool match_attn_chain(const BackendCtx * ctx, const ggml_cgraph * g, int i, AttnChain & m) {
+    const ggml_tensor * kq = g->nodes[i];
+    if (kq->op != GGML_OP_MUL_MAT || kq->type != GGML_TYPE_F32) return false;
+    const ggml_tensor * k = kq->src[0], * q = kq->src[1];
+    if (k->type != GGML_TYPE_F16 || q->type != GGML_TYPE_F32 || k->nb[0] != 2 || q->nb[0] != 4 || q->ne[3] != 1 || k->ne[3] != 1) return false;
+    const int64_t D = q->ne[0], n_q = q->ne[1], n_head = q->ne[2], n_kv = k->ne[1], n_head_kv = k->ne[2];
+    if (k->ne[0] != D || n_head_kv == 0 || n_head % n_head_kv != 0) return false;
+    const int j1 = next_exec(ctx, g, i + 1);
+    if (j1 < 0) return false;
+    const ggml_tensor * sm = g->nodes[j1];
+    if (sm->op != GGML_OP_SOFT_MAX || sm->src[0] != kq || op_param_f32(sm, 1) != 0.0f) return false;          // (ALiBi stays unfused)
+    const ggml_tensor * mask = sm->src[1];
+    if (mask && (mask->type != GGML_TYPE_F16 && mask->type != GGML_TYPE_F32)) return false;
+    if (mask && (mask->ne[0] != n_kv || mask->ne[1] < n_q || mask->ne[2] != 1 || mask->ne[3] != 1 || !t_contiguous(mask))) return false;
+    const int j2 = next_exec(ctx, g, j1 + 1);
+    if (j2 < 0) return false;
+    const ggml_tensor * kqv = g->nodes[j2];
+    if (kqv->op != GGML_OP_MUL_MAT || kqv->src[1] != sm || kqv->type != GGML_TYPE_F32) return false;
+    const ggml_tensor * v = kqv->src[0];
+    if (v->type != GGML_TYPE_F16 || v->nb[0] != 2 || v->ne[0] != n_kv || v->ne[1] != D || v->ne[2] != n_head_kv || v->ne[3] != 1) return false;
+    const int j4 = next_exec(ctx, g, j2 + 1);
+    if (j4 < 0) return false;
+    ggml_tensor * cont = g->nodes[j4];
+    const ggml_tensor * perm = cont->src[0];
+    if (cont->op != GGML_OP_CONT || !perm || perm->op != GGML_OP_PERMUTE || perm->src[0] != kqv || cont->type != GGML_TYPE_F32 || !t_contiguous(cont)) return false;
+    // the permutation swaps queries and heads: [D, n_q, n_head] -> [D, n_head, n_q]
+    if (perm->ne[0] != D || perm->ne[1] != n_head || perm->ne[2] != n_q || perm->nb[1] != kqv->nb[2] || perm->nb[2] != kqv->nb[1]) return false;
+    if (cont->ne[0] * cont->ne[1] * cont->ne[2] * cont->ne[3] != D * n_head * n_q) return false;
+    // nothing else may read the intermediates
+    for (int j = i + 1; j < g->n_nodes; ++j) {
+        const ggml_tensor * n = g->nodes[j];
+        for (int s_ = 0; s_ < GGML_MAX_SRC && n->src[s_]; ++s_) {
+            const ggml_tensor * t = n->src[s_];
+            const ggml_tensor * root = t->view_src ? t->view_src : t;
+            const bool inter = root == kq || root == sm || root == kqv;
+            if (!inter) continue;
+            const bool expected = (n == sm && t == kq) || (n == kqv && t == sm) || (n == perm && t == kqv) || (n == cont && t == perm);
+            if (!expected) return false;
+        }
+    }
+    m.q = q; m.k = k; m.v = v; m.mask = mask; m.out = cont; m.scale = op_param_f32(sm, 0); m.last = j4;
+    return true;
+}
+
 static RopeParams rope_params_of(const ggml_tensor * dst) {
     RopeParams rp;
     rp.n_dims = op_param_i32(dst, 1); rp.mode = op_param_i32(dst, 2); rp.n_ctx_orig = op_param_i32(dst, 4);
@@ -550,6 +600,53 @@ static int run_node(BackendCtx * ctx, ggml_cgraph * g, int i) {
             // activations and a weight leaf, and it may run early if its output does not alias anything the nodes
             // it jumps over touch (ggml-alloc reuses freed memory).
             if (split_extra_of(dst->src[0])) return run_split_mul_mat(ctx, dst) ? 1 : 0;
+            // attention built from MUL_MAT / SOFT_MAX / MUL_MAT (no FLASH_ATTN_EXT in the graph): one flash-attention launch
+            if (ctx->use_fusion && ctx->peers.n_ranks < 2 && a->type == GGML_TYPE_F16) {
+                AttnChain m;
+                if (match_attn_chain(ctx, g, i, m)) {
+                    const int64_t D = m.q->ne[0], n_q = m.q->ne[1], n_head = m.q->ne[2], n_kv = m.k->ne[1];
+                    const TensorD qd = to_desc(m.q), kd = to_desc(m.k);
+                    TensorD vd = to_desc(m.v);                       // described as [D, n_kv, heads] with the head-size dimension strided
+                    vd.ne[0] = D; vd.ne[1] = n_kv; vd.nb[0] = m.v->nb[1]; vd.nb[1] = m.v->nb[0];
+                    TensorD dd = to_desc(m.out);
+                    dd.ne[0] = D; dd.ne[1] = n_head; dd.ne[2] = n_q; dd.ne[3] = 1; dd.nb[0] = 4; dd.nb[1] = D * 4; dd.nb[2] = D * n_head * 4; dd.nb[3] = D * n_head * n_q * 4;
+                    TensorD md; bool have_mask = m.mask != nullptr;
+                    if (have_mask) md = to_desc(m.mask);
+                    const FattnParams fp{m.scale, 0.0f, 0.0f};
+                    bool ok = true;
+                    if (have_mask && m.mask->type == GGML_TYPE_F32) {
+                        const size_t need = (size_t) m.mask->ne[0] * (size_t) m.mask->ne[1] * 2;
+                        if (need > ctx->mask16_cap) {
+                            if (ctx->capturing) { ctx->capture_failed = true; return fail(); }
+                            cudaStreamSynchronize(ctx->stream);
+                            if (ctx->mask16) cudaFree(ctx->mask16);
+                            ctx->mask16_cap = need + need / 2; ctx->mask16_src = nullptr;
+                            if (cudaMalloc(&ctx->mask16, ctx->mask16_cap + 256) != cudaSuccess) { cudaGetLastError(); ctx->mask16 = nullptr; ctx->mask16_cap = 0; ok = false; }
+                        }
+                        if (ok) {
+                            TensorD m16 = md;
+                            m16.type = GGML_TYPE_F16; m16.data = ctx->mask16;
+                            m16.nb[0] = 2; m16.nb[1] = m16.ne[0] * 2; m16.nb[2] = m16.nb[1] * m16.ne[1]; m16.nb[3] = m16.nb[2];
+                            if (ctx->mask16_src != m.mask->data) {
+                                RUN0(launch_cpy(md, m16, lc));
+                                ctx->mask16_src = m.mask->data;
+                            }
+                            md = m16;
+                        }
+                    }
+                    const bool dec = lc.fa_tickets && fattn_dec_applicable(qd, kd, vd, have_mask ? &md : nullptr);
+                    if (ok && (dec || fattn_tc_applicable(qd, kd, vd, have_mask ? &md : nullptr, fp))) {
+                        const size_t ws = fattn_workspace_bytes(qd, kd, lc.sm_count);
+                        void * wsp = ws ? ctx->get_scratch(ws) : nullptr;
+                        if (ctx->capture_failed) return fail();
+                        int nk = 1;
+                        RUN0(launch_fattn(qd, kd, vd, have_mask ? &md : nullptr, dd, fp, wsp, lc, &nk, nullptr));
+                        ctx->n_launches += (uint64_t) (nk - 1);
+                        for (int j = i + 1; j <= m.last; ++j) if (!is_noop(g->nodes[j])) { ctx->node_done[(size_t) j] = 1; invalidate_written(ctx, g->nodes[j]); }
+                        return 1;
+                    }
+                }
+            }
             ggml_tensor * extra[2]; int n_extra = 0;
             const bool tc_head = ctx->use_fusion && ctx->peers.n_ranks < 2 && tc_group_ok(ctx, dst);
             if ((ctx->use_fusion && group_head_ok(dst) && !buft_is_split(dst->src[0]->buffer ? dst->src[0]->buffer->buft : nullptr)) || tc_head) {
@@ -773,6 +870,7 @@ static bool run_all(BackendCtx * ctx, ggml_cgraph * cgraph) {
     pending_full.clear();
     ctx->node_done.assign((size_t) cgraph->n_nodes, 0);
     ctx->mega_tried = false; ctx->mega_ops_used = 0;
+    ctx->mask16_src = nullptr;
     for (int i = 0; i < cgraph->n_nodes;) {
         ggml_tensor * node = cgraph->nodes[i];
         if (is_noop(node) || ctx->node_done[(size_t) i]) { ++i; continue; }

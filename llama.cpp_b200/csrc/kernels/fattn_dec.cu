@@ -31,6 +31,7 @@ struct FdParams {
     int n_splits, kv_per_split;
     float scale, softcap, max_bias, m0, m1; int n_head_log2;
     blk_act128 * act_out;    // optional (D = 128, one query batch): int8 blocks of dst for the MUL_MAT that reads it
+    int v_t; int64_t v_nbd;  // V stored transposed (the cache layout without FLASH_ATTN_EXT): keys contiguous, v_nbd bytes between head-dim rows
 };
 
 // One output row (query iq, head) of D = 128 values is exactly one blk_act128 of the [n_head * D] activation
@@ -64,7 +65,8 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
     const char * vbase = p.v + (int64_t) hk * p.v_nb2 + (int64_t) k3 * p.v_nb3;
 
     const int kv0 = split * p.kv_per_split, kv1 = min(p.n_kv, kv0 + p.kv_per_split);
-    const int per_warp = (max(kv1 - kv0, 0) + FD_WARPS - 1) / FD_WARPS;
+    int per_warp = (max(kv1 - kv0, 0) + FD_WARPS - 1) / FD_WARPS;
+    if (p.v_t) per_warp = (per_warp + 7) & ~7;                     // 16-byte aligned runs of keys in the transposed V rows
     const int kw0 = kv0 + warp * per_warp, kw1 = min(kv1, kw0 + per_warp);
     const int nkeys = max(kw1 - kw0, 0);
 
@@ -184,6 +186,27 @@ __global__ void __launch_bounds__(FD_WARPS * 32) fattn_dec_kernel(const FdParams
         for (int rr = 0; rr < FD_RT; ++rr)
 #pragma unroll
             for (int i = 0; i < DPL; ++i) o[rr][i] = 0.0f;
+        if (p.v_t) {
+            // transposed V: row d of the cache holds the keys contiguously; a lane streams its DPL rows, 8 keys per load
+            for (int kb = 0; kb < nkeys; kb += 8) {
+                uint4 raw[DPL];
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) raw[i] = __ldg((const uint4 *) (vbase + (int64_t) (lane * DPL + i) * p.v_nbd + (int64_t) (kw0 + kb) * 2));
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (kb + u >= nkeys) break;                     // (what lies past the last key of the cache row is not touched)
+                    const float4 pv = *(const float4 *) ps[warp][kb + u];
+                    if (pv.x == 0.0f && pv.y == 0.0f && pv.z == 0.0f && pv.w == 0.0f) continue;   // masked key (warp-uniform)
+                    const float pr[FD_RT] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) {
+                        const float vf = __half2float(((const __half *) &raw[i])[u]);
+#pragma unroll
+                        for (int rr = 0; rr < FD_RT; ++rr) o[rr][i] += pr[rr] * vf;
+                    }
+                }
+            }
+        } else
         for (int kb = 0; kb < nkeys; kb += 8) {                     // 8 V rows in flight per lane
             uint2 raw[8];
 #pragma unroll
@@ -307,7 +330,9 @@ bool fattn_dec_applicable(const TensorD & q, const TensorD & k, const TensorD & 
     if ((q.ne[2] / k.ne[2]) * q.ne[1] > 64) return false;
     if (k.ne[2] * q.ne[3] > FD_TICKETS) return false;
     auto al16 = [](const TensorD & t) { return ((uintptr_t) t.data & 15) == 0 && (t.nb[1] & 15) == 0 && (t.nb[2] & 15) == 0 && (t.nb[3] & 15) == 0; };
-    if (!al16(k) || !al16(v)) return false;
+    if (!al16(k)) return false;
+    if (v.nb[0] == 2) { if (!al16(v)) return false; }
+    else if (v.nb[1] != 2 || ((uintptr_t) v.data & 15) || (v.nb[0] & 15) || (v.nb[2] & 15) || (v.nb[3] & 15)) return false;   // transposed V
     if (((uintptr_t) q.data & 3) || (q.nb[1] & 3) || (q.nb[2] & 3) || (q.nb[3] & 3)) return false;
     (void) mask;
     return true;
@@ -339,6 +364,7 @@ cudaError_t launch_fattn_dec(const TensorD & q, const TensorD & k, const TensorD
     p.q = (const char *) q.data; p.q_nb1 = q.nb[1]; p.q_nb2 = q.nb[2]; p.q_nb3 = q.nb[3];
     p.k = (const char *) k.data; p.k_nb1 = k.nb[1]; p.k_nb2 = k.nb[2]; p.k_nb3 = k.nb[3];
     p.v = (const char *) v.data; p.v_nb1 = v.nb[1]; p.v_nb2 = v.nb[2]; p.v_nb3 = v.nb[3];
+    p.v_t = v.nb[0] != 2 ? 1 : 0; p.v_nbd = v.nb[0];
     p.mask = mask ? (const char *) mask->data : nullptr; p.m_nb1 = mask ? mask->nb[1] : 0;
     p.dst = (float *) dst.data; p.ws = (float *) partials; p.tickets = (unsigned *) tickets;
     p.n_q = (int) q.ne[1]; p.n_kv = (int) k.ne[1]; p.n_head = (int) q.ne[2]; p.n_head_kv = (int) k.ne[2];

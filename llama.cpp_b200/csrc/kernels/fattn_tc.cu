@@ -38,6 +38,7 @@ struct FtParams {
     float * dst;
     int n_q, n_kv, n_head, gqa;
     float scale_log2;                               // scale * log2(e)
+    int v_t;                                        // V stored transposed (keys contiguous): the cache layout without FLASH_ATTN_EXT
     int * status;
 };
 
@@ -221,7 +222,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) fattn_tc_kernel(const FtParams 
     } else if (warp == 4) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc_s = umma_idesc_f16(FT_BM, FT_BN), idesc_o = umma_idesc_f16_bmn(FT_BM, FT_D);
+            constexpr uint32_t idesc_s = umma_idesc_f16(FT_BM, FT_BN), idesc_o = umma_idesc_f16_bmn(FT_BM, FT_D), idesc_ot = umma_idesc_f16(FT_BM, FT_D);
             bool ok = mbar_wait_or_abort(smem_u32(&q_full), 0, &abort_flag);
             // S(j) = Q K(j)^T over the head size: 8 x (128 x 128 x 16); the two 64-value halves are separate swizzle atoms
             auto issue_s = [&](int j) -> bool {
@@ -249,9 +250,16 @@ __global__ void __launch_bounds__(FT_THREADS, 1) fattn_tc_kernel(const FtParams 
                 if (!mbar_wait_or_abort(smem_u32(&v_full[b]), (uint32_t) (j >> 1) & 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t va = smem_u32(v_s + b * FT_TILE_BYTES);
+                if (p.v_t) {
+                    // V^T tile [d][64 keys] x 2: K-major like the K tile (16 keys = 32 bytes inside the swizzle atom)
 #pragma unroll
-                for (int kk = 0; kk < FT_BN / 16; ++kk)               // 16 keys: 8 columns of P, 16 rows (2048 bytes) of V
-                    umma_f16_ts(tmem + COL_O, tmem + COL_P + (uint32_t) (b * 64 + kk * 8), umma_smem_desc_mn(va + kk * 2048, FT_BN * 128), idesc_o, (j | kk) != 0);
+                    for (int kk = 0; kk < FT_BN / 16; ++kk)
+                        umma_f16_ts(tmem + COL_O, tmem + COL_P + (uint32_t) (b * 64 + kk * 8), umma_smem_desc(va + (kk >> 2) * (FT_D * 128) + (kk & 3) * 32), idesc_ot, (j | kk) != 0);
+                } else {
+#pragma unroll
+                    for (int kk = 0; kk < FT_BN / 16; ++kk)           // 16 keys: 8 columns of P, 16 rows (2048 bytes) of V
+                        umma_f16_ts(tmem + COL_O, tmem + COL_P + (uint32_t) (b * 64 + kk * 8), umma_smem_desc_mn(va + kk * 2048, FT_BN * 128), idesc_o, (j | kk) != 0);
+                }
                 umma_commit(&v_empty[b]);
                 umma_commit(&o_done);
             }
@@ -272,8 +280,13 @@ __global__ void __launch_bounds__(FT_THREADS, 1) fattn_tc_kernel(const FtParams 
                 tma_load_3d(k_s + b * FT_TILE_BYTES + FT_BN * 128, &kmap, 64, kt * FT_BN, head_kv, &k_full[b]);
                 if (j >= 2 && !mbar_wait_or_abort(smem_u32(&v_empty[b]), (uint32_t) ((j >> 1) - 1) & 1, &abort_flag)) { ok = false; break; }
                 mbar_arrive_expect_tx(&v_full[b], FT_TILE_BYTES);
-                tma_load_3d(v_s + b * FT_TILE_BYTES, &vmap, 0, kt * FT_BN, head_kv, &v_full[b]);
-                tma_load_3d(v_s + b * FT_TILE_BYTES + FT_BN * 128, &vmap, 64, kt * FT_BN, head_kv, &v_full[b]);
+                if (p.v_t) {                                           // boxes of 64 keys x 128 rows of V^T
+                    tma_load_3d(v_s + b * FT_TILE_BYTES, &vmap, kt * FT_BN, 0, head_kv, &v_full[b]);
+                    tma_load_3d(v_s + b * FT_TILE_BYTES + FT_D * 128, &vmap, kt * FT_BN + 64, 0, head_kv, &v_full[b]);
+                } else {
+                    tma_load_3d(v_s + b * FT_TILE_BYTES, &vmap, 0, kt * FT_BN, head_kv, &v_full[b]);
+                    tma_load_3d(v_s + b * FT_TILE_BYTES + FT_BN * 128, &vmap, 64, kt * FT_BN, head_kv, &v_full[b]);
+                }
                 ++j;
             }
             if (!ok) { atomicExch(p.status, ERR_MBAR_TIMEOUT); abort_flag = 1; }
@@ -294,11 +307,14 @@ __global__ void __launch_bounds__(FT_THREADS, 1) fattn_tc_kernel(const FtParams 
 }
 
 bool fattn_tc_applicable(const TensorD & q, const TensorD & k, const TensorD & v, const TensorD * mask, const FattnParams & fp) {
-    if (q.ne[0] != FT_D || v.ne[0] != FT_D || q.ne[1] < 64 || q.ne[3] != 1 || k.ne[3] != 1 || v.ne[3] != 1) return false;
+    const bool v_t = v.nb[0] != 2;                  // transposed V: keys contiguous, nb[0] bytes between head-dim rows
+    if (q.ne[0] != FT_D || v.ne[0] != FT_D || q.ne[1] < (v_t ? 9 : 64) || q.ne[3] != 1 || k.ne[3] != 1 || v.ne[3] != 1) return false;
     if (q.type != T_F32 || k.type != T_F16 || v.type != T_F16 || fp.max_bias != 0.0f || fp.logit_softcap != 0.0f) return false;
     if (k.ne[2] != v.ne[2] || k.ne[2] == 0 || q.ne[2] % k.ne[2] != 0 || k.ne[1] != v.ne[1]) return false;
     auto al16 = [](const TensorD & t) { return ((uintptr_t) t.data & 15) == 0 && (t.nb[1] & 15) == 0 && (t.nb[2] & 15) == 0; };
-    if (!al16(k) || !al16(v) || !al16(q) || k.nb[0] != 2 || v.nb[0] != 2 || q.nb[0] != 4) return false;
+    if (!al16(k) || !al16(q) || k.nb[0] != 2 || q.nb[0] != 4) return false;
+    if (!v_t) { if (!al16(v)) return false; }
+    else if (v.nb[1] != 2 || ((uintptr_t) v.data & 15) || (v.nb[0] & 15) || (v.nb[2] & 15)) return false;
     if (mask && (mask->type != T_F16 || ((uintptr_t) mask->data & 15) || (mask->nb[1] & 15) || mask->ne[2] != 1 || mask->ne[3] != 1)) return false;
     return true;
 }
@@ -315,6 +331,7 @@ cudaError_t launch_fattn_tc(const TensorD & q, const TensorD & k, const TensorD 
     p.n_q = (int) q.ne[1]; p.n_kv = (int) k.ne[1]; p.n_head = (int) q.ne[2]; p.gqa = (int) (q.ne[2] / k.ne[2]);
     p.scale_log2 = fp.scale * 1.4426950408889634f;
     p.status = c.status;
+    p.v_t = v.nb[0] != 2 ? 1 : 0;
     if (mask) {
         const int kt = (p.n_kv + 63) / 64;                        // flags: one byte per 64 x 64 tile of the mask
         p.flags = (const uint8_t *) workspace; p.flags_stride = kt;
@@ -325,8 +342,9 @@ cudaError_t launch_fattn_tc(const TensorD & q, const TensorD & k, const TensorD 
     CUtensorMap maps[2];
     const TensorD * kv[2] = {&k, &v};
     for (int i = 0; i < 2; ++i) {
-        const cuuint64_t gdim[3] = {(cuuint64_t) FT_D, (cuuint64_t) kv[i]->ne[1], (cuuint64_t) kv[i]->ne[2]};
-        const cuuint64_t gstr[2] = {(cuuint64_t) kv[i]->nb[1], (cuuint64_t) kv[i]->nb[2]};
+        const bool tr = i == 1 && p.v_t;            // V^T: [key][d][kv head], boxes of 64 keys x 128 rows
+        const cuuint64_t gdim[3] = {(cuuint64_t) (tr ? kv[i]->ne[1] : FT_D), (cuuint64_t) (tr ? FT_D : kv[i]->ne[1]), (cuuint64_t) kv[i]->ne[2]};
+        const cuuint64_t gstr[2] = {(cuuint64_t) (tr ? kv[i]->nb[0] : kv[i]->nb[1]), (cuuint64_t) kv[i]->nb[2]};
         const cuuint32_t box[3] = {64, FT_BN, 1}, estr[3] = {1, 1, 1};
         if (enc(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, kv[i]->data, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)

@@ -4,7 +4,8 @@
 // graph-level cases that single-op tests cannot express (memory reused inside a graph).  Public ggml API only;
 // built by oracle/ref.mk against the reference headers; test infrastructure.
 //   graph_cases DEVICE SUITE [N_THREADS]
-//   suites: mul_mat (the projection shapes x types x batch sizes), flash_attn, alias, split (weights in the device's
+//   suites: mul_mat (the projection shapes x types x batch sizes), flash_attn, alias, attn_chain (attention as the model
+//   graphs build it without FLASH_ATTN_EXT: MUL_MAT, SOFT_MAX, MUL_MAT on a transposed V cache, PERMUTE, CONT), split (weights in the device's
 //   row-split buffer type, ggml_backend_split_buffer_type by name: a scatter / gather round trip and MUL_MAT)
 // One line per case: "CASE <name> nmse=<x> max_abs=<y> n=<elements>"
 #include "ggml.h"
@@ -218,6 +219,57 @@ static void suite_alias() {
     });
 }
 
+// Attention without FLASH_ATTN_EXT, shaped like libllama's (src/llama.cpp:601-650): K and the transposed V are views of a
+// larger cache, the mask is F32 and padded, Q is a permuted view.  `extra_user` adds a second reader of the probabilities
+// (the chain must then not be replaced by one fused launch, and the result must still be right).
+static void attn_chain_case(const std::string & name, int64_t D, int64_t n_head, int64_t n_head_kv, int64_t n_q, int64_t n_kv, int64_t n_ctx, bool extra_user) {
+    run_case(name, [=](ggml_context * ctx) {
+        Built b;
+        ggml_tensor * kc = ggml_new_tensor_1d(ctx, GGML_TYPE_F16, D * n_head_kv * n_ctx);      // rows of D * n_head_kv per token
+        ggml_tensor * vc = ggml_new_tensor_1d(ctx, GGML_TYPE_F16, D * n_head_kv * n_ctx);      // transposed: n_ctx values per (head, d) row
+        ggml_tensor * qin = ggml_new_tensor_3d(ctx, GGML_TYPE_F32, D, n_head, n_q);
+        const int64_t n_pad = (n_q + 31) / 32 * 32;
+        ggml_tensor * mask = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, n_kv, n_pad);
+        ggml_tensor * q = ggml_permute(ctx, qin, 0, 2, 1, 3);                                   // [D, n_q, n_head]
+        ggml_tensor * k = ggml_view_3d(ctx, kc, D, n_kv, n_head_kv, (size_t) D * n_head_kv * 2, (size_t) D * 2, 0);
+        ggml_tensor * kq = ggml_mul_mat(ctx, k, q);                                             // [n_kv, n_q, n_head]
+        ggml_tensor * p = ggml_soft_max_ext(ctx, kq, mask, 1.0f / sqrtf((float) D), 0.0f);
+        ggml_tensor * v = ggml_view_3d(ctx, vc, n_kv, D, n_head_kv, (size_t) n_ctx * 2, (size_t) n_ctx * D * 2, 0);
+        ggml_tensor * kqv = ggml_mul_mat(ctx, v, p);                                            // [D, n_q, n_head]
+        ggml_tensor * merged = ggml_permute(ctx, kqv, 0, 2, 1, 3);
+        ggml_tensor * out = ggml_cont_2d(ctx, merged, D * n_head, n_q);
+        b.graph = ggml_new_graph(ctx);
+        ggml_build_forward_expand(b.graph, out);
+        b.outputs = {out};
+        if (extra_user) {
+            ggml_tensor * s2 = ggml_scale(ctx, p, 2.0f);
+            ggml_build_forward_expand(b.graph, s2);
+            b.outputs.push_back(s2);
+        }
+        std::vector<float> kf = normal((size_t) D * n_head_kv * n_ctx, 1.0f, 3), vf = normal((size_t) D * n_head_kv * n_ctx, 1.0f, 4);
+        std::vector<uint8_t> kb(kf.size() * 2), vb(vf.size() * 2);
+        ggml_fp32_to_fp16_row(kf.data(), (ggml_fp16_t *) kb.data(), (int64_t) kf.size());
+        ggml_fp32_to_fp16_row(vf.data(), (ggml_fp16_t *) vb.data(), (int64_t) vf.size());
+        std::vector<float> mf((size_t) n_kv * n_pad, -INFINITY);
+        for (int64_t iq = 0; iq < n_q; ++iq) for (int64_t ik = 0; ik <= n_kv - n_q + iq && ik < n_kv; ++ik) mf[(size_t) iq * n_kv + ik] = 0.0f;
+        b.inputs.push_back({kc, kb});
+        b.inputs.push_back({vc, vb});
+        b.inputs.push_back({qin, as_bytes(normal((size_t) D * n_head * n_q, 1.0f, 5))});
+        b.inputs.push_back({mask, as_bytes(mf)});
+        return b;
+    });
+}
+static void suite_attn_chain() {
+    attn_chain_case("attn_chain.d128.q1.kv512", 128, 32, 8, 1, 512, 1024, false);
+    attn_chain_case("attn_chain.d128.q4.kv320", 128, 32, 8, 4, 320, 512, false);
+    attn_chain_case("attn_chain.d64.q1.kv256", 64, 8, 2, 1, 256, 256, false);
+    attn_chain_case("attn_chain.d128.q37.kv64", 128, 16, 4, 37, 64, 256, false);
+    attn_chain_case("attn_chain.d128.q200.kv1024", 128, 8, 2, 200, 1024, 2048, false);
+    attn_chain_case("attn_chain.d128.q512.kv512", 128, 32, 8, 512, 512, 512, false);
+    attn_chain_case("attn_chain.d128.q512.kv4096", 128, 32, 8, 512, 4096, 4096, false);
+    attn_chain_case("attn_chain.d128.q64.kv128.second_reader", 128, 8, 2, 64, 128, 256, true);
+}
+
 // MUL_MAT with the weights in the row-split buffer type.  Row counts that are not multiples of the 128-row rounding, an
 // uneven split, batch sizes of both the mat-vec and the tensor-core path.
 static void suite_split(ggml_backend_dev_t dev) {
@@ -280,6 +332,7 @@ int main(int argc, char ** argv) {
     else if (suite == "flash_attn") suite_flash_attn();
     else if (suite == "alias") suite_alias();
     else if (suite == "split") suite_split(dev);
+    else if (suite == "attn_chain") suite_attn_chain();
     else { fprintf(stderr, "unknown suite %s\n", argv[2]); return 2; }
     ggml_backend_free(g_dev); ggml_backend_free(g_cpu);
     return g_fail;

@@ -22,6 +22,7 @@ def run_suite(suite: str, env_extra=None, timeout=1800):
     env = dict(os.environ, GGML_BACKEND_PATH=str(ROOT / "llama.cpp_b200" / "lib" / "libggml-b200.so"), **(env_extra or {}))
     r = subprocess.run([str(exe), "B200_0", suite, str(os.cpu_count() or 8)], cwd=REF, env=env, capture_output=True, text=True, timeout=timeout)
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    run_suite.last_stderr = r.stderr
     cases = {m.group(1): (float(m.group(2)), int(m.group(3))) for m in re.finditer(r"CASE (\S+) nmse=(\S+) max_abs=\S+ n=(\d+)", r.stdout)}
     assert cases and "NONFINITE" not in r.stdout, r.stdout[-2000:]
     return cases
@@ -54,3 +55,19 @@ def test_graphs_that_reuse_memory(fuse):
     assert len(cases) == 2
     for name, (nmse, _) in cases.items():
         assert nmse <= NMSE, (name, nmse)
+
+
+def test_attention_without_flash_attn_ext():
+    """Attention as model graphs build it without FLASH_ATTN_EXT (MUL_MAT, SOFT_MAX with an F32 mask, MUL_MAT on the transposed
+    V cache, PERMUTE, CONT), which the backend computes as one flash-attention launch when nothing else reads the
+    intermediates: decode and prefill shapes, and a graph with a second reader of the probabilities (not replaced)."""
+    def launches():
+        return sum(int(x) for x in re.findall(r"(\d+) kernel launches", run_suite.last_stderr))
+    fused = run_suite("attn_chain", {"GGML_B200_VERBOSE": "1"})
+    n_fused = launches()
+    plain = run_suite("attn_chain", {"GGML_B200_FUSE": "0", "GGML_B200_VERBOSE": "1"})
+    n_plain = launches()
+    assert len(fused) == 8 and len(plain) == 8
+    assert 0 < n_fused < n_plain, (n_fused, n_plain)           # the chains really went out as single launches
+    for name in fused:
+        assert fused[name][0] <= NMSE and plain[name][0] <= NMSE, (name, fused[name], plain[name])

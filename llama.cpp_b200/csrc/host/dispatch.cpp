@@ -197,6 +197,16 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
         }
     }
     if (!ids && is_float_type(W->type)) {
+        // 16-bit weight matrices with plain 2-D operands: warp-per-row mat-vec (at most 8 columns) or the tcgen05 GEMM
+        const TensorD wd = to_desc(W), xd = to_desc(X), dd = to_desc(dst);
+        if (mv16_applicable(wd, xd, dd)) {
+            RUN(launch_mv16(wd, xd, dd, lc));
+        } else if (ctx->use_tc && mm16_tc_applicable(wd, xd, dd)) {
+            void * ws = ctx->get_scratch(mm16_tc_workspace_bytes(X->ne[1], W->ne[0]));
+            if (ctx->capture_failed) return false;
+            RUN(launch_mm16_tc(wd, xd, dd, ws, lc));
+            ctx->n_launches++;
+        } else
         RUN(launch_matmul_f(to_desc(W), to_desc(X), to_desc(dst), lc));
         if (sliced && !push_slice(ctx, dst)) return false;
         return true;

@@ -96,6 +96,13 @@ cudaError_t launch_mmq_tc_group(int type, int n_mats, const void * const * W, in
                                 const LaunchCtx & c, bool preconverted = false, void * partials = nullptr);
 size_t      mmq_tc_group_partial_bytes(int n_mats, const int64_t * M, int64_t N, int64_t K, int sm_count);
 
+// ---- F16 / BF16 weight matrices on the fast paths (matmul_f_tc.cu): tcgen05 GEMM for more than 8 columns, warp-per-row mat-vec below ----
+bool        mm16_tc_applicable(const TensorD & W, const TensorD & X, const TensorD & dst);
+size_t      mm16_tc_workspace_bytes(int64_t N, int64_t K);
+cudaError_t launch_mm16_tc(const TensorD & W, const TensorD & X, const TensorD & dst, void * workspace, const LaunchCtx & c);
+bool        mv16_applicable(const TensorD & W, const TensorD & X, const TensorD & dst);
+cudaError_t launch_mv16(const TensorD & W, const TensorD & X, const TensorD & dst, const LaunchCtx & c);
+
 // ---- measurement of the int8 design alternative of the prefill GEMM (tc_i8_probe.cu); not on a product path ----
 cudaError_t launch_tc_i8_probe(int kblocks, int reps, float * us_per_kblock, float * check, float * expected, const LaunchCtx & c);
 

@@ -4,7 +4,7 @@
 // graph-level cases that single-op tests cannot express (memory reused inside a graph).  Public ggml API only;
 // built by oracle/ref.mk against the reference headers; test infrastructure.
 //   graph_cases DEVICE SUITE [N_THREADS]
-//   suites: mul_mat (the projection shapes x types x batch sizes), flash_attn, alias, attn_chain (attention as the model
+//   suites: mul_mat (the projection shapes x types x batch sizes), mul_mat_f16 (F16 / BF16 weights), flash_attn, alias, attn_chain (attention as the model
 //   graphs build it without FLASH_ATTN_EXT: MUL_MAT, SOFT_MAX, MUL_MAT on a transposed V cache, PERMUTE, CONT), split (weights in the device's
 //   row-split buffer type, ggml_backend_split_buffer_type by name: a scatter / gather round trip and MUL_MAT)
 // One line per case: "CASE <name> nmse=<x> max_abs=<y> n=<elements>"
@@ -129,6 +129,28 @@ static void suite_mul_mat() {
             b.graph = ggml_new_graph(ctx);
             ggml_build_forward_expand(b.graph, y);
             b.inputs.push_back({w, quantized(type, K, M, 7)});
+            b.inputs.push_back({x, as_bytes(normal((size_t) K * N, 1.0f, 11 + (unsigned) N))});
+            b.outputs = {y};
+            return b;
+        });
+    }
+}
+
+// 16-bit weight matrices: the warp-per-row mat-vec (at most 8 columns) and the tcgen05 GEMM, row counts off the tile size
+static void suite_mul_mat_f16() {
+    for (ggml_type type : {GGML_TYPE_F16, GGML_TYPE_BF16}) for (int64_t N : {1, 3, 8, 9, 64, 200, 512}) {
+        const int64_t K = 4096, M = 4096 + 200;
+        run_case(std::string("mul_mat_f16.") + ggml_type_name(type) + ".n" + std::to_string(N), [=](ggml_context * ctx) {
+            Built b;
+            ggml_tensor * w = ggml_new_tensor_2d(ctx, type, K, M), * x = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, K, N);
+            ggml_tensor * y = ggml_mul_mat(ctx, w, x);
+            b.graph = ggml_new_graph(ctx);
+            ggml_build_forward_expand(b.graph, y);
+            std::vector<float> wf = normal((size_t) K * M, 0.02f, 5);
+            std::vector<uint8_t> wb((size_t) K * M * 2);
+            if (type == GGML_TYPE_F16) ggml_fp32_to_fp16_row(wf.data(), (ggml_fp16_t *) wb.data(), K * M);
+            else ggml_fp32_to_bf16_row(wf.data(), (ggml_bf16_t *) wb.data(), K * M);
+            b.inputs.push_back({w, wb});
             b.inputs.push_back({x, as_bytes(normal((size_t) K * N, 1.0f, 11 + (unsigned) N))});
             b.outputs = {y};
             return b;
@@ -333,6 +355,7 @@ int main(int argc, char ** argv) {
     else if (suite == "alias") suite_alias();
     else if (suite == "split") suite_split(dev);
     else if (suite == "attn_chain") suite_attn_chain();
+    else if (suite == "mul_mat_f16") suite_mul_mat_f16();
     else { fprintf(stderr, "unknown suite %s\n", argv[2]); return 2; }
     ggml_backend_free(g_dev); ggml_backend_free(g_cpu);
     return g_fail;

@@ -71,3 +71,12 @@ def test_attention_without_flash_attn_ext():
     assert 0 < n_fused < n_plain, (n_fused, n_plain)           # the chains really went out as single launches
     for name in fused:
         assert fused[name][0] <= NMSE and plain[name][0] <= NMSE, (name, fused[name], plain[name])
+
+
+def test_mul_mat_f16_bf16_weights():
+    """F16 and BF16 weight matrices (4296 x 4096) at N in {1, 3, 8, 9, 64, 200, 512}: the warp-per-row mat-vec up to 8 columns,
+    the tcgen05 GEMM above, every element against the reference CPU backend."""
+    cases = run_suite("mul_mat_f16")
+    assert len(cases) == 14, sorted(cases)
+    bad = {k: v for k, v in cases.items() if v[0] > NMSE}
+    assert not bad, bad

@@ -264,6 +264,21 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
         if (sliced && !push_slice(ctx, dst)) return false;
         return true;
     }
+    if (ids && ctx->use_tc) {
+        // MUL_MAT_ID over many (slot, token) pairs (a prompt through a mixture-of-experts layer): the pairs are sorted by
+        // expert on the device and all experts run as one tensor-core launch; few pairs keep the per-pair mat-vec below
+        const int64_t n_used = ids->ne[0], n_tok = ids->ne[1], P = n_used * n_tok, n_expert = W->ne[2];
+        if (P >= 32 && W->ne[3] == 1 && X->ne[3] == 1 && mmq_tc_moe_supported(W->type, M, K, n_expert, P) &&
+            mmq_tc_ptr_ok(W->type, W->data, W->nb[1], X->data, X->nb[1]) && W->nb[2] % 16 == 0 && X->nb[2] % 8 == 0 &&
+            ids->nb[0] == 4 && ids->nb[1] % 4 == 0 && dst->nb[0] == 4 && dst->ne[3] == 1) {
+            void * ws = ctx->get_scratch(mmq_tc_moe_workspace_bytes(P, K, n_expert));
+            if (ctx->capture_failed) return false;
+            RUN(launch_mmq_tc_moe(W->type, W->data, W->nb[1], W->nb[2], n_expert, M, K, (const float *) X->data, X->nb[1], X->nb[2], ne11,
+                                  (const int32_t *) ids->data, ids->nb[1], n_used, n_tok, (float *) dst->data, dst->nb[1], dst->nb[2], ws, lc));
+            ctx->n_launches += 2;
+            return true;
+        }
+    }
     void * xq = nullptr;
     if (act_cacheable(X)) {
         BackendCtx::ActEntry * e = ctx->act_cache_find(X->data, K, ne11 * ne12 * ne13);

@@ -95,6 +95,13 @@ cudaError_t launch_mmq_tc_group(int type, int n_mats, const void * const * W, in
                                 const int64_t * dst_nb1, const float * X, int64_t x_nb1, int64_t N, int64_t K, void * workspace,
                                 const LaunchCtx & c, bool preconverted = false, void * partials = nullptr);
 size_t      mmq_tc_group_partial_bytes(int n_mats, const int64_t * M, int64_t N, int64_t K, int sm_count);
+// MUL_MAT_ID over many (slot, token) pairs on the same GEMM: pairs sorted by expert on the device, one launch for all experts
+bool        mmq_tc_moe_supported(int type, int64_t M, int64_t K, int64_t n_expert, int64_t n_pairs);
+size_t      mmq_tc_moe_workspace_bytes(int64_t n_pairs, int64_t K, int64_t n_expert);
+cudaError_t launch_mmq_tc_moe(int type, const void * W, int64_t w_nb1, int64_t w_nb2, int64_t n_expert, int64_t M, int64_t K,
+                              const float * X, int64_t x_nb1, int64_t x_nb2, int64_t ne11,
+                              const int32_t * ids, int64_t ids_nb1, int64_t n_used, int64_t n_tok,
+                              float * dst, int64_t dst_nb1, int64_t dst_nb2, void * workspace, const LaunchCtx & c);
 
 // ---- F16 / BF16 weight matrices on the fast paths (matmul_f_tc.cu): tcgen05 GEMM for more than 8 columns, warp-per-row mat-vec below ----
 bool        mm16_tc_applicable(const TensorD & W, const TensorD & X, const TensorD & dst);

@@ -1,10 +1,10 @@
 // MUL_MAT for F16 / BF16 weight matrices (unquantized models, float side matrices) on the fast paths:
-//   mm16_tc_kernel   more than 8 activation columns: tcgen05 GEMM.  Both operands are 16-bit K-major tiles brought in by
+//   mm16_tc_kernel   more than 4 activation columns: tcgen05 GEMM.  Both operands are 16-bit K-major tiles brought in by
 //                    tiled tensor copies with the 128-byte swizzle (weights straight from the model's rows, activations
 //                    from the F16 / BF16 copy the caller's workspace holds), `tcgen05.mma kind::f16` 128 x 128 x 16 from
 //                    shared-memory descriptors into an FP32 tensor-memory accumulator, six stages; one thread loads, one
 //                    issues, four warps read the accumulator back and store.
-//   mv16_kernel      at most 8 columns: one warp per weight row, 128-bit loads, FP32 accumulation (HBM-bound).
+//   mv16_kernel      at most 4 columns: one warp per weight row, 128-bit loads, FP32 accumulation (HBM-bound).
 // What the reference does with cuBLAS for these types (ggml_cuda_op_mul_mat_cublas, ggml/src/ggml-cuda/ggml-cuda.cu:1180-1290:
 // 16-bit operands, FP32 result) and with mul_mat_vec (ggml/src/ggml-cuda/mmv.cu:5-91).  Strided / batched / F32-weight
 // products stay on matmul_f_kernel (matmul_f.cu).  Every mbarrier wait is bounded.
@@ -133,7 +133,7 @@ __global__ void mf_convert_f16_kernel(const float * __restrict__ x, int64_t x_nb
 bool mm16_tc_applicable(const TensorD & W, const TensorD & X, const TensorD & dst) {
     if ((W.type != T_F16 && W.type != T_BF16) || X.type != T_F32 || dst.type != T_F32) return false;
     if (W.ne[2] != 1 || W.ne[3] != 1 || X.ne[2] != 1 || X.ne[3] != 1) return false;
-    if (X.ne[1] <= 8 || W.ne[0] % MF_BK != 0 || W.ne[0] < MF_BK) return false;
+    if (X.ne[1] <= 4 || W.ne[0] % MF_BK != 0 || W.ne[0] < MF_BK) return false;
     if (W.nb[0] != 2 || (W.nb[1] & 15) || ((uintptr_t) W.data & 15)) return false;
     if (X.nb[0] != 4 || (X.nb[1] & 7) || ((uintptr_t) X.data & 7) || dst.nb[0] != 4) return false;
     return true;
@@ -181,7 +181,7 @@ cudaError_t launch_mm16_tc(const TensorD & W, const TensorD & X, const TensorD &
     return launch_k(c.use_pdl, c.stream, mm16_tc_kernel, grid, dim3(MF_THREADS), smem, p, wmap, xmap);
 }
 
-// ---- at most 8 columns: warp per row ----
+// ---- at most 4 columns (the template takes up to 8): warp per row ----
 template <int N, bool BF>
 __global__ void __launch_bounds__(256) mv16_kernel(const char * __restrict__ W, int64_t w_nb1, const float * __restrict__ X, int64_t x_nb1 /*bytes*/,
                                                    float * dst, int64_t dst_nb1, int M, int K) {
@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(256) mv16_kernel(const char * __restrict__ W, 
 
 bool mv16_applicable(const TensorD & W, const TensorD & X, const TensorD & dst) {
     if ((W.type != T_F16 && W.type != T_BF16) || X.type != T_F32 || dst.type != T_F32) return false;
-    if (W.ne[2] != 1 || W.ne[3] != 1 || X.ne[2] != 1 || X.ne[3] != 1 || X.ne[1] > 8 || X.ne[1] < 1) return false;
+    if (W.ne[2] != 1 || W.ne[3] != 1 || X.ne[2] != 1 || X.ne[3] != 1 || X.ne[1] > 4 || X.ne[1] < 1) return false;     // (from 5 columns on the GEMM is faster)
     if (W.ne[0] % 8 != 0 || W.nb[0] != 2 || (W.nb[1] & 15) || ((uintptr_t) W.data & 15)) return false;
     return X.nb[0] == 4 && (X.nb[1] & 15) == 0 && ((uintptr_t) X.data & 15) == 0 && dst.nb[0] == 4;
 }

@@ -427,6 +427,11 @@ struct TcParams {
     // [z * kps, z * kps + kps) of tile n_direct + r into the partial tile part + (r * ksplit + z) * 128 * BN, and
     // tc_reduce_kernel sums the splits in order.
     int n_tiles_n, n_direct, ksplit, kps; float * part;
+    // MUL_MAT_ID over many (slot, token) pairs: the pairs are sorted by expert (tc_moe_sort_kernel), their activations
+    // gathered into Xh in that order, and a token tile is a run of up to BN sorted rows of ONE expert, listed on the device:
+    // moe_tiles[t] = {expert, first row, end row, 0}.  CTA = (m-tile, tile slot); slots past *moe_n_tiles leave at once.
+    // Row r of the sorted order is stored at dst + moe_row_off[r].  W[0] is expert 0, w_nb2 bytes between experts.
+    const int4 * moe_tiles; const int * moe_n_tiles; const int64_t * moe_row_off; int moe_nt_max, moe_n_expert; int64_t w_nb2;
 };
 
 
@@ -465,14 +470,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     // which tile, which part of K
     const int cta = (int) blockIdx.x;
-    const bool is_split = cta >= p.n_direct;
+    const bool moe = p.moe_tiles != nullptr;
+    int moe_expert = 0, moe_row0 = 0, moe_row_end = 0;
+    if (moe) {
+        const int slot = cta % p.moe_nt_max;
+        if (slot >= *p.moe_n_tiles) return;                         // (before any barrier or tensor-memory set-up; uniform over the CTA)
+        const int4 t = p.moe_tiles[slot];
+        moe_expert = t.x; moe_row0 = t.y; moe_row_end = t.z;
+    }
+    const bool is_split = !moe && cta >= p.n_direct;
     const int tile = is_split ? p.n_direct + (cta - p.n_direct) / p.ksplit : cta;
     const int zsplit = is_split ? (cta - p.n_direct) % p.ksplit : 0;
-    const int mt = tile / p.n_tiles_n, n0 = (tile - mt * p.n_tiles_n) * BN;
+    const int mt = moe ? cta / p.moe_nt_max : tile / p.n_tiles_n, n0 = moe ? moe_row0 : (tile - mt * p.n_tiles_n) * BN;
     const int mat = (p.n_mats > 2 && mt >= p.mt0[2]) ? 2 : ((p.n_mats > 1 && mt >= p.mt0[1]) ? 1 : 0);
     const int m0 = (mt - p.mt0[mat]) * TC_BM;
     const int M = p.M[mat];
-    const uint8_t * Wm = p.W[mat];
+    const uint8_t * Wm = p.W[mat] + (int64_t) moe_expert * p.w_nb2;
     const CUtensorMap * wmap = mat == 0 ? &wmap0 : (mat == 1 ? &wmap1 : &wmap2);
     const int ks_begin = is_split ? zsplit * p.kps : 0;             // this CTA's range of k-steps
     const int ksteps = is_split ? min(p.kps, p.K / TC_BK - ks_begin) : p.K / TC_BK;
@@ -580,7 +593,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
             char * out = is_split ? (char *) (p.part + (int64_t) (cta - p.n_direct) * TC_BM * BN) - (int64_t) n0 * TC_BM * 4 - (int64_t) m0 * 4
                                   : (char *) p.dst[mat];
             const int64_t out_nb1 = is_split ? (int64_t) TC_BM * 4 : p.dst_nb1[mat];
-            const int n_end = is_split ? n0 + BN : p.N, m_end = is_split ? m0 + TC_BM : M;
+            const int n_end = is_split ? n0 + BN : (moe ? moe_row_end : p.N), m_end = is_split ? m0 + TC_BM : M;
 #pragma unroll 1
             for (int c0 = cq * (BN / 4); c0 < cq * (BN / 4) + BN / 4; c0 += 32) {
                 uint32_t v[32];
@@ -590,7 +603,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int n = n0 + c0 + i;
-                        if (n < n_end) *(float *) (out + (int64_t) n * out_nb1 + (int64_t) m * 4) = __uint_as_float(v[i]);
+                        if (n < n_end) {
+                            if (moe) *(float *) (out + p.moe_row_off[n] + (int64_t) m * 4) = __uint_as_float(v[i]);
+                            else     *(float *) (out + (int64_t) n * out_nb1 + (int64_t) m * 4) = __uint_as_float(v[i]);
+                        }
                     }
                 }
             }
@@ -649,7 +665,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
                     if (c >= NRB && !mbar_wait(&raw_empty[buf], (uint32_t) (c / NRB - 1) & 1)) { ok = false; break; }
                     if (*(volatile int *) &abort_flag) break;
                     mbar_arrive_expect_tx(&raw_full[buf], TC_BM * CB);
-                    tma_load_2d(rawbuf + (size_t) buf * RAW_BYTES, wmap, (((k_base / TC_CHUNK_K + c) * TcChunk<T>::SRC) >> 4) * 4, m0, &raw_full[buf]);
+                    const int wx = (((k_base / TC_CHUNK_K + c) * TcChunk<T>::SRC) >> 4) * 4;
+                    if (moe) tma_load_3d(rawbuf + (size_t) buf * RAW_BYTES, wmap, wx, m0, moe_expert, &raw_full[buf]);      // (the map then has the expert as third dimension)
+                    else     tma_load_2d(rawbuf + (size_t) buf * RAW_BYTES, wmap, wx, m0, &raw_full[buf]);
                 }
                 if (!ok) { atomicExch(p.status, ERR_MBAR_TIMEOUT); abort_flag = 1; }
                 // When the kernel gives up, the last copies of this thread may still be in flight: wait (bounded) for
@@ -684,6 +702,7 @@ template <int T> static bool tc_can_stage(const TcParams & p) {
     if (TcChunk<T>::BYTES == 0 || p.K % TC_CHUNK_K) return false;
     const int64_t row_bytes = (int64_t) (p.K / TC_CHUNK_K) * TcChunk<T>::SRC;
     for (int j = 0; j < p.n_mats; ++j) if ((uintptr_t) p.W[j] & 15) return false;
+    if (p.moe_tiles && (p.w_nb2 & 15)) return false;
     return (p.w_nb1 & 15) == 0 && (row_bytes & 3) == 0 && p.w_nb1 >= row_bytes;
 }
 
@@ -776,7 +795,16 @@ static cudaError_t launch_tc_tb(const TcParams & p_in, int device, int use_pdl, 
         return cudaErrorInvalidValue;
     // per matrix, a tensor map of the raw weight rows as 32-bit words [M][row bytes / 4]: boxes of one 256-value chunk x 128 rows
     CUtensorMap wmap[TC_MAX_MATS] = {xmap, xmap, xmap};
-    if (p.staged) for (int j = 0; j < p.n_mats; ++j) {
+    if (p.staged && p.moe_tiles) {
+        // the experts' matrices as one [row words][M][expert] tensor
+        constexpr cuuint32_t CW = TcChunk<T>::BYTES / 4;
+        const cuuint64_t wdim[3] = {(cuuint64_t) (p.K / TC_CHUNK_K) * TcChunk<T>::SRC / 4, (cuuint64_t) p.M[0], (cuuint64_t) p.moe_n_expert};
+        const cuuint64_t wstr[2] = {(cuuint64_t) p.w_nb1, (cuuint64_t) p.w_nb2};
+        const cuuint32_t wbox[3] = {CW, TC_BM, 1}, estr3[3] = {1, 1, 1};
+        if (enc(&wmap[0], CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void *) p.W[0], wdim, wstr, wbox, estr3, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    } else if (p.staged) for (int j = 0; j < p.n_mats; ++j) {
         constexpr cuuint32_t CW = TcChunk<T>::BYTES / 4;
         const cuuint64_t wdim[2] = {(cuuint64_t) (p.K / TC_CHUNK_K) * TcChunk<T>::SRC / 4, (cuuint64_t) p.M[j]};
         const cuuint64_t wstr[1] = {(cuuint64_t) p.w_nb1};
@@ -784,6 +812,11 @@ static cudaError_t launch_tc_tb(const TcParams & p_in, int device, int use_pdl, 
         if (enc(&wmap[j], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void *) p.W[j], wdim, wstr, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
+    }
+    if (p.moe_tiles) {
+        // the tables are written by the kernel launched just before: no early start
+        const unsigned g = (unsigned) (p.moe_nt_max * p.mt0[p.n_mats]);
+        return launch_k(0, stream, kern, dim3(g), dim3(TC_THREADS), smem, p, xmap, wmap[0], wmap[1], wmap[2]);
     }
     const int n_split_tiles = p.mt0[p.n_mats] * p.n_tiles_n - p.n_direct;
     const unsigned grid = (unsigned) (p.n_direct + n_split_tiles * (p.ksplit > 1 ? p.ksplit : 0));
@@ -798,6 +831,114 @@ template <int T>
 static cudaError_t launch_tc_t(const TcParams & p, int bn, int device, int use_pdl, cudaStream_t stream) {
     if (bn == 256) return launch_tc_tb<T, 256>(p, device, use_pdl, stream);
     return launch_tc_tb<T, TC_BN>(p, device, use_pdl, stream);
+}
+
+// ---- MUL_MAT_ID over many (slot, token) pairs ------------------------------------------------------------------------
+// Sorts the pairs by expert (one CTA; every pair's place is found by the thread of its expert walking the pairs in order, so
+// the result does not depend on timing), lists the token tiles and records where each sorted row's result goes.
+__global__ void __launch_bounds__(1024) tc_moe_sort_kernel(const int32_t * ids, int64_t ids_s1 /*elements between tokens*/, int n_used, int n_tok, int n_expert,
+                                                           int bn, int64_t dst_nb1, int64_t dst_nb2, int * row_pair, int64_t * row_off, int4 * tiles, int * n_tiles) {
+    pdl_enter();
+    extern __shared__ int sh[];                                     // counts[n_expert], offsets[n_expert + 1]
+    int * counts = sh, * off = sh + n_expert;
+    const int P = n_used * n_tok;
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e = ids[(int64_t) (p / n_used) * ids_s1 + p % n_used];
+        if (e >= 0 && e < n_expert) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0, t = 0;
+        for (int e = 0; e < n_expert; ++e) {
+            off[e] = acc;
+            for (int r0 = acc; r0 < acc + counts[e]; r0 += bn) tiles[t++] = make_int4(e, r0, min(acc + counts[e], r0 + bn), 0);
+            acc += counts[e];
+        }
+        off[n_expert] = acc;
+        *n_tiles = t;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        int r = off[e];
+        for (int p = 0; p < P; ++p) {
+            const int it = p / n_used, iu = p - it * n_used;
+            if (ids[(int64_t) it * ids_s1 + iu] != e) continue;
+            row_pair[r] = p;
+            row_off[r] = (int64_t) iu * dst_nb1 + (int64_t) it * dst_nb2;
+            ++r;
+        }
+    }
+}
+// activations of the sorted rows as F16: row r = column (slot iu % ne11, token it) of src1
+__global__ void tc_moe_gather_kernel(const char * __restrict__ x, int64_t x_nb1, int64_t x_nb2, int ne11, int n_used, const int * __restrict__ row_pair,
+                                     __half * __restrict__ y, int64_t K, int64_t P) {
+    pdl_enter();
+    const int64_t total = P * K / 2;
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
+        const int64_t r = (2 * i) / K, k = (2 * i) % K;
+        const int p = row_pair[r], it = p / n_used, iu = p - it * n_used;
+        const float2 v = *(const float2 *) (x + (int64_t) (iu % ne11) * x_nb1 + (int64_t) it * x_nb2 + k * 4);
+        ((__half2 *) y)[i] = __floats2half2_rn(v.x, v.y);
+    }
+}
+
+static size_t moe_align(size_t v) { return (v + 255) & ~(size_t) 255; }
+bool mmq_tc_moe_supported(int type, int64_t M, int64_t K, int64_t n_expert, int64_t n_pairs) {
+    return mmq_tc_supported(type, M, n_pairs > 8 ? n_pairs : 9, K) && n_expert >= 1 && n_expert <= 1024 && n_pairs >= 1 && n_pairs <= (1 << 20);
+}
+size_t mmq_tc_moe_workspace_bytes(int64_t n_pairs, int64_t K, int64_t n_expert) {
+    const int64_t nt_max = (n_pairs + TC_BN - 1) / TC_BN + n_expert;
+    return moe_align((size_t) n_pairs * K * 2) + moe_align((size_t) n_pairs * 4) + moe_align((size_t) n_pairs * 8) + moe_align((size_t) nt_max * 16) + 256 + 256;
+}
+template <int T> static cudaError_t launch_moe_t(const TcParams & p, const LaunchCtx & c) { return launch_tc_tb<T, TC_BN>(p, c.device, 0, c.stream); }
+
+// dst[:, iu, it] = W[:, :, ids[iu, it]] x src1[:, iu % ne11, it] for all pairs at once (ggml_mul_mat_id, ggml/src/ggml.c:2735-2759;
+// the reference sorts on the host after copying ids back, ggml/src/ggml-cuda/ggml-cuda.cu:1956-2092; here nothing leaves the device)
+cudaError_t launch_mmq_tc_moe(int type, const void * W, int64_t w_nb1, int64_t w_nb2, int64_t n_expert, int64_t M, int64_t K,
+                              const float * X, int64_t x_nb1, int64_t x_nb2, int64_t ne11,
+                              const int32_t * ids, int64_t ids_nb1, int64_t n_used, int64_t n_tok,
+                              float * dst, int64_t dst_nb1, int64_t dst_nb2, void * workspace, const LaunchCtx & c) {
+    const int64_t P = n_used * n_tok;
+    const int nt_max = (int) ((P + TC_BN - 1) / TC_BN + n_expert);
+    char * ws = (char *) workspace;
+    __half * xh = (__half *) ws;                 ws += moe_align((size_t) P * K * 2);
+    int * row_pair = (int *) ws;                 ws += moe_align((size_t) P * 4);
+    int64_t * row_off = (int64_t *) ws;          ws += moe_align((size_t) P * 8);
+    int4 * tiles = (int4 *) ws;                  ws += moe_align((size_t) nt_max * 16);
+    int * n_tiles = (int *) ws;
+    cudaError_t e = launch_k(c.use_pdl, c.stream, tc_moe_sort_kernel, dim3(1), dim3(1024), (size_t) (2 * n_expert + 1) * sizeof(int), ids, ids_nb1 / 4,
+                             (int) n_used, (int) n_tok, (int) n_expert, (int) TC_BN, dst_nb1, dst_nb2, row_pair, row_off, tiles, n_tiles);
+    if (e != cudaSuccess) return e;
+    {
+        const int64_t total = P * K / 2;
+        int64_t g = (total + 255) / 256; if (g > (int64_t) c.sm_count * 8) g = (int64_t) c.sm_count * 8;
+        e = launch_k(c.use_pdl, c.stream, tc_moe_gather_kernel, dim3((unsigned) g), dim3(256), 0, (const char *) X, x_nb1, x_nb2, (int) ne11, (int) n_used,
+                     (const int *) row_pair, xh, K, P);
+        if (e != cudaSuccess) return e;
+    }
+    TcParams p = {};
+    p.n_mats = 1; p.w_nb1 = w_nb1; p.Xh = xh; p.N = (int) P; p.K = (int) K; p.status = c.status;
+    p.W[0] = (const uint8_t *) W; p.dst[0] = dst; p.dst_nb1[0] = dst_nb1; p.M[0] = (int) M;
+    p.mt0[0] = 0; for (int j = 1; j <= TC_MAX_MATS; ++j) p.mt0[j] = (int) ((M + TC_BM - 1) / TC_BM);
+    p.n_tiles_n = 1; p.n_direct = 1 << 30; p.ksplit = 1; p.kps = (int) (K / TC_BK); p.part = nullptr;
+    p.moe_tiles = tiles; p.moe_n_tiles = n_tiles; p.moe_row_off = row_off; p.moe_nt_max = nt_max; p.moe_n_expert = (int) n_expert; p.w_nb2 = w_nb2;
+    switch (type) {
+        case T_Q4_0: return launch_moe_t<T_Q4_0>(p, c);
+        case T_Q4_1: return launch_moe_t<T_Q4_1>(p, c);
+        case T_Q5_0: return launch_moe_t<T_Q5_0>(p, c);
+        case T_Q5_1: return launch_moe_t<T_Q5_1>(p, c);
+        case T_Q8_0: return launch_moe_t<T_Q8_0>(p, c);
+        case T_Q4_K: return launch_moe_t<T_Q4_K>(p, c);
+        case T_Q5_K: return launch_moe_t<T_Q5_K>(p, c);
+        case T_Q6_K: return launch_moe_t<T_Q6_K>(p, c);
+        case T_Q2_K: return launch_moe_t<T_Q2_K>(p, c);
+        case T_Q3_K: return launch_moe_t<T_Q3_K>(p, c);
+        case T_IQ4_NL: return launch_moe_t<T_IQ4_NL>(p, c);
+        case T_IQ4_XS: return launch_moe_t<T_IQ4_XS>(p, c);
+    }
+    return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_mmq_tc_group(int type, int n_mats, const void * const * W, int64_t w_nb1, const int64_t * M, float * const * dst,

@@ -4,10 +4,10 @@
 // graph-level cases that single-op tests cannot express (memory reused inside a graph).  Public ggml API only;
 // built by oracle/ref.mk against the reference headers; test infrastructure.
 //   graph_cases DEVICE SUITE [N_THREADS]
-//   suites: mul_mat (the projection shapes x types x batch sizes), mul_mat_f16 (F16 / BF16 weights), flash_attn, alias, attn_chain (attention as the model
+//   suites: mul_mat (the projection shapes x types x batch sizes), mul_mat_f16 (F16 / BF16 weights), mul_mat_id (experts), flash_attn, alias, attn_chain (attention as the model
 //   graphs build it without FLASH_ATTN_EXT: MUL_MAT, SOFT_MAX, MUL_MAT on a transposed V cache, PERMUTE, CONT), split (weights in the device's
 //   row-split buffer type, ggml_backend_split_buffer_type by name: a scatter / gather round trip and MUL_MAT)
-// One line per case: "CASE <name> nmse=<x> max_abs=<y> n=<elements>"
+// One line per case: "CASE <name> nmse=<x> max_abs=<y> n=<elements>"; with GRAPH_CASES_TIME set, a "TIME" line before it
 #include "ggml.h"
 #include "ggml-backend.h"
 
@@ -78,6 +78,15 @@ static std::vector<std::vector<float>> run_on(ggml_backend_t backend, const Buil
     if (!buf) { fprintf(stderr, "buffer allocation failed\n"); exit(1); }
     for (auto & in : b.inputs) ggml_backend_tensor_set(in.t, in.bytes.data(), 0, in.bytes.size());
     if (ggml_backend_graph_compute(backend, b.graph) != GGML_STATUS_SUCCESS) { fprintf(stderr, "graph_compute failed\n"); exit(1); }
+    if (backend == g_dev && getenv("GRAPH_CASES_TIME")) {
+        // host clock around repeated runs of the whole graph on the device (informational: "TIME <us per run>")
+        ggml_backend_synchronize(backend);
+        const int reps = 10;
+        const int64_t t0 = ggml_time_us();
+        for (int i = 0; i < reps; ++i) ggml_backend_graph_compute(backend, b.graph);
+        ggml_backend_synchronize(backend);
+        printf("TIME %.1f us per graph\n", (double) (ggml_time_us() - t0) / reps);
+    }
     std::vector<std::vector<float>> outs;
     for (ggml_tensor * t : b.outputs) {
         std::vector<float> v((size_t) ggml_nelements(t));
@@ -152,6 +161,36 @@ static void suite_mul_mat_f16() {
             else ggml_fp32_to_bf16_row(wf.data(), (ggml_bf16_t *) wb.data(), K * M);
             b.inputs.push_back({w, wb});
             b.inputs.push_back({x, as_bytes(normal((size_t) K * N, 1.0f, 11 + (unsigned) N))});
+            b.outputs = {y};
+            return b;
+        });
+    }
+}
+
+// MUL_MAT_ID: a mixture-of-experts projection for one token, a few, and a prompt (many pairs take the batched path), with
+// src1 broadcast over the slots (ne11 = 1, the gate/up form) and per-slot (ne11 = n_used, the down form); one expert unused
+static void suite_mul_mat_id() {
+    const int64_t n_expert = 8, n_used = 2, K = 2048, M = 1024 + 64;
+    for (ggml_type type : {GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, GGML_TYPE_Q8_0}) for (int64_t n_tok : {1, 7, 64, 512}) for (int per_slot = 0; per_slot < 2; ++per_slot) {
+        run_case(std::string("mul_mat_id.") + ggml_type_name(type) + ".tok" + std::to_string(n_tok) + (per_slot ? ".per_slot" : ".broadcast"), [=](ggml_context * ctx) {
+            Built b;
+            ggml_tensor * as = ggml_new_tensor_3d(ctx, type, K, M, n_expert);
+            ggml_tensor * x = ggml_new_tensor_3d(ctx, GGML_TYPE_F32, K, per_slot ? n_used : 1, n_tok);
+            ggml_tensor * ids = ggml_new_tensor_2d(ctx, GGML_TYPE_I32, n_used, n_tok);
+            ggml_tensor * y = ggml_mul_mat_id(ctx, as, x, ids);
+            b.graph = ggml_new_graph(ctx);
+            ggml_build_forward_expand(b.graph, y);
+            b.inputs.push_back({as, quantized(type, K, M * n_expert, 7)});
+            b.inputs.push_back({x, as_bytes(normal((size_t) K * (per_slot ? n_used : 1) * n_tok, 1.0f, 11 + (unsigned) n_tok))});
+            std::vector<int32_t> idv((size_t) n_used * n_tok);
+            std::mt19937 rng(5 + (unsigned) n_tok);
+            for (int64_t t = 0; t < n_tok; ++t) {                       // two different experts per token, expert 7 never
+                const int a = (int) (rng() % 7), c = (a + 1 + (int) (rng() % 6)) % 7;
+                idv[(size_t) t * n_used] = a; idv[(size_t) t * n_used + 1] = c;
+            }
+            std::vector<uint8_t> ib(idv.size() * 4);
+            memcpy(ib.data(), idv.data(), ib.size());
+            b.inputs.push_back({ids, ib});
             b.outputs = {y};
             return b;
         });
@@ -339,6 +378,7 @@ static void suite_split(ggml_backend_dev_t dev) {
 }
 
 int main(int argc, char ** argv) {
+    ggml_time_init();
     if (argc < 3) { fprintf(stderr, "usage: %s DEVICE SUITE [N_THREADS]\n", argv[0]); return 2; }
     ggml_backend_load_all();
     ggml_backend_dev_t cpu_dev = ggml_backend_dev_by_type(GGML_BACKEND_DEVICE_TYPE_CPU), dev = ggml_backend_dev_by_name(argv[1]);
@@ -356,6 +396,7 @@ int main(int argc, char ** argv) {
     else if (suite == "split") suite_split(dev);
     else if (suite == "attn_chain") suite_attn_chain();
     else if (suite == "mul_mat_f16") suite_mul_mat_f16();
+    else if (suite == "mul_mat_id") suite_mul_mat_id();
     else { fprintf(stderr, "unknown suite %s\n", argv[2]); return 2; }
     ggml_backend_free(g_dev); ggml_backend_free(g_cpu);
     return g_fail;

@@ -80,3 +80,12 @@ def test_mul_mat_f16_bf16_weights():
     assert len(cases) == 14, sorted(cases)
     bad = {k: v for k, v in cases.items() if v[0] > NMSE}
     assert not bad, bad
+
+
+def test_mul_mat_id_single_tokens_and_prompts():
+    """MUL_MAT_ID with 8 experts, 2 used per token, for 1, 7, 64 and 512 tokens (2 to 1024 pairs: the per-pair mat-vec and the
+    batched tensor-core path), activations broadcast over the slots and per slot, Q4_K / Q6_K / Q8_0 experts."""
+    cases = run_suite("mul_mat_id")
+    assert len(cases) == 3 * 4 * 2, sorted(cases)
+    bad = {k: v for k, v in cases.items() if v[0] > NMSE}
+    assert not bad, bad

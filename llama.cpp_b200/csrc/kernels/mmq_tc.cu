@@ -685,9 +685,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const TcParams p,
 }
 
 bool mmq_tc_supported(int type, int64_t M, int64_t N, int64_t K) {
-    (void) M;
     if (!mmvq_type_supported(type)) return false;
-    return N > 8 && K % TC_BK == 0 && K >= TC_BK;
+    // from 9 columns on; for large matrices already from 6 (measured: the dp4a mat-vec needs about 5 us per column on a
+    // 4096 x 14336 matrix, the GEMM about 33 us for any column count up to 128)
+    const bool wide_enough = N > 8 || (N >= 6 && M * K >= (int64_t) 32 << 20);
+    return wide_enough && K % TC_BK == 0 && K >= TC_BK;
 }
 size_t mmq_tc_workspace_bytes(int64_t N, int64_t K) { return (size_t) N * K * 2 + 256; }
 // the fast dequantizers read headers / nibble runs with aligned vector loads

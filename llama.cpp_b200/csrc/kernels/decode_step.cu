@@ -125,7 +125,8 @@ __device__ __forceinline__ void ds_give_up(const DsParams & p, DsMisc * misc, in
 __device__ __forceinline__ void ds_grid_barrier(const DsParams & p, DsMisc * misc, unsigned target) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence();
+        // The release is cumulative: what the other threads of the CTA wrote before the bar.sync above happens before it,
+        // and the acquiring load below orders the next phase's reads after the other CTAs' releases.  No separate fences.
         ds_red_release(&p.sync[0], 1u);
         if (!misc->dead) {
             int spins = 0;
@@ -134,7 +135,6 @@ __device__ __forceinline__ void ds_grid_barrier(const DsParams & p, DsMisc * mis
                 if ((spins & 255) == 0 && ds_ld_acquire(&p.sync[2])) { misc->dead = 1; break; }
             }
         }
-        __threadfence();
     }
     __syncthreads();
 }

@@ -57,6 +57,11 @@ struct Block {
     const ggml_tensor * add = nullptr, * rn = nullptr, * mu = nullptr;
     const ggml_tensor * mm[3] = {nullptr, nullptr, nullptr};
     const ggml_tensor * rope_q = nullptr, * rope_k = nullptr, * cpy_k = nullptr, * cpy_v = nullptr, * fa = nullptr, * wo = nullptr;
+    // the attention itself: FLASH_ATTN_EXT (fa), or the chain MUL_MAT(K, Q) -> SOFT_MAX -> MUL_MAT(V^T, p) -> [PERMUTE] -> CONT that
+    // graphs without it hold (chain[]: those four nodes), on a V cache stored transposed (v_t: v_nbd bytes between its rows)
+    const ggml_tensor * att_K = nullptr, * att_V = nullptr, * att_mask = nullptr, * att_out = nullptr;
+    const ggml_tensor * chain[4] = {nullptr, nullptr, nullptr, nullptr};
+    float att_scale = 0.0f; bool v_t = false; int64_t v_nbd = 0;
     int cpy_k_idx = -1, cpy_v_idx = -1;
     const ggml_tensor * silu = nullptr, * mul3 = nullptr, * down = nullptr;
 };
@@ -158,7 +163,8 @@ struct Matcher {
             const ggml_tensor * mm = b.mm[i];
             if (const ggml_tensor * r = sole_user(mm, GGML_OP_ROPE)) {
                 if (root_of(r->src[0]) != mm) return no(__LINE__);
-                if (sole_user(r, GGML_OP_FLASH_ATTN_EXT)) { q = mm; b.rope_q = r; }
+                const ggml_tensor * qk = sole_user(r, GGML_OP_MUL_MAT);              // (the score product of a graph without FLASH_ATTN_EXT)
+                if (sole_user(r, GGML_OP_FLASH_ATTN_EXT) || (qk && root_of(qk->src[1]) == r && qk->src[0]->type == GGML_TYPE_F16)) { q = mm; b.rope_q = r; }
                 else if (sole_user(r, GGML_OP_CPY))       { k = mm; b.rope_k = r; }
                 else return no(__LINE__);
             } else if (sole_user(mm, GGML_OP_CPY)) v = mm;
@@ -185,22 +191,58 @@ struct Matcher {
             return out->type == GGML_TYPE_F16 && t_contiguous(out) && out->view_src && out->view_src->data && out->view_src->op == GGML_OP_NONE &&
                    t_nelements(out) == from->ne[0] * from->ne[1] * from->ne[2] && ((uintptr_t) out->data & 3) == 0;
         };
-        if (!store_ok(b.cpy_k, rk) || !store_ok(b.cpy_v, v)) return no(__LINE__);
+        // the V row of the token: stored as a row, or (cache kept transposed) as a column of [n_ctx][n_embd_v] with stride nb[1]
+        auto store_t_ok = [&](const ggml_tensor * c, const ggml_tensor * from) {
+            if (!c || root_of(c->src[0]) != from || !c->src[1]) return false;
+            const ggml_tensor * out = c->src[1];
+            return out->type == GGML_TYPE_F16 && out->ne[0] == 1 && out->ne[1] == from->ne[0] && out->ne[2] == 1 && out->ne[3] == 1 && out->nb[0] == 2 &&
+                   out->nb[1] % 8 == 0 && out->view_src && out->view_src->data && out->view_src->op == GGML_OP_NONE && ((uintptr_t) out->data & 1) == 0;
+        };
+        if (!store_ok(b.cpy_k, rk)) return no(__LINE__);
+        if (store_t_ok(b.cpy_v, v)) { b.v_t = true; b.v_nbd = (int64_t) b.cpy_v->src[1]->nb[1]; }
+        else if (!store_ok(b.cpy_v, v)) return no(__LINE__);
         b.cpy_k_idx = idx(b.cpy_k); b.cpy_v_idx = idx(b.cpy_v);
 
-        const ggml_tensor * fa = sole_user(rq, GGML_OP_FLASH_ATTN_EXT);
-        if (!fa || root_of(fa->src[0]) != rq || fa->type != GGML_TYPE_F32 || !t_contiguous(fa)) return no(__LINE__);
-        const ggml_tensor * K = fa->src[1], * V = fa->src[2], * mask = fa->src[3];
-        if (!K || !V || K->type != GGML_TYPE_F16 || V->type != GGML_TYPE_F16 || K->nb[0] != 2 || V->nb[0] != 2) return no(__LINE__);
-        if (K->ne[0] != hd || V->ne[0] != hd || K->ne[1] != V->ne[1] || K->ne[2] != rk->ne[1] || V->ne[2] != K->ne[2] || K->ne[3] != 1 || V->ne[3] != 1) return no(__LINE__);
+        const ggml_tensor * K = nullptr, * V = nullptr, * mask = nullptr, * out = nullptr;
+        if (const ggml_tensor * fa = sole_user(rq, GGML_OP_FLASH_ATTN_EXT)) {
+            if (b.v_t || root_of(fa->src[0]) != rq || fa->type != GGML_TYPE_F32 || !t_contiguous(fa)) return no(__LINE__);
+            if (fa->src[0]->ne[1] != 1 || fa->src[0]->ne[2] != rq->ne[1] || fa->src[0]->ne[3] != 1) return no(__LINE__);
+            if (op_param_f32(fa, 1) != 0.0f || op_param_f32(fa, 2) != 0.0f) return no(__LINE__);   // no ALiBi, no soft-capping
+            K = fa->src[1]; V = fa->src[2]; mask = fa->src[3]; out = fa;
+            b.fa = fa; b.att_scale = op_param_f32(fa, 0);
+            if (!V || V->nb[0] != 2 || V->ne[0] != hd) return no(__LINE__);
+        } else {
+            const ggml_tensor * kq = sole_user(rq, GGML_OP_MUL_MAT);
+            if (!kq || !b.v_t || kq->type != GGML_TYPE_F32 || root_of(kq->src[1]) != rq) return no(__LINE__);
+            const ggml_tensor * qv = kq->src[1];                                  // [hd, 1, n_head]: the rotated row, permuted
+            if (qv->ne[0] != hd || qv->ne[1] != 1 || qv->ne[2] != rq->ne[1] || qv->ne[3] != 1 || qv->nb[0] != 4 || (int64_t) qv->nb[2] != hd * 4) return no(__LINE__);
+            const ggml_tensor * sm = sole_user(kq, GGML_OP_SOFT_MAX);
+            if (!sm || sm->src[0] != kq || op_param_f32(sm, 1) != 0.0f) return no(__LINE__);
+            const ggml_tensor * kqv = sole_user(sm, GGML_OP_MUL_MAT);
+            if (!kqv || kqv->src[1] != sm || kqv->type != GGML_TYPE_F32) return no(__LINE__);
+            const ggml_tensor * cont = sole_user(kqv, GGML_OP_CONT);
+            if (!cont || root_of(cont->src[0]) != kqv || cont->type != GGML_TYPE_F32 || !t_contiguous(cont) || t_nelements(cont) != hd * rq->ne[1]) return no(__LINE__);
+            K = kq->src[0]; V = kqv->src[0]; mask = sm->src[1]; out = cont;
+            // V^T [n_kv, hd, n_head_kv] on the transposed cache; the result [hd, 1, n_head] is read through a permutation that
+            // leaves a single query's memory order alone
+            if (!V || V->type != GGML_TYPE_F16 || V->nb[0] != 2 || V->ne[1] != hd || (int64_t) V->nb[1] != b.v_nbd || (int64_t) V->nb[2] != hd * b.v_nbd) return no(__LINE__);
+            if (kqv->ne[0] != hd || kqv->ne[1] != 1 || kqv->ne[2] != rq->ne[1]) return no(__LINE__);
+            b.chain[0] = kq; b.chain[1] = sm; b.chain[2] = kqv; b.chain[3] = cont;
+            b.att_scale = op_param_f32(sm, 0);
+        }
+        const int64_t n_kv = K ? K->ne[1] : 0;
+        if (!K || K->type != GGML_TYPE_F16 || V->type != GGML_TYPE_F16 || K->nb[0] != 2) return no(__LINE__);
+        if (K->ne[0] != hd || (b.v_t ? V->ne[0] : V->ne[1]) != n_kv || K->ne[2] != rk->ne[1] || V->ne[2] != K->ne[2] || K->ne[3] != 1 || V->ne[3] != 1) return no(__LINE__);
         if (root_of(K) != b.cpy_k->src[1]->view_src || root_of(V) != b.cpy_v->src[1]->view_src) return no(__LINE__);
         auto al16 = [](const ggml_tensor * t) { return ((uintptr_t) t->data & 15) == 0 && (t->nb[1] & 15) == 0 && (t->nb[2] & 15) == 0; };
-        if (!al16(K) || !al16(V) || K->ne[1] < 1 || K->ne[1] > 1 << 20) return no(__LINE__);
-        if (fa->src[0]->ne[1] != 1 || fa->src[0]->ne[2] != rq->ne[1] || fa->src[0]->ne[3] != 1) return no(__LINE__);
+        if (!al16(K) || (!b.v_t && !al16(V)) || (b.v_t && (((uintptr_t) V->data & 7) || (b.v_nbd & 7))) || n_kv < 1 || n_kv > 1 << 20) return no(__LINE__);
         if (rq->ne[1] % rk->ne[1] || rk->ne[1] > 64 || rq->ne[1] / rk->ne[1] > 16) return no(__LINE__);
-        if (mask && (mask->type != GGML_TYPE_F16 || mask->nb[0] != 2 || mask->ne[0] < K->ne[1] || root_of(mask) == nullptr)) return no(__LINE__);
-        if (op_param_f32(fa, 1) != 0.0f || op_param_f32(fa, 2) != 0.0f) return no(__LINE__);   // no ALiBi, no soft-capping
-        b.fa = fa;
+        if (mask) {
+            const bool f16 = mask->type == GGML_TYPE_F16 && mask->nb[0] == 2, f32 = mask->type == GGML_TYPE_F32 && mask->nb[0] == 4;
+            if ((!f16 && !f32) || mask->ne[0] < n_kv || root_of(mask) == nullptr) return no(__LINE__);
+        }
+        b.att_K = K; b.att_V = V; b.att_mask = mask; b.att_out = out;
+        const ggml_tensor * fa = out;
         const ggml_tensor * wo = sole_user(fa, GGML_OP_MUL_MAT);
         if (!wo || root_of(wo->src[1]) != fa || !weight_ok(wo, fa->ne[0] * fa->ne[1])) return no(__LINE__);
         b.wo = wo;
@@ -232,7 +274,8 @@ struct Matcher {
 
     // marks the nodes of block b as consumed; false if one of them is not available
     bool claim(const Block & b) {
-        const ggml_tensor * all[] = {b.add, b.rn, b.mu, b.mm[0], b.mm[1], b.mm[2], b.rope_q, b.rope_k, b.cpy_k, b.cpy_v, b.fa, b.wo, b.silu, b.mul3, b.down};
+        const ggml_tensor * all[] = {b.add, b.rn, b.mu, b.mm[0], b.mm[1], b.mm[2], b.rope_q, b.rope_k, b.cpy_k, b.cpy_v, b.fa, b.chain[0], b.chain[1], b.chain[2], b.chain[3],
+                                     b.wo, b.silu, b.mul3, b.down};
         for (const ggml_tensor * t : all) if (t && !take(t)) return no(__LINE__);
         return true;
     }
@@ -404,8 +447,9 @@ int try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i) {
             };
             o.corr0 = fmaxf(0.0f, floorf(corr_dim(beta_fast)));
             o.corr1 = fminf((float) o.n_dims - 1.0f, ceilf(corr_dim(beta_slow)));
-            {
-                const ggml_tensor * K = b.fa->src[1], * V = b.fa->src[2];
+            o.v_t = b.v_t ? 1 : 0; o.v_nbd = b.v_nbd;
+            if (!b.v_t) {
+                const ggml_tensor * K = b.att_K, * V = b.att_V;
                 const int64_t kb = (int64_t) K->ne[1] * (int64_t) K->nb[1];
                 if ((int64_t) K->nb[2] * K->ne[2] == (int64_t) K->nb[1] && (int64_t) V->nb[2] * V->ne[2] == (int64_t) V->nb[1] && K->nb[1] == V->nb[1] &&
                     kb <= ((int64_t) 8 << 20) && kb % 16 == 0) {
@@ -415,24 +459,25 @@ int try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i) {
             ops.push_back(o);
 
             DsOp a; memset(&a, 0, sizeof(a));
-            const ggml_tensor * K = b.fa->src[1], * V = b.fa->src[2], * mask = b.fa->src[3];
+            const ggml_tensor * K = b.att_K, * V = b.att_V, * mask = b.att_mask;
             a.kind = DS_OP_ATTN;
+            a.v_t = b.v_t ? 1 : 0; a.v_nbd = b.v_nbd; a.mask_f32 = mask && mask->type == GGML_TYPE_F32 ? 1 : 0;
             a.q = o.q_rope;
             a.k = (const char *) K->data; a.k_nb1 = (int64_t) K->nb[1]; a.k_nb2 = (int64_t) K->nb[2];
             a.v = (const char *) V->data; a.v_nb1 = (int64_t) V->nb[1]; a.v_nb2 = (int64_t) V->nb[2];
             a.mask = mask ? mask->data : nullptr;
             a.n_kv = (int) K->ne[1]; a.n_head = (int) rq->ne[1]; a.n_head_kv = (int) K->ne[2];
-            a.scale = op_param_f32(b.fa, 0);
+            a.scale = b.att_scale;
             int slices = (a.n_kv + ctx->mega_keys_per_slice - 1) / ctx->mega_keys_per_slice;     // short contexts are latency, not bandwidth: few keys per warp
             const int max_slices = lc.sm_count / a.n_head_kv;
             if (slices > max_slices) slices = max_slices;
             if (slices < 1) slices = 1;
-            a.n_slices = slices; a.kv_per_slice = (a.n_kv + slices - 1) / slices;
+            a.n_slices = slices; a.kv_per_slice = ((a.n_kv + slices - 1) / slices + 3) & ~3;     // (multiples of 4 keys: 8-byte runs of a transposed V row)
             a.partials = (float *) (arena + MEGA_OFF_PARTIALS); a.tickets = (unsigned *) (arena + MEGA_OFF_TICKETS);
             const size_t pn = (size_t) a.n_head_kv * slices * (size_t) (a.n_head / a.n_head_kv) * DS_PARTIAL_STRIDE * 4;
             a.consumer_merge = slices > 1 && slices <= ctx->mega_consumer_merge && slices <= DS_MAX_MERGE_SLICES;                   // few slices: the wo phase merges them while it builds its input
             if (pn > partial_need) partial_need = pn;
-            a.out = place(b.fa, vec[V_AO]);
+            a.out = place(b.att_out, vec[V_AO]);
             ops.push_back(a);
 
             DsOp c; memset(&c, 0, sizeof(c));
@@ -440,7 +485,7 @@ int try_decode_step(BackendCtx * ctx, ggml_cgraph * g, int i) {
             c.in0 = a.out;
             if (a.consumer_merge) {
                 c.in_kind = DS_IN_ATTN; c.in0 = a.partials; c.in_slices = a.n_slices; c.in_gqa = a.n_head / a.n_head_kv;
-                c.y_out = m.visible(b.fa) ? (float *) b.fa->data : nullptr;
+                c.y_out = m.visible(b.att_out) ? (float *) b.att_out->data : nullptr;
             }
             const ggml_tensor * W = b.wo->src[0];
             c.W[0] = W->data; c.type[0] = (int) W->type; c.M[0] = (int) W->ne[1]; c.w_nb1[0] = (int64_t) W->nb[1];

@@ -527,7 +527,8 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
         const char * kbase = o.k + (int64_t) hk * o.k_nb2;
         const char * vbase = o.v + (int64_t) hk * o.v_nb2;
         const int kv0 = split * o.kv_per_slice, kv1 = min(o.n_kv, kv0 + o.kv_per_slice);
-        const int per_warp = (max(kv1 - kv0, 0) + DS_WARPS - 1) / DS_WARPS;
+        int per_warp = (max(kv1 - kv0, 0) + DS_WARPS - 1) / DS_WARPS;
+        if (o.v_t) per_warp = (per_warp + 3) & ~3;                     // 8-byte aligned runs of keys in the transposed V rows
         const int kw0 = kv0 + warp * per_warp, kw1 = min(kv1, kw0 + per_warp);
         const int nkeys = max(kw1 - kw0, 0);
         float * part = o.partials + ((int64_t) hk * o.n_slices + split) * gqa * DS_PSTRIDE;
@@ -564,13 +565,19 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
                         const char * kr = kbase + (int64_t) (kw0 + kl) * o.k_nb1;
                         kreg[u][0] = __ldcg((const uint4 *) (kr + sub * 16));
                         kreg[u][1] = __ldcg((const uint4 *) (kr + (8 + sub) * 16));
-                        if (mrow) mval[u] = __half2float(__ldg(mrow + kw0 + kl));
+                        if (mrow) mval[u] = o.mask_f32 ? __ldg((const float *) o.mask + kw0 + kl) : __half2float(__ldg(mrow + kw0 + kl));
                     }
                 }
+                if (o.v_t) {
+                    // transposed cache: vreg[i] = the chunk's four keys of head-size row lane * 4 + i
 #pragma unroll
-                for (int t = 0; t < CH; ++t) {
-                    const int kl = min(kb + t, nkeys - 1);
-                    vreg[t] = __ldcg((const uint2 *) (vbase + (int64_t) (kw0 + kl) * o.v_nb1 + lane * 8));
+                    for (int i = 0; i < DPL; ++i) vreg[i] = __ldcg((const uint2 *) (vbase + (int64_t) (lane * DPL + i) * o.v_nbd + (int64_t) (kw0 + kb) * 2));
+                } else {
+#pragma unroll
+                    for (int t = 0; t < CH; ++t) {
+                        const int kl = min(kb + t, nkeys - 1);
+                        vreg[t] = __ldcg((const uint2 *) (vbase + (int64_t) (kw0 + kl) * o.v_nb1 + lane * 8));
+                    }
                 }
                 float cmax[RT];
 #pragma unroll
@@ -640,10 +647,16 @@ __device__ __forceinline__ void ds_attention(const DsOp & o, uint8_t * scratch, 
                     for (int i = 0; i < DPL; ++i) oacc[rr][i] *= fac[rr];
 #pragma unroll
                 for (int t = 0; t < CH; ++t) {
-                    if (t < nk) {
+                    if (t < nk) {                                // (keys past the chunk's end are not touched: the cache row may hold anything there)
                         const float4 pv = *(const float4 *) (ps + t * RT);
-                        const float2 a = __half22float2(*(const __half2 *) &vreg[t].x), b2 = __half22float2(*(const __half2 *) &vreg[t].y);
-                        const float vf[4] = {a.x, a.y, b2.x, b2.y};
+                        float vf[4];
+                        if (o.v_t) {
+#pragma unroll
+                            for (int i = 0; i < DPL; ++i) vf[i] = __half2float(((const __half *) &vreg[i])[t]);
+                        } else {
+                            const float2 a = __half22float2(*(const __half2 *) &vreg[t].x), b2 = __half22float2(*(const __half2 *) &vreg[t].y);
+                            vf[0] = a.x; vf[1] = a.y; vf[2] = b2.x; vf[3] = b2.y;
+                        }
                         const float pr[RT] = {pv.x, pv.y, pv.z, pv.w};
 #pragma unroll
                         for (int rr = 0; rr < RT; ++rr)
@@ -855,7 +868,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
                             const uint32_t row0 = 2 * lg;
                             if (dst) { dst[row0] = acc0; dst[row0 + 1] = acc1; }
                             if (mat == 2) {
-                                ((__half2 *) misc->vc)[lg] = __floats2half2_rn(acc0, acc1);
+                                if (o.v_t) {                    // transposed cache: value j of the row is element [j][token]
+                                    char * vb = (char *) misc->vc + (int64_t) row0 * o.v_nbd;
+                                    *(__half *) vb = __float2half_rn(acc0);
+                                    *(__half *) (vb + o.v_nbd) = __float2half_rn(acc1);
+                                } else ((__half2 *) misc->vc)[lg] = __floats2half2_rn(acc0, acc1);
                             } else {
                                 const int ip = (int) (row0 % (uint32_t) o.head_dim) >> 1;
                                 float o0 = acc0, o1 = acc1;

@@ -201,6 +201,8 @@ struct alignas(16) DsOp {
     float * out;                                 // [n_head][128]
     int n_slices, kv_per_slice;
     int consumer_merge;                          // the slices are merged by the input stage of the next phase (DS_IN_ATTN), not here
+    // both kinds: the V cache is kept transposed (graphs without FLASH_ATTN_EXT): v_nbd bytes between its head-size rows; F32 mask
+    int v_t, mask_f32; int64_t v_nbd;
 };
 static constexpr int DS_MAX_MERGE_SLICES = 16;   // most KV slices the input stage of the next phase merges (consumer_merge)
 static constexpr int DS_PARTIAL_STRIDE = 132;    // floats per (KV head, slice, query row) partial: O[128], max, sum, padding

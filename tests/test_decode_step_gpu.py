@@ -96,9 +96,11 @@ def test_decode_step_gqa8(b200, oracle):
             cpu.close()
 
 
-def test_libllama_graph_takes_the_decode_step(tmp_path, b200):
+@pytest.mark.parametrize("flash_attn", ["1", "0"])
+def test_libllama_graph_takes_the_decode_step(tmp_path, b200, flash_attn):
     """libllama's own graph (the reference's builder, allocator and scheduler) is recognised: the plugin reports
-    persistent launches, and the logits equal those of the per-node path."""
+    persistent launches, and the logits equal those of the per-node path.  With and without FLASH_ATTN_EXT in the graph
+    (without it: MUL_MAT / SOFT_MAX / MUL_MAT on a V cache kept transposed, an F32 mask)."""
     if not (REF / "llama-logits").exists():
         pytest.skip("oracle/_ref/llama-logits not built (make -f oracle/ref.mk tools)")
     from llama_cpp_b200 import gguf_synth
@@ -108,7 +110,7 @@ def test_libllama_graph_takes_the_decode_step(tmp_path, b200):
     for mega in ("0", "1"):
         env = dict(os.environ, GGML_BACKEND_PATH=str(ROOT / "llama.cpp_b200" / "lib" / "libggml-b200.so"), GGML_B200_MEGA=mega, GGML_B200_VERBOSE="1")
         out = tmp_path / f"logits{mega}.bin"
-        r = subprocess.run([str(REF / "llama-logits"), str(model), str(out), "99", "37", "6", "5", "1"], cwd=REF, env=env,
+        r = subprocess.run([str(REF / "llama-logits"), str(model), str(out), "99", "37", "6", "5", flash_attn], cwd=REF, env=env,
                            capture_output=True, text=True, timeout=900)
         assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
         outs[mega] = (np.fromfile(out, dtype=np.float32).reshape(7, -1), r.stderr)

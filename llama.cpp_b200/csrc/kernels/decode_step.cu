@@ -139,7 +139,7 @@ __device__ __forceinline__ void ds_grid_barrier(const DsParams & p, DsMisc * mis
     __syncthreads();
 }
 
-__device__ __forceinline__ int ds_blk_bytes(int type) { return type == T_Q4_K ? 144 : (type == T_Q5_K ? 176 : 210); }
+__device__ __forceinline__ int ds_blk_bytes(int type) { return (type == T_Q4_K || type == T_Q4_0) ? 144 : (type == T_Q5_K ? 176 : (type == T_Q8_0 ? 272 : 210)); }
 
 // ---------------------------------------------------------------------------
 // dot products of one ring slot (a run of super-blocks of one weight row) with the activation blocks
@@ -203,6 +203,59 @@ __device__ __forceinline__ float ds_dot_blk(const uint8_t * blk, const uint8_t *
         accM += ds.y * (float) (mnw & 0xff) + ds.w * (float) ((mnw >> 8) & 0xff);
     }
     return dm.x * (accE + (T == T_Q5_K ? 1.0f : 0.0625f) * accO) - dm.y * accM;
+}
+
+// Q4_0 / Q8_0: eight consecutive 32-value blocks (256 values, 144 / 272 bytes: 16-byte multiples) are one lane's unit, like
+// a super-block of the K types.  Inside, the 18- / 34-byte blocks sit at 2-byte aligned offsets; words are rebuilt with
+// funnel shifts whose amounts are compile-time constants once the loop over the blocks is unrolled.
+// x = d * (q - 8): dot = d * (d_a * sum(q * a) - 8 * d_a * sum(a)), the activation block carries both factors per 32 values.
+__device__ __forceinline__ float ds_dot_q4_0(const uint8_t * grp, const uint8_t * ab) {
+    uint32_t w[36];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) { const uint4 v = *(const uint4 *) (grp + 16 * i); w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w; }
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int o = 18 * j, wi = o >> 2, sh = (o & 3) * 8;            // sh is 0 (even j) or 16 (odd j)
+        const uint32_t dbits = (w[wi] >> sh) & 0xffffu;
+        uint32_t q[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) q[k] = sh == 0 ? __funnelshift_r(w[wi + k], w[wi + k + 1], 16) : w[wi + 1 + k];
+        const uint4 xa = *(const uint4 *) (ab + 32 * j), xb = *(const uint4 *) (ab + 32 * j + 16);      // values 0..15 and 16..31 of the block
+        const float2 ds = *(const float2 *) (ab + 256 + 8 * j);
+        const int xl[4] = {(int) xa.x, (int) xa.y, (int) xa.z, (int) xa.w}, xh[4] = {(int) xb.x, (int) xb.y, (int) xb.z, (int) xb.w};
+        int s0 = 0, s1 = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { s0 = ds_dp4a_us(q[k] & 0x0F0F0F0Fu, xl[k], s0); s1 = ds_dp4a_us((q[k] >> 4) & 0x0F0F0F0Fu, xh[k], s1); }
+        acc += __half2float(__ushort_as_half((unsigned short) dbits)) * (ds.x * (float) (s0 + s1) - 8.0f * ds.y);
+    }
+    return acc;
+}
+__device__ __forceinline__ float ds_dot_q8_0(const uint8_t * grp, const uint8_t * ab) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {                      // blocks 4h .. 4h+3 lie inside bytes [128 h, 128 h + 144): nine 128-bit loads
+        uint32_t w[36];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) { const uint4 v = *(const uint4 *) (grp + 128 * h + 16 * i); w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w; }
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const int j = 4 * h + jj, o = 34 * j - 128 * h, wi = o >> 2, sh = (o & 3) * 8;      // sh is 0 or 16
+            const uint32_t dbits = (w[wi] >> sh) & 0xffffu;
+            const uint4 xa = *(const uint4 *) (ab + 32 * j), xb = *(const uint4 *) (ab + 32 * j + 16);
+            const float2 ds = *(const float2 *) (ab + 256 + 8 * j);
+            const int x[8] = {(int) xa.x, (int) xa.y, (int) xa.z, (int) xa.w, (int) xb.x, (int) xb.y, (int) xb.z, (int) xb.w};
+            int s0 = 0, s1 = 0;
+#pragma unroll
+            for (int k = 0; k < 8; k += 2) {
+                const uint32_t q0 = sh == 0 ? __funnelshift_r(w[wi + k], w[wi + k + 1], 16) : w[wi + k + 1];
+                const uint32_t q1 = sh == 0 ? __funnelshift_r(w[wi + k + 1], w[wi + k + 2], 16) : w[wi + k + 2];
+                s0 = __dp4a((int) q0, x[k], s0); s1 = __dp4a((int) q1, x[k + 1], s1);
+            }
+            acc += __half2float(__ushort_as_half((unsigned short) dbits)) * ds.x * (float) (s0 + s1);
+        }
+    }
+    return acc;
 }
 
 // NW consecutive 32-bit words at a 2-byte aligned shared-memory address
@@ -839,8 +892,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
                             else if (lane < (both ? 2 * nblk : nblk)) {
                                 // `both`: lanes [0, nblk) take the first row of the group, [nblk, 2 nblk) the second
                                 const uint8_t * al = ap + ((both && lane >= nblk) ? lane - nblk : lane) * DS_ACT_STRIDE;
-                                if (type == T_Q4_K) a += ds_dot_blk<T_Q4_K>(slot + lane * 144, al);
-                                else                a += ds_dot_blk<T_Q5_K>(slot + lane * 176, al);
+                                if (type == T_Q4_K)      a += ds_dot_blk<T_Q4_K>(slot + lane * 144, al);
+                                else if (type == T_Q5_K) a += ds_dot_blk<T_Q5_K>(slot + lane * 176, al);
+                                else if (type == T_Q4_0) a += ds_dot_q4_0(slot + lane * 144, al);
+                                else                     a += ds_dot_q8_0(slot + lane * 272, al);
                             }
                             unit_done();
                         }
@@ -926,7 +981,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
 int64_t decode_step_max_k() { return DS_MAX_K; }
 
 bool decode_step_type_ok(int type, int64_t K, int64_t w_nb1, const void * W) {
-    if (type != T_Q4_K && type != T_Q5_K && type != T_Q6_K) return false;
+    if (type != T_Q4_K && type != T_Q5_K && type != T_Q6_K && type != T_Q4_0 && type != T_Q8_0) return false;
     if (K <= 0 || K > DS_MAX_K || K % 256) return false;
     if (type == T_Q6_K && K % 2048) return false;                 // runs of 8 super-blocks are the 16-byte multiples
     if (((uintptr_t) W & 15) || (w_nb1 & 15) || w_nb1 <= 0 || w_nb1 > 0xffffffffll) return false;
@@ -939,6 +994,8 @@ int decode_step_max_matvecs(int) { return (int) ((DS_SMEM_LIMIT - DS_OFF_DESC) /
 
 size_t decode_step_work_bytes(int n_ops) { return (size_t) (n_ops > 0 ? n_ops : 1) * 3 * sizeof(DsPart); }
 
+static int ds_host_blk_bytes(int type) { return (type == T_Q4_K || type == T_Q4_0) ? 144 : (type == T_Q5_K ? 176 : (type == T_Q8_0 ? 272 : 210)); }
+static int ds_host_cap(int type) { return (type == T_Q4_K || type == T_Q4_0) ? 32 : (type == T_Q5_K ? 24 : 16); }      // 256-value units per 4608-byte ring slot
 // the parts of one mat-vec phase (at most three)
 static bool ds_make_parts(const DsOp & o, int phase, uint32_t grid_warps, std::vector<DsPart> & out) {
     const bool zip = o.epilogue == DS_EP_SILU_MUL;
@@ -946,7 +1003,7 @@ static bool ds_make_parts(const DsOp & o, int phase, uint32_t grid_warps, std::v
     bool pair = o.epilogue != DS_EP_STORE;
     if (!pair) {
         pair = true;
-        for (int i = 0; i < o.nmat; ++i) if ((o.M[i] & 1) || o.type[i] == T_Q6_K || o.K / 256 > (o.type[i] == T_Q4_K ? 16 : 12)) pair = false;   // only rows that share a slot
+        for (int i = 0; i < o.nmat; ++i) if ((o.M[i] & 1) || o.type[i] == T_Q6_K || o.K / 256 > ds_host_cap(o.type[i]) / 2) pair = false;   // only rows that share a slot
     }
     if (o.nmat < 1 || o.nmat > 3 || (zip && (o.nmat != 2 || o.M[0] != o.M[1]))) return false;
     uint32_t g = 0;
@@ -955,8 +1012,8 @@ static bool ds_make_parts(const DsOp & o, int phase, uint32_t grid_warps, std::v
         if (!decode_step_type_ok(type, o.K, o.w_nb1[i], o.W[i]) || o.M[i] <= 0) return false;
         if (zip && (!decode_step_type_ok(o.type[1], o.K, o.w_nb1[1], o.W[1]) || o.type[1] != type || o.w_nb1[1] != o.w_nb1[0])) return false;
         if (pair && !zip && (o.M[i] & 1)) return false;
-        const int nblk = o.K / 256, bb = type == T_Q4_K ? 144 : (type == T_Q5_K ? 176 : 210);
-        const int cap = type == T_Q4_K ? 32 : (type == T_Q5_K ? 24 : 16);       // super-blocks per ring slot
+        const int nblk = o.K / 256, bb = ds_host_blk_bytes(type);
+        const int cap = ds_host_cap(type);                                      // super-blocks per ring slot
         const int nseg = (nblk + cap - 1) / cap;
         DsPart P; memset(&P, 0, sizeof(P));
         P.W0 = (uint64_t) (uintptr_t) o.W[i]; P.W1 = zip ? (uint64_t) (uintptr_t) o.W[1] : 0;
@@ -967,7 +1024,7 @@ static bool ds_make_parts(const DsOp & o, int phase, uint32_t grid_warps, std::v
         P.seg_blk = (uint8_t) (nseg > 1 ? cap : nblk); P.last_blk = (uint8_t) (nblk - (nseg - 1) * cap);
         P.seg_b = (uint16_t) (P.seg_blk * bb); P.last_b = (uint16_t) (P.last_blk * bb);
         // short rows of the one-lane-per-block types: both rows of a pair share a ring slot
-        const bool both = pair && type != T_Q6_K && nblk <= (type == T_Q4_K ? 16 : 12);
+        const bool both = pair && type != T_Q6_K && nblk <= cap / 2;
         P.mode = (uint8_t) ((zip ? 1 : 0) | (pair ? 2 : 0) | (both ? 4 : 0));
         P.mat = (uint8_t) i; P.phase = (uint16_t) phase;
         out.push_back(P);

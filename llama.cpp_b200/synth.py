@@ -1,5 +1,5 @@
 """Synthetic model data: random-init weights of a Llama architecture written as valid
-ggml quant blocks (Q4_K, Q6_K) or F32, generated with torch on whatever device is given.
+ggml quant blocks (Q4_K, Q5_K, Q6_K, Q4_0, Q8_0) or F32, generated with torch on whatever device is given.
 
 This is an input generator for benchmarks and tests, not part of the compute path.  The
 quantizers here are plain min/max (Q4_K) and abs-max (Q6_K) rounding to the block formats
@@ -104,12 +104,45 @@ def quantize_q6_K(x: torch.Tensor) -> torch.Tensor:
     return out.reshape(R, nb * 210)
 
 
-QUANTIZERS = {12: quantize_q4_K, 13: quantize_q5_K, 14: quantize_q6_K}
+def quantize_q4_0(x: torch.Tensor) -> torch.Tensor:
+    """x float32 [rows, K] (K % 32 == 0) -> uint8 [rows, K/32*18]: d = (value of largest magnitude) / -8, q = x / d + 8
+    in [0, 15], value l in the low nibble of qs[l], value l + 16 in the high one (ggml/src/ggml-quants.c:67-100)."""
+    R, K = x.shape
+    nb = K // 32
+    xb = x.reshape(R, nb, 32)
+    idx = xb.abs().argmax(-1, keepdim=True)
+    d = torch.gather(xb, -1, idx) / -8.0
+    d16 = _f16_round(d)
+    inv = torch.where(d != 0, 1.0 / torch.where(d != 0, d, torch.ones_like(d)), torch.zeros_like(d))
+    q = torch.floor(xb * inv + 8.5).clamp(0, 15).to(torch.uint8)
+    out = torch.empty(R, nb, 18, dtype=torch.uint8, device=x.device)
+    out[..., 0:2] = d16.view(torch.uint8).reshape(R, nb, 2)
+    out[..., 2:18] = q[..., 0:16] | (q[..., 16:32] << 4)
+    return out.reshape(R, nb * 18)
+
+
+def quantize_q8_0(x: torch.Tensor) -> torch.Tensor:
+    """x float32 [rows, K] (K % 32 == 0) -> uint8 [rows, K/32*34]: d = amax / 127, q = round(x / d)
+    (ggml/src/ggml-quants.c:204-230)."""
+    R, K = x.shape
+    nb = K // 32
+    xb = x.reshape(R, nb, 32)
+    d = xb.abs().amax(-1, keepdim=True) / 127.0
+    d16 = _f16_round(d)
+    inv = torch.where(d != 0, 1.0 / torch.where(d != 0, d, torch.ones_like(d)), torch.zeros_like(d))
+    q = torch.round(xb * inv).clamp(-127, 127).to(torch.int8)
+    out = torch.empty(R, nb, 34, dtype=torch.uint8, device=x.device)
+    out[..., 0:2] = d16.view(torch.uint8).reshape(R, nb, 2)
+    out[..., 2:34] = q.view(torch.uint8)
+    return out.reshape(R, nb * 34)
+
+
+QUANTIZERS = {2: quantize_q4_0, 8: quantize_q8_0, 12: quantize_q4_K, 13: quantize_q5_K, 14: quantize_q6_K}
 
 
 def make_tensor(ggml_type: int, ne0: int, ne1: int, seed: int, device: str | torch.device = "cpu", sigma: float = 0.02,
                 rows_per_chunk: int = 8192) -> np.ndarray:
-    """Random-init tensor [ne1 rows, ne0] as host bytes in the given ggml type (0 F32, 12 Q4_K, 13 Q5_K, 14 Q6_K).
+    """Random-init tensor [ne1 rows, ne0] as host bytes in the given ggml type (0 F32, 2 Q4_0, 8 Q8_0, 12 Q4_K, 13 Q5_K, 14 Q6_K).
     1-row F32 tensors (norm weights) are 1 + N(0, sigma)."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)

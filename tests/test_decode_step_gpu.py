@@ -96,8 +96,8 @@ def test_decode_step_gqa8(b200, oracle):
             cpu.close()
 
 
-@pytest.mark.parametrize("flash_attn", ["1", "0"])
-def test_libllama_graph_takes_the_decode_step(tmp_path, b200, flash_attn):
+@pytest.mark.parametrize("flash_attn,weight_type", [("1", None), ("0", None), ("1", 2), ("1", 8)])      # None: Q4_K_M mixture; 2 Q4_0; 8 Q8_0
+def test_libllama_graph_takes_the_decode_step(tmp_path, b200, flash_attn, weight_type):
     """libllama's own graph (the reference's builder, allocator and scheduler) is recognised: the plugin reports
     persistent launches, and the logits equal those of the per-node path.  With and without FLASH_ATTN_EXT in the graph
     (without it: MUL_MAT / SOFT_MAX / MUL_MAT on a V cache kept transposed, an F32 mask)."""
@@ -105,7 +105,7 @@ def test_libllama_graph_takes_the_decode_step(tmp_path, b200, flash_attn):
         pytest.skip("oracle/_ref/llama-logits not built (make -f oracle/ref.mk tools)")
     from llama_cpp_b200 import gguf_synth
     model = tmp_path / "m.gguf"
-    gguf_synth.write_llama_gguf(model, ARCH, device="cuda")
+    gguf_synth.write_llama_gguf(model, ARCH, device="cuda", weight_type=weight_type)
     outs = {}
     for mega in ("0", "1"):
         env = dict(os.environ, GGML_BACKEND_PATH=str(ROOT / "llama.cpp_b200" / "lib" / "libggml-b200.so"), GGML_B200_MEGA=mega, GGML_B200_VERBOSE="1")

@@ -35,7 +35,9 @@ def oracle_k_quant(oracle, qt, m, k, rng):
 # (type, K, M): one and several ring-slot segments per row, both rows of a pair in one slot, Q6_K's half-block lanes,
 # row counts that do not fill the grid evenly
 SHAPES = [("q4_K", 2048, 512), ("q4_K", 4096, 4096), ("q4_K", 14336, 1024), ("q4_K", 8192, 1000), ("q4_K", 4096, 1001),
-          ("q6_K", 2048, 512), ("q6_K", 4096, 2048), ("q6_K", 14336, 1024), ("q5_K", 4096, 1024), ("q5_K", 8192, 1024), ("q5_K", 2048, 514)]
+          ("q6_K", 2048, 512), ("q6_K", 4096, 2048), ("q6_K", 14336, 1024), ("q5_K", 4096, 1024), ("q5_K", 8192, 1024), ("q5_K", 2048, 514),
+          ("q4_0", 2048, 512), ("q4_0", 4096, 4096), ("q4_0", 14336, 1024), ("q4_0", 8192, 1001),
+          ("q8_0", 2048, 512), ("q8_0", 4096, 2048), ("q8_0", 14336, 1024), ("q8_0", 4096, 1001)]
 
 
 @pytest.mark.parametrize("qt,k,m", SHAPES)
@@ -51,7 +53,7 @@ def test_mat_vec_phase_plain(b200, oracle, qt, k, m):
     assert oracle.nmse(b200.mul_mat_q(qt, w, x[None, :])[0], got) <= 1e-5
 
 
-@pytest.mark.parametrize("qt,k,m", [("q4_K", 4096, 2048), ("q6_K", 4096, 512), ("q4_K", 8192, 512)])
+@pytest.mark.parametrize("qt,k,m", [("q4_K", 4096, 2048), ("q6_K", 4096, 512), ("q4_K", 8192, 512), ("q4_0", 4096, 1024), ("q8_0", 4096, 1024)])
 def test_mat_vec_phase_residual_and_norm(b200, oracle, qt, k, m):
     rng = np.random.default_rng(5)
     w = weights(oracle, qt, m, k, seed=4)

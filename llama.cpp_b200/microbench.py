@@ -119,13 +119,16 @@ def bench_mul_mat(pkg, torch, qtype, k, m, n, copies=None, reps=20):
     return us
 
 
-def bench_flash_attn(pkg, torch, n_kv, n_q, n_head=32, n_head_kv=8, d=128, copies=None, reps=20):
+def bench_flash_attn(pkg, torch, n_kv, n_q, n_head=32, n_head_kv=8, d=128, copies=None, reps=20, layout="token"):
     l = pkg.lib()
     kv_bytes = 2 * 2 * d * n_kv * n_head_kv
     copies = copies or max(2, int(600e6 // kv_bytes) + 1)
     # cache layout of the reference's KV views: a token's heads are adjacent (nb1 = n_head_kv * d * 2, nb2 = d * 2)
-    kc = torch.randn(copies, n_kv, n_head_kv, d, device="cuda").half()
-    vc = torch.randn(copies, n_kv, n_head_kv, d, device="cuda").half()
+    # (layout "head": each head's rows contiguous, nb1 = d * 2, nb2 = n_kv * d * 2 -- the contiguous tensors of test-backend-ops)
+    shape = (copies, n_kv, n_head_kv, d) if layout == "token" else (copies, n_head_kv, n_kv, d)
+    kc = torch.randn(*shape, device="cuda").half()
+    vc = torch.randn(*shape, device="cuda").half()
+    nb1, nb2 = (n_head_kv * d * 2, d * 2) if layout == "token" else (d * 2, n_kv * d * 2)
     q = torch.randn(n_head, n_q, d, device="cuda")
     n_pad = (n_q + 63) // 64 * 64
     mask = torch.full((n_pad, n_kv), float("-inf"), device="cuda", dtype=torch.float16)
@@ -139,15 +142,15 @@ def bench_flash_attn(pkg, torch, n_kv, n_q, n_head=32, n_head_kv=8, d=128, copie
     def run():
         s = torch.cuda.current_stream().cuda_stream
         for c in range(copies):
-            rc = l.b200_flash_attn(q.data_ptr(), d * 4, n_q * d * 4, kc[c].data_ptr(), n_head_kv * d * 2, d * 2,
-                                   vc[c].data_ptr(), n_head_kv * d * 2, d * 2, mask.data_ptr(), n_kv * 2, dst.data_ptr(),
+            rc = l.b200_flash_attn(q.data_ptr(), d * 4, n_q * d * 4, kc[c].data_ptr(), nb1, nb2,
+                                   vc[c].data_ptr(), nb1, nb2, mask.data_ptr(), n_kv * 2, dst.data_ptr(),
                                    d, n_q, n_head, n_kv, n_head_kv, d ** -0.5, 0.0, 0.0, sc.data_ptr(), sb, s)
             assert rc == 0, l.b200_last_error()
     us = _time(torch, run, reps, graph=n_q <= 8) * 1e3 / copies
     nbytes = kv_bytes + 2 * 4 * d * n_q * n_head + 2 * n_kv * n_q
     flops = 4.0 * n_head * n_q * d * n_kv
     print(f"FLASH_ATTN_EXT D={d} heads {n_head}/{n_head_kv} n_kv={n_kv:6d} n_q={n_q:4d}  {us:9.2f} us  {nbytes / us / 1e3:8.1f} GB/s"
-          f"  {flops / us / 1e6:8.1f} TFLOP/s  ({copies} copies)", flush=True)
+          f"  {flops / us / 1e6:8.1f} TFLOP/s  ({copies} copies, K/V rows by {layout})", flush=True)
     return us
 
 
@@ -179,6 +182,7 @@ def main():
     ap.add_argument("-n", type=int, default=1)
     ap.add_argument("--n-kv", type=int, default=4096)
     ap.add_argument("--n-q", type=int, default=1)
+    ap.add_argument("--kv-layout", default="token", choices=["token", "head"], help="flash_attn: K/V rows of one token adjacent (the cache views of libllama) or of one head")
     ap.add_argument("--copies", type=int, default=None)
     ap.add_argument("--reps", type=int, default=20)
     a = ap.parse_args()
@@ -202,7 +206,7 @@ def main():
     elif a.op == "mul_mat":
         bench_mul_mat(pkg, torch, a.type, a.k, a.m, a.n, a.copies, a.reps)
     elif a.op == "flash_attn":
-        bench_flash_attn(pkg, torch, a.n_kv, a.n_q, copies=a.copies, reps=a.reps)
+        bench_flash_attn(pkg, torch, a.n_kv, a.n_q, copies=a.copies, reps=a.reps, layout=a.kv_layout)
     else:
         shapes = [(4096, 4096), (4096, 14336), (14336, 4096)]
         for n in (1, 8, 32, 128, 512):

@@ -107,6 +107,22 @@ def test_mul_mat_llama_shapes_prefill(b200, oracle, golden, qt, k, m, n):
     assert oracle.nmse(alone[0], got[cols[0]]) <= NMSE_MM
 
 
+@pytest.mark.parametrize("qt,k,m", [("q4_K", 2048, 300), ("q8_0", 1024, 77), ("q4_K", 4096, 14336), ("q8_0", 4096, 14336)])
+@pytest.mark.parametrize("n", [2, 5, 8, 13, 16, 24, 32])
+def test_mul_mat_small_batches(b200, oracle, golden, qt, k, m, n):
+    """2 .. 32 activation columns (the mat-vec kernels up to 8, the tensor-core GEMM with a mostly empty token tile above):
+    ragged row counts, column counts that do not fill a tile; against the oracle and the one-column path of the library."""
+    w = quantized_weights(oracle, golden, qt, m, k, seed=7)
+    x = np.random.default_rng(30 + n).standard_normal((n, k)).astype(np.float32)
+    got = b200.mul_mat_q(qt, w, x)
+    assert got.shape == (n, m) and np.isfinite(got).all()
+    rows = np.arange(m) if m <= 300 else np.random.default_rng(6).choice(m, 64, replace=False)
+    assert oracle.nmse(oracle.mul_mat(qt, w[rows], x), got[:, rows]) <= NMSE_MM
+    # a column does not depend on its neighbours (the GEMM path dequantizes to F16, the mat-vec multiplies int8: same tolerance)
+    for c in (0, n - 1):
+        assert oracle.nmse(b200.mul_mat_q(qt, w, x[c:c + 1])[0], got[c]) <= NMSE_MM
+
+
 @pytest.mark.parametrize("qt", ["q4_K", "q6_K", "q8_0"])
 def test_mul_mat_vocab_shape(b200, oracle, golden, qt):
     """[K=4096, M=128256], the output matrix: one column, oracle on a sample of rows incl. the first and last."""

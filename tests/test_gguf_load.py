@@ -123,6 +123,38 @@ def _logits(m):
     return [m.decode(toks[:20], 0).copy(), m.decode(toks[20:], 20).copy()]
 
 
+
+@pytest.mark.parametrize("weight_type,file_type", [(2, 2), (8, 7)])           # Q4_0, Q8_0
+def test_single_type_files(b200, oracle, tmp_path, weight_type, file_type):
+    """Files with every matrix in one simple type (what `llama-quantize ... Q4_0 / Q8_0` leaves, output.weight in Q6_K for
+    Q4_0): types and sizes as the reader sees them, and the model loads and decodes on the reference CPU backend with the
+    logits of the same weights stored as F32 (the blocks' decoded values) within the activation-quantization error."""
+    from llama_cpp_b200 import gguf, gguf_synth, llama
+    path = tmp_path / "m.gguf"
+    gguf_synth.write_llama_gguf(path, TINY, seed_base=90, weight_type=weight_type)
+    with gguf.GGUF(path) as g:
+        assert g.get_u32("general.file_type") == file_type
+        for t in g.tensors():
+            one_d = len(t["ne"]) < 2 or t["ne"][1] == 1
+            want = 0 if one_d else (14 if (t["name"] == "output.weight" and weight_type == 2) else weight_type)
+            assert t["type"] == want, t
+            assert t["nbytes"] == gguf_synth.row_bytes(want, t["ne"][0]) * (1 if one_d else t["ne"][1])
+    if not oracle.ref_available():
+        pytest.skip("reference build (oracle/_ref) not present")
+    reg = oracle.ref_cpu_backend_reg()
+    names = {0: "f32", 2: "q4_0", 8: "q8_0", 14: "q6_K"}
+    exact = tmp_path / "exact.gguf"
+    gguf_synth.write_llama_gguf(exact, TINY, seed_base=90, weight_type=weight_type,
+                                dequantize=lambda ty, raw, ne0: oracle.dequantize_rows(names[ty], np.asarray(raw).reshape(-1, gguf_synth.row_bytes(ty, ne0)), ne0))
+    a = llama.Llama.from_gguf(path, n_ctx=512, n_ubatch=64, reg=reg, n_threads=2)
+    b = llama.Llama.from_gguf(exact, n_ctx=512, n_ubatch=64, reg=reg, n_threads=2)
+    try:
+        for x, y in zip(_logits(a), _logits(b)):
+            assert np.isfinite(x).all() and oracle.nmse(y, x) < 2e-3
+    finally:
+        a.close(); b.close()
+
+
 def test_load_into_driver_on_reference_cpu_backend(b200, oracle, tiny_gguf):
     if not oracle.ref_available():
         pytest.skip("reference build (oracle/_ref) not present")

@@ -177,6 +177,15 @@ static bool peer_barrier(BackendCtx * ctx) {
     return true;
 }
 
+// A few activation columns of a plain 2-D Q4_K / Q8_0 MUL_MAT go to the integer tensor-core kernel (mmq_s8.cu), not to the
+// tcgen05 GEMM; row-sliced results (several GPUs) keep their path
+static bool s8_takes(const BackendCtx * ctx, const ggml_tensor * n) {
+    const ggml_tensor * W = n->src[0], * X = n->src[1];
+    if (!W || !X || X->ne[2] != 1 || X->ne[3] != 1 || W->ne[2] != 1 || W->ne[3] != 1) return false;
+    if (!mmq_s8_shape_ok(W->type, X->ne[1], W->ne[0]) || ((uintptr_t) W->data & 15) || (W->nb[1] & 15) || (n->nb[1] & 3)) return false;
+    return ctx->row_slice_of(n) == nullptr;
+}
+
 static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_tensor * ids, ggml_tensor * const * extra = nullptr, int n_extra = 0) {
     const ggml_tensor * W = dst->src[0];
     const ggml_tensor * X = dst->src[1];
@@ -213,7 +222,7 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
     }
     const int64_t K = W->ne[0], M = W->ne[1];
     const int64_t ne11 = X->ne[1], ne12 = X->ne[2], ne13 = X->ne[3];
-    if (!ids && ctx->use_tc && mmq_tc_supported(W->type, M, ne11, K) && mmq_tc_ptr_ok(W->type, W->data, W->nb[1], X->data, X->nb[1]) &&
+    if (!ids && ctx->use_tc && !s8_takes(ctx, dst) && mmq_tc_supported(W->type, M, ne11, K) && mmq_tc_ptr_ok(W->type, W->data, W->nb[1], X->data, X->nb[1]) &&
         W->nb[2] % 16 == 0 && W->nb[3] % 16 == 0 && X->nb[2] % 8 == 0 && X->nb[3] % 8 == 0) {
         // prefill: tensor-core GEMM per 2-D slice (weights broadcast over the batch dims).  The F16 copy of the
         // activations is kept for the next mat-mul that reads the same tensor (wq/wk/wv, gate/up).
@@ -311,6 +320,12 @@ static bool run_mul_mat(BackendCtx * ctx, const ggml_tensor * dst, const ggml_te
         a.r2 = (int) (ne12 / W->ne[2]); a.r3 = (int) (ne13 / W->ne[3]);
         a.dst_nb1 = dst->nb[1]; a.dst_nb2 = dst->nb[2]; a.dst_nb3 = dst->nb[3];
         a.x_ncols = (int) ne11; a.xq_ne12 = (int) ne12;
+        if (!sliced && mmq_s8_applicable(a, ne11)) {        // a few columns at once on the integer tensor-core instruction
+            a.x_col0 = 0; a.N = (int) ne11; a.dst = (float *) dst->data;
+            RUN(launch_mmq_s8(a, ne11, lc.stream));
+            ctx->n_launches += n_extra;
+            return true;
+        }
         bool pushed = true;
         for (int64_t n0 = 0; n0 < ne11; n0 += 8) {
             a.N = (int) (ne11 - n0 < 8 ? ne11 - n0 : 8);
@@ -362,7 +377,7 @@ static void * tc_f16_out_for(BackendCtx * ctx, const ggml_cgraph * g, int from, 
         const ggml_tensor * n = g->nodes[i];
         if (n->op != GGML_OP_MUL_MAT || n->src[1] != t) continue;
         const ggml_tensor * W = n->src[0];
-        feeds = !is_float_type(W->type) && mmq_tc_supported(W->type, W->ne[1], t->ne[1], W->ne[0]) &&
+        feeds = !is_float_type(W->type) && !s8_takes(ctx, n) && mmq_tc_supported(W->type, W->ne[1], t->ne[1], W->ne[0]) &&
                 mmq_tc_ptr_ok(W->type, W->data, W->nb[1], t->data, t->nb[1]) && W->nb[2] % 16 == 0 && W->nb[3] % 16 == 0;
     }
     if (!feeds) return nullptr;
@@ -492,7 +507,7 @@ static bool tc_group_ok(const BackendCtx * ctx, const ggml_tensor * n) {
     const ggml_tensor * w = n->src[0], * x = n->src[1];
     if (!ctx->use_tc || is_float_type(w->type) || x->type != GGML_TYPE_F32 || x->ne[1] <= 8) return false;
     if (x->ne[2] != 1 || x->ne[3] != 1 || w->ne[2] != 1 || w->ne[3] != 1 || n->type != GGML_TYPE_F32 || n->nb[0] != 4) return false;
-    if (!mmq_tc_supported(w->type, w->ne[1], x->ne[1], w->ne[0]) || !mmq_tc_ptr_ok(w->type, w->data, w->nb[1], x->data, x->nb[1])) return false;
+    if (s8_takes(ctx, n) || !mmq_tc_supported(w->type, w->ne[1], x->ne[1], w->ne[0]) || !mmq_tc_ptr_ok(w->type, w->data, w->nb[1], x->data, x->nb[1])) return false;
     if (w->nb[2] % 16 || w->nb[3] % 16 || x->nb[2] % 8 || x->nb[3] % 8) return false;      // (what run_mul_mat asks of the tensor-core path)
     return !buft_is_split(w->buffer ? w->buffer->buft : nullptr);
 }

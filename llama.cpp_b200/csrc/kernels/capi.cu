@@ -115,7 +115,8 @@ API int b200_mul_mat_q(int type, const void * W, int64_t w_nb1, int64_t M, int64
     if (!aligned_to(W, 2) || (w_nb1 & 1) || !aligned_to(X, 4) || !aligned_to(dst, 4) || !aligned_to(scratch, 16))
         return fail(B200_E_BAD_ARG, "null or misaligned pointer (weights 2, X and dst 4, scratch 16 bytes)");
     LaunchCtx lc; int rc = get_ctx(stream, lc); if (rc) return rc;
-    if (mmq_tc_supported(type, M, N, K) && mmq_tc_ptr_ok(type, W, w_nb1, X, x_stride * 4)) {
+    const bool s8 = mmq_s8_shape_ok(type, N, K) && aligned_to(W, 16) && (w_nb1 & 15) == 0;      // a few columns: the integer tensor-core kernel
+    if (!s8 && mmq_tc_supported(type, M, N, K) && mmq_tc_ptr_ok(type, W, w_nb1, X, x_stride * 4)) {
         // split-K partial tiles: never more than the scratch size function allowed for, whatever this device's SM count
         LaunchCtx tc = lc;
         if (tc.sm_count > FLAT_SPLITK_SMS) tc.sm_count = FLAT_SPLITK_SMS;
@@ -131,6 +132,11 @@ API int b200_mul_mat_q(int type, const void * W, int64_t w_nb1, int64_t M, int64
     a.ne12 = 1; a.ne13 = 1; a.r2 = 1; a.r3 = 1; a.x_ncols = (int) N; a.xq_ne12 = 1;
     a.dst_nb1 = dst_stride * 4;
     a.status = lc.status; a.sm_count = lc.sm_count; a.device = lc.device; a.use_pdl = lc.use_pdl;
+    a.dst = dst;
+    if (s8 && mmq_s8_applicable(a, N)) {
+        CK(launch_mmq_s8(a, N, lc.stream));
+        return 0;
+    }
     for (int64_t n0 = 0; n0 < N; n0 += 8) {
         a.N = (int) (N - n0 < 8 ? N - n0 : 8);
         a.x_col0 = (int) n0;

@@ -76,6 +76,12 @@ cudaError_t launch_mmvq_q32(const MmvqArgs & a, cudaStream_t stream);
 // warp-staged variant for Q6_K (mmvq_q6k.cu)
 bool        mmvq_q6k_applicable(const MmvqArgs & a);
 cudaError_t launch_mmvq_q6k(const MmvqArgs & a, cudaStream_t stream);
+// 3 .. 8 columns of Q4_K (GGML_B200_MMQ_S8: 0 = off, 1 = also 2 columns and Q8_0, 9..16 = the largest column count) on the
+// integer tensor-core instruction (mmq_s8.cu): all n_cols columns from a.x_col0 on, the grouped matrices (n_extra) one launch each.
+// shape_ok: what can be told from the node alone.
+bool        mmq_s8_shape_ok(int type, int64_t n_cols, int64_t K);
+bool        mmq_s8_applicable(const MmvqArgs & a, int64_t n_cols);
+cudaError_t launch_mmq_s8(const MmvqArgs & a, int64_t n_cols, cudaStream_t stream);
 
 // ---- float mat-mul for F32/F16/BF16 weights (matmul_f.cu) ----
 // dst[i3][i2][n][m] = sum_k W[..][m][k] * X[i3][i2][n][k]; W broadcast over dims 2,3

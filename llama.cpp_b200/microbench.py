@@ -84,14 +84,14 @@ def _time(torch, run, reps, graph=True):
     return e0.elapsed_time(e1) / reps
 
 
-def bench_mul_mat(pkg, torch, qtype, k, m, n, copies=None, reps=20):
+def bench_mul_mat(pkg, torch, qtype, k, m, n, copies=None, reps=20, whole=False):
     l = pkg.lib()
     rb = int(l.b200_row_size(pkg.TYPES[qtype], k))
     copies = copies or max(2, int(600e6 // (rb * m)) + 1)
     w, rb, t = _weights(pkg, torch, qtype, k, m, copies)
     x = torch.randn(n, k, device="cuda")
     dst = torch.empty(n, m, device="cuda")
-    if n <= 8:          # decode: activations quantized once, then the mat-vec kernel alone
+    if n <= 8 and not whole:   # decode: activations quantized once, then the mat-vec kernel alone
         xq = torch.empty(int(l.b200_act_bytes(k, n)), dtype=torch.uint8, device="cuda")
         assert l.b200_quantize_act(x.data_ptr(), k, k, n, xq.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
 
@@ -101,7 +101,7 @@ def bench_mul_mat(pkg, torch, qtype, k, m, n, copies=None, reps=20):
                 rc = l.b200_mul_mat_vec_q(t, w[c].data_ptr(), rb, m, k, xq.data_ptr(), n, dst.data_ptr(), m, s)
                 assert rc == 0, l.b200_last_error()
         graph = True
-    else:               # prefill: the whole MUL_MAT (activation conversion + tensor-core GEMM)
+    else:               # the whole MUL_MAT as the graph path runs it (activation conversion + the kernel the library picks)
         sb = int(l.b200_mul_mat_q_scratch_bytes(t, m, k, n))
         sc = torch.empty(sb + 256, dtype=torch.uint8, device="cuda")
 
@@ -182,6 +182,7 @@ def main():
     ap.add_argument("-n", type=int, default=1)
     ap.add_argument("--n-kv", type=int, default=4096)
     ap.add_argument("--n-q", type=int, default=1)
+    ap.add_argument("--whole", action="store_true", help="mul_mat with N <= 8: time the whole MUL_MAT entry point (quantization + the kernel the library picks) instead of the mat-vec kernel alone")
     ap.add_argument("--kv-layout", default="token", choices=["token", "head"], help="flash_attn: K/V rows of one token adjacent (the cache views of libllama) or of one head")
     ap.add_argument("--copies", type=int, default=None)
     ap.add_argument("--reps", type=int, default=20)
@@ -204,7 +205,7 @@ def main():
     elif a.op == "load":
         bench_load(pkg, a.path, reps=min(a.reps, 3))
     elif a.op == "mul_mat":
-        bench_mul_mat(pkg, torch, a.type, a.k, a.m, a.n, a.copies, a.reps)
+        bench_mul_mat(pkg, torch, a.type, a.k, a.m, a.n, a.copies, a.reps, whole=a.whole)
     elif a.op == "flash_attn":
         bench_flash_attn(pkg, torch, a.n_kv, a.n_q, copies=a.copies, reps=a.reps, layout=a.kv_layout)
     else:

@@ -110,8 +110,9 @@ def test_mul_mat_llama_shapes_prefill(b200, oracle, golden, qt, k, m, n):
 @pytest.mark.parametrize("qt,k,m", [("q4_K", 2048, 300), ("q8_0", 1024, 77), ("q4_K", 4096, 14336), ("q8_0", 4096, 14336)])
 @pytest.mark.parametrize("n", [2, 5, 8, 13, 16, 24, 32])
 def test_mul_mat_small_batches(b200, oracle, golden, qt, k, m, n):
-    """2 .. 32 activation columns (the mat-vec kernels up to 8, the tensor-core GEMM with a mostly empty token tile above):
-    ragged row counts, column counts that do not fill a tile; against the oracle and the one-column path of the library."""
+    """2 .. 32 activation columns (mat-vec kernels, the integer tensor-core kernel for 3 .. 8 columns of Q4_K, the tcgen05
+    GEMM with a mostly empty token tile above): ragged row counts, column counts that do not fill a tile; against the
+    oracle and the one-column path of the library."""
     w = quantized_weights(oracle, golden, qt, m, k, seed=7)
     x = np.random.default_rng(30 + n).standard_normal((n, k)).astype(np.float32)
     got = b200.mul_mat_q(qt, w, x)
